@@ -1,0 +1,2 @@
+def lora_converter(model_cfg, arg, job_config):
+    raise NotImplementedError

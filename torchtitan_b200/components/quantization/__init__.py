@@ -1,0 +1,42 @@
+"""Model converters: config-tree rewrites applied before the model is built.
+
+``apply_converters(model_cfg, names, job_config)`` runs them in order; quantization
+converters must precede ``lora`` (parity: torchtitan/models/utils.py:23-42).
+"""
+
+from __future__ import annotations
+
+__all__ = ["apply_converters", "CONVERTERS", "has_quantization"]
+
+QUANT = ("mxfp8", "float8", "nvfp4")
+
+
+def _registry():
+    from .mx import mxfp8_converter
+    from .float8 import float8_converter
+    from torchtitan_b200.components.lora import lora_converter
+
+    return {"mxfp8": mxfp8_converter, "float8": float8_converter, "lora": lora_converter}
+
+
+CONVERTERS = ("mxfp8", "float8", "lora")
+
+
+def has_quantization(names) -> bool:
+    return any(n.split(":")[0] in QUANT for n in names)
+
+
+def apply_converters(model_cfg, names, job_config=None) -> None:
+    if not names:
+        return
+    reg = _registry()
+    seen_lora = False
+    for entry in names:
+        name, _, arg = entry.partition(":")
+        if name not in reg:
+            raise ValueError(f"unknown model converter '{name}' (have {sorted(reg)})")
+        if name == "lora":
+            seen_lora = True
+        elif seen_lora and name in QUANT:
+            raise ValueError("quantization converters must come before 'lora'")
+        reg[name](model_cfg, arg, job_config)

@@ -1,0 +1,159 @@
+"""Grouped-query attention with a fused QKV projection.
+
+The projection weight ``wqkv`` stacks ``[q heads | k heads | v heads]``; it is
+saved to checkpoints as ``qkv_linear.wq/wk/wv`` (parity with the key layout of
+torchtitan/models/common/attention.py:722-867).  RoPE is applied in place on the
+packed projection output, q/k/v are strided views of it, and the pre-norm is
+folded into the projection's autograd function.
+
+Masking.  ``AttentionContext`` carries what the inner kernel needs: document ids
+derived from ``positions`` (a document starts where ``positions == 0``), an
+optional sliding window, and for context parallelism the global token indices of
+this rank's queries.  (Reference: mask mods in attention.py:429-565, CP
+placements in decoder_sharding.py:263-302.)
+"""
+
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass, field
+
+import torch
+import torch.nn as nn
+
+from torchtitan_b200.ops import functional as OF
+from torchtitan_b200.parallel import tp_ops
+
+from .layers import Linear, RMSNorm, RoPE, TPContext
+from .module import InitSpec, Module, set_init
+
+__all__ = ["GQAttention", "AttentionContext", "build_attention_context"]
+
+
+@dataclass
+class AttentionContext:
+    doc_ids: torch.Tensor | None = None  # [T_local] int32, None = single document
+    q_pos: torch.Tensor | None = None  # global token index of local rows (CP)
+    cp: object | None = None  # parallel.context_parallel.CPContext
+    max_doc_len: int | None = None
+
+
+def build_attention_context(positions: torch.Tensor, *, assume_single_document: bool = False,
+                            cp=None, q_pos: torch.Tensor | None = None) -> AttentionContext:
+    """Derive document ids from ``positions`` (no host sync)."""
+    if assume_single_document:
+        return AttentionContext(None, q_pos, cp)
+    starts = (positions == 0).to(torch.int32)
+    doc_ids = torch.cumsum(starts, dim=0, dtype=torch.int32)
+    return AttentionContext(doc_ids, q_pos, cp)
+
+
+class GQAttention(Module):
+    @dataclass(kw_only=True, slots=True)
+    class Config(Module.Config):
+        dim: int = 0
+        n_heads: int = 0
+        n_kv_heads: int | None = None
+        head_dim: int | None = None
+        wqkv: Linear.Config = field(default_factory=Linear.Config)
+        wo: Linear.Config = field(default_factory=Linear.Config)
+        qk_norm: RMSNorm.Config | None = None
+        rope: RoPE.Config = field(default_factory=RoPE.Config)
+        sliding_window: int | None = None
+        use_sinks: bool = False
+        softmax_scale: float | None = None
+
+    def __init__(self, config: "GQAttention.Config", **_):
+        super().__init__(config)
+        c = config
+        self.n_heads = c.n_heads
+        self.n_kv_heads = c.n_kv_heads or c.n_heads
+        self.head_dim = c.head_dim or c.dim // c.n_heads
+        hd = self.head_dim
+        c.wqkv.in_features = c.dim
+        c.wqkv.out_features = (self.n_heads + 2 * self.n_kv_heads) * hd
+        c.wqkv.row_blocks = [self.n_heads * hd, self.n_kv_heads * hd, self.n_kv_heads * hd]
+        c.wo.in_features, c.wo.out_features = self.n_heads * hd, c.dim
+        self.wqkv = c.wqkv.build()
+        self.wo = c.wo.build()
+        self.q_norm = self.k_norm = None
+        if c.qk_norm is not None:
+            c.qk_norm.dim = hd
+            self.q_norm = c.qk_norm.build()
+            self.k_norm = c.qk_norm.build()
+        c.rope.dim = c.rope.dim or hd
+        self.rope = c.rope.build()
+        self.scale = c.softmax_scale if c.softmax_scale is not None else 1.0 / math.sqrt(hd)
+        self.window = c.sliding_window
+        self.sinks = None
+        if c.use_sinks:
+            self.sinks = nn.Parameter(torch.empty(self.n_heads))
+            set_init(self.sinks, InitSpec(kind="trunc_normal", std=0.02))
+        self.tp: TPContext | None = None
+
+    # -- parallel ----------------------------------------------------------
+    def shard_(self, tp: TPContext) -> None:
+        if self.n_kv_heads % tp.size:
+            raise ValueError(f"n_kv_heads={self.n_kv_heads} must divide by tp={tp.size}")
+        self.wqkv.shard_("colwise", tp)
+        self.wo.shard_("rowwise", tp)
+        if self.sinks is not None:
+            n = self.n_heads // tp.size
+            s = nn.Parameter(torch.empty(n, device=self.sinks.device, dtype=self.sinks.dtype))
+            s._tp_slices = (0, [(tp.rank * n, (tp.rank + 1) * n)], (self.n_heads,))
+            set_init(s, self.sinks._init_spec)
+            self.sinks = s
+        self.n_heads //= tp.size
+        self.n_kv_heads //= tp.size
+        self.tp = tp
+
+    def checkpoint_slices(self):
+        hd = self.head_dim
+        q, kv = self.n_heads * hd, self.n_kv_heads * hd
+        return {
+            "wqkv.weight": [
+                ("qkv_linear.wq.weight", 0, q),
+                ("qkv_linear.wk.weight", q, q + kv),
+                ("qkv_linear.wv.weight", q + kv, q + 2 * kv),
+            ]
+        }
+
+    # -- forward -----------------------------------------------------------
+    def forward(self, x: torch.Tensor, positions: torch.Tensor, ctx: AttentionContext | None = None,
+                norm: RMSNorm | None = None) -> torch.Tensor:
+        tp = self.tp
+        hd, hq, hkv = self.head_dim, self.n_heads, self.n_kv_heads
+        if tp is not None:
+            if norm is not None:
+                x = norm(x)
+            x = tp_ops.all_gather_rows(x, tp) if tp.sequence_parallel else tp_ops.copy_to_tp(x, tp)
+            qkv = self.wqkv(x)
+        elif norm is not None and type(self.wqkv) is Linear and norm.weight is not None and self.wqkv.bias is None:
+            qkv = OF.norm_linear(x, norm.weight, self.wqkv.weight, norm.eps)
+        else:
+            qkv = self.wqkv(norm(x) if norm is not None else x)
+        T = qkv.shape[0]
+        if self.q_norm is None:
+            qkv = self.rope.apply_packed_(qkv, positions, hq + hkv, hd)
+        qkv = qkv.view(T, hq + 2 * hkv, hd)
+        if self.q_norm is not None:
+            # QK-norm normalises each head vector before RoPE (Qwen3).
+            qn = self.q_norm(qkv[:, :hq])
+            kn = self.k_norm(qkv[:, hq:hq + hkv])
+            q = self.rope(qn, positions)
+            k = self.rope(kn, positions)
+            v = qkv[:, hq + hkv:]
+        else:
+            q, k, v = qkv[:, :hq], qkv[:, hq:hq + hkv], qkv[:, hq + hkv:]
+        ctx = ctx or AttentionContext()
+        if ctx.cp is not None:
+            from torchtitan_b200.parallel.context_parallel import cp_attention
+
+            o = cp_attention(q, k, v, ctx, scale=self.scale, window=self.window, sinks=self.sinks)
+        else:
+            o = OF.attention(q, k, v, scale=self.scale, causal=True, doc_ids=ctx.doc_ids, window=self.window,
+                             sinks=self.sinks)
+        y = self.wo(o.reshape(T, hq * hd))
+        if tp is not None:
+            return tp_ops.reduce_scatter_rows(y, tp) if tp.sequence_parallel else tp_ops.all_reduce(y, tp)
+        return y

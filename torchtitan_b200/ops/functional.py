@@ -1,0 +1,595 @@
+"""Differentiable operators used by the models.
+
+Every operator has one CUDA implementation (the in-tree sm_100a extension,
+``torch.ops.tb200``) and one plain-PyTorch implementation used for CPU tensors.
+A CUDA tensor never takes the PyTorch path: if the extension is missing the call
+raises.
+
+Memory policy.  The fused functions below are where op-level selective
+recomputation lives: ``norm_linear`` keeps only the un-normalised input and the
+per-row ``rstd`` and recomputes the normalised activations for the weight
+gradient; ``swiglu_linear`` keeps the gate/up GEMM output and recomputes the
+activation.  GEMM and attention outputs are kept.  (The reference expresses the
+same intent as a per-op save list, torchtitan/distributed/activation_checkpoint.py:31-94.)
+
+Weight gradients.  When a weight carries a ``main_grad`` attribute (set by the
+sharded-data-parallel engine, a view into the unit's flat gradient buffer) the
+linear backward writes the weight gradient straight into it and reports no
+gradient to autograd, which removes the extra zero-fill and accumulate passes
+over the gradient buffer.
+"""
+
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+
+import torch
+import torch.nn.functional as F
+
+from . import ext, reference as ref
+
+__all__ = [
+    "settings", "rms_norm", "linear", "norm_linear", "swiglu", "swiglu_linear", "rope_qk_", "rope",
+    "attention", "linear_cross_entropy", "cross_entropy_sum", "gemm_nt", "gemm_nn", "gemm_tn", "embedding",
+]
+
+
+@dataclass
+class _Settings:
+    gemm: str = "cublas"  # "cublas" | "tcgen05"
+    attention: str = "sdpa"  # "sdpa" | "native"
+    recompute: bool = True  # fused functions recompute norm / SwiGLU activations in backward
+    launches: int = 0  # count of launches of this package's own kernels
+    count_launches: bool = False
+
+
+settings = _Settings()
+
+
+def _count(n: int = 1) -> None:
+    if settings.count_launches:
+        settings.launches += n
+
+
+def _cuda(t: torch.Tensor) -> bool:
+    return t.is_cuda
+
+
+# =====================================================================
+# GEMM front-ends (bf16 in, fp32 accumulate)
+# =====================================================================
+def _tc_ok(*ts: torch.Tensor) -> bool:
+    return (
+        settings.gemm == "tcgen05"
+        and all(t.is_cuda and t.dtype == torch.bfloat16 for t in ts)
+    )
+
+
+def gemm_nt(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None = None, accumulate: bool = False) -> torch.Tensor:
+    """``a[M,K] @ b[N,K]^T``; with ``accumulate`` adds into ``out``."""
+    if _tc_ok(a, b) and ext.available() and hasattr(torch.ops.tb200, "gemm_bf16"):
+        r = _tc_gemm(a, b, 0, out, accumulate)
+        if r is not None:
+            return r
+    if out is None:
+        return torch.mm(a, b.t())
+    if accumulate:
+        return out.addmm_(a, b.t())
+    return torch.mm(a, b.t(), out=out)
+
+
+def gemm_nn(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None = None, accumulate: bool = False) -> torch.Tensor:
+    """``a[M,K] @ b[K,N]``."""
+    if _tc_ok(a, b) and ext.available() and hasattr(torch.ops.tb200, "gemm_bf16"):
+        r = _tc_gemm(a, b, 1, out, accumulate)
+        if r is not None:
+            return r
+    if out is None:
+        return torch.mm(a, b)
+    if accumulate:
+        return out.addmm_(a, b)
+    return torch.mm(a, b, out=out)
+
+
+def gemm_tn(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None = None, accumulate: bool = False) -> torch.Tensor:
+    """``a[K,M]^T @ b[K,N]`` (weight-gradient shape)."""
+    if _tc_ok(a, b) and ext.available() and hasattr(torch.ops.tb200, "gemm_bf16"):
+        r = _tc_gemm(a, b, 2, out, accumulate)
+        if r is not None:
+            return r
+    if out is None:
+        return torch.mm(a.t(), b)
+    if accumulate:
+        return out.addmm_(a.t(), b)
+    return torch.mm(a.t(), b, out=out)
+
+
+def _tc_gemm(a, b, mode, out, accumulate):
+    """Hand-written tcgen05 GEMM; returns None when the shape is not supported."""
+    if not (a.is_contiguous() and b.is_contiguous()):
+        return None
+    if mode == 0:
+        M, K = a.shape
+        N = b.shape[0]
+    elif mode == 1:
+        M, K = a.shape
+        N = b.shape[1]
+    else:
+        K, M = a.shape
+        N = b.shape[1]
+    if (K % 64) or (N % 8) or (M % 8) or K == 0:
+        return None
+    if out is None:
+        out = torch.empty(M, N, dtype=torch.bfloat16, device=a.device)
+        accumulate = False
+    elif not (out.is_contiguous() and out.dtype == torch.bfloat16):
+        return None
+    torch.ops.tb200.gemm_bf16(a, b, out, mode, accumulate)
+    _count()
+    return out
+
+
+# =====================================================================
+# RMSNorm
+# =====================================================================
+def _rms_fwd(x2, w, eps):
+    if _cuda(x2):
+        _count()
+        return ext.require().rmsnorm_fwd(x2, w, eps)
+    return ref.rms_norm_fwd(x2, w, eps)
+
+
+def _rms_bwd(dy2, x2, w, rstd):
+    if _cuda(x2):
+        _count(2 if w is not None else 1)
+        dx, dw = ext.require().rmsnorm_bwd(dy2, x2, w, rstd)
+        return dx, (dw if w is not None else None)
+    return ref.rms_norm_bwd(dy2, x2, w, rstd)
+
+
+def _deliver_wgrad(weight: torch.Tensor, dw: torch.Tensor | None):
+    """Route a weight gradient to ``main_grad`` when present; else return it for autograd."""
+    if dw is None:
+        return None
+    mg = getattr(weight, "main_grad", None)
+    if mg is None:
+        return dw.to(weight.dtype) if dw.dtype != weight.dtype else dw
+    dwv = dw.view_as(mg)
+    if getattr(weight, "_main_grad_written", False):
+        mg.add_(dwv)
+    else:
+        mg.copy_(dwv)
+        weight._main_grad_written = True
+    return None
+
+
+class _RMSNormFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, weight, eps):
+        x2 = x.reshape(-1, x.shape[-1])
+        if not x2.is_contiguous():
+            x2 = x2.contiguous()
+        y, rstd = _rms_fwd(x2, weight, eps)
+        ctx.save_for_backward(x2, weight, rstd)
+        ctx.shape = x.shape
+        return y.view(x.shape)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, weight, rstd = ctx.saved_tensors
+        dy2 = dy.reshape(x2.shape)
+        if not dy2.is_contiguous():
+            dy2 = dy2.contiguous()
+        dx, dw = _rms_bwd(dy2, x2, weight, rstd)
+        dwr = _deliver_wgrad(weight, dw) if weight is not None else None
+        return dx.view(ctx.shape), dwr, None
+
+
+def rms_norm(x: torch.Tensor, weight: torch.Tensor | None, eps: float = 1e-5) -> torch.Tensor:
+    return _RMSNormFn.apply(x, weight, eps)
+
+
+# =====================================================================
+# Linear (+ fused prologues)
+# =====================================================================
+def _wgrad(dy2: torch.Tensor, x2: torch.Tensor, weight: torch.Tensor):
+    """dW[N,K] = dy2[M,N]^T @ x2[M,K], delivered to main_grad when available."""
+    mg = getattr(weight, "main_grad", None)
+    if mg is not None and mg.dtype == dy2.dtype:
+        acc = getattr(weight, "_main_grad_written", False)
+        gemm_tn(dy2, x2, out=mg.view(weight.shape), accumulate=acc)
+        weight._main_grad_written = True
+        return None
+    dw = gemm_tn(dy2, x2)
+    return _deliver_wgrad(weight, dw)
+
+
+class _LinearFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, weight, bias):
+        x2 = x.reshape(-1, x.shape[-1])
+        y = gemm_nt(x2, weight)
+        if bias is not None:
+            y = y + bias
+        ctx.save_for_backward(x2, weight)
+        ctx.has_bias = bias is not None
+        ctx.xshape = x.shape
+        return y if x.dim() == 2 else y.view(*x.shape[:-1], weight.shape[0])
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, weight = ctx.saved_tensors
+        dy2 = dy.reshape(-1, dy.shape[-1])
+        if not dy2.is_contiguous():
+            dy2 = dy2.contiguous()
+        dx = gemm_nn(dy2, weight).view(ctx.xshape) if ctx.needs_input_grad[0] else None
+        dw = _wgrad(dy2, x2, weight) if weight.requires_grad else None
+        db = dy2.sum(dim=0) if ctx.has_bias else None
+        return dx, dw, db
+
+
+def linear(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = None) -> torch.Tensor:
+    if x.dtype != weight.dtype:
+        x = x.to(weight.dtype)
+    return _LinearFn.apply(x, weight, bias)
+
+
+class _NormLinearFn(torch.autograd.Function):
+    """``rms_norm(x) @ W^T`` keeping only ``x`` and ``rstd`` for backward."""
+
+    @staticmethod
+    def forward(ctx, x, norm_w, weight, eps):
+        x2 = x.reshape(-1, x.shape[-1])
+        xn, rstd = _rms_fwd(x2, norm_w, eps)
+        y = gemm_nt(xn, weight)
+        ctx.save_for_backward(x2, norm_w, weight, rstd)
+        ctx.eps = eps
+        ctx.xshape = x.shape
+        return y if x.dim() == 2 else y.view(*x.shape[:-1], weight.shape[0])
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, norm_w, weight, rstd = ctx.saved_tensors
+        dy2 = dy.reshape(-1, dy.shape[-1])
+        if not dy2.is_contiguous():
+            dy2 = dy2.contiguous()
+        xn, _ = _rms_fwd(x2, norm_w, ctx.eps)
+        dw = _wgrad(dy2, xn, weight) if weight.requires_grad else None
+        del xn
+        dxn = gemm_nn(dy2, weight)
+        dx, dnw = _rms_bwd(dxn, x2, norm_w, rstd)
+        dnw = _deliver_wgrad(norm_w, dnw) if norm_w is not None else None
+        return dx.view(ctx.xshape), dnw, dw, None
+
+
+def norm_linear(x: torch.Tensor, norm_weight: torch.Tensor | None, weight: torch.Tensor, eps: float) -> torch.Tensor:
+    if not settings.recompute:
+        return linear(rms_norm(x, norm_weight, eps), weight)
+    return _NormLinearFn.apply(x, norm_weight, weight, eps)
+
+
+# =====================================================================
+# SwiGLU
+# =====================================================================
+def _swiglu_fwd(gu2: torch.Tensor) -> torch.Tensor:
+    if _cuda(gu2):
+        _count()
+        return ext.require().swiglu_fwd(gu2)
+    f = gu2.shape[-1] // 2
+    return ref.swiglu_fwd(gu2[:, :f], gu2[:, f:])
+
+
+def _swiglu_bwd(gu2: torch.Tensor, da: torch.Tensor) -> torch.Tensor:
+    if _cuda(gu2):
+        _count()
+        return ext.require().swiglu_bwd(gu2, da)
+    f = gu2.shape[-1] // 2
+    dg, du = ref.swiglu_bwd(gu2[:, :f], gu2[:, f:], da)
+    return torch.cat([dg, du], dim=-1)
+
+
+class _SwiGLUFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, gu):
+        gu2 = gu.reshape(-1, gu.shape[-1])
+        ctx.save_for_backward(gu2)
+        ctx.shape = gu.shape
+        return _swiglu_fwd(gu2).view(*gu.shape[:-1], gu.shape[-1] // 2)
+
+    @staticmethod
+    def backward(ctx, da):
+        (gu2,) = ctx.saved_tensors
+        da2 = da.reshape(gu2.shape[0], -1)
+        if not da2.is_contiguous():
+            da2 = da2.contiguous()
+        return _swiglu_bwd(gu2, da2).view(ctx.shape)
+
+
+def swiglu(gate_up: torch.Tensor) -> torch.Tensor:
+    """``silu(gate) * up`` where ``gate_up[..., :F]`` is the gate and ``[..., F:]`` the up projection."""
+    return _SwiGLUFn.apply(gate_up)
+
+
+class _SwiGLULinearFn(torch.autograd.Function):
+    """``swiglu(gu) @ W^T`` keeping only ``gu``; the activation is recomputed in backward."""
+
+    @staticmethod
+    def forward(ctx, gu, weight):
+        gu2 = gu.reshape(-1, gu.shape[-1])
+        a = _swiglu_fwd(gu2)
+        y = gemm_nt(a, weight)
+        ctx.save_for_backward(gu2, weight)
+        ctx.shape = gu.shape
+        return y if gu.dim() == 2 else y.view(*gu.shape[:-1], weight.shape[0])
+
+    @staticmethod
+    def backward(ctx, dy):
+        gu2, weight = ctx.saved_tensors
+        dy2 = dy.reshape(-1, dy.shape[-1])
+        if not dy2.is_contiguous():
+            dy2 = dy2.contiguous()
+        a = _swiglu_fwd(gu2)
+        dw = _wgrad(dy2, a, weight) if weight.requires_grad else None
+        del a
+        da = gemm_nn(dy2, weight)
+        dgu = _swiglu_bwd(gu2, da)
+        return dgu.view(ctx.shape), dw
+
+
+def swiglu_linear(gate_up: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
+    if not settings.recompute:
+        return linear(swiglu(gate_up), weight)
+    return _SwiGLULinearFn.apply(gate_up, weight)
+
+
+# =====================================================================
+# RoPE
+# =====================================================================
+def _rope_inplace(x: torch.Tensor, table: torch.Tensor, positions: torch.Tensor, interleaved: bool, inverse: bool):
+    """Rotate ``x[T, H, D]`` (last dim contiguous, arbitrary row stride) in place."""
+    if _cuda(x):
+        _count()
+        ext.require().rope_(x, table, positions, interleaved, inverse)
+        return x
+    x.copy_(ref.rope_apply(x, table, positions, interleaved, inverse))
+    return x
+
+
+class _RopeFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, table, positions, interleaved):
+        ctx.save_for_backward(table, positions)
+        ctx.interleaved = interleaved
+        out = x.clone() if x.is_contiguous() else x.contiguous()
+        return _rope_inplace(out, table, positions, interleaved, False)
+
+    @staticmethod
+    def backward(ctx, dy):
+        table, positions = ctx.saved_tensors
+        d = dy.clone() if dy.is_contiguous() else dy.contiguous()
+        return _rope_inplace(d, table, positions, ctx.interleaved, True), None, None, None
+
+
+def rope(x: torch.Tensor, table: torch.Tensor, positions: torch.Tensor, interleaved: bool) -> torch.Tensor:
+    """Out-of-place RoPE on ``x[T, H, D]``."""
+    return _RopeFn.apply(x, table, positions, interleaved)
+
+
+class _RopeQKInplaceFn(torch.autograd.Function):
+    """Rotate the first ``n_rot_heads`` heads of a packed ``[T, H_total * D]`` tensor in place."""
+
+    @staticmethod
+    def forward(ctx, qkv, table, positions, interleaved, n_rot_heads, head_dim):
+        ctx.save_for_backward(table, positions)
+        ctx.interleaved = interleaved
+        ctx.n_rot, ctx.hd = n_rot_heads, head_dim
+        ctx.mark_dirty(qkv)
+        v = qkv.view(qkv.shape[0], -1, head_dim)
+        _rope_inplace(v[:, :n_rot_heads], table, positions, interleaved, False)
+        return qkv
+
+    @staticmethod
+    def backward(ctx, d):
+        table, positions = ctx.saved_tensors
+        d = d.contiguous() if not d.is_contiguous() else d.clone()
+        v = d.view(d.shape[0], -1, ctx.hd)
+        _rope_inplace(v[:, : ctx.n_rot], table, positions, ctx.interleaved, True)
+        return d, None, None, None, None, None
+
+
+def rope_qk_(qkv: torch.Tensor, table: torch.Tensor, positions: torch.Tensor, interleaved: bool, n_rot_heads: int,
+             head_dim: int):
+    """In-place RoPE on the q and k heads of a packed projection output ``[T, (Hq+2Hkv)*D]``."""
+    return _RopeQKInplaceFn.apply(qkv, table, positions, interleaved, n_rot_heads, head_dim)
+
+
+# =====================================================================
+# Attention
+# =====================================================================
+def _sdpa_causal(q, k, v, scale):
+    """Library attention (cuDNN / flash) on ``[T,H,D]`` tensors: the baseline path."""
+    qh, kh, vh = (t.transpose(0, 1).unsqueeze(0) for t in (q, k, v))
+    out = F.scaled_dot_product_attention(qh, kh, vh, is_causal=True, scale=scale, enable_gqa=(q.shape[1] != k.shape[1]))
+    return out.squeeze(0).transpose(0, 1)
+
+
+def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, scale: float | None = None, causal: bool = True,
+              doc_ids: torch.Tensor | None = None, window: int | None = None, sinks: torch.Tensor | None = None,
+              q_pos: torch.Tensor | None = None, k_pos: torch.Tensor | None = None) -> torch.Tensor:
+    """Attention over folded tokens: ``q[T,Hq,D]``, ``k/v[T,Hkv,D]`` -> ``[T,Hq,Dv]``.
+
+    Documents are separated with ``doc_ids`` (``None`` = one document).
+    """
+    if scale is None:
+        scale = 1.0 / math.sqrt(q.shape[-1])
+    plain = doc_ids is None and window is None and sinks is None and q_pos is None and k_pos is None and causal
+    if _cuda(q) and settings.attention == "native" and plain and ext.available() and hasattr(torch.ops.tb200, "flash_fwd"):
+        from .flash import flash_attention
+
+        return flash_attention(q, k, v, scale)
+    if plain and q.shape[-1] == v.shape[-1]:
+        return _sdpa_causal(q, k, v, scale)
+    return _masked_attention(q, k, v, scale, causal, doc_ids, window, sinks, q_pos, k_pos)
+
+
+def _masked_attention(q, k, v, scale, causal, doc_ids, window, sinks, q_pos, k_pos):
+    """General masks (documents, windows, sinks): dense-mask SDPA with autograd."""
+    Tq, Hq, _ = q.shape
+    Tk, Hkv, _ = k.shape
+    dev = q.device
+    qp = torch.arange(Tq, device=dev) if q_pos is None else q_pos
+    kp = torch.arange(Tk, device=dev) if k_pos is None else k_pos
+    mask = torch.ones(Tq, Tk, dtype=torch.bool, device=dev)
+    if causal:
+        mask &= qp[:, None] >= kp[None, :]
+    if window is not None and window > 0:
+        mask &= (qp[:, None] - kp[None, :]) < window
+    if doc_ids is not None:
+        qd, kd = doc_ids if isinstance(doc_ids, tuple) else (doc_ids, doc_ids)
+        mask &= qd[:, None] == kd[None, :]
+    rep = Hq // Hkv
+    qh = q.transpose(0, 1)
+    kh = k.transpose(0, 1).repeat_interleave(rep, dim=0) if rep > 1 else k.transpose(0, 1)
+    vh = v.transpose(0, 1).repeat_interleave(rep, dim=0) if rep > 1 else v.transpose(0, 1)
+    s = torch.matmul(qh.float(), kh.float().transpose(1, 2)) * scale
+    s = s.masked_fill(~mask[None], float("-inf"))
+    if sinks is not None:
+        s_ext = torch.cat([s, sinks.float()[:, None, None].expand(Hq, Tq, 1)], dim=-1)
+        p = torch.softmax(s_ext, dim=-1)[..., :-1]
+    else:
+        p = torch.softmax(s, dim=-1)
+    p = torch.nan_to_num(p, nan=0.0)
+    return torch.matmul(p, vh.float()).transpose(0, 1).to(q.dtype)
+
+
+# =====================================================================
+# Embedding
+# =====================================================================
+class _EmbeddingFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, tokens, weight):
+        ctx.save_for_backward(tokens, weight)
+        return weight.index_select(0, tokens.reshape(-1)).view(*tokens.shape, weight.shape[1])
+
+    @staticmethod
+    def backward(ctx, dy):
+        tokens, weight = ctx.saved_tensors
+        mg = getattr(weight, "main_grad", None)
+        flat = dy.reshape(-1, dy.shape[-1])
+        if mg is not None:
+            g = mg.view(weight.shape)
+            if not getattr(weight, "_main_grad_written", False):
+                g.zero_()
+                weight._main_grad_written = True
+            g.index_add_(0, tokens.reshape(-1), flat.to(g.dtype))
+            return None, None
+        dw = torch.zeros_like(weight)
+        dw.index_add_(0, tokens.reshape(-1), flat.to(dw.dtype))
+        return None, dw
+
+
+def embedding(tokens: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
+    return _EmbeddingFn.apply(tokens, weight)
+
+
+# =====================================================================
+# Cross entropy
+# =====================================================================
+def _ce_inplace(logits: torch.Tensor, labels: torch.Tensor, grad_scale: torch.Tensor, loss_acc: torch.Tensor):
+    """Turn ``logits`` into ``dlogits`` in place and add the summed loss into ``loss_acc``."""
+    if _cuda(logits):
+        _count()
+        ext.require().cross_entropy_(logits, labels, grad_scale, loss_acc)
+        return logits
+    loss, dl, _ = ref.cross_entropy_fwd_bwd(logits, labels, grad_scale)
+    loss_acc.add_(loss)
+    logits.copy_(dl)
+    return logits
+
+
+class _LinearCrossEntropyFn(torch.autograd.Function):
+    """Chunked ``lm_head`` GEMM + cross entropy with gradients produced in the forward.
+
+    Each chunk of rows computes its logits, turns them into ``dlogits`` in place
+    (scaled by ``1 / global_valid_tokens``), and immediately produces the hidden
+    and weight gradients, so the ``[T, V]`` logits never exist.  Parity with the
+    chunked loss wrapper of the reference: torchtitan/components/loss.py:501-809.
+    """
+
+    @staticmethod
+    def forward(ctx, hidden, weight, labels, inv_tokens, num_chunks):
+        h2 = hidden.reshape(-1, hidden.shape[-1])
+        lab = labels.reshape(-1)
+        T = h2.shape[0]
+        loss_acc = torch.zeros(1, dtype=torch.float32, device=h2.device)
+        need_grad = ctx.needs_input_grad[0] or ctx.needs_input_grad[1]
+        dh = torch.empty_like(h2) if need_grad else None
+        mg = getattr(weight, "main_grad", None)
+        direct = need_grad and mg is not None and mg.dtype == h2.dtype
+        dw = None
+        if need_grad and weight.requires_grad and not direct:
+            dw = torch.zeros(weight.shape, dtype=torch.float32, device=h2.device)
+        chunk = max(1, -(-T // max(1, num_chunks)))
+        scale = inv_tokens.to(torch.float32).reshape(1)
+        for s in range(0, T, chunk):
+            e = min(T, s + chunk)
+            logits = gemm_nt(h2[s:e], weight)
+            _ce_inplace(logits, lab[s:e], scale, loss_acc)
+            if need_grad:
+                gemm_nn(logits, weight, out=dh[s:e])
+                if weight.requires_grad:
+                    if direct:
+                        acc = getattr(weight, "_main_grad_written", False)
+                        gemm_tn(logits, h2[s:e], out=mg.view(weight.shape), accumulate=acc)
+                        weight._main_grad_written = True
+                    else:
+                        dw.addmm_(logits.t().float(), h2[s:e].float())
+            del logits
+        ctx.save_for_backward(dh, dw)
+        ctx.weight = weight
+        ctx.hshape = hidden.shape
+        ctx.direct = direct
+        return (loss_acc * scale).squeeze(0)
+
+    @staticmethod
+    def backward(ctx, dloss):
+        dh, dw = ctx.saved_tensors
+        weight = ctx.weight
+        # Gradients were computed for d(loss)=1; the trainer calls backward on the loss
+        # itself, so dloss is one.  A different upstream scale is applied here.
+        dhid = (dh * dloss.to(dh.dtype)).view(ctx.hshape) if dh is not None else None
+        dwr = None
+        if dw is not None:
+            dwr = _deliver_wgrad(weight, (dw * dloss).to(weight.dtype))
+        return dhid, dwr, None, None, None
+
+
+def linear_cross_entropy(hidden: torch.Tensor, weight: torch.Tensor, labels: torch.Tensor,
+                         inv_global_tokens: torch.Tensor, num_chunks: int = 8) -> torch.Tensor:
+    """``sum(CE(hidden @ W^T, labels)) * inv_global_tokens`` without materialising the logits."""
+    if hidden.dtype != weight.dtype:
+        hidden = hidden.to(weight.dtype)
+    return _LinearCrossEntropyFn.apply(hidden, weight, labels, inv_global_tokens, num_chunks)
+
+
+class _CrossEntropyFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, logits, labels):
+        l2 = logits.reshape(-1, logits.shape[-1]).clone()
+        loss_acc = torch.zeros(1, dtype=torch.float32, device=logits.device)
+        one = torch.ones(1, dtype=torch.float32, device=logits.device)
+        _ce_inplace(l2, labels.reshape(-1), one, loss_acc)
+        ctx.save_for_backward(l2)
+        ctx.shape = logits.shape
+        return loss_acc.squeeze(0)
+
+    @staticmethod
+    def backward(ctx, dloss):
+        (dl,) = ctx.saved_tensors
+        return (dl * dloss.to(dl.dtype)).view(ctx.shape), None
+
+
+def cross_entropy_sum(logits: torch.Tensor, labels: torch.Tensor) -> torch.Tensor:
+    """Sum over non-ignored tokens of the fp32 cross entropy."""
+    return _CrossEntropyFn.apply(logits, labels)

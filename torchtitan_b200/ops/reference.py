@@ -1,0 +1,244 @@
+"""Plain PyTorch statements of every operator, with fp32 math.
+
+These are (a) the CPU execution path (gloo tests, meta/CPU debugging) and
+(b) the oracles the CUDA kernels are tested against.  They restate the
+reference's math: RMSNorm (torchtitan/models/common/nn_modules.py:133-147),
+RoPE (models/common/rope.py:253-346), SwiGLU (models/common/feed_forward.py:53),
+cross entropy with sum reduction (components/loss.py:27-62), AdamW
+(torch.optim.AdamW semantics, components/optimizer/optimizer.py:378-399) and the
+token-choice router (models/common/moe.py:277-335).
+"""
+
+from __future__ import annotations
+
+import math
+
+import torch
+import torch.nn.functional as F
+
+IGNORE_INDEX = -100
+
+
+# ---------------------------------------------------------------- RMSNorm
+def rms_norm_fwd(x: torch.Tensor, weight: torch.Tensor | None, eps: float):
+    xf = x.float()
+    rstd = torch.rsqrt(xf.pow(2).mean(dim=-1, keepdim=True) + eps)
+    y = xf * rstd
+    if weight is not None:
+        y = y * weight.float()
+    return y.to(x.dtype), rstd.squeeze(-1)
+
+
+def rms_norm_bwd(dy: torch.Tensor, x: torch.Tensor, weight: torch.Tensor | None, rstd: torch.Tensor):
+    xf, dyf = x.float(), dy.float()
+    r = rstd.float().unsqueeze(-1)
+    xhat = xf * r
+    wdy = dyf * weight.float() if weight is not None else dyf
+    c = (wdy * xhat).mean(dim=-1, keepdim=True)
+    dx = (wdy - xhat * c) * r
+    dw = None
+    if weight is not None:
+        dw = (dyf * xhat).reshape(-1, x.shape[-1]).sum(dim=0)
+    return dx.to(x.dtype), dw
+
+
+# ------------------------------------------------------------------- RoPE
+def rope_table(head_dim: int, max_pos: int, theta: float, scaling: str = "none", *, scaling_factor: float = 8.0,
+               low_freq_factor: float = 1.0, high_freq_factor: float = 4.0, original_max_pos: int = 8192,
+               rope_factor: float = 1.0, beta_fast: float = 32.0, beta_slow: float = 1.0,
+               original_seq_len: int = 4096, truncate: bool = True) -> torch.Tensor:
+    """``[max_pos, head_dim]`` fp32 table holding ``cos | sin`` of ``pos * inv_freq``."""
+    half = head_dim // 2
+    inv = 1.0 / (theta ** (torch.arange(0, head_dim, 2)[:half].float() / head_dim))
+    if scaling == "llama":
+        wavelen = 2 * math.pi / inv
+        low_wl = original_max_pos / low_freq_factor
+        high_wl = original_max_pos / high_freq_factor
+        scaled = torch.where(wavelen > low_wl, inv / scaling_factor, inv)
+        s = (original_max_pos / wavelen - low_freq_factor) / (high_freq_factor - low_freq_factor)
+        smooth = (1 - s) * inv / scaling_factor + s * inv
+        medium = (~(wavelen < high_wl)) & (~(wavelen > low_wl))
+        inv = torch.where(medium, smooth, scaled)
+    elif scaling == "yarn" and rope_factor > 1.0:
+        inv = yarn_inv_freq(head_dim, theta, rope_factor, beta_fast, beta_slow, original_seq_len, truncate)
+    ang = torch.outer(torch.arange(max_pos, dtype=torch.float32), inv.float())
+    return torch.cat([ang.cos(), ang.sin()], dim=-1).contiguous()
+
+
+def yarn_inv_freq(dim, base, factor, beta_fast, beta_slow, original_seq_len, truncate=True):
+    def corr_dim(n_rot):
+        return dim * math.log(original_seq_len / (n_rot * 2 * math.pi)) / (2 * math.log(base))
+
+    low, high = corr_dim(beta_fast), corr_dim(beta_slow)
+    if truncate:
+        low, high = math.floor(low), math.ceil(high)
+    low, high = max(low, 0), min(high, dim - 1)
+    if low == high:
+        high += 0.001
+    ramp = ((torch.arange(dim // 2, dtype=torch.float32) - low) / (high - low)).clamp(0, 1)
+    smooth = 1 - ramp
+    inv = 1.0 / (base ** (torch.arange(0, dim, 2, dtype=torch.float32) / dim))
+    return inv / factor * (1 - smooth) + inv * smooth
+
+
+def rope_apply(x: torch.Tensor, table: torch.Tensor, positions: torch.Tensor, interleaved: bool,
+               inverse: bool = False) -> torch.Tensor:
+    """Rotate ``x[T, H, D]`` by the angles of ``positions[T]``.
+
+    ``interleaved`` pairs dims ``(2i, 2i+1)`` (Llama "complex" RoPE); otherwise
+    dims ``(i, i + D/2)`` (rotate-half).  ``inverse`` applies the transpose
+    rotation, i.e. the backward pass.  ``table`` may be narrower than ``D``
+    (partial rotary): only the first ``table.shape[1]`` dims rotate.
+    """
+    rot = table.shape[1]
+    half = rot // 2
+    cs = table[positions.long()]
+    cos, sin = cs[:, None, :half], cs[:, None, half:]
+    if inverse:
+        sin = -sin
+    xf = x.float()
+    xr, xpass = xf[..., :rot], xf[..., rot:]
+    if interleaved:
+        x0, x1 = xr[..., 0::2], xr[..., 1::2]
+        o0 = x0 * cos - x1 * sin
+        o1 = x0 * sin + x1 * cos
+        out = torch.stack([o0, o1], dim=-1).flatten(-2)
+    else:
+        x0, x1 = xr[..., :half], xr[..., half:]
+        out = torch.cat([x0 * cos - x1 * sin, x1 * cos + x0 * sin], dim=-1)
+    if xpass.shape[-1]:
+        out = torch.cat([out, xpass], dim=-1)
+    return out.to(x.dtype)
+
+
+# ----------------------------------------------------------------- SwiGLU
+def swiglu_fwd(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
+    return (F.silu(gate.float()) * up.float()).to(gate.dtype)
+
+
+def swiglu_bwd(gate: torch.Tensor, up: torch.Tensor, dout: torch.Tensor):
+    g, u, d = gate.float(), up.float(), dout.float()
+    sig = torch.sigmoid(g)
+    silu = g * sig
+    dg = d * u * (sig + silu * (1 - sig))
+    du = d * silu
+    return dg.to(gate.dtype), du.to(up.dtype)
+
+
+# ---------------------------------------------------------- cross entropy
+def cross_entropy_fwd_bwd(logits: torch.Tensor, labels: torch.Tensor, grad_scale: torch.Tensor | float):
+    """Sum-reduced CE and ``dlogits = (softmax - onehot) * grad_scale``.
+
+    Returns ``(loss_sum fp32 scalar, dlogits in logits.dtype, n_valid)``.
+    """
+    lf = logits.float()
+    valid = labels != IGNORE_INDEX
+    lse = torch.logsumexp(lf, dim=-1)
+    safe = labels.clamp_min(0).long()
+    tgt = lf.gather(-1, safe[:, None]).squeeze(-1)
+    loss = ((lse - tgt) * valid).sum()
+    p = torch.exp(lf - lse[:, None])
+    p.scatter_add_(-1, safe[:, None], -torch.ones_like(tgt)[:, None])
+    p = p * valid[:, None]
+    if isinstance(grad_scale, torch.Tensor):
+        grad_scale = grad_scale.float()
+    return loss, (p * grad_scale).to(logits.dtype), valid.sum()
+
+
+# ------------------------------------------------------------------ AdamW
+def adamw_step(master: torch.Tensor, grad: torch.Tensor, exp_avg: torch.Tensor, exp_avg_sq: torch.Tensor,
+               *, lr: float, beta1: float, beta2: float, eps: float, weight_decay: float, step: int,
+               grad_scale: torch.Tensor | float = 1.0, out_lowp: torch.Tensor | None = None) -> None:
+    """In-place decoupled-weight-decay Adam on flat fp32 ``master``.
+
+    ``exp_avg``/``exp_avg_sq`` may be bf16 (math is fp32, state is rounded on
+    store).  ``grad_scale`` is the clip coefficient; ``out_lowp`` receives the
+    updated parameters cast to its dtype.
+    """
+    g = grad.float() * grad_scale
+    m = exp_avg.float().mul_(beta1).add_(g, alpha=1 - beta1)
+    v = exp_avg_sq.float().mul_(beta2).addcmul_(g, g, value=1 - beta2)
+    bc1 = 1 - beta1 ** step
+    bc2 = 1 - beta2 ** step
+    master.mul_(1 - lr * weight_decay)
+    denom = (v.sqrt() / math.sqrt(bc2)).add_(eps)
+    master.addcdiv_(m, denom, value=-lr / bc1)
+    exp_avg.copy_(m)
+    exp_avg_sq.copy_(v)
+    if out_lowp is not None:
+        out_lowp.copy_(master)
+
+
+# -------------------------------------------------------------- attention
+def attention_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, scale: float, causal: bool = True,
+                  doc_ids: torch.Tensor | None = None, window: int | None = None,
+                  q_pos: torch.Tensor | None = None, k_pos: torch.Tensor | None = None,
+                  sinks: torch.Tensor | None = None):
+    """Dense-math attention over folded tokens.
+
+    ``q[Tq, Hq, D]``, ``k/v[Tk, Hkv, D(v)]``; GQA by head repetition.  ``doc_ids``
+    (``[T]`` ints, same for q and k unless a tuple ``(q_doc, k_doc)``) restricts
+    attention to the same document; ``q_pos``/``k_pos`` are global token indices
+    used by the causal and sliding-window tests (default ``arange``).  ``sinks``
+    (``[Hq]``) adds a per-head logit to the softmax denominator.
+    Returns ``(out[Tq, Hq, Dv], lse[Hq, Tq])``.
+    """
+    Tq, Hq, D = q.shape
+    Tk, Hkv, _ = k.shape
+    rep = Hq // Hkv
+    qf = q.float().transpose(0, 1)  # [Hq, Tq, D]
+    kf = k.float().transpose(0, 1).repeat_interleave(rep, dim=0)
+    vf = v.float().transpose(0, 1).repeat_interleave(rep, dim=0)
+    s = torch.matmul(qf, kf.transpose(1, 2)) * scale  # [Hq, Tq, Tk]
+    dev = q.device
+    qp = torch.arange(Tq, device=dev) if q_pos is None else q_pos
+    kp = torch.arange(Tk, device=dev) if k_pos is None else k_pos
+    mask = torch.ones(Tq, Tk, dtype=torch.bool, device=dev)
+    if causal:
+        mask &= qp[:, None] >= kp[None, :]
+    if window is not None and window > 0:
+        mask &= (qp[:, None] - kp[None, :]) < window
+    if doc_ids is not None:
+        qd, kd = doc_ids if isinstance(doc_ids, tuple) else (doc_ids, doc_ids)
+        mask &= qd[:, None] == kd[None, :]
+    s = s.masked_fill(~mask[None], float("-inf"))
+    if sinks is not None:
+        s_ext = torch.cat([s, sinks.float()[:, None, None].expand(Hq, Tq, 1)], dim=-1)
+        lse = torch.logsumexp(s_ext, dim=-1)
+    else:
+        lse = torch.logsumexp(s, dim=-1)
+    lse_safe = torch.where(torch.isinf(lse), torch.zeros_like(lse), lse)
+    p = torch.exp(s - lse_safe[..., None])
+    p = torch.where(mask[None], p, torch.zeros_like(p))
+    out = torch.matmul(p, vf).transpose(0, 1)
+    return out.to(q.dtype), lse
+
+
+# ----------------------------------------------------------------- router
+def router_topk(scores_logits: torch.Tensor, top_k: int, score_func: str, expert_bias: torch.Tensor | None,
+                route_norm: bool, route_scale: float, num_expert_groups: int | None = None,
+                num_limited_groups: int | None = None):
+    """Token-choice routing on fp32 gate logits ``[T, E]``.
+
+    Returns ``(top_scores[T,K] fp32, selected[T,K] int64, tokens_per_expert[E] fp32)``.
+    """
+    logits = scores_logits.float()
+    scores = torch.softmax(logits, dim=-1) if score_func == "softmax" else torch.sigmoid(logits)
+    sel_scores = scores if expert_bias is None else scores + expert_bias.float()
+    E = scores.shape[-1]
+    if num_expert_groups and num_limited_groups and num_expert_groups > 1:
+        T = scores.shape[0]
+        grp = sel_scores.view(T, num_expert_groups, E // num_expert_groups)
+        gscore = grp.topk(2, dim=-1).values.sum(dim=-1)
+        keep = gscore.topk(num_limited_groups, dim=-1).indices
+        gmask = torch.zeros(T, num_expert_groups, dtype=torch.bool, device=scores.device)
+        gmask.scatter_(1, keep, True)
+        sel_scores = grp.masked_fill(~gmask[..., None], float("-inf")).reshape(T, E)
+    sel = sel_scores.topk(top_k, dim=-1, sorted=False).indices
+    top = scores.gather(-1, sel)
+    if route_norm:
+        top = top / (top.sum(dim=-1, keepdim=True) + 1e-20)
+    top = top * route_scale
+    counts = torch.zeros(E, dtype=torch.float32, device=scores.device)
+    counts.scatter_add_(0, sel.reshape(-1), torch.ones(sel.numel(), dtype=torch.float32, device=scores.device))
+    return top, sel, counts

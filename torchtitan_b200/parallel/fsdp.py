@@ -1,0 +1,535 @@
+"""Sharded data parallelism with flat per-unit buffers (ZeRO-style, B200 layout).
+
+Design.  Parameters are grouped into *units* (embedding, each transformer block,
+final norm + lm_head -- the same unit structure the reference gives FSDP2,
+torchtitan/distributed/fsdp.py:168-381).  Per unit there are
+
+* ``flat_param``  full-size buffer in the compute dtype (bf16); module parameters
+  are views into it.  With 180 GB of HBM the bf16 weights of every target model
+  stay resident, so there is no all-gather on the forward critical path: the
+  gathered weights are refreshed once per optimizer step.  (``reshard`` mode for
+  models that do not fit re-gathers units on demand.)
+* ``flat_grad``   full-size local gradient buffer (compute dtype).  The linear
+  backward writes weight gradients straight into it (``main_grad`` views).
+* ``master`` / ``exp_avg`` / ``exp_avg_sq`` / ``grad_shard``: this rank's 1/N slice
+  in fp32 (optimizer moments optionally bf16).
+
+Sharding is by *flat offset*: rank r owns elements ``[r*S, (r+1)*S)`` of the padded
+flat buffer, so both collectives run in place on the buffers without copy-in /
+copy-out, and the same layout is what the in-kernel NVLink path reads and writes.
+
+Per optimizer step and unit:  local grads --(reduce-scatter, fp32 accumulate)-->
+``grad_shard``; global grad-norm from per-unit partial sums; AdamW on the shard
+which also writes the updated bf16 weights into ``flat_param``; all-gather of
+``flat_param``.  Gradient division is never applied: the loss is already divided
+by the global token count (torchtitan/distributed/fsdp.py:85-99).
+
+Two communication back ends: ``nccl`` (library collectives; also ``gloo`` on CPU)
+and ``nvlink`` (peer loads / stores from our own kernels over symmetric memory,
+:mod:`torchtitan_b200.parallel.symm`).
+"""
+
+from __future__ import annotations
+
+import math
+import re
+from dataclasses import dataclass, field
+from typing import Any, Callable, Iterable
+
+import torch
+import torch.distributed as dist
+import torch.nn as nn
+
+from torchtitan_b200.models.common.module import InitSpec, iter_checkpoint_slices, materialize_param
+from torchtitan_b200.ops import optim as optim_ops
+
+__all__ = ["ShardedModel", "FlatUnit", "ParamSlot", "UnitSpec"]
+
+_ALIGN = 128  # elements; keeps every shard boundary 256-byte aligned for bf16
+
+
+@dataclass
+class ParamSlot:
+    fqn: str
+    param: nn.Parameter
+    shape: tuple[int, ...]
+    numel: int
+    offset: int  # element offset inside the unit's flat buffer
+    init: InitSpec
+    tp_slices: Any = None  # (dim, [(a,b),...], global_shape) when tensor-parallel sharded
+    tp_replicated: bool = False
+    group_idx: int = 0  # optimizer param group
+
+
+@dataclass
+class UnitSpec:
+    name: str
+    modules: list[nn.Module]
+    group_name: str = "fsdp"  # which mesh axis shards this unit ("fsdp" or "efsdp")
+    param_filter: Callable[[str, nn.Parameter], bool] | None = None
+
+
+class FlatUnit:
+    def __init__(self, name: str, slots: list[ParamSlot], group, group_size: int, group_rank: int,
+                 replicate_group=None):
+        self.name = name
+        self.slots = slots
+        self.group = group
+        self.size = group_size
+        self.rank = group_rank
+        self.replicate_group = replicate_group
+        total = sum(s.numel for s in slots)
+        quantum = _ALIGN * group_size
+        self.numel = total
+        self.padded = max(quantum, (total + quantum - 1) // quantum * quantum)
+        self.shard_numel = self.padded // group_size
+        self.flat_param: torch.Tensor | None = None
+        self.flat_grad: torch.Tensor | None = None
+        self.master: torch.Tensor | None = None
+        self.grad_shard: torch.Tensor | None = None
+        self.exp_avg: torch.Tensor | None = None
+        self.exp_avg_sq: torch.Tensor | None = None
+        self.rep_numel = 0  # leading elements that are replicated across tensor-parallel ranks
+        self.pending = False  # gradients written, reduction not yet launched
+        self.grad_shard_valid = False
+        self.sumsq: torch.Tensor | None = None  # [2]: (tp-replicated part, rest)
+
+    # shard geometry -----------------------------------------------------
+    @property
+    def shard_start(self) -> int:
+        return self.rank * self.shard_numel
+
+    def shard_view(self, flat: torch.Tensor) -> torch.Tensor:
+        return flat[self.shard_start:self.shard_start + self.shard_numel]
+
+    def slot_pieces(self, rank: int | None = None):
+        """Intersections of this rank's shard with each parameter:
+        ``(slot, param_flat_start, shard_start, length)``."""
+        r = self.rank if rank is None else rank
+        lo, hi = r * self.shard_numel, (r + 1) * self.shard_numel
+        for s in self.slots:
+            a, b = max(lo, s.offset), min(hi, s.offset + s.numel)
+            if a < b:
+                yield s, a - s.offset, a - lo, b - a
+
+
+class ShardedModel:
+    """Owns the flat buffers of a model (or pipeline stage) and its sharded optimizer state."""
+
+    def __init__(self, model: nn.Module, units: list[UnitSpec], *, pdims, device: torch.device,
+                 param_dtype: torch.dtype = torch.bfloat16, master_dtype: torch.dtype = torch.float32,
+                 state_dtype: torch.dtype = torch.float32, seed: int = 0, comm: str = "nccl",
+                 grad_accum_steps: int = 1, fqn_prefix: str = "", tp=None):
+        self.model = model
+        self.pdims = pdims
+        self.device = device
+        self.param_dtype = param_dtype
+        self.state_dtype = state_dtype
+        self.seed = seed
+        self.comm = comm
+        self.tp = tp
+        self.grad_accum_steps = grad_accum_steps
+        self.fqn_prefix = fqn_prefix
+        self.units: list[FlatUnit] = []
+        self.frozen: dict[str, nn.Parameter] = {}
+        self.step_count = 0
+        self._comm_stream = torch.cuda.Stream(device) if device.type == "cuda" else None
+        self._fp32_tmp: list[torch.Tensor] = []
+        self._tmp_idx = 0
+        self._symm = None
+        self._callback_queued = False
+        self._build_units(units)
+
+    # ------------------------------------------------------------------
+    # construction
+    # ------------------------------------------------------------------
+    def _build_units(self, specs: list[UnitSpec]) -> None:
+        fqn_of: dict[int, str] = {}
+        for name, p in self.model.named_parameters(remove_duplicate=True):
+            fqn_of[id(p)] = name
+        claimed: set[int] = set()
+        for spec in specs:
+            slots: list[ParamSlot] = []
+            plist: list[tuple[str, nn.Parameter]] = []
+            for m in spec.modules:
+                for _, p in m.named_parameters(remove_duplicate=True):
+                    if id(p) in claimed or id(p) not in fqn_of:
+                        continue
+                    if spec.param_filter is not None and not spec.param_filter(fqn_of[id(p)], p):
+                        continue
+                    claimed.add(id(p))
+                    plist.append((fqn_of[id(p)], p))
+            trainable = [(n, p) for n, p in plist if p.requires_grad]
+            for n, p in plist:
+                if not p.requires_grad:
+                    self.frozen[n] = p
+            if not trainable:
+                continue
+            # tensor-parallel-replicated parameters first: their gradients need one
+            # all-reduce over the leading range of the flat buffer
+            trainable.sort(key=lambda np_: 0 if getattr(np_[1], "_replicated_over_tp", False) else 1)
+            off = 0
+            rep = 0
+            for n, p in trainable:
+                slot = ParamSlot(
+                    fqn=n, param=p, shape=tuple(p.shape), numel=p.numel(), offset=off,
+                    init=getattr(p, "_init_spec", None) or InitSpec(),
+                    tp_slices=getattr(p, "_tp_slices", None),
+                    tp_replicated=bool(getattr(p, "_replicated_over_tp", False)),
+                )
+                slots.append(slot)
+                off += (p.numel() + 7) // 8 * 8  # keep every parameter 16-byte aligned
+                if slot.tp_replicated:
+                    rep = off
+            # compact numel accounting: last slot's padding is part of unit padding
+            gname = spec.group_name
+            group = self.pdims.group(gname)
+            gsize = self.pdims.size(gname)
+            grank = self.pdims.local_rank(gname) if gsize > 1 else 0
+            rgroup = self.pdims.group("dp_replicate")
+            unit = FlatUnit(spec.name, slots, group, gsize, grank, rgroup)
+            quantum = _ALIGN * gsize
+            unit.numel = off
+            unit.padded = max(quantum, (off + quantum - 1) // quantum * quantum)
+            unit.shard_numel = unit.padded // gsize
+            unit.rep_numel = rep if (self.tp is not None and self.tp.size > 1) else 0
+            self.units.append(unit)
+        missing = [n for i, n in fqn_of.items() if i not in claimed]
+        if missing:
+            raise ValueError(f"parameters not assigned to any sharding unit: {missing[:5]} ...")
+
+    def materialize(self, init: bool = True) -> None:
+        """Allocate buffers, point module parameters at them, initialise the fp32 master shards."""
+        dev, pd = self.device, self.param_dtype
+        use_symm = self.comm == "nvlink" and dev.type == "cuda" and any(u.size > 1 for u in self.units)
+        if use_symm:
+            from . import symm
+
+            self._symm = symm.SymmetricArena(self.pdims, dev)
+        replaced: dict[int, nn.Parameter] = {}
+        for u in self.units:
+            if use_symm and u.size > 1:
+                u.flat_param = self._symm.alloc(u.padded, pd, u.group, tag=f"{u.name}.param")
+                u.flat_grad = self._symm.alloc(u.padded, pd, u.group, tag=f"{u.name}.grad")
+                u.flat_param.zero_()
+                u.flat_grad.zero_()
+            else:
+                u.flat_param = torch.zeros(u.padded, dtype=pd, device=dev)
+                u.flat_grad = torch.zeros(u.padded, dtype=pd, device=dev)
+            u.master = torch.zeros(u.shard_numel, dtype=torch.float32, device=dev)
+            u.sumsq = torch.zeros(2, dtype=torch.float32, device=dev)
+            # A separate fp32 gradient shard is needed whenever gradients are summed across
+            # ranks or across microbatches; a lone owner with one microbatch lets the
+            # optimizer read the local gradient buffer directly.
+            if u.size > 1 or self.grad_accum_steps > 1 or u.replicate_group is not None:
+                u.grad_shard = torch.zeros(u.shard_numel, dtype=torch.float32, device=dev)
+            for s in u.slots:
+                new = nn.Parameter(u.flat_param[s.offset:s.offset + s.numel].view(s.shape), requires_grad=True)
+                for attr in ("_init_spec", "_tp_slices", "_replicated_over_tp", "_is_expert"):
+                    if hasattr(s.param, attr):
+                        setattr(new, attr, getattr(s.param, attr))
+                new.main_grad = u.flat_grad[s.offset:s.offset + s.numel].view(s.shape)
+                new._main_grad_written = False
+                new._unit = u
+                replaced[id(s.param)] = new
+                s.param = new
+        for name, p in list(self.frozen.items()):
+            spec = getattr(p, "_init_spec", None) or InitSpec()
+            full = self._materialize_full(name, p, spec)
+            new = nn.Parameter(full.to(pd), requires_grad=False)
+            replaced[id(p)] = new
+            self.frozen[name] = new
+        _swap_parameters(self.model, replaced)
+        if init:
+            self.init_weights()
+
+    def _materialize_full(self, fqn: str, p, spec: InitSpec) -> torch.Tensor:
+        """Local (tensor-parallel sliced) fp32 initial value of parameter ``fqn``."""
+        tps = getattr(p, "_tp_slices", None) if not isinstance(p, ParamSlot) else p.tp_slices
+        name = self.fqn_prefix + fqn
+        if tps is None:
+            shape = p.shape
+            return materialize_param(shape, spec, self.seed, name, self.device)
+        dim, ranges, gshape = tps
+        full = materialize_param(gshape, spec, self.seed, name, "cpu")
+        parts = [full.narrow(dim, a, b - a) for a, b in ranges]
+        return torch.cat(parts, dim=dim).contiguous().to(self.device)
+
+    @torch.no_grad()
+    def init_weights(self) -> None:
+        for u in self.units:
+            for s in u.slots:
+                full = None
+                for slot, pstart, sstart, n in u.slot_pieces():
+                    if slot is not s:
+                        continue
+                    if full is None:
+                        full = self._materialize_full(s.fqn, s, s.init).reshape(-1)
+                    u.master[sstart:sstart + n].copy_(full[pstart:pstart + n])
+                del full
+        self.publish_params()
+        init_b = getattr(self.model, "init_buffers", None)
+        if init_b is not None:
+            init_b(self.device)
+
+    @torch.no_grad()
+    def publish_params(self) -> None:
+        """master shard -> compute-dtype flat_param (own slice) -> all ranks."""
+        for u in self.units:
+            u.shard_view(u.flat_param).copy_(u.master)
+        self._all_gather_params()
+
+    def _all_gather_params(self) -> None:
+        for u in self.units:
+            if u.size > 1:
+                dist.all_gather_into_tensor(u.flat_param, u.shard_view(u.flat_param), group=u.group)
+
+    # ------------------------------------------------------------------
+    # backward-time gradient reduction
+    # ------------------------------------------------------------------
+    def attach_hooks(self, unit_modules: list[tuple[FlatUnit, nn.Module]]) -> None:
+        """Fire the unit's gradient reduction when the gradient reaches the unit's input."""
+        for unit, module in unit_modules:
+            module.register_forward_pre_hook(_make_pre_hook(self, unit), with_kwargs=True)
+
+    def _on_unit_backward_done(self, unit: FlatUnit) -> None:
+        self._collect_autograd_grads(unit)
+        self._launch_reduce(unit)
+
+    def _collect_autograd_grads(self, unit: FlatUnit) -> None:
+        """Fold gradients delivered through ``.grad`` (ops without direct main_grad writes)."""
+        for s in unit.slots:
+            p = s.param
+            if p.grad is not None:
+                if p._main_grad_written:
+                    p.main_grad.add_(p.grad)
+                else:
+                    p.main_grad.copy_(p.grad)
+                    p._main_grad_written = True
+                p.grad = None
+
+    def _launch_reduce(self, unit: FlatUnit) -> None:
+        if unit.pending:
+            return
+        written = [s.param._main_grad_written for s in unit.slots]
+        if not any(written):
+            return
+        # parameters that received no gradient this pass contribute zeros
+        for s, w in zip(unit.slots, written):
+            if not w:
+                s.param.main_grad.zero_()
+        unit.pending = True
+        for s in unit.slots:
+            s.param._main_grad_written = False
+        cs = self._comm_stream
+        if cs is not None:
+            cs.wait_stream(torch.cuda.current_stream(self.device))
+            with torch.cuda.stream(cs):
+                self._reduce_unit(unit)
+        else:
+            self._reduce_unit(unit)
+
+    @torch.no_grad()
+    def _reduce_unit(self, u: FlatUnit) -> None:
+        tp = self.tp
+        if u.rep_numel and tp is not None and tp.size > 1:
+            dist.all_reduce(u.flat_grad[:u.rep_numel], group=tp.group)
+        if u.grad_shard is None:
+            # single shard owner, no accumulation: the optimizer reads flat_grad directly
+            u.grad_shard_valid = True
+            return
+        first = not u.grad_shard_valid
+        if u.size == 1:
+            src = u.flat_grad
+            if first:
+                u.grad_shard.copy_(src)
+            else:
+                u.grad_shard.add_(src)
+        elif self.comm == "nvlink" and self._symm is not None:
+            self._symm.reduce_scatter_accumulate(u.flat_grad, u.grad_shard, u.group, accumulate=not first)
+        else:
+            tmp = self._get_fp32_tmp(u.padded)
+            tmp.copy_(u.flat_grad)
+            if first:
+                dist.reduce_scatter_tensor(u.grad_shard, tmp, group=u.group)
+            else:
+                out = self._get_fp32_tmp(u.shard_numel, slot=2)
+                dist.reduce_scatter_tensor(out, tmp, group=u.group)
+                u.grad_shard.add_(out)
+        u.grad_shard_valid = True
+
+    def _get_fp32_tmp(self, numel: int, slot: int | None = None) -> torch.Tensor:
+        if slot is None:
+            slot = self._tmp_idx
+            self._tmp_idx ^= 1
+        while len(self._fp32_tmp) <= slot:
+            self._fp32_tmp.append(torch.empty(0, dtype=torch.float32, device=self.device))
+        if self._fp32_tmp[slot].numel() < numel:
+            self._fp32_tmp[slot] = torch.empty(numel, dtype=torch.float32, device=self.device)
+        return self._fp32_tmp[slot][:numel]
+
+    def finish_backward(self) -> None:
+        """Reduce units whose input hook did not fire (first unit), then join the comm stream."""
+        for u in self.units:
+            self._collect_autograd_grads(u)
+            self._launch_reduce(u)
+        if self._comm_stream is not None:
+            torch.cuda.current_stream(self.device).wait_stream(self._comm_stream)
+        for u in self.units:
+            u.pending = False
+        self._callback_queued = False
+
+    # ------------------------------------------------------------------
+    # optimizer-side API
+    # ------------------------------------------------------------------
+    def _grad_of(self, u: FlatUnit) -> torch.Tensor:
+        return u.grad_shard if u.grad_shard is not None else u.shard_view(u.flat_grad)
+
+    @torch.no_grad()
+    def finalize_grads(self) -> None:
+        """HSDP: sum the reduced shards over the replicate axis."""
+        for u in self.units:
+            if u.replicate_group is not None and u.grad_shard_valid:
+                dist.all_reduce(self._grad_of(u), group=u.replicate_group)
+
+    @torch.no_grad()
+    def local_sumsq(self) -> torch.Tensor:
+        """``[2]`` fp32: squared norm of this rank's gradient shards, split into the
+        tensor-parallel-replicated part and the rest."""
+        total = torch.zeros(2, dtype=torch.float32, device=self.device)
+        for u in self.units:
+            if not u.grad_shard_valid:
+                continue
+            g = self._grad_of(u)
+            lo = u.shard_start
+            rep_end = max(0, min(u.rep_numel - lo, u.shard_numel))
+            if rep_end > 0:
+                optim_ops.sumsq_accumulate(g[:rep_end], total[0:1])
+            if rep_end < u.shard_numel:
+                optim_ops.sumsq_accumulate(g[rep_end:], total[1:2])
+        return total
+
+    def ensure_state(self) -> None:
+        for u in self.units:
+            if u.exp_avg is None:
+                u.exp_avg = torch.zeros(u.shard_numel, dtype=self.state_dtype, device=self.device)
+                u.exp_avg_sq = torch.zeros(u.shard_numel, dtype=self.state_dtype, device=self.device)
+
+    @torch.no_grad()
+    def adamw_step(self, groups: list[dict], grad_scale: torch.Tensor | float = 1.0) -> None:
+        """AdamW on every shard; ``groups[i]`` holds lr/betas/eps/weight_decay of param group i."""
+        self.ensure_state()
+        self.step_count += 1
+        step = self.step_count
+        for u in self.units:
+            if not u.grad_shard_valid:
+                continue
+            g = self._grad_of(u)
+            lowp = u.shard_view(u.flat_param)
+            for gi, a, b in _group_runs(u):
+                h = groups[gi]
+                optim_ops.adamw_(
+                    u.master[a:b], g[a:b], u.exp_avg[a:b], u.exp_avg_sq[a:b], lowp[a:b],
+                    lr=h["lr"], beta1=h["betas"][0], beta2=h["betas"][1], eps=h["eps"],
+                    weight_decay=h["weight_decay"], step=step, grad_scale=grad_scale,
+                )
+            u.grad_shard_valid = False
+        self._all_gather_params()
+
+    def zero_grad(self) -> None:
+        for u in self.units:
+            u.grad_shard_valid = False
+            u.pending = False
+            for s in u.slots:
+                s.param._main_grad_written = False
+                s.param.grad = None
+
+    # ------------------------------------------------------------------
+    # parameter-group assignment and state export
+    # ------------------------------------------------------------------
+    def assign_groups(self, patterns: list[str]) -> list[list[str]]:
+        """First matching regex wins; unmatched parameters go to the last (default) group."""
+        compiled = [re.compile(p) for p in patterns]
+        members: list[list[str]] = [[] for _ in range(len(patterns) + 1)]
+        for u in self.units:
+            for s in u.slots:
+                gi = len(patterns)
+                for i, rx in enumerate(compiled):
+                    if rx.search(s.fqn):
+                        gi = i
+                        break
+                s.group_idx = gi
+                members[gi].append(s.fqn)
+        return members
+
+    def named_slots(self) -> Iterable[tuple[FlatUnit, ParamSlot]]:
+        for u in self.units:
+            for s in u.slots:
+                yield u, s
+
+    def memory_summary(self) -> dict[str, float]:
+        gib = 1 << 30
+        tot = {"flat_param": 0, "flat_grad": 0, "master": 0, "grad_shard": 0, "opt_state": 0}
+        for u in self.units:
+            tot["flat_param"] += u.flat_param.numel() * u.flat_param.element_size()
+            tot["flat_grad"] += u.flat_grad.numel() * u.flat_grad.element_size()
+            tot["master"] += u.master.numel() * 4
+            if u.grad_shard is not None:
+                tot["grad_shard"] += u.grad_shard.numel() * 4
+            if u.exp_avg is not None:
+                tot["opt_state"] += 2 * u.exp_avg.numel() * u.exp_avg.element_size()
+        return {k: v / gib for k, v in tot.items()}
+
+
+def _group_runs(u: FlatUnit):
+    """Maximal runs ``(group_idx, shard_lo, shard_hi)`` of this rank's shard with one param group.
+    Padding between parameters rides along with the preceding run."""
+    runs: list[list[int]] = []
+    for slot, _pstart, sstart, n in u.slot_pieces():
+        if runs and runs[-1][0] == slot.group_idx:
+            runs[-1][2] = sstart + n
+        else:
+            runs.append([slot.group_idx, sstart, sstart + n])
+    if runs:
+        runs[-1][2] = max(runs[-1][2], min(u.shard_numel, runs[-1][2]))
+    return [(g, a, b) for g, a, b in runs]
+
+
+def _swap_parameters(model: nn.Module, replaced: dict[int, nn.Parameter]) -> None:
+    for mod in model.modules():
+        for name, p in list(mod._parameters.items()):
+            if p is not None and id(p) in replaced:
+                mod._parameters[name] = replaced[id(p)]
+
+
+class _UnitBackwardEnd(torch.autograd.Function):
+    """Identity on the unit's inputs whose backward marks the end of the unit's backward."""
+
+    @staticmethod
+    def forward(ctx, engine, unit, *tensors):
+        ctx.engine, ctx.unit = engine, unit
+        return tuple(t.view_as(t) for t in tensors)
+
+    @staticmethod
+    def backward(ctx, *grads):
+        ctx.engine._on_unit_backward_done(ctx.unit)
+        return (None, None) + grads
+
+
+def _make_pre_hook(engine: ShardedModel, unit: FlatUnit):
+    def hook(module, args, kwargs):
+        if not torch.is_grad_enabled():
+            return None
+        if not engine._callback_queued:
+            # runs once per backward pass, after the last autograd node
+            engine._callback_queued = True
+        idx = [i for i, a in enumerate(args) if isinstance(a, torch.Tensor) and a.requires_grad]
+        if not idx:
+            return None
+        outs = _UnitBackwardEnd.apply(engine, unit, *[args[i] for i in idx])
+        args = list(args)
+        for i, o in zip(idx, outs):
+            args[i] = o
+        return tuple(args), kwargs
+
+    return hook

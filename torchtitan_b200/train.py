@@ -1,0 +1,50 @@
+"""Entry point: ``python -m torchtitan_b200.train --module llama3 --config llama3_8b [--a.b v]``
+or ``python -m torchtitan_b200.train --job.config_file job.toml``.
+
+Flow (parity: torchtitan/train.py:17-79): logger -> config -> structured logger ->
+build trainer -> (seed checkpoint | train) -> close, destroy the process group.
+"""
+
+from __future__ import annotations
+
+import os
+import sys
+
+import torch
+
+from torchtitan_b200.config import ConfigManager
+from torchtitan_b200.utils import structured_logger as sl
+from torchtitan_b200.utils.logging import init_logger, logger
+
+
+def main(argv: list[str] | None = None) -> None:
+    init_logger()
+    from torchtitan_b200.trainer import Trainer
+    from torchtitan_b200.parallel import utils as dist_utils
+
+    config = ConfigManager().parse_args(argv)
+    sl.init_structured_logger("training", config.dump_folder, enable=config.debug.enable_structured_logging)
+    trainer = None
+    try:
+        if config.checkpoint.create_seed_checkpoint:
+            if int(os.environ.get("WORLD_SIZE", "1")) != 1:
+                raise RuntimeError("a seed checkpoint must be created by a single process")
+            if not config.checkpoint.enable:
+                raise RuntimeError("checkpoint.create_seed_checkpoint needs checkpoint.enable")
+        trainer = config.build()
+        if config.checkpoint.create_seed_checkpoint:
+            trainer.checkpointer.create_seed_checkpoint()
+        else:
+            trainer.train()
+    except Exception:
+        logger.exception("training failed")
+        raise
+    finally:
+        if trainer is not None:
+            trainer.close()
+        sl.close()
+        dist_utils.destroy()
+
+
+if __name__ == "__main__":
+    main()
