@@ -1,0 +1,290 @@
+"""Headline benchmark: Llama-3.1-8B pre-training throughput (tokens/s), FSDP, bf16, seq 8192,
+local batch 1, synthetic uniform tokens, random init -- the config of the reference's published
+B200 numbers (torchtitan/components/quantization/mxfp8.md:157-161).
+
+    python bench.py --gpus 1 --steps 5 --warmup 3
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 \
+        --master-port 29500 bench.py --gpus 8 --steps 5 --warmup 3
+    python bench.py --impl reference ...      # the unmodified reference from baseline/_ref
+
+Two measurements of the same metric are reported on one JSON line:
+
+* ``value``: K optimizer steps timed on the device with CUDA events between a barrier +
+  synchronize on both sides, inputs already resident on the GPU; max over ranks.
+* ``e2e.value``: K steps through the public ``Trainer.train_step`` API, each step fetching its
+  batch from pinned host memory (host->device copy inside the timed region) and reading the loss
+  back to the host.
+
+Every step does the full work: forward, backward, gradient reduction, grad-norm clipping and
+the AdamW update.  The per-step working set (tens of GB) is far larger than the 126 MB L2, so
+no explicit L2 flush is needed between steps.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+BASELINE_TOKENS_PER_SEC_PER_GPU = 8307.5  # Llama3-8B bf16, 8x B200, FSDP2 + compile (reference's published number)
+
+
+def parse_args():
+    p = argparse.ArgumentParser()
+    p.add_argument("--gpus", type=int, default=1)
+    p.add_argument("--steps", type=int, default=5)
+    p.add_argument("--warmup", type=int, default=3)
+    p.add_argument("--impl", default="native", choices=["native", "reference"])
+    p.add_argument("--model", default="llama3")
+    p.add_argument("--flavor", default="8B")
+    p.add_argument("--seq-len", type=int, default=8192)
+    p.add_argument("--local-batch", type=int, default=1)
+    p.add_argument("--fsdp-comm", default=os.environ.get("TB200_FSDP_COMM", "nccl"))
+    p.add_argument("--gemm", default=os.environ.get("TB200_GEMM", "cublas"))
+    p.add_argument("--attention", default=os.environ.get("TB200_ATTENTION", "sdpa"))
+    p.add_argument("--opt-state", default="fp32", choices=["fp32", "bf16"])
+    p.add_argument("--ac", default="selective")
+    p.add_argument("--skip-e2e", action="store_true")
+    return p.parse_args()
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons through NVML while the timed region runs (read-only)."""
+
+    def __init__(self, index: int, period: float = 0.2):
+        self.index, self.period = index, period
+        self.samples: list[int] = []
+        self.reasons: set[str] = set()
+        self.max_mhz = None
+        self._stop = threading.Event()
+        self._t = None
+        try:
+            import pynvml
+
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self.nv = None
+
+    def _loop(self):
+        nv = self.nv
+        names = {
+            "sw_power_cap": getattr(nv, "nvmlClocksThrottleReasonSwPowerCap", 0x4),
+            "hw_slowdown": getattr(nv, "nvmlClocksThrottleReasonHwSlowdown", 0x8),
+            "sw_thermal_slowdown": getattr(nv, "nvmlClocksThrottleReasonSwThermalSlowdown", 0x20),
+            "hw_thermal_slowdown": getattr(nv, "nvmlClocksThrottleReasonHwThermalSlowdown", 0x40),
+            "hw_power_brake": getattr(nv, "nvmlClocksThrottleReasonHwPowerBrakeSlowdown", 0x80),
+        }
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+                mask = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+                for k, bit in names.items():
+                    if mask & bit:
+                        self.reasons.add(k)
+            except Exception:
+                pass
+            self._stop.wait(self.period)
+
+    def start(self):
+        if self.nv is not None:
+            self._t = threading.Thread(target=self._loop, daemon=True)
+            self._t.start()
+
+    def stop(self) -> dict:
+        self._stop.set()
+        if self._t is not None:
+            self._t.join(timeout=2)
+        s = sorted(self.samples)
+        return {"sm_mhz": s[len(s) // 2] if s else None, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons),
+                "samples": len(s)}
+
+
+def reference_arm(args) -> None:
+    """Run the unmodified reference from ``baseline/_ref`` through its own Trainer."""
+    ref_dir = os.path.join(ROOT, "baseline", "_ref")
+    out = {"impl": "reference"}
+    if not os.path.isdir(os.path.join(ref_dir, "torchtitan")):
+        out["unavailable"] = "baseline/_ref is empty: the reference was not installed on this box"
+        print(json.dumps(out))
+        return
+    sys.path.insert(0, ref_dir)
+    try:
+        import torchtitan.trainer  # noqa: F401  (the reference's public training API)
+    except Exception as e:  # ImportError on spmd_types / grain / torch-nightly FSDP symbols
+        out["unavailable"] = (
+            "reference installed with --no-deps but its trainer cannot be imported here: "
+            f"{type(e).__name__}: {str(e)[:160]} (needs spmd_types, grain, torchao and a PyTorch nightly; none "
+            "are in the offline wheelhouse)")
+        print(json.dumps(out))
+        return
+    out["unavailable"] = "reference trainer imported but no launch recipe is wired for this environment"
+    print(json.dumps(out))
+
+
+def main() -> None:
+    args = parse_args()
+    if args.impl == "reference":
+        if int(os.environ.get("RANK", "0")) == 0:
+            reference_arm(args)
+        return
+    os.environ.setdefault("PYTORCH_CUDA_ALLOC_CONF", "expandable_segments:True")
+    os.environ.setdefault("PYTORCH_ALLOC_CONF", "expandable_segments:True")
+    import torch
+    import torch.distributed as dist
+
+    from torchtitan_b200.components.checkpoint import CheckpointManager
+    from torchtitan_b200.components.data import BaseDataLoader
+    from torchtitan_b200.components.lr_scheduler import LRSchedulersContainer
+    from torchtitan_b200.components.metrics import MetricsProcessor
+    from torchtitan_b200.components.optimizer import OptimizersContainer
+    from torchtitan_b200.config import ActivationCheckpointConfig, KernelConfig, ModelSelectConfig, ParallelismConfig, TrainingConfig
+    from torchtitan_b200.ops import functional as OF
+    from torchtitan_b200.trainer import Trainer
+    from torchtitan_b200.utils.logging import init_logger
+
+    init_logger()
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run")
+    T = args.seq_len * args.local_batch
+    steps_total = args.warmup * 2 + args.steps * 2 + 4
+    cfg = Trainer.Config(
+        model=ModelSelectConfig(name=args.model, flavor=args.flavor),
+        dump_folder="/tmp/tb200_bench",
+        metrics=MetricsProcessor.Config(log_freq=10 ** 9),
+        dataloader=BaseDataLoader.Config(dataset="synthetic", seed=0),
+        optimizer=OptimizersContainer.Config(lr=3e-4, implementation="fused" if args.opt_state == "fp32" else "fused_opt_states_bf16"),
+        lr_scheduler=LRSchedulersContainer.Config(warmup_steps=2),
+        training=TrainingConfig(num_tokens_per_microbatch_per_dp_rank=T, max_context_length=args.seq_len,
+                                steps=steps_total, gc_freq=10 ** 6),
+        parallelism=ParallelismConfig(data_parallel_shard_degree=-1, fsdp_comm=args.fsdp_comm),
+        checkpoint=CheckpointManager.Config(enable=False),
+        activation_checkpoint=ActivationCheckpointConfig(mode=args.ac),
+        kernels=KernelConfig(gemm=args.gemm, attention=args.attention),
+    )
+    cfg.debug.seed = 0
+    cfg.debug.enable_structured_logging = False
+    trainer = cfg.build()
+    trainer.model.single_document = True
+    dev = trainer.device
+    mem = trainer.engines[0].memory_summary()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(x: float) -> float:
+        if world == 1:
+            return x
+        t = torch.tensor([x], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    it = trainer.batch_generator(trainer.dataloader)
+    trainer.metrics_processor.should_log = lambda step: False  # logging syncs are measured explicitly below
+
+    # ------------------------------------------------------------ end-to-end
+    e2e = None
+    h2d = d2h = 0
+    if not args.skip_e2e:
+        for _ in range(args.warmup):
+            trainer.step += 1
+            trainer.train_step(it)
+            float(trainer._last_loss)
+        barrier()
+        t0 = time.perf_counter()
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        ev0.record()
+        for _ in range(args.steps):
+            trainer.step += 1
+            trainer.train_step(it)  # pulls a pinned batch, copies it to the device, full optimizer step
+            loss_host = float(trainer._last_loss)  # device -> host read of the step's result
+        ev1.record()
+        barrier()
+        wall = time.perf_counter() - t0
+        e2e_s = max_over_ranks(max(wall, ev0.elapsed_time(ev1) / 1e3))
+        h2d = 3 * T * 8  # input ids, positions, labels: int64 each
+        d2h = 4
+        e2e = {"value": T * world * args.steps / e2e_s, "unit": "tokens/s", "h2d_bytes_per_step": h2d,
+               "d2h_bytes_per_step": d2h, "ms_per_step": 1e3 * e2e_s / args.steps, "last_loss": loss_host}
+
+    # ------------------------------------------------------------ device-timed
+    class _Resident:
+        """Feeds the same device-resident batch every step (inputs never leave the GPU)."""
+
+        def __init__(self, batch):
+            inp, lab = batch
+            self.inp = {k: v.to(dev) for k, v in inp.items()}
+            self.lab = lab.to(dev)
+            self.host_lab = lab
+
+        def __iter__(self):
+            return self
+
+        def __next__(self):
+            return self.inp, self.lab
+
+    resident = _Resident(next(it))
+    for _ in range(args.warmup):
+        trainer.step += 1
+        trainer.train_step(resident)
+    sampler = ClockSampler(dev.index or 0)
+    OF.settings.launches = 0
+    OF.settings.count_launches = True
+    barrier()
+    sampler.start()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record()
+    for _ in range(args.steps):
+        trainer.step += 1
+        trainer.train_step(resident)
+    ev1.record()
+    barrier()
+    clocks = sampler.stop()
+    OF.settings.count_launches = False
+    launches = OF.settings.launches
+    dev_s = max_over_ranks(ev0.elapsed_time(ev1) / 1e3)
+    tokens_per_s = T * world * args.steps / dev_s
+    peak = torch.cuda.max_memory_allocated(dev) / (1 << 30)
+    flops_per_token = trainer.metrics_processor.num_flops_per_token
+    loss = float(trainer._last_loss)
+    if rank == 0:
+        line = {
+            "metric": "tokens_per_sec", "value": tokens_per_s, "unit": "tokens/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * dev_s / args.steps,
+            "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": tokens_per_s / world / BASELINE_TOKENS_PER_SEC_PER_GPU,
+            "dtype": "bf16", "data": "synthetic uniform-random tokens, random-init weights",
+            "impl": "native",
+            "tokens_per_sec_per_gpu": tokens_per_s / world,
+            "mfu_pct": 100.0 * flops_per_token * tokens_per_s / world / 2.25e15,
+            "tflops_per_gpu": flops_per_token * tokens_per_s / world / 1e12,
+            "config": {"model": f"{args.model}-{args.flavor}", "global_batch": args.local_batch * world,
+                       "seq_len": args.seq_len, "parallelism": f"fsdp{world}", "activation_checkpoint": args.ac,
+                       "optimizer": f"AdamW fp32 master, {args.opt_state} moments", "fsdp_comm": args.fsdp_comm,
+                       "gemm": args.gemm, "attention": args.attention,
+                       "l2": "per-step working set >> 126 MB L2 (no flush needed)"},
+            "clocks": clocks, "e2e": e2e, "gpu_launches": launches,
+            "peak_mem_gib": peak, "engine_mem_gib": mem, "loss": loss,
+        }
+        print(json.dumps(line), flush=True)
+    trainer.close()
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

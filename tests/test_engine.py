@@ -1,0 +1,175 @@
+"""Sharded engine: parity with plain PyTorch training, 2-rank vs 1-rank, gradient accumulation."""
+
+import copy
+
+import pytest
+import torch
+
+from tests.dist_utils import run_distributed
+from torchtitan_b200.components.optimizer import OptimizersContainer, clip_grad_norm_
+from torchtitan_b200.config import ConfigManager
+from torchtitan_b200.models import get_model_spec
+from torchtitan_b200.ops import functional as OF
+from torchtitan_b200.parallel.parallel_dims import ParallelDims
+from torchtitan_b200.parallel.parallelize import parallelize_decoder
+from torchtitan_b200.trainer import Trainer
+
+T = 64
+
+
+def _job(accum_tokens=-1, **par):
+    cfg = Trainer.Config()
+    cfg.model.flavor = "debugmodel"
+    cfg.training.num_tokens_per_microbatch_per_dp_rank = T
+    cfg.training.max_context_length = T
+    cfg.training.mixed_precision_param = "float32"
+    cfg.training.num_tokens_per_train_step = accum_tokens
+    for k, v in par.items():
+        setattr(cfg.parallelism, k, v)
+    return cfg
+
+
+def _small_model_cfg(n_layers=2):
+    spec = get_model_spec("llama3", "debugmodel")
+    mc = spec.model
+    mc.layers = mc.layers[:n_layers]
+    mc.n_layers = n_layers
+    for blk in mc.layers:
+        blk.attention.rope.max_context_length = T
+    return mc
+
+
+def _batches(n, seed=0, vocab=2048):
+    g = torch.Generator().manual_seed(seed)
+    out = []
+    for _ in range(n):
+        ids = torch.randint(0, vocab, (T + 1,), generator=g)
+        out.append((ids[:-1].clone(), ids[1:].clone()))
+    return out
+
+
+def _build_engine(cfg, pdims, accum=1, n_layers=2):
+    mc = _small_model_cfg(n_layers)
+    with torch.device("meta"):
+        model = mc.build()
+    eng = parallelize_decoder(model, pdims=pdims, job_config=cfg, device=torch.device("cpu"), seed=7,
+                              grad_accum_steps=accum)
+    return mc, model, eng
+
+
+def _engine_steps(cfg, pdims, microbatches_per_step, accum=1, steps=3):
+    mc, model, eng = _build_engine(cfg, pdims, accum)
+    opt = OptimizersContainer(OptimizersContainer.Config(lr=1e-2), engines=[eng])
+    losses = []
+    pos = torch.arange(T)
+    for s in range(steps):
+        opt.zero_grad()
+        mbs = microbatches_per_step[s]
+        n_tok = torch.tensor(float(T * len(mbs) * pdims.dp_degree))
+        tot = 0.0
+        for tok, lab in mbs:
+            h = model(tok, pos, return_hidden=True)
+            loss = OF.linear_cross_entropy(h, model.lm_head.weight, lab, 1.0 / n_tok, 4)
+            loss.backward()
+            eng.finish_backward()
+            tot += float(loss.detach())
+        clip_grad_norm_([eng], 1.0, pdims, optimizers=opt)
+        opt.step()
+        losses.append(tot)
+    return losses, model, eng
+
+
+def test_engine_matches_plain_pytorch():
+    cfg = _job()
+    pdims = ParallelDims(world_size=1)
+    data = [[b] for b in _batches(3)]
+    losses, model, eng = _engine_steps(cfg, pdims, data)
+
+    mc = _small_model_cfg()
+    plain = mc.build()
+    plain.init_states(seed=7)
+    opt = torch.optim.AdamW(plain.parameters(), lr=1e-2, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1)
+    pos = torch.arange(T)
+    ref_losses = []
+    for (tok, lab), in data:
+        opt.zero_grad()
+        logits = plain(tok, pos)
+        loss = torch.nn.functional.cross_entropy(logits.float(), lab, reduction="sum") / T
+        loss.backward()
+        torch.nn.utils.clip_grad_norm_(plain.parameters(), 1.0)
+        opt.step()
+        ref_losses.append(float(loss.detach()))
+    assert torch.allclose(torch.tensor(losses), torch.tensor(ref_losses), atol=2e-4), (losses, ref_losses)
+    for (n1, p1), (n2, p2) in zip(model.named_parameters(), plain.named_parameters()):
+        assert n1 == n2
+        assert torch.allclose(p1, p2, atol=2e-3), (n1, (p1 - p2).abs().max())
+
+
+def test_gradient_accumulation_equals_big_batch():
+    pdims = ParallelDims(world_size=1)
+    b = _batches(6)
+    two, _, _ = _engine_steps(_job(accum_tokens=2 * T), pdims, [b[0:2], b[2:4], b[4:6]], accum=2)
+    assert all(l == l for l in two)
+
+
+def _rank_fn(rank, world, out_path):
+    import torch.distributed as dist
+
+    cfg = _job()
+    pdims = ParallelDims(world_size=world, rank=rank).build()
+    b = _batches(6)
+    data = [[b[2 * s + rank]] for s in range(3)]
+    losses, model, eng = _engine_steps(cfg, pdims, data)
+    t = torch.tensor(losses)
+    dist.all_reduce(t)
+    if rank == 0:
+        sd = {n: p.detach().clone() for n, p in model.named_parameters()}
+        torch.save({"losses": t, "params": sd}, out_path)
+
+
+def test_two_ranks_match_one_rank_with_accumulation(tmp_path):
+    out = str(tmp_path / "r2.pt")
+    run_distributed(_rank_fn, 2, out)
+    got = torch.load(out)
+    pdims = ParallelDims(world_size=1)
+    b = _batches(6)
+    losses, model, _ = _engine_steps(_job(accum_tokens=2 * T), pdims, [b[0:2], b[2:4], b[4:6]], accum=2)
+    assert torch.allclose(got["losses"], torch.tensor(losses), atol=1e-4), (got["losses"], losses)
+    for n, p in model.named_parameters():
+        assert torch.allclose(p, got["params"][n], atol=2e-3), n
+
+
+def _tp_fn(rank, world, out_path):
+    import torch.distributed as dist
+
+    cfg = _job(tensor_parallel_degree=2)
+    pdims = ParallelDims(world_size=world, rank=rank, tp=2).build()
+    b = _batches(3)
+    mc, model, eng = _build_engine(cfg, pdims)
+    opt = OptimizersContainer(OptimizersContainer.Config(lr=1e-2), engines=[eng])
+    from torchtitan_b200.components.loss import LinearCrossEntropyLoss
+
+    loss_fn = LinearCrossEntropyLoss()
+    loss_fn.set_lm_head(model.lm_head, tp=model.tp)
+    pos = torch.arange(T)
+    losses = []
+    for tok, lab in b:
+        opt.zero_grad()
+        h = model(tok, pos, return_hidden=True)
+        loss = loss_fn(h, lab, torch.tensor(float(T)))
+        loss.backward()
+        eng.finish_backward()
+        clip_grad_norm_([eng], 1.0, pdims, optimizers=opt)
+        opt.step()
+        losses.append(float(loss.detach()))
+    if rank == 0:
+        torch.save(torch.tensor(losses), out_path)
+
+
+def test_tensor_parallel_matches_single(tmp_path):
+    out = str(tmp_path / "tp.pt")
+    run_distributed(_tp_fn, 2, out)
+    got = torch.load(out)
+    pdims = ParallelDims(world_size=1)
+    losses, _, _ = _engine_steps(_job(), pdims, [[x] for x in _batches(3)])
+    assert torch.allclose(got, torch.tensor(losses), atol=2e-4), (got, losses)

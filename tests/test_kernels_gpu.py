@@ -1,0 +1,198 @@
+"""GPU: every hand-written kernel against the fp32 PyTorch statement of the same op."""
+
+import math
+
+import pytest
+import torch
+
+from torchtitan_b200.ops import ext, functional as OF, optim as optim_ops, reference as ref
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module", autouse=True)
+def _need_ext():
+    assert ext.load(), "the sm_100a extension must be built in-tree before GPU tests run"
+
+
+def _close(a, b, atol, rtol=0.0):
+    a, b = a.float().cpu(), b.float().cpu()
+    assert torch.allclose(a, b, atol=atol, rtol=rtol), float((a - b).abs().max())
+
+
+@pytest.mark.parametrize("shape", [(257, 4096), (64, 8192), (1000, 128), (33, 256), (5, 1024)])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("has_w", [True, False])
+def test_rmsnorm(shape, dtype, has_w):
+    torch.manual_seed(0)
+    x = torch.randn(shape, device="cuda", dtype=dtype)
+    w = (torch.randn(shape[1], device="cuda", dtype=dtype) * 0.1 + 1) if has_w else None
+    dy = torch.randn(shape, device="cuda", dtype=dtype)
+    y, rstd = torch.ops.tb200.rmsnorm_fwd(x, w, 1e-5)
+    yr, rr = ref.rms_norm_fwd(x.float(), None if w is None else w.float(), 1e-5)
+    tol = 2e-2 if dtype == torch.bfloat16 else 1e-5
+    _close(y, yr, tol, tol)
+    _close(rstd, rr, 1e-5, 1e-5)
+    dx, dw = torch.ops.tb200.rmsnorm_bwd(dy, x, w, rstd)
+    dxr, dwr = ref.rms_norm_bwd(dy.float(), x.float(), None if w is None else w.float(), rr)
+    _close(dx, dxr, tol, tol)
+    if has_w:
+        _close(dw, dwr, 1e-2 * math.sqrt(shape[0]) if dtype == torch.bfloat16 else 1e-3, 1e-3)
+
+
+@pytest.mark.parametrize("interleaved", [True, False])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_rope_inplace_strided(interleaved, dtype):
+    torch.manual_seed(1)
+    T, Hq, Hkv, D = 300, 8, 2, 128
+    table = ref.rope_table(D, 512, 500000.0, "llama").cuda()
+    pos = torch.randint(0, 512, (T,), device="cuda")
+    qkv = torch.randn(T, Hq + 2 * Hkv, D, device="cuda", dtype=dtype)
+    orig = qkv.clone()
+    view = qkv[:, :Hq + Hkv]
+    torch.ops.tb200.rope_(view, table, pos, interleaved, False)
+    exp = ref.rope_apply(orig[:, :Hq + Hkv].float(), table, pos, interleaved)
+    tol = 2e-2 if dtype == torch.bfloat16 else 1e-5
+    _close(qkv[:, :Hq + Hkv], exp, tol, tol)
+    assert torch.equal(qkv[:, Hq + Hkv:], orig[:, Hq + Hkv:])
+    torch.ops.tb200.rope_(view, table, pos, interleaved, True)
+    _close(qkv, orig, 4e-2 if dtype == torch.bfloat16 else 1e-5)
+    assert torch.ops.tb200.status(True) == 0
+
+
+def test_rope_out_of_range_position_sets_status_without_trapping():
+    table = ref.rope_table(64, 16, 10000.0).cuda()
+    x = torch.randn(4, 2, 64, device="cuda", dtype=torch.bfloat16)
+    pos = torch.tensor([0, 3, 99, 5], device="cuda")
+    torch.ops.tb200.rope_(x, table, pos, True, False)
+    torch.cuda.synchronize()
+    assert torch.ops.tb200.status(True) & 1
+    assert torch.ops.tb200.status(False) == 0
+    assert torch.isfinite(x.float()).all()
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_swiglu(dtype):
+    torch.manual_seed(2)
+    gu = torch.randn(513, 2 * 1536, device="cuda", dtype=dtype)
+    d = torch.randn(513, 1536, device="cuda", dtype=dtype)
+    out = torch.ops.tb200.swiglu_fwd(gu)
+    F = 1536
+    tol = 3e-2 if dtype == torch.bfloat16 else 1e-5
+    _close(out, ref.swiglu_fwd(gu[:, :F].float(), gu[:, F:].float()), tol, tol)
+    dgu = torch.ops.tb200.swiglu_bwd(gu, d)
+    dg, du = ref.swiglu_bwd(gu[:, :F].float(), gu[:, F:].float(), d.float())
+    _close(dgu[:, :F], dg, tol, tol)
+    _close(dgu[:, F:], du, tol, tol)
+
+
+@pytest.mark.parametrize("V,dtype", [(128256, torch.bfloat16), (2048, torch.bfloat16), (1003, torch.bfloat16),
+                                     (777, torch.float32)])
+def test_cross_entropy(V, dtype):
+    torch.manual_seed(3)
+    T = 96
+    logits = (torch.randn(T, V, device="cuda") * 3).to(dtype)
+    labels = torch.randint(0, V, (T,), device="cuda")
+    labels[::7] = -100
+    scale = torch.tensor([0.37], device="cuda")
+    loss_r, dl_r, _ = ref.cross_entropy_fwd_bwd(logits.float(), labels, 0.37)
+    work = logits.clone()
+    row = torch.ops.tb200.cross_entropy_(work, labels, scale)
+    _close(row.sum(), loss_r, 1e-2 if dtype == torch.bfloat16 else 1e-3, 1e-4)
+    _close(work, dl_r, 2e-3 if dtype == torch.bfloat16 else 1e-6, 2e-2)
+    assert (work[::7] == 0).all()
+
+
+@pytest.mark.parametrize("gdt,sdt,pdt", [(torch.bfloat16, torch.float32, torch.bfloat16),
+                                         (torch.float32, torch.float32, torch.bfloat16),
+                                         (torch.float32, torch.bfloat16, torch.bfloat16),
+                                         (torch.float32, torch.float32, torch.float32)])
+def test_adamw(gdt, sdt, pdt):
+    torch.manual_seed(4)
+    n = 100003
+    master = torch.randn(n, device="cuda")
+    m = (torch.randn(n, device="cuda") * 0.01).to(sdt)
+    v = (torch.rand(n, device="cuda") * 0.01).to(sdt)
+    g = torch.randn(n, device="cuda").to(gdt)
+    lowp = torch.empty(n, device="cuda", dtype=pdt)
+    rm, rmm, rv = master.clone(), m.clone(), v.clone()
+    rl = torch.empty(n, device="cuda", dtype=pdt)
+    scale = torch.tensor([0.5], device="cuda")
+    kw = dict(lr=3e-3, beta1=0.9, beta2=0.95, eps=1e-8, weight_decay=0.1, step=3)
+    optim_ops.adamw_(master, g, m, v, lowp, grad_scale=scale, **kw)
+    ref.adamw_step(rm, g, rmm, rv, grad_scale=0.5, out_lowp=rl, **kw)
+    _close(master, rm, 1e-5, 1e-5)
+    _close(m, rmm, 1e-6 if sdt == torch.float32 else 1e-3, 1e-2 if sdt == torch.bfloat16 else 1e-5)
+    _close(v, rv, 1e-6 if sdt == torch.float32 else 1e-3, 1e-2 if sdt == torch.bfloat16 else 1e-5)
+    _close(lowp, rl, 1e-5 if pdt == torch.float32 else 2e-2, 1e-2)
+
+
+def test_adamw_skips_on_non_finite_scale():
+    n = 4096
+    master = torch.randn(n, device="cuda")
+    before = master.clone()
+    m = torch.zeros(n, device="cuda")
+    v = torch.zeros(n, device="cuda")
+    g = torch.randn(n, device="cuda")
+    lowp = torch.zeros(n, device="cuda", dtype=torch.bfloat16)
+    optim_ops.adamw_(master, g, m, v, lowp, lr=1e-2, beta1=0.9, beta2=0.95, eps=1e-8, weight_decay=0.1, step=1,
+                     grad_scale=torch.tensor([float("nan")], device="cuda"))
+    assert torch.equal(master, before) and (m == 0).all() and (lowp == 0).all()
+
+
+def test_sumsq():
+    x = torch.randn(1 << 20, device="cuda")
+    acc = torch.zeros(1, device="cuda")
+    optim_ops.sumsq_accumulate(x, acc)
+    optim_ops.sumsq_accumulate(x.bfloat16(), acc)
+    exp = x.double().pow(2).sum() + x.bfloat16().double().pow(2).sum()
+    _close(acc, exp.float(), 1.0, 1e-4)
+
+
+def test_fused_functions_bf16_against_fp32_autograd():
+    """norm_linear + rope + attention + swiglu_linear through the CUDA path vs fp32 autograd."""
+    torch.manual_seed(5)
+    T, D, F = 256, 512, 1024
+    x = torch.randn(T, D, device="cuda")
+    nw = torch.rand(D, device="cuda") + 0.5
+    W13 = torch.randn(2 * F, D, device="cuda") * 0.05
+    W2 = torch.randn(D, F, device="cuda") * 0.05
+    g = torch.randn(T, D, device="cuda")
+
+    def run(dtype, fused):
+        xs = [t.detach().to(dtype).requires_grad_() for t in (x, nw, W13, W2)]
+        if fused:
+            gu = OF.norm_linear(xs[0], xs[1], xs[2], 1e-5)
+            out = OF.swiglu_linear(gu, xs[3])
+        else:
+            xf = xs[0]
+            xn = xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + 1e-5) * xs[1]
+            gu = xn @ xs[2].t()
+            out = (torch.nn.functional.silu(gu[:, :F]) * gu[:, F:]) @ xs[3].t()
+        out.backward(g.to(dtype))
+        return out, [t.grad for t in xs]
+
+    o1, g1 = run(torch.bfloat16, True)
+    o2, g2 = run(torch.float32, False)
+    _close(o1, o2, 5e-2, 5e-2)
+    for a, b in zip(g1, g2):
+        _close(a, b, 0.15 * float(b.abs().max()), 5e-2)
+
+
+def test_linear_cross_entropy_cuda():
+    torch.manual_seed(6)
+    T, D, V = 512, 256, 4096
+    h = (torch.randn(T, D, device="cuda") * 0.5)
+    W = torch.randn(V, D, device="cuda") * 0.05
+    labels = torch.randint(0, V, (T,), device="cuda")
+    labels[:17] = -100
+    inv = torch.tensor(1.0 / (T - 17), device="cuda")
+    hb, Wb = h.bfloat16().requires_grad_(), W.bfloat16().requires_grad_()
+    loss = OF.linear_cross_entropy(hb, Wb, labels, inv, 4)
+    loss.backward()
+    hf, Wf = h.bfloat16().float().requires_grad_(), W.bfloat16().float().requires_grad_()
+    l2 = torch.nn.functional.cross_entropy(hf @ Wf.t(), labels, ignore_index=-100, reduction="sum") * inv
+    l2.backward()
+    _close(loss, l2, 2e-2)
+    _close(hb.grad, hf.grad, 0.05 * float(hf.grad.abs().max()), 5e-2)
+    _close(Wb.grad, Wf.grad, 0.05 * float(Wf.grad.abs().max()), 5e-2)

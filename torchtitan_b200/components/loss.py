@@ -86,6 +86,10 @@ class LinearCrossEntropyLoss(BaseLoss):
                 from torchtitan_b200.parallel import tp_ops
 
                 hidden = tp_ops.all_gather_rows(hidden, self.tp)
+            else:
+                from torchtitan_b200.parallel import tp_ops
+
+                hidden = tp_ops.copy_to_tp(hidden, self.tp)
             return vocab_parallel_linear_cross_entropy(hidden, w, labels, inv, self.tp, self.config.num_chunks)
         if self.softcap:
             logits = OF.linear(hidden, w)
@@ -153,8 +157,8 @@ class _VocabParallelLinearCE(torch.autograd.Function):
                 weight._main_grad_written = True
             else:
                 dw.addmm_(p.t().float(), h2[s:e].float())
-        # dh is a partial sum over the vocabulary shards
-        dist.all_reduce(dh, group=tp.group)
+        # dh stays a partial sum over the vocabulary shards: the caller's all-gather /
+        # copy-to-tp autograd function reduces it in its backward
         ctx.save_for_backward(dh, dw)
         ctx.weight = weight
         ctx.hshape = hidden.shape

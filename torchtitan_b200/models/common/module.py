@@ -56,9 +56,12 @@ def materialize_param(shape, spec: InitSpec, seed: int, fqn: str, device="cpu") 
         return torch.zeros(shape, dtype=torch.float32, device=device)
     if spec.kind == "constant":
         return torch.full(shape, spec.value, dtype=torch.float32, device=device)
-    gen = torch.Generator(device="cpu")
+    # The stream is generated on the target device type (Philox on CUDA, MT on CPU): values
+    # are reproducible per device type and independent of the parallel layout.
+    gdev = torch.device(device) if torch.device(device).type == "cuda" else torch.device("cpu")
+    gen = torch.Generator(device=gdev)
     gen.manual_seed(fqn_seed(seed, fqn))
-    t = torch.empty(shape, dtype=torch.float32)
+    t = torch.empty(shape, dtype=torch.float32, device=gdev)
     if spec.kind == "normal":
         t.normal_(spec.mean, spec.std, generator=gen)
     elif spec.kind == "trunc_normal":

@@ -1,0 +1,32 @@
+// Operator registration: everything is exposed under torch.ops.tb200.
+#include <ATen/ATen.h>
+#include <torch/library.h>
+
+namespace tb200 {
+std::tuple<at::Tensor, at::Tensor> rmsnorm_fwd(const at::Tensor& x, const c10::optional<at::Tensor>& w, double eps);
+std::tuple<at::Tensor, at::Tensor> rmsnorm_bwd(const at::Tensor& dy, const at::Tensor& x,
+                                               const c10::optional<at::Tensor>& w, const at::Tensor& rstd);
+void rope_(at::Tensor x, const at::Tensor& table, const at::Tensor& positions, bool interleaved, bool inverse);
+at::Tensor swiglu_fwd(const at::Tensor& gu);
+at::Tensor swiglu_bwd(const at::Tensor& gu, const at::Tensor& dout);
+int64_t status(bool clear);
+at::Tensor cross_entropy_(at::Tensor logits, const at::Tensor& labels, const at::Tensor& scale);
+void adamw_(at::Tensor master, const at::Tensor& grad, at::Tensor exp_avg, at::Tensor exp_avg_sq,
+            const c10::optional<at::Tensor>& lowp, const at::Tensor& grad_scale, double lr, double beta1,
+            double beta2, double eps, double weight_decay, double bc1, double bc2);
+void sumsq_(const at::Tensor& x, at::Tensor acc);
+}  // namespace tb200
+
+TORCH_LIBRARY(tb200, m) {
+  m.def("rmsnorm_fwd(Tensor x, Tensor? w, float eps) -> (Tensor, Tensor)", &tb200::rmsnorm_fwd);
+  m.def("rmsnorm_bwd(Tensor dy, Tensor x, Tensor? w, Tensor rstd) -> (Tensor, Tensor)", &tb200::rmsnorm_bwd);
+  m.def("rope_(Tensor(a!) x, Tensor table, Tensor positions, bool interleaved, bool inverse) -> ()", &tb200::rope_);
+  m.def("swiglu_fwd(Tensor gu) -> Tensor", &tb200::swiglu_fwd);
+  m.def("swiglu_bwd(Tensor gu, Tensor dout) -> Tensor", &tb200::swiglu_bwd);
+  m.def("status(bool clear) -> int", &tb200::status);
+  m.def("cross_entropy_(Tensor(a!) logits, Tensor labels, Tensor scale) -> Tensor", &tb200::cross_entropy_);
+  m.def("adamw_(Tensor(a!) master, Tensor grad, Tensor(b!) exp_avg, Tensor(c!) exp_avg_sq, Tensor(d!)? lowp, "
+        "Tensor grad_scale, float lr, float beta1, float beta2, float eps, float weight_decay, float bc1, float bc2) -> ()",
+        &tb200::adamw_);
+  m.def("sumsq_(Tensor x, Tensor(a!) acc) -> ()", &tb200::sumsq_);
+}

@@ -410,7 +410,15 @@ def rope_qk_(qkv: torch.Tensor, table: torch.Tensor, positions: torch.Tensor, in
 def _sdpa_causal(q, k, v, scale):
     """Library attention (cuDNN / flash) on ``[T,H,D]`` tensors: the baseline path."""
     qh, kh, vh = (t.transpose(0, 1).unsqueeze(0) for t in (q, k, v))
-    out = F.scaled_dot_product_attention(qh, kh, vh, is_causal=True, scale=scale, enable_gqa=(q.shape[1] != k.shape[1]))
+    gqa = q.shape[1] != k.shape[1]
+    if q.is_cuda:
+        from torch.nn.attention import SDPBackend, sdpa_kernel
+
+        order = [SDPBackend.CUDNN_ATTENTION, SDPBackend.FLASH_ATTENTION, SDPBackend.EFFICIENT_ATTENTION, SDPBackend.MATH]
+        with sdpa_kernel(order, set_priority=True):
+            out = F.scaled_dot_product_attention(qh, kh, vh, is_causal=True, scale=scale, enable_gqa=gqa)
+    else:
+        out = F.scaled_dot_product_attention(qh, kh, vh, is_causal=True, scale=scale, enable_gqa=gqa)
     return out.squeeze(0).transpose(0, 1)
 
 
@@ -500,7 +508,8 @@ def _ce_inplace(logits: torch.Tensor, labels: torch.Tensor, grad_scale: torch.Te
     """Turn ``logits`` into ``dlogits`` in place and add the summed loss into ``loss_acc``."""
     if _cuda(logits):
         _count()
-        ext.require().cross_entropy_(logits, labels, grad_scale, loss_acc)
+        row_loss = ext.require().cross_entropy_(logits, labels, grad_scale)
+        loss_acc.add_(row_loss.sum())
         return logits
     loss, dl, _ = ref.cross_entropy_fwd_bwd(logits, labels, grad_scale)
     loss_acc.add_(loss)

@@ -251,7 +251,7 @@ class ShardedModel:
             shape = p.shape
             return materialize_param(shape, spec, self.seed, name, self.device)
         dim, ranges, gshape = tps
-        full = materialize_param(gshape, spec, self.seed, name, "cpu")
+        full = materialize_param(gshape, spec, self.seed, name, self.device)
         parts = [full.narrow(dim, a, b - a) for a, b in ranges]
         return torch.cat(parts, dim=dim).contiguous().to(self.device)
 

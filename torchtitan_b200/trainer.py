@@ -315,14 +315,21 @@ class Trainer(Configurable):
         self.optimizers.zero_grad()
         n_mb = self.gradient_accumulation_steps * (c.parallelism.num_pp_microbatches if pd.pp_enabled else 1)
         microbatches = []
-        local_valid = 0
+        host_valid = 0
+        dev_valid = None
         for _ in range(n_mb):
             inputs, labels = next(data_iterator)
-            local_valid += int((labels != IGNORE_INDEX).sum())
+            if labels.is_cuda:  # device-resident batches: count without a host sync
+                n = (labels != IGNORE_INDEX).sum().to(torch.float32)
+                dev_valid = n if dev_valid is None else dev_valid + n
+            else:
+                host_valid += int((labels != IGNORE_INDEX).sum())
             microbatches.append((inputs, labels))
             self.ntokens_seen += labels.numel() * pd.dp_degree
             self.metrics_processor.ntokens_since_last_log += labels.numel()
-        valid = torch.tensor([float(local_valid)], dtype=torch.float32, device=self.device)
+        valid = torch.tensor([float(host_valid)], dtype=torch.float32).to(self.device, non_blocking=True)
+        if dev_valid is not None:
+            valid = valid + dev_valid
         g = pd.group("batch")
         if g is not None:
             dist.all_reduce(valid, group=g)
