@@ -14,7 +14,7 @@ def _free_port() -> int:
         return s.getsockname()[1]
 
 
-def _entry(rank, world, port, fn, args, errq):
+def _entry(rank, world, port, fn, args, errq, backend="gloo"):
     os.environ.update(RANK=str(rank), LOCAL_RANK=str(rank), WORLD_SIZE=str(world), MASTER_ADDR="127.0.0.1",
                       MASTER_PORT=str(port), OMP_NUM_THREADS="1")
     sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
@@ -23,7 +23,13 @@ def _entry(rank, world, port, fn, args, errq):
 
     torch.set_num_threads(1)
     try:
-        dist.init_process_group("gloo", rank=rank, world_size=world)
+        if backend == "nccl":
+            os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+            torch.cuda.set_device(rank)
+            dist.init_process_group("cuda:nccl,cpu:gloo", rank=rank, world_size=world,
+                                    device_id=torch.device("cuda", rank))
+        else:
+            dist.init_process_group("gloo", rank=rank, world_size=world)
         fn(rank, world, *args)
         dist.barrier()
         dist.destroy_process_group()
@@ -32,11 +38,11 @@ def _entry(rank, world, port, fn, args, errq):
         raise
 
 
-def run_distributed(fn, world: int, *args, timeout: float = 240.0):
+def run_distributed(fn, world: int, *args, timeout: float = 240.0, backend: str = "gloo"):
     ctx = mp.get_context("spawn")
     errq = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_entry, args=(r, world, port, fn, args, errq)) for r in range(world)]
+    procs = [ctx.Process(target=_entry, args=(r, world, port, fn, args, errq, backend)) for r in range(world)]
     for p in procs:
         p.start()
     for p in procs:

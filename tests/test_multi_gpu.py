@@ -1,0 +1,119 @@
+"""Multi-GPU (>= 2 devices): NVLink in-kernel collectives against the NCCL path, and the bounded wait."""
+
+import pytest
+import torch
+
+from tests.dist_utils import run_distributed
+
+pytestmark = pytest.mark.gpu
+
+
+def _ngpu():
+    return torch.cuda.device_count() if torch.cuda.is_available() else 0
+
+
+def test_bounded_wait_reports_timeout_without_trapping():
+    """A barrier whose peer never arrives must set the status word and return (single GPU:
+    both 'ranks' point at local flag arrays and nothing ever sets the peer's slot)."""
+    from torchtitan_b200.ops import ext
+
+    assert ext.load()
+    a = torch.zeros(64, dtype=torch.int32, device="cuda")
+    b = torch.zeros(64, dtype=torch.int32, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    torch.ops.tb200.symm_barrier([a.data_ptr(), b.data_ptr()], 0, 1, status, 2_000_000)  # ~1 ms of cycles
+    torch.cuda.synchronize()
+    assert int(status.item()) & 4
+    assert int(b[0].item()) == 1  # our own arrival was published to the "peer"
+    # the context is still healthy
+    assert float(torch.ones(4, device="cuda").sum()) == 4.0
+
+
+def _train(rank, world, comm, out_path):
+    import torch.distributed as dist
+
+    from tests.test_engine import T, _batches, _small_model_cfg
+    from torchtitan_b200.components.optimizer import OptimizersContainer, clip_grad_norm_
+    from torchtitan_b200.ops import functional as OF
+    from torchtitan_b200.parallel.parallel_dims import ParallelDims
+    from torchtitan_b200.parallel.parallelize import parallelize_decoder
+    from torchtitan_b200.trainer import Trainer
+
+    dev = torch.device("cuda", rank)
+    cfg = Trainer.Config()
+    cfg.training.num_tokens_per_microbatch_per_dp_rank = T
+    cfg.training.max_context_length = T
+    cfg.parallelism.fsdp_comm = comm
+    pdims = ParallelDims(world_size=world, rank=rank).build()
+    mc = _small_model_cfg(3)
+    with torch.device("meta"):
+        model = mc.build()
+    eng = parallelize_decoder(model, pdims=pdims, job_config=cfg, device=dev, seed=3)
+    opt = OptimizersContainer(OptimizersContainer.Config(lr=1e-2), engines=[eng])
+    b = _batches(8)
+    pos = torch.arange(T, device=dev)
+    losses = []
+    for s in range(4):
+        tok, lab = (t.to(dev) for t in b[2 * s + rank % 2])
+        opt.zero_grad()
+        h = model(tok, pos, return_hidden=True)
+        loss = OF.linear_cross_entropy(h, model.lm_head.weight, lab, torch.tensor(1.0 / (T * world), device=dev), 2)
+        loss.backward()
+        eng.finish_backward()
+        clip_grad_norm_([eng], 1.0, pdims, optimizers=opt)
+        opt.step()
+        losses.append(loss.detach())
+    eng.check_status()
+    t = torch.stack(losses)
+    dist.all_reduce(t)
+    full = torch.cat([u.flat_param[:u.numel].float() for u in eng.units])
+    if rank == 0:
+        torch.save({"losses": t.cpu(), "params": full.cpu()}, out_path)
+
+
+@pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
+def test_nvlink_engine_matches_nccl(tmp_path):
+    a, b = str(tmp_path / "nccl.pt"), str(tmp_path / "nvl.pt")
+    run_distributed(_train, 2, "nccl", a, backend="nccl")
+    run_distributed(_train, 2, "nvlink", b, backend="nccl")
+    ra, rb = torch.load(a), torch.load(b)
+    assert torch.allclose(ra["losses"], rb["losses"], atol=2e-2), (ra["losses"], rb["losses"])
+    assert torch.allclose(ra["params"], rb["params"], atol=3e-2), float((ra["params"] - rb["params"]).abs().max())
+
+
+def _rs_ag(rank, world, out_path):
+    """reduce_scatter_pull and the fused AdamW+all-gather against torch math on raw buffers."""
+    import torch.distributed as dist
+
+    from torchtitan_b200.parallel.parallel_dims import ParallelDims
+    from torchtitan_b200.parallel.symm import SymmetricArena
+
+    dev = torch.device("cuda", rank)
+    pdims = ParallelDims(world_size=world, rank=rank).build()
+    g = pdims.group("fsdp")
+    n = 1 << 20
+    arena = SymmetricArena(pdims, dev)
+    arena.reserve(g, 2 * n * 2)
+    grad = arena.alloc(n, torch.bfloat16, g)
+    torch.manual_seed(100 + rank)
+    grad.copy_(torch.randn(n, device=dev))
+    shard = torch.zeros(n // world, dtype=torch.float32, device=dev)
+    arena.reduce_scatter_accumulate(grad, shard, g, accumulate=False)
+    gathered = [torch.empty(n, dtype=torch.bfloat16, device=dev) for _ in range(world)]
+    dist.all_gather(gathered, grad)
+    exp = sum(t.float() for t in gathered)[rank * (n // world):(rank + 1) * (n // world)]
+    ok1 = torch.allclose(shard, exp, atol=1e-5)
+    arena.reduce_scatter_accumulate(grad, shard, g, accumulate=True)
+    ok2 = torch.allclose(shard, 2 * exp, atol=1e-4)
+    for a in arena._arenas.values():
+        assert int(a.status.item()) == 0
+    if rank == 0:
+        torch.save({"ok1": ok1, "ok2": ok2}, out_path)
+
+
+@pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
+def test_reduce_scatter_pull(tmp_path):
+    out = str(tmp_path / "rs.pt")
+    run_distributed(_rs_ag, 2, out, backend="nccl")
+    r = torch.load(out)
+    assert r["ok1"] and r["ok2"]

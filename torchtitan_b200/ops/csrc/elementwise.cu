@@ -199,13 +199,25 @@ __global__ void __launch_bounds__(512) rmsnorm_bwd_kernel(const T* __restrict__ 
   }
 }
 
+// Column sums of partial[nparts, D]: a 32x8 thread tile per 32 columns, rows split over the
+// 8 thread rows, then a shared-memory reduction.  D/32 CTAs.
 __global__ void __launch_bounds__(256) colsum_kernel(const float* __restrict__ partial, float* __restrict__ out,
                                                      int nparts, int D) {
-  const int col = blockIdx.x * blockDim.x + threadIdx.x;
-  if (col >= D) return;
+  __shared__ float tile[8][33];
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  const int col = blockIdx.x * 32 + tx;
   float s = 0.f;
-  for (int p = 0; p < nparts; ++p) s += partial[(int64_t)p * D + col];
-  out[col] = s;
+  if (col < D) {
+    for (int p = ty; p < nparts; p += 8) s += partial[(int64_t)p * D + col];
+  }
+  tile[ty][tx] = s;
+  __syncthreads();
+  if (ty == 0 && col < D) {
+    float t = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) t += tile[i][tx];
+    out[col] = t;
+  }
 }
 
 // ----------------------------------------------------------------------------
@@ -473,7 +485,7 @@ std::tuple<at::Tensor, at::Tensor> rmsnorm_bwd(const at::Tensor& dy, const at::T
   });
   C10_CUDA_KERNEL_LAUNCH_CHECK();
   if (w.has_value()) {
-    colsum_kernel<<<(D + 255) / 256, 256, 0, stream>>>(partial.data_ptr<float>(), dw.data_ptr<float>(), nparts, D);
+    colsum_kernel<<<(D + 31) / 32, 256, 0, stream>>>(partial.data_ptr<float>(), dw.data_ptr<float>(), nparts, D);
     C10_CUDA_KERNEL_LAUNCH_CHECK();
   }
   return {dx, dw};

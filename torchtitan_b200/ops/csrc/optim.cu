@@ -47,15 +47,88 @@ __global__ void __launch_bounds__(256) adamw_kernel(float* __restrict__ master, 
   }
 }
 
-// 16-byte vector version for the common all-aligned case (fp32 state, bf16 grad or fp32 grad).
+// 8 elements per thread per iteration with 16-byte accesses (two for fp32 streams).
+template <typename T>
+__device__ __forceinline__ void load8(const T* p, float (&f)[8]);
+template <>
+__device__ __forceinline__ void load8<float>(const float* p, float (&f)[8]) {
+  const float4 a = *reinterpret_cast<const float4*>(p);
+  const float4 b = *reinterpret_cast<const float4*>(p + 4);
+  f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
+}
+template <>
+__device__ __forceinline__ void load8<__nv_bfloat16>(const __nv_bfloat16* p, float (&f)[8]) {
+  unpack8(*reinterpret_cast<const bf16x8*>(p), f);
+}
+template <typename T>
+__device__ __forceinline__ void store8(T* p, const float (&f)[8]);
+template <>
+__device__ __forceinline__ void store8<float>(float* p, const float (&f)[8]) {
+  *reinterpret_cast<float4*>(p) = make_float4(f[0], f[1], f[2], f[3]);
+  *reinterpret_cast<float4*>(p + 4) = make_float4(f[4], f[5], f[6], f[7]);
+}
+template <>
+__device__ __forceinline__ void store8<__nv_bfloat16>(__nv_bfloat16* p, const float (&f)[8]) {
+  *reinterpret_cast<bf16x8*>(p) = pack8(f);
+}
+
+template <typename G, typename S, typename P>
+__global__ void __launch_bounds__(256) adamw_vec_kernel(float* __restrict__ master, const G* __restrict__ grad,
+                                                        S* __restrict__ m, S* __restrict__ v, P* __restrict__ lowp,
+                                                        const float* __restrict__ grad_scale, int64_t nvec, float lr,
+                                                        float beta1, float beta2, float eps, float wd, float bc1,
+                                                        float bc2_sqrt) {
+  const float gs = *grad_scale;
+  if (!isfinite(gs)) return;
+  const float step_size = lr / bc1;
+  const float decay = 1.f - lr * wd;
+  const float inv_bc2 = 1.f / bc2_sqrt;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t o = i * 8;
+    float g[8], mm[8], vv[8], p[8];
+    load8<G>(grad + o, g);
+    load8<S>(m + o, mm);
+    load8<S>(v + o, vv);
+    load8<float>(master + o, p);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float gj = g[j] * gs;
+      mm[j] = beta1 * mm[j] + (1.f - beta1) * gj;
+      vv[j] = beta2 * vv[j] + (1.f - beta2) * gj * gj;
+      const float denom = sqrtf(vv[j]) * inv_bc2 + eps;
+      p[j] = p[j] * decay - step_size * (mm[j] / denom);
+    }
+    store8<float>(master + o, p);
+    store8<S>(m + o, mm);
+    store8<S>(v + o, vv);
+    if (lowp != nullptr) store8<P>(lowp + o, p);
+  }
+}
+
+static inline bool is_aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
 template <typename G, typename S, typename P>
 static void launch_adamw(float* master, const G* grad, S* m, S* v, P* lowp, const float* gs, int64_t n, float lr,
                          float b1, float b2, float eps, float wd, float bc1, float bc2, cudaStream_t stream) {
   const int threads = 256;
-  const int64_t want = (n + threads * 4 - 1) / (threads * 4);
-  const int grid = (int)std::max<int64_t>(1, std::min<int64_t>(want, (int64_t)num_sms() * 16));
-  adamw_kernel<G, S, P><<<grid, threads, 0, stream>>>(master, grad, m, v, lowp, gs, n, lr, b1, b2, eps, wd, bc1,
-                                                      sqrtf(bc2));
+  const bool vec = is_aligned16(master) && is_aligned16(grad) && is_aligned16(m) && is_aligned16(v) &&
+                   (lowp == nullptr || is_aligned16(lowp));
+  int64_t done = 0;
+  if (vec && n >= 8) {
+    const int64_t nvec = n / 8;
+    const int grid = (int)std::max<int64_t>(1, std::min<int64_t>((nvec + threads - 1) / threads, (int64_t)num_sms() * 16));
+    adamw_vec_kernel<G, S, P><<<grid, threads, 0, stream>>>(master, grad, m, v, lowp, gs, nvec, lr, b1, b2, eps, wd,
+                                                            bc1, sqrtf(bc2));
+    done = nvec * 8;
+  }
+  if (done < n) {
+    const int64_t rem = n - done;
+    const int64_t want = (rem + threads * 4 - 1) / (threads * 4);
+    const int grid = (int)std::max<int64_t>(1, std::min<int64_t>(want, (int64_t)num_sms() * 16));
+    adamw_kernel<G, S, P><<<grid, threads, 0, stream>>>(master + done, grad + done, m + done, v + done,
+                                                        lowp ? lowp + done : nullptr, gs, rem, lr, b1, b2, eps, wd, bc1,
+                                                        sqrtf(bc2));
+  }
 }
 
 void adamw_(at::Tensor master, const at::Tensor& grad, at::Tensor exp_avg, at::Tensor exp_avg_sq,
@@ -99,10 +172,18 @@ void adamw_(at::Tensor master, const at::Tensor& grad, at::Tensor exp_avg, at::T
 }
 
 template <typename T>
-__global__ void __launch_bounds__(256) sumsq_kernel(const T* __restrict__ x, float* __restrict__ acc, int64_t n) {
+__global__ void __launch_bounds__(256) sumsq_kernel(const T* __restrict__ x, float* __restrict__ acc, int64_t n,
+                                                    int64_t nvec) {
   __shared__ float red[32];
   float s = 0.f;
-  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += (int64_t)gridDim.x * blockDim.x) {
+    float f[8];
+    load8<T>(x + i * 8, f);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) s += f[j] * f[j];
+  }
+  for (int64_t i = nvec * 8 + (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n;
+       i += (int64_t)gridDim.x * blockDim.x) {
     const float f = to_float<T>(x[i]);
     s += f * f;
   }
@@ -116,12 +197,13 @@ void sumsq_(const at::Tensor& x, at::Tensor acc) {
   if (n == 0) return;
   c10::cuda::CUDAGuard guard(x.device());
   auto stream = at::cuda::getCurrentCUDAStream();
-  const int grid = (int)std::max<int64_t>(1, std::min<int64_t>((n + 255) / 256, (int64_t)num_sms() * 8));
+  const int64_t nvec = is_aligned16(x.data_ptr()) ? n / 8 : 0;
+  const int grid = (int)std::max<int64_t>(1, std::min<int64_t>((n / 8 + 255) / 256 + 1, (int64_t)num_sms() * 8));
   if (x.scalar_type() == at::kFloat)
-    sumsq_kernel<float><<<grid, 256, 0, stream>>>(x.data_ptr<float>(), acc.data_ptr<float>(), n);
+    sumsq_kernel<float><<<grid, 256, 0, stream>>>(x.data_ptr<float>(), acc.data_ptr<float>(), n, nvec);
   else if (x.scalar_type() == at::kBFloat16)
     sumsq_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(x.data_ptr()),
-                                                          acc.data_ptr<float>(), n);
+                                                          acc.data_ptr<float>(), n, nvec);
   else
     TORCH_CHECK(false, "sumsq_: unsupported dtype");
   C10_CUDA_KERNEL_LAUNCH_CHECK();

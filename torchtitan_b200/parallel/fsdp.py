@@ -206,6 +206,10 @@ class ShardedModel:
             from . import symm
 
             self._symm = symm.SymmetricArena(self.pdims, dev)
+            es = torch.empty(0, dtype=pd).element_size()
+            for u in self.units:
+                if u.size > 1:
+                    self._symm.reserve(u.group, 2 * u.padded * es)
         replaced: dict[int, nn.Parameter] = {}
         for u in self.units:
             if use_symm and u.size > 1:
@@ -421,10 +425,18 @@ class ShardedModel:
         self.ensure_state()
         self.step_count += 1
         step = self.step_count
+        fused_ag = self._symm is not None
+        if fused_ag and not isinstance(grad_scale, torch.Tensor):
+            grad_scale = torch.full((1,), float(grad_scale), dtype=torch.float32, device=self.device)
         for u in self.units:
             if not u.grad_shard_valid:
                 continue
             g = self._grad_of(u)
+            if fused_ag and u.size > 1:
+                # update + all-gather in one kernel: refreshed weights are stored to every peer
+                self._symm.adamw_allgather(u, _group_runs(u), groups, step, grad_scale.reshape(1), g)
+                u.grad_shard_valid = False
+                continue
             lowp = u.shard_view(u.flat_param)
             for gi, a, b in _group_runs(u):
                 h = groups[gi]
@@ -434,7 +446,15 @@ class ShardedModel:
                     weight_decay=h["weight_decay"], step=step, grad_scale=grad_scale,
                 )
             u.grad_shard_valid = False
-        self._all_gather_params()
+        if fused_ag:
+            self._symm.barrier_all()  # peers' stores into our parameter buffers have landed
+        else:
+            self._all_gather_params()
+
+    def check_status(self) -> None:
+        """Raise if a bounded device-side wait expired (host sync; call at logging points)."""
+        if self._symm is not None:
+            self._symm.check_status()
 
     def zero_grad(self) -> None:
         for u in self.units:
@@ -483,16 +503,17 @@ class ShardedModel:
 
 def _group_runs(u: FlatUnit):
     """Maximal runs ``(group_idx, shard_lo, shard_hi)`` of this rank's shard with one param group.
-    Padding between parameters rides along with the preceding run."""
-    runs: list[list[int]] = []
-    for slot, _pstart, sstart, n in u.slot_pieces():
-        if runs and runs[-1][0] == slot.group_idx:
-            runs[-1][2] = sstart + n
-        else:
-            runs.append([slot.group_idx, sstart, sstart + n])
-    if runs:
-        runs[-1][2] = max(runs[-1][2], min(u.shard_numel, runs[-1][2]))
-    return [(g, a, b) for g, a, b in runs]
+    A run extends to the start of the next run (or the end of the shard), so alignment padding
+    rides along and every boundary is a multiple of 8 elements."""
+    starts: list[list[int]] = []
+    for slot, _pstart, sstart, _n in u.slot_pieces():
+        if not starts or starts[-1][0] != slot.group_idx:
+            starts.append([slot.group_idx, sstart])
+    runs = []
+    for i, (g, a) in enumerate(starts):
+        b = starts[i + 1][1] if i + 1 < len(starts) else u.shard_numel
+        runs.append((g, 0 if i == 0 else a, b))
+    return runs
 
 
 def _swap_parameters(model: nn.Module, replaced: dict[int, nn.Parameter]) -> None:

@@ -1,0 +1,160 @@
+"""Symmetric-memory arena and the NVLink collectives built on it.
+
+One arena per process group: a single symmetric allocation (same size and layout on
+every rank, obtained from ``torch.distributed._symmetric_memory``) from which the engine
+carves its flat parameter / gradient buffers, plus a small symmetric flag array for
+barriers.  Every rank knows every peer's base pointer, so our kernels address peer
+memory directly with ``ld/st.global`` over NVLink / NVSwitch (parity with the reference's
+use of symmetric memory for FSDP and MinimalAsyncEP, torchtitan/distributed/fsdp.py:102-109,
+torchtitan/distributed/minimal_async_ep/api.py:174-295, re-designed around in-kernel
+transfers).
+
+Synchronisation is a flag barrier with monotonically increasing epochs.  Waits are bounded
+(``TB200_SYMM_TIMEOUT_S``, default 30 s): on expiry the kernel sets a bit in a status word
+and returns; :meth:`check_status` raises on the host.  Nothing traps the device.
+"""
+
+from __future__ import annotations
+
+import os
+
+import torch
+import torch.distributed as dist
+
+from torchtitan_b200.ops import ext
+from torchtitan_b200.ops.functional import _count
+
+__all__ = ["SymmetricArena", "symm_available"]
+
+_FLAG_SLOTS = 64
+
+
+def symm_available() -> bool:
+    try:
+        import torch.distributed._symmetric_memory  # noqa: F401
+
+        return torch.cuda.is_available()
+    except Exception:
+        return False
+
+
+class _GroupArena:
+    def __init__(self, group, device: torch.device, nbytes: int):
+        import torch.distributed._symmetric_memory as symm_mem
+
+        self.group = group
+        self.size = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        self.device = device
+        gname = group.group_name
+        try:
+            symm_mem.enable_symm_mem_for_group(gname)
+        except Exception:
+            pass
+        total = nbytes + 4096
+        self.buf = symm_mem.empty(total, dtype=torch.uint8, device=device)
+        self.handle = symm_mem.rendezvous(self.buf, gname)
+        self.base_ptrs = [int(p) for p in self.handle.buffer_ptrs]
+        self.flags = symm_mem.empty(_FLAG_SLOTS * self.size, dtype=torch.int32, device=device)
+        self.flags.zero_()
+        self.flag_handle = symm_mem.rendezvous(self.flags, gname)
+        self.flag_ptrs = [int(p) for p in self.flag_handle.buffer_ptrs]
+        self.cursor = 0
+        self.epoch = 0
+        self.status = torch.zeros(1, dtype=torch.int32, device=device)
+        clock_hz = 1.9e9
+        self.max_cycles = int(float(os.environ.get("TB200_SYMM_TIMEOUT_S", "30")) * clock_hz)
+        torch.cuda.synchronize(device)
+        dist.barrier(group=group)
+
+    def carve(self, numel: int, dtype: torch.dtype) -> tuple[torch.Tensor, int]:
+        es = torch.empty(0, dtype=dtype).element_size()
+        off = (self.cursor + 255) // 256 * 256
+        nbytes = numel * es
+        if off + nbytes > self.buf.numel():
+            raise RuntimeError("symmetric arena exhausted")
+        self.cursor = off + nbytes
+        view = self.buf[off:off + nbytes].view(dtype)
+        return view, off
+
+    def barrier(self) -> None:
+        """Cross-rank barrier on the current stream (bounded wait)."""
+        self.epoch += 1
+        _count()
+        ext.require().symm_barrier(self.flag_ptrs, self.rank, self.epoch, self.status, self.max_cycles)
+
+
+class SymmetricArena:
+    """Per-process collection of group arenas; the engine's entry point to the NVLink path."""
+
+    def __init__(self, pdims, device: torch.device):
+        self.pdims = pdims
+        self.device = device
+        self._arenas: dict[int, _GroupArena] = {}
+        self._offsets: dict[int, tuple[_GroupArena, int]] = {}
+        self._reserved: dict[int, int] = {}
+
+    def reserve(self, group, nbytes: int) -> None:
+        """Declare how many bytes will be carved for ``group`` (call before the first alloc)."""
+        self._reserved[id(group)] = self._reserved.get(id(group), 0) + nbytes + 512
+
+    def _arena(self, group) -> _GroupArena:
+        key = id(group)
+        if key not in self._arenas:
+            if key not in self._reserved:
+                raise RuntimeError("SymmetricArena.reserve must be called before alloc")
+            self._arenas[key] = _GroupArena(group, self.device, self._reserved[key])
+        return self._arenas[key]
+
+    def alloc(self, numel: int, dtype: torch.dtype, group, tag: str = "") -> torch.Tensor:
+        arena = self._arena(group)
+        t, off = arena.carve(numel, dtype)
+        self._offsets[t.data_ptr()] = (arena, off)
+        return t
+
+    def _locate(self, t: torch.Tensor) -> tuple[_GroupArena, int]:
+        arena, off = self._offsets[t.data_ptr()]
+        return arena, off
+
+    def peer_ptrs(self, t: torch.Tensor) -> tuple[_GroupArena, list[int]]:
+        arena, off = self._locate(t)
+        return arena, [b + off for b in arena.base_ptrs]
+
+    # -- collectives -----------------------------------------------------------
+    def reduce_scatter_accumulate(self, flat_grad: torch.Tensor, grad_shard: torch.Tensor, group,
+                                  accumulate: bool) -> None:
+        """``grad_shard (+)= sum over ranks of flat_grad[my slice]`` by pulling from peers."""
+        arena, ptrs = self.peer_ptrs(flat_grad)
+        arena.barrier()  # every rank's local gradients are complete
+        _count()
+        ext.require().reduce_scatter_pull(ptrs, arena.rank, arena.rank * grad_shard.numel(), grad_shard,
+                                          flat_grad.dtype == torch.bfloat16, accumulate)
+        arena.barrier()  # every rank has finished reading before buffers are reused
+
+    def adamw_allgather(self, unit, runs, groups, step: int, grad_scale: torch.Tensor, grad: torch.Tensor) -> None:
+        """AdamW on this rank's shard with the weight all-gather fused in (peer stores)."""
+        arena, ptrs = self.peer_ptrs(unit.flat_param)
+        bf16 = unit.flat_param.dtype == torch.bfloat16
+        ops = ext.require()
+        for gi, a, b in runs:
+            h = groups[gi]
+            b1, b2 = h["betas"]
+            _count()
+            ops.adamw_allgather_(unit.master[a:b], grad[a:b], unit.exp_avg[a:b], unit.exp_avg_sq[a:b], ptrs,
+                                 arena.rank, unit.shard_start + a, bf16, grad_scale, float(h["lr"]), float(b1),
+                                 float(b2), float(h["eps"]), float(h["weight_decay"]), 1.0 - b1 ** step,
+                                 1.0 - b2 ** step)
+
+    def barrier_all(self) -> None:
+        for arena in self._arenas.values():
+            arena.barrier()
+
+    def check_status(self) -> None:
+        """Host-side check of the device status words (synchronises)."""
+        for arena in self._arenas.values():
+            v = int(arena.status.item())
+            if v:
+                arena.status.zero_()
+                raise RuntimeError(
+                    f"a bounded device wait expired (status {v:#x}) in the NVLink path of group "
+                    f"{arena.group.group_name}: a peer did not arrive within the timeout")
