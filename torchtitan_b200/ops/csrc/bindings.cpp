@@ -15,6 +15,8 @@ void adamw_(at::Tensor master, const at::Tensor& grad, at::Tensor exp_avg, at::T
             const c10::optional<at::Tensor>& lowp, const at::Tensor& grad_scale, double lr, double beta1,
             double beta2, double eps, double weight_decay, double bc1, double bc2);
 void sumsq_(const at::Tensor& x, at::Tensor acc);
+void gemm_bf16(const at::Tensor& a, const at::Tensor& b, at::Tensor c, int64_t mode, bool accumulate);
+int64_t gemm_status(bool clear);
 void symm_barrier(at::IntArrayRef flag_ptrs, int64_t my_rank, int64_t epoch, at::Tensor status, int64_t max_cycles);
 void reduce_scatter_pull(at::IntArrayRef grad_ptrs, int64_t my_rank, int64_t offset, at::Tensor out, bool grad_is_bf16,
                          bool accumulate);
@@ -36,6 +38,8 @@ TORCH_LIBRARY(tb200, m) {
         "Tensor grad_scale, float lr, float beta1, float beta2, float eps, float weight_decay, float bc1, float bc2) -> ()",
         &tb200::adamw_);
   m.def("sumsq_(Tensor x, Tensor(a!) acc) -> ()", &tb200::sumsq_);
+  m.def("gemm_bf16(Tensor a, Tensor b, Tensor(a!) c, int mode, bool accumulate) -> ()", &tb200::gemm_bf16);
+  m.def("gemm_status(bool clear) -> int", &tb200::gemm_status);
   m.def("symm_barrier(int[] flag_ptrs, int my_rank, int epoch, Tensor(a!) status, int max_cycles) -> ()",
         &tb200::symm_barrier);
   m.def("reduce_scatter_pull(int[] grad_ptrs, int my_rank, int offset, Tensor(a!) out, bool grad_is_bf16, "

@@ -118,7 +118,7 @@ def _tc_gemm(a, b, mode, out, accumulate):
     else:
         K, M = a.shape
         N = b.shape[1]
-    if (K % 64) or (N % 8) or (M % 8) or K == 0:
+    if (N % 8) or K == 0 or ((M % 8) if mode == 2 else (K % 8)):
         return None
     if out is None:
         out = torch.empty(M, N, dtype=torch.bfloat16, device=a.device)

@@ -74,8 +74,12 @@ class _GroupArena:
         if off + nbytes > self.buf.numel():
             raise RuntimeError("symmetric arena exhausted")
         self.cursor = off + nbytes
-        view = self.buf[off:off + nbytes].view(dtype)
-        return view, off
+        # A fresh tensor over the same storage (not an autograd view of ``buf``): carved buffers
+        # must not share a version counter, or writing gradients would invalidate tensors that
+        # autograd saved from the parameter buffer.
+        t = torch.empty(0, dtype=dtype, device=self.device)
+        t.set_(self.buf.untyped_storage(), (self.buf.storage_offset() + off) // es, (numel,), (1,))
+        return t, off
 
     def barrier(self) -> None:
         """Cross-rank barrier on the current stream (bounded wait)."""
