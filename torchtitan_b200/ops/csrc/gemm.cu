@@ -370,6 +370,9 @@ void gemm_bf16(const at::Tensor& a, const at::Tensor& b, at::Tensor c, int64_t m
               (reinterpret_cast<uintptr_t>(c.data_ptr()) & 15) == 0, "gemm_bf16: operands must be 16-byte aligned");
   if (M == 0 || N == 0) return;
   c10::cuda::CUDAGuard guard(a.device());
+  // The tensor-map encoder is a driver-API call and needs the primary context current on this
+  // thread; autograd worker threads may not have bound it yet.
+  C10_CUDA_CHECK(cudaSetDevice(a.device().index()));
   using namespace gemm;
   // K-major: inner = K, box {64, rows};  MN-major: inner = MN extent, box {64, 64 k-rows}
   const CUtensorMap ta = a_mn ? make_tmap_2d(a.data_ptr(), M, K, M * 2, 64, BK)
