@@ -46,7 +46,7 @@ def parse_args():
     p.add_argument("--flavor", default="8B")
     p.add_argument("--seq-len", type=int, default=8192)
     p.add_argument("--local-batch", type=int, default=1)
-    p.add_argument("--fsdp-comm", default=os.environ.get("TB200_FSDP_COMM", "nccl"))
+    p.add_argument("--fsdp-comm", default=os.environ.get("TB200_FSDP_COMM", "auto"))
     p.add_argument("--gemm", default=os.environ.get("TB200_GEMM", "cublas"))
     p.add_argument("--attention", default=os.environ.get("TB200_ATTENTION", "sdpa"))
     p.add_argument("--opt-state", default="fp32", choices=["fp32", "bf16"])
@@ -273,7 +273,7 @@ def main() -> None:
             "tflops_per_gpu": flops_per_token * tokens_per_s / world / 1e12,
             "config": {"model": f"{args.model}-{args.flavor}", "global_batch": args.local_batch * world,
                        "seq_len": args.seq_len, "parallelism": f"fsdp{world}", "activation_checkpoint": args.ac,
-                       "optimizer": f"AdamW fp32 master, {args.opt_state} moments", "fsdp_comm": args.fsdp_comm,
+                       "optimizer": f"AdamW fp32 master, {args.opt_state} moments", "fsdp_comm": trainer.engines[0].comm if trainer.engines[0]._symm is None else "nvlink",
                        "gemm": args.gemm, "attention": args.attention,
                        "l2": "per-step working set >> 126 MB L2 (no flush needed)"},
             "clocks": clocks, "e2e": e2e, "gpu_launches": launches,

@@ -76,9 +76,10 @@ class ParallelismConfig:
     context_parallel_ptrr_mask_key: str | None = None
     expert_parallel_degree: int = 1
     # ---- framework-specific -------------------------------------------
-    fsdp_comm: Literal["nccl", "nvlink"] = "nccl"
-    """``nvlink`` runs the gradient reduce-scatter and the parameter broadcast as
-    in-kernel peer loads/stores over symmetric memory; ``nccl`` is the baseline."""
+    fsdp_comm: Literal["auto", "nccl", "nvlink"] = "auto"
+    """``nvlink`` runs the gradient reduce-scatter and the parameter all-gather as in-kernel
+    peer loads/stores over symmetric memory; ``nccl`` is the library baseline; ``auto`` uses
+    NVLink when symmetric memory can be set up on every rank and NCCL otherwise."""
     tp_comm: Literal["nccl", "nvlink"] = "nccl"
     cp_comm: Literal["allgather", "ring"] = "allgather"
     ep_comm: Literal["nccl", "nvlink"] = "nccl"

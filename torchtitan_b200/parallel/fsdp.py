@@ -201,15 +201,9 @@ class ShardedModel:
     def materialize(self, init: bool = True) -> None:
         """Allocate buffers, point module parameters at them, initialise the fp32 master shards."""
         dev, pd = self.device, self.param_dtype
-        use_symm = self.comm == "nvlink" and dev.type == "cuda" and any(u.size > 1 for u in self.units)
+        use_symm = self.comm in ("nvlink", "auto") and dev.type == "cuda" and any(u.size > 1 for u in self.units)
         if use_symm:
-            from . import symm
-
-            self._symm = symm.SymmetricArena(self.pdims, dev)
-            es = torch.empty(0, dtype=pd).element_size()
-            for u in self.units:
-                if u.size > 1:
-                    self._symm.reserve(u.group, 2 * u.padded * es)
+            use_symm = self._setup_symmetric(pd)
         replaced: dict[int, nn.Parameter] = {}
         for u in self.units:
             if use_symm and u.size > 1:
@@ -246,6 +240,40 @@ class ShardedModel:
         _swap_parameters(self.model, replaced)
         if init:
             self.init_weights()
+
+    def _setup_symmetric(self, pd: torch.dtype) -> bool:
+        """Create the symmetric arenas; with ``comm="auto"`` fall back to NCCL when any rank fails."""
+        from . import symm
+
+        ok = True
+        err: Exception | None = None
+        try:
+            if not symm.symm_available():
+                raise RuntimeError("torch symmetric memory is unavailable")
+            arena = symm.SymmetricArena(self.pdims, self.device)
+            es = torch.empty(0, dtype=pd).element_size()
+            groups = {}
+            for u in self.units:
+                if u.size > 1:
+                    arena.reserve(u.group, 2 * u.padded * es)
+                    groups[id(u.group)] = u.group
+            for g in groups.values():
+                arena._arena(g)
+            self._symm = arena
+        except Exception as e:  # noqa: BLE001 - any failure means "use the library path"
+            ok, err = False, e
+        flag = torch.tensor([1 if ok else 0], device=self.device)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        if int(flag.item()) == 1:
+            return True
+        self._symm = None
+        if self.comm == "nvlink":
+            raise RuntimeError(f"fsdp_comm=nvlink requested but symmetric memory setup failed: {err}")
+        from torchtitan_b200.utils.logging import logger
+
+        logger.warning(f"symmetric memory unavailable ({err}); FSDP falls back to NCCL collectives")
+        self.comm = "nccl"
+        return False
 
     def _materialize_full(self, fqn: str, p, spec: InitSpec) -> torch.Tensor:
         """Local (tensor-parallel sliced) fp32 initial value of parameter ``fqn``."""
@@ -349,7 +377,7 @@ class ShardedModel:
                 u.grad_shard.copy_(src)
             else:
                 u.grad_shard.add_(src)
-        elif self.comm == "nvlink" and self._symm is not None:
+        elif self._symm is not None:
             self._symm.reduce_scatter_accumulate(u.flat_grad, u.grad_shard, u.group, accumulate=not first)
         else:
             tmp = self._get_fp32_tmp(u.padded)
