@@ -61,6 +61,10 @@ def parallelize_decoder(model: nn.Module, *, pdims, job_config, device: torch.de
                         grad_accum_steps: int = 1, fqn_prefix: str = "", materialize: bool = True) -> ShardedModel:
     par = job_config.parallelism
     tr = job_config.training
+    if pdims.ep_enabled:
+        from .expert_parallel import apply_expert_parallel
+
+        apply_expert_parallel(model, pdims, par)
     tp = apply_tensor_parallel(model, pdims, par)
 
     if pdims.cp_enabled:
@@ -68,11 +72,6 @@ def parallelize_decoder(model: nn.Module, *, pdims, job_config, device: torch.de
 
         model.cp = CPContext(group=pdims.group("cp"), size=pdims.cp, rank=pdims.local_rank("cp"),
                              mode=par.cp_comm, load_balancer=par.context_parallel_load_balancer or "none")
-    if pdims.ep_enabled:
-        from .expert_parallel import apply_expert_parallel
-
-        apply_expert_parallel(model, pdims, par)
-
     apply_activation_checkpointing(model, job_config.activation_checkpoint)
 
     param_dtype = torch.bfloat16 if tr.mixed_precision_param == "bfloat16" else torch.float32
