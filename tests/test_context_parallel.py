@@ -1,0 +1,58 @@
+"""Context parallel attention (all-gather and ring) equals single-device causal attention."""
+
+import pytest
+import torch
+
+from tests.dist_utils import run_distributed
+
+
+def _cp_fn(rank, world, mode, with_docs, out_path):
+    import torch.distributed as dist
+
+    from torchtitan_b200.models.common.attention import AttentionContext
+    from torchtitan_b200.ops import functional as OF
+    from torchtitan_b200.parallel.context_parallel import CPContext, cp_attention, shard_for_cp, unshard_from_cp
+
+    torch.manual_seed(0)
+    T, Hq, Hkv, D = 32, 4, 2, 8
+    q, k, v = torch.randn(T, Hq, D), torch.randn(T, Hkv, D), torch.randn(T, Hkv, D)
+    g = torch.randn(T, Hq, D)
+    doc = None
+    if with_docs:
+        doc = torch.tensor([1] * 10 + [2] * 15 + [3] * 7, dtype=torch.int32)
+    qf, kf, vf = (t.clone().requires_grad_() for t in (q, k, v))
+    ref = OF.attention(qf, kf, vf, doc_ids=doc)
+    ref.backward(g)
+
+    cp = CPContext(group=dist.group.WORLD, size=world, rank=rank, mode=mode)
+    idx = shard_for_cp(cp, torch.arange(T), torch.arange(T), torch.arange(T))[3]
+    ql, kl, vl = (t[idx].clone().requires_grad_() for t in (q, k, v))
+    ctx = AttentionContext(doc_ids=None if doc is None else doc[idx], q_pos=idx, cp=cp)
+    out = cp_attention(ql, kl, vl, ctx)
+    out.backward(g[idx])
+    ok = torch.allclose(out, ref[idx].detach(), atol=1e-5)
+    ok = ok and torch.allclose(ql.grad, qf.grad[idx], atol=1e-5)
+    ok = ok and torch.allclose(kl.grad, kf.grad[idx], atol=1e-5)
+    ok = ok and torch.allclose(vl.grad, vf.grad[idx], atol=1e-5)
+    full = unshard_from_cp(cp, out.detach())
+    ok = ok and torch.allclose(full, ref.detach(), atol=1e-5)
+    flag = torch.tensor([1.0 if ok else 0.0])
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+    if rank == 0:
+        torch.save(flag, out_path)
+
+
+@pytest.mark.parametrize("mode", ["allgather", "ring"])
+@pytest.mark.parametrize("with_docs", [False, True])
+def test_cp_attention_matches_full(tmp_path, mode, with_docs):
+    out = str(tmp_path / "cp.pt")
+    run_distributed(_cp_fn, 2, mode, with_docs, out)
+    assert float(torch.load(out)) == 1.0
+
+
+def test_headtail_chunks():
+    from torchtitan_b200.parallel.context_parallel import CPContext, cp_chunk_ids
+
+    cp = CPContext(group=None, size=4, rank=1)
+    assert cp_chunk_ids(cp) == [1, 6]
+    assert sorted(c for r in range(4) for c in cp_chunk_ids(cp, r)) == list(range(8))
