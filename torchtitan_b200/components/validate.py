@@ -53,17 +53,26 @@ class Validator(Configurable):
         total = torch.zeros((), dtype=torch.float32, device=t.device)
         ntok = torch.zeros((), dtype=torch.float32, device=t.device)
         n = 0
+        n_mb = t.config.parallelism.num_pp_microbatches if pd.pp_enabled else 1
+        pending: list = []
         for inputs, labels in self.dataloader:
             if 0 < self.config.steps <= n:
                 break
             t.metrics_processor.ntokens_since_last_log += labels.numel()
-            tokens, positions, lab, q_pos = t.post_dataloading_process(inputs, labels)
             one = torch.ones((), dtype=torch.float32, device=t.device)
             if pd.pp_enabled:
                 from torchtitan_b200.parallel.pipeline import run_pipeline_eval
 
+                pending.append((inputs, labels))
+                if len(pending) < n_mb:
+                    continue
+                stacked = {k: torch.stack([p[0][k] for p in pending]) for k in pending[0][0]}
+                slab = torch.stack([p[1] for p in pending])
+                pending = []
+                tokens, positions, lab, q_pos = t.post_dataloading_process(stacked, slab)
                 loss = run_pipeline_eval(t, tokens, positions, lab, q_pos)
             else:
+                tokens, positions, lab, q_pos = t.post_dataloading_process(inputs, labels)
                 model = t.model
                 ctx = model.build_context(positions, q_pos)
                 pred = model(tokens, positions, ctx, return_hidden=t.loss_fn.needs_hidden)

@@ -57,8 +57,8 @@ def _local_index(cp: CPContext, T: int, device, rank: int | None = None) -> torc
 
 def shard_for_cp(cp: CPContext, tokens, positions, labels):
     """Returns the local slices and ``q_pos`` (global token index of each local row)."""
-    idx = _local_index(cp, tokens.shape[0], tokens.device)
-    return tokens.index_select(0, idx), positions.index_select(0, idx), labels.index_select(0, idx), idx
+    idx = _local_index(cp, tokens.shape[-1], tokens.device)
+    return tokens.index_select(-1, idx), positions.index_select(-1, idx), labels.index_select(-1, idx), idx
 
 
 def unshard_from_cp(cp: CPContext, local: torch.Tensor) -> torch.Tensor:

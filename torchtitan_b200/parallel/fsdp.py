@@ -138,6 +138,7 @@ class ShardedModel:
         self._tmp_idx = 0
         self._symm = None
         self._callback_queued = False
+        self.defer_reduce = False
         self._build_units(units)
 
     # ------------------------------------------------------------------
@@ -326,7 +327,8 @@ class ShardedModel:
 
     def _on_unit_backward_done(self, unit: FlatUnit) -> None:
         self._collect_autograd_grads(unit)
-        self._launch_reduce(unit)
+        if not self.defer_reduce:
+            self._launch_reduce(unit)
 
     def _collect_autograd_grads(self, unit: FlatUnit) -> None:
         """Fold gradients delivered through ``.grad`` (ops without direct main_grad writes)."""
@@ -400,10 +402,16 @@ class ShardedModel:
             self._fp32_tmp[slot] = torch.empty(numel, dtype=torch.float32, device=self.device)
         return self._fp32_tmp[slot][:numel]
 
-    def finish_backward(self) -> None:
-        """Reduce units whose input hook did not fire (first unit), then join the comm stream."""
+    def finish_backward(self, flush: bool = False) -> None:
+        """Reduce units whose input hook did not fire (first unit), then join the comm stream.
+
+        With ``defer_reduce`` (pipeline stages) local gradients keep accumulating over the
+        microbatches of a step and nothing is reduced until ``flush=True``."""
         for u in self.units:
             self._collect_autograd_grads(u)
+        if self.defer_reduce and not flush:
+            return
+        for u in self.units:
             self._launch_reduce(u)
         if self._comm_stream is not None:
             torch.cuda.current_stream(self.device).wait_stream(self._comm_stream)

@@ -28,6 +28,8 @@ def init_distributed(comm_config, device: torch.device, *, dump_folder: str = ".
                      enable_cpu_backend: bool = False) -> int:
     """Initialise the default process group when launched with more than one rank."""
     rank, _, world = world_info()
+    if dist.is_initialized():  # embedded use (tests, notebooks): keep the caller's process group
+        return dist.get_world_size()
     mode = getattr(comm_config, "mode", "default")
     if mode == "fake_backend":
         from torch.testing._internal.distributed.fake_pg import FakeStore
