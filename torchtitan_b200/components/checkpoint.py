@@ -320,7 +320,8 @@ class ChunkLoadPlanner(DefaultLoadPlanner):
         return plan
 
     def plain_state(self) -> dict[str, Any]:
-        return self._plain
+        # the base planner may have replaced the dict it was given by a processed copy
+        return self.state_dict
 
 
 def _unflatten_into(nested: dict, flat: dict[str, Any], prefix: str = "") -> None:
