@@ -8,7 +8,7 @@ from torchtitan_b200.ops import ext
 pytestmark = pytest.mark.gpu
 
 SHAPES = [(128, 256, 64), (256, 512, 256), (200, 264, 136), (1024, 768, 4096), (8, 8, 8), (4096, 6144, 512),
-          (304, 1000, 72)]
+          (304, 1000, 72), (2560, 2304, 1088)]
 
 
 def _operands(mode, M, N, K):
@@ -20,14 +20,20 @@ def _operands(mode, M, N, K):
     return a, b, af @ bf
 
 
+@pytest.mark.parametrize("variant", [1, 2])
 @pytest.mark.parametrize("mode", [0, 1, 2])
 @pytest.mark.parametrize("M,N,K", SHAPES)
-def test_gemm_matches_fp32(mode, M, N, K):
+def test_gemm_matches_fp32(mode, M, N, K, variant):
+    """variant 1 = one CTA per 128x256 tile, variant 2 = CTA pair per 256x256 tile."""
     assert ext.load()
     a, b, ref = _operands(mode, M, N, K)
     c = torch.full((M, N), float("nan"), device="cuda", dtype=torch.bfloat16)
-    torch.ops.tb200.gemm_bf16(a, b, c, mode, False)
-    torch.cuda.synchronize()
+    torch.ops.tb200.gemm_set_variant(variant)
+    try:
+        torch.ops.tb200.gemm_bf16(a, b, c, mode, False)
+        torch.cuda.synchronize()
+    finally:
+        torch.ops.tb200.gemm_set_variant(0)
     assert torch.ops.tb200.gemm_status(True) == 0
     err = (c.float() - ref).abs().max().item()
     tol = 2e-2 * ref.abs().max().item() + 1e-2

@@ -17,6 +17,8 @@ void adamw_(at::Tensor master, const at::Tensor& grad, at::Tensor exp_avg, at::T
 void sumsq_(const at::Tensor& x, at::Tensor acc);
 void gemm_bf16(const at::Tensor& a, const at::Tensor& b, at::Tensor c, int64_t mode, bool accumulate);
 int64_t gemm_status(bool clear);
+void gemm_set_variant(int64_t v);
+void gemm_set_debug(int64_t v);
 void symm_barrier(at::IntArrayRef flag_ptrs, int64_t my_rank, int64_t epoch, at::Tensor status, int64_t max_cycles);
 void reduce_scatter_pull(at::IntArrayRef grad_ptrs, int64_t my_rank, int64_t offset, at::Tensor out, bool grad_is_bf16,
                          bool accumulate);
@@ -40,6 +42,8 @@ TORCH_LIBRARY(tb200, m) {
   m.def("sumsq_(Tensor x, Tensor(a!) acc) -> ()", &tb200::sumsq_);
   m.def("gemm_bf16(Tensor a, Tensor b, Tensor(a!) c, int mode, bool accumulate) -> ()", &tb200::gemm_bf16);
   m.def("gemm_status(bool clear) -> int", &tb200::gemm_status);
+  m.def("gemm_set_variant(int v) -> ()", &tb200::gemm_set_variant);
+  m.def("gemm_set_debug(int v) -> ()", &tb200::gemm_set_debug);
   m.def("symm_barrier(int[] flag_ptrs, int my_rank, int epoch, Tensor(a!) status, int max_cycles) -> ()",
         &tb200::symm_barrier);
   m.def("reduce_scatter_pull(int[] grad_ptrs, int my_rank, int offset, Tensor(a!) out, bool grad_is_bf16, "

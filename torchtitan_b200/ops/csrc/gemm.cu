@@ -6,7 +6,14 @@
 //   mode 2 (TN): C[M,N] = A[K,M]^T . B[K,N]      weight gradient
 // `accumulate` adds the product to the existing C (bf16) in the epilogue.
 //
-// One CTA per SM, tile 128 x 256, K step 64, 4-stage TMA pipeline (48 KB per stage).
+// Two instantiations of one kernel body:
+//   kCta = 1 : one CTA per SM computes a 128 x 256 tile, 4-stage TMA pipeline (48 KB per stage).
+//   kCta = 2 : a cluster of two CTAs (one SM pair) computes a 256 x 256 tile with
+//              tcgen05.mma.cta_group::2.  Each CTA stages its own 128 rows of A and its own 128
+//              rows (columns of C) of B, so a stage is 32 KB per CTA and the pipeline has 6
+//              stages; the B traffic per SM halves.  The MMA is issued by CTA 0 only and writes the
+//              accumulator rows of both CTAs' TMEM; both CTAs run a producer and an epilogue.
+// Roles inside a CTA:
 //   warp 0      : TMA producer (one elected lane)
 //   warp 1      : allocates TMEM, issues tcgen05.mma (one elected lane), commits to mbarriers
 //   warps 2..5  : epilogue; each warp owns the 32 TMEM lanes of its quarter (warp_id % 4),
@@ -14,226 +21,185 @@
 // The 512 TMEM columns hold two 128 x 256 fp32 accumulators, so the epilogue of tile i
 // overlaps the main loop of tile i+1.
 //
+// Tiles are visited in groups of kGroupRows rows of C (about 2048) so that the CTAs that run
+// at the same time share A and B panels in L2.
+//
 // Operand layouts.  K-major operands ([rows, K] row-major) are loaded as boxes of 64 K-elements
 // (128 B) x rows; MN-major operands ([K, cols] row-major) as boxes of 64 columns (128 B) x 64
 // K-rows, one box per 64 columns.  Both use the 128-byte swizzle, which is what the shared
-// memory matrix descriptors below describe.
+// memory matrix descriptors describe.
 //
-// Every mbarrier wait is bounded: after kSpinLimit polls the waiter raises an abort flag in
-// shared memory, all roles leave their loops, TMEM is freed and the kernel sets bit
-// kStatusWaitTimedOut in the status word.  TMA loads are plain (no cluster multicast).
+// Every mbarrier wait is bounded: after a fixed number of polls the waiter raises an abort flag
+// in shared memory, all roles leave their loops, TMEM is freed and the kernel sets bit
+// kStatusWaitTimedOut in the status word.  TMA loads are plain tile loads: the CTA pair uses the
+// cta_group::2 form only so that both CTAs can report bytes to the barrier of CTA 0.
 #include <ATen/ATen.h>
 #include <ATen/cuda/CUDAContext.h>
 #include <c10/cuda/CUDAGuard.h>
 #include <cuda.h>
 
 #include "common.cuh"
+#include "tc.cuh"
 
 namespace tb200 {
 
 namespace gemm {
 
-constexpr int BM = 128;
-constexpr int BN = 256;
+using namespace tc;
+
+constexpr int BM = 128;   // rows of C per CTA
+constexpr int BN = 256;   // columns of C per tile
 constexpr int BK = 64;
-constexpr int kStages = 4;
 constexpr int UMMA_K = 16;
 constexpr int kThreads = 192;
 constexpr uint32_t kTmemCols = 512;
-constexpr uint32_t kABytes = BM * BK * 2;   // 16 KB
-constexpr uint32_t kBBytes = BN * BK * 2;   // 32 KB
-constexpr uint32_t kStageBytes = kABytes + kBBytes;
-constexpr uint32_t kSmemBytes = kStages * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
-constexpr uint32_t kSpinLimit = 20u * 1000u * 1000u;
+constexpr int kGroupRows = 2048;
 
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
-// Bounded wait: false when the limit was hit or another role already aborted.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
-  for (uint32_t i = 0; i < kSpinLimit; ++i) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if ((i & 1023u) == 1023u && *abort_flag) return false;
-  }
-  *abort_flag = 1;
-  return false;
-}
-
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-      ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1)
-      : "memory");
-}
-
-__device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t ncols) {
-  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(ncols) : "memory");
-}
-__device__ __forceinline__ void tmem_relinquish() {
-  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
-  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-
-__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
-                                          uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-// Arrive on an mbarrier once all previously issued tcgen05.mma of this thread have completed.
-__device__ __forceinline__ void umma_commit(uint32_t bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
-        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
-        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-      : "r"(taddr)
-      : "memory");
-}
-__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-
-// Shared-memory matrix descriptor (sm_100 format, 128-byte swizzle).
-//   bits [0,14)  start address >> 4      bits [16,30) leading byte offset >> 4
-//   bits [32,46) stride byte offset >> 4 bits [46,48) version = 1      bits [61,64) layout = 2 (SW128)
-__device__ __forceinline__ uint64_t make_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
-  uint64_t d = 0;
-  d |= (uint64_t)((saddr & 0x3FFFFu) >> 4);
-  d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFFu) << 16;
-  d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFFu) << 32;
-  d |= (uint64_t)1 << 46;
-  d |= (uint64_t)2 << 61;
-  return d;
-}
-
-// Instruction descriptor for kind::f16: D fp32, A/B bf16, majorness per operand, N and M.
-__host__ __device__ constexpr uint32_t make_idesc(bool a_mn_major, bool b_mn_major) {
-  return (1u << 4) | (1u << 7) | (1u << 10) | ((a_mn_major ? 1u : 0u) << 15) | ((b_mn_major ? 1u : 0u) << 16) |
-         ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
-}
+template <int kCta>
+struct Cfg {
+  static constexpr int kStages = kCta == 1 ? 4 : 6;
+  static constexpr int kBRows = BN / kCta;                 // rows of B staged by one CTA
+  static constexpr uint32_t kABytes = BM * BK * 2;         // 16 KB
+  static constexpr uint32_t kBBytes = kBRows * BK * 2;     // 32 KB or 16 KB
+  static constexpr uint32_t kStageBytes = kABytes + kBBytes;
+  static constexpr uint32_t kEpiBytes = 4 * 2 * 4096;      // per epilogue warp: two 32-row x 128 B staging tiles
+  static constexpr uint32_t kSmemBytes = kStages * kStageBytes + kEpiBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
+};
 
 struct Params {
   int M, N, K;
   int a_mn_major;  // A is stored [K, M]
   int b_mn_major;  // B is stored [K, N]
   int accumulate;
+  int debug;       // bit 0: no TMA loads (MMA issue rate on stale shared memory), bit 1: no stores
   __nv_bfloat16* C;
   int* status;
 };
 
+template <int kCta>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                 const Params p) {
+                 const __grid_constant__ CUtensorMap tmap_c, const Params p) {
+  using C_ = Cfg<kCta>;
+  constexpr int kStages = C_::kStages;
+  constexpr uint32_t kABytes = C_::kABytes, kStageBytes = C_::kStageBytes;
   extern __shared__ uint8_t smem_raw[];
   // stage buffers need 1024-byte alignment for the 128B swizzle atoms
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
   uint8_t* gen_base = smem_raw + (base - raw);
-  const uint32_t bar_base = base + kStages * kStageBytes;
+  const uint32_t epi_base = base + kStages * kStageBytes;
+  const uint32_t bar_base = epi_base + C_::kEpiBytes;
   // barrier layout: full[kStages], empty[kStages], tmem_full[2], tmem_empty[2], then tmem ptr, abort flag
   auto full_bar = [&](int s) { return bar_base + 8u * s; };
   auto empty_bar = [&](int s) { return bar_base + 8u * (kStages + s); };
   auto tfull_bar = [&](int a) { return bar_base + 8u * (2 * kStages + a); };
   auto tempty_bar = [&](int a) { return bar_base + 8u * (2 * kStages + 2 + a); };
-  uint32_t* tmem_ptr_smem = reinterpret_cast<uint32_t*>(gen_base + kStages * kStageBytes + 8 * (2 * kStages + 4));
+  uint32_t* tmem_ptr_smem =
+      reinterpret_cast<uint32_t*>(gen_base + kStages * kStageBytes + C_::kEpiBytes + 8 * (2 * kStages + 4));
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_ptr_smem + 1);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int num_m = (p.M + BM - 1) / BM;
+  const uint32_t cta_rank = kCta == 1 ? 0u : cluster_ctarank();
+  const int unit = kCta == 1 ? (int)blockIdx.x : (int)(blockIdx.x >> 1);       // CTA or CTA pair
+  const int num_units = kCta == 1 ? (int)gridDim.x : (int)(gridDim.x >> 1);
+  constexpr int kTileM = BM * kCta;
+  const int num_m = (p.M + kTileM - 1) / kTileM;
   const int num_n = (p.N + BN - 1) / BN;
   const int num_tiles = num_m * num_n;
   const int num_kb = (p.K + BK - 1) / BK;
+  constexpr int kGroupM = kGroupRows / kTileM;
+  // tile index -> (row tile, column tile): groups of kGroupM row tiles, row index fastest
+  auto tile_coord = [&](int t, int& tm, int& tn) {
+    const int per_group = kGroupM * num_n;
+    const int g = t / per_group;
+    const int first = g * kGroupM;
+    const int gsz = min(kGroupM, num_m - first);
+    const int r = t - g * per_group;
+    tm = first + r % gsz;
+    tn = r / gsz;
+  };
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
-      mbar_init(full_bar(s), 1);
+      mbar_init(full_bar(s), kCta);      // one arrive.expect_tx per producing CTA
       mbar_init(empty_bar(s), 1);
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(tfull_bar(a), 1);
-      mbar_init(tempty_bar(a), 4);
+      mbar_init(tempty_bar(a), 4 * kCta);  // epilogue warps of every CTA of the pair
     }
     *abort_flag = 0;
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_a) : "memory");
-    asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_b) : "memory");
+    mbar_fence_init();
+    tma_prefetch_desc(&tmap_a);
+    tma_prefetch_desc(&tmap_b);
+    tma_prefetch_desc(&tmap_c);
   }
   if (warp == 1) {
+    // The whole TMEM of the SM: both CTAs of a pair therefore get base column 0.
     tmem_alloc(smem_u32(tmem_ptr_smem), kTmemCols);
     tmem_relinquish();
   }
   tc_fence_before();
   __syncthreads();
+  if constexpr (kCta == 2) cluster_sync();   // the peer's barriers exist before anyone signals them
   tc_fence_after();
   const uint32_t tmem_base = *tmem_ptr_smem;
 
   if (warp == 0) {
-    // ------------------------------------------------------------- TMA producer
+    // ------------------------------------------------------------- TMA producer (every CTA)
     if (lane == 0) {
       uint32_t it = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-        const int m0 = (tile % num_m) * BM;
-        const int n0 = (tile / num_m) * BN;
+      for (int tile = unit; tile < num_tiles && ok; tile += num_units) {
+        int tm, tn;
+        tile_coord(tile, tm, tn);
+        const int m0 = tm * kTileM + (int)cta_rank * BM;
+        const int n0 = tn * BN + (int)cta_rank * C_::kBRows;
         for (int kb = 0; kb < num_kb; ++kb, ++it) {
           const int s = it % kStages;
           const uint32_t parity = ((it / kStages) & 1u) ^ 1u;
-          if (!mbar_wait(empty_bar(s), parity, abort_flag)) { ok = false; break; }
+          const bool got = kCta == 1 ? mbar_wait(empty_bar(s), parity, abort_flag)
+                                     : mbar_wait_cluster(empty_bar(s), parity, abort_flag);
+          if (!got) { ok = false; break; }
           const uint32_t sa = base + s * kStageBytes;
           const uint32_t sb = sa + kABytes;
-          mbar_expect_tx(full_bar(s), kStageBytes);
           const int k0 = kb * BK;
+          // bytes of both CTAs are counted by the barrier of CTA 0
+          const uint32_t fb = kCta == 1 ? full_bar(s) : mapa(full_bar(s), 0);
+          auto load = [&](uint32_t dst, const CUtensorMap* map, int c0, int c1) {
+            if constexpr (kCta == 1) tma_load_2d(dst, map, fb, c0, c1);
+            else tma_load_2d_pair(dst, map, fb, c0, c1);
+          };
+          if (p.debug & 1) {
+            if constexpr (kCta == 1) mbar_arrive(fb);
+            else mbar_arrive_cluster(fb);
+            continue;
+          }
+          if constexpr (kCta == 1) mbar_expect_tx(fb, kStageBytes);
+          else mbar_expect_tx_cluster(fb, kStageBytes);
           if (!p.a_mn_major) {
-            tma_load_2d(sa, &tmap_a, full_bar(s), k0, m0);            // box {64 k, 128 rows}
+            load(sa, &tmap_a, k0, m0);                                // box {64 k, 128 rows}
           } else {
 #pragma unroll
             for (int b = 0; b < BM / 64; ++b)                         // boxes {64 m, 64 k-rows}
-              tma_load_2d(sa + b * (BK * 128), &tmap_a, full_bar(s), m0 + b * 64, k0);
+              load(sa + b * (BK * 128), &tmap_a, m0 + b * 64, k0);
           }
           if (!p.b_mn_major) {
-            tma_load_2d(sb, &tmap_b, full_bar(s), k0, n0);            // box {64 k, 256 rows}
+            load(sb, &tmap_b, k0, n0);                                // box {64 k, kBRows rows}
           } else {
 #pragma unroll
-            for (int b = 0; b < BN / 64; ++b)
-              tma_load_2d(sb + b * (BK * 128), &tmap_b, full_bar(s), n0 + b * 64, k0);
+            for (int b = 0; b < C_::kBRows / 64; ++b)
+              load(sb + b * (BK * 128), &tmap_b, n0 + b * 64, k0);
           }
         }
       }
     }
   } else if (warp == 1) {
-    // ------------------------------------------------------------- MMA issuer
-    if (lane == 0) {
-      const uint32_t idesc = make_idesc(p.a_mn_major != 0, p.b_mn_major != 0);
+    // ------------------------------------------------------------- MMA issuer (CTA 0 of a pair)
+    if (lane == 0 && cta_rank == 0) {
+      const uint32_t idesc = make_idesc(p.a_mn_major != 0, p.b_mn_major != 0, kTileM, BN);
       // K-major: SBO = 1024 B between 8-row groups, one MMA K step = 32 B inside the swizzled row.
       // MN-major: LBO = BK*128 B between 64-column boxes, SBO = 1024 B between 8-k-row groups,
       //           one MMA K step = 16 k-rows = 2048 B.
@@ -241,16 +207,20 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       const uint32_t b_lbo = p.b_mn_major ? BK * 128 : 16, b_step = p.b_mn_major ? 2048 : 32;
       uint32_t it = 0, tcount = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++tcount) {
+      for (int tile = unit; tile < num_tiles && ok; tile += num_units, ++tcount) {
         const int acc = tcount & 1;
         const uint32_t acc_parity = ((tcount >> 1) & 1u) ^ 1u;
-        if (!mbar_wait(tempty_bar(acc), acc_parity, abort_flag)) { ok = false; break; }
+        const bool got = kCta == 1 ? mbar_wait(tempty_bar(acc), acc_parity, abort_flag)
+                                   : mbar_wait_cluster(tempty_bar(acc), acc_parity, abort_flag);
+        if (!got) { ok = false; break; }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
         for (int kb = 0; kb < num_kb; ++kb, ++it) {
           const int s = it % kStages;
           const uint32_t parity = (it / kStages) & 1u;
-          if (!mbar_wait(full_bar(s), parity, abort_flag)) { ok = false; break; }
+          const bool gotf = kCta == 1 ? mbar_wait(full_bar(s), parity, abort_flag)
+                                      : mbar_wait_cluster(full_bar(s), parity, abort_flag);
+          if (!gotf) { ok = false; break; }
           tc_fence_after();
           const uint32_t sa = base + s * kStageBytes;
           const uint32_t sb = sa + kABytes;
@@ -258,26 +228,75 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           for (int k = 0; k < BK / UMMA_K; ++k) {
             const uint64_t ad = make_desc(sa + k * a_step, a_lbo, 1024);
             const uint64_t bd = make_desc(sb + k * b_step, b_lbo, 1024);
-            umma_bf16(d_tmem, ad, bd, idesc, (kb | k) != 0 ? 1u : 0u);
+            umma_bf16<kCta>(d_tmem, ad, bd, idesc, (kb | k) != 0 ? 1u : 0u);
           }
-          umma_commit(empty_bar(s));  // the stage can be refilled once these MMAs have read it
+          // the stage can be refilled (in both CTAs) once these MMAs have read it
+          if constexpr (kCta == 1) umma_commit(empty_bar(s));
+          else umma_commit_pair(empty_bar(s), 3);
         }
-        if (ok) umma_commit(tfull_bar(acc));
+        if (ok) {
+          if constexpr (kCta == 1) umma_commit(tfull_bar(acc));
+          else umma_commit_pair(tfull_bar(acc), 3);
+        }
       }
     }
   } else {
-    // ------------------------------------------------------------- epilogue (warps 2..5)
+    // ------------------------------------------------------------- epilogue (warps 2..5, every CTA)
     const int q = warp & 3;  // TMEM lane quarter this warp may access
-    uint32_t tcount = 0;
+    uint32_t tcount = 0, sbuf = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++tcount) {
+    const uint32_t te_leader = kCta == 1 ? 0u : mapa(tempty_bar(0), 0);
+    for (int tile = unit; tile < num_tiles && ok; tile += num_units, ++tcount) {
       const int acc = tcount & 1;
       const uint32_t acc_parity = (tcount >> 1) & 1u;
-      const int m0 = (tile % num_m) * BM;
-      const int n0 = (tile / num_m) * BN;
-      if (!mbar_wait(tfull_bar(acc), acc_parity, abort_flag)) { ok = false; break; }
+      int tm, tn;
+      tile_coord(tile, tm, tn);
+      const int m0 = tm * kTileM + (int)cta_rank * BM;
+      const int n0 = tn * BN;
+      const bool got = kCta == 1 ? mbar_wait(tfull_bar(acc), acc_parity, abort_flag)
+                                 : mbar_wait_cluster(tfull_bar(acc), acc_parity, abort_flag);
+      if (!got) { ok = false; break; }
       tc_fence_after();
       const int row = m0 + q * 32 + lane;
+      if (!p.accumulate) {
+        // Plain store: 64 columns at a time go through a 128B-swizzled staging tile in shared
+        // memory and leave as one TMA tile store (full 128-byte lines; edges are clipped).
+        const uint32_t stage0 = epi_base + (uint32_t)(warp - 2) * 8192u;
+#pragma unroll 1
+        for (int c = 0; c < BN / 64; ++c) {
+          uint32_t r0[32], r1[32];
+          const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN + c * 64);
+          tmem_ld32(taddr, r0);
+          tmem_ld32(taddr + 32, r1);
+          tmem_ld_wait();
+          if (lane == 0) tma_store_wait_read<1>();   // the tile written two steps ago has been read
+          __syncwarp();
+          const uint32_t buf = stage0 + (sbuf ? 4096u : 0u);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            uint32_t w[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const int i = (j & 3) * 8 + 2 * e;
+              const float lo = __uint_as_float(j < 4 ? r0[i] : r1[i]);
+              const float hi = __uint_as_float(j < 4 ? r0[i + 1] : r1[i + 1]);
+              __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+              w[e] = *reinterpret_cast<uint32_t*>(&h);
+            }
+            const uint32_t dst = buf + (uint32_t)lane * 128u + (uint32_t)((j ^ (lane & 7)) << 4);
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3])
+                         : "memory");
+          }
+          fence_proxy_async_smem();
+          __syncwarp();
+          const int col0 = n0 + c * 64;
+          if (lane == 0 && col0 < p.N && m0 + q * 32 < p.M && !(p.debug & 2)) {
+            tma_store_2d(&tmap_c, buf, col0, m0 + q * 32);
+            tma_store_commit();
+          }
+          sbuf ^= 1u;
+        }
+      } else {
       __nv_bfloat16* crow = p.C + (int64_t)row * p.N;
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
@@ -286,39 +305,41 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         tmem_ld32(taddr, r);
         tmem_ld_wait();
         const int col0 = n0 + c * 32;
-        if (row < p.M && col0 < p.N) {
+        if (row < p.M && col0 < p.N && !(p.debug & 2)) {
           if (col0 + 32 <= p.N) {
 #pragma unroll
             for (int v = 0; v < 4; ++v) {
-              float f[8];
+              float f[8], o[8];
 #pragma unroll
               for (int j = 0; j < 8; ++j) f[j] = __uint_as_float(r[v * 8 + j]);
               bf16x8* dst = reinterpret_cast<bf16x8*>(crow + col0 + v * 8);
-              if (p.accumulate) {
-                float o[8];
-                unpack8(*dst, o);
+              unpack8(*dst, o);
 #pragma unroll
-                for (int j = 0; j < 8; ++j) f[j] += o[j];
-              }
+              for (int j = 0; j < 8; ++j) f[j] += o[j];
               *dst = pack8(f);
             }
           } else {
-            for (int j = 0; j < 32 && col0 + j < p.N; ++j) {
-              float f = __uint_as_float(r[j]);
-              if (p.accumulate) f += __bfloat162float(crow[col0 + j]);
-              crow[col0 + j] = __float2bfloat16_rn(f);
-            }
+            for (int j = 0; j < 32 && col0 + j < p.N; ++j)
+              crow[col0 + j] = __float2bfloat16_rn(__uint_as_float(r[j]) + __bfloat162float(crow[col0 + j]));
           }
         }
       }
+      }
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(tempty_bar(acc));
+      if (lane == 0) {
+        if constexpr (kCta == 1) mbar_arrive(tempty_bar(acc));
+        else mbar_arrive_cluster(te_leader + 8u * acc);
+      }
     }
+    if (lane == 0) tma_store_wait<0>();   // shared memory must outlive the stores that read it
   }
 
   tc_fence_before();
   __syncthreads();
+  // A CTA of a pair may not free its TMEM or leave while the other one can still issue MMAs
+  // that read this CTA's shared memory and write its TMEM.
+  if constexpr (kCta == 2) cluster_sync();
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc(tmem_base, kTmemCols);
@@ -351,6 +372,57 @@ static at::Tensor& gemm_status_tensor(const at::Device& dev) {
   return t;
 }
 
+static int g_gemm_debug = 0;
+void gemm_set_debug(int64_t v) { g_gemm_debug = (int)v; }
+static int g_gemm_variant = 0;  // 0 = choose by shape, 1 = single CTA tiles, 2 = CTA-pair tiles
+
+void gemm_set_variant(int64_t v) {
+  TORCH_CHECK(v >= 0 && v <= 2, "gemm_set_variant: 0 (auto), 1 (single CTA) or 2 (CTA pair)");
+  g_gemm_variant = (int)v;
+}
+
+template <int kCta>
+static void launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc_, const gemm::Params& p,
+                        cudaStream_t stream) {
+  using namespace gemm;
+  using C_ = Cfg<kCta>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    C10_CUDA_CHECK(cudaFuncSetAttribute(gemm_bf16_kernel<kCta>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        C_::kSmemBytes));
+    attr_set = true;
+  }
+  const int tile_m = BM * kCta;
+  const int tiles = ((p.M + tile_m - 1) / tile_m) * ((p.N + BN - 1) / BN);
+  cudaLaunchConfig_t cfg = {};
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = C_::kSmemBytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  if (kCta == 1) {
+    cfg.gridDim = dim3(std::min(tiles, num_sms()));
+    cfg.numAttrs = 0;
+  } else {
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    // A persistent grid must be resident at once: ask how many CTA pairs the device can hold
+    // (SM pairs that cannot host a cluster would otherwise serialise a second wave).
+    static int max_pairs = 0;
+    if (max_pairs == 0) {
+      cfg.gridDim = dim3(num_sms() & ~1);
+      int n = 0;
+      C10_CUDA_CHECK(cudaOccupancyMaxActiveClusters(&n, gemm_bf16_kernel<kCta>, &cfg));
+      max_pairs = std::max(1, std::min(n, num_sms() / 2));
+    }
+    cfg.gridDim = dim3(2 * std::min(tiles, max_pairs));
+  }
+  C10_CUDA_CHECK(cudaLaunchKernelEx(&cfg, gemm_bf16_kernel<kCta>, ta, tb, tc_, p));
+}
+
 // mode: 0 = NT (a[M,K], b[N,K]), 1 = NN (a[M,K], b[K,N]), 2 = TN (a[K,M], b[K,N]).
 void gemm_bf16(const at::Tensor& a, const at::Tensor& b, at::Tensor c, int64_t mode, bool accumulate) {
   TORCH_CHECK(a.is_cuda() && b.is_cuda() && c.is_cuda());
@@ -374,26 +446,24 @@ void gemm_bf16(const at::Tensor& a, const at::Tensor& b, at::Tensor c, int64_t m
   // thread; autograd worker threads may not have bound it yet.
   C10_CUDA_CHECK(cudaSetDevice(a.device().index()));
   using namespace gemm;
+  // The CTA pair pays off once a 256-row tile is full and there is more than one wave of work.
+  const bool pair = g_gemm_variant == 2 || (g_gemm_variant == 0 && M >= 512);
+  const uint32_t b_rows = pair ? Cfg<2>::kBRows : Cfg<1>::kBRows;
   // K-major: inner = K, box {64, rows};  MN-major: inner = MN extent, box {64, 64 k-rows}
   const CUtensorMap ta = a_mn ? make_tmap_2d(a.data_ptr(), M, K, M * 2, 64, BK)
                               : make_tmap_2d(a.data_ptr(), K, M, K * 2, BK, BM);
   const CUtensorMap tb = b_mn ? make_tmap_2d(b.data_ptr(), N, K, N * 2, 64, BK)
-                              : make_tmap_2d(b.data_ptr(), K, N, K * 2, BK, BN);
+                              : make_tmap_2d(b.data_ptr(), K, N, K * 2, BK, b_rows);
   Params p;
   p.M = (int)M; p.N = (int)N; p.K = (int)K;
   p.a_mn_major = a_mn; p.b_mn_major = b_mn; p.accumulate = accumulate ? 1 : 0;
+  p.debug = g_gemm_debug;
   p.C = reinterpret_cast<__nv_bfloat16*>(c.data_ptr());
   p.status = gemm_status_tensor(a.device()).data_ptr<int>();
-  static bool attr_set = false;
-  if (!attr_set) {
-    C10_CUDA_CHECK(cudaFuncSetAttribute(gemm_bf16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
-    attr_set = true;
-  }
-  const int tiles = (int)(((M + BM - 1) / BM) * ((N + BN - 1) / BN));
-  const int grid = std::min(tiles, num_sms());
   auto stream = at::cuda::getCurrentCUDAStream();
-  gemm_bf16_kernel<<<grid, kThreads, kSmemBytes, stream>>>(ta, tb, p);
-  C10_CUDA_KERNEL_LAUNCH_CHECK();
+  const CUtensorMap tcm = make_tmap_2d(c.data_ptr(), N, M, N * 2, 64, 32);   // store tiles: 64 columns x 32 rows
+  if (pair) launch_gemm<2>(ta, tb, tcm, p, stream);
+  else launch_gemm<1>(ta, tb, tcm, p, stream);
 }
 
 int64_t gemm_status(bool clear) {

@@ -1,0 +1,150 @@
+"""Kernel micro-benchmarks: ``python -m torchtitan_b200.ops.microbench <kernel> [--case small|8b]``.
+
+Times one hand-written kernel against the library operator that the reference would call
+for the same shape (cuBLAS ``torch.mm``, ATen ``rms_norm``...), with CUDA events on the
+launching stream, three warm-up launches, and a write larger than the L2 between timed
+launches.  Prints one line per shape with achieved TFLOP/s or GB/s.  ``--once`` runs each
+shape a single time without the library arm, which is the form to put under a profiler.
+"""
+
+from __future__ import annotations
+
+import argparse
+import sys
+
+import torch
+
+T = 8192  # tokens per step in the Llama-3 8B headline configuration
+
+# (name, mode, M, N, K) : mode 0 = NT (forward), 1 = NN (input gradient), 2 = TN (weight gradient)
+GEMM_8B = [
+    ("qkv fwd", 0, T, 6144, 4096), ("wo fwd", 0, T, 4096, 4096), ("w13 fwd", 0, T, 28672, 4096),
+    ("w2 fwd", 0, T, 4096, 14336), ("w13 dgrad", 1, T, 4096, 28672), ("w2 dgrad", 1, T, 14336, 4096),
+    ("qkv dgrad", 1, T, 4096, 6144), ("w13 wgrad", 2, 28672, 4096, T), ("w2 wgrad", 2, 4096, 14336, T),
+    ("qkv wgrad", 2, 6144, 4096, T), ("square", 0, 8192, 8192, 8192),
+]
+GEMM_SMALL = [("square", 0, 8192, 8192, 8192)]
+
+
+class Timer:
+    def __init__(self):
+        self.flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+
+    def __call__(self, fn, n: int = 10) -> float:
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        ts = []
+        for _ in range(n):
+            self.flush.zero_()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            torch.cuda.synchronize()
+            ts.append(e0.elapsed_time(e1))
+        ts.sort()
+        return ts[len(ts) // 2]
+
+
+def bench_gemm(args) -> None:
+    ops = torch.ops.tb200
+    timer = Timer()
+    for name, mode, M, N, K in (GEMM_SMALL if args.case == "small" else GEMM_8B):
+        a = torch.randn((K, M) if mode == 2 else (M, K), device="cuda").bfloat16()
+        b = torch.randn((N, K) if mode == 0 else (K, N), device="cuda").bfloat16()
+        c = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+        ours = lambda: ops.gemm_bf16(a, b, c, mode, False)  # noqa: E731
+        ops.gemm_set_variant(args.variant)
+        if args.once:
+            ours()
+            torch.cuda.synchronize()
+            continue
+        lib = {0: lambda: torch.mm(a, b.t(), out=c), 1: lambda: torch.mm(a, b, out=c),
+               2: lambda: torch.mm(a.t(), b, out=c)}[mode]
+        t1, t2 = timer(ours), timer(lib)
+        fl = 2 * M * N * K
+        print(f"gemm {name:10s} mode{mode} M{M} N{N} K{K}: tcgen05 {t1:.3f} ms {fl / t1 / 1e9:.0f} TFLOPS | "
+              f"cuBLAS {t2:.3f} ms {fl / t2 / 1e9:.0f} TFLOPS | speedup {t2 / t1:.2f}", flush=True)
+    print("gemm status word", ops.gemm_status(True))
+
+
+def bench_attention(args) -> None:
+    from . import functional as OF
+
+    timer = Timer()
+    cases = [(8192, 32, 8, 128)] if args.case != "small" else [(4096, 32, 8, 128)]
+    for Tn, H, Hkv, D in cases:
+        q = torch.randn(Tn, H, D, device="cuda").bfloat16().requires_grad_()
+        k = torch.randn(Tn, Hkv, D, device="cuda").bfloat16().requires_grad_()
+        v = torch.randn(Tn, Hkv, D, device="cuda").bfloat16().requires_grad_()
+        do = torch.randn(Tn, H, D, device="cuda").bfloat16()
+        fl_f = 4 * Tn * Tn * H * D / 2
+        for impl in (("native",) if args.once else ("native", "sdpa")):
+            OF.settings.attention = impl
+            fwd = lambda: OF.attention(q, k, v, causal=True)  # noqa: E731
+            if args.once:
+                fwd().backward(do)
+                torch.cuda.synchronize()
+                continue
+            tf = timer(lambda: fwd())
+            o = fwd()
+            tb = timer(lambda: o.backward(do, retain_graph=True))
+            print(f"attention {impl:7s} T{Tn} H{H}/{Hkv} D{D}: fwd {tf:.3f} ms {fl_f / tf / 1e9:.0f} TFLOPS | "
+                  f"bwd {tb:.3f} ms {2.5 * fl_f / tb / 1e9:.0f} TFLOPS", flush=True)
+
+
+def bench_elementwise(args) -> None:
+    ops = torch.ops.tb200
+    timer = Timer()
+    rows, D, F_ = T, 4096, 14336
+    x = torch.randn(rows, D, device="cuda").bfloat16()
+    w = torch.ones(D, device="cuda").bfloat16()
+    gu = torch.randn(rows, 2 * F_, device="cuda").bfloat16()
+    dy = torch.randn(rows, F_, device="cuda").bfloat16()
+
+    def gbs(nbytes, ms):
+        return nbytes / ms / 1e6
+
+    y, rstd = ops.rmsnorm_fwd(x, w, 1e-5)
+    rows_ = [
+        ("rmsnorm_fwd", lambda: ops.rmsnorm_fwd(x, w, 1e-5), 2 * x.numel() * 2),
+        ("rmsnorm_bwd", lambda: ops.rmsnorm_bwd(x, x, w, rstd), 3 * x.numel() * 2),
+        ("swiglu_fwd", lambda: ops.swiglu_fwd(gu), gu.numel() * 2 + dy.numel() * 2),
+        ("swiglu_bwd", lambda: ops.swiglu_bwd(gu, dy), 2 * gu.numel() * 2 + dy.numel() * 2),
+    ]
+    n = 64 << 20
+    master = torch.randn(n, device="cuda")
+    g = torch.randn(n, device="cuda").bfloat16()
+    m = torch.zeros(n, device="cuda")
+    v = torch.zeros(n, device="cuda")
+    lowp = torch.empty(n, device="cuda", dtype=torch.bfloat16)
+    one = torch.ones(1, device="cuda")
+    rows_.append(("adamw", lambda: ops.adamw_(master, g, m, v, lowp, one, 1e-3, 0.9, 0.95, 1e-8, 0.1, 0.1, 0.05),
+                  n * (4 + 2 + 4 + 4 + 4 + 4 + 4 + 2)))
+    for name, fn, nbytes in rows_:
+        if args.once:
+            fn()
+            torch.cuda.synchronize()
+            continue
+        t = timer(fn)
+        print(f"{name:12s}: {t:.3f} ms, {gbs(nbytes, t):.0f} GB/s algorithmic", flush=True)
+
+
+def main(argv=None) -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("kernel", choices=["gemm", "attention", "elementwise"])
+    ap.add_argument("--case", default="8b", choices=["small", "8b"])
+    ap.add_argument("--variant", type=int, default=0, help="GEMM tiling: 0 auto, 1 single CTA, 2 CTA pair")
+    ap.add_argument("--once", action="store_true", help="one launch per shape, no library arm (profiler form)")
+    args = ap.parse_args(argv)
+    from . import ext
+
+    assert torch.cuda.is_available(), "microbench needs a GPU"
+    ext.require()
+    {"gemm": bench_gemm, "attention": bench_attention, "elementwise": bench_elementwise}[args.kernel](args)
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())
