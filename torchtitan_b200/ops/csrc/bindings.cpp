@@ -19,6 +19,10 @@ void gemm_bf16(const at::Tensor& a, const at::Tensor& b, at::Tensor c, int64_t m
 int64_t gemm_status(bool clear);
 void gemm_set_variant(int64_t v);
 void gemm_set_debug(int64_t v);
+std::tuple<at::Tensor, at::Tensor> flash_fwd(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v, double scale,
+                                             bool causal, int64_t causal_offset,
+                                             const c10::optional<at::Tensor>& kv_first);
+int64_t flash_status(bool clear);
 void symm_barrier(at::IntArrayRef flag_ptrs, int64_t my_rank, int64_t epoch, at::Tensor status, int64_t max_cycles);
 void reduce_scatter_pull(at::IntArrayRef grad_ptrs, int64_t my_rank, int64_t offset, at::Tensor out, bool grad_is_bf16,
                          bool accumulate);
@@ -44,6 +48,9 @@ TORCH_LIBRARY(tb200, m) {
   m.def("gemm_status(bool clear) -> int", &tb200::gemm_status);
   m.def("gemm_set_variant(int v) -> ()", &tb200::gemm_set_variant);
   m.def("gemm_set_debug(int v) -> ()", &tb200::gemm_set_debug);
+  m.def("flash_fwd(Tensor q, Tensor k, Tensor v, float scale, bool causal, int causal_offset, Tensor? kv_first) -> "
+        "(Tensor, Tensor)", &tb200::flash_fwd);
+  m.def("flash_status(bool clear) -> int", &tb200::flash_status);
   m.def("symm_barrier(int[] flag_ptrs, int my_rank, int epoch, Tensor(a!) status, int max_cycles) -> ()",
         &tb200::symm_barrier);
   m.def("reduce_scatter_pull(int[] grad_ptrs, int my_rank, int offset, Tensor(a!) out, bool grad_is_bf16, "

@@ -4,7 +4,7 @@
 //   mode 0 (NT): C[M,N] = A[M,K] . B[N,K]^T      forward of a linear layer
 //   mode 1 (NN): C[M,N] = A[M,K] . B[K,N]        input gradient
 //   mode 2 (TN): C[M,N] = A[K,M]^T . B[K,N]      weight gradient
-// `accumulate` adds the product to the existing C (bf16) in the epilogue.
+// `accumulate` adds the product, rounded to bf16, to the existing C with a TMA reduce-add.
 //
 // Two instantiations of one kernel body:
 //   kCta = 1 : one CTA per SM computes a 128 x 256 tile, 4-stage TMA pipeline (48 KB per stage).
@@ -257,10 +257,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                                  : mbar_wait_cluster(tfull_bar(acc), acc_parity, abort_flag);
       if (!got) { ok = false; break; }
       tc_fence_after();
-      const int row = m0 + q * 32 + lane;
-      if (!p.accumulate) {
-        // Plain store: 64 columns at a time go through a 128B-swizzled staging tile in shared
-        // memory and leave as one TMA tile store (full 128-byte lines; edges are clipped).
+      {
+        // 64 columns at a time go through a 128B-swizzled staging tile in shared memory and leave
+        // as one TMA tile store, or a TMA reduce-add when accumulating into C (full 128-byte
+        // lines; edges are clipped).
         const uint32_t stage0 = epi_base + (uint32_t)(warp - 2) * 8192u;
 #pragma unroll 1
         for (int c = 0; c < BN / 64; ++c) {
@@ -291,39 +291,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           __syncwarp();
           const int col0 = n0 + c * 64;
           if (lane == 0 && col0 < p.N && m0 + q * 32 < p.M && !(p.debug & 2)) {
-            tma_store_2d(&tmap_c, buf, col0, m0 + q * 32);
+            if (p.accumulate) tma_reduce_add_2d(&tmap_c, buf, col0, m0 + q * 32);
+            else tma_store_2d(&tmap_c, buf, col0, m0 + q * 32);
             tma_store_commit();
           }
           sbuf ^= 1u;
         }
-      } else {
-      __nv_bfloat16* crow = p.C + (int64_t)row * p.N;
-#pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        uint32_t r[32];
-        const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN + c * 32);
-        tmem_ld32(taddr, r);
-        tmem_ld_wait();
-        const int col0 = n0 + c * 32;
-        if (row < p.M && col0 < p.N && !(p.debug & 2)) {
-          if (col0 + 32 <= p.N) {
-#pragma unroll
-            for (int v = 0; v < 4; ++v) {
-              float f[8], o[8];
-#pragma unroll
-              for (int j = 0; j < 8; ++j) f[j] = __uint_as_float(r[v * 8 + j]);
-              bf16x8* dst = reinterpret_cast<bf16x8*>(crow + col0 + v * 8);
-              unpack8(*dst, o);
-#pragma unroll
-              for (int j = 0; j < 8; ++j) f[j] += o[j];
-              *dst = pack8(f);
-            }
-          } else {
-            for (int j = 0; j < 32 && col0 + j < p.N; ++j)
-              crow[col0 + j] = __float2bfloat16_rn(__uint_as_float(r[j]) + __bfloat162float(crow[col0 + j]));
-          }
-        }
-      }
       }
       tc_fence_before();
       __syncwarp();

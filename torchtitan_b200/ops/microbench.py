@@ -21,7 +21,8 @@ GEMM_8B = [
     ("qkv fwd", 0, T, 6144, 4096), ("wo fwd", 0, T, 4096, 4096), ("w13 fwd", 0, T, 28672, 4096),
     ("w2 fwd", 0, T, 4096, 14336), ("w13 dgrad", 1, T, 4096, 28672), ("w2 dgrad", 1, T, 14336, 4096),
     ("qkv dgrad", 1, T, 4096, 6144), ("w13 wgrad", 2, 28672, 4096, T), ("w2 wgrad", 2, 4096, 14336, T),
-    ("qkv wgrad", 2, 6144, 4096, T), ("square", 0, 8192, 8192, 8192),
+    ("qkv wgrad", 2, 6144, 4096, T), ("wo wgrad", 2, 4096, 4096, T), ("lmhead fwd", 0, 1024, 128256, 4096),
+    ("lmhead dgrad", 1, 1024, 4096, 128256), ("lmhead wgrad+", 2, 128256, 4096, 1024), ("square", 0, 8192, 8192, 8192),
 ]
 GEMM_SMALL = [("square", 0, 8192, 8192, 8192)]
 
@@ -54,14 +55,15 @@ def bench_gemm(args) -> None:
         a = torch.randn((K, M) if mode == 2 else (M, K), device="cuda").bfloat16()
         b = torch.randn((N, K) if mode == 0 else (K, N), device="cuda").bfloat16()
         c = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
-        ours = lambda: ops.gemm_bf16(a, b, c, mode, False)  # noqa: E731
+        acc = name.endswith("+")  # accumulate into C (chunked lm_head weight gradient)
+        ours = lambda: ops.gemm_bf16(a, b, c, mode, acc)  # noqa: E731
         ops.gemm_set_variant(args.variant)
         if args.once:
             ours()
             torch.cuda.synchronize()
             continue
         lib = {0: lambda: torch.mm(a, b.t(), out=c), 1: lambda: torch.mm(a, b, out=c),
-               2: lambda: torch.mm(a.t(), b, out=c)}[mode]
+               2: (lambda: c.addmm_(a.t(), b)) if acc else (lambda: torch.mm(a.t(), b, out=c))}[mode]
         t1, t2 = timer(ours), timer(lib)
         fl = 2 * M * N * K
         print(f"gemm {name:10s} mode{mode} M{M} N{N} K{K}: tcgen05 {t1:.3f} ms {fl / t1 / 1e9:.0f} TFLOPS | "
