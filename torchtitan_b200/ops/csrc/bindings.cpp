@@ -22,6 +22,13 @@ void gemm_set_debug(int64_t v);
 std::tuple<at::Tensor, at::Tensor> flash_fwd(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v, double scale,
                                              bool causal, int64_t causal_offset,
                                              const c10::optional<at::Tensor>& kv_first);
+std::tuple<at::Tensor, at::Tensor, at::Tensor> flash_bwd(const at::Tensor& d_o, const at::Tensor& q, const at::Tensor& k,
+                                                         const at::Tensor& v, const at::Tensor& o, const at::Tensor& lse,
+                                                         double scale, bool causal, int64_t causal_offset,
+                                                         const c10::optional<at::Tensor>& kv_first,
+                                                         const c10::optional<at::Tensor>& dq_out,
+                                                         const c10::optional<at::Tensor>& dk_out,
+                                                         const c10::optional<at::Tensor>& dv_out);
 int64_t flash_status(bool clear);
 void symm_barrier(at::IntArrayRef flag_ptrs, int64_t my_rank, int64_t epoch, at::Tensor status, int64_t max_cycles);
 void reduce_scatter_pull(at::IntArrayRef grad_ptrs, int64_t my_rank, int64_t offset, at::Tensor out, bool grad_is_bf16,
@@ -50,6 +57,9 @@ TORCH_LIBRARY(tb200, m) {
   m.def("gemm_set_debug(int v) -> ()", &tb200::gemm_set_debug);
   m.def("flash_fwd(Tensor q, Tensor k, Tensor v, float scale, bool causal, int causal_offset, Tensor? kv_first) -> "
         "(Tensor, Tensor)", &tb200::flash_fwd);
+  m.def("flash_bwd(Tensor d_o, Tensor q, Tensor k, Tensor v, Tensor o, Tensor lse, float scale, bool causal, "
+        "int causal_offset, Tensor? kv_first, Tensor(a!)? dq_out, Tensor(b!)? dk_out, Tensor(c!)? dv_out) -> "
+        "(Tensor, Tensor, Tensor)", &tb200::flash_bwd);
   m.def("flash_status(bool clear) -> int", &tb200::flash_status);
   m.def("symm_barrier(int[] flag_ptrs, int my_rank, int epoch, Tensor(a!) status, int max_cycles) -> ()",
         &tb200::symm_barrier);

@@ -72,28 +72,47 @@ def bench_gemm(args) -> None:
 
 
 def bench_attention(args) -> None:
-    from . import functional as OF
+    import math
 
+    import torch.nn.functional as F
+
+    ops = torch.ops.tb200
     timer = Timer()
     cases = [(8192, 32, 8, 128)] if args.case != "small" else [(4096, 32, 8, 128)]
     for Tn, H, Hkv, D in cases:
-        q = torch.randn(Tn, H, D, device="cuda").bfloat16().requires_grad_()
-        k = torch.randn(Tn, Hkv, D, device="cuda").bfloat16().requires_grad_()
-        v = torch.randn(Tn, Hkv, D, device="cuda").bfloat16().requires_grad_()
+        qkv = torch.randn(Tn, (H + 2 * Hkv) * D, device="cuda").bfloat16()
+        v3 = qkv.view(Tn, H + 2 * Hkv, D)
+        q, k, v = v3[:, :H], v3[:, H:H + Hkv], v3[:, H + Hkv:]
         do = torch.randn(Tn, H, D, device="cuda").bfloat16()
+        scale = 1.0 / math.sqrt(D)
         fl_f = 4 * Tn * Tn * H * D / 2
-        for impl in (("native",) if args.once else ("native", "sdpa")):
-            OF.settings.attention = impl
-            fwd = lambda: OF.attention(q, k, v, causal=True)  # noqa: E731
-            if args.once:
-                fwd().backward(do)
-                torch.cuda.synchronize()
-                continue
+        has_bwd = hasattr(ops, "flash_bwd")
+        if args.once:
+            o, lse = ops.flash_fwd(q, k, v, scale, True, 0, None)
+            if has_bwd:
+                ops.flash_bwd(do, q, k, v, o, lse, scale, True, 0, None)
+            torch.cuda.synchronize()
+            continue
+        tf = timer(lambda: ops.flash_fwd(q, k, v, scale, True, 0, None))
+        line = f"attention tcgen05 T{Tn} H{H}/{Hkv} D{D}: fwd {tf:.3f} ms {fl_f / tf / 1e9:.0f} TFLOPS"
+        if has_bwd:
+            o, lse = ops.flash_fwd(q, k, v, scale, True, 0, None)
+            tb = timer(lambda: ops.flash_bwd(do, q, k, v, o, lse, scale, True, 0, None))
+            line += f" | bwd {tb:.3f} ms {2.5 * fl_f / tb / 1e9:.0f} TFLOPS"
+        print(line, flush=True)
+        # library arm: cuDNN / flash SDPA on [1, H, T, D]
+        from torch.nn.attention import SDPBackend, sdpa_kernel
+
+        qh, kh, vh = (t.transpose(0, 1).unsqueeze(0).detach().requires_grad_() for t in (q, k, v))
+        with sdpa_kernel([SDPBackend.CUDNN_ATTENTION, SDPBackend.FLASH_ATTENTION], set_priority=True):
+            fwd = lambda: F.scaled_dot_product_attention(qh, kh, vh, is_causal=True, scale=scale, enable_gqa=True)  # noqa: E731
             tf = timer(lambda: fwd())
-            o = fwd()
-            tb = timer(lambda: o.backward(do, retain_graph=True))
-            print(f"attention {impl:7s} T{Tn} H{H}/{Hkv} D{D}: fwd {tf:.3f} ms {fl_f / tf / 1e9:.0f} TFLOPS | "
-                  f"bwd {tb:.3f} ms {2.5 * fl_f / tb / 1e9:.0f} TFLOPS", flush=True)
+            out = fwd()
+            doh = do.transpose(0, 1).unsqueeze(0)
+            tb = timer(lambda: torch.autograd.grad(out, (qh, kh, vh), doh, retain_graph=True))
+        print(f"attention sdpa    T{Tn} H{H}/{Hkv} D{D}: fwd {tf:.3f} ms {fl_f / tf / 1e9:.0f} TFLOPS | "
+              f"bwd {tb:.3f} ms {2.5 * fl_f / tb / 1e9:.0f} TFLOPS", flush=True)
+    print("flash status word", ops.flash_status(True))
 
 
 def bench_elementwise(args) -> None:
