@@ -36,6 +36,7 @@ class AttentionContext:
     q_pos: torch.Tensor | None = None  # global token index of local rows (CP)
     cp: object | None = None  # parallel.context_parallel.CPContext
     max_doc_len: int | None = None
+    kv_first: torch.Tensor | None = None  # [T_local] int32: index of the first token of each token's document
 
 
 def build_attention_context(positions: torch.Tensor, *, assume_single_document: bool = False,
@@ -45,7 +46,11 @@ def build_attention_context(positions: torch.Tensor, *, assume_single_document: 
         return AttentionContext(None, q_pos, cp)
     starts = (positions == 0).to(torch.int32)
     doc_ids = torch.cumsum(starts, dim=0, dtype=torch.int32)
-    return AttentionContext(doc_ids, q_pos, cp)
+    kv_first = None
+    if cp is None:
+        # a document starts where positions == 0, so token i's document starts at i - positions[i]
+        kv_first = (torch.arange(positions.shape[0], device=positions.device) - positions).to(torch.int32)
+    return AttentionContext(doc_ids, q_pos, cp, kv_first=kv_first)
 
 
 class GQAttention(Module):
@@ -150,9 +155,11 @@ class GQAttention(Module):
             from torchtitan_b200.parallel.context_parallel import cp_attention
 
             o = cp_attention(q, k, v, ctx, scale=self.scale, window=self.window, sinks=self.sinks)
+        elif self.q_norm is None and self.window is None and self.sinks is None:
+            o = OF.attention_packed(qkv, hq, hkv, self.scale, doc_ids=ctx.doc_ids, kv_first=ctx.kv_first)
         else:
             o = OF.attention(q, k, v, scale=self.scale, causal=True, doc_ids=ctx.doc_ids, window=self.window,
-                             sinks=self.sinks)
+                             sinks=self.sinks, kv_first=ctx.kv_first)
         y = self.wo(o.reshape(T, hq * hd))
         if tp is not None:
             return tp_ops.reduce_scatter_rows(y, tp) if tp.sequence_parallel else tp_ops.all_reduce(y, tp)

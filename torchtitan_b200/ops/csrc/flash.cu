@@ -52,7 +52,8 @@ struct FwdParams {
   int ctas_per_kv_head;    // group / slots
   float scale_log2;        // softmax scale * log2(e)
   const int* kv_first;     // [Tq] first visible key per query row, or nullptr
-  float* lse;              // [Hq, Tq] natural-log sum-exp of the scaled scores
+  float* lse;              // [Hq, Tq] natural-log sum-exp of the scaled scores, row stride lse_stride
+  int lse_stride;
   int* status;
 };
 
@@ -314,7 +315,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
           tma_store_wait<0>();
         }
         if (row < p.Tq)
-          p.lse[(int64_t)(head0 + slot) * p.Tq + row] = l > 0.f ? (m_used + log2f(l)) * 0.6931471805599453f : -INFINITY;
+          p.lse[(int64_t)(head0 + slot) * p.lse_stride + row] = l > 0.f ? (m_used + log2f(l)) * 0.6931471805599453f : -INFINITY;
       }
     }
   }
@@ -330,27 +331,28 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
 
 
 // =========================================================================================
-// Backward.  One CTA owns a block of 128 keys of one key/value head and walks over every query
-// head of its group and every block of 64 query rows that can see those keys.  Scores are
-// computed transposed (keys on the TMEM lanes), so the probabilities feed the dV and dK MMAs
-// straight from tensor memory, and dK / dV accumulate in tensor memory over all query heads of
-// the group and leave once.  Per step:
+// Backward, in two kernels that share no memory traffic besides their inputs, so that nothing
+// is accumulated through global memory (an earlier single kernel that reduced dQ partials with
+// TMA reduce-add into an fp32 buffer ran at 9 % tensor-pipe utilisation, bound by the L2
+// reduction rate).
+//
+// flash_bwd_dkv_kernel.  One CTA owns a block of 128 keys of one key/value head and walks over
+// every query head of its group and every block of 64 query rows that can see those keys.
+// Scores are computed transposed (keys on the TMEM lanes), so the probabilities feed the dV and
+// dK MMAs straight from tensor memory, and dK / dV accumulate in tensor memory over all query
+// heads of the group and leave once.  Per step:
 //     S^T  = K . Q^T,  dP^T = V . dO^T                      (tcgen05.mma, shared-memory operands)
 //     P^T  = exp2(S^T c - lse),  dS^T = P^T (dP^T - delta) scale     (8 warps, one key row each,
-//            written back over S^T / dP^T as packed bf16 and, for dS^T, also to shared memory)
+//            written back over S^T / dP^T as packed bf16)
 //     dV  += P^T . dO,  dK += dS^T . Q                      (A operand from tensor memory)
-//     dQ^T = K^T . dS^T                                     (fresh accumulator, two buffers)
-// dQ^T leaves through a shared-memory staging tile as a TMA reduce-add into an fp32 [Tq, Hq, D]
-// buffer (no atomics issued by threads), which a small kernel converts to bf16 afterwards.
-//
-//   warp 0       TMA producer (K, V once; Q and dO blocks through a two-stage ring)
+// S^T / dP^T are double buffered: the MMAs of step t+1 run while the warps work on step t.
+//   warp 0       TMA producer (K, V once; Q and dO blocks through a four-stage ring)
 //   warp 1       TMEM allocation, MMA issue
-//   warps 2..9   softmax-gradient math, dQ drain, dK / dV epilogue (lane quarter = warp % 4,
-//                column half = (warp - 2) / 4)
-//   warp 10      issues the dQ reduce-add and recycles the staging tile
-// Tensor memory: S^T [0,64)  dP^T [64,128)  dQ^T buffers [128,192) [192,256)  dK [256,384)  dV [384,512)
+//   warps 2..9   lane quarter = warp % 4, column half = (warp - 2) / 4
+// Tensor memory: S^T [0,64) [64,128)   dP^T [128,192) [192,256)   dK [256,384)   dV [384,512)
 constexpr int kBQ = 64;                       // query rows per step
-constexpr int kThreadsBwd = 352;
+constexpr int kThreadsBwd = 320;
+constexpr int kRing = 4;
 constexpr uint32_t kQBytes = kBQ * kD * 2;    // 16 KB: 64 x 128 bf16 (two 64-column halves of 8 KB)
 
 struct BwdParams {
@@ -358,30 +360,31 @@ struct BwdParams {
   int causal, causal_offset;
   float scale, scale_log2;
   const int* kv_first;     // [Tq] or nullptr
-  const float* lse;        // [Hq, Tq]
-  const float* delta;      // [Hq, Tq] rowsum(dO * O)
+  const float* lse;        // [Hq, Tq], row stride `stat_stride`
+  const float* delta;      // [Hq, Tq] rowsum(dO * O), row stride `stat_stride`
+  int stat_stride;         // a multiple of 64 floats, so that 64-row slices can be fetched with bulk copies
   int* status;
 };
 
 __global__ void __launch_bounds__(kThreadsBwd, 1)
-flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_do,
-                 const __grid_constant__ CUtensorMap tmap_k, const __grid_constant__ CUtensorMap tmap_v,
-                 const __grid_constant__ CUtensorMap tmap_dk, const __grid_constant__ CUtensorMap tmap_dv,
-                 const __grid_constant__ CUtensorMap tmap_dq, const BwdParams p) {
+flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_do,
+                     const __grid_constant__ CUtensorMap tmap_k, const __grid_constant__ CUtensorMap tmap_v,
+                     const __grid_constant__ CUtensorMap tmap_dk, const __grid_constant__ CUtensorMap tmap_dv,
+                     const BwdParams p) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
   uint8_t* gen_base = smem_raw + (base - raw);
-  // shared memory: K | V | ring[2] of (Q, dO) | dS^T staging | dQ staging (fp32) | barriers
+  // shared memory: K | V | ring[kRing] of (Q, dO) | barriers
   const uint32_t k_smem = base;
   const uint32_t v_smem = base + kTileBytes;
   const uint32_t ring_smem = base + 2 * kTileBytes;                 // stage s: Q at +s*32K, dO at +s*32K+16K
-  const uint32_t ds_smem = ring_smem + 4 * kQBytes;                 // 128 keys x 64 queries bf16 = 16 KB
-  const uint32_t dq_smem = ds_smem + kQBytes;                       // 64 queries x 128 fp32 = 32 KB
-  constexpr uint32_t kBarOff = 2 * kTileBytes + 4 * kQBytes + kQBytes + kBQ * kD * 4;
+  constexpr uint32_t kStatOff = 2 * kTileBytes + kRing * 2 * kQBytes;   // per stage: lse[64] | delta[64] (fp32)
+  const uint32_t stat_smem = base + kStatOff;
+  constexpr uint32_t kBarOff = kStatOff + kRing * 512;
   const uint32_t bar_base = base + kBarOff;
-  enum { KV_FULL = 0, R_FULL = 1, R_EMPTY = 3, ST_FULL = 5, PS_READY = 6, DQ_FREE = 7, DQ_STAGED = 9, STAGE_FREE = 10,
-         ALL_DONE = 11, OUT_STAGED = 12, NBAR = 13 };
+  enum { KV_FULL = 0, R_FULL = 1, R_EMPTY = 1 + kRing, ST_FULL = 1 + 2 * kRing, PS_READY = 3 + 2 * kRing,
+         ALL_DONE = 5 + 2 * kRing, OUT_STAGED = 6 + 2 * kRing, NBAR = 7 + 2 * kRing };
   auto bar = [&](int i) { return bar_base + 8u * i; };
   uint32_t* tmem_ptr_smem = reinterpret_cast<uint32_t*>(gen_base + kBarOff + 8 * NBAR);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_ptr_smem + 1);
@@ -390,22 +393,22 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int num_k_tiles = (p.Tk + kBN - 1) / kBN;
-  const int j = num_k_tiles - 1 - (int)blockIdx.x % num_k_tiles;   // interleave long and short key blocks
-  const int kv_head = (int)blockIdx.x / num_k_tiles;
+  // causal: the first key blocks see the most query rows; they are scheduled first
+  const int j = (int)blockIdx.x / p.Hkv;
+  const int kv_head = (int)blockIdx.x % p.Hkv;
   const int group = p.Hq / p.Hkv;
   const int k0 = j * kBN;
 
   if (threadIdx.x == 0) {
     mbar_init(bar(KV_FULL), 1);
-    for (int s = 0; s < 2; ++s) {
+    for (int s = 0; s < kRing; ++s) {
       mbar_init(bar(R_FULL + s), 1);
       mbar_init(bar(R_EMPTY + s), 1);
-      mbar_init(bar(DQ_FREE + s), 256);
     }
-    mbar_init(bar(ST_FULL), 1);
-    mbar_init(bar(PS_READY), 256);
-    mbar_init(bar(DQ_STAGED), 256);
-    mbar_init(bar(STAGE_FREE), 1);
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(bar(ST_FULL + b), 1);
+      mbar_init(bar(PS_READY + b), 256);
+    }
     mbar_init(bar(ALL_DONE), 1);
     mbar_init(bar(OUT_STAGED), 256);
     *abort_flag = 0;
@@ -442,8 +445,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
   const int q_lo = q_range[0];
   const int n_sub = q_range[1];
   const int n_iter = n_sub * group;
-  constexpr uint32_t T_ST = 0, T_DPT = 64, T_DQ = 128, T_DK = 256, T_DV = 384;
-
+  constexpr uint32_t T_ST = 0, T_DPT = 128, T_DK = 256, T_DV = 384;
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
@@ -454,16 +456,18 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         tma_load_3d(v_smem + h * kHalfBytes, &tmap_v, bar(KV_FULL), h * 64, kv_head, k0);
       }
       for (int t = 0; t < n_iter; ++t) {
-        const int st = t & 1;
-        if (!mbar_wait(bar(R_EMPTY + st), ((t >> 1) & 1u) ^ 1u, abort_flag)) break;
+        const int st = t % kRing;
+        if (!mbar_wait(bar(R_EMPTY + st), ((t / kRing) & 1u) ^ 1u, abort_flag)) break;
         const int head = kv_head * group + t / n_sub;
         const int qs = q_lo + (t % n_sub) * kBQ;
         const uint32_t qa = ring_smem + st * 2 * kQBytes, doa = qa + kQBytes;
-        mbar_expect_tx(bar(R_FULL + st), 2 * kQBytes);
+        mbar_expect_tx(bar(R_FULL + st), 2 * kQBytes + 512);
         for (int h = 0; h < 2; ++h) {
           tma_load_3d(qa + h * (kQBytes / 2), &tmap_q, bar(R_FULL + st), h * 64, head, qs);
           tma_load_3d(doa + h * (kQBytes / 2), &tmap_do, bar(R_FULL + st), h * 64, head, qs);
         }
+        bulk_load(stat_smem + st * 512, p.lse + (int64_t)head * p.stat_stride + qs, 256, bar(R_FULL + st));
+        bulk_load(stat_smem + st * 512 + 256, p.delta + (int64_t)head * p.stat_stride + qs, 256, bar(R_FULL + st));
       }
     }
   } else if (warp == 1) {
@@ -471,127 +475,88 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
     if (lane == 0 && n_iter > 0) {
       const uint32_t idesc_st = make_idesc(false, false, kBN, kBQ);   // K / V and Q / dO all K-major (head dim contiguous)
       const uint32_t idesc_acc = make_idesc(false, true, kBN, kD);    // A from TMEM, B = dO or Q as [query, head dim]: MN-major
-      const uint32_t idesc_dq = make_idesc(true, true, kD, kBQ);      // A = K as [key, head dim], B = dS^T as [key, query]
-      bool ok = mbar_wait(bar(KV_FULL), 0, abort_flag);
-      for (int t = 0; t < n_iter && ok; ++t) {
-        const int st = t & 1;
-        if (!mbar_wait(bar(R_FULL + st), (t >> 1) & 1u, abort_flag)) { ok = false; break; }
+      auto issue_scores = [&](int t) -> bool {
+        const int st = t % kRing, b = t & 1;
+        if (!mbar_wait(bar(R_FULL + st), (t / kRing) & 1u, abort_flag)) return false;
         tc_fence_after();
         const uint32_t qa = ring_smem + st * 2 * kQBytes, doa = qa + kQBytes;
 #pragma unroll
         for (int k = 0; k < kD / 16; ++k) {
           const uint32_t koff = (uint32_t)(k >> 2) * kHalfBytes + (uint32_t)(k & 3) * 32u;
           const uint32_t qoff = (uint32_t)(k >> 2) * (kQBytes / 2) + (uint32_t)(k & 3) * 32u;
-          umma_bf16<1>(tmem_base + T_ST, make_desc(k_smem + koff, 16, 1024), make_desc(qa + qoff, 16, 1024), idesc_st,
-                       k != 0 ? 1u : 0u);
+          umma_bf16<1>(tmem_base + T_ST + b * 64, make_desc(k_smem + koff, 16, 1024), make_desc(qa + qoff, 16, 1024),
+                       idesc_st, k != 0 ? 1u : 0u);
         }
 #pragma unroll
         for (int k = 0; k < kD / 16; ++k) {
           const uint32_t koff = (uint32_t)(k >> 2) * kHalfBytes + (uint32_t)(k & 3) * 32u;
           const uint32_t qoff = (uint32_t)(k >> 2) * (kQBytes / 2) + (uint32_t)(k & 3) * 32u;
-          umma_bf16<1>(tmem_base + T_DPT, make_desc(v_smem + koff, 16, 1024), make_desc(doa + qoff, 16, 1024), idesc_st,
-                       k != 0 ? 1u : 0u);
+          umma_bf16<1>(tmem_base + T_DPT + b * 64, make_desc(v_smem + koff, 16, 1024), make_desc(doa + qoff, 16, 1024),
+                       idesc_st, k != 0 ? 1u : 0u);
         }
-        umma_commit(bar(ST_FULL));
-        if (!mbar_wait(bar(PS_READY), t & 1u, abort_flag)) { ok = false; break; }
+        umma_commit(bar(ST_FULL + b));
+        return true;
+      };
+      bool ok = mbar_wait(bar(KV_FULL), 0, abort_flag) && issue_scores(0);
+      for (int t = 0; t < n_iter && ok; ++t) {
+        const int st = t % kRing, b = t & 1;
+        if (t + 1 < n_iter && !issue_scores(t + 1)) { ok = false; break; }
+        if (!mbar_wait(bar(PS_READY + b), (t >> 1) & 1u, abort_flag)) { ok = false; break; }
         tc_fence_after();
+        const uint32_t qa = ring_smem + st * 2 * kQBytes, doa = qa + kQBytes;
 #pragma unroll
         for (int ks = 0; ks < kBQ / 16; ++ks) {   // 16 queries per step: 8 packed columns, 16 rows (2048 B) of dO
-          const uint32_t a_col = (uint32_t)(ks >> 1) * 32u + (uint32_t)(ks & 1) * 8u;
+          const uint32_t a_col = (uint32_t)b * 64u + (uint32_t)(ks >> 1) * 32u + (uint32_t)(ks & 1) * 8u;
           umma_bf16_ts(tmem_base + T_DV, tmem_base + T_ST + a_col, make_desc(doa + ks * 2048, kQBytes / 2, 1024),
                        idesc_acc, (t > 0 || ks > 0) ? 1u : 0u);
         }
 #pragma unroll
         for (int ks = 0; ks < kBQ / 16; ++ks) {
-          const uint32_t a_col = (uint32_t)(ks >> 1) * 32u + (uint32_t)(ks & 1) * 8u;
+          const uint32_t a_col = (uint32_t)b * 64u + (uint32_t)(ks >> 1) * 32u + (uint32_t)(ks & 1) * 8u;
           umma_bf16_ts(tmem_base + T_DK, tmem_base + T_DPT + a_col, make_desc(qa + ks * 2048, kQBytes / 2, 1024),
                        idesc_acc, (t > 0 || ks > 0) ? 1u : 0u);
         }
         umma_commit(bar(R_EMPTY + st));   // Q and dO of this stage are no longer read
-        if (!mbar_wait(bar(DQ_FREE + (t & 1)), ((t >> 1) & 1u) ^ 1u, abort_flag)) { ok = false; break; }
-        tc_fence_after();
-#pragma unroll
-        for (int ks = 0; ks < kBN / 16; ++ks)      // 16 keys per step
-          umma_bf16<1>(tmem_base + T_DQ + (t & 1) * 64, make_desc(k_smem + ks * 2048, kHalfBytes, 1024),
-                       make_desc(ds_smem + ks * 2048, kHalfBytes, 1024), idesc_dq, ks != 0 ? 1u : 0u);
       }
       if (ok) umma_commit(bar(ALL_DONE));
     }
-  } else if (warp == 10) {
-    // ------------------------------------------------------------------ dQ reduce-add issuer
-    if (lane == 0) {
-      for (int u = 0; u < n_iter; ++u) {
-        if (!mbar_wait(bar(DQ_STAGED), u & 1u, abort_flag)) break;
-        const int head = kv_head * group + u / n_sub;
-        const int qs = q_lo + (u % n_sub) * kBQ;
-        tma_reduce_add_3d(&tmap_dq, dq_smem, 0, head, qs);
-        tma_store_commit();
-        tma_store_wait_read<0>();
-        mbar_arrive(bar(STAGE_FREE));
-      }
-      tma_store_wait<0>();
-    }
   } else {
-    // ------------------------------------------------------------------ softmax gradient, drains, epilogue
+    // ------------------------------------------------------------------ softmax gradient, epilogue
     const int quarter = warp & 3;
     const int half = (warp - 2) >> 2;
-    const int r = quarter * 32 + lane;             // key row of this thread (and head-dim row when draining dQ^T)
+    const int r = quarter * 32 + lane;             // key row of this thread
     const int kv_idx = k0 + r;
     const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
     bool ok = true;
-    auto drain = [&](int u) -> bool {
-      if (!mbar_wait(bar(STAGE_FREE), (u & 1u) ^ 1u, abort_flag)) return false;
-      uint32_t v[32];
-      tmem_ld32(tmem_base + lane_addr + T_DQ + (u & 1) * 64 + half * 32, v);
-      tmem_ld_wait();
-#pragma unroll
-      for (int e = 0; e < 32; ++e) {
-        const uint32_t dst = dq_smem + (uint32_t)(half * 32 + e) * (kD * 4) + (uint32_t)r * 4u;
-        asm volatile("st.shared.b32 [%0], %1;" ::"r"(dst), "r"(v[e]) : "memory");
-      }
-      tc_fence_before();
-      mbar_arrive(bar(DQ_FREE + (u & 1)));
-      fence_proxy_async_smem();
-      mbar_arrive(bar(DQ_STAGED));
-      return true;
-    };
     for (int t = 0; t < n_iter; ++t) {
+      const int b = t & 1;
       const int head = kv_head * group + t / n_sub;
       const int qc0 = q_lo + (t % n_sub) * kBQ + half * 32;    // first query column of this thread
-      if (!mbar_wait(bar(ST_FULL), t & 1u, abort_flag)) { ok = false; break; }
+      if (!mbar_wait(bar(ST_FULL + b), (t >> 1) & 1u, abort_flag)) { ok = false; break; }
       tc_fence_after();
       uint32_t sv[32], dv[32];
-      tmem_ld32(tmem_base + lane_addr + T_ST + half * 32, sv);
-      tmem_ld32(tmem_base + lane_addr + T_DPT + half * 32, dv);
+      tmem_ld32(tmem_base + lane_addr + T_ST + b * 64 + half * 32, sv);
+      tmem_ld32(tmem_base + lane_addr + T_DPT + b * 64 + half * 32, dv);
       tmem_ld_wait();
-      const float* lse_h = p.lse + (int64_t)head * p.Tq;
-      const float* del_h = p.delta + (int64_t)head * p.Tq;
+      // lse and delta of the 64 query rows of this step were staged next to Q / dO by the producer
+      // (the stage's barrier has completed long ago: the MMAs that filled S^T waited on it)
+      if (!mbar_wait(bar(R_FULL + t % kRing), (t / kRing) & 1u, abort_flag)) { ok = false; break; }
+      const uint32_t stat = stat_smem + (uint32_t)(t % kRing) * 512u + (uint32_t)half * 128u;
       const bool edge = p.kv_first != nullptr || qc0 + 32 > p.Tq || k0 + kBN > p.Tk ||
                         (p.causal && qc0 + p.causal_offset < k0 + kBN - 1);
-      const bool vec = (p.Tq & 3) == 0 && qc0 + 32 <= p.Tq;
       uint32_t pk[16], dk[16];
 #pragma unroll
       for (int g = 0; g < 8; ++g) {
         float l4[4], d4[4];
-        if (vec) {
-          const float4 a = *reinterpret_cast<const float4*>(lse_h + qc0 + g * 4);
-          const float4 b = *reinterpret_cast<const float4*>(del_h + qc0 + g * 4);
-          l4[0] = a.x; l4[1] = a.y; l4[2] = a.z; l4[3] = a.w;
-          d4[0] = b.x; d4[1] = b.y; d4[2] = b.z; d4[3] = b.w;
-        } else {
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const int qi = min(qc0 + g * 4 + e, p.Tq - 1);
-            l4[e] = lse_h[qi];
-            d4[e] = del_h[qi];
-          }
-        }
+        asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];"
+                     : "=f"(l4[0]), "=f"(l4[1]), "=f"(l4[2]), "=f"(l4[3]) : "r"(stat + g * 16));
+        asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];"
+                     : "=f"(d4[0]), "=f"(d4[1]), "=f"(d4[2]), "=f"(d4[3]) : "r"(stat + 256 + g * 16));
         float pv[4], ds[4];
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
           const int i = g * 4 + e;
-          float x = __uint_as_float(sv[i]) * p.scale_log2 - l4[e] * 1.4426950408889634f;
-          float pe = exp2f(x);
+          float pe = exp2f(fmaf(__uint_as_float(sv[i]), p.scale_log2, -l4[e] * 1.4426950408889634f));
           if (edge) {
             const int qi = qc0 + i;
             bool vis = qi < p.Tq && kv_idx < p.Tk;
@@ -600,37 +565,23 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
             if (!vis) pe = 0.f;
           }
           pv[e] = pe;
-          ds[e] = pe * (__uint_as_float(dv[i]) - d4[e]) * p.scale;
+          ds[e] = pe * fmaf(__uint_as_float(dv[i]), p.scale, -d4[e] * p.scale);
         }
         pk[2 * g] = pack_bf16(pv[0], pv[1]);
         pk[2 * g + 1] = pack_bf16(pv[2], pv[3]);
         dk[2 * g] = pack_bf16(ds[0], ds[1]);
         dk[2 * g + 1] = pack_bf16(ds[2], ds[3]);
       }
-      tmem_st16(tmem_base + lane_addr + T_ST + half * 32, pk);
-      tmem_st16(tmem_base + lane_addr + T_DPT + half * 32, dk);
-#pragma unroll
-      for (int jj = 0; jj < 4; ++jj) {
-        const int chunk = half * 4 + jj;
-        const uint32_t dst = ds_smem + (uint32_t)r * 128u + (uint32_t)((chunk ^ (r & 7)) << 4);
-        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(dk[jj * 4]), "r"(dk[jj * 4 + 1]),
-                     "r"(dk[jj * 4 + 2]), "r"(dk[jj * 4 + 3]) : "memory");
-      }
+      tmem_st16(tmem_base + lane_addr + T_ST + b * 64 + half * 32, pk);
+      tmem_st16(tmem_base + lane_addr + T_DPT + b * 64 + half * 32, dk);
       tmem_st_wait();
       tc_fence_before();
-      fence_proxy_async_smem();
-      mbar_arrive(bar(PS_READY));
-      if (t > 0 && !drain(t - 1)) { ok = false; break; }
+      mbar_arrive(bar(PS_READY + b));
     }
-    if (ok && n_iter > 0) {
-      ok = mbar_wait(bar(ALL_DONE), 0, abort_flag);
-      if (ok) {
-        tc_fence_after();
-        ok = drain(n_iter - 1);
-      }
-    }
+    if (ok && n_iter > 0) ok = mbar_wait(bar(ALL_DONE), 0, abort_flag);
     // ---- dK, dV: tensor memory -> bf16 -> swizzled staging tiles (the Q / dO ring) -> TMA store
     if (ok) {
+      tc_fence_after();
 #pragma unroll 1
       for (int which = 0; which < 2; ++which) {
         const uint32_t stage = ring_smem + which * kTileBytes + half * kHalfBytes;
@@ -679,9 +630,260 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
   if (threadIdx.x == 0 && *abort_flag && p.status != nullptr) atomicOr(p.status, kStatusWaitTimedOut);
 }
 
+// flash_bwd_dq_kernel.  One CTA owns 128 query rows of one head and walks over the key blocks
+// those rows can see (the forward's loop).  Per key block:
+//     S = Q . K^T,  dP = dO . V^T             (tcgen05.mma, shared-memory operands)
+//     dS = exp2(S c - lse) (dP - delta) scale  (8 warps: one query row, 64 keys per thread),
+//          written over S as packed bf16
+//     dQ += dS . K                             (A operand from tensor memory)
+// dP is double buffered, so the dP MMA of the next block runs during the warps' math.
+//   warp 0 TMA producer (Q, dO once; K and V through two-stage rings), warp 1 MMA, warps 2..9 math
+// Tensor memory: S / dS [0,128)   dP [128,256) [256,384)   dQ [384,512)
+__global__ void __launch_bounds__(kThreadsBwd, 1)
+flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_do,
+                    const __grid_constant__ CUtensorMap tmap_k, const __grid_constant__ CUtensorMap tmap_v,
+                    const __grid_constant__ CUtensorMap tmap_dq, const BwdParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  uint8_t* gen_base = smem_raw + (base - raw);
+  // shared memory: Q | dO | K ring[2] | V ring[2] | barriers
+  const uint32_t q_smem = base;
+  const uint32_t do_smem = base + kTileBytes;
+  const uint32_t k_smem = base + 2 * kTileBytes;
+  const uint32_t v_smem = base + 4 * kTileBytes;
+  constexpr uint32_t kBarOff = 6 * kTileBytes;
+  const uint32_t bar_base = base + kBarOff;
+  enum { Q_FULL = 0, K_FULL = 1, K_EMPTY = 3, V_FULL = 5, V_EMPTY = 7, S_FULL = 9, DP_FULL = 10, DS_READY = 12, DQ_FULL = 13,
+         OUT_STAGED = 14, NBAR = 15 };
+  auto bar = [&](int i) { return bar_base + 8u * i; };
+  uint32_t* tmem_ptr_smem = reinterpret_cast<uint32_t*>(gen_base + kBarOff + 8 * NBAR);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_ptr_smem + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int num_q_tiles = (p.Tq + kBM - 1) / kBM;
+  const int q_tile = num_q_tiles - 1 - (int)blockIdx.x / p.Hq;      // longest rows first
+  const int head = (int)blockIdx.x % p.Hq;
+  const int kv_head = head / (p.Hq / p.Hkv);
+  const int q0 = q_tile * kBM;
+  const int num_k_tiles = (p.Tk + kBN - 1) / kBN;
+  int j_hi = num_k_tiles - 1;
+  if (p.causal) j_hi = min(j_hi, (min(q0 + kBM - 1, p.Tq - 1) + p.causal_offset) / kBN);
+  int j_lo = 0;
+  if (p.kv_first != nullptr) j_lo = max(0, p.kv_first[q0]) / kBN;
+  const int n_tiles = j_hi - j_lo + 1;
+
+  if (threadIdx.x == 0) {
+    mbar_init(bar(Q_FULL), 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(bar(K_FULL + s), 1);
+      mbar_init(bar(K_EMPTY + s), 1);
+      mbar_init(bar(V_FULL + s), 1);
+      mbar_init(bar(V_EMPTY + s), 1);
+      mbar_init(bar(DP_FULL + s), 1);
+    }
+    mbar_init(bar(S_FULL), 1);
+    mbar_init(bar(DS_READY), 256);
+    mbar_init(bar(DQ_FULL), 1);
+    mbar_init(bar(OUT_STAGED), 256);
+    *abort_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&tmap_q);
+    tma_prefetch_desc(&tmap_do);
+    tma_prefetch_desc(&tmap_k);
+    tma_prefetch_desc(&tmap_v);
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(tmem_ptr_smem), 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_ptr_smem;
+  constexpr uint32_t T_S = 0, T_DP = 128, T_DQ = 384;
+
+  if (warp == 0) {
+    if (lane == 0 && n_tiles > 0) {
+      mbar_expect_tx(bar(Q_FULL), 2 * kTileBytes);
+      for (int h = 0; h < 2; ++h) {
+        tma_load_3d(q_smem + h * kHalfBytes, &tmap_q, bar(Q_FULL), h * 64, head, q0);
+        tma_load_3d(do_smem + h * kHalfBytes, &tmap_do, bar(Q_FULL), h * 64, head, q0);
+      }
+      for (int i = 0; i < n_tiles; ++i) {
+        const int st = i & 1;
+        const uint32_t parity = ((i >> 1) & 1u) ^ 1u;
+        const int k0 = (j_lo + i) * kBN;
+        if (!mbar_wait(bar(K_EMPTY + st), parity, abort_flag)) break;
+        mbar_expect_tx(bar(K_FULL + st), kTileBytes);
+        for (int h = 0; h < 2; ++h)
+          tma_load_3d(k_smem + st * kTileBytes + h * kHalfBytes, &tmap_k, bar(K_FULL + st), h * 64, kv_head, k0);
+        if (!mbar_wait(bar(V_EMPTY + st), parity, abort_flag)) break;
+        mbar_expect_tx(bar(V_FULL + st), kTileBytes);
+        for (int h = 0; h < 2; ++h)
+          tma_load_3d(v_smem + st * kTileBytes + h * kHalfBytes, &tmap_v, bar(V_FULL + st), h * 64, kv_head, k0);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && n_tiles > 0) {
+      const uint32_t idesc_s = make_idesc(false, false, kBM, kBN);
+      const uint32_t idesc_dq = make_idesc(false, true, kBM, kD);     // A = dS from TMEM, B = K as [key, head dim]
+      auto issue_nt = [&](uint32_t d_col, uint32_t a_smem, uint32_t b_smem) {
+#pragma unroll
+        for (int k = 0; k < kD / 16; ++k) {
+          const uint32_t off = (uint32_t)(k >> 2) * kHalfBytes + (uint32_t)(k & 3) * 32u;
+          umma_bf16<1>(tmem_base + d_col, make_desc(a_smem + off, 16, 1024), make_desc(b_smem + off, 16, 1024), idesc_s,
+                       k != 0 ? 1u : 0u);
+        }
+      };
+      bool ok = mbar_wait(bar(Q_FULL), 0, abort_flag) && mbar_wait(bar(K_FULL), 0, abort_flag);
+      if (ok) {
+        tc_fence_after();
+        issue_nt(T_S, q_smem, k_smem);
+        umma_commit(bar(S_FULL));
+        ok = mbar_wait(bar(V_FULL), 0, abort_flag);
+      }
+      if (ok) {
+        tc_fence_after();
+        issue_nt(T_DP, do_smem, v_smem);
+        umma_commit(bar(DP_FULL));
+        umma_commit(bar(V_EMPTY));
+      }
+      for (int i = 0; i < n_tiles && ok; ++i) {
+        const int st = i & 1;
+        if (i + 1 < n_tiles) {
+          const int s1 = (i + 1) & 1;
+          if (!mbar_wait(bar(V_FULL + s1), ((i + 1) >> 1) & 1u, abort_flag)) { ok = false; break; }
+          tc_fence_after();
+          issue_nt(T_DP + s1 * 128, do_smem, v_smem + s1 * kTileBytes);
+          umma_commit(bar(DP_FULL + s1));
+          umma_commit(bar(V_EMPTY + s1));
+        }
+        if (!mbar_wait(bar(DS_READY), i & 1u, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+#pragma unroll
+        for (int ks = 0; ks < kBN / 16; ++ks) {
+          const uint32_t a_col = (uint32_t)(ks >> 2) * 64u + (uint32_t)(ks & 3) * 8u;
+          umma_bf16_ts(tmem_base + T_DQ, tmem_base + T_S + a_col,
+                       make_desc(k_smem + st * kTileBytes + ks * 2048, kHalfBytes, 1024), idesc_dq,
+                       (i > 0 || ks > 0) ? 1u : 0u);
+        }
+        umma_commit(bar(K_EMPTY + st));
+        if (i + 1 < n_tiles) {
+          const int s1 = (i + 1) & 1;
+          if (!mbar_wait(bar(K_FULL + s1), ((i + 1) >> 1) & 1u, abort_flag)) { ok = false; break; }
+          tc_fence_after();
+          issue_nt(T_S, q_smem, k_smem + s1 * kTileBytes);
+          umma_commit(bar(S_FULL));
+        }
+      }
+      if (ok) umma_commit(bar(DQ_FULL));
+    }
+  } else {
+    const int quarter = warp & 3;
+    const int half = (warp - 2) >> 2;
+    const int row_in_tile = quarter * 32 + lane;
+    const int row = q0 + row_in_tile;
+    const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
+    const bool row_ok = row < p.Tq;
+    const float l2 = row_ok ? p.lse[(int64_t)head * p.stat_stride + row] * 1.4426950408889634f : INFINITY;
+    const float dl = row_ok ? p.delta[(int64_t)head * p.stat_stride + row] : 0.f;
+    const int lo = p.kv_first != nullptr ? p.kv_first[min(row, p.Tq - 1)] : 0;
+    const int hi = min(p.Tk - 1, p.causal ? row + p.causal_offset : p.Tk - 1);
+    bool ok = true;
+    for (int i = 0; i < n_tiles; ++i) {
+      if (!mbar_wait(bar(S_FULL), i & 1u, abort_flag) || !mbar_wait(bar(DP_FULL + (i & 1)), (i >> 1) & 1u, abort_flag)) {
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      const int c0 = (j_lo + i) * kBN + half * 64;
+      const bool edge = (c0 + 63 > hi) || (c0 < lo);
+      uint32_t out[32];
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        uint32_t sv[32], dv[32];
+        tmem_ld32(tmem_base + lane_addr + T_S + half * 64 + c * 32, sv);
+        tmem_ld32(tmem_base + lane_addr + T_DP + (i & 1) * 128 + half * 64 + c * 32, dv);
+        tmem_ld_wait();
+#pragma unroll
+        for (int e = 0; e < 16; ++e) {
+          float ds2[2];
+#pragma unroll
+          for (int u = 0; u < 2; ++u) {
+            const int idx = 2 * e + u;
+            float pe = exp2f(fmaf(__uint_as_float(sv[idx]), p.scale_log2, -l2));
+            if (edge) {
+              const int col = c0 + c * 32 + idx;
+              if (col > hi || col < lo) pe = 0.f;
+            }
+            ds2[u] = pe * (__uint_as_float(dv[idx]) - dl) * p.scale;
+          }
+          out[c * 16 + e] = pack_bf16(ds2[0], ds2[1]);
+        }
+      }
+      // all S columns of this thread are in registers: the packed dS may now overwrite them
+      {
+        uint32_t a[16], b[16];
+#pragma unroll
+        for (int e = 0; e < 16; ++e) { a[e] = out[e]; b[e] = out[16 + e]; }
+        tmem_st16(tmem_base + lane_addr + T_S + half * 64, a);
+        tmem_st16(tmem_base + lane_addr + T_S + half * 64 + 16, b);
+      }
+      tmem_st_wait();
+      tc_fence_before();
+      mbar_arrive(bar(DS_READY));
+    }
+    if (ok && n_tiles > 0) ok = mbar_wait(bar(DQ_FULL), 0, abort_flag);
+    if (ok) {
+      tc_fence_after();
+      // dQ -> bf16 -> swizzled staging (the Q tile) -> TMA store; thread = (row, 64-column half)
+      const uint32_t stage = q_smem + half * kHalfBytes;
+#pragma unroll 1
+      for (int c = 0; c < 2; ++c) {
+        uint32_t o[32];
+        if (n_tiles > 0) {
+          tmem_ld32(tmem_base + lane_addr + T_DQ + half * 64 + c * 32, o);
+          tmem_ld_wait();
+        } else {
+#pragma unroll
+          for (int e = 0; e < 32; ++e) o[e] = 0u;
+        }
+#pragma unroll
+        for (int jj = 0; jj < 4; ++jj) {
+          uint32_t w[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e)
+            w[e] = pack_bf16(__uint_as_float(o[jj * 8 + 2 * e]), __uint_as_float(o[jj * 8 + 2 * e + 1]));
+          const int chunk = c * 4 + jj;
+          const uint32_t dst = stage + (uint32_t)row_in_tile * 128u + (uint32_t)((chunk ^ (row_in_tile & 7)) << 4);
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3])
+                       : "memory");
+        }
+      }
+      fence_proxy_async_smem();
+      mbar_arrive(bar(OUT_STAGED));
+      if (warp == 2 && lane == 0 && mbar_wait(bar(OUT_STAGED), 0, abort_flag)) {
+        for (int h = 0; h < 2; ++h) tma_store_3d(&tmap_dq, q_smem + h * kHalfBytes, h * 64, head, q0);
+        tma_store_commit();
+        tma_store_wait<0>();
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+  if (threadIdx.x == 0 && *abort_flag && p.status != nullptr) atomicOr(p.status, kStatusWaitTimedOut);
+}
+
 // delta[h, t] = sum_d dO[t, h, d] * O[t, h, d]: one warp per (token, head).
 __global__ void flash_delta_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ d_o,
-                                   float* __restrict__ delta, int T, int H) {
+                                   float* __restrict__ delta, int T, int H, int stride) {
   const int64_t w = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
   if (w >= (int64_t)T * H) return;
@@ -693,22 +895,9 @@ __global__ void flash_delta_kernel(const __nv_bfloat16* __restrict__ o, const __
   const float2 b0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&b.x));
   const float2 b1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&b.y));
   const float s = warp_sum(a0.x * b0.x + a0.y * b0.y + a1.x * b1.x + a1.y * b1.y);
-  if (lane == 0) delta[(int64_t)h * T + t] = s;
+  if (lane == 0) delta[(int64_t)h * stride + t] = s;
 }
 
-// fp32 [T, H, D] accumulator -> bf16 [T, H, D] view with arbitrary token / head strides.
-__global__ void flash_dq_cast_kernel(const float* __restrict__ acc, __nv_bfloat16* __restrict__ out, int64_t n_vec,
-                                     int H, int64_t stride_t, int64_t stride_h) {
-  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;   // one thread per 8 elements
-  if (i >= n_vec) return;
-  const int64_t row = i / (kD / 8);            // token * H + head
-  const int c = (int)(i % (kD / 8)) * 8;
-  const int64_t t = row / H, h = row % H;
-  const float4 x = *reinterpret_cast<const float4*>(acc + row * kD + c);
-  const float4 y = *reinterpret_cast<const float4*>(acc + row * kD + c + 4);
-  const float f[8] = {x.x, x.y, x.z, x.w, y.x, y.y, y.z, y.w};
-  *reinterpret_cast<bf16x8*>(out + t * stride_t + h * stride_h + c) = pack8(f);
-}
 }  // namespace flash
 
 // ----------------------------------------------------------------------------------------
@@ -752,7 +941,9 @@ std::tuple<at::Tensor, at::Tensor> flash_fwd(const at::Tensor& q, const at::Tens
   c10::cuda::CUDAGuard guard(q.device());
   C10_CUDA_CHECK(cudaSetDevice(q.device().index()));
   auto o = at::empty({Tq, Hq, kD}, q.options());
-  auto lse = at::empty({Hq, Tq}, q.options().dtype(at::kFloat));
+  // rows padded to a multiple of 64 floats: the backward fetches 64-row slices with bulk copies
+  const int64_t Tpad = (Tq + 63) / 64 * 64;
+  auto lse = at::empty({Hq, Tpad}, q.options().dtype(at::kFloat)).narrow(1, 0, Tq);
   if (Tq == 0) return {o, lse};
   TORCH_CHECK(Tk > 0, "flash_fwd: empty key sequence");
   const int group = (int)(Hq / Hkv);
@@ -770,6 +961,7 @@ std::tuple<at::Tensor, at::Tensor> flash_fwd(const at::Tensor& q, const at::Tens
     p.kv_first = kv_first->data_ptr<int>();
   }
   p.lse = lse.data_ptr<float>();
+  p.lse_stride = (int)Tpad;
   p.status = flash_status_tensor(q.device()).data_ptr<int>();
   const CUtensorMap tq = make_tmap_thd(q, kBM), tk = make_tmap_thd(k, kBN), tv = make_tmap_thd(v, kBN),
                     to = make_tmap_thd(o, kBM);
@@ -801,7 +993,7 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor> flash_bwd(const at::Tensor& d_o, 
               v.scalar_type() == at::kBFloat16 && o.scalar_type() == at::kBFloat16 && lse.scalar_type() == at::kFloat);
   const int64_t Tq = q.size(0), Hq = q.size(1), Tk = k.size(0), Hkv = k.size(1);
   TORCH_CHECK(q.size(2) == kD && k.size(2) == kD && v.size(2) == kD, "flash_bwd: head dimension must be 128");
-  TORCH_CHECK(o.is_contiguous() && d_o.is_contiguous() && lse.is_contiguous(), "flash_bwd: o, dO and lse must be contiguous");
+  TORCH_CHECK(o.is_contiguous() && d_o.is_contiguous(), "flash_bwd: o and dO must be contiguous");
   TORCH_CHECK(o.size(0) == Tq && o.size(1) == Hq && d_o.sizes() == o.sizes() && lse.size(0) == Hq && lse.size(1) == Tq);
   c10::cuda::CUDAGuard guard(q.device());
   C10_CUDA_CHECK(cudaSetDevice(q.device().index()));
@@ -813,16 +1005,22 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor> flash_bwd(const at::Tensor& d_o, 
   TORCH_CHECK(dk.dim() == 3 && dk.size(0) == Tk && dk.size(1) == Hkv && dk.size(2) == kD);
   TORCH_CHECK(dv.dim() == 3 && dv.size(0) == Tk && dv.size(1) == Hkv && dv.size(2) == kD);
   if (Tq == 0 || Tk == 0) return {dq, dk, dv};
-  auto delta = at::empty({Hq, Tq}, lse.options());
+  const int64_t Tpad = (Tq + 63) / 64 * 64;
+  // lse as returned by flash_fwd has padded rows; anything else is copied into that layout
+  at::Tensor lse_p = lse;
+  if (!(lse.stride(1) == 1 && lse.stride(0) == Tpad && (reinterpret_cast<uintptr_t>(lse.data_ptr()) & 15) == 0)) {
+    lse_p = at::zeros({Hq, Tpad}, lse.options()).narrow(1, 0, Tq);
+    lse_p.copy_(lse);
+  }
+  auto delta = at::zeros({Hq, Tpad}, lse.options());
   {
     const int64_t warps = Tq * Hq;
     const int threads = 256;
     flash_delta_kernel<<<(unsigned)((warps * 32 + threads - 1) / threads), threads, 0, stream>>>(
         reinterpret_cast<const __nv_bfloat16*>(o.data_ptr()), reinterpret_cast<const __nv_bfloat16*>(d_o.data_ptr()),
-        delta.data_ptr<float>(), (int)Tq, (int)Hq);
+        delta.data_ptr<float>(), (int)Tq, (int)Hq, (int)Tpad);
     C10_CUDA_KERNEL_LAUNCH_CHECK();
   }
-  auto dq_acc = at::zeros({Tq, Hq, kD}, lse.options());
   BwdParams p;
   p.Tq = (int)Tq; p.Tk = (int)Tk; p.Hq = (int)Hq; p.Hkv = (int)Hkv;
   p.causal = causal ? 1 : 0;
@@ -835,35 +1033,34 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor> flash_bwd(const at::Tensor& d_o, 
                 kv_first->is_contiguous(), "flash_bwd: kv_first must be an int32 [Tq] CUDA tensor");
     p.kv_first = kv_first->data_ptr<int>();
   }
-  p.lse = lse.data_ptr<float>();
+  p.lse = lse_p.data_ptr<float>();
   p.delta = delta.data_ptr<float>();
+  p.stat_stride = (int)Tpad;
   p.status = flash_status_tensor(q.device()).data_ptr<int>();
-  const CUtensorMap tq = make_tmap_thd(q, kBQ), tdo = make_tmap_thd(d_o, kBQ), tk = make_tmap_thd(k, kBN),
-                    tv = make_tmap_thd(v, kBN), tdk = make_tmap_thd(dk, kBN), tdv = make_tmap_thd(dv, kBN);
-  CUtensorMap tdq;
   {
-    const cuuint64_t dims[3] = {(cuuint64_t)kD, (cuuint64_t)Hq, (cuuint64_t)Tq};
-    const cuuint64_t strides[2] = {(cuuint64_t)kD * 4, (cuuint64_t)Hq * kD * 4};
-    const cuuint32_t box[3] = {(cuuint32_t)kD, 1, (cuuint32_t)kBQ};
-    const cuuint32_t elem[3] = {1, 1, 1};
-    const CUresult r = cuTensorMapEncodeTiled(&tdq, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, dq_acc.data_ptr(), dims, strides, box,
-                                              elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
-                                              CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    TORCH_CHECK(r == CUDA_SUCCESS, "cuTensorMapEncodeTiled (dq accumulator) failed with code ", (int)r);
+    const CUtensorMap tq = make_tmap_thd(q, kBQ), tdo = make_tmap_thd(d_o, kBQ), tk = make_tmap_thd(k, kBN),
+                      tv = make_tmap_thd(v, kBN), tdk = make_tmap_thd(dk, kBN), tdv = make_tmap_thd(dv, kBN);
+    constexpr uint32_t smem = 2 * kTileBytes + kRing * 2 * kQBytes + kRing * 512 + 1024 + 256;
+    static bool attr_set = false;
+    if (!attr_set) {
+      C10_CUDA_CHECK(cudaFuncSetAttribute(flash_bwd_dkv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+      attr_set = true;
+    }
+    const int num_k_tiles = (int)((Tk + kBN - 1) / kBN);
+    flash_bwd_dkv_kernel<<<num_k_tiles * (int)Hkv, kThreadsBwd, smem, stream>>>(tq, tdo, tk, tv, tdk, tdv, p);
+    C10_CUDA_KERNEL_LAUNCH_CHECK();
   }
-  constexpr uint32_t smem = 2 * kTileBytes + 4 * kQBytes + kQBytes + kBQ * kD * 4 + 1024 + 256;
-  static bool attr_set = false;
-  if (!attr_set) {
-    C10_CUDA_CHECK(cudaFuncSetAttribute(flash_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-    attr_set = true;
-  }
-  const int num_k_tiles = (int)((Tk + kBN - 1) / kBN);
-  flash_bwd_kernel<<<num_k_tiles * (int)Hkv, kThreadsBwd, smem, stream>>>(tq, tdo, tk, tv, tdk, tdv, tdq, p);
-  C10_CUDA_KERNEL_LAUNCH_CHECK();
   {
-    const int64_t n_vec = Tq * Hq * (kD / 8);
-    flash_dq_cast_kernel<<<(unsigned)((n_vec + 255) / 256), 256, 0, stream>>>(
-        dq_acc.data_ptr<float>(), reinterpret_cast<__nv_bfloat16*>(dq.data_ptr()), n_vec, (int)Hq, dq.stride(0), dq.stride(1));
+    const CUtensorMap tq = make_tmap_thd(q, kBM), tdo = make_tmap_thd(d_o, kBM), tk = make_tmap_thd(k, kBN),
+                      tv = make_tmap_thd(v, kBN), tdq = make_tmap_thd(dq, kBM);
+    constexpr uint32_t smem = 6 * kTileBytes + 1024 + 256;
+    static bool attr_set = false;
+    if (!attr_set) {
+      C10_CUDA_CHECK(cudaFuncSetAttribute(flash_bwd_dq_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+      attr_set = true;
+    }
+    const int num_q_tiles = (int)((Tq + kBM - 1) / kBM);
+    flash_bwd_dq_kernel<<<num_q_tiles * (int)Hq, kThreadsBwd, smem, stream>>>(tq, tdo, tk, tv, tdq, p);
     C10_CUDA_KERNEL_LAUNCH_CHECK();
   }
   return {dq, dk, dv};

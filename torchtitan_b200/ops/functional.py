@@ -31,7 +31,7 @@ from . import ext, reference as ref
 
 __all__ = [
     "settings", "rms_norm", "linear", "norm_linear", "swiglu", "swiglu_linear", "rope_qk_", "rope",
-    "attention", "linear_cross_entropy", "cross_entropy_sum", "gemm_nt", "gemm_nn", "gemm_tn", "embedding",
+    "attention", "attention_packed", "linear_cross_entropy", "cross_entropy_sum", "gemm_nt", "gemm_nn", "gemm_tn", "embedding",
 ]
 
 
@@ -422,23 +422,70 @@ def _sdpa_causal(q, k, v, scale):
     return out.squeeze(0).transpose(0, 1)
 
 
+def _native_attention_ok(q, k, v) -> bool:
+    if not (_cuda(q) and settings.attention == "native"):
+        return False
+    from . import flash
+
+    return flash.supported(q, k, v)
+
+
 def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, scale: float | None = None, causal: bool = True,
               doc_ids: torch.Tensor | None = None, window: int | None = None, sinks: torch.Tensor | None = None,
-              q_pos: torch.Tensor | None = None, k_pos: torch.Tensor | None = None) -> torch.Tensor:
+              q_pos: torch.Tensor | None = None, k_pos: torch.Tensor | None = None,
+              kv_first: torch.Tensor | None = None) -> torch.Tensor:
     """Attention over folded tokens: ``q[T,Hq,D]``, ``k/v[T,Hkv,D]`` -> ``[T,Hq,Dv]``.
 
-    Documents are separated with ``doc_ids`` (``None`` = one document).
+    Documents are separated with ``doc_ids`` (``None`` = one document); ``kv_first`` is the same
+    information as the index of the first token of each query's document, the form the
+    tcgen05 kernel consumes.
     """
     if scale is None:
         scale = 1.0 / math.sqrt(q.shape[-1])
-    plain = doc_ids is None and window is None and sinks is None and q_pos is None and k_pos is None and causal
-    if _cuda(q) and settings.attention == "native" and plain and ext.available() and hasattr(torch.ops.tb200, "flash_fwd"):
+    simple = window is None and sinks is None and q_pos is None and k_pos is None and causal
+    if simple and (doc_ids is None or kv_first is not None) and _native_attention_ok(q, k, v):
         from .flash import flash_attention
 
-        return flash_attention(q, k, v, scale)
-    if plain and q.shape[-1] == v.shape[-1]:
+        _count(4)  # forward + (delta, backward, dq cast)
+        return flash_attention(q, k, v, scale, causal=True, kv_first=kv_first)
+    if simple and doc_ids is None and q.shape[-1] == v.shape[-1]:
         return _sdpa_causal(q, k, v, scale)
     return _masked_attention(q, k, v, scale, causal, doc_ids, window, sinks, q_pos, k_pos)
+
+
+class _PackedFlashFn(torch.autograd.Function):
+    """Causal attention on a packed projection output ``[T, Hq + 2 Hkv, 128]``; the gradient
+    comes back as one packed tensor, written in place by the backward kernel."""
+
+    @staticmethod
+    def forward(ctx, qkv3, hq, hkv, scale, kv_first):
+        ops = ext.require()
+        q, k, v = qkv3[:, :hq], qkv3[:, hq:hq + hkv], qkv3[:, hq + hkv:]
+        o, lse = ops.flash_fwd(q, k, v, scale, True, 0, kv_first)
+        ctx.save_for_backward(qkv3, o, lse, kv_first if kv_first is not None else torch.empty(0))
+        ctx.meta = (hq, hkv, scale, kv_first is not None)
+        return o
+
+    @staticmethod
+    def backward(ctx, d_o):
+        qkv3, o, lse, kv_first = ctx.saved_tensors
+        hq, hkv, scale, has_first = ctx.meta
+        ops = ext.require()
+        q, k, v = qkv3[:, :hq], qkv3[:, hq:hq + hkv], qkv3[:, hq + hkv:]
+        g = torch.empty_like(qkv3)
+        ops.flash_bwd(d_o.contiguous(), q, k, v, o, lse, scale, True, 0, kv_first if has_first else None,
+                      g[:, :hq], g[:, hq:hq + hkv], g[:, hq + hkv:])
+        return g, None, None, None, None
+
+
+def attention_packed(qkv3: torch.Tensor, hq: int, hkv: int, scale: float, *, doc_ids: torch.Tensor | None = None,
+                     kv_first: torch.Tensor | None = None) -> torch.Tensor:
+    """Causal attention where q, k and v are head slices of one ``[T, Hq + 2 Hkv, D]`` tensor."""
+    q, k, v = qkv3[:, :hq], qkv3[:, hq:hq + hkv], qkv3[:, hq + hkv:]
+    if (doc_ids is None or kv_first is not None) and qkv3.is_contiguous() and _native_attention_ok(q, k, v):
+        _count(4)
+        return _PackedFlashFn.apply(qkv3, hq, hkv, float(scale), kv_first)
+    return attention(q, k, v, scale=scale, causal=True, doc_ids=doc_ids, kv_first=kv_first)
 
 
 def _masked_attention(q, k, v, scale, causal, doc_ids, window, sinks, q_pos, k_pos):

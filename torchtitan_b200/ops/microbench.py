@@ -90,14 +90,14 @@ def bench_attention(args) -> None:
         if args.once:
             o, lse = ops.flash_fwd(q, k, v, scale, True, 0, None)
             if has_bwd:
-                ops.flash_bwd(do, q, k, v, o, lse, scale, True, 0, None)
+                ops.flash_bwd(do, q, k, v, o, lse, scale, True, 0, None, None, None, None)
             torch.cuda.synchronize()
             continue
         tf = timer(lambda: ops.flash_fwd(q, k, v, scale, True, 0, None))
         line = f"attention tcgen05 T{Tn} H{H}/{Hkv} D{D}: fwd {tf:.3f} ms {fl_f / tf / 1e9:.0f} TFLOPS"
         if has_bwd:
             o, lse = ops.flash_fwd(q, k, v, scale, True, 0, None)
-            tb = timer(lambda: ops.flash_bwd(do, q, k, v, o, lse, scale, True, 0, None))
+            tb = timer(lambda: ops.flash_bwd(do, q, k, v, o, lse, scale, True, 0, None, None, None, None))
             line += f" | bwd {tb:.3f} ms {2.5 * fl_f / tb / 1e9:.0f} TFLOPS"
         print(line, flush=True)
         # library arm: cuDNN / flash SDPA on [1, H, T, D]
