@@ -47,8 +47,8 @@ def parse_args():
     p.add_argument("--seq-len", type=int, default=8192)
     p.add_argument("--local-batch", type=int, default=1)
     p.add_argument("--fsdp-comm", default=os.environ.get("TB200_FSDP_COMM", "auto"))
-    p.add_argument("--gemm", default=os.environ.get("TB200_GEMM", "cublas"))
-    p.add_argument("--attention", default=os.environ.get("TB200_ATTENTION", "sdpa"))
+    p.add_argument("--gemm", default=os.environ.get("TB200_GEMM", "tcgen05"))
+    p.add_argument("--attention", default=os.environ.get("TB200_ATTENTION", "native"))
     p.add_argument("--opt-state", default="fp32", choices=["fp32", "bf16"])
     p.add_argument("--ac", default="selective")
     p.add_argument("--skip-e2e", action="store_true")

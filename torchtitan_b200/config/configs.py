@@ -141,6 +141,6 @@ class ActivationCheckpointConfig:
 class KernelConfig:
     """Selects hand-written sm_100a kernels vs. the library baseline per op."""
 
-    gemm: Literal["cublas", "tcgen05"] = "cublas"
-    attention: Literal["sdpa", "native"] = "sdpa"
+    gemm: Literal["cublas", "tcgen05"] = "tcgen05"
+    attention: Literal["sdpa", "native"] = "native"
     elementwise: Literal["native", "torch"] = "native"

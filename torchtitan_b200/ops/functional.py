@@ -37,8 +37,8 @@ __all__ = [
 
 @dataclass
 class _Settings:
-    gemm: str = "cublas"  # "cublas" | "tcgen05"
-    attention: str = "sdpa"  # "sdpa" | "native"
+    gemm: str = "tcgen05"  # "cublas" | "tcgen05"
+    attention: str = "native"  # "sdpa" | "native"
     recompute: bool = True  # fused functions recompute norm / SwiGLU activations in backward
     launches: int = 0  # count of launches of this package's own kernels
     count_launches: bool = False
