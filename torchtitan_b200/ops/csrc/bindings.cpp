@@ -16,6 +16,8 @@ void adamw_(at::Tensor master, const at::Tensor& grad, at::Tensor exp_avg, at::T
             double beta2, double eps, double weight_decay, double bc1, double bc2);
 void sumsq_(const at::Tensor& x, at::Tensor acc);
 void gemm_bf16(const at::Tensor& a, const at::Tensor& b, at::Tensor c, int64_t mode, bool accumulate);
+void gemm_grouped_bf16(const at::Tensor& a, const at::Tensor& b, at::Tensor c, const at::Tensor& offs, int64_t mode,
+                       int64_t align, bool accumulate);
 int64_t gemm_status(bool clear);
 void gemm_set_variant(int64_t v);
 void gemm_set_debug(int64_t v);
@@ -52,6 +54,8 @@ TORCH_LIBRARY(tb200, m) {
         &tb200::adamw_);
   m.def("sumsq_(Tensor x, Tensor(a!) acc) -> ()", &tb200::sumsq_);
   m.def("gemm_bf16(Tensor a, Tensor b, Tensor(a!) c, int mode, bool accumulate) -> ()", &tb200::gemm_bf16);
+  m.def("gemm_grouped_bf16(Tensor a, Tensor b, Tensor(a!) c, Tensor offs, int mode, int align, bool accumulate) -> ()",
+        &tb200::gemm_grouped_bf16);
   m.def("gemm_status(bool clear) -> int", &tb200::gemm_status);
   m.def("gemm_set_variant(int v) -> ()", &tb200::gemm_set_variant);
   m.def("gemm_set_debug(int v) -> ()", &tb200::gemm_set_debug);

@@ -74,6 +74,20 @@ struct Params {
   int debug;       // bit 0: no TMA loads (MMA issue rate on stale shared memory), bit 1: no stores
   __nv_bfloat16* C;
   int* status;
+  // Grouped forms (rows sorted by group, e.g. tokens sorted by expert).  group_offs[g] is the first
+  // row of group g, group_offs[num_groups] the number of valid rows; every offset is a multiple of
+  // the row tile, so no tile straddles two groups.
+  //   group_mode 1: rows of A and C are grouped, B holds one matrix per group (b_group_rows rows each)
+  //   group_mode 2: the K dimension (rows of A and B in TN mode) is grouped, C holds one M x N matrix per group
+  const int* group_offs;
+  int num_groups;
+  int group_mode;
+  int b_group_rows;
+  int c_rows;       // rows of the 2-D view of C
+};
+
+struct Tile {
+  int skip, m_base, n0, c_row, b_row_off, k_beg, nkb;
 };
 
 template <int kCta>
@@ -107,8 +121,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   constexpr int kTileM = BM * kCta;
   const int num_m = (p.M + kTileM - 1) / kTileM;
   const int num_n = (p.N + BN - 1) / BN;
-  const int num_tiles = num_m * num_n;
-  const int num_kb = (p.K + BK - 1) / BK;
+  const int tiles_per_group = num_m * num_n;
+  const int num_tiles = p.group_mode == 2 ? tiles_per_group * p.num_groups : tiles_per_group;
   constexpr int kGroupM = kGroupRows / kTileM;
   // tile index -> (row tile, column tile): groups of kGroupM row tiles, row index fastest
   auto tile_coord = [&](int t, int& tm, int& tn) {
@@ -119,6 +133,41 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     const int r = t - g * per_group;
     tm = first + r % gsz;
     tn = r / gsz;
+  };
+  // Every role derives the same description of a tile (and skips the same tiles).
+  auto tile_info = [&](int t) {
+    Tile ti;
+    int tm, tn, e = 0;
+    if (p.group_mode == 2) {
+      e = t / tiles_per_group;
+      t -= e * tiles_per_group;
+    }
+    tile_coord(t, tm, tn);
+    ti.skip = 0;
+    ti.m_base = tm * kTileM;
+    ti.n0 = tn * BN;
+    ti.c_row = ti.m_base;
+    ti.b_row_off = 0;
+    ti.k_beg = 0;
+    ti.nkb = (p.K + BK - 1) / BK;
+    if (p.group_mode == 1) {
+      const int total = p.group_offs[p.num_groups];
+      if (ti.m_base >= total) {
+        ti.skip = 1;
+      } else {
+        int lo = 0, hi = p.num_groups;     // largest g with group_offs[g] <= m_base
+        while (hi - lo > 1) {
+          const int mid = (lo + hi) >> 1;
+          if (p.group_offs[mid] <= ti.m_base) lo = mid; else hi = mid;
+        }
+        ti.b_row_off = lo * p.b_group_rows;
+      }
+    } else if (p.group_mode == 2) {
+      ti.k_beg = p.group_offs[e];
+      ti.nkb = (p.group_offs[e + 1] - ti.k_beg + BK - 1) / BK;
+      ti.c_row = e * p.M + ti.m_base;
+    }
+    return ti;
   };
 
   if (threadIdx.x == 0) {
@@ -153,11 +202,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       uint32_t it = 0;
       bool ok = true;
       for (int tile = unit; tile < num_tiles && ok; tile += num_units) {
-        int tm, tn;
-        tile_coord(tile, tm, tn);
-        const int m0 = tm * kTileM + (int)cta_rank * BM;
-        const int n0 = tn * BN + (int)cta_rank * C_::kBRows;
-        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+        const Tile ti = tile_info(tile);
+        if (ti.skip) continue;
+        const int m0 = ti.m_base + (int)cta_rank * BM;
+        const int n0 = ti.n0 + (int)cta_rank * C_::kBRows;
+        for (int kb = 0; kb < ti.nkb; ++kb, ++it) {
           const int s = it % kStages;
           const uint32_t parity = ((it / kStages) & 1u) ^ 1u;
           const bool got = kCta == 1 ? mbar_wait(empty_bar(s), parity, abort_flag)
@@ -165,7 +214,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           if (!got) { ok = false; break; }
           const uint32_t sa = base + s * kStageBytes;
           const uint32_t sb = sa + kABytes;
-          const int k0 = kb * BK;
+          const int k0 = ti.k_beg + kb * BK;
           // bytes of both CTAs are counted by the barrier of CTA 0
           const uint32_t fb = kCta == 1 ? full_bar(s) : mapa(full_bar(s), 0);
           auto load = [&](uint32_t dst, const CUtensorMap* map, int c0, int c1) {
@@ -187,11 +236,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
               load(sa + b * (BK * 128), &tmap_a, m0 + b * 64, k0);
           }
           if (!p.b_mn_major) {
-            load(sb, &tmap_b, k0, n0);                                // box {64 k, kBRows rows}
+            load(sb, &tmap_b, k0, n0 + ti.b_row_off);                 // box {64 k, kBRows rows}
           } else {
 #pragma unroll
             for (int b = 0; b < C_::kBRows / 64; ++b)
-              load(sb + b * (BK * 128), &tmap_b, n0 + b * 64, k0);
+              load(sb + b * (BK * 128), &tmap_b, n0 + b * 64, k0 + ti.b_row_off);
           }
         }
       }
@@ -207,9 +256,13 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       const uint32_t b_lbo = p.b_mn_major ? BK * 128 : 16, b_step = p.b_mn_major ? 2048 : 32;
       uint32_t it = 0, tcount = 0;
       bool ok = true;
-      for (int tile = unit; tile < num_tiles && ok; tile += num_units, ++tcount) {
+      for (int tile = unit; tile < num_tiles && ok; tile += num_units) {
+        const Tile ti = tile_info(tile);
+        if (ti.skip) continue;
+        const int num_kb = ti.nkb;
         const int acc = tcount & 1;
         const uint32_t acc_parity = ((tcount >> 1) & 1u) ^ 1u;
+        ++tcount;
         const bool got = kCta == 1 ? mbar_wait(tempty_bar(acc), acc_parity, abort_flag)
                                    : mbar_wait_cluster(tempty_bar(acc), acc_parity, abort_flag);
         if (!got) { ok = false; break; }
@@ -234,9 +287,13 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           if constexpr (kCta == 1) umma_commit(empty_bar(s));
           else umma_commit_pair(empty_bar(s), 3);
         }
-        if (ok) {
+        if (ok && num_kb > 0) {
           if constexpr (kCta == 1) umma_commit(tfull_bar(acc));
           else umma_commit_pair(tfull_bar(acc), 3);
+        } else if (ok) {
+          // an empty group: nothing was issued, the epilogue writes zeros
+          mbar_arrive(tfull_bar(acc));
+          if constexpr (kCta == 2) mbar_arrive_cluster(mapa(tfull_bar(acc), 1));
         }
       }
     }
@@ -246,13 +303,14 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     uint32_t tcount = 0, sbuf = 0;
     bool ok = true;
     const uint32_t te_leader = kCta == 1 ? 0u : mapa(tempty_bar(0), 0);
-    for (int tile = unit; tile < num_tiles && ok; tile += num_units, ++tcount) {
+    for (int tile = unit; tile < num_tiles && ok; tile += num_units) {
+      const Tile ti = tile_info(tile);
+      if (ti.skip) continue;
       const int acc = tcount & 1;
       const uint32_t acc_parity = (tcount >> 1) & 1u;
-      int tm, tn;
-      tile_coord(tile, tm, tn);
-      const int m0 = tm * kTileM + (int)cta_rank * BM;
-      const int n0 = tn * BN;
+      ++tcount;
+      const int m0 = ti.c_row + (int)cta_rank * BM;
+      const int n0 = ti.n0;
       const bool got = kCta == 1 ? mbar_wait(tfull_bar(acc), acc_parity, abort_flag)
                                  : mbar_wait_cluster(tfull_bar(acc), acc_parity, abort_flag);
       if (!got) { ok = false; break; }
@@ -266,9 +324,14 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         for (int c = 0; c < BN / 64; ++c) {
           uint32_t r0[32], r1[32];
           const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN + c * 64);
-          tmem_ld32(taddr, r0);
-          tmem_ld32(taddr + 32, r1);
-          tmem_ld_wait();
+          if (ti.nkb > 0) {
+            tmem_ld32(taddr, r0);
+            tmem_ld32(taddr + 32, r1);
+            tmem_ld_wait();
+          } else {
+#pragma unroll
+            for (int e = 0; e < 32; ++e) r0[e] = r1[e] = 0u;
+          }
           if (lane == 0) tma_store_wait_read<1>();   // the tile written two steps ago has been read
           __syncwarp();
           const uint32_t buf = stage0 + (sbuf ? 4096u : 0u);
@@ -290,7 +353,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           fence_proxy_async_smem();
           __syncwarp();
           const int col0 = n0 + c * 64;
-          if (lane == 0 && col0 < p.N && m0 + q * 32 < p.M && !(p.debug & 2)) {
+          if (lane == 0 && col0 < p.N && m0 + q * 32 < p.c_rows && !(p.debug & 2)) {
             if (p.accumulate) tma_reduce_add_2d(&tmap_c, buf, col0, m0 + q * 32);
             else tma_store_2d(&tmap_c, buf, col0, m0 + q * 32);
             tma_store_commit();
@@ -366,7 +429,7 @@ static void launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const CUte
     attr_set = true;
   }
   const int tile_m = BM * kCta;
-  const int tiles = ((p.M + tile_m - 1) / tile_m) * ((p.N + BN - 1) / BN);
+  const int tiles = ((p.M + tile_m - 1) / tile_m) * ((p.N + BN - 1) / BN) * (p.group_mode == 2 ? p.num_groups : 1);
   cudaLaunchConfig_t cfg = {};
   cfg.blockDim = dim3(kThreads);
   cfg.dynamicSmemBytes = C_::kSmemBytes;
@@ -396,47 +459,115 @@ static void launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const CUte
   C10_CUDA_CHECK(cudaLaunchKernelEx(&cfg, gemm_bf16_kernel<kCta>, ta, tb, tc_, p));
 }
 
+struct GroupArgs {
+  const int* offs = nullptr;
+  int num_groups = 0;
+  int mode = 0;
+  int b_group_rows = 0;
+  int align = 0;        // every group offset is a multiple of this many rows
+};
+
+// Shared launcher.  a / b / c are the 2-D row-major views described by (rows, cols); the logical
+// problem is M x N x K with A stored [K, M] when a_mn and B stored [K, N] when b_mn.
+static void run_gemm(const at::Tensor& ref, const void* a, int64_t a_rows, int64_t a_cols, const void* b, int64_t b_rows,
+                     int64_t b_cols, void* c, int64_t c_rows, int64_t M, int64_t N, int64_t K, bool a_mn, bool b_mn,
+                     bool accumulate, const GroupArgs& g) {
+  using namespace gemm;
+  c10::cuda::CUDAGuard guard(ref.device());
+  // The tensor-map encoder is a driver-API call and needs the primary context current on this
+  // thread; autograd worker threads may not have bound it yet.
+  C10_CUDA_CHECK(cudaSetDevice(ref.device().index()));
+  bool pair;
+  if (g.mode == 1) pair = g.align % 256 == 0 && M >= 512;
+  else if (g.mode == 2) pair = M % 256 == 0;
+  else pair = M >= 512;   // the CTA pair pays off once a 256-row tile is full
+  if (g_gemm_variant == 1 && !(g.mode == 2 && false)) pair = false;
+  if (g_gemm_variant == 2 && (g.mode == 0 || (g.mode == 1 && g.align % 256 == 0) || (g.mode == 2 && M % 256 == 0))) pair = true;
+  if (g.mode == 1) TORCH_CHECK(g.align % (pair ? 256 : 128) == 0, "grouped gemm: group offsets must be multiples of the row tile");
+  if (g.mode == 2) TORCH_CHECK(M % (pair ? 256 : 128) == 0 && g.align % 64 == 0, "grouped gemm: M must be a multiple of the row tile");
+  const uint32_t b_box_rows = pair ? Cfg<2>::kBRows : Cfg<1>::kBRows;
+  // K-major: inner = K, box {64, rows};  MN-major: inner = MN extent, box {64, 64 k-rows}
+  const CUtensorMap ta = a_mn ? make_tmap_2d(a, a_cols, a_rows, a_cols * 2, 64, BK)
+                              : make_tmap_2d(a, a_cols, a_rows, a_cols * 2, BK, BM);
+  const CUtensorMap tb = b_mn ? make_tmap_2d(b, b_cols, b_rows, b_cols * 2, 64, BK)
+                              : make_tmap_2d(b, b_cols, b_rows, b_cols * 2, BK, b_box_rows);
+  const CUtensorMap tcm = make_tmap_2d(c, N, c_rows, N * 2, 64, 32);   // store tiles: 64 columns x 32 rows
+  Params p;
+  p.M = (int)M; p.N = (int)N; p.K = (int)K;
+  p.a_mn_major = a_mn; p.b_mn_major = b_mn; p.accumulate = accumulate ? 1 : 0;
+  p.debug = g_gemm_debug;
+  p.C = reinterpret_cast<__nv_bfloat16*>(c);
+  p.status = gemm_status_tensor(ref.device()).data_ptr<int>();
+  p.group_offs = g.offs; p.num_groups = g.num_groups; p.group_mode = g.mode; p.b_group_rows = g.b_group_rows;
+  p.c_rows = (int)c_rows;
+  auto stream = at::cuda::getCurrentCUDAStream();
+  if (pair) launch_gemm<2>(ta, tb, tcm, p, stream);
+  else launch_gemm<1>(ta, tb, tcm, p, stream);
+}
+
+static void check_bf16_2d(const at::Tensor& t, const char* name) {
+  TORCH_CHECK(t.is_cuda() && t.scalar_type() == at::kBFloat16 && t.is_contiguous(), "gemm: ", name,
+              " must be a contiguous CUDA bf16 tensor");
+  TORCH_CHECK((reinterpret_cast<uintptr_t>(t.data_ptr()) & 15) == 0, "gemm: ", name, " must be 16-byte aligned");
+}
+
 // mode: 0 = NT (a[M,K], b[N,K]), 1 = NN (a[M,K], b[K,N]), 2 = TN (a[K,M], b[K,N]).
 void gemm_bf16(const at::Tensor& a, const at::Tensor& b, at::Tensor c, int64_t mode, bool accumulate) {
-  TORCH_CHECK(a.is_cuda() && b.is_cuda() && c.is_cuda());
-  TORCH_CHECK(a.scalar_type() == at::kBFloat16 && b.scalar_type() == at::kBFloat16 && c.scalar_type() == at::kBFloat16);
-  TORCH_CHECK(a.dim() == 2 && b.dim() == 2 && c.dim() == 2 && a.is_contiguous() && b.is_contiguous() && c.is_contiguous());
+  check_bf16_2d(a, "a"); check_bf16_2d(b, "b"); check_bf16_2d(c, "c");
+  TORCH_CHECK(a.dim() == 2 && b.dim() == 2 && c.dim() == 2);
   const bool a_mn = mode == 2, b_mn = mode != 0;
   const int64_t M = a_mn ? a.size(1) : a.size(0);
   const int64_t K = a_mn ? a.size(0) : a.size(1);
   const int64_t N = b_mn ? b.size(1) : b.size(0);
   TORCH_CHECK((b_mn ? b.size(0) : b.size(1)) == K, "gemm_bf16: inner dimensions differ");
   TORCH_CHECK(c.size(0) == M && c.size(1) == N, "gemm_bf16: bad output shape");
-  // Row strides of every operand must be multiples of 16 bytes (TMA), and the epilogue stores 16-byte vectors.
+  // Row strides of every operand must be multiples of 16 bytes (TMA).
   TORCH_CHECK(N % 8 == 0, "gemm_bf16: N must be a multiple of 8");
   TORCH_CHECK(a_mn ? (M % 8 == 0) : (K % 8 == 0), "gemm_bf16: the contiguous dimension of A must be a multiple of 8");
   TORCH_CHECK(b_mn || K % 8 == 0, "gemm_bf16: the contiguous dimension of B must be a multiple of 8");
-  TORCH_CHECK((reinterpret_cast<uintptr_t>(a.data_ptr()) & 15) == 0 && (reinterpret_cast<uintptr_t>(b.data_ptr()) & 15) == 0 &&
-              (reinterpret_cast<uintptr_t>(c.data_ptr()) & 15) == 0, "gemm_bf16: operands must be 16-byte aligned");
   if (M == 0 || N == 0) return;
-  c10::cuda::CUDAGuard guard(a.device());
-  // The tensor-map encoder is a driver-API call and needs the primary context current on this
-  // thread; autograd worker threads may not have bound it yet.
-  C10_CUDA_CHECK(cudaSetDevice(a.device().index()));
-  using namespace gemm;
-  // The CTA pair pays off once a 256-row tile is full and there is more than one wave of work.
-  const bool pair = g_gemm_variant == 2 || (g_gemm_variant == 0 && M >= 512);
-  const uint32_t b_rows = pair ? Cfg<2>::kBRows : Cfg<1>::kBRows;
-  // K-major: inner = K, box {64, rows};  MN-major: inner = MN extent, box {64, 64 k-rows}
-  const CUtensorMap ta = a_mn ? make_tmap_2d(a.data_ptr(), M, K, M * 2, 64, BK)
-                              : make_tmap_2d(a.data_ptr(), K, M, K * 2, BK, BM);
-  const CUtensorMap tb = b_mn ? make_tmap_2d(b.data_ptr(), N, K, N * 2, 64, BK)
-                              : make_tmap_2d(b.data_ptr(), K, N, K * 2, BK, b_rows);
-  Params p;
-  p.M = (int)M; p.N = (int)N; p.K = (int)K;
-  p.a_mn_major = a_mn; p.b_mn_major = b_mn; p.accumulate = accumulate ? 1 : 0;
-  p.debug = g_gemm_debug;
-  p.C = reinterpret_cast<__nv_bfloat16*>(c.data_ptr());
-  p.status = gemm_status_tensor(a.device()).data_ptr<int>();
-  auto stream = at::cuda::getCurrentCUDAStream();
-  const CUtensorMap tcm = make_tmap_2d(c.data_ptr(), N, M, N * 2, 64, 32);   // store tiles: 64 columns x 32 rows
-  if (pair) launch_gemm<2>(ta, tb, tcm, p, stream);
-  else launch_gemm<1>(ta, tb, tcm, p, stream);
+  run_gemm(a, a.data_ptr(), a.size(0), a.size(1), b.data_ptr(), b.size(0), b.size(1), c.data_ptr(), M, M, N, K, a_mn, b_mn,
+           accumulate, GroupArgs());
+}
+
+// Grouped GEMM over rows sorted by group (tokens sorted by expert).  offs: int32 [G + 1] on the
+// device, offs[g] = first row of group g, offs[G] = number of valid rows, all multiples of `align`
+// (128 or 256): groups are padded, padded rows of the inputs are zero.
+//   mode 0: c[rows of g] = a[rows of g] . b[g]^T      a [R, K], b [G, N, K], c [R, N]
+//   mode 1: c[rows of g] = a[rows of g] . b[g]        a [R, K], b [G, K, N], c [R, N]
+//   mode 2: c[g] = a[rows of g]^T . b[rows of g]      a [R, M], b [R, N],    c [G, M, N]
+// Rows of c at or beyond offs[G] (modes 0, 1) are not written.
+void gemm_grouped_bf16(const at::Tensor& a, const at::Tensor& b, at::Tensor c, const at::Tensor& offs, int64_t mode,
+                       int64_t align, bool accumulate) {
+  check_bf16_2d(a, "a"); check_bf16_2d(b, "b"); check_bf16_2d(c, "c");
+  TORCH_CHECK(offs.is_cuda() && offs.scalar_type() == at::kInt && offs.is_contiguous() && offs.numel() >= 2,
+              "gemm_grouped_bf16: offs must be an int32 CUDA tensor of G + 1 entries");
+  const int G = (int)offs.numel() - 1;
+  GroupArgs g;
+  g.offs = offs.data_ptr<int>();
+  g.num_groups = G;
+  g.align = (int)align;
+  TORCH_CHECK(a.dim() == 2, "gemm_grouped_bf16: a must be 2-D");
+  const int64_t R = a.size(0);
+  if (R == 0) return;
+  if (mode == 0 || mode == 1) {
+    TORCH_CHECK(b.dim() == 3 && b.size(0) == G && c.dim() == 2 && c.size(0) == R);
+    const int64_t K = a.size(1);
+    const int64_t N = mode == 0 ? b.size(1) : b.size(2);
+    TORCH_CHECK((mode == 0 ? b.size(2) : b.size(1)) == K && c.size(1) == N, "gemm_grouped_bf16: shapes do not match");
+    TORCH_CHECK(K % 8 == 0 && N % 8 == 0);
+    if (mode == 1) TORCH_CHECK(K % 64 == 0, "gemm_grouped_bf16: mode 1 needs K to be a multiple of 64");
+    g.mode = 1;
+    g.b_group_rows = (int)(mode == 0 ? N : K);
+    run_gemm(a, a.data_ptr(), R, K, b.data_ptr(), (int64_t)G * b.size(1), b.size(2), c.data_ptr(), R, R, N, K, false,
+             mode == 1, accumulate, g);
+  } else {
+    TORCH_CHECK(mode == 2 && b.dim() == 2 && b.size(0) == R && c.dim() == 3 && c.size(0) == G);
+    const int64_t M = a.size(1), N = b.size(1);
+    TORCH_CHECK(c.size(1) == M && c.size(2) == N && M % 8 == 0 && N % 8 == 0);
+    g.mode = 2;
+    run_gemm(a, a.data_ptr(), R, M, b.data_ptr(), R, N, c.data_ptr(), (int64_t)G * M, M, N, R, true, true, accumulate, g);
+  }
 }
 
 int64_t gemm_status(bool clear) {
