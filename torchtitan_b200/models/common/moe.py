@@ -111,6 +111,18 @@ class GroupedExperts(Module):
             set_init(new, p._init_spec)
             setattr(self, name, new)
 
+    def native_ok(self, x: torch.Tensor) -> bool:
+        """The tcgen05 grouped GEMMs need bf16 CUDA rows and tile-friendly expert shapes."""
+        from torchtitan_b200.ops import moe_ops
+
+        return OF.settings.gemm == "tcgen05" and moe_ops.native_ok(x, self.w1_EFD.shape[2], self.w1_EFD.shape[1])
+
+    def forward_padded(self, x: torch.Tensor, offs: torch.Tensor) -> torch.Tensor:
+        """``x[R, dim]`` in the padded expert-major layout of ``ops.moe_ops`` (``offs[E_local + 1]``)."""
+        from torchtitan_b200.ops import moe_ops
+
+        return moe_ops.grouped_swiglu_experts(x, self.w1_EFD, self.w3_EFD, self.w2_EDF, offs)
+
     def forward(self, x: torch.Tensor, offs: torch.Tensor) -> torch.Tensor:
         """``x[N, dim]`` rows sorted by local expert; ``offs[E_local]`` cumulative counts (int32)."""
         h = grouped_mm(x, self.w1_EFD.transpose(-2, -1), offs)
@@ -149,6 +161,12 @@ class TokenChoiceTopKRouter(Module):
         # the gate runs in fp32 (parity: fp32 autocast of the router GEMM)
         logits = F.linear(x.float(), self.gate.weight.float(),
                           None if self.gate.bias is None else self.gate.bias.float())
+        grouped = bool(c.num_expert_groups and c.num_limited_groups and c.num_expert_groups > 1)
+        if logits.is_cuda and not grouped and not c._debug_force_load_balance and c.num_experts <= 512 and c.top_k <= 16:
+            # fused sm_100a router: scores, biased top-k, renormalisation, scaling and histogram in one kernel
+            from torchtitan_b200.ops import moe_ops
+
+            return moe_ops.router_topk(logits, expert_bias, c.top_k, c.score_func, c.route_norm, c.route_scale)
         scores = torch.softmax(logits, dim=-1) if c.score_func == "softmax" else torch.sigmoid(logits)
         with torch.no_grad():
             if c._debug_force_load_balance:
@@ -184,7 +202,14 @@ class RoutedExperts(Module):
                 counts: torch.Tensor) -> torch.Tensor:
         T, D = x.shape
         K = selected.shape[1]
-        flat = selected.reshape(-1)
+        if self.ep is None and self.inner_experts.native_ok(x):
+            from torchtitan_b200.ops import moe_ops
+
+            dest, offs, cap = moe_ops.padded_layout(selected, counts)
+            xp = moe_ops.permute_rows(x, dest, cap)
+            yp = self.inner_experts.forward_padded(xp, offs)
+            return moe_ops.combine_rows(yp, dest, top_scores)
+        flat = selected.reshape(-1).long()
         order = torch.argsort(flat, stable=True)  # slots sorted expert-major
         token_idx = order // K
         rows = x.index_select(0, token_idx)

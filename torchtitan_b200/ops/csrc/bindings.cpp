@@ -39,6 +39,15 @@ void adamw_allgather_(at::Tensor master, const at::Tensor& grad, at::Tensor exp_
                       at::IntArrayRef param_ptrs, int64_t my_rank, int64_t offset, bool param_is_bf16,
                       const at::Tensor& grad_scale, double lr, double beta1, double beta2, double eps,
                       double weight_decay, double bc1, double bc2);
+std::tuple<at::Tensor, at::Tensor, at::Tensor> moe_router_fwd(const at::Tensor& logits, const c10::optional<at::Tensor>& bias,
+                                                              int64_t top_k, bool sigmoid, bool route_norm,
+                                                              double route_scale);
+at::Tensor moe_router_bwd(const at::Tensor& logits, const at::Tensor& sel, const at::Tensor& dtop, bool sigmoid,
+                          bool route_norm, double route_scale);
+at::Tensor moe_permute_rows(const at::Tensor& x, const at::Tensor& dest, int64_t rows);
+at::Tensor moe_combine_rows(const at::Tensor& y, const at::Tensor& dest, const c10::optional<at::Tensor>& wts);
+std::tuple<at::Tensor, at::Tensor> moe_combine_bwd(const at::Tensor& dout, const at::Tensor& y, const at::Tensor& dest,
+                                                   const at::Tensor& wts);
 }  // namespace tb200
 
 TORCH_LIBRARY(tb200, m) {
@@ -65,6 +74,13 @@ TORCH_LIBRARY(tb200, m) {
         "int causal_offset, Tensor? kv_first, Tensor(a!)? dq_out, Tensor(b!)? dk_out, Tensor(c!)? dv_out) -> "
         "(Tensor, Tensor, Tensor)", &tb200::flash_bwd);
   m.def("flash_status(bool clear) -> int", &tb200::flash_status);
+  m.def("moe_router_fwd(Tensor logits, Tensor? bias, int top_k, bool sigmoid, bool route_norm, float route_scale) -> "
+        "(Tensor, Tensor, Tensor)", &tb200::moe_router_fwd);
+  m.def("moe_router_bwd(Tensor logits, Tensor sel, Tensor dtop, bool sigmoid, bool route_norm, float route_scale) -> Tensor",
+        &tb200::moe_router_bwd);
+  m.def("moe_permute_rows(Tensor x, Tensor dest, int rows) -> Tensor", &tb200::moe_permute_rows);
+  m.def("moe_combine_rows(Tensor y, Tensor dest, Tensor? wts) -> Tensor", &tb200::moe_combine_rows);
+  m.def("moe_combine_bwd(Tensor dout, Tensor y, Tensor dest, Tensor wts) -> (Tensor, Tensor)", &tb200::moe_combine_bwd);
   m.def("symm_barrier(int[] flag_ptrs, int my_rank, int epoch, Tensor(a!) status, int max_cycles) -> ()",
         &tb200::symm_barrier);
   m.def("reduce_scatter_pull(int[] grad_ptrs, int my_rank, int offset, Tensor(a!) out, bool grad_is_bf16, "

@@ -1,0 +1,345 @@
+// Mixture-of-experts routing kernels (CUDA cores; the expert GEMMs are the grouped tcgen05 GEMM).
+//
+//  * router_fwd / router_bwd: fp32 gate logits [T, E] -> softmax or sigmoid scores, expert-bias
+//    aware top-k selection, optional renormalisation and scaling of the selected scores, and the
+//    per-expert token histogram.  One warp per token, the score row lives in registers.
+//  * permute_rows: tokens [T, D] -> expert-major padded layout [R, D] (row `dest[t, k]` receives
+//    token t; rows that no slot maps to stay zero).
+//  * combine_rows: out[t] = sum_k w[t, k] * y[dest[t, k]] in fp32, no atomics (deterministic), and
+//    its two gradients (scatter of w * dout, and dw = <dout[t], y[dest]>).
+#include <ATen/ATen.h>
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+
+#include "common.cuh"
+
+namespace tb200 {
+
+constexpr int kMaxExpertsPerLane = 16;   // experts <= 512
+constexpr int kMaxTopK = 16;
+
+struct RouterArgs {
+  int T, E, K;
+  int sigmoid;
+  int route_norm;
+  float route_scale;
+};
+
+template <int kPerLane>
+__device__ __forceinline__ void router_scores(const float* __restrict__ row, int E, int lane, bool sigmoid,
+                                              float (&s)[kPerLane]) {
+  float m = -INFINITY;
+#pragma unroll
+  for (int i = 0; i < kPerLane; ++i) {
+    const int e = i * 32 + lane;
+    s[i] = e < E ? row[e] : -INFINITY;
+    m = fmaxf(m, s[i]);
+  }
+  if (sigmoid) {
+#pragma unroll
+    for (int i = 0; i < kPerLane; ++i) s[i] = (i * 32 + lane) < E ? 1.f / (1.f + __expf(-s[i])) : 0.f;
+    return;
+  }
+  m = warp_max(m);
+  float sum = 0.f;
+#pragma unroll
+  for (int i = 0; i < kPerLane; ++i) {
+    s[i] = (i * 32 + lane) < E ? __expf(s[i] - m) : 0.f;
+    sum += s[i];
+  }
+  sum = warp_sum(sum);
+  const float inv = 1.f / sum;
+#pragma unroll
+  for (int i = 0; i < kPerLane; ++i) s[i] *= inv;
+}
+
+template <int kPerLane>
+__global__ void router_fwd_kernel(const float* __restrict__ logits, const float* __restrict__ bias,
+                                  float* __restrict__ top, int* __restrict__ sel, float* __restrict__ counts,
+                                  RouterArgs a) {
+  const int64_t w = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (w >= a.T) return;
+  float s[kPerLane], c[kPerLane];
+  router_scores<kPerLane>(logits + w * a.E, a.E, lane, a.sigmoid != 0, s);
+#pragma unroll
+  for (int i = 0; i < kPerLane; ++i) {
+    const int e = i * 32 + lane;
+    c[i] = e < a.E ? s[i] + (bias != nullptr ? bias[e] : 0.f) : -INFINITY;
+  }
+  float picked[kMaxTopK];
+  int picked_e[kMaxTopK];
+  float total = 0.f;
+  for (int k = 0; k < a.K; ++k) {
+    // lane-local best (lowest expert index wins ties), then across the warp
+    float bv = -INFINITY, bs = 0.f;
+    int be = 0x7fffffff;
+#pragma unroll
+    for (int i = 0; i < kPerLane; ++i) {
+      const int e = i * 32 + lane;
+      if (c[i] > bv) { bv = c[i]; be = e; bs = s[i]; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+      const int oe = __shfl_xor_sync(0xffffffffu, be, o);
+      const float os = __shfl_xor_sync(0xffffffffu, bs, o);
+      if (ov > bv || (ov == bv && oe < be)) { bv = ov; be = oe; bs = os; }
+    }
+    picked[k] = bs;
+    picked_e[k] = be;
+    total += bs;
+#pragma unroll
+    for (int i = 0; i < kPerLane; ++i)
+      if (i * 32 + lane == be) c[i] = -INFINITY;
+  }
+  if (lane == 0) {
+    const float norm = a.route_norm ? 1.f / (total + 1e-20f) : 1.f;
+    for (int k = 0; k < a.K; ++k) {
+      top[w * a.K + k] = picked[k] * norm * a.route_scale;
+      sel[w * a.K + k] = picked_e[k];
+      atomicAdd(counts + picked_e[k], 1.0f);   // integer-valued: the sum does not depend on the order
+    }
+  }
+}
+
+// dlogits from dtop: through the scaling / renormalisation, the gather and the score function.
+template <int kPerLane>
+__global__ void router_bwd_kernel(const float* __restrict__ logits, const int* __restrict__ sel,
+                                  const float* __restrict__ dtop, float* __restrict__ dlogits, RouterArgs a) {
+  const int64_t w = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (w >= a.T) return;
+  float s[kPerLane], ds[kPerLane];
+  router_scores<kPerLane>(logits + w * a.E, a.E, lane, a.sigmoid != 0, s);
+#pragma unroll
+  for (int i = 0; i < kPerLane; ++i) ds[i] = 0.f;
+  // every lane walks the K selected experts (K is small) and keeps what lands on its own experts
+  float raw_sum = 0.f, dot = 0.f;
+  for (int k = 0; k < a.K; ++k) {
+    const int e = sel[w * a.K + k];
+    float mine = 0.f;
+#pragma unroll
+    for (int i = 0; i < kPerLane; ++i)
+      if (i == (e >> 5)) mine = s[i];
+    const float raw = __shfl_sync(0xffffffffu, mine, e & 31);
+    raw_sum += raw;
+    dot += dtop[w * a.K + k] * raw;
+  }
+  const float S = raw_sum + 1e-20f;
+  for (int k = 0; k < a.K; ++k) {
+    const int e = sel[w * a.K + k];
+    const float g = dtop[w * a.K + k];
+    const float draw = a.route_norm ? a.route_scale * (g / S - dot / (S * S)) : a.route_scale * g;
+    if ((e & 31) == lane) {
+#pragma unroll
+      for (int i = 0; i < kPerLane; ++i)
+        if (i == (e >> 5)) ds[i] += draw;
+    }
+  }
+  if (a.sigmoid) {
+#pragma unroll
+    for (int i = 0; i < kPerLane; ++i) {
+      const int e = i * 32 + lane;
+      if (e < a.E) dlogits[w * a.E + e] = ds[i] * s[i] * (1.f - s[i]);
+    }
+  } else {
+    float inner = 0.f;
+#pragma unroll
+    for (int i = 0; i < kPerLane; ++i) inner += ds[i] * s[i];
+    inner = warp_sum(inner);
+#pragma unroll
+    for (int i = 0; i < kPerLane; ++i) {
+      const int e = i * 32 + lane;
+      if (e < a.E) dlogits[w * a.E + e] = s[i] * (ds[i] - inner);
+    }
+  }
+}
+
+template <typename F>
+static void dispatch_per_lane(int E, F&& f) {
+  if (E <= 64) f(std::integral_constant<int, 2>());
+  else if (E <= 128) f(std::integral_constant<int, 4>());
+  else if (E <= 256) f(std::integral_constant<int, 8>());
+  else f(std::integral_constant<int, kMaxExpertsPerLane>());
+}
+
+std::tuple<at::Tensor, at::Tensor, at::Tensor> moe_router_fwd(const at::Tensor& logits, const c10::optional<at::Tensor>& bias,
+                                                              int64_t top_k, bool sigmoid, bool route_norm,
+                                                              double route_scale) {
+  TORCH_CHECK(logits.is_cuda() && logits.scalar_type() == at::kFloat && logits.dim() == 2 && logits.is_contiguous());
+  const int64_t T = logits.size(0), E = logits.size(1);
+  TORCH_CHECK(E <= 32 * kMaxExpertsPerLane && top_k >= 1 && top_k <= kMaxTopK && top_k <= E, "moe_router: unsupported E or top_k");
+  c10::cuda::CUDAGuard guard(logits.device());
+  auto top = at::empty({T, top_k}, logits.options());
+  auto sel = at::empty({T, top_k}, logits.options().dtype(at::kInt));
+  auto counts = at::zeros({E}, logits.options());
+  if (T == 0) return {top, sel, counts};
+  const float* bp = nullptr;
+  if (bias.has_value() && bias->defined()) {
+    TORCH_CHECK(bias->is_cuda() && bias->scalar_type() == at::kFloat && bias->numel() == E && bias->is_contiguous());
+    bp = bias->data_ptr<float>();
+  }
+  RouterArgs a{(int)T, (int)E, (int)top_k, sigmoid ? 1 : 0, route_norm ? 1 : 0, (float)route_scale};
+  const int threads = 128;
+  const unsigned blocks = (unsigned)((T * 32 + threads - 1) / threads);
+  auto stream = at::cuda::getCurrentCUDAStream();
+  dispatch_per_lane((int)E, [&](auto tag) {
+    router_fwd_kernel<decltype(tag)::value><<<blocks, threads, 0, stream>>>(
+        logits.data_ptr<float>(), bp, top.data_ptr<float>(), sel.data_ptr<int>(), counts.data_ptr<float>(), a);
+  });
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+  return {top, sel, counts};
+}
+
+at::Tensor moe_router_bwd(const at::Tensor& logits, const at::Tensor& sel, const at::Tensor& dtop, bool sigmoid,
+                          bool route_norm, double route_scale) {
+  TORCH_CHECK(logits.is_cuda() && logits.scalar_type() == at::kFloat && logits.is_contiguous());
+  TORCH_CHECK(sel.scalar_type() == at::kInt && sel.is_contiguous() && dtop.scalar_type() == at::kFloat && dtop.is_contiguous());
+  const int64_t T = logits.size(0), E = logits.size(1), K = sel.size(1);
+  c10::cuda::CUDAGuard guard(logits.device());
+  auto dl = at::empty_like(logits);
+  if (T == 0) return dl;
+  RouterArgs a{(int)T, (int)E, (int)K, sigmoid ? 1 : 0, route_norm ? 1 : 0, (float)route_scale};
+  const int threads = 128;
+  const unsigned blocks = (unsigned)((T * 32 + threads - 1) / threads);
+  auto stream = at::cuda::getCurrentCUDAStream();
+  dispatch_per_lane((int)E, [&](auto tag) {
+    router_bwd_kernel<decltype(tag)::value><<<blocks, threads, 0, stream>>>(
+        logits.data_ptr<float>(), sel.data_ptr<int>(), dtop.data_ptr<float>(), dl.data_ptr<float>(), a);
+  });
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+  return dl;
+}
+
+// ---------------------------------------------------------------------------------------------
+// out[dest[i]] = x[i / K]   (one warp per slot, 16-byte vectors; D % 8 == 0)
+__global__ void permute_rows_kernel(const __nv_bfloat16* __restrict__ x, const int* __restrict__ dest,
+                                    __nv_bfloat16* __restrict__ out, int64_t slots, int K, int D) {
+  const int64_t w = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (w >= slots) return;
+  const int d = dest[w];
+  if (d < 0) return;
+  const bf16x8* src = reinterpret_cast<const bf16x8*>(x + (w / K) * D);
+  bf16x8* dst = reinterpret_cast<bf16x8*>(out + (int64_t)d * D);
+  for (int i = lane; i < D / 8; i += 32) dst[i] = src[i];
+}
+
+// out[t] = sum_k w[t,k] * y[dest[t,k]]  (w == nullptr: plain sum).  One warp per token.
+template <bool kWeighted>
+__global__ void combine_rows_kernel(const __nv_bfloat16* __restrict__ y, const int* __restrict__ dest,
+                                    const float* __restrict__ wts, __nv_bfloat16* __restrict__ out, int64_t T, int K, int D) {
+  const int64_t t = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (t >= T) return;
+  for (int i = lane; i < D / 8; i += 32) {
+    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    for (int k = 0; k < K; ++k) {
+      const int d = dest[t * K + k];
+      if (d < 0) continue;
+      float v[8];
+      unpack8(reinterpret_cast<const bf16x8*>(y + (int64_t)d * D)[i], v);
+      const float wk = kWeighted ? wts[t * K + k] : 1.f;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] += wk * v[j];
+    }
+    reinterpret_cast<bf16x8*>(out + t * D)[i] = pack8(acc);
+  }
+}
+
+// dy[dest[t,k]] = w[t,k] * dout[t];  dw[t,k] = <dout[t], y[dest[t,k]]>.  One warp per slot.
+__global__ void combine_bwd_kernel(const __nv_bfloat16* __restrict__ dout, const __nv_bfloat16* __restrict__ y,
+                                   const int* __restrict__ dest, const float* __restrict__ wts,
+                                   __nv_bfloat16* __restrict__ dy, float* __restrict__ dw, int64_t slots, int K, int D) {
+  const int64_t s = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (s >= slots) return;
+  const int d = dest[s];
+  if (d < 0) {
+    if (lane == 0) dw[s] = 0.f;
+    return;
+  }
+  const float wk = wts[s];
+  const bf16x8* g = reinterpret_cast<const bf16x8*>(dout + (s / K) * D);
+  const bf16x8* yr = reinterpret_cast<const bf16x8*>(y + (int64_t)d * D);
+  bf16x8* o = reinterpret_cast<bf16x8*>(dy + (int64_t)d * D);
+  float dot = 0.f;
+  for (int i = lane; i < D / 8; i += 32) {
+    float gv[8], yv[8], r[8];
+    unpack8(g[i], gv);
+    unpack8(yr[i], yv);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      dot += gv[j] * yv[j];
+      r[j] = wk * gv[j];
+    }
+    o[i] = pack8(r);
+  }
+  dot = warp_sum(dot);
+  if (lane == 0) dw[s] = dot;
+}
+
+static void check_rows(const at::Tensor& t, const char* n) {
+  TORCH_CHECK(t.is_cuda() && t.scalar_type() == at::kBFloat16 && t.dim() == 2 && t.is_contiguous() && t.size(1) % 8 == 0,
+              "moe: ", n, " must be a contiguous bf16 [rows, D] CUDA tensor with D % 8 == 0");
+}
+
+at::Tensor moe_permute_rows(const at::Tensor& x, const at::Tensor& dest, int64_t rows) {
+  check_rows(x, "x");
+  TORCH_CHECK(dest.is_cuda() && dest.scalar_type() == at::kInt && dest.dim() == 2 && dest.size(0) == x.size(0) && dest.is_contiguous());
+  c10::cuda::CUDAGuard guard(x.device());
+  auto out = at::zeros({rows, x.size(1)}, x.options());
+  const int64_t slots = dest.numel();
+  if (slots == 0) return out;
+  const int threads = 256;
+  permute_rows_kernel<<<(unsigned)((slots * 32 + threads - 1) / threads), threads, 0, at::cuda::getCurrentCUDAStream()>>>(
+      reinterpret_cast<const __nv_bfloat16*>(x.data_ptr()), dest.data_ptr<int>(),
+      reinterpret_cast<__nv_bfloat16*>(out.data_ptr()), slots, (int)dest.size(1), (int)x.size(1));
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+  return out;
+}
+
+at::Tensor moe_combine_rows(const at::Tensor& y, const at::Tensor& dest, const c10::optional<at::Tensor>& wts) {
+  check_rows(y, "y");
+  TORCH_CHECK(dest.is_cuda() && dest.scalar_type() == at::kInt && dest.dim() == 2 && dest.is_contiguous());
+  c10::cuda::CUDAGuard guard(y.device());
+  const int64_t T = dest.size(0);
+  const int K = (int)dest.size(1), D = (int)y.size(1);
+  auto out = at::empty({T, D}, y.options());
+  if (T == 0) return out;
+  const int threads = 256;
+  const unsigned blocks = (unsigned)((T * 32 + threads - 1) / threads);
+  auto stream = at::cuda::getCurrentCUDAStream();
+  auto yp = reinterpret_cast<const __nv_bfloat16*>(y.data_ptr());
+  auto op = reinterpret_cast<__nv_bfloat16*>(out.data_ptr());
+  if (wts.has_value() && wts->defined()) {
+    TORCH_CHECK(wts->is_cuda() && wts->scalar_type() == at::kFloat && wts->is_contiguous() && wts->numel() == dest.numel());
+    combine_rows_kernel<true><<<blocks, threads, 0, stream>>>(yp, dest.data_ptr<int>(), wts->data_ptr<float>(), op, T, K, D);
+  } else {
+    combine_rows_kernel<false><<<blocks, threads, 0, stream>>>(yp, dest.data_ptr<int>(), nullptr, op, T, K, D);
+  }
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+  return out;
+}
+
+std::tuple<at::Tensor, at::Tensor> moe_combine_bwd(const at::Tensor& dout, const at::Tensor& y, const at::Tensor& dest,
+                                                   const at::Tensor& wts) {
+  check_rows(dout, "dout");
+  check_rows(y, "y");
+  TORCH_CHECK(dest.scalar_type() == at::kInt && dest.is_contiguous() && wts.scalar_type() == at::kFloat && wts.is_contiguous());
+  c10::cuda::CUDAGuard guard(y.device());
+  auto dy = at::zeros_like(y);
+  auto dw = at::empty_like(wts);
+  const int64_t slots = dest.numel();
+  if (slots == 0) return {dy, dw};
+  const int threads = 256;
+  combine_bwd_kernel<<<(unsigned)((slots * 32 + threads - 1) / threads), threads, 0, at::cuda::getCurrentCUDAStream()>>>(
+      reinterpret_cast<const __nv_bfloat16*>(dout.data_ptr()), reinterpret_cast<const __nv_bfloat16*>(y.data_ptr()),
+      dest.data_ptr<int>(), wts.data_ptr<float>(), reinterpret_cast<__nv_bfloat16*>(dy.data_ptr()), dw.data_ptr<float>(),
+      slots, (int)dest.size(1), (int)y.size(1));
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+  return {dy, dw};
+}
+
+}  // namespace tb200

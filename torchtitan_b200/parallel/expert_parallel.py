@@ -75,6 +75,17 @@ def ep_experts(ep: EPContext, experts, rows: torch.Tensor, counts: torch.Tensor)
         seg = recv_counts.reshape(-1)  # length n * E_local, segment s = src * E_local + e
         seg_expert = torch.arange(n * E_local, device=rows.device) % E_local
         row_expert = torch.repeat_interleave(seg_expert, seg, output_size=recv.shape[0])
+    if experts.native_ok(recv):
+        # padded expert-major layout for the tcgen05 grouped GEMMs (own permute / gather kernels)
+        from torchtitan_b200.ops import moe_ops
+
+        with torch.no_grad():
+            dest, offs_pad, cap = moe_ops.padded_layout(row_expert.view(-1, 1), recv_counts.sum(0).float())
+        xp = moe_ops.permute_rows(recv, dest, cap)
+        yp = experts.forward_padded(xp, offs_pad)
+        back = moe_ops.gather_rows(yp, dest)
+        return _AllToAllRows.apply(back, out_splits, in_splits, ep.group)
+    with torch.no_grad():
         perm = torch.argsort(row_expert, stable=True)
         offs = torch.cumsum(recv_counts.sum(0), 0).to(torch.int32)
     x = recv.index_select(0, perm)
