@@ -115,13 +115,20 @@ class GQAttention(Module):
     def checkpoint_slices(self):
         hd = self.head_dim
         q, kv = self.n_heads * hd, self.n_kv_heads * hd
-        return {
+        out = {
             "wqkv.weight": [
                 ("qkv_linear.wq.weight", 0, q),
                 ("qkv_linear.wk.weight", q, q + kv),
                 ("qkv_linear.wv.weight", q + kv, q + 2 * kv),
             ]
         }
+        if self.wqkv.bias is not None:
+            out["wqkv.bias"] = [
+                ("qkv_linear.wq.bias", 0, q),
+                ("qkv_linear.wk.bias", q, q + kv),
+                ("qkv_linear.wv.bias", q + kv, q + 2 * kv),
+            ]
+        return out
 
     # -- forward -----------------------------------------------------------
     def forward(self, x: torch.Tensor, positions: torch.Tensor, ctx: AttentionContext | None = None,

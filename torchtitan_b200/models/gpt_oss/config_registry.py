@@ -1,0 +1,46 @@
+"""Registered GPT-OSS training configs (parity: torchtitan/models/gpt_oss/config_registry.py)."""
+
+from __future__ import annotations
+
+from torchtitan_b200.components.checkpoint import CheckpointManager
+from torchtitan_b200.components.data import BaseDataLoader
+from torchtitan_b200.components.lr_scheduler import LRSchedulersContainer
+from torchtitan_b200.components.metrics import MetricsProcessor
+from torchtitan_b200.components.optimizer import OptimizersContainer
+from torchtitan_b200.config import ActivationCheckpointConfig, ModelSelectConfig, ParallelismConfig, TrainingConfig
+from torchtitan_b200.trainer import Trainer
+
+
+def gpt_oss_debugmodel() -> Trainer.Config:
+    return Trainer.Config(
+        model=ModelSelectConfig(name="gpt_oss", flavor="debugmodel"),
+        metrics=MetricsProcessor.Config(log_freq=1),
+        dataloader=BaseDataLoader.Config(dataset="synthetic"),
+        optimizer=OptimizersContainer.Config(lr=8e-4),
+        lr_scheduler=LRSchedulersContainer.Config(warmup_steps=2, decay_ratio=0.8),
+        training=TrainingConfig(num_tokens_per_microbatch_per_dp_rank=8 * 2048, max_context_length=2048, steps=10),
+        checkpoint=CheckpointManager.Config(interval=10, last_save_model_only=False),
+        activation_checkpoint=ActivationCheckpointConfig(mode="selective"),
+    )
+
+
+def _full(flavor: str) -> Trainer.Config:
+    return Trainer.Config(
+        model=ModelSelectConfig(name="gpt_oss", flavor=flavor),
+        hf_assets_path=f"./assets/hf/gpt-oss-{flavor.lower()}",
+        dataloader=BaseDataLoader.Config(dataset="c4"),
+        optimizer=OptimizersContainer.Config(lr=8e-4),
+        lr_scheduler=LRSchedulersContainer.Config(warmup_steps=2000, decay_ratio=0.8),
+        training=TrainingConfig(num_tokens_per_microbatch_per_dp_rank=8 * 8192, max_context_length=8192, steps=10000),
+        parallelism=ParallelismConfig(data_parallel_shard_degree=-1, expert_parallel_degree=8),
+        checkpoint=CheckpointManager.Config(interval=500),
+        activation_checkpoint=ActivationCheckpointConfig(mode="full"),
+    )
+
+
+def gpt_oss_20b() -> Trainer.Config:
+    return _full("20B")
+
+
+def gpt_oss_120b() -> Trainer.Config:
+    return _full("120B")

@@ -40,6 +40,10 @@ def count_params_and_flops(cfg, model: nn.Module | None, seq_len: int) -> tuple[
             m = blk.moe
             per_expert = 3 * dim * m.hidden_dim
             router = m.num_experts * dim
+            if hasattr(m.routed_experts.inner_experts, "swiglu_limit"):  # biased experts (GPT-OSS)
+                per_expert += 2 * m.hidden_dim + dim
+            if getattr(m.router, "gate_bias", False):
+                router += m.num_experts
             shared = 3 * dim * m.shared_hidden_dim if m.shared_hidden_dim else 0
             layer += m.num_experts * per_expert + router + shared
             layer_active += m.top_k * per_expert + router + shared
