@@ -1,0 +1,77 @@
+"""Quantisation converters and LoRA on CPU: the reference quantisers, the config rewrites, and
+training through the trainer with converted models."""
+
+import math
+
+import pytest
+import torch
+
+from torchtitan_b200.components.quantization import apply_converters
+from torchtitan_b200.components.quantization.linear import QuantLinear
+from torchtitan_b200.config import ConfigManager
+from torchtitan_b200.models import get_model_spec
+from torchtitan_b200.ops import reference as ref
+
+
+def test_mxfp8_reference_properties():
+    torch.manual_seed(0)
+    x = torch.randn(64, 128) * torch.logspace(-3, 3, 64)[:, None]
+    for axis in (0, 1):
+        q = ref.mxfp8_fake_quant(x, axis)
+        # e4m3 has 3 mantissa bits and RCEIL never saturates: relative error per block <= 2^-4 of the block max
+        blocks = (x if axis == 1 else x.t()).reshape(-1, 32)
+        qb = (q if axis == 1 else q.t()).reshape(-1, 32)
+        err = (blocks - qb).abs().amax(dim=1)
+        assert (err <= blocks.abs().amax(dim=1) * 2 ** -4 + 1e-30).all()
+        assert torch.equal(ref.mxfp8_fake_quant(q, axis), q)  # idempotent
+    z = torch.zeros(4, 32)
+    assert torch.equal(ref.mxfp8_fake_quant(z, 1), z)
+    # the scale is the smallest power of two >= amax / 448
+    e = ref.mxfp8_scale_exponent(torch.tensor([448.0, 449.0, 1.0, 0.0]))
+    assert e.tolist() == [0, 1, math.ceil(math.log2(1 / 448)), -127]
+
+
+def test_converters_rewrite_config_tree():
+    spec = get_model_spec("llama3", "debugmodel")
+    n = apply_converters(spec.model, ["mxfp8"]) if False else None
+    apply_converters(spec.model, ["mxfp8", "lora:rank=4,alpha=8"])
+    blk = spec.model.layers[0]
+    assert type(blk.attention.wqkv).__qualname__ == "LoRAQuantLinear.Config"
+    assert type(spec.model.lm_head).__qualname__ == "Linear.Config"
+    model = spec.model.build()
+    names = [n for n, p in model.named_parameters() if p.requires_grad]
+    assert names and all(n.endswith("lora_a") or n.endswith("lora_b") for n in names)
+    with pytest.raises(ValueError):
+        apply_converters(get_model_spec("llama3", "debugmodel").model, ["lora", "float8"])
+
+
+def test_quant_linear_gradients_follow_recipe():
+    torch.manual_seed(1)
+    lin = QuantLinear.Config(in_features=64, out_features=96, recipe="mxfp8").build()
+    lin.init_states(seed=0)
+    x = torch.randn(40, 64, requires_grad=True)
+    y = lin(x)
+    g = torch.randn_like(y)
+    y.backward(g)
+    fq = ref.mxfp8_fake_quant
+    w = lin.weight.detach()
+    assert torch.allclose(y, fq(x.detach(), 1) @ fq(w, 1).t(), atol=1e-5)
+    assert torch.allclose(x.grad, fq(g, 1) @ fq(w, 0), atol=1e-5)
+    gp = torch.nn.functional.pad(g, (0, 0, 0, 24))  # token blocks of 32: the last one is ragged
+    assert torch.allclose(lin.weight.grad, fq(g, 0).t() @ fq(x.detach(), 0), atol=1e-4)
+
+
+@pytest.mark.parametrize("converters", [["mxfp8"], ["float8:rowwise_with_gw_hp"], ["float8", "lora:rank=4"]])
+def test_converted_models_train(converters, tmp_path):
+    cfg = ConfigManager().parse_args([
+        "--module", "llama3", "--config", "llama3_debugmodel", "--training.steps", "3",
+        "--training.num_tokens_per_microbatch_per_dp_rank", "128", "--training.max_context_length", "64",
+        "--training.mixed_precision_param", "float32", "--debug.seed", "0", "--dump_folder", str(tmp_path),
+        "--debug.no-enable_structured_logging", "--checkpoint.no-enable",
+        "--model.converters", ",".join(converters),
+    ])
+    trainer = cfg.build()
+    trainer.train()
+    loss = float(trainer._last_loss)
+    assert loss == loss and loss < 9.0, loss
+    trainer.close()

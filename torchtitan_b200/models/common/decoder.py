@@ -70,6 +70,9 @@ class Decoder(Module):
         single_document: bool = False
         """Skip document masking (every batch row is one document starting at 0)."""
         final_logit_softcap: float | None = None
+        trainable_param_pattern: str | None = None
+        """Regular expression of the parameter names that stay trainable (set by the LoRA converter);
+        every other parameter is frozen after construction."""
 
         # -- accounting ---------------------------------------------------
         def update_from_config(self, *, trainer_config=None, **_) -> None:
@@ -101,6 +104,13 @@ class Decoder(Module):
         self.single_document = c.single_document
         self.cp = None  # set by parallelize when context parallel is on
         self.tp = None
+        if c.trainable_param_pattern:
+            import re
+
+            pat = re.compile(c.trainable_param_pattern)
+            for n, p in self.named_parameters():
+                if not pat.search(n):
+                    p.requires_grad_(False)
 
     def build_context(self, positions: torch.Tensor, q_pos: torch.Tensor | None = None) -> AttentionContext:
         return build_attention_context(positions, assume_single_document=self.single_document, cp=self.cp, q_pos=q_pos)

@@ -48,6 +48,11 @@ at::Tensor moe_permute_rows(const at::Tensor& x, const at::Tensor& dest, int64_t
 at::Tensor moe_combine_rows(const at::Tensor& y, const at::Tensor& dest, const c10::optional<at::Tensor>& wts);
 std::tuple<at::Tensor, at::Tensor> moe_combine_bwd(const at::Tensor& dout, const at::Tensor& y, const at::Tensor& dest,
                                                    const at::Tensor& wts);
+std::tuple<at::Tensor, at::Tensor> mxfp8_quantize(const at::Tensor& x, int64_t axis);
+at::Tensor mxfp8_fake_quant(const at::Tensor& x, int64_t axis);
+at::Tensor mxfp8_dequantize(const at::Tensor& data, const at::Tensor& scales, int64_t axis);
+std::tuple<at::Tensor, at::Tensor> float8_rowwise_quantize(const at::Tensor& x);
+at::Tensor float8_rowwise_fake_quant(const at::Tensor& x);
 }  // namespace tb200
 
 TORCH_LIBRARY(tb200, m) {
@@ -74,6 +79,11 @@ TORCH_LIBRARY(tb200, m) {
         "int causal_offset, Tensor? kv_first, Tensor(a!)? dq_out, Tensor(b!)? dk_out, Tensor(c!)? dv_out) -> "
         "(Tensor, Tensor, Tensor)", &tb200::flash_bwd);
   m.def("flash_status(bool clear) -> int", &tb200::flash_status);
+  m.def("mxfp8_quantize(Tensor x, int axis) -> (Tensor, Tensor)", &tb200::mxfp8_quantize);
+  m.def("mxfp8_fake_quant(Tensor x, int axis) -> Tensor", &tb200::mxfp8_fake_quant);
+  m.def("mxfp8_dequantize(Tensor data, Tensor scales, int axis) -> Tensor", &tb200::mxfp8_dequantize);
+  m.def("float8_rowwise_quantize(Tensor x) -> (Tensor, Tensor)", &tb200::float8_rowwise_quantize);
+  m.def("float8_rowwise_fake_quant(Tensor x) -> Tensor", &tb200::float8_rowwise_fake_quant);
   m.def("moe_router_fwd(Tensor logits, Tensor? bias, int top_k, bool sigmoid, bool route_norm, float route_scale) -> "
         "(Tensor, Tensor, Tensor)", &tb200::moe_router_fwd);
   m.def("moe_router_bwd(Tensor logits, Tensor sel, Tensor dtop, bool sigmoid, bool route_norm, float route_scale) -> Tensor",

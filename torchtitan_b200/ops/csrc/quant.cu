@@ -1,0 +1,262 @@
+// Block-scaled fp8 quantisation kernels.
+//
+// MXFP8 (OCP microscaling): blocks of 32 elements along the contraction dimension share one
+// e8m0 (power-of-two) scale, the elements are e4m3.  The scale exponent is rounded up
+// ("RCEIL": 2^e >= amax / 448), so no element saturates.  `axis = 1` scales along the last
+// (contiguous) dimension, `axis = 0` along the first; the data keeps the input's [R, C] layout
+// either way, the scales are [R, C/32] or [R/32, C].
+//   mxfp8_quantize      bf16 -> (e4m3 bytes, e8m0 bytes)
+//   mxfp8_dequantize    (e4m3, e8m0) -> bf16
+//   mxfp8_fake_quant    bf16 -> bf16 holding exactly the values the MXFP8 pair represents
+//                       (one pass; used by the linear layers' emulated GEMM path)
+// Float8 row-wise: one fp32 scale per row, e4m3 data (float8_rowwise_quantize / fake_quant).
+#include <ATen/ATen.h>
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <cuda_fp8.h>
+
+#include "common.cuh"
+
+namespace tb200 {
+
+constexpr float kE4M3Max = 448.f;
+
+// e8m0 exponent byte of the smallest power of two >= amax / 448 (0 for an all-zero block).
+__device__ __forceinline__ uint32_t e8m0_rceil(float amax) {
+  if (!(amax > 0.f)) return 0u;
+  const uint32_t bits = __float_as_uint(__fdiv_rn(amax, kE4M3Max));
+  uint32_t e = (bits >> 23) & 0xffu;
+  if (bits & 0x7fffffu) e += 1;            // round the exponent up
+  return min(max(e, 1u), 254u);
+}
+__device__ __forceinline__ float e8m0_to_float(uint32_t e) { return __uint_as_float(e << 23); }        // 2^(e-127)
+__device__ __forceinline__ float e8m0_inverse(uint32_t e) { return __uint_as_float((254u - e) << 23); } // 2^(127-e)
+
+__device__ __forceinline__ uint32_t to_e4m3x4(float a, float b, float c, float d) {
+  const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(a, b), __NV_SATFINITE, __NV_E4M3);
+  const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(c, d), __NV_SATFINITE, __NV_E4M3);
+  return lo | (hi << 16);
+}
+__device__ __forceinline__ float from_e4m3(uint32_t byte) {
+  const __half_raw h = __nv_cvt_fp8_to_halfraw((__nv_fp8_storage_t)byte, __NV_E4M3);
+  return __half2float(*reinterpret_cast<const __half*>(&h));
+}
+
+// ---- axis 1: 4 consecutive lanes own one block of 32 contiguous elements (8 each)
+template <bool kFake>
+__global__ void mx_rowwise_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* __restrict__ data,
+                                  uint8_t* __restrict__ scales, __nv_bfloat16* __restrict__ fake, int64_t n_vec, int C) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;   // vector of 8 elements
+  const bool live = i < n_vec;
+  float v[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  if (live) unpack8(reinterpret_cast<const bf16x8*>(x)[i], v);
+  float amax = 0.f;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(v[j]));
+  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+  if (!live) return;
+  const uint32_t e = e8m0_rceil(amax);
+  const float inv = e8m0_inverse(e);
+  const uint32_t lo = to_e4m3x4(v[0] * inv, v[1] * inv, v[2] * inv, v[3] * inv);
+  const uint32_t hi = to_e4m3x4(v[4] * inv, v[5] * inv, v[6] * inv, v[7] * inv);
+  if (kFake) {
+    const float s = e8m0_to_float(e);
+    float r[8];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      r[j] = from_e4m3((lo >> (8 * j)) & 0xffu) * s;
+      r[4 + j] = from_e4m3((hi >> (8 * j)) & 0xffu) * s;
+    }
+    reinterpret_cast<bf16x8*>(fake)[i] = pack8(r);
+  } else {
+    reinterpret_cast<uint2*>(data)[i] = make_uint2(lo, hi);
+    if ((i & 3) == 0) scales[i >> 2] = (uint8_t)e;   // element index 8 i -> block 8 i / 32
+  }
+}
+
+// ---- axis 0: one thread owns a column pair over a block of 32 rows
+template <bool kFake>
+__global__ void mx_colwise_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* __restrict__ data,
+                                  uint8_t* __restrict__ scales, __nv_bfloat16* __restrict__ fake, int R, int C) {
+  const int c2 = blockIdx.x * blockDim.x + threadIdx.x;   // column pair
+  const int rb = blockIdx.y;                               // block of 32 rows
+  if (c2 * 2 >= C) return;
+  const int r0 = rb * 32;
+  const int rows = min(32, R - r0);
+  float2 v[32];
+  float a0 = 0.f, a1 = 0.f;
+#pragma unroll
+  for (int r = 0; r < 32; ++r) {
+    v[r] = make_float2(0.f, 0.f);
+    if (r < rows) v[r] = __bfloat1622float2(reinterpret_cast<const __nv_bfloat162*>(x + (int64_t)(r0 + r) * C)[c2]);
+    a0 = fmaxf(a0, fabsf(v[r].x));
+    a1 = fmaxf(a1, fabsf(v[r].y));
+  }
+  const uint32_t e0 = e8m0_rceil(a0), e1 = e8m0_rceil(a1);
+  const float i0 = e8m0_inverse(e0), i1 = e8m0_inverse(e1);
+  const float s0 = e8m0_to_float(e0), s1 = e8m0_to_float(e1);
+#pragma unroll
+  for (int r = 0; r < 32; ++r) {
+    if (r >= rows) break;
+    const uint32_t q = __nv_cvt_float2_to_fp8x2(make_float2(v[r].x * i0, v[r].y * i1), __NV_SATFINITE, __NV_E4M3);
+    if (kFake) {
+      reinterpret_cast<__nv_bfloat162*>(fake + (int64_t)(r0 + r) * C)[c2] =
+          __floats2bfloat162_rn(from_e4m3(q & 0xffu) * s0, from_e4m3((q >> 8) & 0xffu) * s1);
+    } else {
+      reinterpret_cast<uint16_t*>(data + (int64_t)(r0 + r) * C)[c2] = (uint16_t)q;
+    }
+  }
+  if (!kFake) {
+    scales[(int64_t)rb * C + 2 * c2] = (uint8_t)e0;
+    scales[(int64_t)rb * C + 2 * c2 + 1] = (uint8_t)e1;
+  }
+}
+
+__global__ void mx_dequant_kernel(const uint8_t* __restrict__ data, const uint8_t* __restrict__ scales,
+                                  __nv_bfloat16* __restrict__ out, int64_t n_vec, int C, int axis) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;   // 8 elements
+  if (i >= n_vec) return;
+  const uint2 q = reinterpret_cast<const uint2*>(data)[i];
+  const int64_t el = i * 8;
+  const int64_t row = el / C;
+  const int col = (int)(el % C);
+  float r[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const uint32_t byte = ((j < 4 ? q.x : q.y) >> (8 * (j & 3))) & 0xffu;
+    const uint32_t e = axis == 1 ? scales[el >> 5] : scales[(row >> 5) * C + col + j];
+    r[j] = from_e4m3(byte) * e8m0_to_float(e);
+  }
+  reinterpret_cast<bf16x8*>(out)[i] = pack8(r);
+}
+
+// ---- float8 row-wise: one warp per row, scale = amax / 448 (fp32)
+template <bool kFake>
+__global__ void f8_rowwise_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* __restrict__ data,
+                                  float* __restrict__ scales, __nv_bfloat16* __restrict__ fake, int64_t R, int C) {
+  const int64_t row = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (row >= R) return;
+  const bf16x8* src = reinterpret_cast<const bf16x8*>(x + row * C);
+  float amax = 0.f;
+  for (int i = lane; i < C / 8; i += 32) {
+    float v[8];
+    unpack8(src[i], v);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(v[j]));
+  }
+  amax = warp_max(amax);
+  const float scale = __fdiv_rn(fmaxf(amax, 1e-12f), kE4M3Max);
+  for (int i = lane; i < C / 8; i += 32) {
+    float v[8];
+    unpack8(src[i], v);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) v[j] = __fdiv_rn(v[j], scale);   // the exact quotient, as the PyTorch restatement computes it
+    const uint32_t lo = to_e4m3x4(v[0], v[1], v[2], v[3]);
+    const uint32_t hi = to_e4m3x4(v[4], v[5], v[6], v[7]);
+    if (kFake) {
+      float r[8];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        r[j] = from_e4m3((lo >> (8 * j)) & 0xffu) * scale;
+        r[4 + j] = from_e4m3((hi >> (8 * j)) & 0xffu) * scale;
+      }
+      reinterpret_cast<bf16x8*>(fake + row * C)[i] = pack8(r);
+    } else {
+      reinterpret_cast<uint2*>(data + row * C)[i] = make_uint2(lo, hi);
+    }
+  }
+  if (!kFake && lane == 0) scales[row] = scale;
+}
+
+static void check_q_input(const at::Tensor& x, int64_t axis) {
+  TORCH_CHECK(x.is_cuda() && x.scalar_type() == at::kBFloat16 && x.dim() == 2 && x.is_contiguous(),
+              "quantize: a contiguous bf16 [R, C] CUDA tensor is expected");
+  TORCH_CHECK(axis == 0 || axis == 1, "quantize: axis must be 0 or 1");
+  if (axis == 1) {
+    TORCH_CHECK(x.size(1) % 32 == 0, "mxfp8 along the last dimension needs C % 32 == 0");
+  } else {
+    TORCH_CHECK(x.size(1) % 8 == 0, "mxfp8 along the first dimension needs C % 8 == 0");
+  }
+}
+
+template <bool kFake>
+static void launch_mx(const at::Tensor& x, int64_t axis, uint8_t* data, uint8_t* scales, __nv_bfloat16* fake) {
+  const int64_t R = x.size(0);
+  const int C = (int)x.size(1);
+  auto stream = at::cuda::getCurrentCUDAStream();
+  auto xp = reinterpret_cast<const __nv_bfloat16*>(x.data_ptr());
+  if (R == 0 || C == 0) return;
+  if (axis == 1) {
+    const int64_t n_vec = R * C / 8;
+    mx_rowwise_kernel<kFake><<<(unsigned)((n_vec + 255) / 256), 256, 0, stream>>>(xp, data, scales, fake, n_vec, C);
+  } else {
+    dim3 grid((unsigned)((C / 2 + 127) / 128), (unsigned)((R + 31) / 32));
+    mx_colwise_kernel<kFake><<<grid, 128, 0, stream>>>(xp, data, scales, fake, (int)R, C);
+  }
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+}
+
+std::tuple<at::Tensor, at::Tensor> mxfp8_quantize(const at::Tensor& x, int64_t axis) {
+  check_q_input(x, axis);
+  c10::cuda::CUDAGuard guard(x.device());
+  const int64_t R = x.size(0), C = x.size(1);
+  auto data = at::empty({R, C}, x.options().dtype(at::kByte));
+  auto scales = axis == 1 ? at::empty({R, C / 32}, x.options().dtype(at::kByte))
+                          : at::empty({(R + 31) / 32, C}, x.options().dtype(at::kByte));
+  launch_mx<false>(x, axis, data.data_ptr<uint8_t>(), scales.data_ptr<uint8_t>(), nullptr);
+  return {data, scales};
+}
+
+at::Tensor mxfp8_fake_quant(const at::Tensor& x, int64_t axis) {
+  check_q_input(x, axis);
+  c10::cuda::CUDAGuard guard(x.device());
+  auto out = at::empty_like(x);
+  launch_mx<true>(x, axis, nullptr, nullptr, reinterpret_cast<__nv_bfloat16*>(out.data_ptr()));
+  return out;
+}
+
+at::Tensor mxfp8_dequantize(const at::Tensor& data, const at::Tensor& scales, int64_t axis) {
+  TORCH_CHECK(data.is_cuda() && data.scalar_type() == at::kByte && data.dim() == 2 && data.is_contiguous());
+  TORCH_CHECK(scales.is_cuda() && scales.scalar_type() == at::kByte && scales.is_contiguous());
+  TORCH_CHECK(data.size(1) % 8 == 0 && (axis == 0 || data.size(1) % 32 == 0));
+  c10::cuda::CUDAGuard guard(data.device());
+  auto out = at::empty({data.size(0), data.size(1)}, data.options().dtype(at::kBFloat16));
+  const int64_t n_vec = data.numel() / 8;
+  if (n_vec == 0) return out;
+  mx_dequant_kernel<<<(unsigned)((n_vec + 255) / 256), 256, 0, at::cuda::getCurrentCUDAStream()>>>(
+      data.data_ptr<uint8_t>(), scales.data_ptr<uint8_t>(), reinterpret_cast<__nv_bfloat16*>(out.data_ptr()), n_vec,
+      (int)data.size(1), (int)axis);
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+  return out;
+}
+
+std::tuple<at::Tensor, at::Tensor> float8_rowwise_quantize(const at::Tensor& x) {
+  check_q_input(x, 0);
+  c10::cuda::CUDAGuard guard(x.device());
+  const int64_t R = x.size(0);
+  auto data = at::empty({R, x.size(1)}, x.options().dtype(at::kByte));
+  auto scales = at::empty({R}, x.options().dtype(at::kFloat));
+  if (R > 0)
+    f8_rowwise_kernel<false><<<(unsigned)((R * 32 + 255) / 256), 256, 0, at::cuda::getCurrentCUDAStream()>>>(
+        reinterpret_cast<const __nv_bfloat16*>(x.data_ptr()), data.data_ptr<uint8_t>(), scales.data_ptr<float>(), nullptr, R,
+        (int)x.size(1));
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+  return {data, scales};
+}
+
+at::Tensor float8_rowwise_fake_quant(const at::Tensor& x) {
+  check_q_input(x, 0);
+  c10::cuda::CUDAGuard guard(x.device());
+  auto out = at::empty_like(x);
+  const int64_t R = x.size(0);
+  if (R > 0)
+    f8_rowwise_kernel<true><<<(unsigned)((R * 32 + 255) / 256), 256, 0, at::cuda::getCurrentCUDAStream()>>>(
+        reinterpret_cast<const __nv_bfloat16*>(x.data_ptr()), nullptr, nullptr,
+        reinterpret_cast<__nv_bfloat16*>(out.data_ptr()), R, (int)x.size(1));
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+  return out;
+}
+
+}  // namespace tb200

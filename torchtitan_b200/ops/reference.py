@@ -242,3 +242,37 @@ def router_topk(scores_logits: torch.Tensor, top_k: int, score_func: str, expert
     counts = torch.zeros(E, dtype=torch.float32, device=scores.device)
     counts.scatter_add_(0, sel.reshape(-1), torch.ones(sel.numel(), dtype=torch.float32, device=scores.device))
     return top, sel, counts
+
+
+# ---------------------------------------------------------------------------------------------
+# fp8 quantisation (oracles of ops/csrc/quant.cu)
+# ---------------------------------------------------------------------------------------------
+def mxfp8_scale_exponent(amax: torch.Tensor) -> torch.Tensor:
+    """Unbiased exponent ``e`` of the smallest power of two ``2^e >= amax / 448`` (RCEIL), clamped to
+    the e8m0 range; zero blocks get the smallest scale."""
+    m, ex = torch.frexp(amax.float() / 448.0)      # amax / 448 = m * 2^ex, m in [0.5, 1)
+    e = torch.where(m == 0.5, ex - 1, ex).clamp(-126, 127)
+    return torch.where(amax > 0, e, torch.full_like(e, -127))
+
+
+def mxfp8_fake_quant(x: torch.Tensor, axis: int) -> torch.Tensor:
+    """MXFP8 round trip of ``x[R, C]`` with 1x32 blocks along ``axis`` (ragged last block allowed on axis 0)."""
+    xt = x.float() if axis == 1 else x.float().t()
+    R, C = xt.shape
+    pad = (-C) % 32
+    if pad:
+        xt = torch.nn.functional.pad(xt, (0, pad))
+    blocks = xt.reshape(R, -1, 32)
+    amax = blocks.abs().amax(dim=-1, keepdim=True)
+    e = mxfp8_scale_exponent(amax)
+    scale = torch.exp2(e.float())
+    q = (blocks / scale).clamp(-448.0, 448.0).to(torch.float8_e4m3fn).float() * scale
+    out = q.reshape(R, -1)[:, :C]
+    out = out if axis == 1 else out.t()
+    return out.to(x.dtype)
+
+
+def float8_rowwise_fake_quant(x: torch.Tensor) -> torch.Tensor:
+    xf = x.float()
+    scale = xf.abs().amax(dim=1, keepdim=True).clamp_min(1e-12) / 448.0
+    return ((xf / scale).clamp(-448.0, 448.0).to(torch.float8_e4m3fn).float() * scale).to(x.dtype)
