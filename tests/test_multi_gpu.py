@@ -117,3 +117,63 @@ def test_reduce_scatter_pull(tmp_path):
     run_distributed(_rs_ag, 2, out, backend="nccl")
     r = torch.load(out)
     assert r["ok1"] and r["ok2"]
+
+
+def _fused_tp(rank, world, out_path):
+    """All-gather -> GEMM and GEMM -> reduce-scatter kernels against NCCL + fp32 matmul."""
+    import torch.distributed as dist
+
+    from torchtitan_b200.parallel.tp_fused import FusedTP, all_gather_linear, linear_reduce_scatter
+
+    dev = torch.device("cuda", rank)
+    ftp = FusedTP(dist.group.WORLD, dev, nbytes=256 << 20)
+    T, K, N = 1024 * world, 512, 768
+    S = T // world
+    res = {}
+    for it in range(3):   # three rounds: both buffers of each pair get reused
+        g = torch.Generator(device=dev).manual_seed(10 * it + rank)
+        x = (torch.randn(S, K, device=dev, generator=g) * 0.5).bfloat16().requires_grad_()
+        w = (torch.randn(N, K, device=dev, generator=g) * 0.05).bfloat16().requires_grad_()
+        y = all_gather_linear(x, w, ftp)
+        xs = [torch.empty_like(x) for _ in range(world)]
+        dist.all_gather(xs, x.detach())
+        x_full = torch.cat(xs).float()
+        ref = x_full @ w.detach().float().t()
+        e1 = (y.float() - ref).abs().max().item() / ref.abs().max().item()
+        dy = (torch.randn(T, N, device=dev, generator=g) * 0.1).bfloat16()
+        y.backward(dy)
+        dxp = dy.float() @ w.detach().float()          # partial: summed over ranks, my rows
+        dist.all_reduce(dxp)
+        e2 = (x.grad.float() - dxp[rank * S:(rank + 1) * S]).abs().max().item() / dxp.abs().max().item()
+        e3 = (w.grad.float() - dy.float().t() @ x_full).abs().max().item() / (dy.float().t() @ x_full).abs().max().item()
+        # row-parallel
+        x2 = (torch.randn(T, K, device=dev, generator=g) * 0.5).bfloat16().requires_grad_()
+        w2 = (torch.randn(N, K, device=dev, generator=g) * 0.05).bfloat16().requires_grad_()
+        y2 = linear_reduce_scatter(x2, w2, ftp)
+        ref2 = x2.detach().float() @ w2.detach().float().t()
+        dist.all_reduce(ref2)
+        e4 = (y2.float() - ref2[rank * S:(rank + 1) * S]).abs().max().item() / ref2.abs().max().item()
+        dy2 = (torch.randn(S, N, device=dev, generator=g) * 0.1).bfloat16()
+        y2.backward(dy2)
+        dys = [torch.empty_like(dy2) for _ in range(world)]
+        dist.all_gather(dys, dy2)
+        dy_full = torch.cat(dys).float()
+        e5 = (x2.grad.float() - dy_full @ w2.detach().float()).abs().max().item() / (dy_full @ w2.detach().float()).abs().max().item()
+        wref = dy_full.t() @ x2.detach().float()
+        e6 = (w2.grad.float() - wref).abs().max().item() / wref.abs().max().item()
+        res[it] = [e1, e2, e3, e4, e5, e6]
+    torch.cuda.synchronize()
+    status = int(ftp.arena.status.item()) | int(torch.ops.tb200.gemm_status(True))
+    t = torch.tensor([max(v) for v in res.values()] + [float(status)], device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    if rank == 0:
+        torch.save({"errs": t.cpu(), "detail": res}, out_path)
+
+
+@pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
+def test_fused_tensor_parallel_gemms(tmp_path):
+    out = str(tmp_path / "ftp.pt")
+    run_distributed(_fused_tp, 2, out, backend="nccl")
+    r = torch.load(out)
+    assert r["errs"][-1] == 0, "a bounded wait expired"
+    assert (r["errs"][:-1] < 3e-2).all(), r

@@ -18,6 +18,10 @@ void sumsq_(const at::Tensor& x, at::Tensor acc);
 void gemm_bf16(const at::Tensor& a, const at::Tensor& b, at::Tensor c, int64_t mode, bool accumulate);
 void gemm_grouped_bf16(const at::Tensor& a, const at::Tensor& b, at::Tensor c, const at::Tensor& offs, int64_t mode,
                        int64_t align, bool accumulate);
+void gemm_allgather_bf16(const at::Tensor& a_gather, const at::Tensor& b, at::Tensor c, at::IntArrayRef peer_ptrs,
+                         int64_t rank, at::Tensor flags, int64_t epoch, int64_t mode);
+void gemm_scatter_bf16(const at::Tensor& a, const at::Tensor& b, at::IntArrayRef staging_ptrs, int64_t rank, int64_t mode);
+at::Tensor sum_slots(const at::Tensor& staging);
 int64_t gemm_status(bool clear);
 void gemm_set_variant(int64_t v);
 void gemm_set_debug(int64_t v);
@@ -70,6 +74,10 @@ TORCH_LIBRARY(tb200, m) {
   m.def("gemm_bf16(Tensor a, Tensor b, Tensor(a!) c, int mode, bool accumulate) -> ()", &tb200::gemm_bf16);
   m.def("gemm_grouped_bf16(Tensor a, Tensor b, Tensor(a!) c, Tensor offs, int mode, int align, bool accumulate) -> ()",
         &tb200::gemm_grouped_bf16);
+  m.def("gemm_allgather_bf16(Tensor(a!) a_gather, Tensor b, Tensor(b!) c, int[] peer_ptrs, int rank, Tensor(c!) flags, "
+        "int epoch, int mode) -> ()", &tb200::gemm_allgather_bf16);
+  m.def("gemm_scatter_bf16(Tensor a, Tensor b, int[] staging_ptrs, int rank, int mode) -> ()", &tb200::gemm_scatter_bf16);
+  m.def("sum_slots(Tensor staging) -> Tensor", &tb200::sum_slots);
   m.def("gemm_status(bool clear) -> int", &tb200::gemm_status);
   m.def("gemm_set_variant(int v) -> ()", &tb200::gemm_set_variant);
   m.def("gemm_set_debug(int v) -> ()", &tb200::gemm_set_debug);

@@ -84,16 +84,37 @@ struct Params {
   int group_mode;
   int b_group_rows;
   int c_rows;       // rows of the 2-D view of C
+  // ---- communication fused into the kernel (kComm instantiation only)
+  // All-gather -> GEMM: A is this rank's gather buffer [ranks * shard_rows, K].  The rank's own
+  // shard is already there; 128 extra threads per CTA pull the other shards from the peers' gather
+  // buffers (plain 16-byte peer loads over NVLink, local stores) in blocks of 128 rows and publish
+  // one flag per block; the TMA producer waits for the flag of a row block before it loads it,
+  // and row tiles are visited starting with the local shard, in the order the blocks arrive.
+  // GEMM -> reduce-scatter: the epilogue stores each tile into the staging buffer of the rank that
+  // owns those rows (slot = this rank) with TMA stores to peer memory; rows of the next ranks first.
+  uint32_t* a_flags;          // [ranks * shard_rows / 128], value = epoch once the block is local
+  uint32_t a_epoch;
+  int m_rotate;               // row tiles are visited from this tile index on (wrapping)
+  int gather_ranks, gather_rank, gather_shard_rows, gather_row_bytes;
+  const uint8_t* gather_src[8];
+  uint8_t* gather_dst;
+  int scatter_ranks, scatter_rank, scatter_shard_rows;
 };
+
+struct CommMaps {
+  CUtensorMap m[8];           // staging buffers of the ranks (GEMM -> reduce-scatter)
+};
+
+constexpr int kCommThreads = 128;
 
 struct Tile {
   int skip, m_base, n0, c_row, b_row_off, k_beg, nkb;
 };
 
-template <int kCta>
-__global__ void __launch_bounds__(kThreads, 1)
+template <int kCta, bool kComm>
+__global__ void __launch_bounds__(kThreads + (kComm ? kCommThreads : 0), 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                 const __grid_constant__ CUtensorMap tmap_c, const Params p) {
+                 const __grid_constant__ CUtensorMap tmap_c, const __grid_constant__ CommMaps cmaps, const Params p) {
   using C_ = Cfg<kCta>;
   constexpr int kStages = C_::kStages;
   constexpr uint32_t kABytes = C_::kABytes, kStageBytes = C_::kStageBytes;
@@ -143,6 +164,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       t -= e * tiles_per_group;
     }
     tile_coord(t, tm, tn);
+    if (kComm && p.m_rotate) tm = (tm + p.m_rotate) % num_m;
     ti.skip = 0;
     ti.m_base = tm * kTileM;
     ti.n0 = tn * BN;
@@ -206,6 +228,18 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         if (ti.skip) continue;
         const int m0 = ti.m_base + (int)cta_rank * BM;
         const int n0 = ti.n0 + (int)cta_rank * C_::kBRows;
+        if (kComm && p.a_flags != nullptr && m0 < p.M && m0 / p.gather_shard_rows != p.gather_rank) {
+          // rows of another rank: wait (bounded) until the copy threads have brought this block in
+          const uint32_t* f = p.a_flags + m0 / BM;
+          uint32_t seen = 0, spins = 0;
+          while (true) {
+            asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(f) : "memory");
+            if ((int32_t)(seen - p.a_epoch) >= 0) break;
+            if (++spins > kSpinLimit || *abort_flag) { *abort_flag = 1; ok = false; break; }
+          }
+          if (!ok) break;
+          asm volatile("fence.proxy.async.global;" ::: "memory");   // the TMA engine reads what generic stores wrote
+        }
         for (int kb = 0; kb < ti.nkb; ++kb, ++it) {
           const int s = it % kStages;
           const uint32_t parity = ((it / kStages) & 1u) ^ 1u;
@@ -297,6 +331,33 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         }
       }
     }
+  } else if (kComm && warp >= 6) {
+    // ------------------------------------------------------------- shard copy threads (all-gather)
+    if (p.gather_ranks > 1) {
+      const int ct = (int)threadIdx.x - kThreads;
+      const int per_shard = p.gather_shard_rows / BM;
+      const int total = (p.gather_ranks - 1) * per_shard;
+      const int n16 = BM * p.gather_row_bytes / 16;
+      for (int c = (int)blockIdx.x; c < total; c += (int)gridDim.x) {
+        const int src = (p.gather_rank + 1 + c / per_shard) % p.gather_ranks;
+        const int blk = src * per_shard + c % per_shard;
+        const int64_t off = (int64_t)blk * BM * p.gather_row_bytes;
+        const uint4* sp = reinterpret_cast<const uint4*>(p.gather_src[src] + off);
+        uint4* dp = reinterpret_cast<uint4*>(p.gather_dst + off);
+        for (int i = ct; i < n16; i += kCommThreads * 4) {
+          uint4 v[4];
+#pragma unroll
+          for (int u = 0; u < 4; ++u)
+            if (i + u * kCommThreads < n16) v[u] = sp[i + u * kCommThreads];
+#pragma unroll
+          for (int u = 0; u < 4; ++u)
+            if (i + u * kCommThreads < n16) dp[i + u * kCommThreads] = v[u];
+        }
+        __threadfence();
+        asm volatile("bar.sync 1, %0;" ::"n"(kCommThreads) : "memory");   // the four copy warps (no waits inside this loop)
+        if (ct == 0) asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p.a_flags + blk), "r"(p.a_epoch) : "memory");
+      }
+    }
   } else {
     // ------------------------------------------------------------- epilogue (warps 2..5, every CTA)
     const int q = warp & 3;  // TMEM lane quarter this warp may access
@@ -354,8 +415,15 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           __syncwarp();
           const int col0 = n0 + c * 64;
           if (lane == 0 && col0 < p.N && m0 + q * 32 < p.c_rows && !(p.debug & 2)) {
-            if (p.accumulate) tma_reduce_add_2d(&tmap_c, buf, col0, m0 + q * 32);
-            else tma_store_2d(&tmap_c, buf, col0, m0 + q * 32);
+            if (kComm && p.scatter_ranks > 0) {
+              const int r0 = m0 + q * 32;
+              const int dst = r0 / p.scatter_shard_rows;
+              tma_store_2d(&cmaps.m[dst], buf, col0, p.scatter_rank * p.scatter_shard_rows + r0 % p.scatter_shard_rows);
+            } else if (p.accumulate) {
+              tma_reduce_add_2d(&tmap_c, buf, col0, m0 + q * 32);
+            } else {
+              tma_store_2d(&tmap_c, buf, col0, m0 + q * 32);
+            }
             tma_store_commit();
           }
           sbuf ^= 1u;
@@ -368,7 +436,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         else mbar_arrive_cluster(te_leader + 8u * acc);
       }
     }
-    if (lane == 0) tma_store_wait<0>();   // shared memory must outlive the stores that read it
+    if (lane == 0) {
+      tma_store_wait<0>();   // shared memory must outlive the stores that read it
+      if (kComm && p.scatter_ranks > 0) __threadfence_system();   // tiles stored into peers' staging buffers
+    }
   }
 
   tc_fence_before();
@@ -417,21 +488,21 @@ void gemm_set_variant(int64_t v) {
   g_gemm_variant = (int)v;
 }
 
-template <int kCta>
+template <int kCta, bool kComm = false>
 static void launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc_, const gemm::Params& p,
-                        cudaStream_t stream) {
+                        cudaStream_t stream, const gemm::CommMaps* comm_maps = nullptr) {
   using namespace gemm;
   using C_ = Cfg<kCta>;
   static bool attr_set = false;
   if (!attr_set) {
-    C10_CUDA_CHECK(cudaFuncSetAttribute(gemm_bf16_kernel<kCta>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    C10_CUDA_CHECK(cudaFuncSetAttribute(gemm_bf16_kernel<kCta, kComm>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                         C_::kSmemBytes));
     attr_set = true;
   }
   const int tile_m = BM * kCta;
   const int tiles = ((p.M + tile_m - 1) / tile_m) * ((p.N + BN - 1) / BN) * (p.group_mode == 2 ? p.num_groups : 1);
   cudaLaunchConfig_t cfg = {};
-  cfg.blockDim = dim3(kThreads);
+  cfg.blockDim = dim3(kThreads + (kComm ? kCommThreads : 0));
   cfg.dynamicSmemBytes = C_::kSmemBytes;
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
@@ -451,12 +522,20 @@ static void launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const CUte
     if (max_pairs == 0) {
       cfg.gridDim = dim3(num_sms() & ~1);
       int n = 0;
-      C10_CUDA_CHECK(cudaOccupancyMaxActiveClusters(&n, gemm_bf16_kernel<kCta>, &cfg));
+      C10_CUDA_CHECK(cudaOccupancyMaxActiveClusters(&n, gemm_bf16_kernel<kCta, kComm>, &cfg));
       max_pairs = std::max(1, std::min(n, num_sms() / 2));
     }
     cfg.gridDim = dim3(2 * std::min(tiles, max_pairs));
   }
-  C10_CUDA_CHECK(cudaLaunchKernelEx(&cfg, gemm_bf16_kernel<kCta>, ta, tb, tc_, p));
+  static const CommMaps no_maps = {};
+  C10_CUDA_CHECK(cudaLaunchKernelEx(&cfg, gemm_bf16_kernel<kCta, kComm>, ta, tb, tc_, comm_maps ? *comm_maps : no_maps, p));
+}
+
+static void clear_comm(gemm::Params& p) {
+  p.a_flags = nullptr; p.a_epoch = 0; p.m_rotate = 0;
+  p.gather_ranks = 0; p.gather_rank = 0; p.gather_shard_rows = 1; p.gather_row_bytes = 0; p.gather_dst = nullptr;
+  for (auto& g : p.gather_src) g = nullptr;
+  p.scatter_ranks = 0; p.scatter_rank = 0; p.scatter_shard_rows = 1;
 }
 
 struct GroupArgs {
@@ -500,6 +579,7 @@ static void run_gemm(const at::Tensor& ref, const void* a, int64_t a_rows, int64
   p.status = gemm_status_tensor(ref.device()).data_ptr<int>();
   p.group_offs = g.offs; p.num_groups = g.num_groups; p.group_mode = g.mode; p.b_group_rows = g.b_group_rows;
   p.c_rows = (int)c_rows;
+  clear_comm(p);
   auto stream = at::cuda::getCurrentCUDAStream();
   if (pair) launch_gemm<2>(ta, tb, tcm, p, stream);
   else launch_gemm<1>(ta, tb, tcm, p, stream);
@@ -568,6 +648,116 @@ void gemm_grouped_bf16(const at::Tensor& a, const at::Tensor& b, at::Tensor c, c
     g.mode = 2;
     run_gemm(a, a.data_ptr(), R, M, b.data_ptr(), R, N, c.data_ptr(), (int64_t)G * M, M, N, R, true, true, accumulate, g);
   }
+}
+
+// ---- tensor-parallel GEMMs with the collective inside the kernel --------------------------
+// All-gather -> GEMM.  `a_gather` is this rank's gather buffer [ranks * shard_rows, K] in symmetric
+// memory with the rank's own rows already in place; `peer_ptrs[r]` is the address of rank r's
+// gather buffer; `flags` (uint32 [ranks * shard_rows / 128], zero-initialised once) and the
+// monotonically increasing `epoch` tell the GEMM which row blocks have arrived.  Every rank must
+// have passed a barrier after writing its own rows and before this call.
+//   mode 0: c = gathered . b^T (b [N, K]);  mode 1: c = gathered . b (b [K, N]).
+void gemm_allgather_bf16(const at::Tensor& a_gather, const at::Tensor& b, at::Tensor c, at::IntArrayRef peer_ptrs,
+                         int64_t rank, at::Tensor flags, int64_t epoch, int64_t mode) {
+  using namespace gemm;
+  check_bf16_2d(a_gather, "a_gather"); check_bf16_2d(b, "b"); check_bf16_2d(c, "c");
+  TORCH_CHECK(mode == 0 || mode == 1, "gemm_allgather_bf16: mode 0 (NT) or 1 (NN)");
+  const int R = (int)peer_ptrs.size();
+  TORCH_CHECK(R >= 1 && R <= 8 && rank >= 0 && rank < R, "gemm_allgather_bf16: 1..8 ranks");
+  const int64_t M = a_gather.size(0), K = a_gather.size(1);
+  const int64_t N = mode == 0 ? b.size(0) : b.size(1);
+  TORCH_CHECK((mode == 0 ? b.size(1) : b.size(0)) == K && c.size(0) == M && c.size(1) == N);
+  TORCH_CHECK(M % R == 0 && (M / R) % 256 == 0, "gemm_allgather_bf16: the shard must be a multiple of 256 rows");
+  TORCH_CHECK(K % 8 == 0 && N % 8 == 0);
+  TORCH_CHECK(flags.is_cuda() && flags.scalar_type() == at::kInt && flags.numel() >= M / BM && flags.is_contiguous());
+  c10::cuda::CUDAGuard guard(a_gather.device());
+  C10_CUDA_CHECK(cudaSetDevice(a_gather.device().index()));
+  const bool b_mn = mode == 1;
+  const CUtensorMap ta = make_tmap_2d(a_gather.data_ptr(), K, M, K * 2, BK, BM);
+  const CUtensorMap tb = b_mn ? make_tmap_2d(b.data_ptr(), N, K, N * 2, 64, BK)
+                              : make_tmap_2d(b.data_ptr(), K, N, K * 2, BK, Cfg<2>::kBRows);
+  const CUtensorMap tcm = make_tmap_2d(c.data_ptr(), N, M, N * 2, 64, 32);
+  Params p;
+  p.M = (int)M; p.N = (int)N; p.K = (int)K;
+  p.a_mn_major = 0; p.b_mn_major = b_mn; p.accumulate = 0; p.debug = 0;
+  p.C = reinterpret_cast<__nv_bfloat16*>(c.data_ptr());
+  p.status = gemm_status_tensor(a_gather.device()).data_ptr<int>();
+  p.group_offs = nullptr; p.num_groups = 0; p.group_mode = 0; p.b_group_rows = 0; p.c_rows = (int)M;
+  clear_comm(p);
+  const int shard = (int)(M / R);
+  p.a_flags = reinterpret_cast<uint32_t*>(flags.data_ptr<int>());
+  p.a_epoch = (uint32_t)epoch;
+  p.m_rotate = (int)rank * (shard / (2 * BM));
+  p.gather_ranks = R; p.gather_rank = (int)rank; p.gather_shard_rows = shard; p.gather_row_bytes = (int)(K * 2);
+  for (int r = 0; r < R; ++r) p.gather_src[r] = reinterpret_cast<const uint8_t*>(static_cast<uintptr_t>(peer_ptrs[r]));
+  p.gather_dst = reinterpret_cast<uint8_t*>(a_gather.data_ptr());
+  launch_gemm<2, true>(ta, tb, tcm, p, at::cuda::getCurrentCUDAStream());
+}
+
+// GEMM -> reduce-scatter, first half: every tile of this rank's partial product [M, N] is stored
+// into the staging buffer [ranks, M / ranks, N] of the rank that owns its rows, in slot `rank`
+// (TMA stores to peer memory from the epilogue).  After a barrier, `sum_slots` of the local staging
+// buffer gives this rank's rows of the sum.  mode 0: a . b^T, mode 1: a . b.
+void gemm_scatter_bf16(const at::Tensor& a, const at::Tensor& b, at::IntArrayRef staging_ptrs, int64_t rank, int64_t mode) {
+  using namespace gemm;
+  check_bf16_2d(a, "a"); check_bf16_2d(b, "b");
+  TORCH_CHECK(mode == 0 || mode == 1);
+  const int R = (int)staging_ptrs.size();
+  TORCH_CHECK(R >= 1 && R <= 8 && rank >= 0 && rank < R);
+  const int64_t M = a.size(0), K = a.size(1);
+  const int64_t N = mode == 0 ? b.size(0) : b.size(1);
+  TORCH_CHECK((mode == 0 ? b.size(1) : b.size(0)) == K);
+  TORCH_CHECK(M % R == 0 && (M / R) % 256 == 0, "gemm_scatter_bf16: the shard must be a multiple of 256 rows");
+  TORCH_CHECK(K % 8 == 0 && N % 8 == 0);
+  c10::cuda::CUDAGuard guard(a.device());
+  C10_CUDA_CHECK(cudaSetDevice(a.device().index()));
+  const bool b_mn = mode == 1;
+  const CUtensorMap ta = make_tmap_2d(a.data_ptr(), K, M, K * 2, BK, BM);
+  const CUtensorMap tb = b_mn ? make_tmap_2d(b.data_ptr(), N, K, N * 2, 64, BK)
+                              : make_tmap_2d(b.data_ptr(), K, N, K * 2, BK, Cfg<2>::kBRows);
+  CommMaps maps = {};
+  for (int r = 0; r < R; ++r)
+    maps.m[r] = make_tmap_2d(reinterpret_cast<const void*>(static_cast<uintptr_t>(staging_ptrs[r])), N, M, N * 2, 64, 32);
+  Params p;
+  p.M = (int)M; p.N = (int)N; p.K = (int)K;
+  p.a_mn_major = 0; p.b_mn_major = b_mn; p.accumulate = 0; p.debug = 0;
+  p.C = nullptr;
+  p.status = gemm_status_tensor(a.device()).data_ptr<int>();
+  p.group_offs = nullptr; p.num_groups = 0; p.group_mode = 0; p.b_group_rows = 0; p.c_rows = (int)M;
+  clear_comm(p);
+  const int shard = (int)(M / R);
+  p.scatter_ranks = R; p.scatter_rank = (int)rank; p.scatter_shard_rows = shard;
+  p.m_rotate = (int)((rank + 1) % R) * (shard / (2 * BM));
+  launch_gemm<2, true>(ta, tb, maps.m[rank], p, at::cuda::getCurrentCUDAStream(), &maps);
+}
+
+// out[rows, N] = sum over slots of staging[slot, rows, N] (fp32 accumulation).
+__global__ void sum_slots_kernel(const __nv_bfloat16* __restrict__ st, __nv_bfloat16* __restrict__ out, int64_t n_vec,
+                                 int slots) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n_vec) return;
+  float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  for (int s = 0; s < slots; ++s) {
+    float v[8];
+    unpack8(reinterpret_cast<const bf16x8*>(st)[(int64_t)s * n_vec + i], v);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] += v[j];
+  }
+  reinterpret_cast<bf16x8*>(out)[i] = pack8(acc);
+}
+
+at::Tensor sum_slots(const at::Tensor& staging) {
+  TORCH_CHECK(staging.is_cuda() && staging.scalar_type() == at::kBFloat16 && staging.dim() == 3 && staging.is_contiguous());
+  TORCH_CHECK((staging.size(1) * staging.size(2)) % 8 == 0);
+  c10::cuda::CUDAGuard guard(staging.device());
+  auto out = at::empty({staging.size(1), staging.size(2)}, staging.options());
+  const int64_t n_vec = out.numel() / 8;
+  if (n_vec > 0)
+    sum_slots_kernel<<<(unsigned)((n_vec + 255) / 256), 256, 0, at::cuda::getCurrentCUDAStream()>>>(
+        reinterpret_cast<const __nv_bfloat16*>(staging.data_ptr()), reinterpret_cast<__nv_bfloat16*>(out.data_ptr()), n_vec,
+        (int)staging.size(0));
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+  return out;
 }
 
 int64_t gemm_status(bool clear) {
