@@ -177,3 +177,65 @@ def test_fused_tensor_parallel_gemms(tmp_path):
     r = torch.load(out)
     assert r["errs"][-1] == 0, "a bounded wait expired"
     assert (r["errs"][:-1] < 3e-2).all(), r
+
+
+def _train_tp(rank, world, tp_comm, out_path):
+    import torch.distributed as dist
+
+    from tests.test_engine import _small_model_cfg
+    from torchtitan_b200.components.optimizer import OptimizersContainer, clip_grad_norm_
+    from torchtitan_b200.ops import functional as OF
+    from torchtitan_b200.parallel.parallel_dims import ParallelDims
+    from torchtitan_b200.parallel.parallelize import parallelize_decoder
+    from torchtitan_b200.trainer import Trainer
+
+    Tn = 1024
+    dev = torch.device("cuda", rank)
+    cfg = Trainer.Config()
+    cfg.training.num_tokens_per_microbatch_per_dp_rank = Tn
+    cfg.training.max_context_length = Tn
+    cfg.parallelism.tensor_parallel_degree = world
+    cfg.parallelism.tp_comm = tp_comm
+    cfg.parallelism.tp_symm_bytes = 64 << 20
+    pdims = ParallelDims(world_size=world, rank=rank, tp=world).build()
+    mc = _small_model_cfg(2)
+    for blk in mc.layers:
+        blk.attention.rope.max_context_length = Tn
+    with torch.device("meta"):
+        model = mc.build()
+    eng = parallelize_decoder(model, pdims=pdims, job_config=cfg, device=dev, seed=3)
+    if tp_comm == "nvlink":
+        assert model.tp.fused is not None
+    opt = OptimizersContainer(OptimizersContainer.Config(lr=1e-2), engines=[eng])
+    from torchtitan_b200.components.loss import LinearCrossEntropyLoss
+
+    loss_fn = LinearCrossEntropyLoss()
+    loss_fn.set_lm_head(model.lm_head, tp=model.tp)
+    g = torch.Generator().manual_seed(0)
+    pos = torch.arange(Tn, device=dev)
+    losses = []
+    for s in range(3):
+        ids = torch.randint(0, 2048, (Tn + 1,), generator=g)
+        tok, lab = ids[:-1].to(dev), ids[1:].to(dev)
+        opt.zero_grad()
+        h = model(tok, pos, return_hidden=True)
+        loss = loss_fn(h, lab, torch.tensor(float(Tn), device=dev))
+        loss.backward()
+        eng.finish_backward()
+        clip_grad_norm_([eng], 1.0, pdims, optimizers=opt)
+        opt.step()
+        losses.append(loss.detach())
+    eng.check_status()
+    torch.cuda.synchronize()
+    assert int(torch.ops.tb200.gemm_status(True)) == 0
+    if rank == 0:
+        torch.save({"losses": torch.stack(losses).cpu()}, out_path)
+
+
+@pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
+def test_tensor_parallel_fused_matches_nccl(tmp_path):
+    a, b = str(tmp_path / "tp_nccl.pt"), str(tmp_path / "tp_nvl.pt")
+    run_distributed(_train_tp, 2, "nccl", a, backend="nccl")
+    run_distributed(_train_tp, 2, "nvlink", b, backend="nccl")
+    ra, rb = torch.load(a), torch.load(b)
+    assert torch.allclose(ra["losses"], rb["losses"], atol=3e-2), (ra["losses"], rb["losses"])

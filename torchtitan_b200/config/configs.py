@@ -81,6 +81,10 @@ class ParallelismConfig:
     peer loads/stores over symmetric memory; ``nccl`` is the library baseline; ``auto`` uses
     NVLink when symmetric memory can be set up on every rank and NCCL otherwise."""
     tp_comm: Literal["nccl", "nvlink"] = "nccl"
+    """``nvlink``: all-gather -> GEMM and GEMM -> reduce-scatter of the tensor-parallel linears run as one
+    kernel each over symmetric memory (the eager form of the reference's async tensor parallelism)."""
+    tp_symm_bytes: int = 2 << 30
+    """Symmetric memory reserved per tensor-parallel group for gather / staging buffers."""
     cp_comm: Literal["allgather", "ring"] = "allgather"
     ep_comm: Literal["nccl", "nvlink"] = "nccl"
 

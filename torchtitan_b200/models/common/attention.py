@@ -135,11 +135,18 @@ class GQAttention(Module):
                 norm: RMSNorm | None = None) -> torch.Tensor:
         tp = self.tp
         hd, hq, hkv = self.head_dim, self.n_heads, self.n_kv_heads
+        fused = False
         if tp is not None:
             if norm is not None:
                 x = norm(x)
-            x = tp_ops.all_gather_rows(x, tp) if tp.sequence_parallel else tp_ops.copy_to_tp(x, tp)
-            qkv = self.wqkv(x)
+            fused = tp.fused_ok(x, self.wqkv, self.wo) and tp.fused.supported(x.shape[0] * tp.size, x.shape[1], hq * hd)
+            if fused:
+                from torchtitan_b200.parallel import tp_fused
+
+                qkv = tp_fused.all_gather_linear(x, self.wqkv.weight, tp.fused)
+            else:
+                x = tp_ops.all_gather_rows(x, tp) if tp.sequence_parallel else tp_ops.copy_to_tp(x, tp)
+                qkv = self.wqkv(x)
         elif norm is not None and type(self.wqkv) is Linear and norm.weight is not None and self.wqkv.bias is None:
             qkv = OF.norm_linear(x, norm.weight, self.wqkv.weight, norm.eps)
         else:
@@ -167,6 +174,10 @@ class GQAttention(Module):
         else:
             o = OF.attention(q, k, v, scale=self.scale, causal=True, doc_ids=ctx.doc_ids, window=self.window,
                              sinks=self.sinks, kv_first=ctx.kv_first)
+        if fused:
+            from torchtitan_b200.parallel import tp_fused
+
+            return tp_fused.linear_reduce_scatter(o.reshape(T, hq * hd), self.wo.weight, tp.fused)
         y = self.wo(o.reshape(T, hq * hd))
         if tp is not None:
             return tp_ops.reduce_scatter_rows(y, tp) if tp.sequence_parallel else tp_ops.all_reduce(y, tp)

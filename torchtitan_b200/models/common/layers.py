@@ -35,6 +35,12 @@ class TPContext:
     rank: int
     sequence_parallel: bool = True
     comm: str = "nccl"
+    fused: object | None = None  # parallel.tp_fused.FusedTP when comm == "nvlink" on CUDA
+
+    def fused_ok(self, x, *weights) -> bool:
+        """The in-kernel collectives need sequence parallelism, bf16 CUDA rows and 256-row shards."""
+        return (self.fused is not None and self.sequence_parallel and x.is_cuda and x.dtype == torch.bfloat16
+                and x.dim() == 2 and all(type(w).__name__ == "Linear" and w.bias is None for w in weights))
 
 
 def _block_slices(blocks: list[int], tp_size: int, tp_rank: int) -> list[tuple[int, int]]:
@@ -275,6 +281,11 @@ class FeedForward(Module):
         if tp is not None:
             if norm is not None:
                 x = norm(x)
+            if tp.fused_ok(x, self.w13, self.w2) and tp.fused.supported(x.shape[0] * tp.size, x.shape[1], self.hidden_dim):
+                from torchtitan_b200.parallel import tp_fused
+
+                gu = tp_fused.all_gather_linear(x, self.w13.weight, tp.fused)
+                return tp_fused.linear_reduce_scatter(OF.swiglu(gu), self.w2.weight, tp.fused)
             if tp.sequence_parallel:
                 x = tp_ops.all_gather_rows(x, tp)
             else:

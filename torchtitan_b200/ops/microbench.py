@@ -152,9 +152,65 @@ def bench_elementwise(args) -> None:
         print(f"{name:12s}: {t:.3f} ms, {gbs(nbytes, t):.0f} GB/s algorithmic", flush=True)
 
 
+def bench_tp(args) -> None:
+    """Fused tensor-parallel GEMMs vs NCCL collective + cuBLAS; run under torchrun with >= 2 ranks:
+    ``python -m torch.distributed.run --nproc-per-node 2 --master-addr 127.0.0.1 -m torchtitan_b200.ops.microbench tp``."""
+    import os
+
+    import torch.distributed as dist
+
+    from torchtitan_b200.parallel.tp_fused import FusedTP
+
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", rank)))
+    dev = torch.device("cuda", torch.cuda.current_device())
+    dist.init_process_group("nccl", device_id=dev)
+    ftp = FusedTP(dist.group.WORLD, dev, nbytes=3 << 30)
+    timer = Timer()
+    Tn = T
+    S = Tn // world
+    shapes = [("wqkv  ag->gemm", "ag", 4096, 6144 // world), ("w13   ag->gemm", "ag", 4096, 28672 // world),
+              ("wo    gemm->rs", "rs", 4096 // world, 4096), ("w2    gemm->rs", "rs", 14336 // world, 4096)]
+    for name, kind, K, N in shapes:
+        w = (torch.randn(N, K, device=dev) * 0.02).bfloat16()
+        if kind == "ag":
+            x = torch.randn(S, K, device=dev).bfloat16()
+            full = torch.empty(Tn, K, device=dev, dtype=torch.bfloat16)
+            out = torch.empty(Tn, N, device=dev, dtype=torch.bfloat16)
+            fused = lambda: ftp.ag_gemm(x, w, 0)  # noqa: E731
+
+            def lib():
+                dist.all_gather_into_tensor(full, x)
+                torch.mm(full, w.t(), out=out)
+            nv_bytes = (world - 1) * S * K * 2
+        else:
+            x = torch.randn(Tn, K, device=dev).bfloat16()
+            part = torch.empty(Tn, N, device=dev, dtype=torch.bfloat16)
+            outs = torch.empty(S, N, device=dev, dtype=torch.bfloat16)
+            fused = lambda: ftp.gemm_rs(x, w, 0)  # noqa: E731
+
+            def lib():
+                torch.mm(x, w.t(), out=part)
+                dist.reduce_scatter_tensor(outs, part)
+            nv_bytes = (world - 1) * S * N * 2
+        t = torch.tensor([timer(fused), timer(lib)], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        fl = 2 * Tn * N * K
+        roof = max(fl / 1654.7e12, nv_bytes / 770e9) * 1e3
+        if rank == 0:
+            print(f"tp{world} {name} T{Tn} K{K} N{N}: fused {t[0]:.3f} ms | NCCL+cuBLAS {t[1]:.3f} ms | speedup "
+                  f"{t[1] / t[0]:.2f} | roofline {roof:.3f} ms ({roof / t[0]:.2f} of it)", flush=True)
+    torch.cuda.synchronize()
+    st = int(ftp.arena.status.item()) | int(torch.ops.tb200.gemm_status(True))
+    if rank == 0:
+        print("status words", st)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser()
-    ap.add_argument("kernel", choices=["gemm", "attention", "elementwise"])
+    ap.add_argument("kernel", choices=["gemm", "attention", "elementwise", "tp"])
     ap.add_argument("--case", default="8b", choices=["small", "8b"])
     ap.add_argument("--variant", type=int, default=0, help="GEMM tiling: 0 auto, 1 single CTA, 2 CTA pair")
     ap.add_argument("--once", action="store_true", help="one launch per shape, no library arm (profiler form)")
@@ -163,7 +219,7 @@ def main(argv=None) -> int:
 
     assert torch.cuda.is_available(), "microbench needs a GPU"
     ext.require()
-    {"gemm": bench_gemm, "attention": bench_attention, "elementwise": bench_elementwise}[args.kernel](args)
+    {"gemm": bench_gemm, "attention": bench_attention, "elementwise": bench_elementwise, "tp": bench_tp}[args.kernel](args)
     return 0
 
 

@@ -24,6 +24,14 @@ def apply_tensor_parallel(model: nn.Module, pdims, parallelism) -> TPContext | N
         return None
     tp = TPContext(group=pdims.group("tp"), size=pdims.tp, rank=pdims.local_rank("tp"),
                    sequence_parallel=parallelism.enable_sequence_parallel, comm=parallelism.tp_comm)
+    if parallelism.tp_comm == "nvlink" and torch.cuda.is_available() and tp.sequence_parallel:
+        # async tensor parallelism: the all-gather / reduce-scatter run inside the GEMM kernels
+        from .symm import symm_available
+        from .tp_fused import FusedTP
+
+        if symm_available():
+            dev = torch.device("cuda", torch.cuda.current_device())
+            tp.fused = FusedTP(tp.group, dev, nbytes=int(parallelism.tp_symm_bytes))
     if model.tok_embeddings is not None:
         model.tok_embeddings.shard_(tp)
     for blk in model.layers.values():
