@@ -14,6 +14,8 @@ FAMILIES = [
     ("qwen3", "qwen3_moe_debug", "debugmodel_moe"),
     ("deepseek_v3", "deepseek_v3_debugmodel", "debugmodel"),
     ("gpt_oss", "gpt_oss_debugmodel", "debugmodel"),
+    ("muse_glimmer", "muse_glimmer_debugmodel", "debugmodel"),
+    ("kimi_k2_7", "kimi_debugmodel", "debugmodel"),
 ]
 
 

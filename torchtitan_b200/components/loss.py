@@ -72,9 +72,10 @@ class LinearCrossEntropyLoss(BaseLoss):
         self.lm_head = None
         self.tp = None
         self.softcap = None
+        self.multiplier = 1.0
 
-    def set_lm_head(self, lm_head, tp=None, softcap: float | None = None) -> None:
-        self.lm_head, self.tp, self.softcap = lm_head, tp, softcap
+    def set_lm_head(self, lm_head, tp=None, softcap: float | None = None, multiplier: float = 1.0) -> None:
+        self.lm_head, self.tp, self.softcap, self.multiplier = lm_head, tp, softcap, multiplier
 
     def __call__(self, hidden, labels, global_valid_tokens):
         if self.lm_head is None:
@@ -91,9 +92,10 @@ class LinearCrossEntropyLoss(BaseLoss):
 
                 hidden = tp_ops.copy_to_tp(hidden, self.tp)
             return vocab_parallel_linear_cross_entropy(hidden, w, labels, inv, self.tp, self.config.num_chunks)
-        if self.softcap:
-            logits = OF.linear(hidden, w)
-            logits = self.softcap * torch.tanh(logits.float() / self.softcap)
+        if self.softcap or self.multiplier != 1.0:
+            logits = OF.linear(hidden, w).float() * self.multiplier
+            if self.softcap:
+                logits = self.softcap * torch.tanh(logits / self.softcap)
             return OF.cross_entropy_sum(logits, labels.reshape(-1)) * inv
         return OF.linear_cross_entropy(hidden, w, labels, inv, self.config.num_chunks)
 

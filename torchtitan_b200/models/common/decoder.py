@@ -70,6 +70,7 @@ class Decoder(Module):
         single_document: bool = False
         """Skip document masking (every batch row is one document starting at 0)."""
         final_logit_softcap: float | None = None
+        final_logit_multiplier: float = 1.0
         trainable_param_pattern: str | None = None
         """Regular expression of the parameter names that stay trainable (set by the LoRA converter);
         every other parameter is frozen after construction."""
@@ -134,6 +135,8 @@ class Decoder(Module):
 
             h = tp_ops.all_gather_rows(h, self.tp)
         logits = self.lm_head(h)
+        if self.config.final_logit_multiplier != 1.0:
+            logits = logits * self.config.final_logit_multiplier
         cap = self.config.final_logit_softcap
         if cap:
             logits = cap * torch.tanh(logits / cap)

@@ -14,7 +14,7 @@ from typing import Any, Callable
 
 __all__ = ["ModelSpec", "get_model_spec", "SUPPORTED_MODELS"]
 
-SUPPORTED_MODELS = ("llama3", "qwen3", "deepseek_v3", "gpt_oss")
+SUPPORTED_MODELS = ("llama3", "qwen3", "deepseek_v3", "gpt_oss", "kimi_k2_7", "muse_glimmer", "qwen3_5", "flux")
 
 
 @dataclass

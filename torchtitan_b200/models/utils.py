@@ -31,6 +31,8 @@ def count_params_and_flops(cfg, model: nn.Module | None, seq_len: int) -> tuple[
         a = blk.attention
         n_attn, qk_dim, v_dim, heads = attention_params(a, dim)
         layer = n_attn + 2 * dim
+        if hasattr(blk, "post_attention_norm"):
+            layer += 2 * dim
         layer_active = layer
         if blk.feed_forward is not None:
             f = 3 * dim * blk.feed_forward.hidden_dim
@@ -76,8 +78,10 @@ def attention_params(a, dim: int) -> tuple[int, int, int, int]:
         n += (h + 2 * kv) * hd
     if getattr(a.wo, "bias", False):
         n += dim
-    if a.qk_norm is not None:
+    if a.qk_norm is not None and getattr(a.qk_norm, "elementwise_affine", True):
         n += 2 * hd
+    if getattr(a, "o_gate", None) is not None:
+        n += dim * h * hd
     if getattr(a, "use_sinks", False):
         n += h
     return n, hd, hd, h

@@ -203,7 +203,8 @@ class Trainer(Configurable):
                 self.engines = [engine]
                 if isinstance(self.loss_fn, LinearCrossEntropyLoss):
                     self.loss_fn.set_lm_head(model.lm_head, tp=model.tp,
-                                             softcap=getattr(model_cfg, "final_logit_softcap", None))
+                                             softcap=getattr(model_cfg, "final_logit_softcap", None),
+                                             multiplier=getattr(model_cfg, "final_logit_multiplier", 1.0))
         self.model = self.model_parts[0]
 
         nparams, flops = model_cfg.get_nparams_and_flops(None, c.training.max_context_length)
