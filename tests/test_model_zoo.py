@@ -16,6 +16,8 @@ FAMILIES = [
     ("gpt_oss", "gpt_oss_debugmodel", "debugmodel"),
     ("muse_glimmer", "muse_glimmer_debugmodel", "debugmodel"),
     ("kimi_k2_7", "kimi_debugmodel", "debugmodel"),
+    ("qwen3_5", "qwen3_5_debugmodel", "debugmodel"),
+    ("qwen3_5", "qwen3_5_moe_debug", "debugmodel_moe"),
 ]
 
 
@@ -45,6 +47,24 @@ def test_param_count_matches_module_tree(module, flavor):
     n_cfg, flops = count_params_and_flops(spec.model, model, 2048)
     assert n_cfg == n_module, (n_cfg, n_module)
     assert flops > 0
+
+
+def test_gated_delta_rule_chunked_equals_recurrent():
+    from torchtitan_b200.models.qwen3_5.gdn import causal_conv_silu, chunk_gated_delta_rule, recurrent_gated_delta_rule
+
+    torch.manual_seed(0)
+    T, H, dk, dv = 150, 3, 16, 24
+    q, k, v = torch.randn(T, H, dk), torch.randn(T, H, dk), torch.randn(T, H, dv)
+    g, beta = -torch.rand(T, H) * 0.5, torch.rand(T, H)
+    g[70] = -1e3  # a document boundary: the state restarts
+    a, b = recurrent_gated_delta_rule(q, k, v, g, beta), chunk_gated_delta_rule(q, k, v, g, beta, chunk=32)
+    assert torch.allclose(a, b, atol=1e-4)
+    assert torch.allclose(a[70:], recurrent_gated_delta_rule(q[70:], k[70:], v[70:], g[70:], beta[70:]), atol=1e-5)
+    # the convolution does not reach across a document start
+    x, w = torch.randn(20, 6), torch.randn(6, 4)
+    pos = torch.cat([torch.arange(12), torch.arange(8)])
+    y = causal_conv_silu(x, w, pos)
+    assert torch.allclose(y[12:], causal_conv_silu(x[12:], w, None), atol=1e-6)
 
 
 @pytest.mark.parametrize("module,flavor", [("deepseek_v3", "debugmodel"), ("gpt_oss", "debugmodel"), ("qwen3", "debugmodel_moe")])

@@ -58,6 +58,11 @@ def count_params_and_flops(cfg, model: nn.Module | None, seq_len: int) -> tuple[
 
 def attention_params(a, dim: int) -> tuple[int, int, int, int]:
     """``(param count, qk head dim, v head dim, n_heads)`` of an attention config."""
+    if hasattr(a, "n_key_heads"):  # gated delta net: no softmax attention FLOPs (state updates are linear in T)
+        kd, vd = a.n_key_heads * a.key_head_dim, a.n_value_heads * a.value_head_dim
+        n = dim * (2 * kd + 2 * vd + 2 * a.n_value_heads) + (2 * kd + vd) * a.conv_kernel_size
+        n += 2 * a.n_value_heads + a.value_head_dim + vd * dim
+        return n, 0, 0, 0
     if hasattr(a, "kv_lora_rank"):  # multi-head latent attention
         h = a.n_heads
         qk = a.qk_nope_head_dim + a.qk_rope_head_dim
