@@ -23,16 +23,19 @@ def main(argv: list[str] | None = None) -> None:
     from torchtitan_b200.parallel import utils as dist_utils
 
     config = ConfigManager().parse_args(argv)
-    sl.init_structured_logger("training", config.dump_folder, enable=config.debug.enable_structured_logging)
+    debug = getattr(config, "debug", None)
+    sl.init_structured_logger("training", getattr(config, "dump_folder", "./outputs"),
+                              enable=bool(debug and debug.enable_structured_logging))
     trainer = None
+    seed_ckpt = bool(getattr(getattr(config, "checkpoint", None), "create_seed_checkpoint", False))
     try:
-        if config.checkpoint.create_seed_checkpoint:
+        if seed_ckpt:
             if int(os.environ.get("WORLD_SIZE", "1")) != 1:
                 raise RuntimeError("a seed checkpoint must be created by a single process")
             if not config.checkpoint.enable:
                 raise RuntimeError("checkpoint.create_seed_checkpoint needs checkpoint.enable")
-        trainer = config.build()
-        if config.checkpoint.create_seed_checkpoint:
+        trainer = config.build()   # the LLM trainer, or a family's own trainer (e.g. flux)
+        if seed_ckpt:
             trainer.checkpointer.create_seed_checkpoint()
         else:
             trainer.train()
