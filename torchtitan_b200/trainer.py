@@ -240,6 +240,17 @@ class Trainer(Configurable):
         if c.validator.enable:
             self.validator = c.validator.build(trainer=self)
         self.profiler_config = c.profiler
+        self._graph_runner = None
+        self._mb_index = 0
+        if (not c.training.disable_cuda_graphs and self.device.type == "cuda" and not pd.pp_enabled
+                and not (pd.ep_enabled and c.parallelism.ep_comm == "nccl")):
+            from torchtitan_b200.parallel.cudagraph import CUDAGraphRunner
+
+            eng = self.engines[0]
+            self._graph_runner = CUDAGraphRunner(
+                self._fwd_bwd_tensors,
+                snapshot=lambda: [u.grad_shard_valid for u in eng.units],
+                after_replay=lambda st: [setattr(u, "grad_shard_valid", v) for u, v in zip(eng.units, st)])
         self._status_pending: list[tuple[int, torch.Tensor]] = []
         self._inv_tokens_cache = None
         logger.info(
@@ -292,6 +303,14 @@ class Trainer(Configurable):
             tokens, positions, labels, q_pos = self.post_dataloading_process(inputs, labels)
         if self.pdims.pp_enabled:
             return self.pp_forward_backward_step(tokens, positions, labels, q_pos, global_valid)
+        if self._graph_runner is not None and q_pos is None:
+            key = (min(self._mb_index, 1), tuple(tokens.shape))
+            self._mb_index += 1
+            with sl.span("fwd_bwd"):
+                return self._graph_runner(key, tokens, positions, labels, global_valid).detach()
+        return self._fwd_bwd_tensors(tokens, positions, labels, global_valid, q_pos)
+
+    def _fwd_bwd_tensors(self, tokens, positions, labels, global_valid, q_pos=None) -> torch.Tensor:
         model = self.model
         with sl.span("fwd_bwd"):
             ctx = model.build_context(positions, q_pos)
@@ -314,6 +333,7 @@ class Trainer(Configurable):
         c = self.config
         pd = self.pdims
         self.optimizers.zero_grad()
+        self._mb_index = 0
         n_mb = self.gradient_accumulation_steps * (c.parallelism.num_pp_microbatches if pd.pp_enabled else 1)
         microbatches = []
         host_valid = 0
