@@ -1,0 +1,60 @@
+"""Scripts and tools: HF conversion round trip, loss comparison, activation tracing."""
+
+import os
+
+import torch
+
+from torchtitan_b200.models import get_model_spec
+
+
+def test_convert_hf_round_trip(tmp_path):
+    import torch.distributed.checkpoint as dcp
+
+    from torchtitan_b200.scripts import convert_hf
+
+    spec = get_model_spec("llama3", "debugmodel")
+    tmpl = convert_hf._native_template(spec)
+    g = torch.Generator().manual_seed(0)
+    state = {f"model.{k}": torch.randn(shape, generator=g) for k, (_, _, shape) in tmpl.items()}
+    ck = str(tmp_path / "step-1")
+    dcp.save(state, checkpoint_id=ck, no_dist=True)
+    convert_hf.main(["to_hf", "--module", "llama3", "--flavor", "debugmodel", "--checkpoint", ck,
+                     "--out", str(tmp_path / "hf"), "--dtype", "float32"])
+    assert os.path.exists(tmp_path / "hf" / "model.safetensors.index.json")
+    convert_hf.main(["from_hf", "--module", "llama3", "--flavor", "debugmodel", "--hf-dir", str(tmp_path / "hf"),
+                     "--out", str(tmp_path / "back"), "--dtype", "float32"])
+    back = {k: torch.empty_like(v) for k, v in state.items()}
+    dcp.load(back, checkpoint_id=str(tmp_path / "back"), no_dist=True)
+    for k in state:
+        assert torch.equal(state[k], back[k]), k
+
+
+def test_loss_compare_detects_equal_and_different(tmp_path):
+    from torchtitan_b200.scripts import loss_compare
+
+    base = ("--module llama3 --config llama3_debugmodel --training.num_tokens_per_microbatch_per_dp_rank 128 "
+            "--training.max_context_length 64 --training.mixed_precision_param float32")
+    golden = str(tmp_path / "golden.json")
+    assert loss_compare.main(["--baseline", base, "--test", base, "--steps", "3", "--assert-equal",
+                              "--export", golden]) == 0
+    assert loss_compare.main(["--import", golden, "--test", base + " --optimizer.lr 1e-2", "--steps", "3",
+                              "--assert-equal"]) == 1
+
+
+def test_activation_tracer_finds_first_divergence():
+    from torchtitan_b200.tools.numerics import ActivationTracer, compare_traces
+
+    torch.manual_seed(0)
+    net = torch.nn.Sequential(torch.nn.Linear(8, 8), torch.nn.ReLU(), torch.nn.Linear(8, 4))
+    x = torch.randn(5, 8)
+    with ActivationTracer(net, grads=True) as a:
+        net(x).sum().backward()
+    with ActivationTracer(net, grads=True) as b:
+        net(x).sum().backward()
+    assert "no statistic differs" in compare_traces(a, b)
+    with torch.no_grad():
+        net[2].weight.mul_(3.0)
+    with ActivationTracer(net) as c:
+        net(x)
+    rep = compare_traces([r for r in a.records if r["kind"] == "out"], c)
+    assert "first divergence" in rep and ": 2 (" in rep
