@@ -36,6 +36,7 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor> flash_bwd(const at::Tensor& d_o, 
                                                          const c10::optional<at::Tensor>& dk_out,
                                                          const c10::optional<at::Tensor>& dv_out);
 int64_t flash_status(bool clear);
+void flash_set_debug(int64_t v);
 void symm_barrier(at::IntArrayRef flag_ptrs, int64_t my_rank, int64_t epoch, at::Tensor status, int64_t max_cycles);
 void reduce_scatter_pull(at::IntArrayRef grad_ptrs, int64_t my_rank, int64_t offset, at::Tensor out, bool grad_is_bf16,
                          bool accumulate);
@@ -87,6 +88,7 @@ TORCH_LIBRARY(tb200, m) {
         "int causal_offset, Tensor? kv_first, Tensor(a!)? dq_out, Tensor(b!)? dk_out, Tensor(c!)? dv_out) -> "
         "(Tensor, Tensor, Tensor)", &tb200::flash_bwd);
   m.def("flash_status(bool clear) -> int", &tb200::flash_status);
+  m.def("flash_set_debug(int v) -> ()", &tb200::flash_set_debug);
   m.def("mxfp8_quantize(Tensor x, int axis) -> (Tensor, Tensor)", &tb200::mxfp8_quantize);
   m.def("mxfp8_fake_quant(Tensor x, int axis) -> Tensor", &tb200::mxfp8_fake_quant);
   m.def("mxfp8_dequantize(Tensor data, Tensor scales, int axis) -> Tensor", &tb200::mxfp8_dequantize);

@@ -54,6 +54,7 @@ struct FwdParams {
   const int* kv_first;     // [Tq] first visible key per query row, or nullptr
   float* lse;              // [Hq, Tq] natural-log sum-exp of the scaled scores, row stride lse_stride
   int lse_stride;
+  int debug;               // timing diagnostics: bit 0 skips the softmax math, bit 1 skips the MMAs (results are garbage)
   int* status;
 };
 
@@ -116,8 +117,8 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
       mbar_init(bar(V_FULL + s), 1);
       mbar_init(bar(V_EMPTY + s), 1);
       mbar_init(bar(S_FULL + s), 1);
-      mbar_init(bar(P_READY + s), 128);
-      mbar_init(bar(O_STAGED + s), 128);
+      mbar_init(bar(P_READY + s), 4);      // one arrival per warp (lane 0 after __syncwarp)
+      mbar_init(bar(O_STAGED + s), 4);
     }
     mbar_init(bar(O_FULL), 1);
     *abort_flag = 0;
@@ -163,6 +164,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
       const uint32_t idesc_s = make_idesc(false, false, kBM, kBN);   // Q, K both K-major (head dim contiguous)
       const uint32_t idesc_pv = make_idesc(false, true, kBM, kD);    // V is [keys, head dim]: MN-major B
       auto issue_s = [&](int slot, int st) {
+        if (p.debug & 2) return;
         const uint32_t qa = q_smem + slot * kTileBytes, ka = k_smem + st * kTileBytes;
 #pragma unroll
         for (int k = 0; k < kD / 16; ++k) {
@@ -172,6 +174,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         }
       };
       auto issue_pv = [&](int slot, int st, bool accumulate) {
+        if (p.debug & 2) return;
         const uint32_t va = v_smem + st * kTileBytes;
 #pragma unroll
         for (int k = 0; k < kBN / 16; ++k)   // 16 keys per step: 8 packed columns of P, 16 rows (2048 B) of V
@@ -223,6 +226,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
       for (int i = 0; i < n_tiles; ++i) {
         if (!mbar_wait(bar(S_FULL + slot), i & 1u, abort_flag)) { ok = false; break; }
         tc_fence_after();
+        if (p.debug & 1) { tc_fence_before(); __syncwarp(); if (lane == 0) mbar_arrive(bar(P_READY + slot)); continue; }
         uint32_t r[4][32];
 #pragma unroll
         for (int c = 0; c < 4; ++c) tmem_ld32(s_t + c * 32, r[c]);
@@ -276,7 +280,8 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         }
         tmem_st_wait();
         tc_fence_before();
-        mbar_arrive(bar(P_READY + slot));
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(P_READY + slot));
       }
       // ---- epilogue: O / l -> bf16 -> swizzled staging tile (the slot's Q buffer) -> TMA store
       if (ok && n_tiles > 0) ok = mbar_wait(bar(O_FULL), 0, abort_flag);
@@ -308,7 +313,8 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
           }
         }
         fence_proxy_async_smem();
-        mbar_arrive(bar(O_STAGED + slot));                               // the four warps of this slot
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(O_STAGED + slot));                               // the four warps of this slot
         if (quarter == 0 && lane == 0 && mbar_wait(bar(O_STAGED + slot), 0, abort_flag)) {
           for (int h = 0; h < 2; ++h) tma_store_3d(&tmap_o, stage + h * kHalfBytes, h * 64, head0 + slot, q0);
           tma_store_commit();
@@ -348,10 +354,11 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
 // S^T / dP^T are double buffered: the MMAs of step t+1 run while the warps work on step t.
 //   warp 0       TMA producer (K, V once; Q and dO blocks through a four-stage ring)
 //   warp 1       TMEM allocation, MMA issue
-//   warps 2..9   lane quarter = warp % 4, column half = (warp - 2) / 4
+//   warps 2..17  lane quarter = warp % 4, column group (16 query columns) = (warp - 2) / 4
 // Tensor memory: S^T [0,64) [64,128)   dP^T [128,192) [192,256)   dK [256,384)   dV [384,512)
 constexpr int kBQ = 64;                       // query rows per step
-constexpr int kThreadsBwd = 320;
+constexpr int kMathGroups = 4;                // column groups: 4 warps (one per TMEM lane quarter) each
+constexpr int kThreadsBwd = 64 + 128 * kMathGroups;
 constexpr int kRing = 4;
 constexpr uint32_t kQBytes = kBQ * kD * 2;    // 16 KB: 64 x 128 bf16 (two 64-column halves of 8 KB)
 
@@ -362,6 +369,7 @@ struct BwdParams {
   const int* kv_first;     // [Tq] or nullptr
   const float* lse;        // [Hq, Tq], row stride `stat_stride`
   const float* delta;      // [Hq, Tq] rowsum(dO * O), row stride `stat_stride`
+  int debug;               // timing diagnostics: bit 0 skips the warps' math, bit 1 skips the MMAs (results are garbage)
   int stat_stride;         // a multiple of 64 floats, so that 64-row slices can be fetched with bulk copies
   int* status;
 };
@@ -407,10 +415,10 @@ flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(bar(ST_FULL + b), 1);
-      mbar_init(bar(PS_READY + b), 256);
+      mbar_init(bar(PS_READY + b), 4 * kMathGroups);   // one arrival per warp
     }
     mbar_init(bar(ALL_DONE), 1);
-    mbar_init(bar(OUT_STAGED), 256);
+    mbar_init(bar(OUT_STAGED), 4 * kMathGroups);
     *abort_flag = 0;
     mbar_fence_init();
     // query rows that can see this key block: [q_lo, q_hi)
@@ -479,18 +487,15 @@ flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
         const int st = t % kRing, b = t & 1;
         if (!mbar_wait(bar(R_FULL + st), (t / kRing) & 1u, abort_flag)) return false;
         tc_fence_after();
+        if (p.debug & 2) { umma_commit(bar(ST_FULL + b)); return true; }
         const uint32_t qa = ring_smem + st * 2 * kQBytes, doa = qa + kQBytes;
 #pragma unroll
         for (int k = 0; k < kD / 16; ++k) {
+          // the two accumulators alternate, so consecutive MMAs do not depend on each other
           const uint32_t koff = (uint32_t)(k >> 2) * kHalfBytes + (uint32_t)(k & 3) * 32u;
           const uint32_t qoff = (uint32_t)(k >> 2) * (kQBytes / 2) + (uint32_t)(k & 3) * 32u;
           umma_bf16<1>(tmem_base + T_ST + b * 64, make_desc(k_smem + koff, 16, 1024), make_desc(qa + qoff, 16, 1024),
                        idesc_st, k != 0 ? 1u : 0u);
-        }
-#pragma unroll
-        for (int k = 0; k < kD / 16; ++k) {
-          const uint32_t koff = (uint32_t)(k >> 2) * kHalfBytes + (uint32_t)(k & 3) * 32u;
-          const uint32_t qoff = (uint32_t)(k >> 2) * (kQBytes / 2) + (uint32_t)(k & 3) * 32u;
           umma_bf16<1>(tmem_base + T_DPT + b * 64, make_desc(v_smem + koff, 16, 1024), make_desc(doa + qoff, 16, 1024),
                        idesc_st, k != 0 ? 1u : 0u);
         }
@@ -504,15 +509,12 @@ flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
         if (!mbar_wait(bar(PS_READY + b), (t >> 1) & 1u, abort_flag)) { ok = false; break; }
         tc_fence_after();
         const uint32_t qa = ring_smem + st * 2 * kQBytes, doa = qa + kQBytes;
+        if (!(p.debug & 2))
 #pragma unroll
-        for (int ks = 0; ks < kBQ / 16; ++ks) {   // 16 queries per step: 8 packed columns, 16 rows (2048 B) of dO
-          const uint32_t a_col = (uint32_t)b * 64u + (uint32_t)(ks >> 1) * 32u + (uint32_t)(ks & 1) * 8u;
+        for (int ks = 0; ks < kBQ / 16; ++ks) {   // 16 queries per step: 8 packed columns, 16 rows (2048 B) of dO / Q
+          const uint32_t a_col = (uint32_t)b * 64u + (uint32_t)ks * 16u;
           umma_bf16_ts(tmem_base + T_DV, tmem_base + T_ST + a_col, make_desc(doa + ks * 2048, kQBytes / 2, 1024),
                        idesc_acc, (t > 0 || ks > 0) ? 1u : 0u);
-        }
-#pragma unroll
-        for (int ks = 0; ks < kBQ / 16; ++ks) {
-          const uint32_t a_col = (uint32_t)b * 64u + (uint32_t)(ks >> 1) * 32u + (uint32_t)(ks & 1) * 8u;
           umma_bf16_ts(tmem_base + T_DK, tmem_base + T_DPT + a_col, make_desc(qa + ks * 2048, kQBytes / 2, 1024),
                        idesc_acc, (t > 0 || ks > 0) ? 1u : 0u);
         }
@@ -523,30 +525,30 @@ flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
   } else {
     // ------------------------------------------------------------------ softmax gradient, epilogue
     const int quarter = warp & 3;
-    const int half = (warp - 2) >> 2;
+    const int grp = (warp - 2) >> 2;               // 16 of the 64 query columns of a step
     const int r = quarter * 32 + lane;             // key row of this thread
     const int kv_idx = k0 + r;
     const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
     bool ok = true;
     for (int t = 0; t < n_iter; ++t) {
       const int b = t & 1;
-      const int head = kv_head * group + t / n_sub;
-      const int qc0 = q_lo + (t % n_sub) * kBQ + half * 32;    // first query column of this thread
+      const int qc0 = q_lo + (t % n_sub) * kBQ + grp * 16;    // first query column of this thread
       if (!mbar_wait(bar(ST_FULL + b), (t >> 1) & 1u, abort_flag)) { ok = false; break; }
       tc_fence_after();
-      uint32_t sv[32], dv[32];
-      tmem_ld32(tmem_base + lane_addr + T_ST + b * 64 + half * 32, sv);
-      tmem_ld32(tmem_base + lane_addr + T_DPT + b * 64 + half * 32, dv);
+      if (p.debug & 1) { tc_fence_before(); __syncwarp(); if (lane == 0) mbar_arrive(bar(PS_READY + b)); continue; }
+      uint32_t sv[16], dv[16];
+      tmem_ld16(tmem_base + lane_addr + T_ST + b * 64 + grp * 16, sv);
+      tmem_ld16(tmem_base + lane_addr + T_DPT + b * 64 + grp * 16, dv);
       tmem_ld_wait();
       // lse and delta of the 64 query rows of this step were staged next to Q / dO by the producer
       // (the stage's barrier has completed long ago: the MMAs that filled S^T waited on it)
       if (!mbar_wait(bar(R_FULL + t % kRing), (t / kRing) & 1u, abort_flag)) { ok = false; break; }
-      const uint32_t stat = stat_smem + (uint32_t)(t % kRing) * 512u + (uint32_t)half * 128u;
-      const bool edge = p.kv_first != nullptr || qc0 + 32 > p.Tq || k0 + kBN > p.Tk ||
+      const uint32_t stat = stat_smem + (uint32_t)(t % kRing) * 512u + (uint32_t)grp * 64u;
+      const bool edge = p.kv_first != nullptr || qc0 + 16 > p.Tq || k0 + kBN > p.Tk ||
                         (p.causal && qc0 + p.causal_offset < k0 + kBN - 1);
-      uint32_t pk[16], dk[16];
+      uint32_t pk[8], dk[8];
 #pragma unroll
-      for (int g = 0; g < 8; ++g) {
+      for (int g = 0; g < 4; ++g) {
         float l4[4], d4[4];
         asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];"
                      : "=f"(l4[0]), "=f"(l4[1]), "=f"(l4[2]), "=f"(l4[3]) : "r"(stat + g * 16));
@@ -572,11 +574,13 @@ flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
         dk[2 * g] = pack_bf16(ds[0], ds[1]);
         dk[2 * g + 1] = pack_bf16(ds[2], ds[3]);
       }
-      tmem_st16(tmem_base + lane_addr + T_ST + b * 64 + half * 32, pk);
-      tmem_st16(tmem_base + lane_addr + T_DPT + b * 64 + half * 32, dk);
+      // packed P^T / dS^T of this group's 16 columns go to the first 8 of its own 16 TMEM columns
+      tmem_st8(tmem_base + lane_addr + T_ST + b * 64 + grp * 16, pk);
+      tmem_st8(tmem_base + lane_addr + T_DPT + b * 64 + grp * 16, dk);
       tmem_st_wait();
       tc_fence_before();
-      mbar_arrive(bar(PS_READY + b));
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(PS_READY + b));
     }
     if (ok && n_iter > 0) ok = mbar_wait(bar(ALL_DONE), 0, abort_flag);
     // ---- dK, dV: tensor memory -> bf16 -> swizzled staging tiles (the Q / dO ring) -> TMA store
@@ -584,32 +588,31 @@ flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
       tc_fence_after();
 #pragma unroll 1
       for (int which = 0; which < 2; ++which) {
-        const uint32_t stage = ring_smem + which * kTileBytes + half * kHalfBytes;
-#pragma unroll 1
-        for (int c = 0; c < 2; ++c) {
-          uint32_t o[32];
-          if (n_iter > 0) {
-            tmem_ld32(tmem_base + lane_addr + (which ? T_DV : T_DK) + half * 64 + c * 32, o);
-            tmem_ld_wait();
-          } else {
+        // this thread's 32 head-dim columns: 64-column half grp / 2, 16-byte chunks (grp % 2) * 4 ...
+        const uint32_t stage = ring_smem + which * kTileBytes + (grp >> 1) * kHalfBytes;
+        uint32_t o[32];
+        if (n_iter > 0) {
+          tmem_ld32(tmem_base + lane_addr + (which ? T_DV : T_DK) + grp * 32, o);
+          tmem_ld_wait();
+        } else {
 #pragma unroll
-            for (int e = 0; e < 32; ++e) o[e] = 0u;
-          }
+          for (int e = 0; e < 32; ++e) o[e] = 0u;
+        }
 #pragma unroll
-          for (int jj = 0; jj < 4; ++jj) {
-            uint32_t w[4];
+        for (int jj = 0; jj < 4; ++jj) {
+          uint32_t w[4];
 #pragma unroll
-            for (int e = 0; e < 4; ++e)
-              w[e] = pack_bf16(__uint_as_float(o[jj * 8 + 2 * e]), __uint_as_float(o[jj * 8 + 2 * e + 1]));
-            const int chunk = c * 4 + jj;
-            const uint32_t dst = stage + (uint32_t)r * 128u + (uint32_t)((chunk ^ (r & 7)) << 4);
-            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3])
-                         : "memory");
-          }
+          for (int e = 0; e < 4; ++e)
+            w[e] = pack_bf16(__uint_as_float(o[jj * 8 + 2 * e]), __uint_as_float(o[jj * 8 + 2 * e + 1]));
+          const int chunk = (grp & 1) * 4 + jj;
+          const uint32_t dst = stage + (uint32_t)r * 128u + (uint32_t)((chunk ^ (r & 7)) << 4);
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3])
+                       : "memory");
         }
       }
       fence_proxy_async_smem();
-      mbar_arrive(bar(OUT_STAGED));
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(OUT_STAGED));
       if (warp == 2 && lane == 0 && mbar_wait(bar(OUT_STAGED), 0, abort_flag)) {
         for (int h = 0; h < 2; ++h) {
           tma_store_3d(&tmap_dk, ring_smem + h * kHalfBytes, h * 64, kv_head, k0);
@@ -633,11 +636,12 @@ flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
 // flash_bwd_dq_kernel.  One CTA owns 128 query rows of one head and walks over the key blocks
 // those rows can see (the forward's loop).  Per key block:
 //     S = Q . K^T,  dP = dO . V^T             (tcgen05.mma, shared-memory operands)
-//     dS = exp2(S c - lse) (dP - delta) scale  (8 warps: one query row, 64 keys per thread),
+//     dS = exp2(S c - lse) (dP - delta) scale  (16 warps: one query row, 32 keys per thread),
 //          written over S as packed bf16
 //     dQ += dS . K                             (A operand from tensor memory)
 // dP is double buffered, so the dP MMA of the next block runs during the warps' math.
-//   warp 0 TMA producer (Q, dO once; K and V through two-stage rings), warp 1 MMA, warps 2..9 math
+//   warp 0 TMA producer (Q, dO once; K and V through two-stage rings), warp 1 MMA, warps 2..17 math
+//   (lane quarter = warp % 4, group of 32 keys = (warp - 2) / 4)
 // Tensor memory: S / dS [0,128)   dP [128,256) [256,384)   dQ [384,512)
 __global__ void __launch_bounds__(kThreadsBwd, 1)
 flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_do,
@@ -684,9 +688,9 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
       mbar_init(bar(DP_FULL + s), 1);
     }
     mbar_init(bar(S_FULL), 1);
-    mbar_init(bar(DS_READY), 256);
+    mbar_init(bar(DS_READY), 4 * kMathGroups);
     mbar_init(bar(DQ_FULL), 1);
-    mbar_init(bar(OUT_STAGED), 256);
+    mbar_init(bar(OUT_STAGED), 4 * kMathGroups);
     *abort_flag = 0;
     mbar_fence_init();
     tma_prefetch_desc(&tmap_q);
@@ -730,6 +734,7 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
       const uint32_t idesc_s = make_idesc(false, false, kBM, kBN);
       const uint32_t idesc_dq = make_idesc(false, true, kBM, kD);     // A = dS from TMEM, B = K as [key, head dim]
       auto issue_nt = [&](uint32_t d_col, uint32_t a_smem, uint32_t b_smem) {
+        if (p.debug & 2) return;
 #pragma unroll
         for (int k = 0; k < kD / 16; ++k) {
           const uint32_t off = (uint32_t)(k >> 2) * kHalfBytes + (uint32_t)(k & 3) * 32u;
@@ -762,9 +767,10 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
         }
         if (!mbar_wait(bar(DS_READY), i & 1u, abort_flag)) { ok = false; break; }
         tc_fence_after();
+        if (!(p.debug & 2))
 #pragma unroll
         for (int ks = 0; ks < kBN / 16; ++ks) {
-          const uint32_t a_col = (uint32_t)(ks >> 2) * 64u + (uint32_t)(ks & 3) * 8u;
+          const uint32_t a_col = (uint32_t)(ks >> 1) * 32u + (uint32_t)(ks & 1) * 8u;
           umma_bf16_ts(tmem_base + T_DQ, tmem_base + T_S + a_col,
                        make_desc(k_smem + st * kTileBytes + ks * 2048, kHalfBytes, 1024), idesc_dq,
                        (i > 0 || ks > 0) ? 1u : 0u);
@@ -782,13 +788,13 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
     }
   } else {
     const int quarter = warp & 3;
-    const int half = (warp - 2) >> 2;
+    const int grp = (warp - 2) >> 2;               // 32 of the 128 keys of a block
     const int row_in_tile = quarter * 32 + lane;
     const int row = q0 + row_in_tile;
     const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
     const bool row_ok = row < p.Tq;
     const float l2 = row_ok ? p.lse[(int64_t)head * p.stat_stride + row] * 1.4426950408889634f : INFINITY;
-    const float dl = row_ok ? p.delta[(int64_t)head * p.stat_stride + row] : 0.f;
+    const float dl = (row_ok ? p.delta[(int64_t)head * p.stat_stride + row] : 0.f) * p.scale;
     const int lo = p.kv_first != nullptr ? p.kv_first[min(row, p.Tq - 1)] : 0;
     const int hi = min(p.Tk - 1, p.causal ? row + p.causal_offset : p.Tk - 1);
     bool ok = true;
@@ -798,72 +804,62 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
         break;
       }
       tc_fence_after();
-      const int c0 = (j_lo + i) * kBN + half * 64;
-      const bool edge = (c0 + 63 > hi) || (c0 < lo);
-      uint32_t out[32];
+      if (p.debug & 1) { tc_fence_before(); __syncwarp(); if (lane == 0) mbar_arrive(bar(DS_READY)); continue; }
+      const int c0 = (j_lo + i) * kBN + grp * 32;
+      const bool edge = (c0 + 31 > hi) || (c0 < lo);
+      uint32_t sv[32], dv[32], out[16];
+      tmem_ld32(tmem_base + lane_addr + T_S + grp * 32, sv);
+      tmem_ld32(tmem_base + lane_addr + T_DP + (i & 1) * 128 + grp * 32, dv);
+      tmem_ld_wait();
 #pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        uint32_t sv[32], dv[32];
-        tmem_ld32(tmem_base + lane_addr + T_S + half * 64 + c * 32, sv);
-        tmem_ld32(tmem_base + lane_addr + T_DP + (i & 1) * 128 + half * 64 + c * 32, dv);
-        tmem_ld_wait();
+      for (int e = 0; e < 16; ++e) {
+        float ds2[2];
 #pragma unroll
-        for (int e = 0; e < 16; ++e) {
-          float ds2[2];
-#pragma unroll
-          for (int u = 0; u < 2; ++u) {
-            const int idx = 2 * e + u;
-            float pe = exp2f(fmaf(__uint_as_float(sv[idx]), p.scale_log2, -l2));
-            if (edge) {
-              const int col = c0 + c * 32 + idx;
-              if (col > hi || col < lo) pe = 0.f;
-            }
-            ds2[u] = pe * (__uint_as_float(dv[idx]) - dl) * p.scale;
+        for (int u = 0; u < 2; ++u) {
+          const int idx = 2 * e + u;
+          float pe = exp2f(fmaf(__uint_as_float(sv[idx]), p.scale_log2, -l2));
+          if (edge) {
+            const int col = c0 + idx;
+            if (col > hi || col < lo) pe = 0.f;
           }
-          out[c * 16 + e] = pack_bf16(ds2[0], ds2[1]);
+          ds2[u] = pe * fmaf(__uint_as_float(dv[idx]), p.scale, -dl);
         }
+        out[e] = pack_bf16(ds2[0], ds2[1]);
       }
-      // all S columns of this thread are in registers: the packed dS may now overwrite them
-      {
-        uint32_t a[16], b[16];
-#pragma unroll
-        for (int e = 0; e < 16; ++e) { a[e] = out[e]; b[e] = out[16 + e]; }
-        tmem_st16(tmem_base + lane_addr + T_S + half * 64, a);
-        tmem_st16(tmem_base + lane_addr + T_S + half * 64 + 16, b);
-      }
+      // this thread's S columns are in registers: the packed dS overwrites the first half of them
+      tmem_st16(tmem_base + lane_addr + T_S + grp * 32, out);
       tmem_st_wait();
       tc_fence_before();
-      mbar_arrive(bar(DS_READY));
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(DS_READY));
     }
     if (ok && n_tiles > 0) ok = mbar_wait(bar(DQ_FULL), 0, abort_flag);
     if (ok) {
       tc_fence_after();
-      // dQ -> bf16 -> swizzled staging (the Q tile) -> TMA store; thread = (row, 64-column half)
-      const uint32_t stage = q_smem + half * kHalfBytes;
-#pragma unroll 1
-      for (int c = 0; c < 2; ++c) {
-        uint32_t o[32];
-        if (n_tiles > 0) {
-          tmem_ld32(tmem_base + lane_addr + T_DQ + half * 64 + c * 32, o);
-          tmem_ld_wait();
-        } else {
+      // dQ -> bf16 -> swizzled staging (the Q tile) -> TMA store; thread = (row, 32 head-dim columns)
+      const uint32_t stage = q_smem + (grp >> 1) * kHalfBytes;
+      uint32_t o[32];
+      if (n_tiles > 0) {
+        tmem_ld32(tmem_base + lane_addr + T_DQ + grp * 32, o);
+        tmem_ld_wait();
+      } else {
 #pragma unroll
-          for (int e = 0; e < 32; ++e) o[e] = 0u;
-        }
+        for (int e = 0; e < 32; ++e) o[e] = 0u;
+      }
 #pragma unroll
-        for (int jj = 0; jj < 4; ++jj) {
-          uint32_t w[4];
+      for (int jj = 0; jj < 4; ++jj) {
+        uint32_t w[4];
 #pragma unroll
-          for (int e = 0; e < 4; ++e)
-            w[e] = pack_bf16(__uint_as_float(o[jj * 8 + 2 * e]), __uint_as_float(o[jj * 8 + 2 * e + 1]));
-          const int chunk = c * 4 + jj;
-          const uint32_t dst = stage + (uint32_t)row_in_tile * 128u + (uint32_t)((chunk ^ (row_in_tile & 7)) << 4);
-          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3])
-                       : "memory");
-        }
+        for (int e = 0; e < 4; ++e)
+          w[e] = pack_bf16(__uint_as_float(o[jj * 8 + 2 * e]), __uint_as_float(o[jj * 8 + 2 * e + 1]));
+        const int chunk = (grp & 1) * 4 + jj;
+        const uint32_t dst = stage + (uint32_t)row_in_tile * 128u + (uint32_t)((chunk ^ (row_in_tile & 7)) << 4);
+        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3])
+                     : "memory");
       }
       fence_proxy_async_smem();
-      mbar_arrive(bar(OUT_STAGED));
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(OUT_STAGED));
       if (warp == 2 && lane == 0 && mbar_wait(bar(OUT_STAGED), 0, abort_flag)) {
         for (int h = 0; h < 2; ++h) tma_store_3d(&tmap_dq, q_smem + h * kHalfBytes, h * 64, head, q0);
         tma_store_commit();
@@ -919,6 +915,9 @@ static CUtensorMap make_tmap_thd(const at::Tensor& t, uint32_t rows) {
   return map;
 }
 
+static int g_flash_debug = 0;
+void flash_set_debug(int64_t v) { g_flash_debug = (int)v; }
+
 static at::Tensor& flash_status_tensor(const at::Device& dev) {
   static std::vector<at::Tensor> per_device(64);
   auto& t = per_device[dev.index()];
@@ -962,6 +961,7 @@ std::tuple<at::Tensor, at::Tensor> flash_fwd(const at::Tensor& q, const at::Tens
   }
   p.lse = lse.data_ptr<float>();
   p.lse_stride = (int)Tpad;
+  p.debug = g_flash_debug;
   p.status = flash_status_tensor(q.device()).data_ptr<int>();
   const CUtensorMap tq = make_tmap_thd(q, kBM), tk = make_tmap_thd(k, kBN), tv = make_tmap_thd(v, kBN),
                     to = make_tmap_thd(o, kBM);
@@ -1036,6 +1036,7 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor> flash_bwd(const at::Tensor& d_o, 
   p.lse = lse_p.data_ptr<float>();
   p.delta = delta.data_ptr<float>();
   p.stat_stride = (int)Tpad;
+  p.debug = g_flash_debug;
   p.status = flash_status_tensor(q.device()).data_ptr<int>();
   {
     const CUtensorMap tq = make_tmap_thd(q, kBQ), tdo = make_tmap_thd(d_o, kBQ), tk = make_tmap_thd(k, kBN),
