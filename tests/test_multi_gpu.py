@@ -239,3 +239,70 @@ def test_tensor_parallel_fused_matches_nccl(tmp_path):
     run_distributed(_train_tp, 2, "nvlink", b, backend="nccl")
     ra, rb = torch.load(a), torch.load(b)
     assert torch.allclose(ra["losses"], rb["losses"], atol=3e-2), (ra["losses"], rb["losses"])
+
+
+def _ep_nvlink(rank, world, out_path):
+    """Expert parallelism: NVLink scatter / gather kernels against the NCCL all-to-all dispatcher."""
+    import copy
+
+    import torch.distributed as dist
+
+    from torchtitan_b200.models.common.moe import MoE, TokenChoiceTopKRouter
+    from torchtitan_b200.parallel.ep_nvlink import EPNvlink
+    from torchtitan_b200.parallel.expert_parallel import EPContext
+
+    dev = torch.device("cuda", rank)
+    E, K, dim, hidden, T = 8, 2, 256, 384, 600
+    cfg = MoE.Config(dim=dim, hidden_dim=hidden, num_experts=E, top_k=K,
+                     router=TokenChoiceTopKRouter.Config(score_func="softmax", route_norm=True))
+    base = cfg.build()
+    base.init_states(seed=5)
+    n = E // world
+
+    def make(comm):
+        m = copy.deepcopy(base)
+        ie = m.routed_experts.inner_experts
+        for name in ("w1_EFD", "w2_EDF", "w3_EFD"):
+            setattr(ie, name, torch.nn.Parameter(getattr(ie, name).detach()[rank * n:(rank + 1) * n].clone()))
+        ie.num_experts = n
+        m = m.to(dev).bfloat16()
+        m.expert_bias_E = m.expert_bias_E.float()
+        m.tokens_per_expert_E = m.tokens_per_expert_E.float()
+        ep = EPContext(group=dist.group.WORLD, size=world, rank=rank, comm=comm)
+        if comm == "nvlink":
+            ep.nvlink = EPNvlink(dist.group.WORLD, dev, world * T * K + n * 128, dim)
+        m.routed_experts.ep = ep
+        return m
+
+    res = []
+    models = {comm: make(comm) for comm in ("nccl", "nvlink")}
+    for it in range(2):   # two rounds: the symmetric buffers are reused
+        g = torch.Generator(device=dev).manual_seed(50 + 7 * it + rank)
+        x = (torch.randn(T, dim, device=dev, generator=g) * 0.5).bfloat16()
+        dy = (torch.randn(T, dim, device=dev, generator=g) * 0.1).bfloat16()
+        outs = {}
+        for comm in ("nccl", "nvlink"):
+            m = models[comm]
+            m.zero_grad()
+            xi = x.clone().requires_grad_()
+            y = m(xi)
+            y.backward(dy)
+            outs[comm] = (y.detach().float(), xi.grad.float(), m.routed_experts.inner_experts.w1_EFD.grad.float(),
+                          m.router.gate.weight.grad.float())
+        for a, b in zip(outs["nccl"], outs["nvlink"]):
+            res.append((a - b).abs().max().item() / (a.abs().max().item() + 1e-6))
+    torch.cuda.synchronize()
+    st = int(models["nvlink"].routed_experts.ep.nvlink.arena.status.item()) | int(torch.ops.tb200.gemm_status(True))
+    t = torch.tensor(res + [float(st)], device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    if rank == 0:
+        torch.save(t.cpu(), out_path)
+
+
+@pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
+def test_expert_parallel_nvlink_matches_nccl(tmp_path):
+    out = str(tmp_path / "ep.pt")
+    run_distributed(_ep_nvlink, 2, out, backend="nccl")
+    r = torch.load(out)
+    assert r[-1] == 0, "a bounded wait expired"
+    assert (r[:-1] < 3e-2).all(), r

@@ -87,6 +87,10 @@ class ParallelismConfig:
     """Symmetric memory reserved per tensor-parallel group for gather / staging buffers."""
     cp_comm: Literal["allgather", "ring"] = "allgather"
     ep_comm: Literal["nccl", "nvlink"] = "nccl"
+    """``nvlink``: token dispatch / combine as in-kernel peer stores / loads over symmetric memory."""
+    ep_capacity_factor: float = 0.0
+    """Rows of the nvlink receive buffer = factor * tokens * top_k (0 = the worst case, ep degree)."""
+    _tokens_per_rank: int = 0
 
 
 @dataclass(kw_only=True, slots=True)

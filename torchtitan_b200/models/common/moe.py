@@ -209,6 +209,11 @@ class RoutedExperts(Module):
             xp = moe_ops.permute_rows(x, dest, cap)
             yp = self.inner_experts.forward_padded(xp, offs)
             return moe_ops.combine_rows(yp, dest, top_scores)
+        nv = getattr(self.ep, "nvlink", None) if self.ep is not None else None
+        if nv is not None and self.inner_experts.native_ok(x):
+            from torchtitan_b200.parallel.ep_nvlink import ep_experts_nvlink
+
+            return ep_experts_nvlink(nv, self.inner_experts, x, top_scores, selected, counts)
         flat = selected.reshape(-1).long()
         order = torch.argsort(flat, stable=True)  # slots sorted expert-major
         token_idx = order // K

@@ -53,6 +53,13 @@ at::Tensor moe_permute_rows(const at::Tensor& x, const at::Tensor& dest, int64_t
 at::Tensor moe_combine_rows(const at::Tensor& y, const at::Tensor& dest, const c10::optional<at::Tensor>& wts);
 std::tuple<at::Tensor, at::Tensor> moe_combine_bwd(const at::Tensor& dout, const at::Tensor& y, const at::Tensor& dest,
                                                    const at::Tensor& wts);
+void ep_scatter_rows(const at::Tensor& x, const at::Tensor& dest_rank, const at::Tensor& dest_row,
+                     const c10::optional<at::Tensor>& wts, at::IntArrayRef peer_ptrs);
+std::tuple<at::Tensor, at::Tensor> ep_gather_rows(at::IntArrayRef peer_ptrs, const at::Tensor& dest_rank,
+                                                  const at::Tensor& dest_row, const c10::optional<at::Tensor>& wts,
+                                                  int64_t D, bool keep_rows, const at::Tensor& like);
+void moe_zero_pad_rows(at::Tensor buf, const at::Tensor& offs, const at::Tensor& counts);
+at::Tensor moe_slot_dot(const at::Tensor& dout, const at::Tensor& rows, int64_t K);
 std::tuple<at::Tensor, at::Tensor> mxfp8_quantize(const at::Tensor& x, int64_t axis);
 at::Tensor mxfp8_fake_quant(const at::Tensor& x, int64_t axis);
 at::Tensor mxfp8_dequantize(const at::Tensor& data, const at::Tensor& scales, int64_t axis);
@@ -89,6 +96,11 @@ TORCH_LIBRARY(tb200, m) {
         "(Tensor, Tensor, Tensor)", &tb200::flash_bwd);
   m.def("flash_status(bool clear) -> int", &tb200::flash_status);
   m.def("flash_set_debug(int v) -> ()", &tb200::flash_set_debug);
+  m.def("ep_scatter_rows(Tensor x, Tensor dest_rank, Tensor dest_row, Tensor? wts, int[] peer_ptrs) -> ()", &tb200::ep_scatter_rows);
+  m.def("ep_gather_rows(int[] peer_ptrs, Tensor dest_rank, Tensor dest_row, Tensor? wts, int D, bool keep_rows, Tensor like) -> "
+        "(Tensor, Tensor)", &tb200::ep_gather_rows);
+  m.def("moe_zero_pad_rows(Tensor(a!) buf, Tensor offs, Tensor counts) -> ()", &tb200::moe_zero_pad_rows);
+  m.def("moe_slot_dot(Tensor dout, Tensor rows, int K) -> Tensor", &tb200::moe_slot_dot);
   m.def("mxfp8_quantize(Tensor x, int axis) -> (Tensor, Tensor)", &tb200::mxfp8_quantize);
   m.def("mxfp8_fake_quant(Tensor x, int axis) -> Tensor", &tb200::mxfp8_fake_quant);
   m.def("mxfp8_dequantize(Tensor data, Tensor scales, int axis) -> Tensor", &tb200::mxfp8_dequantize);

@@ -343,3 +343,188 @@ std::tuple<at::Tensor, at::Tensor> moe_combine_bwd(const at::Tensor& dout, const
 }
 
 }  // namespace tb200
+
+// =============================================================================================
+// Expert-parallel exchange over NVLink symmetric memory (no NCCL all-to-all on the data path).
+// Every rank knows, for each of its routing slots, the rank that hosts the chosen expert and the
+// row of that rank's receive buffer (padded expert-major layout) reserved for the slot.
+//   ep_scatter_rows: out_peer[dest_rank][dest_row] = (w *) x[token]       P2P stores, warp per slot
+//   ep_gather_rows : out[token] = sum_k (w *) y_peer[dest_rank][dest_row]  P2P loads, warp per token;
+//                    optionally keeps the gathered rows (needed for the gate-score gradient)
+//   zero_pad_rows  : rows between the end of an expert's tokens and the next 128-row boundary
+//   slot_dot       : dw[t, k] = <dout[t], rows[t, k]>
+// Peer memory is touched with plain 16-byte loads / stores only.
+namespace tb200 {
+
+constexpr int kEpMaxPeers = 16;
+struct EpPeers {
+  __nv_bfloat16* p[kEpMaxPeers];
+};
+
+static EpPeers make_ep_peers(at::IntArrayRef ptrs) {
+  TORCH_CHECK(ptrs.size() >= 1 && (int)ptrs.size() <= kEpMaxPeers, "ep: 1..", kEpMaxPeers, " ranks supported");
+  EpPeers pp;
+  for (int i = 0; i < kEpMaxPeers; ++i) pp.p[i] = nullptr;
+  for (size_t i = 0; i < ptrs.size(); ++i) pp.p[i] = reinterpret_cast<__nv_bfloat16*>(static_cast<uintptr_t>(ptrs[i]));
+  return pp;
+}
+
+__global__ void ep_scatter_rows_kernel(const __nv_bfloat16* __restrict__ x, const int* __restrict__ dest_rank,
+                                       const int* __restrict__ dest_row, const float* __restrict__ wts, EpPeers out,
+                                       int64_t slots, int K, int D) {
+  const int64_t s = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (s >= slots) return;
+  const int row = dest_row[s];
+  if (row < 0) return;
+  const bf16x8* src = reinterpret_cast<const bf16x8*>(x + (s / K) * D);
+  bf16x8* dst = reinterpret_cast<bf16x8*>(out.p[dest_rank[s]] + (int64_t)row * D);
+  if (wts == nullptr) {
+    for (int i = lane; i < D / 8; i += 32) dst[i] = src[i];
+  } else {
+    const float w = wts[s];
+    for (int i = lane; i < D / 8; i += 32) {
+      float v[8];
+      unpack8(src[i], v);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[j] *= w;
+      dst[i] = pack8(v);
+    }
+  }
+}
+
+template <bool kWeighted>
+__global__ void ep_gather_rows_kernel(EpPeers y, const int* __restrict__ dest_rank, const int* __restrict__ dest_row,
+                                      const float* __restrict__ wts, __nv_bfloat16* __restrict__ out,
+                                      __nv_bfloat16* __restrict__ keep, int64_t T, int K, int D) {
+  const int64_t t = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (t >= T) return;
+  for (int i = lane; i < D / 8; i += 32) {
+    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    for (int k = 0; k < K; ++k) {
+      const int row = dest_row[t * K + k];
+      if (row < 0) continue;
+      const bf16x8 raw = reinterpret_cast<const bf16x8*>(y.p[dest_rank[t * K + k]] + (int64_t)row * D)[i];
+      if (keep != nullptr) reinterpret_cast<bf16x8*>(keep + (t * K + k) * D)[i] = raw;
+      float v[8];
+      unpack8(raw, v);
+      const float w = kWeighted ? wts[t * K + k] : 1.f;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] += w * v[j];
+    }
+    reinterpret_cast<bf16x8*>(out + t * D)[i] = pack8(acc);
+  }
+}
+
+__global__ void zero_pad_rows_kernel(__nv_bfloat16* __restrict__ buf, const int* __restrict__ offs,
+                                     const int* __restrict__ counts, int D) {
+  const int e = blockIdx.x;
+  const int first = offs[e] + counts[e], last = offs[e + 1];
+  const int n_vec = D / 8;
+  const bf16x8 zero = {};
+  for (int64_t i = threadIdx.x; i < (int64_t)(last - first) * n_vec; i += blockDim.x)
+    reinterpret_cast<bf16x8*>(buf + (int64_t)first * D)[i] = zero;
+}
+
+__global__ void slot_dot_kernel(const __nv_bfloat16* __restrict__ dout, const __nv_bfloat16* __restrict__ rows,
+                                float* __restrict__ dw, int64_t slots, int K, int D) {
+  const int64_t s = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (s >= slots) return;
+  const bf16x8* g = reinterpret_cast<const bf16x8*>(dout + (s / K) * D);
+  const bf16x8* r = reinterpret_cast<const bf16x8*>(rows + s * D);
+  float dot = 0.f;
+  for (int i = lane; i < D / 8; i += 32) {
+    float a[8], b[8];
+    unpack8(g[i], a);
+    unpack8(r[i], b);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) dot += a[j] * b[j];
+  }
+  dot = warp_sum(dot);
+  if (lane == 0) dw[s] = dot;
+}
+
+static void check_slots(const at::Tensor& dest_rank, const at::Tensor& dest_row) {
+  TORCH_CHECK(dest_rank.is_cuda() && dest_rank.scalar_type() == at::kInt && dest_rank.is_contiguous() && dest_rank.dim() == 2);
+  TORCH_CHECK(dest_row.is_cuda() && dest_row.scalar_type() == at::kInt && dest_row.is_contiguous() &&
+              dest_row.sizes() == dest_rank.sizes());
+}
+
+void ep_scatter_rows(const at::Tensor& x, const at::Tensor& dest_rank, const at::Tensor& dest_row,
+                     const c10::optional<at::Tensor>& wts, at::IntArrayRef peer_ptrs) {
+  check_rows(x, "x");
+  check_slots(dest_rank, dest_row);
+  TORCH_CHECK(dest_rank.size(0) == x.size(0));
+  c10::cuda::CUDAGuard guard(x.device());
+  const int64_t slots = dest_rank.numel();
+  if (slots == 0) return;
+  const float* wp = nullptr;
+  if (wts.has_value() && wts->defined()) {
+    TORCH_CHECK(wts->is_cuda() && wts->scalar_type() == at::kFloat && wts->is_contiguous() && wts->numel() == slots);
+    wp = wts->data_ptr<float>();
+  }
+  const int threads = 256;
+  ep_scatter_rows_kernel<<<(unsigned)((slots * 32 + threads - 1) / threads), threads, 0, at::cuda::getCurrentCUDAStream()>>>(
+      reinterpret_cast<const __nv_bfloat16*>(x.data_ptr()), dest_rank.data_ptr<int>(), dest_row.data_ptr<int>(), wp,
+      make_ep_peers(peer_ptrs), slots, (int)dest_rank.size(1), (int)x.size(1));
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+}
+
+std::tuple<at::Tensor, at::Tensor> ep_gather_rows(at::IntArrayRef peer_ptrs, const at::Tensor& dest_rank,
+                                                  const at::Tensor& dest_row, const c10::optional<at::Tensor>& wts,
+                                                  int64_t D, bool keep_rows, const at::Tensor& like) {
+  check_slots(dest_rank, dest_row);
+  TORCH_CHECK(D % 8 == 0 && like.is_cuda() && like.scalar_type() == at::kBFloat16);
+  c10::cuda::CUDAGuard guard(like.device());
+  const int64_t T = dest_rank.size(0);
+  const int K = (int)dest_rank.size(1);
+  auto out = at::empty({T, D}, like.options());
+  auto keep = keep_rows ? at::empty({T * K, D}, like.options()) : at::empty({0}, like.options());
+  if (T == 0) return {out, keep};
+  const int threads = 256;
+  const unsigned blocks = (unsigned)((T * 32 + threads - 1) / threads);
+  auto stream = at::cuda::getCurrentCUDAStream();
+  auto kp = keep_rows ? reinterpret_cast<__nv_bfloat16*>(keep.data_ptr()) : nullptr;
+  auto op = reinterpret_cast<__nv_bfloat16*>(out.data_ptr());
+  const EpPeers pp = make_ep_peers(peer_ptrs);
+  if (wts.has_value() && wts->defined()) {
+    TORCH_CHECK(wts->is_cuda() && wts->scalar_type() == at::kFloat && wts->is_contiguous() && wts->numel() == T * K);
+    ep_gather_rows_kernel<true><<<blocks, threads, 0, stream>>>(pp, dest_rank.data_ptr<int>(), dest_row.data_ptr<int>(),
+                                                                 wts->data_ptr<float>(), op, kp, T, K, (int)D);
+  } else {
+    ep_gather_rows_kernel<false><<<blocks, threads, 0, stream>>>(pp, dest_rank.data_ptr<int>(), dest_row.data_ptr<int>(),
+                                                                  nullptr, op, kp, T, K, (int)D);
+  }
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+  return {out, keep};
+}
+
+void moe_zero_pad_rows(at::Tensor buf, const at::Tensor& offs, const at::Tensor& counts) {
+  check_rows(buf, "buf");
+  TORCH_CHECK(offs.scalar_type() == at::kInt && counts.scalar_type() == at::kInt && offs.numel() == counts.numel() + 1 &&
+              offs.is_contiguous() && counts.is_contiguous());
+  c10::cuda::CUDAGuard guard(buf.device());
+  if (counts.numel() == 0) return;
+  zero_pad_rows_kernel<<<(unsigned)counts.numel(), 256, 0, at::cuda::getCurrentCUDAStream()>>>(
+      reinterpret_cast<__nv_bfloat16*>(buf.data_ptr()), offs.data_ptr<int>(), counts.data_ptr<int>(), (int)buf.size(1));
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+}
+
+at::Tensor moe_slot_dot(const at::Tensor& dout, const at::Tensor& rows, int64_t K) {
+  check_rows(dout, "dout");
+  check_rows(rows, "rows");
+  TORCH_CHECK(rows.size(0) == dout.size(0) * K && rows.size(1) == dout.size(1));
+  c10::cuda::CUDAGuard guard(dout.device());
+  auto dw = at::empty({dout.size(0), K}, dout.options().dtype(at::kFloat));
+  const int64_t slots = rows.size(0);
+  if (slots > 0)
+    slot_dot_kernel<<<(unsigned)((slots * 32 + 255) / 256), 256, 0, at::cuda::getCurrentCUDAStream()>>>(
+        reinterpret_cast<const __nv_bfloat16*>(dout.data_ptr()), reinterpret_cast<const __nv_bfloat16*>(rows.data_ptr()),
+        dw.data_ptr<float>(), slots, (int)K, (int)dout.size(1));
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+  return dw;
+}
+
+}  // namespace tb200

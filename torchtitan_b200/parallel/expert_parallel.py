@@ -28,10 +28,24 @@ class EPContext:
     size: int
     rank: int
     comm: str = "nccl"
+    nvlink: object | None = None  # parallel.ep_nvlink.EPNvlink when comm == "nvlink" on CUDA
 
 
 def apply_expert_parallel(model, pdims, parallelism) -> None:
     ep = EPContext(group=pdims.group("ep"), size=pdims.ep, rank=pdims.local_rank("ep"), comm=parallelism.ep_comm)
+    if ep.comm == "nvlink" and torch.cuda.is_available():
+        from .symm import symm_available
+
+        if symm_available():
+            from .ep_nvlink import EPNvlink
+
+            moes = [blk.moe for blk in model.layers.values() if blk.moe is not None]
+            if moes:
+                t = getattr(parallelism, "_tokens_per_rank", 0) or 8192
+                k, e_local = moes[0].config.top_k, moes[0].num_experts // ep.size
+                factor = parallelism.ep_capacity_factor or float(ep.size)
+                cap = int(factor * t * k) + e_local * 128
+                ep.nvlink = EPNvlink(ep.group, torch.device("cuda", torch.cuda.current_device()), cap, moes[0].config.dim)
     for blk in model.layers.values():
         if blk.moe is not None:
             blk.moe.routed_experts.ep = ep

@@ -72,6 +72,7 @@ def parallelize_decoder(model: nn.Module, *, pdims, job_config, device: torch.de
     if pdims.ep_enabled:
         from .expert_parallel import apply_expert_parallel
 
+        par._tokens_per_rank = tr.num_tokens_per_microbatch_per_dp_rank // max(1, pdims.tp * pdims.cp)
         apply_expert_parallel(model, pdims, par)
     tp = apply_tensor_parallel(model, pdims, par)
 
