@@ -97,6 +97,12 @@ def _prefix_attention(q, k, v, n_prefix: int, scale: float):
     bottom-right aligned causal mask."""
     Tq = q.shape[0]
     kk, vv = k[:n_prefix], v[:n_prefix]
+    if OF._native_attention_ok(q, kk, vv):
+        # tcgen05 flash kernel: query row i sees keys j <= i + (n_prefix - Tq)
+        from torchtitan_b200.ops.flash import flash_attention
+
+        OF._count(4)
+        return flash_attention(q, kk, vv, scale, causal=True, causal_offset=n_prefix - Tq)
     if q.is_cuda:
         from torch.nn.attention.bias import causal_lower_right
 
