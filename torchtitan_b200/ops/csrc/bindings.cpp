@@ -62,6 +62,8 @@ void moe_zero_pad_rows(at::Tensor buf, const at::Tensor& offs, const at::Tensor&
 at::Tensor moe_slot_dot(const at::Tensor& dout, const at::Tensor& rows, int64_t K);
 std::tuple<at::Tensor, at::Tensor> mxfp8_quantize(const at::Tensor& x, int64_t axis);
 at::Tensor mxfp8_fake_quant(const at::Tensor& x, int64_t axis);
+std::tuple<at::Tensor, at::Tensor> mxfp8_quantize_tiled(const at::Tensor& x);
+at::Tensor gemm_mxfp8(const at::Tensor& a, const at::Tensor& sfa, const at::Tensor& b, const at::Tensor& sfb);
 at::Tensor mxfp8_dequantize(const at::Tensor& data, const at::Tensor& scales, int64_t axis);
 std::tuple<at::Tensor, at::Tensor> float8_rowwise_quantize(const at::Tensor& x);
 at::Tensor float8_rowwise_fake_quant(const at::Tensor& x);
@@ -103,6 +105,8 @@ TORCH_LIBRARY(tb200, m) {
   m.def("moe_slot_dot(Tensor dout, Tensor rows, int K) -> Tensor", &tb200::moe_slot_dot);
   m.def("mxfp8_quantize(Tensor x, int axis) -> (Tensor, Tensor)", &tb200::mxfp8_quantize);
   m.def("mxfp8_fake_quant(Tensor x, int axis) -> Tensor", &tb200::mxfp8_fake_quant);
+  m.def("mxfp8_quantize_tiled(Tensor x) -> (Tensor, Tensor)", &tb200::mxfp8_quantize_tiled);
+  m.def("gemm_mxfp8(Tensor a, Tensor sfa, Tensor b, Tensor sfb) -> Tensor", &tb200::gemm_mxfp8);
   m.def("mxfp8_dequantize(Tensor data, Tensor scales, int axis) -> Tensor", &tb200::mxfp8_dequantize);
   m.def("float8_rowwise_quantize(Tensor x) -> (Tensor, Tensor)", &tb200::float8_rowwise_quantize);
   m.def("float8_rowwise_fake_quant(Tensor x) -> Tensor", &tb200::float8_rowwise_fake_quant);

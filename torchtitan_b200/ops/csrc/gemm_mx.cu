@@ -1,0 +1,291 @@
+// MXFP8 block-scaled GEMM: C[M,N] (bf16) = (A . diag-block scales) (B . scales)^T with e4m3 elements and
+// one e8m0 scale per 32 K-elements, on tcgen05.mma.kind::mxf8f6f4.block_scale.
+//
+// A [M, K] and B [N, K] are K-major e4m3 bytes.  Scale factors come in the tiled layout the tensor
+// core consumes: for every tile of 128 rows x 128 K-elements (4 scale blocks) one 512-byte atom,
+// atoms ordered row-tile major; inside an atom the scale of (row r, block b) sits at byte
+// (r % 32) * 16 + (r / 32) * 4 + b.  One atom is a 32-row x 16-byte matrix that tcgen05.cp copies
+// into tensor memory, replicated into the four 32-lane quarters ("32x128b.warpx4"); the MMA of a
+// lane quarter then finds its rows' scales in its own copy.
+//
+// Kernel shape: one CTA per 128 x 128 tile (persistent), K step 128 (four MMAs of K = 32 per stage,
+// which select scale byte 0..3 of the staged atom through the instruction descriptor), 5-stage TMA
+// pipeline (A 16 KB + B 16 KB + scales 1 KB per stage), two TMEM accumulators of 128 columns and
+// 8 columns of scale factors per stage.  Roles and the bounded waits are those of the bf16 GEMM.
+#include <ATen/ATen.h>
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <cuda.h>
+
+#include "common.cuh"
+#include "tc.cuh"
+
+namespace tb200 {
+namespace gemm_mx {
+
+using namespace tc;
+
+constexpr int BM = 128, BN = 128, BK = 128;      // BK in elements = bytes
+constexpr int kStages = 5;
+constexpr int kThreads = 192;
+constexpr uint32_t kABytes = BM * BK, kBBytes = BN * BK, kSfBytes = 512;
+constexpr uint32_t kStageBytes = kABytes + kBBytes + 2 * kSfBytes;     // 33 KB
+constexpr uint32_t kEpiBytes = 4 * 2 * 4096;
+constexpr uint32_t kSmemBytes = kStages * kStageBytes + kEpiBytes + 1024 + 256;
+constexpr uint32_t kAccCols = 2 * BN;            // two accumulators
+constexpr uint32_t kSfColBase = kAccCols;        // 8 scale columns per stage behind the accumulators
+
+struct Params {
+  int M, N, K;
+  const uint8_t* sfa;     // tiled scales of A: [ceil(M/128)][K/128][512]
+  const uint8_t* sfb;     // tiled scales of B
+  int* status;
+};
+
+// Instruction descriptor of the block-scaled kinds: e4m3 x e4m3, ue8m0 scales, fp32 accumulate.
+__host__ __device__ constexpr uint32_t make_idesc_mx(int m, int n, uint32_t a_sf_id, uint32_t b_sf_id) {
+  return (b_sf_id << 4) | (0u << 7) | (0u << 10) | (0u << 15) | (0u << 16) | ((uint32_t)(n >> 3) << 17) | (1u << 23) |
+         ((uint32_t)(m >> 4) << 24) | (a_sf_id << 29);
+}
+
+// Shared-memory descriptor of a 32-row x 16-byte scale atom (no swizzle: 8-row groups 128 B apart).
+__device__ __forceinline__ uint64_t make_sf_desc(uint32_t saddr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((saddr & 0x3FFFFu) >> 4);
+  d |= (uint64_t)((16u >> 4) & 0x3FFFu) << 16;
+  d |= (uint64_t)((128u >> 4) & 0x3FFFu) << 32;
+  d |= (uint64_t)1 << 46;
+  return d;
+}
+
+__device__ __forceinline__ void tmem_cp_sf(uint32_t taddr, uint64_t sdesc) {
+  asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
+}
+
+__device__ __forceinline__ void umma_mxf8(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t sfa,
+                                          uint32_t sfb, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %6, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale.scale_vec::1X [%0], %1, %2, %3, [%4], [%5], p;\n\t}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(sfa), "r"(sfb), "r"(accumulate)
+      : "memory");
+}
+
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                  const __grid_constant__ CUtensorMap tmap_c, const Params p) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  uint8_t* gen_base = smem_raw + (base - raw);
+  const uint32_t epi_base = base + kStages * kStageBytes;
+  const uint32_t bar_base = epi_base + kEpiBytes;
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (kStages + s); };
+  auto tfull_bar = [&](int a) { return bar_base + 8u * (2 * kStages + a); };
+  auto tempty_bar = [&](int a) { return bar_base + 8u * (2 * kStages + 2 + a); };
+  uint32_t* tmem_ptr_smem = reinterpret_cast<uint32_t*>(gen_base + kStages * kStageBytes + kEpiBytes + 8 * (2 * kStages + 4));
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_ptr_smem + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int num_m = (p.M + BM - 1) / BM, num_n = (p.N + BN - 1) / BN;
+  const int num_tiles = num_m * num_n;
+  const int num_kb = (p.K + BK - 1) / BK;
+  constexpr int kGroupM = 16;
+  auto tile_coord = [&](int t, int& tm, int& tn) {
+    const int per_group = kGroupM * num_n;
+    const int g = t / per_group;
+    const int first = g * kGroupM;
+    const int gsz = min(kGroupM, num_m - first);
+    const int r = t - g * per_group;
+    tm = first + r % gsz;
+    tn = r / gsz;
+  };
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(tfull_bar(a), 1);
+      mbar_init(tempty_bar(a), 4);
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&tmap_a);
+    tma_prefetch_desc(&tmap_b);
+    tma_prefetch_desc(&tmap_c);
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(tmem_ptr_smem), 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_ptr_smem;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      uint32_t it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        int tm, tn;
+        tile_coord(tile, tm, tn);
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % kStages;
+          if (!mbar_wait(empty_bar(s), ((it / kStages) & 1u) ^ 1u, abort_flag)) { ok = false; break; }
+          const uint32_t sa = base + s * kStageBytes, sb = sa + kABytes, ssf = sb + kBBytes;
+          mbar_expect_tx(full_bar(s), kStageBytes);
+          tma_load_2d(sa, &tmap_a, full_bar(s), kb * BK, tm * BM);
+          tma_load_2d(sb, &tmap_b, full_bar(s), kb * BK, tn * BN);
+          bulk_load(ssf, p.sfa + ((int64_t)tm * num_kb + kb) * kSfBytes, kSfBytes, full_bar(s));
+          bulk_load(ssf + kSfBytes, p.sfb + ((int64_t)tn * num_kb + kb) * kSfBytes, kSfBytes, full_bar(s));
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      uint32_t it = 0, tcount = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++tcount) {
+        const int acc = tcount & 1;
+        if (!mbar_wait(tempty_bar(acc), ((tcount >> 1) & 1u) ^ 1u, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % kStages;
+          if (!mbar_wait(full_bar(s), (it / kStages) & 1u, abort_flag)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t sa = base + s * kStageBytes, sb = sa + kABytes, ssf = sb + kBBytes;
+          const uint32_t t_sfa = tmem_base + kSfColBase + s * 8, t_sfb = t_sfa + 4;
+          tmem_cp_sf(t_sfa, make_sf_desc(ssf));
+          tmem_cp_sf(t_sfb, make_sf_desc(ssf + kSfBytes));
+#pragma unroll
+          for (int k = 0; k < BK / 32; ++k)
+            umma_mxf8(d_tmem, make_desc(sa + k * 32, 16, 1024), make_desc(sb + k * 32, 16, 1024),
+                      make_idesc_mx(BM, BN, k, k), t_sfa, t_sfb, (kb | k) != 0 ? 1u : 0u);
+          umma_commit(empty_bar(s));
+        }
+        if (ok) umma_commit(tfull_bar(acc));
+      }
+    }
+  } else {
+    const int q = warp & 3;
+    uint32_t tcount = 0, sbuf = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++tcount) {
+      const int acc = tcount & 1;
+      int tm, tn;
+      tile_coord(tile, tm, tn);
+      const int m0 = tm * BM, n0 = tn * BN;
+      if (!mbar_wait(tfull_bar(acc), (tcount >> 1) & 1u, abort_flag)) { ok = false; break; }
+      tc_fence_after();
+      const uint32_t stage0 = epi_base + (uint32_t)(warp - 2) * 8192u;
+#pragma unroll 1
+      for (int c = 0; c < BN / 64; ++c) {
+        uint32_t r0[32], r1[32];
+        const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN + c * 64);
+        tmem_ld32(taddr, r0);
+        tmem_ld32(taddr + 32, r1);
+        tmem_ld_wait();
+        if (lane == 0) tma_store_wait_read<1>();
+        __syncwarp();
+        const uint32_t buf = stage0 + (sbuf ? 4096u : 0u);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          uint32_t w[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int i = (j & 3) * 8 + 2 * e;
+            __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(j < 4 ? r0[i] : r1[i]),
+                                                      __uint_as_float(j < 4 ? r0[i + 1] : r1[i + 1]));
+            w[e] = *reinterpret_cast<uint32_t*>(&h);
+          }
+          const uint32_t dst = buf + (uint32_t)lane * 128u + (uint32_t)((j ^ (lane & 7)) << 4);
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3])
+                       : "memory");
+        }
+        fence_proxy_async_smem();
+        __syncwarp();
+        const int col0 = n0 + c * 64;
+        if (lane == 0 && col0 < p.N && m0 + q * 32 < p.M) {
+          tma_store_2d(&tmap_c, buf, col0, m0 + q * 32);
+          tma_store_commit();
+        }
+        sbuf ^= 1u;
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(tempty_bar(acc));
+    }
+    if (lane == 0) tma_store_wait<0>();
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+  if (threadIdx.x == 0 && *abort_flag && p.status != nullptr) atomicOr(p.status, kStatusWaitTimedOut);
+}
+
+}  // namespace gemm_mx
+
+static CUtensorMap make_tmap_2d_t(const void* ptr, CUtensorMapDataType dt, uint64_t esz, uint64_t inner, uint64_t outer,
+                                  uint32_t box_inner, uint32_t box_outer) {
+  CUtensorMap map;
+  const cuuint64_t dims[2] = {inner, outer};
+  const cuuint64_t strides[1] = {inner * esz};
+  const cuuint32_t box[2] = {box_inner, box_outer};
+  const cuuint32_t elem[2] = {1, 1};
+  const CUresult r = cuTensorMapEncodeTiled(&map, dt, 2, const_cast<void*>(ptr), dims, strides, box, elem,
+                                            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                            CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  TORCH_CHECK(r == CUDA_SUCCESS, "cuTensorMapEncodeTiled (mxfp8 gemm) failed with code ", (int)r);
+  return map;
+}
+
+int64_t gemm_status(bool clear);
+
+// a [M, K], b [N, K]: e4m3 bytes (uint8), K a multiple of 128; sfa / sfb: tiled e8m0 scales
+// (`mxfp8_quantize_tiled`); returns C [M, N] bf16 = dequant(a) . dequant(b)^T.
+at::Tensor gemm_mxfp8(const at::Tensor& a, const at::Tensor& sfa, const at::Tensor& b, const at::Tensor& sfb) {
+  using namespace gemm_mx;
+  TORCH_CHECK(a.is_cuda() && b.is_cuda() && a.scalar_type() == at::kByte && b.scalar_type() == at::kByte);
+  TORCH_CHECK(a.dim() == 2 && b.dim() == 2 && a.is_contiguous() && b.is_contiguous() && a.size(1) == b.size(1));
+  const int64_t M = a.size(0), N = b.size(0), K = a.size(1);
+  TORCH_CHECK(K % BK == 0 && N % 8 == 0, "gemm_mxfp8: K must be a multiple of 128 and N of 8");
+  const int64_t kt = K / BK;
+  TORCH_CHECK(sfa.is_cuda() && sfa.scalar_type() == at::kByte && sfa.is_contiguous() &&
+              sfa.numel() == (M + 127) / 128 * kt * 512, "gemm_mxfp8: sfa has the wrong size");
+  TORCH_CHECK(sfb.is_cuda() && sfb.scalar_type() == at::kByte && sfb.is_contiguous() &&
+              sfb.numel() == (N + 127) / 128 * kt * 512, "gemm_mxfp8: sfb has the wrong size");
+  c10::cuda::CUDAGuard guard(a.device());
+  C10_CUDA_CHECK(cudaSetDevice(a.device().index()));
+  auto c = at::empty({M, N}, a.options().dtype(at::kBFloat16));
+  if (M == 0 || N == 0) return c;
+  const CUtensorMap ta = make_tmap_2d_t(a.data_ptr(), CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, K, M, BK, BM);
+  const CUtensorMap tb = make_tmap_2d_t(b.data_ptr(), CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, K, N, BK, BN);
+  const CUtensorMap tcm = make_tmap_2d_t(c.data_ptr(), CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, N, M, 64, 32);
+  Params p;
+  p.M = (int)M; p.N = (int)N; p.K = (int)K;
+  p.sfa = sfa.data_ptr<uint8_t>();
+  p.sfb = sfb.data_ptr<uint8_t>();
+  static at::Tensor status;
+  if (!status.defined()) status = at::zeros({1}, a.options().dtype(at::kInt));
+  p.status = status.data_ptr<int>();
+  static bool attr_set = false;
+  if (!attr_set) {
+    C10_CUDA_CHECK(cudaFuncSetAttribute(gemm_mxfp8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
+    attr_set = true;
+  }
+  const int tiles = (int)(((M + BM - 1) / BM) * ((N + BN - 1) / BN));
+  gemm_mxfp8_kernel<<<std::min(tiles, num_sms()), kThreads, kSmemBytes, at::cuda::getCurrentCUDAStream()>>>(ta, tb, tcm, p);
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+  return c;
+}
+
+}  // namespace tb200

@@ -43,7 +43,9 @@ __device__ __forceinline__ float from_e4m3(uint32_t byte) {
 }
 
 // ---- axis 1: 4 consecutive lanes own one block of 32 contiguous elements (8 each)
-template <bool kFake>
+// kTiled: scales go to the 512-byte atoms (128 rows x 4 blocks) that the block-scaled MMA reads
+// through tcgen05.cp: byte (r % 32) * 16 + (r / 32) * 4 + b inside atom (row tile, k tile).
+template <bool kFake, bool kTiled = false>
 __global__ void mx_rowwise_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* __restrict__ data,
                                   uint8_t* __restrict__ scales, __nv_bfloat16* __restrict__ fake, int64_t n_vec, int C) {
   const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;   // vector of 8 elements
@@ -71,7 +73,18 @@ __global__ void mx_rowwise_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* 
     reinterpret_cast<bf16x8*>(fake)[i] = pack8(r);
   } else {
     reinterpret_cast<uint2*>(data)[i] = make_uint2(lo, hi);
-    if ((i & 3) == 0) scales[i >> 2] = (uint8_t)e;   // element index 8 i -> block 8 i / 32
+    if ((i & 3) == 0) {
+      if (kTiled) {
+        const int64_t el = i * 8;
+        const int64_t row = el / C;
+        const int blk = (int)(el % C) >> 5;
+        const int r = (int)(row & 127);
+        const int64_t atom = (row >> 7) * (C >> 7) + (blk >> 2);
+        scales[atom * 512 + (r & 31) * 16 + (r >> 5) * 4 + (blk & 3)] = (uint8_t)e;
+      } else {
+        scales[i >> 2] = (uint8_t)e;   // element index 8 i -> block 8 i / 32
+      }
+    }
   }
 }
 
@@ -206,6 +219,23 @@ std::tuple<at::Tensor, at::Tensor> mxfp8_quantize(const at::Tensor& x, int64_t a
   auto scales = axis == 1 ? at::empty({R, C / 32}, x.options().dtype(at::kByte))
                           : at::empty({(R + 31) / 32, C}, x.options().dtype(at::kByte));
   launch_mx<false>(x, axis, data.data_ptr<uint8_t>(), scales.data_ptr<uint8_t>(), nullptr);
+  return {data, scales};
+}
+
+// Row-wise MXFP8 with the scale layout of the block-scaled GEMM (`gemm_mxfp8`); C % 128 == 0.
+std::tuple<at::Tensor, at::Tensor> mxfp8_quantize_tiled(const at::Tensor& x) {
+  check_q_input(x, 1);
+  TORCH_CHECK(x.size(1) % 128 == 0, "mxfp8_quantize_tiled: the contraction dimension must be a multiple of 128");
+  c10::cuda::CUDAGuard guard(x.device());
+  const int64_t R = x.size(0), C = x.size(1);
+  auto data = at::empty({R, C}, x.options().dtype(at::kByte));
+  auto scales = at::zeros({(R + 127) / 128 * (C / 128) * 512}, x.options().dtype(at::kByte));
+  const int64_t n_vec = R * C / 8;
+  if (n_vec > 0)
+    mx_rowwise_kernel<false, true><<<(unsigned)((n_vec + 255) / 256), 256, 0, at::cuda::getCurrentCUDAStream()>>>(
+        reinterpret_cast<const __nv_bfloat16*>(x.data_ptr()), data.data_ptr<uint8_t>(), scales.data_ptr<uint8_t>(), nullptr,
+        n_vec, (int)C);
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
   return {data, scales};
 }
 
