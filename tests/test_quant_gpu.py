@@ -62,3 +62,65 @@ def test_quant_linear_runs_on_gpu():
     want = fq(x.detach().cpu(), 1).float() @ fq(lin.weight.detach().cpu(), 1).float().t()
     assert (y.float().cpu() - want).abs().max().item() <= 2e-2 * want.abs().max().item() + 1e-2
     assert x.grad is not None and lin.weight.grad is not None
+
+
+def _untile(sf, R, K):
+    """Tiled scale atoms -> [R, K/32] exponent bytes."""
+    kt = K // 128
+    a = sf.view((R + 127) // 128, kt, 32, 4, 4)          # [row tile, k tile, r % 32, r / 32, block]
+    return a.permute(0, 3, 2, 1, 4).reshape(-1, kt * 4)[:R]
+
+
+@pytest.mark.parametrize("R,C", [(128, 128), (300, 256), (1000, 384)])
+def test_mxfp8_tiled_quantisers(R, C):
+    ops = ext.require()
+    x = _input(R, C, seed=R)
+    data, scales = ops.mxfp8_quantize(x, 1)
+    td, ts = ops.mxfp8_quantize_tiled(x)
+    assert torch.equal(td, data) and torch.equal(_untile(ts, R, C), scales)
+    # transposing form: x [Rt, Ct] scaled along its rows, written as [Ct, Rt]
+    Rt, Ct = C, (R + 7) // 8 * 8
+    xt = _input(Rt, Ct, seed=R + 1)
+    d0, s0 = ops.mxfp8_quantize(xt, 0)                   # data [Rt, Ct], scales [Rt/32, Ct]
+    dt, st = ops.mxfp8_quantize_tiled_t(xt)
+    assert dt.shape == (Ct, Rt)
+    assert torch.equal(dt, d0.t().contiguous()) and torch.equal(_untile(st, Ct, Rt), s0.t().contiguous())
+
+
+@pytest.mark.parametrize("variant", [1, 2])
+@pytest.mark.parametrize("M,N,K", [(128, 128, 128), (512, 256, 256), (1000, 520, 1024), (2048, 768, 512)])
+def test_gemm_mxfp8_block_scaled(M, N, K, variant):
+    ops = ext.require()
+    x = (torch.randn(M, K, device="cuda") * torch.logspace(-2, 2, M, device="cuda")[:, None]).bfloat16()
+    w = (torch.randn(N, K, device="cuda") * torch.logspace(-1, 1, N, device="cuda")[:, None]).bfloat16()
+    xa, xs = ops.mxfp8_quantize_tiled(x)
+    wa, ws = ops.mxfp8_quantize_tiled(w)
+    ops.gemm_mx_set_variant(variant)
+    try:
+        c = ops.gemm_mxfp8(xa, xs, wa, ws)
+        torch.cuda.synchronize()
+    finally:
+        ops.gemm_mx_set_variant(0)
+    assert ops.gemm_status(True) == 0
+    want = ops.mxfp8_fake_quant(x, 1).float() @ ops.mxfp8_fake_quant(w, 1).float().t()
+    # bf16 rounding of the output, fp32 accumulation order
+    err = (c.float() - want).abs()
+    assert (err <= 1e-2 * want.abs() + 1e-3 * want.abs().max()).all(), err.max().item()
+
+
+def test_quant_linear_block_scaled_matches_emulated():
+    from torchtitan_b200.components.quantization.linear import QuantLinear
+
+    ext.require()
+    outs = []
+    for block_scaled in (True, False):
+        lin = QuantLinear.Config(in_features=256, out_features=384, recipe="mxfp8", block_scaled=block_scaled).build()
+        lin.init_states(seed=0)
+        lin = lin.cuda().bfloat16()
+        g = torch.Generator(device="cuda").manual_seed(5)
+        x = torch.randn(4, 128, 256, device="cuda", generator=g).bfloat16().requires_grad_()
+        y = lin(x)
+        y.backward(torch.randn(y.shape, device="cuda", generator=g).bfloat16())
+        outs.append((y.detach().float(), x.grad.float(), lin.weight.grad.float()))
+    for a, b in zip(*outs):
+        assert (a - b).abs().max().item() <= 1e-2 * b.abs().max().item()

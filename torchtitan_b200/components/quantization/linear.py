@@ -8,11 +8,15 @@ tokens.  Outputs and accumulation stay bf16 / fp32.  ``float8_rowwise``: one fp3
 each operand (e4m3).  Parity: torchao ``MXFP8Linear`` / row-wise ``Float8Linear`` as configured
 by torchtitan/components/quantization/mx.py:50-98 and float8.py:53-173.
 
-Execution.  The quantiser is a hand-written kernel (``ops/csrc/quant.cu``).  The GEMM itself runs
-on the operands' *exact* MXFP8 values in bf16 (every e4m3 x 2^e product is representable in
-bf16), on the tcgen05 bf16 GEMM with fp32 accumulation, so the numerics are those of a
-block-scaled fp8 GEMM while the throughput is that of bf16.  On CPU the same math runs in
-PyTorch (``ops.reference``), which is also the oracle of the kernel tests.
+Execution.  The quantisers are hand-written kernels (``ops/csrc/quant.cu``).  With the ``mxfp8``
+recipe on a GPU, every GEMM whose contraction dimension is a multiple of 128 runs on the
+block-scaled tensor-core path (``ops/csrc/gemm_mx.cu``: ``tcgen05.mma.kind::mxf8f6f4.block_scale``
+on e4m3 bytes and e8m0 scales; the operands that are contracted over their rows are quantised by a
+transposing kernel so that both arrive K-major).  Otherwise, and for ``float8_rowwise``, the GEMM
+runs on the operands' *exact* fp8 values held in bf16 (every e4m3 x 2^e product is representable
+in bf16) on the tcgen05 bf16 GEMM with fp32 accumulation: the same numerics at bf16 throughput.
+On CPU the same math runs in PyTorch (``ops.reference``), which is also the oracle of the kernel
+tests.  ``block_scaled = False`` in the layer's config forces the emulated path.
 """
 
 from __future__ import annotations
@@ -45,13 +49,36 @@ def fake_quant(x: torch.Tensor, recipe: str, axis: int) -> torch.Tensor:
     raise ValueError(f"unknown quantisation recipe '{recipe}'")
 
 
+def _mx_native(recipe: str, block_scaled: bool, contraction: int, n_out: int, *ts: torch.Tensor) -> bool:
+    """Whether a GEMM can run on the block-scaled tensor-core kernel."""
+    return (block_scaled and recipe == "mxfp8" and contraction > 0 and contraction % 128 == 0 and n_out % 8 == 0
+            and all(t.is_cuda and t.dtype == torch.bfloat16 and t.shape[1] % 8 == 0 for t in ts) and ext.available())
+
+
+def _mx_gemm(a: torch.Tensor, a_rows_contracted: bool, b: torch.Tensor, b_rows_contracted: bool) -> torch.Tensor:
+    """Block-scaled GEMM of two bf16 operands, each quantised along its contraction dimension.
+
+    An operand given as [contraction, rows] (``*_rows_contracted``) goes through the transposing
+    quantiser; the result is ``A_q [M, K] . B_q [N, K]^T`` in bf16."""
+    ops = ext.require()
+    OF._count(3)
+    qa = ops.mxfp8_quantize_tiled_t(a) if a_rows_contracted else ops.mxfp8_quantize_tiled(a)
+    qb = ops.mxfp8_quantize_tiled_t(b) if b_rows_contracted else ops.mxfp8_quantize_tiled(b)
+    return ops.gemm_mxfp8(qa[0], qa[1], qb[0], qb[1])
+
+
 class _QuantLinearFn(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, weight, recipe, hp_wgrad):
+    def forward(ctx, x, weight, recipe, hp_wgrad, block_scaled=True):
         x2 = x.reshape(-1, x.shape[-1])
-        y = OF.gemm_nt(fake_quant(x2, recipe, 1), fake_quant(weight, recipe, 1))
+        if not x2.is_contiguous():
+            x2 = x2.contiguous()
+        if _mx_native(recipe, block_scaled, x2.shape[1], weight.shape[0], x2, weight):
+            y = _mx_gemm(x2, False, weight, False)
+        else:
+            y = OF.gemm_nt(fake_quant(x2, recipe, 1), fake_quant(weight, recipe, 1))
         ctx.save_for_backward(x2, weight)
-        ctx.recipe, ctx.hp_wgrad, ctx.xshape = recipe, hp_wgrad, x.shape
+        ctx.recipe, ctx.hp_wgrad, ctx.xshape, ctx.block_scaled = recipe, hp_wgrad, x.shape, block_scaled
         return y if x.dim() == 2 else y.view(*x.shape[:-1], weight.shape[0])
 
     @staticmethod
@@ -62,16 +89,22 @@ class _QuantLinearFn(torch.autograd.Function):
         if not dy2.is_contiguous():
             dy2 = dy2.contiguous()
         dx = None
+        bs = ctx.block_scaled
         if ctx.needs_input_grad[0]:
             # contraction over the output features: dy along its columns, w along its rows
-            dx = OF.gemm_nn(fake_quant(dy2, r, 1), fake_quant(weight, r, 0)).view(ctx.xshape)
+            if _mx_native(r, bs, weight.shape[0], weight.shape[1], dy2, weight):
+                dx = _mx_gemm(dy2, False, weight, True).view(ctx.xshape)
+            else:
+                dx = OF.gemm_nn(fake_quant(dy2, r, 1), fake_quant(weight, r, 0)).view(ctx.xshape)
         dw = None
         if weight.requires_grad:
             if ctx.hp_wgrad:
                 dw = OF._wgrad(dy2, x2, weight)
-            else:  # contraction over the tokens
+            elif _mx_native(r, bs, dy2.shape[0], weight.shape[1], dy2, x2):   # contraction over the tokens
+                dw = OF._deliver_wgrad(weight, _mx_gemm(dy2, True, x2, True))
+            else:
                 dw = OF._wgrad(fake_quant(dy2, r, 0), fake_quant(x2, r, 0), weight)
-        return dx, dw, None, None
+        return dx, dw, None, None, None
 
 
 class QuantLinear(Linear):
@@ -79,10 +112,11 @@ class QuantLinear(Linear):
     class Config(Linear.Config):
         recipe: str = "mxfp8"  # "mxfp8" | "float8_rowwise"
         high_precision_wgrad: bool = False  # rowwise_with_gw_hp of the float8 recipe
+        block_scaled: bool = True  # mxfp8 on a GPU: run the GEMMs on the block-scaled tensor-core kernel
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         c = self.config
         if x.dtype != self.weight.dtype:
             x = x.to(self.weight.dtype)
-        y = _QuantLinearFn.apply(x, self.weight, c.recipe, c.high_precision_wgrad)
+        y = _QuantLinearFn.apply(x, self.weight, c.recipe, c.high_precision_wgrad, c.block_scaled)
         return y if self.bias is None else y + self.bias

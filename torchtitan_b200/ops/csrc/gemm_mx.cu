@@ -232,6 +232,211 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
   if (threadIdx.x == 0 && *abort_flag && p.status != nullptr) atomicOr(p.status, kStatusWaitTimedOut);
 }
 
+// ---------------------------------------------------------------------------------------------
+// CTA-pair form: a cluster of two CTAs (one SM pair) computes a 256 x 256 tile with
+// tcgen05.mma.cta_group::2.  Each CTA stages its own 128 rows of A, its own 128 of the tile's 256
+// rows of B, the scale atom of its A rows and both scale atoms of B; CTA 0 issues every
+// tcgen05.cp (which runs in both CTAs, each from its own shared memory into its own tensor
+// memory) and every MMA.  Tensor memory holds ONE 256-column accumulator plus 16 scale columns
+// per stage, so the accumulator cannot be double buffered there: eight epilogue warps copy it to
+// registers (128 columns of 32 lanes each, packed to bf16), release it at once, and store from
+// registers while the MMAs of the next tile run.
+namespace pair {
+constexpr int BN2 = 256;                          // columns of the pair tile
+constexpr int kPStages = 5;
+constexpr int kPThreads = 64 + 8 * 32;
+constexpr uint32_t kPABytes = BM * BK, kPBBytes = (BN2 / 2) * BK;
+constexpr uint32_t kDataBytes = kPABytes + kPBBytes;                     // 32 KB per stage (1024-byte multiple)
+constexpr uint32_t kSfStage = 3 * kSfBytes;                            // A atom, two B atoms
+constexpr uint32_t kStageTx = kDataBytes + kSfStage;                   // bytes one CTA brings per stage
+constexpr uint32_t kPEpiBytes = 8 * 4096;
+constexpr uint32_t kSfRegion = (kPStages * kSfStage + 1023u) & ~1023u;   // keeps the swizzled epilogue tiles 1024-byte aligned
+constexpr uint32_t kPSmemBytes = kPStages * kDataBytes + kSfRegion + kPEpiBytes + 1024 + 256;
+constexpr uint32_t kSfCol0 = BN2;                                      // 16 scale columns per stage
+}  // namespace pair
+
+__device__ __forceinline__ void tmem_cp_sf_pair(uint32_t taddr, uint64_t sdesc) {
+  asm volatile("tcgen05.cp.cta_group::2.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
+}
+__device__ __forceinline__ void umma_mxf8_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t sfa,
+                                               uint32_t sfb, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %6, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::mxf8f6f4.block_scale.scale_vec::1X [%0], %1, %2, %3, [%4], [%5], p;\n\t}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(sfa), "r"(sfb), "r"(accumulate)
+      : "memory");
+}
+
+__global__ void __launch_bounds__(pair::kPThreads, 1)
+gemm_mxfp8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                       const __grid_constant__ CUtensorMap tmap_c, const __grid_constant__ CUtensorMap tmap_sfa,
+                       const __grid_constant__ CUtensorMap tmap_sfb, const Params p) {
+  using namespace pair;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  uint8_t* gen_base = smem_raw + (base - raw);
+  const uint32_t sf_base = base + kPStages * kDataBytes;
+  const uint32_t epi_base = sf_base + kSfRegion;
+  const uint32_t bar_base = epi_base + kPEpiBytes;
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (kPStages + s); };
+  const uint32_t tfull_bar = bar_base + 8u * (2 * kPStages), tempty_bar = tfull_bar + 8u;
+  uint32_t* tmem_ptr_smem = reinterpret_cast<uint32_t*>(gen_base + (bar_base - base) + 8 * (2 * kPStages + 2));
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_ptr_smem + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t cta_rank = cluster_ctarank();
+  const int unit = (int)(blockIdx.x >> 1), num_units = (int)(gridDim.x >> 1);
+  constexpr int kTileM = 2 * BM;
+  const int num_m = (p.M + kTileM - 1) / kTileM, num_n = (p.N + BN2 - 1) / BN2;
+  const int num_tiles = num_m * num_n;
+  const int num_kb = (p.K + BK - 1) / BK;
+  constexpr int kGroupM = 8;
+  auto tile_coord = [&](int t, int& tm, int& tn) {
+    const int per_group = kGroupM * num_n;
+    const int g = t / per_group;
+    const int first = g * kGroupM;
+    const int gsz = min(kGroupM, num_m - first);
+    const int r = t - g * per_group;
+    tm = first + r % gsz;
+    tn = r / gsz;
+  };
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kPStages; ++s) {
+      mbar_init(full_bar(s), 2);       // one arrive.expect_tx per producing CTA
+      mbar_init(empty_bar(s), 1);
+    }
+    mbar_init(tfull_bar, 1);
+    mbar_init(tempty_bar, 16);         // eight epilogue warps of each CTA
+    *abort_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&tmap_a);
+    tma_prefetch_desc(&tmap_b);
+    tma_prefetch_desc(&tmap_c);
+    tma_prefetch_desc(&tmap_sfa);
+    tma_prefetch_desc(&tmap_sfb);
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(tmem_ptr_smem), 512);     // the whole TMEM: both CTAs get base column 0
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_ptr_smem;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      uint32_t it = 0;
+      bool ok = true;
+      for (int tile = unit; tile < num_tiles && ok; tile += num_units) {
+        int tm, tn;
+        tile_coord(tile, tm, tn);
+        const int mt = tm * 2 + (int)cta_rank;                       // 128-row tile of A staged here
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % kPStages;
+          if (!mbar_wait_cluster(empty_bar(s), ((it / kPStages) & 1u) ^ 1u, abort_flag)) { ok = false; break; }
+          const uint32_t sa = base + s * kDataBytes, sb = sa + kPABytes, ssf = sf_base + s * kSfStage;
+          const uint32_t fb = mapa(full_bar(s), 0);                  // CTA 0 counts the bytes of both
+          mbar_expect_tx_cluster(fb, kStageTx);
+          tma_load_2d_pair(sa, &tmap_a, fb, kb * BK, mt * BM);
+          tma_load_2d_pair(sb, &tmap_b, fb, kb * BK, tn * BN2 + (int)cta_rank * (BN2 / 2));
+          tma_load_3d_pair(ssf, &tmap_sfa, fb, 0, kb, mt);
+          tma_load_3d_pair(ssf + kSfBytes, &tmap_sfb, fb, 0, kb, tn * 2);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && cta_rank == 0) {
+      uint32_t it = 0, tcount = 0;
+      bool ok = true;
+      for (int tile = unit; tile < num_tiles && ok; tile += num_units, ++tcount) {
+        if (!mbar_wait_cluster(tempty_bar, (tcount & 1u) ^ 1u, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % kPStages;
+          if (!mbar_wait_cluster(full_bar(s), (it / kPStages) & 1u, abort_flag)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t sa = base + s * kDataBytes, sb = sa + kPABytes, ssf = sf_base + s * kSfStage;
+          const uint32_t t_sfa = tmem_base + kSfCol0 + s * 16, t_sfb = t_sfa + 4;
+          tmem_cp_sf_pair(t_sfa, make_sf_desc(ssf));
+          tmem_cp_sf_pair(t_sfb, make_sf_desc(ssf + kSfBytes));
+          tmem_cp_sf_pair(t_sfb + 4, make_sf_desc(ssf + 2 * kSfBytes));
+#pragma unroll
+          for (int k = 0; k < BK / 32; ++k)
+            umma_mxf8_pair(tmem_base, make_desc(sa + k * 32, 16, 1024), make_desc(sb + k * 32, 16, 1024),
+                           make_idesc_mx(kTileM, BN2, k, k), t_sfa, t_sfb, (kb | k) != 0 ? 1u : 0u);
+          umma_commit_pair(empty_bar(s), 3);
+        }
+        if (ok) umma_commit_pair(tfull_bar, 3);
+      }
+    }
+  } else {
+    const int q = warp & 3;                 // TMEM lane quarter of this warp
+    const int h = (warp - 2) >> 2;          // column half of the tile
+    uint32_t tcount = 0;
+    bool ok = true;
+    const uint32_t te_leader = mapa(tempty_bar, 0);
+    const uint32_t buf = epi_base + (uint32_t)(warp - 2) * 4096u;
+    for (int tile = unit; tile < num_tiles && ok; tile += num_units, ++tcount) {
+      int tm, tn;
+      tile_coord(tile, tm, tn);
+      const int m0 = tm * kTileM + (int)cta_rank * BM + q * 32, n0 = tn * BN2 + h * 128;
+      if (!mbar_wait_cluster(tfull_bar, tcount & 1u, abort_flag)) { ok = false; break; }
+      tc_fence_after();
+      uint32_t packed[64];                  // 128 columns of this lane's row as bf16 pairs
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t r[32];
+        tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(h * 128 + c * 32), r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int e = 0; e < 16; ++e) {
+          __nv_bfloat162 v = __floats2bfloat162_rn(__uint_as_float(r[2 * e]), __uint_as_float(r[2 * e + 1]));
+          packed[c * 16 + e] = *reinterpret_cast<uint32_t*>(&v);
+        }
+      }
+      // the accumulator is free again: the MMAs of the next tile may overwrite it
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(te_leader);
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        if (lane == 0) tma_store_wait_read<0>();   // the previous store has read the staging tile
+        __syncwarp();
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const uint32_t dst = buf + (uint32_t)lane * 128u + (uint32_t)((j ^ (lane & 7)) << 4);
+          const int e = c * 32 + j * 4;
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(packed[e]), "r"(packed[e + 1]),
+                       "r"(packed[e + 2]), "r"(packed[e + 3])
+                       : "memory");
+        }
+        fence_proxy_async_smem();
+        __syncwarp();
+        const int col0 = n0 + c * 64;
+        if (lane == 0 && col0 < p.N && m0 < p.M) {
+          tma_store_2d(&tmap_c, buf, col0, m0);
+          tma_store_commit();
+        }
+      }
+    }
+    if (lane == 0) tma_store_wait<0>();
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync();      // neither CTA frees its TMEM or leaves while the other can still issue MMAs
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+  if (threadIdx.x == 0 && *abort_flag && p.status != nullptr) atomicOr(p.status, kStatusWaitTimedOut);
+}
+
 }  // namespace gemm_mx
 
 static CUtensorMap make_tmap_2d_t(const void* ptr, CUtensorMapDataType dt, uint64_t esz, uint64_t inner, uint64_t outer,
@@ -246,6 +451,26 @@ static CUtensorMap make_tmap_2d_t(const void* ptr, CUtensorMapDataType dt, uint6
                                             CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   TORCH_CHECK(r == CUDA_SUCCESS, "cuTensorMapEncodeTiled (mxfp8 gemm) failed with code ", (int)r);
   return map;
+}
+
+// Scale atoms as a 3-D tensor [row tile][K tile][128 words] for the pair kernel's tile loads.
+static CUtensorMap make_tmap_sf(const void* ptr, uint64_t row_tiles, uint64_t k_tiles, uint32_t box_tiles) {
+  CUtensorMap map;
+  const cuuint64_t dims[3] = {128, k_tiles, row_tiles};
+  const cuuint64_t strides[2] = {512, 512 * k_tiles};
+  const cuuint32_t box[3] = {128, 1, box_tiles};
+  const cuuint32_t elem[3] = {1, 1, 1};
+  const CUresult r = cuTensorMapEncodeTiled(&map, CU_TENSOR_MAP_DATA_TYPE_UINT32, 3, const_cast<void*>(ptr), dims, strides,
+                                            box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                                            CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  TORCH_CHECK(r == CUDA_SUCCESS, "cuTensorMapEncodeTiled (mxfp8 scales) failed with code ", (int)r);
+  return map;
+}
+
+static int g_mx_variant = 0;   // 0: by shape, 1: one CTA per tile, 2: CTA pairs
+void gemm_mx_set_variant(int64_t v) {
+  TORCH_CHECK(v >= 0 && v <= 2, "gemm_mx_set_variant: 0 (auto), 1 (single CTA) or 2 (CTA pair)");
+  g_mx_variant = (int)v;
 }
 
 int64_t gemm_status(bool clear);
@@ -277,6 +502,40 @@ at::Tensor gemm_mxfp8(const at::Tensor& a, const at::Tensor& sfa, const at::Tens
   static at::Tensor status;
   if (!status.defined()) status = at::zeros({1}, a.options().dtype(at::kInt));
   p.status = status.data_ptr<int>();
+  const bool use_pair = g_mx_variant == 2 || (g_mx_variant == 0 && M >= 512 && N >= 256);
+  if (use_pair) {
+    const CUtensorMap tb2 = make_tmap_2d_t(b.data_ptr(), CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, K, N, BK, pair::BN2 / 2);
+    const CUtensorMap tsa = make_tmap_sf(sfa.data_ptr(), (M + 127) / 128, kt, 1);
+    const CUtensorMap tsb = make_tmap_sf(sfb.data_ptr(), (N + 127) / 128, kt, 2);
+    static bool pair_attr_set = false;
+    if (!pair_attr_set) {
+      C10_CUDA_CHECK(cudaFuncSetAttribute(gemm_mxfp8_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                          pair::kPSmemBytes));
+      pair_attr_set = true;
+    }
+    const int tiles = (int)(((M + 255) / 256) * ((N + pair::BN2 - 1) / pair::BN2));
+    cudaLaunchConfig_t cfg = {};
+    cfg.blockDim = dim3(pair::kPThreads);
+    cfg.dynamicSmemBytes = pair::kPSmemBytes;
+    cfg.stream = at::cuda::getCurrentCUDAStream();
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    static int max_pairs = 0;
+    if (max_pairs == 0) {
+      cfg.gridDim = dim3(num_sms() & ~1);
+      int n = 0;
+      C10_CUDA_CHECK(cudaOccupancyMaxActiveClusters(&n, gemm_mxfp8_pair_kernel, &cfg));
+      max_pairs = std::max(1, std::min(n, num_sms() / 2));
+    }
+    cfg.gridDim = dim3(2 * std::min(tiles, max_pairs));
+    C10_CUDA_CHECK(cudaLaunchKernelEx(&cfg, gemm_mxfp8_pair_kernel, ta, tb2, tcm, tsa, tsb, p));
+    return c;
+  }
   static bool attr_set = false;
   if (!attr_set) {
     C10_CUDA_CHECK(cudaFuncSetAttribute(gemm_mxfp8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));

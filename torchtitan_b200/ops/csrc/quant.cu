@@ -126,6 +126,52 @@ __global__ void mx_colwise_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* 
   }
 }
 
+// ---- transposing quantiser: x [R, C] -> data [C, R] e4m3, scaled along R (blocks of 32 rows of x
+// become blocks of 32 contiguous bytes of an output row), scales in the GEMM's tiled layout over
+// (rows = C, contraction = R).  One CTA moves a tile of 128 rows x 64 columns through shared
+// memory (16-byte chunks, XOR-swizzled by the row block so that the column reads below do not
+// collide); thread (c, b) then owns column c over row block b and writes 32 contiguous bytes, the
+// four threads of a column one 128-byte line.
+constexpr int kTqRows = 128, kTqCols = 64;
+__global__ void __launch_bounds__(256)
+mx_transpose_tiled_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* __restrict__ data, uint8_t* __restrict__ scales,
+                          int R, int C) {
+  __shared__ __align__(16) uint8_t tile[kTqRows * kTqCols * 2];
+  const int r0 = blockIdx.y * kTqRows, c0 = blockIdx.x * kTqCols;
+  // load: 1024 chunks of 8 elements, 4 per thread (row = chunk / 8)
+#pragma unroll
+  for (int u = 0; u < 4; ++u) {
+    const int ch = threadIdx.x + u * 256;
+    const int r = ch >> 3, cc = ch & 7;
+    uint4 v = make_uint4(0u, 0u, 0u, 0u);
+    if (c0 + cc * 8 < C) v = *reinterpret_cast<const uint4*>(x + (int64_t)(r0 + r) * C + c0 + cc * 8);
+    *reinterpret_cast<uint4*>(tile + r * 128 + ((cc ^ ((r >> 5) * 2)) << 4)) = v;
+  }
+  __syncthreads();
+  const int b = threadIdx.x & 3, c = threadIdx.x >> 2;
+  if (c0 + c >= C) return;
+  const int cc = (c >> 3) ^ (b * 2);
+  const uint8_t* src = tile + (b * 32) * 128 + (cc << 4) + (c & 7) * 2;
+  float v[32];
+  float amax = 0.f;
+#pragma unroll
+  for (int i = 0; i < 32; ++i) {
+    v[i] = __bfloat162float(*reinterpret_cast<const __nv_bfloat16*>(src + i * 128));
+    amax = fmaxf(amax, fabsf(v[i]));
+  }
+  const uint32_t e = e8m0_rceil(amax);
+  const float inv = e8m0_inverse(e);
+  uint32_t w[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) w[i] = to_e4m3x4(v[4 * i] * inv, v[4 * i + 1] * inv, v[4 * i + 2] * inv, v[4 * i + 3] * inv);
+  uint4* dst = reinterpret_cast<uint4*>(data + (int64_t)(c0 + c) * R + r0 + b * 32);
+  dst[0] = make_uint4(w[0], w[1], w[2], w[3]);
+  dst[1] = make_uint4(w[4], w[5], w[6], w[7]);
+  const int row = c0 + c;
+  const int64_t atom = (int64_t)(row >> 7) * (R >> 7) + blockIdx.y;
+  scales[atom * 512 + (row & 31) * 16 + ((row & 127) >> 5) * 4 + b] = (uint8_t)e;
+}
+
 __global__ void mx_dequant_kernel(const uint8_t* __restrict__ data, const uint8_t* __restrict__ scales,
                                   __nv_bfloat16* __restrict__ out, int64_t n_vec, int C, int axis) {
   const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;   // 8 elements
@@ -229,13 +275,34 @@ std::tuple<at::Tensor, at::Tensor> mxfp8_quantize_tiled(const at::Tensor& x) {
   c10::cuda::CUDAGuard guard(x.device());
   const int64_t R = x.size(0), C = x.size(1);
   auto data = at::empty({R, C}, x.options().dtype(at::kByte));
-  auto scales = at::zeros({(R + 127) / 128 * (C / 128) * 512}, x.options().dtype(at::kByte));
+  const int64_t n_sf = (R + 127) / 128 * (C / 128) * 512;   // rows past R keep scale byte 0 (2^-127), never NaN
+  auto scales = R % 128 == 0 ? at::empty({n_sf}, x.options().dtype(at::kByte)) : at::zeros({n_sf}, x.options().dtype(at::kByte));
   const int64_t n_vec = R * C / 8;
   if (n_vec > 0)
     mx_rowwise_kernel<false, true><<<(unsigned)((n_vec + 255) / 256), 256, 0, at::cuda::getCurrentCUDAStream()>>>(
         reinterpret_cast<const __nv_bfloat16*>(x.data_ptr()), data.data_ptr<uint8_t>(), scales.data_ptr<uint8_t>(), nullptr,
         n_vec, (int)C);
   C10_CUDA_KERNEL_LAUNCH_CHECK();
+  return {data, scales};
+}
+
+// Column-wise MXFP8 of x [R, C] written transposed, as a K-major GEMM operand: data [C, R] scaled
+// along R, with the tiled scale layout over (rows = C, contraction = R); R % 128 == 0, C % 8 == 0.
+std::tuple<at::Tensor, at::Tensor> mxfp8_quantize_tiled_t(const at::Tensor& x) {
+  check_q_input(x, 0);
+  TORCH_CHECK(x.size(0) % 128 == 0, "mxfp8_quantize_tiled_t: the contraction dimension (rows) must be a multiple of 128");
+  c10::cuda::CUDAGuard guard(x.device());
+  const int64_t R = x.size(0), C = x.size(1);
+  auto data = at::empty({C, R}, x.options().dtype(at::kByte));
+  const int64_t n_sf = (C + 127) / 128 * (R / 128) * 512;
+  auto scales = C % 128 == 0 ? at::empty({n_sf}, x.options().dtype(at::kByte)) : at::zeros({n_sf}, x.options().dtype(at::kByte));
+  if (R > 0 && C > 0) {
+    dim3 grid((unsigned)((C + kTqCols - 1) / kTqCols), (unsigned)(R / kTqRows));
+    mx_transpose_tiled_kernel<<<grid, 256, 0, at::cuda::getCurrentCUDAStream()>>>(
+        reinterpret_cast<const __nv_bfloat16*>(x.data_ptr()), data.data_ptr<uint8_t>(), scales.data_ptr<uint8_t>(), (int)R,
+        (int)C);
+    C10_CUDA_KERNEL_LAUNCH_CHECK();
+  }
   return {data, scales};
 }
 

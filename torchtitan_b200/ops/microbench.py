@@ -152,6 +152,40 @@ def bench_elementwise(args) -> None:
         print(f"{name:12s}: {t:.3f} ms, {gbs(nbytes, t):.0f} GB/s algorithmic", flush=True)
 
 
+def bench_gemm_mx(args) -> None:
+    """MXFP8 block-scaled GEMM (tcgen05 kind::mxf8f6f4) vs the bf16 tcgen05 GEMM and cuBLAS MXFP8."""
+    ops = torch.ops.tb200
+    timer = Timer()
+    shapes = [s for s in GEMM_8B if s[1] == 0]
+    for name, _, M, N, K in (shapes if args.case != "small" else [("square", 0, 8192, 8192, 8192)]):
+        x = torch.randn(M, K, device="cuda").bfloat16()
+        w = torch.randn(N, K, device="cuda").bfloat16()
+        xa, xs = ops.mxfp8_quantize_tiled(x)
+        wa, ws = ops.mxfp8_quantize_tiled(w)
+        c = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+        if args.once:
+            ops.gemm_mxfp8(xa, xs, wa, ws)
+            torch.cuda.synchronize()
+            continue
+        t_mx = timer(lambda: ops.gemm_mxfp8(xa, xs, wa, ws))
+        t_bf = timer(lambda: ops.gemm_bf16(x, w, c, 0, False))
+        t_q = timer(lambda: ops.mxfp8_quantize_tiled(x))
+        lib = ""
+        try:
+            a8, b8 = xa.view(torch.float8_e4m3fn), wa.view(torch.float8_e4m3fn)
+            sa, sb = xs.view(torch.float8_e8m0fnu), ws.view(torch.float8_e8m0fnu)
+            f = lambda: torch._scaled_mm(a8, b8.t(), sa, sb, out_dtype=torch.bfloat16)  # noqa: E731
+            ref = f()
+            ok = torch.allclose(ref.float(), ops.gemm_mxfp8(xa, xs, wa, ws).float(), atol=1.0, rtol=2e-2)
+            t_lib = timer(f)
+            lib = f" | cuBLAS mxfp8 {t_lib:.3f} ms {2 * M * N * K / t_lib / 1e9:.0f} TFLOPS (same result: {ok})"
+        except Exception as e:  # the library arm is optional
+            lib = f" | cuBLAS mxfp8 unavailable ({type(e).__name__})"
+        fl = 2 * M * N * K
+        print(f"gemm_mx {name:10s} M{M} N{N} K{K}: mxfp8 {t_mx:.3f} ms {fl / t_mx / 1e9:.0f} TFLOPS | bf16 tcgen05 {t_bf:.3f} ms "
+              f"{fl / t_bf / 1e9:.0f} | quantize x {t_q:.3f} ms{lib}", flush=True)
+
+
 def bench_tp(args) -> None:
     """Fused tensor-parallel GEMMs vs NCCL collective + cuBLAS; run under torchrun with >= 2 ranks:
     ``python -m torch.distributed.run --nproc-per-node 2 --master-addr 127.0.0.1 -m torchtitan_b200.ops.microbench tp``."""
@@ -210,7 +244,7 @@ def bench_tp(args) -> None:
 
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser()
-    ap.add_argument("kernel", choices=["gemm", "attention", "elementwise", "tp"])
+    ap.add_argument("kernel", choices=["gemm", "gemm_mx", "attention", "elementwise", "tp"])
     ap.add_argument("--case", default="8b", choices=["small", "8b"])
     ap.add_argument("--variant", type=int, default=0, help="GEMM tiling: 0 auto, 1 single CTA, 2 CTA pair")
     ap.add_argument("--once", action="store_true", help="one launch per shape, no library arm (profiler form)")
@@ -219,7 +253,7 @@ def main(argv=None) -> int:
 
     assert torch.cuda.is_available(), "microbench needs a GPU"
     ext.require()
-    {"gemm": bench_gemm, "attention": bench_attention, "elementwise": bench_elementwise, "tp": bench_tp}[args.kernel](args)
+    {"gemm": bench_gemm, "attention": bench_attention, "elementwise": bench_elementwise, "tp": bench_tp, "gemm_mx": bench_gemm_mx}[args.kernel](args)
     return 0
 
 
