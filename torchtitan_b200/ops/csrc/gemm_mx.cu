@@ -40,6 +40,7 @@ struct Params {
   const uint8_t* sfa;     // tiled scales of A: [ceil(M/128)][K/128][512]
   const uint8_t* sfb;     // tiled scales of B
   int* status;
+  int debug;              // timing switches: 1 = no loads (barriers only), 2 = no scale copies
 };
 
 // Instruction descriptor of the block-scaled kinds: e4m3 x e4m3, ue8m0 scales, fp32 accumulate.
@@ -235,29 +236,28 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
 // ---------------------------------------------------------------------------------------------
 // CTA-pair form: a cluster of two CTAs (one SM pair) computes a 256 x 256 tile with
 // tcgen05.mma.cta_group::2.  Each CTA stages its own 128 rows of A, its own 128 of the tile's 256
-// rows of B, the scale atom of its A rows and both scale atoms of B; CTA 0 issues every
-// tcgen05.cp (which runs in both CTAs, each from its own shared memory into its own tensor
-// memory) and every MMA.  Tensor memory holds ONE 256-column accumulator plus 16 scale columns
+// rows of B, the scale atom of its A rows and both scale atoms of B; four warps of each CTA move
+// the atoms from shared to tensor memory with tcgen05.st (a tcgen05.cp between the MMAs measured
+// 25 % slower: the copy drains the tensor pipe); CTA 0 issues every MMA.  Tensor memory holds ONE 256-column accumulator plus 16 scale columns
 // per stage, so the accumulator cannot be double buffered there: eight epilogue warps copy it to
 // registers (128 columns of 32 lanes each, packed to bf16), release it at once, and store from
-// registers while the MMAs of the next tile run.
+// registers (32 x 32 tiles through a 64B-swizzled staging buffer and TMA) while the MMAs of the next
+// tile run.  What limits this kernel is operand feed: without cluster multicast every CTA pulls its
+// own 32 KB per K step from L2, so throughput is bytes in flight / L2 latency; hence six stages and a
+// small epilogue buffer.
 namespace pair {
 constexpr int BN2 = 256;                          // columns of the pair tile
-constexpr int kPStages = 5;
-constexpr int kPThreads = 64 + 8 * 32;
+constexpr int kPStages = 6;
+constexpr int kPThreads = 64 + 8 * 32 + 4 * 32;    // producer, MMA, 8 epilogue warps, 4 scale warps
 constexpr uint32_t kPABytes = BM * BK, kPBBytes = (BN2 / 2) * BK;
 constexpr uint32_t kDataBytes = kPABytes + kPBBytes;                     // 32 KB per stage (1024-byte multiple)
 constexpr uint32_t kSfStage = 3 * kSfBytes;                            // A atom, two B atoms
-constexpr uint32_t kStageTx = kDataBytes + kSfStage;                   // bytes one CTA brings per stage
-constexpr uint32_t kPEpiBytes = 8 * 4096;
+constexpr uint32_t kPEpiBytes = 8 * 2048;                                // one 32 x 32 bf16 tile per epilogue warp
 constexpr uint32_t kSfRegion = (kPStages * kSfStage + 1023u) & ~1023u;   // keeps the swizzled epilogue tiles 1024-byte aligned
 constexpr uint32_t kPSmemBytes = kPStages * kDataBytes + kSfRegion + kPEpiBytes + 1024 + 256;
 constexpr uint32_t kSfCol0 = BN2;                                      // 16 scale columns per stage
 }  // namespace pair
 
-__device__ __forceinline__ void tmem_cp_sf_pair(uint32_t taddr, uint64_t sdesc) {
-  asm volatile("tcgen05.cp.cta_group::2.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
-}
 __device__ __forceinline__ void umma_mxf8_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t sfa,
                                                uint32_t sfb, uint32_t accumulate) {
   asm volatile(
@@ -281,8 +281,10 @@ gemm_mxfp8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
   const uint32_t bar_base = epi_base + kPEpiBytes;
   auto full_bar = [&](int s) { return bar_base + 8u * s; };
   auto empty_bar = [&](int s) { return bar_base + 8u * (kPStages + s); };
-  const uint32_t tfull_bar = bar_base + 8u * (2 * kPStages), tempty_bar = tfull_bar + 8u;
-  uint32_t* tmem_ptr_smem = reinterpret_cast<uint32_t*>(gen_base + (bar_base - base) + 8 * (2 * kPStages + 2));
+  auto sf_full_bar = [&](int s) { return bar_base + 8u * (2 * kPStages + s); };      // this CTA's scale atoms landed
+  auto sf_ready_bar = [&](int s) { return bar_base + 8u * (3 * kPStages + s); };     // scales of both CTAs are in TMEM
+  const uint32_t tfull_bar = bar_base + 8u * (4 * kPStages), tempty_bar = tfull_bar + 8u;
+  uint32_t* tmem_ptr_smem = reinterpret_cast<uint32_t*>(gen_base + (bar_base - base) + 8 * (4 * kPStages + 2));
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_ptr_smem + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -307,6 +309,8 @@ gemm_mxfp8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
     for (int s = 0; s < kPStages; ++s) {
       mbar_init(full_bar(s), 2);       // one arrive.expect_tx per producing CTA
       mbar_init(empty_bar(s), 1);
+      mbar_init(sf_full_bar(s), 1);
+      mbar_init(sf_ready_bar(s), 8);   // four scale warps of each CTA
     }
     mbar_init(tfull_bar, 1);
     mbar_init(tempty_bar, 16);         // eight epilogue warps of each CTA
@@ -330,48 +334,93 @@ gemm_mxfp8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
 
   if (warp == 0) {
     if (lane == 0) {
-      uint32_t it = 0;
+      uint32_t s = 0, phase = 1;
       bool ok = true;
+      const uint32_t fb0 = mapa(full_bar(0), 0);                       // CTA 0 counts the bytes of both
       for (int tile = unit; tile < num_tiles && ok; tile += num_units) {
         int tm, tn;
         tile_coord(tile, tm, tn);
         const int mt = tm * 2 + (int)cta_rank;                       // 128-row tile of A staged here
-        for (int kb = 0; kb < num_kb; ++kb, ++it) {
-          const int s = it % kPStages;
-          if (!mbar_wait_cluster(empty_bar(s), ((it / kPStages) & 1u) ^ 1u, abort_flag)) { ok = false; break; }
+        const int b_row = tn * BN2 + (int)cta_rank * (BN2 / 2);
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait_cluster(empty_bar(s), phase, abort_flag)) { ok = false; break; }
           const uint32_t sa = base + s * kDataBytes, sb = sa + kPABytes, ssf = sf_base + s * kSfStage;
-          const uint32_t fb = mapa(full_bar(s), 0);                  // CTA 0 counts the bytes of both
-          mbar_expect_tx_cluster(fb, kStageTx);
-          tma_load_2d_pair(sa, &tmap_a, fb, kb * BK, mt * BM);
-          tma_load_2d_pair(sb, &tmap_b, fb, kb * BK, tn * BN2 + (int)cta_rank * (BN2 / 2));
-          tma_load_3d_pair(ssf, &tmap_sfa, fb, 0, kb, mt);
-          tma_load_3d_pair(ssf + kSfBytes, &tmap_sfb, fb, 0, kb, tn * 2);
+          const uint32_t fb = fb0 + 8u * s;
+          if (p.debug & 1) {
+            mbar_arrive_cluster(fb);
+            mbar_arrive(sf_full_bar(s));
+          } else {
+            mbar_expect_tx_cluster(fb, kDataBytes);
+            tma_load_2d_pair(sa, &tmap_a, fb, kb * BK, mt * BM);
+            tma_load_2d_pair(sb, &tmap_b, fb, kb * BK, b_row);
+            mbar_expect_tx(sf_full_bar(s), kSfStage);                  // scales: this CTA's own barrier
+            tma_load_3d(ssf, &tmap_sfa, sf_full_bar(s), 0, kb, mt);
+            tma_load_3d(ssf + kSfBytes, &tmap_sfb, sf_full_bar(s), 0, kb, tn * 2);
+          }
+          if (++s == kPStages) { s = 0; phase ^= 1u; }
         }
       }
     }
   } else if (warp == 1) {
     if (lane == 0 && cta_rank == 0) {
-      uint32_t it = 0, tcount = 0;
+      // One thread feeds a tensor pipe that retires a stage in ~512 cycles, so the loop is kept short:
+      // descriptors are a constant high word and a low word that advances by adds, the stage index
+      // and barrier phase are counters (no division), the instruction descriptors are constants.
+      const uint32_t desc_hi = (1024u >> 4) | (1u << 14) | (2u << 29);        // SBO 1024 B, version 1, 128B swizzle
+      const uint32_t a_lo0 = ((base & 0x3FFFFu) >> 4) | (1u << 16);           // LBO 16 B
+      uint32_t s = 0, phase = 0, tcount = 0;
       bool ok = true;
       for (int tile = unit; tile < num_tiles && ok; tile += num_units, ++tcount) {
         if (!mbar_wait_cluster(tempty_bar, (tcount & 1u) ^ 1u, abort_flag)) { ok = false; break; }
         tc_fence_after();
-        for (int kb = 0; kb < num_kb; ++kb, ++it) {
-          const int s = it % kPStages;
-          if (!mbar_wait_cluster(full_bar(s), (it / kPStages) & 1u, abort_flag)) { ok = false; break; }
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait_cluster(full_bar(s), phase, abort_flag) || !mbar_wait_cluster(sf_ready_bar(s), phase, abort_flag)) {
+            ok = false;
+            break;
+          }
           tc_fence_after();
-          const uint32_t sa = base + s * kDataBytes, sb = sa + kPABytes, ssf = sf_base + s * kSfStage;
+          const uint32_t a_lo = a_lo0 + s * (kDataBytes >> 4), b_lo = a_lo + (kPABytes >> 4);
           const uint32_t t_sfa = tmem_base + kSfCol0 + s * 16, t_sfb = t_sfa + 4;
-          tmem_cp_sf_pair(t_sfa, make_sf_desc(ssf));
-          tmem_cp_sf_pair(t_sfb, make_sf_desc(ssf + kSfBytes));
-          tmem_cp_sf_pair(t_sfb + 4, make_sf_desc(ssf + 2 * kSfBytes));
 #pragma unroll
           for (int k = 0; k < BK / 32; ++k)
-            umma_mxf8_pair(tmem_base, make_desc(sa + k * 32, 16, 1024), make_desc(sb + k * 32, 16, 1024),
-                           make_idesc_mx(kTileM, BN2, k, k), t_sfa, t_sfb, (kb | k) != 0 ? 1u : 0u);
+            umma_mxf8_pair(tmem_base, ((uint64_t)desc_hi << 32) | (a_lo + 2u * k), ((uint64_t)desc_hi << 32) | (b_lo + 2u * k),
+                           make_idesc_mx(kTileM, BN2, k, k), t_sfa, t_sfb, k != 0 ? 1u : (uint32_t)(kb != 0));
           umma_commit_pair(empty_bar(s), 3);
+          if (++s == kPStages) { s = 0; phase ^= 1u; }
         }
         if (ok) umma_commit_pair(tfull_bar, 3);
+      }
+    }
+  } else if (warp >= 10) {
+    // ------------------------------------------------------------- scale warps (every CTA)
+    // Each of the four warps writes the stage's scale atoms (A: 4 columns, B: 8 columns) into its own
+    // 32-lane quarter of this CTA's tensor memory: the layout a tcgen05.cp "32x128b.warpx4" would
+    // produce, without putting a copy between the MMAs of the tensor pipe.
+    const uint32_t q = (uint32_t)(warp & 3);
+    const uint32_t ready_leader = mapa(sf_ready_bar(0), 0);
+    uint32_t it = 0;
+    bool ok = true;
+    for (int tile = unit; tile < num_tiles && ok; tile += num_units) {
+      for (int kb = 0; kb < num_kb; ++kb, ++it) {
+        const int s = it % kPStages;
+        if (!mbar_wait(sf_full_bar(s), (it / kPStages) & 1u, abort_flag)) { ok = false; break; }
+        if (!(p.debug & 2)) {
+          const uint32_t ssf = sf_base + s * kSfStage + (uint32_t)lane * 16u;
+          uint32_t a[4], b[8];
+          asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(a[0]), "=r"(a[1]), "=r"(a[2]), "=r"(a[3]) : "r"(ssf));
+          asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+                       : "=r"(b[0]), "=r"(b[1]), "=r"(b[2]), "=r"(b[3]) : "r"(ssf + kSfBytes));
+          asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+                       : "=r"(b[4]), "=r"(b[5]), "=r"(b[6]), "=r"(b[7]) : "r"(ssf + 2 * kSfBytes));
+          const uint32_t t = tmem_base + ((q * 32u) << 16) + kSfCol0 + (uint32_t)s * 16u;
+          asm volatile("tcgen05.st.sync.aligned.32x32b.x4.b32 [%0], {%1, %2, %3, %4};"
+                       ::"r"(t), "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]) : "memory");
+          tmem_st8(t + 4, b);
+          tmem_st_wait();
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(ready_leader + 8u * s);
       }
     }
   } else {
@@ -380,7 +429,7 @@ gemm_mxfp8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
     uint32_t tcount = 0;
     bool ok = true;
     const uint32_t te_leader = mapa(tempty_bar, 0);
-    const uint32_t buf = epi_base + (uint32_t)(warp - 2) * 4096u;
+    const uint32_t buf = epi_base + (uint32_t)(warp - 2) * 2048u;
     for (int tile = unit; tile < num_tiles && ok; tile += num_units, ++tcount) {
       int tm, tn;
       tile_coord(tile, tm, tn);
@@ -404,20 +453,20 @@ gemm_mxfp8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(te_leader);
 #pragma unroll
-      for (int c = 0; c < 2; ++c) {
+      for (int c = 0; c < 4; ++c) {
         if (lane == 0) tma_store_wait_read<0>();   // the previous store has read the staging tile
         __syncwarp();
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          const uint32_t dst = buf + (uint32_t)lane * 128u + (uint32_t)((j ^ (lane & 7)) << 4);
-          const int e = c * 32 + j * 4;
+        for (int j = 0; j < 4; ++j) {              // 64-byte rows, 16-byte chunks XOR-swizzled by (row / 2) % 4
+          const uint32_t dst = buf + (uint32_t)lane * 64u + (uint32_t)((j ^ ((lane >> 1) & 3)) << 4);
+          const int e = c * 16 + j * 4;
           asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(packed[e]), "r"(packed[e + 1]),
                        "r"(packed[e + 2]), "r"(packed[e + 3])
                        : "memory");
         }
         fence_proxy_async_smem();
         __syncwarp();
-        const int col0 = n0 + c * 64;
+        const int col0 = n0 + c * 32;
         if (lane == 0 && col0 < p.N && m0 < p.M) {
           tma_store_2d(&tmap_c, buf, col0, m0);
           tma_store_commit();
@@ -440,14 +489,15 @@ gemm_mxfp8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
 }  // namespace gemm_mx
 
 static CUtensorMap make_tmap_2d_t(const void* ptr, CUtensorMapDataType dt, uint64_t esz, uint64_t inner, uint64_t outer,
-                                  uint32_t box_inner, uint32_t box_outer) {
+                                  uint32_t box_inner, uint32_t box_outer,
+                                  CUtensorMapSwizzle swizzle = CU_TENSOR_MAP_SWIZZLE_128B) {
   CUtensorMap map;
   const cuuint64_t dims[2] = {inner, outer};
   const cuuint64_t strides[1] = {inner * esz};
   const cuuint32_t box[2] = {box_inner, box_outer};
   const cuuint32_t elem[2] = {1, 1};
   const CUresult r = cuTensorMapEncodeTiled(&map, dt, 2, const_cast<void*>(ptr), dims, strides, box, elem,
-                                            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                            CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle,
                                             CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   TORCH_CHECK(r == CUDA_SUCCESS, "cuTensorMapEncodeTiled (mxfp8 gemm) failed with code ", (int)r);
   return map;
@@ -467,6 +517,8 @@ static CUtensorMap make_tmap_sf(const void* ptr, uint64_t row_tiles, uint64_t k_
   return map;
 }
 
+static int g_mx_debug = 0;
+void gemm_mx_set_debug(int64_t v) { g_mx_debug = (int)v; }
 static int g_mx_variant = 0;   // 0: by shape, 1: one CTA per tile, 2: CTA pairs
 void gemm_mx_set_variant(int64_t v) {
   TORCH_CHECK(v >= 0 && v <= 2, "gemm_mx_set_variant: 0 (auto), 1 (single CTA) or 2 (CTA pair)");
@@ -502,9 +554,12 @@ at::Tensor gemm_mxfp8(const at::Tensor& a, const at::Tensor& sfa, const at::Tens
   static at::Tensor status;
   if (!status.defined()) status = at::zeros({1}, a.options().dtype(at::kInt));
   p.status = status.data_ptr<int>();
+  p.debug = g_mx_debug;
   const bool use_pair = g_mx_variant == 2 || (g_mx_variant == 0 && M >= 512 && N >= 256);
   if (use_pair) {
     const CUtensorMap tb2 = make_tmap_2d_t(b.data_ptr(), CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, K, N, BK, pair::BN2 / 2);
+    const CUtensorMap tc2 = make_tmap_2d_t(c.data_ptr(), CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, N, M, 32, 32,
+                                           CU_TENSOR_MAP_SWIZZLE_64B);
     const CUtensorMap tsa = make_tmap_sf(sfa.data_ptr(), (M + 127) / 128, kt, 1);
     const CUtensorMap tsb = make_tmap_sf(sfb.data_ptr(), (N + 127) / 128, kt, 2);
     static bool pair_attr_set = false;
@@ -533,7 +588,7 @@ at::Tensor gemm_mxfp8(const at::Tensor& a, const at::Tensor& sfa, const at::Tens
       max_pairs = std::max(1, std::min(n, num_sms() / 2));
     }
     cfg.gridDim = dim3(2 * std::min(tiles, max_pairs));
-    C10_CUDA_CHECK(cudaLaunchKernelEx(&cfg, gemm_mxfp8_pair_kernel, ta, tb2, tcm, tsa, tsb, p));
+    C10_CUDA_CHECK(cudaLaunchKernelEx(&cfg, gemm_mxfp8_pair_kernel, ta, tb2, tc2, tsa, tsb, p));
     return c;
   }
   static bool attr_set = false;
