@@ -16,6 +16,7 @@ FAMILIES = [
     ("gpt_oss", "gpt_oss_debugmodel", "debugmodel"),
     ("muse_glimmer", "muse_glimmer_debugmodel", "debugmodel"),
     ("kimi_k2_7", "kimi_debugmodel", "debugmodel"),
+    ("kimi_k2_7", "kimi_debugmodel_muon", "debugmodel"),
     ("qwen3_5", "qwen3_5_debugmodel", "debugmodel"),
     ("qwen3_5", "qwen3_5_moe_debug", "debugmodel_moe"),
 ]

@@ -6,7 +6,9 @@ the parameter-group assignment (regex on the FQN, first match wins), the gradien
 clipping coefficient and the checkpoint view.  ``implementation`` keeps the
 reference's names: ``fused`` (our flat AdamW kernel, fp32 moments) and
 ``fused_opt_states_bf16`` (bf16 moments, fp32 math); ``foreach`` / ``for-loop`` map to
-the same kernel.  Parity: torchtitan/components/optimizer/optimizer.py:41-526.
+the same kernel.  Optimizers: ``Adam``, ``AdamW`` and ``DistMuon`` (matrix parameters; see
+:mod:`torchtitan_b200.parallel.muon`), mixed per param group.
+Parity: torchtitan/components/optimizer/optimizer.py:41-526.
 
 Non-finite protection.  The clip coefficient is a device scalar.  When the loss or
 the gradient norm is not finite the coefficient becomes NaN, the AdamW kernel then
@@ -53,27 +55,41 @@ class OptimizersContainer(Configurable):
         self.config = config
         self.engines = list(engines)
         c = config
-        if c.name not in ("AdamW", "Adam"):
-            raise NotImplementedError(f"optimizer '{c.name}' is not available (have Adam, AdamW)")
+        known = ("AdamW", "Adam", "DistMuon")
+        if c.name not in known:
+            raise NotImplementedError(f"optimizer '{c.name}' is not available (have {', '.join(known)})")
         self.optimizer_name = c.name
-        base = dict(lr=c.lr, betas=(c.beta1, c.beta2), eps=c.eps,
-                    weight_decay=c.weight_decay if c.name == "AdamW" else 0.0)
-        base.update(c.optimizer_factory_kwargs_by_name.get(c.name, {}))
-        self.param_groups: list[dict] = []
-        patterns = []
-        for pg in c.param_groups:
-            if pg.optimizer_name not in ("AdamW", "Adam"):
-                raise NotImplementedError(f"optimizer '{pg.optimizer_name}' is not available")
-            re.compile(pg.pattern)
-            g = dict(base)
-            kw = dict(pg.optimizer_kwargs)
+
+        def group_for(name: str, kwargs: dict) -> dict:
+            """Hyper-parameters of one param group: the optimizer's defaults, the container's
+            fields, the factory kwargs of that optimizer, then the group's own kwargs."""
+            if name not in known:
+                raise NotImplementedError(f"optimizer '{name}' is not available (have {', '.join(known)})")
+            if name == "DistMuon":
+                from torchtitan_b200.parallel.muon import MUON_DEFAULTS
+
+                g = dict(MUON_DEFAULTS, lr=c.lr, weight_decay=c.weight_decay)
+            else:
+                g = dict(lr=c.lr, betas=(c.beta1, c.beta2), eps=c.eps,
+                         weight_decay=c.weight_decay if name == "AdamW" else 0.0)
+            g.update(c.optimizer_factory_kwargs_by_name.get(name, {}))
+            kw = dict(kwargs)
+            kw.pop("foreach", None)   # accepted for recipe compatibility; one implementation here
             if "betas" in kw:
                 kw["betas"] = tuple(kw["betas"])
             g.update(kw)
+            g["optimizer_name"] = name
+            return g
+
+        self.param_groups: list[dict] = []
+        patterns = []
+        for pg in c.param_groups:
+            re.compile(pg.pattern)
+            g = group_for(pg.optimizer_name, pg.optimizer_kwargs)
             g["pattern"] = pg.pattern
             self.param_groups.append(g)
             patterns.append(pg.pattern)
-        default = dict(base)
+        default = group_for(c.name, {})
         default["pattern"] = None
         self.param_groups.append(default)
         self.group_members: list[list[str]] = [[] for _ in self.param_groups]

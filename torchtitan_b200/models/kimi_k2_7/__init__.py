@@ -1,8 +1,8 @@
 """Kimi / Moonlight family: DeepSeek-V3 style decoders (multi-head latent attention, shared
 experts, sigmoid routing) with Moonshot's hyper-parameters.  Flavors: debugmodel, moonlight
-(16B-A3B) and kimi_k2 (1T-A32B); parity: torchtitan/models/kimi_k2_7/__init__.py.  The vision tower
-of the VL flavors and the DistMuon optimizer recipes are not built here; the text decoders train
-with the framework's sharded AdamW.
+(16B-A3B) and kimi_k2 (1T-A32B); parity: torchtitan/models/kimi_k2_7/__init__.py.  The training
+recipes put the matrix parameters on DistMuon (``config_registry.kimi_muon_optimizer``) and the rest
+on AdamW.  The vision tower of the VL flavors is not built here.
 """
 
 from __future__ import annotations

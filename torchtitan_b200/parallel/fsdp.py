@@ -468,6 +468,17 @@ class ShardedModel:
             if not u.grad_shard_valid:
                 continue
             g = self._grad_of(u)
+            runs = _group_runs(u)
+            if any(groups[gi].get("optimizer_name") == "DistMuon" for gi, _a, _b in runs) or any(
+                    groups[s.group_idx].get("optimizer_name") == "DistMuon" for s in u.slots):
+                # Muon needs whole matrices: owner-computes over the unit's group (parallel/muon.py)
+                from .muon import muon_unit_step
+
+                muon_unit_step(self, u, groups, runs, step, grad_scale)
+                if fused_ag and u.size > 1:
+                    dist.all_gather_into_tensor(u.flat_param, u.shard_view(u.flat_param).clone(), group=u.group)
+                u.grad_shard_valid = False
+                continue
             if fused_ag and u.size > 1:
                 # update + all-gather in one kernel: refreshed weights are stored to every peer
                 self._symm.adamw_allgather(u, _group_runs(u), groups, step, grad_scale.reshape(1), g)
