@@ -13,6 +13,7 @@ FAMILIES = [
     ("qwen3", "qwen3_debugmodel", "debugmodel"),
     ("qwen3", "qwen3_moe_debug", "debugmodel_moe"),
     ("deepseek_v3", "deepseek_v3_debugmodel", "debugmodel"),
+    ("deepseek_v3", "deepseek_v3_debugmodel_mtp", "debugmodel_mtp"),
     ("gpt_oss", "gpt_oss_debugmodel", "debugmodel"),
     ("muse_glimmer", "muse_glimmer_debugmodel", "debugmodel"),
     ("kimi_k2_7", "kimi_debugmodel", "debugmodel"),
@@ -107,3 +108,49 @@ def test_flux_flow_matching_trains():
     assert all(l == l for l in losses)
     assert abs(losses[0] - 2.0) < 0.5    # the model starts as the zero map: E|noise - x0|^2 = 2
     assert losses[-1] < 0.8 * losses[0]
+
+
+def test_mtp_roll_respects_documents():
+    from torchtitan_b200.models.deepseek_v3.mtp import roll_mtp_sequence
+
+    seq = torch.tensor([10, 11, 12, 20, 21])
+    pos = torch.tensor([0, 1, 2, 0, 1])
+    out, valid = roll_mtp_sequence(seq, shift=1, fill_value=-1, positions=pos, return_valid_mask=True)
+    assert out.tolist() == [11, 12, -1, 21, -1] and valid.tolist() == [True, True, False, True, False]
+    assert roll_mtp_sequence(seq, shift=2, fill_value=-1, positions=pos).tolist() == [12, -1, -1, -1, -1]
+    assert roll_mtp_sequence(seq, shift=2, fill_value=0).tolist() == [12, 20, 21, 0, 0]
+
+
+def test_mtp_loss_is_main_plus_scaled_depth_mean():
+    """The trainer's MTP loss equals the formula evaluated on materialised logits."""
+    from torchtitan_b200.components.loss import IGNORE_INDEX
+    from torchtitan_b200.models.deepseek_v3.mtp import MTPDecoder, roll_mtp_sequence
+
+    spec = get_model_spec("deepseek_v3", "debugmodel_mtp")
+    assert isinstance(spec.model, MTPDecoder.Config) and len(spec.model.mtp_layers) == 2
+    model = spec.model.build()
+    model.init_states(seed=3)
+    T = 48
+    g = torch.Generator().manual_seed(1)
+    ids = torch.randint(0, 2048, (T + 1,), generator=g)
+    tok, lab = ids[:-1], ids[1:].clone()
+    pos = torch.cat([torch.arange(30), torch.arange(18)])
+    logits = model(tok, pos)
+    assert isinstance(logits, list) and len(logits) == 3
+    ce = lambda lg, lb: torch.nn.functional.cross_entropy(lg.float(), lb, ignore_index=IGNORE_INDEX, reduction="sum")
+    want = ce(logits[0], lab) + 0.3 / 2 * sum(
+        ce(logits[k], roll_mtp_sequence(lab, shift=k, fill_value=IGNORE_INDEX, positions=pos)) for k in (1, 2))
+    want = want / T
+
+    from torchtitan_b200.components.loss import LinearCrossEntropyLoss
+    from torchtitan_b200.models.deepseek_v3.mtp import MTPLoss
+
+    inner = LinearCrossEntropyLoss()
+    inner.set_lm_head(model.lm_head)
+    loss_fn = MTPLoss(inner, mtp_scale=0.3)
+    hidden = model(tok, pos, return_hidden=True)
+    got = loss_fn(hidden, lab, torch.tensor(float(T)), positions=pos)
+    assert torch.allclose(got, want, rtol=1e-4), (got, want)
+    got.backward()
+    assert all(p.grad is not None or getattr(p, "main_grad", None) is not None
+               for n, p in model.named_parameters() if "mtp_layers" in n and "moe" not in n)

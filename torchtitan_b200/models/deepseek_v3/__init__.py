@@ -23,9 +23,9 @@ def build_deepseek_v3_config(*, vocab_size, dim, inter_dim, moe_inter_dim, n_lay
                              n_limited_groups=1, score_func="softmax", route_scale=1.0, route_norm=False,
                              q_lora_rank=0, kv_lora_rank=512, qk_nope_head_dim=128, qk_rope_head_dim=64, v_head_dim=128,
                              mscale=0.70, rope_theta=10000.0, rope_factor=40.0, original_seq_len=4096,
-                             max_context_length=4096, load_balance_coeff=1e-3) -> Decoder.Config:
+                             max_context_length=4096, load_balance_coeff=1e-3, n_mtp_layers=0, mtp_scale=0.3) -> Decoder.Config:
     layers = []
-    for i in range(n_layers):
+    for i in range(n_layers + n_mtp_layers):
         out_std = 0.02 / (2 * (i + 1)) ** 0.5
         attn = MLAttention.Config(
             dim=dim, n_heads=n_heads, q_lora_rank=q_lora_rank, kv_lora_rank=kv_lora_rank,
@@ -49,19 +49,33 @@ def build_deepseek_v3_config(*, vocab_size, dim, inter_dim, moe_inter_dim, n_lay
                 shared_hidden_dim=n_shared_experts * moe_inter_dim,
                 shared_experts=FeedForward.Config(w13=Linear.Config(init_std=0.02), w2=Linear.Config(init_std=out_std)),
                 load_balance_coeff=load_balance_coeff)
-        layers.append(TransformerBlock.Config(layer_id=i, attention=attn, feed_forward=ff, moe=moe,
-                                              attention_norm=RMSNorm.Config(dim=dim, eps=_EPS),
-                                              ffn_norm=RMSNorm.Config(dim=dim, eps=_EPS)))
-    return Decoder.Config(dim=dim, vocab_size=vocab_size, n_layers=n_layers, layers=layers,
-                          tok_embeddings=Embedding.Config(init_std=1.0), norm=RMSNorm.Config(dim=dim, eps=_EPS),
-                          lm_head=Linear.Config(init_std=dim ** -0.5, init_cutoff=3.0),
-                          max_context_length=max_context_length)
+        common = dict(layer_id=i, attention=attn, feed_forward=ff, moe=moe,
+                      attention_norm=RMSNorm.Config(dim=dim, eps=_EPS), ffn_norm=RMSNorm.Config(dim=dim, eps=_EPS))
+        if i < n_layers:
+            layers.append(TransformerBlock.Config(**common))
+        else:   # multi-token prediction depths: a regular block behind the embedding / hidden fusion
+            from .mtp import MTPBlock
+
+            layers.append(MTPBlock.Config(**common, dim=dim, enorm=RMSNorm.Config(dim=dim, eps=_EPS),
+                                          hnorm=RMSNorm.Config(dim=dim, eps=_EPS), mtp_norm=RMSNorm.Config(dim=dim, eps=_EPS),
+                                          eh_proj=Linear.Config(init_std=0.02)))
+    base = dict(dim=dim, vocab_size=vocab_size, n_layers=n_layers, layers=layers[:n_layers],
+                tok_embeddings=Embedding.Config(init_std=1.0), norm=RMSNorm.Config(dim=dim, eps=_EPS),
+                lm_head=Linear.Config(init_std=dim ** -0.5, init_cutoff=3.0), max_context_length=max_context_length)
+    if n_mtp_layers:
+        from .mtp import MTPDecoder
+
+        return MTPDecoder.Config(**base, mtp_layers=layers[n_layers:], mtp_scale=mtp_scale)
+    return Decoder.Config(**base)
 
 
 deepseek_v3_configs = {
     "debugmodel": lambda: build_deepseek_v3_config(
         vocab_size=2048, dim=256, inter_dim=1024, moe_inter_dim=256, n_layers=6, n_dense_layers=1, n_heads=16,
         n_routed_experts=8, n_shared_experts=2, n_activated_experts=3, route_scale=1.0),
+    "debugmodel_mtp": lambda: build_deepseek_v3_config(
+        vocab_size=2048, dim=256, inter_dim=1024, moe_inter_dim=256, n_layers=3, n_dense_layers=1, n_heads=16,
+        n_routed_experts=8, n_shared_experts=2, n_activated_experts=3, route_scale=1.0, n_mtp_layers=2),
     "16B": lambda: build_deepseek_v3_config(
         vocab_size=102400, dim=2048, inter_dim=10944, moe_inter_dim=1408, n_layers=27, n_dense_layers=1, n_heads=16,
         n_routed_experts=64, n_shared_experts=2, n_activated_experts=6, route_scale=1.0),
@@ -73,6 +87,10 @@ deepseek_v3_configs = {
         vocab_size=129280, dim=7168, inter_dim=18432, moe_inter_dim=2048, n_layers=61, n_dense_layers=3, n_heads=128,
         n_routed_experts=256, n_shared_experts=1, n_activated_experts=8, n_expert_groups=8, n_limited_groups=4,
         score_func="sigmoid", route_norm=True, route_scale=2.5, q_lora_rank=1536, mscale=1.0),
+    "671B_mtp": lambda: build_deepseek_v3_config(
+        vocab_size=129280, dim=7168, inter_dim=18432, moe_inter_dim=2048, n_layers=61, n_dense_layers=3, n_heads=128,
+        n_routed_experts=256, n_shared_experts=1, n_activated_experts=8, n_expert_groups=8, n_limited_groups=4,
+        score_func="sigmoid", route_norm=True, route_scale=2.5, q_lora_rank=1536, mscale=1.0, n_mtp_layers=1),
 }
 
 

@@ -24,6 +24,13 @@ def deepseek_v3_debugmodel() -> Trainer.Config:
     )
 
 
+def deepseek_v3_debugmodel_mtp() -> Trainer.Config:
+    """Debug model with two multi-token-prediction depths."""
+    cfg = deepseek_v3_debugmodel()
+    cfg.model.flavor = "debugmodel_mtp"
+    return cfg
+
+
 def _full(flavor: str, tokens: int, ctx: int, lr: float, steps: int, **par) -> Trainer.Config:
     return Trainer.Config(
         model=ModelSelectConfig(name="deepseek_v3", flavor=flavor),

@@ -27,10 +27,12 @@ def count_params_and_flops(cfg, model: nn.Module | None, seq_len: int) -> tuple[
         total += emb
     active = total
     attn_flops = 0.0
-    for blk in cfg.layers:
+    for blk in list(cfg.layers) + list(getattr(cfg, "mtp_layers", None) or []):
         a = blk.attention
         n_attn, qk_dim, v_dim, heads = attention_params(a, dim)
         layer = n_attn + 2 * dim
+        if hasattr(blk, "eh_proj"):   # multi-token prediction depth: three more norms and the fusion projection
+            layer += 3 * dim + 2 * dim * dim
         if hasattr(blk, "post_attention_norm"):
             layer += 2 * dim
         layer_active = layer

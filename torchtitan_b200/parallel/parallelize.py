@@ -22,6 +22,8 @@ __all__ = ["parallelize_decoder", "apply_tensor_parallel", "decoder_units"]
 def apply_tensor_parallel(model: nn.Module, pdims, parallelism) -> TPContext | None:
     if not pdims.tp_enabled:
         return None
+    if getattr(model, "mtp_layers", None) is not None:
+        raise NotImplementedError("multi-token prediction layers are not tensor-parallel")
     tp = TPContext(group=pdims.group("tp"), size=pdims.tp, rank=pdims.local_rank("tp"),
                    sequence_parallel=parallelism.enable_sequence_parallel, comm=parallelism.tp_comm)
     if parallelism.tp_comm == "nvlink" and torch.cuda.is_available() and tp.sequence_parallel:
@@ -59,6 +61,13 @@ def decoder_units(model: nn.Module, pdims) -> list[UnitSpec]:
             units.append(UnitSpec(f"layers.{name}", [blk], param_filter=lambda fqn, p: not getattr(p, "_is_expert", False)))
         else:
             units.append(UnitSpec(f"layers.{name}", [blk]))
+    for name, blk in (getattr(model, "mtp_layers", None) or {}).items():
+        if blk.moe is not None and pdims.ep_enabled:
+            is_expert = lambda fqn, p: bool(getattr(p, "_is_expert", False))
+            units.append(UnitSpec(f"mtp_layers.{name}.experts", [blk], group_name="efsdp", param_filter=is_expert))
+            units.append(UnitSpec(f"mtp_layers.{name}", [blk], param_filter=lambda fqn, p: not getattr(p, "_is_expert", False)))
+        else:
+            units.append(UnitSpec(f"mtp_layers.{name}", [blk]))
     tail = [m for m in ((model.tok_embeddings if tied else None), model.norm, model.lm_head) if m is not None]
     if tail:
         units.append(UnitSpec("output", tail))
@@ -101,6 +110,10 @@ def parallelize_decoder(model: nn.Module, *, pdims, job_config, device: torch.de
         by_name = {u.name: u for u in engine.units}
         for name, blk in model.layers.items():
             for key in (f"layers.{name}", f"layers.{name}.experts"):
+                if key in by_name:
+                    hooks.append((by_name[key], blk))
+        for name, blk in (getattr(model, "mtp_layers", None) or {}).items():
+            for key in (f"mtp_layers.{name}", f"mtp_layers.{name}.experts"):
                 if key in by_name:
                     hooks.append((by_name[key], blk))
         if "output" in by_name and model.norm is not None:

@@ -205,6 +205,11 @@ class Trainer(Configurable):
                     self.loss_fn.set_lm_head(model.lm_head, tp=model.tp,
                                              softcap=getattr(model_cfg, "final_logit_softcap", None),
                                              multiplier=getattr(model_cfg, "final_logit_multiplier", 1.0))
+                if getattr(model, "mtp_layers", None) is not None:
+                    # multi-token prediction: the same loss on every depth's output, weighted
+                    from torchtitan_b200.models.deepseek_v3.mtp import MTPLoss
+
+                    self.loss_fn = MTPLoss(self.loss_fn, mtp_scale=getattr(model_cfg, "mtp_scale", 0.3))
         self.model = self.model_parts[0]
 
         nparams, flops = model_cfg.get_nparams_and_flops(None, c.training.max_context_length)
@@ -318,7 +323,10 @@ class Trainer(Configurable):
                 pred = model(tokens, positions, ctx, return_hidden=True)
             else:
                 pred = model(tokens, positions, ctx)
-            loss = self.loss_fn(pred, labels, global_valid)
+            if getattr(self.loss_fn, "needs_positions", False):
+                loss = self.loss_fn(pred, labels, global_valid, positions=positions)
+            else:
+                loss = self.loss_fn(pred, labels, global_valid)
             del pred
             loss.backward()
             self.engines[0].finish_backward()
