@@ -78,7 +78,10 @@ def test_nvlink_engine_matches_nccl(tmp_path):
     run_distributed(_train, 2, "nvlink", b, backend="nccl")
     ra, rb = torch.load(a), torch.load(b)
     assert torch.allclose(ra["losses"], rb["losses"], atol=2e-2), (ra["losses"], rb["losses"])
-    assert torch.allclose(ra["params"], rb["params"], atol=3e-2), float((ra["params"] - rb["params"]).abs().max())
+    # AdamW's g / (|g| + eps) turns last-bit differences of near-zero gradients (reduction order) into
+    # up to one learning rate per step for single elements: bound the maximum loosely, the mean tightly
+    d = (ra["params"] - rb["params"]).abs()
+    assert float(d.max()) <= 0.1 and float(d.mean()) <= 1e-3, (float(d.max()), float(d.mean()))
 
 
 def _rs_ag(rank, world, out_path):
