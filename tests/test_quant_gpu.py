@@ -124,3 +124,32 @@ def test_quant_linear_block_scaled_matches_emulated():
         outs.append((y.detach().float(), x.grad.float(), lin.weight.grad.float()))
     for a, b in zip(*outs):
         assert (a - b).abs().max().item() <= 1e-2 * b.abs().max().item()
+
+
+def test_quant_grouped_linear_padded_layout():
+    """Expert GEMMs with MXFP8 numerics on the tcgen05 grouped GEMM against per-expert PyTorch."""
+    from torchtitan_b200.components.quantization.grouped import quant_grouped_linear
+
+    ext.require()
+    torch.manual_seed(4)
+    E, N, K = 3, 256, 128
+    starts = [0, 256, 256, 640]            # padded groups (multiples of 128); expert 1 is empty
+    offs = torch.tensor(starts, dtype=torch.int32, device="cuda")
+    x = torch.randn(starts[-1], K, device="cuda").bfloat16().requires_grad_()
+    w = (torch.randn(E, N, K, device="cuda") * 0.1).bfloat16().requires_grad_()
+    y = quant_grouped_linear(x, w, offs, "mxfp8", True)
+    g = torch.randn_like(y)
+    y.backward(g)
+    fq = lambda t, a: ops_fq(t, a)
+    ops_fq = ext.require().mxfp8_fake_quant
+    for e in range(E):
+        lo, hi = starts[e], starts[e + 1]
+        if hi == lo:
+            assert float(w.grad[e].abs().max()) == 0.0
+            continue
+        xe, ge, we = x.detach()[lo:hi].contiguous(), g[lo:hi].contiguous(), w.detach()[e].contiguous()
+        want_y = fq(xe, 1).float() @ fq(we, 1).float().t()
+        want_dx = fq(ge, 1).float() @ fq(we, 0).float()
+        want_dw = fq(ge, 0).float().t() @ fq(xe, 0).float()
+        for got, want in ((y[lo:hi], want_y), (x.grad[lo:hi], want_dx), (w.grad[e], want_dw)):
+            assert (got.float() - want).abs().max().item() <= 1e-2 * want.abs().max().item() + 1e-3

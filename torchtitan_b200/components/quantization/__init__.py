@@ -8,7 +8,7 @@ from __future__ import annotations
 
 __all__ = ["apply_converters", "CONVERTERS", "has_quantization"]
 
-QUANT = ("mxfp8", "float8", "nvfp4")
+QUANT = ("mxfp8", "float8", "nvfp4", "mxfp8_experts", "float8_experts")
 
 
 def _registry():
@@ -16,10 +16,14 @@ def _registry():
     from .float8 import float8_converter
     from torchtitan_b200.components.lora import lora_converter
 
-    return {"mxfp8": mxfp8_converter, "float8": float8_converter, "lora": lora_converter}
+    from .grouped import quantize_experts
+
+    return {"mxfp8": mxfp8_converter, "float8": float8_converter, "lora": lora_converter,
+            "mxfp8_experts": lambda cfg, arg, job: quantize_experts(cfg, "mxfp8"),
+            "float8_experts": lambda cfg, arg, job: quantize_experts(cfg, "float8_rowwise")}
 
 
-CONVERTERS = ("mxfp8", "float8", "lora")
+CONVERTERS = ("mxfp8", "float8", "mxfp8_experts", "float8_experts", "lora")
 
 
 def has_quantization(names) -> bool:

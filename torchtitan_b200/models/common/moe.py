@@ -66,11 +66,15 @@ class GroupedExperts(Module):
         num_experts: int = 0
         init_std: float = 0.02
         out_init_std: float = 0.02
+        quant_recipe: str | None = None
+        """``mxfp8`` / ``float8_rowwise``: block-scaled fp8 numerics for the three grouped GEMMs
+        (set by the grouped-experts quantisation converters)."""
 
     def __init__(self, config: "GroupedExperts.Config", **_):
         super().__init__(config)
         c = config
         self.num_experts = c.num_experts
+        self.quant_recipe = c.quant_recipe
         self.w1_EFD = nn.Parameter(torch.empty(c.num_experts, c.hidden_dim, c.dim))
         self.w2_EDF = nn.Parameter(torch.empty(c.num_experts, c.dim, c.hidden_dim))
         self.w3_EFD = nn.Parameter(torch.empty(c.num_experts, c.hidden_dim, c.dim))
@@ -121,10 +125,23 @@ class GroupedExperts(Module):
         """``x[R, dim]`` in the padded expert-major layout of ``ops.moe_ops`` (``offs[E_local + 1]``)."""
         from torchtitan_b200.ops import moe_ops
 
+        if self.quant_recipe:
+            return self._quant_forward(x, offs, padded=True)
         return moe_ops.grouped_swiglu_experts(x, self.w1_EFD, self.w3_EFD, self.w2_EDF, offs)
+
+    def _quant_forward(self, x: torch.Tensor, offs: torch.Tensor, padded: bool) -> torch.Tensor:
+        from torchtitan_b200.components.quantization.grouped import quant_grouped_linear as qgl
+
+        r = self.quant_recipe
+        h = qgl(x, self.w1_EFD, offs, r, padded)
+        u = qgl(x, self.w3_EFD, offs, r, padded)
+        a = (F.silu(h.float()) * u.float()).to(x.dtype)
+        return qgl(a, self.w2_EDF, offs, r, padded)
 
     def forward(self, x: torch.Tensor, offs: torch.Tensor) -> torch.Tensor:
         """``x[N, dim]`` rows sorted by local expert; ``offs[E_local]`` cumulative counts (int32)."""
+        if self.quant_recipe:
+            return self._quant_forward(x, offs, padded=False)
         h = grouped_mm(x, self.w1_EFD.transpose(-2, -1), offs)
         u = grouped_mm(x, self.w3_EFD.transpose(-2, -1), offs)
         a = (F.silu(h.float()) * u.float()).to(x.dtype)
