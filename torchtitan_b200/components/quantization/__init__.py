@@ -17,13 +17,14 @@ def _registry():
     from torchtitan_b200.components.lora import lora_converter
 
     from .grouped import quantize_experts
+    from .nvfp4 import nvfp4_converter
 
-    return {"mxfp8": mxfp8_converter, "float8": float8_converter, "lora": lora_converter,
+    return {"mxfp8": mxfp8_converter, "float8": float8_converter, "lora": lora_converter, "nvfp4": nvfp4_converter,
             "mxfp8_experts": lambda cfg, arg, job: quantize_experts(cfg, "mxfp8"),
             "float8_experts": lambda cfg, arg, job: quantize_experts(cfg, "float8_rowwise")}
 
 
-CONVERTERS = ("mxfp8", "float8", "mxfp8_experts", "float8_experts", "lora")
+CONVERTERS = ("mxfp8", "float8", "nvfp4", "mxfp8_experts", "float8_experts", "lora")
 
 
 def has_quantization(names) -> bool:
