@@ -20,6 +20,8 @@ FAMILIES = [
     ("kimi_k2_7", "kimi_debugmodel_muon", "debugmodel"),
     ("qwen3_5", "qwen3_5_debugmodel", "debugmodel"),
     ("qwen3_5", "qwen3_5_moe_debug", "debugmodel_moe"),
+    ("qwen3_5", "qwen3_5_debugmodel_vl", "debugmodel_vl"),
+    ("kimi_k2_7", "kimi_debugmodel_vl", "debugmodel_vl"),
 ]
 
 

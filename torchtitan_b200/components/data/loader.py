@@ -32,7 +32,8 @@ class BaseDataLoader(Configurable):
     @dataclass(kw_only=True, slots=True)
     class Config(Configurable.Config):
         dataset: str = "synthetic"
-        """``synthetic`` or the name of a registered text dataset (``c4``, ``c4_test`` ...)."""
+        """``synthetic``, ``synthetic_mm`` / ``mm_jsonl`` (interleaved text and images) or the name of
+        a registered text dataset (``c4``, ``c4_test`` ...)."""
         dataset_path: str | None = None
         seed: int = 42
         shuffle: bool = True
@@ -49,6 +50,10 @@ class BaseDataLoader(Configurable):
         if cls is BaseDataLoader and config is not None:
             if config.dataset == "synthetic":
                 return object.__new__(SyntheticDataLoader)
+            if config.dataset in ("synthetic_mm", "mm_jsonl"):
+                from .multimodal import MultimodalDataLoader
+
+                return object.__new__(MultimodalDataLoader)
             from .text import TextDataLoader
 
             return object.__new__(TextDataLoader)

@@ -37,6 +37,7 @@ class AttentionContext:
     cp: object | None = None  # parallel.context_parallel.CPContext
     max_doc_len: int | None = None
     kv_first: torch.Tensor | None = None  # [T_local] int32: index of the first token of each token's document
+    rope_positions: torch.Tensor | None = None  # [3, T_local] multimodal rotary positions (overrides ``positions``)
 
 
 def build_attention_context(positions: torch.Tensor, *, assume_single_document: bool = False,
@@ -152,6 +153,8 @@ class GQAttention(Module):
         else:
             qkv = self.wqkv(norm(x) if norm is not None else x)
         T = qkv.shape[0]
+        if ctx is not None and ctx.rope_positions is not None:
+            positions = ctx.rope_positions          # multimodal: [3, T] temporal / height / width
         if self.q_norm is None:
             qkv = self.rope.apply_packed_(qkv, positions, hq + hkv, hd)
         qkv = qkv.view(T, hq + 2 * hkv, hd)

@@ -201,10 +201,15 @@ class RoPE(Module):
         beta_slow: float = 1.0
         original_seq_len: int = 4096
         truncate: bool = True
+        mrope_sections: tuple[int, ...] | None = None
+        """Multimodal RoPE: how many of the ``dim / 2`` rotary frequencies follow the temporal,
+        height and width position axis.  Positions are then ``[3, T]``."""
 
     def __init__(self, config: "RoPE.Config", **_):
         super().__init__(config)
         self.interleaved = config.style == "complex"
+        if config.mrope_sections is not None and sum(config.mrope_sections) * 2 != config.dim:
+            raise ValueError(f"mrope_sections {config.mrope_sections} must sum to dim / 2 = {config.dim // 2}")
         self.register_buffer("cache", torch.empty(config.max_context_length, config.dim), persistent=False)
 
     def _table(self) -> torch.Tensor:
@@ -223,11 +228,30 @@ class RoPE(Module):
             return
         self.cache = self._table().to(dev)
 
+    def _table_for(self, positions: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+        """``(table, positions)`` for the rotation op.  Multimodal ``[3, T]`` positions become a
+        per-batch table whose row t takes every frequency from the row of its own axis' position
+        (``cos | sin`` halves alike), indexed by ``arange(T)``."""
+        if positions.dim() == 1:
+            return self.cache, positions
+        secs = self.config.mrope_sections
+        if secs is None:
+            raise ValueError("3-axis positions need RoPE.Config.mrope_sections")
+        half = self.cache.shape[1] // 2
+        axis_of_freq = torch.repeat_interleave(torch.arange(len(secs), device=positions.device),
+                                               torch.tensor(secs, device=positions.device))          # [half]
+        pos_tf = positions.long()[axis_of_freq].t()                                                   # [T, half]
+        f = torch.arange(half, device=positions.device)
+        table = torch.cat([self.cache[pos_tf, f], self.cache[pos_tf, f + half]], dim=1).contiguous()
+        return table, torch.arange(positions.shape[1], device=positions.device, dtype=torch.int64)
+
     def forward(self, x: torch.Tensor, positions: torch.Tensor) -> torch.Tensor:
-        return OF.rope(x, self.cache, positions, self.interleaved)
+        table, pos = self._table_for(positions)
+        return OF.rope(x, table, pos, self.interleaved)
 
     def apply_packed_(self, qkv: torch.Tensor, positions: torch.Tensor, n_rot_heads: int, head_dim: int) -> torch.Tensor:
-        return OF.rope_qk_(qkv, self.cache, positions, self.interleaved, n_rot_heads, head_dim)
+        table, pos = self._table_for(positions)
+        return OF.rope_qk_(qkv, table, pos, self.interleaved, n_rot_heads, head_dim)
 
 
 def ffn_hidden_dim(dim: int, multiple_of: int = 256, ffn_dim_multiplier: float | None = None) -> int:

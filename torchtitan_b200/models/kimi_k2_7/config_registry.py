@@ -50,6 +50,13 @@ def kimi_debugmodel() -> Trainer.Config:
     return cfg
 
 
+def kimi_debugmodel_vl() -> Trainer.Config:
+    cfg = kimi_debugmodel()
+    cfg.model.flavor = "debugmodel_vl"
+    cfg.dataloader.dataset = "synthetic_mm"
+    return cfg
+
+
 def kimi_debugmodel_muon() -> Trainer.Config:
     cfg = kimi_debugmodel()
     cfg.optimizer = kimi_muon_optimizer("debugmodel", cfg.optimizer.lr)

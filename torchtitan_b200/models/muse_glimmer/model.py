@@ -71,7 +71,8 @@ class MuseAttention(GQAttention):
         k = self.k_norm(qkv[:, hq:hq + hkv])
         v = qkv[:, hq + hkv:]
         if self.use_rope:
-            q, k = self.rope(q, positions), self.rope(k, positions)
+            rp = ctx.rope_positions if ctx is not None and ctx.rope_positions is not None else positions
+            q, k = self.rope(q, rp), self.rope(k, rp)
         ctx = ctx or AttentionContext()
         o = OF.attention(q, k, v, scale=self.scale, causal=True, doc_ids=ctx.doc_ids, window=self.window,
                          kv_first=ctx.kv_first)

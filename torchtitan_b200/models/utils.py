@@ -54,6 +54,14 @@ def count_params_and_flops(cfg, model: nn.Module | None, seq_len: int) -> tuple[
         total += layer
         active += layer_active
         attn_flops += 6 * heads * (qk_dim + v_dim) * seq_len
+    vis = getattr(cfg, "vision_encoder", None)
+    if vis is not None:     # vision tower: counted as parameters; its FLOPs depend on the images, not on seq_len
+        d, mlp, dm = vis.dim, vis.mlp_dim, vis.dim * vis.spatial_merge ** 2
+        n_blocks = len(vis.layers) or vis.n_layers
+        v = vis.in_channels * vis.patch_size ** 2 * d + d
+        v += n_blocks * (3 * d * d + 3 * d + d * d + d + d * mlp + mlp + mlp * d + d + 4 * d)
+        v += 2 * d + dm * dm + dm + dm * dim + dim
+        total += v
     matmul_params = active if cfg.enable_weight_tying else active - emb
     return total, 6 * matmul_params + attn_flops
 

@@ -61,6 +61,8 @@ def decoder_units(model: nn.Module, pdims) -> list[UnitSpec]:
             units.append(UnitSpec(f"layers.{name}", [blk], param_filter=lambda fqn, p: not getattr(p, "_is_expert", False)))
         else:
             units.append(UnitSpec(f"layers.{name}", [blk]))
+    if getattr(model, "vision_encoder", None) is not None:
+        units.append(UnitSpec("vision_encoder", [model.vision_encoder]))
     for name, blk in (getattr(model, "mtp_layers", None) or {}).items():
         if blk.moe is not None and pdims.ep_enabled:
             is_expert = lambda fqn, p: bool(getattr(p, "_is_expert", False))
@@ -112,6 +114,8 @@ def parallelize_decoder(model: nn.Module, *, pdims, job_config, device: torch.de
             for key in (f"layers.{name}", f"layers.{name}.experts"):
                 if key in by_name:
                     hooks.append((by_name[key], blk))
+        if "vision_encoder" in by_name:
+            hooks.append((by_name["vision_encoder"], model.vision_encoder))
         for name, blk in (getattr(model, "mtp_layers", None) or {}).items():
             for key in (f"mtp_layers.{name}", f"mtp_layers.{name}.experts"):
                 if key in by_name:

@@ -231,12 +231,17 @@ class Trainer(Configurable):
         self.lr_schedulers: LRSchedulersContainer = c.lr_scheduler.build(
             optimizers=self.optimizers, training_steps=c.training.steps)
         self.tokenizer = None
-        if c.dataloader.dataset != "synthetic":
+        if c.dataloader.dataset not in ("synthetic", "synthetic_mm"):
             self.tokenizer = c.tokenizer.build(tokenizer_path=c.hf_assets_path)
+        mm_kw = {}
+        vis = getattr(model_cfg, "vision_encoder", None)
+        if vis is not None:     # the collator patchifies for this tower
+            mm_kw = dict(patch_size=vis.patch_size, spatial_merge=vis.spatial_merge, in_channels=vis.in_channels,
+                         image_token_id=model_cfg.image_token_id)
         self.dataloader = c.dataloader.build(
             dp_world_size=pd.dp_degree, dp_rank=pd.dp_rank, num_tokens_per_batch=tok_mb,
             max_context_length=c.training.max_context_length, vocab_size=model_cfg.vocab_size,
-            tokenizer=self.tokenizer)
+            tokenizer=self.tokenizer, **mm_kw)
         self.step = 0
         self.ntokens_seen = 0
         self.checkpointer = c.checkpoint.build(
@@ -297,7 +302,12 @@ class Trainer(Configurable):
         labels = labels.to(dev, non_blocking=True)
         q_pos = None
         model = self.model
+        # anything else in the batch (image patches, grids) goes to the model as keyword arguments
+        self._extra_inputs = {k: (v.to(dev, non_blocking=True) if k != "grid_hw" else v)
+                              for k, v in inputs.items() if k not in ("input", "positions")}
         if self.pdims.cp_enabled:
+            if self._extra_inputs:
+                raise NotImplementedError("multimodal batches are not supported with context parallelism")
             from torchtitan_b200.parallel.context_parallel import shard_for_cp
 
             tokens, positions, labels, q_pos = shard_for_cp(model.cp, tokens, positions, labels)
@@ -308,7 +318,7 @@ class Trainer(Configurable):
             tokens, positions, labels, q_pos = self.post_dataloading_process(inputs, labels)
         if self.pdims.pp_enabled:
             return self.pp_forward_backward_step(tokens, positions, labels, q_pos, global_valid)
-        if self._graph_runner is not None and q_pos is None:
+        if self._graph_runner is not None and q_pos is None and not self._extra_inputs:
             key = (min(self._mb_index, 1), tuple(tokens.shape))
             self._mb_index += 1
             with sl.span("fwd_bwd"):
@@ -319,10 +329,11 @@ class Trainer(Configurable):
         model = self.model
         with sl.span("fwd_bwd"):
             ctx = model.build_context(positions, q_pos)
+            extra = getattr(self, "_extra_inputs", None) or {}
             if self.loss_fn.needs_hidden:
-                pred = model(tokens, positions, ctx, return_hidden=True)
+                pred = model(tokens, positions, ctx, return_hidden=True, **extra)
             else:
-                pred = model(tokens, positions, ctx)
+                pred = model(tokens, positions, ctx, **extra)
             if getattr(self.loss_fn, "needs_positions", False):
                 loss = self.loss_fn(pred, labels, global_valid, positions=positions)
             else:
