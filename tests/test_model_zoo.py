@@ -22,6 +22,7 @@ FAMILIES = [
     ("qwen3_5", "qwen3_5_moe_debug", "debugmodel_moe"),
     ("qwen3_5", "qwen3_5_debugmodel_vl", "debugmodel_vl"),
     ("kimi_k2_7", "kimi_debugmodel_vl", "debugmodel_vl"),
+    ("muse_glimmer", "muse_glimmer_debugmodel_mm", "debugmodel_mm"),
 ]
 
 

@@ -68,10 +68,21 @@ def build_muse_glimmer_config(*, dim, n_layers, n_heads, n_kv_heads, head_dim, v
         max_context_length=max_context_length)
 
 
+def _mm(text_cfg, *, dim, heads, mlp, layers, patch, image_token_id):
+    """Multimodal flavor: the shared ViT tower and adapter in front of the text decoder."""
+    from torchtitan_b200.models.common.multimodal import to_multimodal
+    from torchtitan_b200.models.common.vision_encoder import VisionEncoder
+
+    vis = VisionEncoder.Config(patch_size=patch, dim=dim, num_heads=heads, mlp_dim=mlp, n_layers=layers, spatial_merge=2)
+    return to_multimodal(text_cfg, vis, image_token_id)
+
+
 muse_glimmer_configs = {
     "debugmodel": lambda: build_muse_glimmer_config(dim=256, n_layers=8, n_heads=4, n_kv_heads=2, head_dim=64,
                                                     vocab_size=2048, max_context_length=4096,
                                                     window_pattern=[128, 128, 128, 0], output_multiplier=1.0),
+    "debugmodel_mm": lambda: _mm(muse_glimmer_configs["debugmodel"](), dim=64, heads=2, mlp=128, layers=2, patch=4,
+                                 image_token_id=2047),
     "30B": lambda: build_muse_glimmer_config(dim=6656, n_layers=52, n_heads=32, n_kv_heads=2, head_dim=128,
                                              vocab_size=202048, max_context_length=16384,
                                              window_pattern=[2048, 2048, 2048, 0], output_multiplier=0.19611613513),

@@ -24,6 +24,13 @@ def muse_glimmer_debugmodel() -> Trainer.Config:
     )
 
 
+def muse_glimmer_debugmodel_mm() -> Trainer.Config:
+    cfg = muse_glimmer_debugmodel()
+    cfg.model.flavor = "debugmodel_mm"
+    cfg.dataloader.dataset = "synthetic_mm"
+    return cfg
+
+
 def muse_glimmer_30b() -> Trainer.Config:
     return Trainer.Config(
         model=ModelSelectConfig(name="muse_glimmer", flavor="30B"),
