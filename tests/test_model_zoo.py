@@ -157,3 +157,40 @@ def test_mtp_loss_is_main_plus_scaled_depth_mean():
     got.backward()
     assert all(p.grad is not None or getattr(p, "main_grad", None) is not None
                for n, p in model.named_parameters() if "mtp_layers" in n and "moe" not in n)
+
+
+def test_flux_autoencoder_and_sampling(tmp_path):
+    from torchtitan_b200.models.flux.autoencoder import AutoEncoder
+    from torchtitan_b200.models.flux.config_registry import flux_debugmodel
+    from torchtitan_b200.models.flux.sampling import get_schedule, unpack_latents
+    from torchtitan_b200.models.flux.trainer import pack_latents
+
+    ae_cfg = AutoEncoder.Config(resolution=32, ch=32, ch_mult=(1, 2, 2, 2), num_res_blocks=1, z_channels=16)
+    ae = ae_cfg.build()
+    ae.init_states(seed=0)
+    names = set(dict(ae.named_parameters()))
+    for n in ("encoder.down.0.block.0.conv1.weight", "encoder.down.0.downsample.conv.weight", "encoder.mid.attn_1.q.weight",
+              "decoder.up.3.upsample.conv.weight", "decoder.up.0.block.1.norm2.weight", "decoder.conv_out.bias"):
+        assert n in names, n
+    assert "encoder.down.3.downsample.conv.weight" not in names and "decoder.up.0.upsample.conv.weight" not in names
+    x = torch.rand(2, 3, 32, 32) * 2 - 1
+    z = ae.encode(x)
+    assert z.shape == (2, 16, 4, 4) and ae.decode(z).shape == x.shape and ae.downsample_factor == 8
+    lat = torch.randn(2, 16, 6, 4)
+    assert torch.equal(unpack_latents(pack_latents(lat), 6, 4), lat)
+    ts = get_schedule(8, 64)
+    assert ts[0] == 1.0 and ts[-1] == 0.0 and all(a > b for a, b in zip(ts, ts[1:]))
+    assert get_schedule(8, 4096)[4] > get_schedule(8, 256)[4] > get_schedule(8, 256, shift=False)[4] - 1e-9
+
+    cfg = flux_debugmodel()
+    cfg.steps, cfg.img_size, cfg.autoencoder = 2, 32, ae_cfg
+    trainer = cfg.build()
+    trainer.train()
+    v = trainer.validate()
+    assert v == v and v > 0
+    out = str(tmp_path / "sample.png")
+    img = trainer.generate(torch.randint(0, 1024, (1, cfg.txt_len)), steps=2, guidance_scale=2.0, path=out)
+    assert img.shape == (1, 3, 32, 32) and torch.isfinite(img).all()
+    import os
+
+    assert os.path.exists(out) or os.path.exists(out[:-4] + ".ppm")

@@ -63,6 +63,12 @@ class FluxTrainer(Configurable):
         encoders: str = "random"
         dtype: str = "float32"
         log_freq: int = 1
+        autoencoder: object | None = None
+        """``AutoEncoder.Config``: train on pixels (synthetic images are encoded to latents by the
+        frozen autoencoder) instead of on synthetic latents."""
+        autoencoder_path: str | None = None
+        eval_timesteps: int = 8
+        """Validation: the flow-matching loss at this many evenly spaced noise levels."""
 
     def __init__(self, config: "FluxTrainer.Config", **_):
         super().__init__(config)
@@ -75,6 +81,13 @@ class FluxTrainer(Configurable):
         g = torch.Generator().manual_seed(c.seed + 1)
         self.t5_table = torch.randn(1024, c.model.context_in_dim, generator=g).to(self.device, self.dtype)
         self.clip_table = torch.randn(1024, c.model.vec_in_dim, generator=g).to(self.device, self.dtype)
+        self.autoencoder = None
+        if c.autoencoder is not None:
+            self.autoencoder = c.autoencoder.build()
+            self.autoencoder.init_states(seed=c.seed + 2)
+            if c.autoencoder_path:
+                self.autoencoder.load_released_weights(c.autoencoder_path)
+            self.autoencoder.to(self.device, self.dtype).requires_grad_(False).eval()
         self.opt = torch.optim.AdamW(self.model.parameters(), lr=c.lr, weight_decay=c.weight_decay)
         self.sched = torch.optim.lr_scheduler.LambdaLR(
             self.opt, lambda s: min(1.0, (s + 1) / max(1, c.warmup_steps)) * 0.5 * (1 + math.cos(math.pi * min(1.0, s / max(1, c.steps)))))
@@ -83,8 +96,14 @@ class FluxTrainer(Configurable):
 
     def synthetic_batch(self):
         c = self.config
-        lat = c.img_size // 8
-        z = torch.randn(c.batch_size, c.latent_channels, lat, lat, generator=self.gen, device=self.device, dtype=self.dtype)
+        if self.autoencoder is not None:
+            img = torch.rand(c.batch_size, 3, c.img_size, c.img_size, generator=self.gen, device=self.device, dtype=self.dtype) * 2 - 1
+            with torch.no_grad():
+                z = self.autoencoder.encode(img, generator=self.gen)
+            lat = z.shape[-1]
+        else:
+            lat = c.img_size // 8
+            z = torch.randn(c.batch_size, c.latent_channels, lat, lat, generator=self.gen, device=self.device, dtype=self.dtype)
         tokens = torch.randint(0, 1024, (c.batch_size, c.txt_len), generator=self.gen, device=self.device)
         return pack_latents(z), self.t5_table[tokens], self.clip_table[tokens[:, 0]], lat // 2
 
@@ -104,6 +123,47 @@ class FluxTrainer(Configurable):
         self.opt.step()
         self.sched.step()
         return float(loss.detach())
+
+    @torch.no_grad()
+    def validate(self, batches: int = 1) -> float:
+        """Mean flow-matching loss over ``eval_timesteps`` fixed noise levels (the stratified
+        evaluation of torchtitan/models/flux/validate.py: every sample is scored at each level
+        instead of at one random time)."""
+        was_training = self.model.training
+        self.model.eval()
+        tot, n = 0.0, 0
+        levels = [(i + 0.5) / self.config.eval_timesteps for i in range(self.config.eval_timesteps)]
+        for _ in range(batches):
+            x0, txt, y, side = self.synthetic_batch()
+            img_ids, txt_ids = make_ids(x0.shape[0], side, side, txt.shape[1], self.device)
+            noise = torch.randn(x0.shape, generator=self.gen, device=x0.device, dtype=x0.dtype)
+            for tv in levels:
+                t = torch.full((x0.shape[0],), tv, device=x0.device, dtype=x0.dtype)
+                xt = (1 - tv) * x0 + tv * noise
+                pred = self.model(xt, img_ids, txt, txt_ids, t, y)
+                tot += float(nn.functional.mse_loss(pred.float(), (noise - x0).float()))
+                n += 1
+        self.model.train(was_training)
+        return tot / max(n, 1)
+
+    @torch.no_grad()
+    def generate(self, prompt_tokens: torch.Tensor, *, steps: int = 4, guidance_scale: float | None = None, path: str | None = None):
+        """Sample images for ``prompt_tokens[B, L]`` (ids into the stand-in encoder tables); needs
+        the autoencoder.  Returns the images, and writes the first one to ``path`` when given."""
+        from .sampling import generate_image, save_image
+
+        if self.autoencoder is None:
+            raise RuntimeError("image generation needs FluxTrainer.Config.autoencoder")
+        tok = prompt_tokens.to(self.device)
+        empty = torch.zeros_like(tok)
+        img = generate_image(self.model, self.autoencoder, txt=self.t5_table[tok], vec=self.clip_table[tok[:, 0]],
+                             img_height=self.config.img_size, img_width=self.config.img_size, steps=steps,
+                             empty_txt=self.t5_table[empty] if guidance_scale is not None else None,
+                             empty_vec=self.clip_table[empty[:, 0]] if guidance_scale is not None else None,
+                             guidance_scale=guidance_scale, generator=self.gen)
+        if path is not None:
+            save_image(img, path)
+        return img
 
     def train(self) -> None:
         t0 = time.time()
