@@ -103,8 +103,8 @@ class Configurable:
     def __init_subclass__(cls, **kw):
         super().__init_subclass__(**kw)
         cfg = cls.__dict__.get("Config")
-        if cfg is None:
-            return
+        if cfg is None or cfg.__qualname__ != f"{cls.__qualname__}.Config":
+            return      # no own Config, or an alias of another component's Config (which keeps its owner)
         if not is_dataclass(cfg):
             raise TypeError(f"{cls.__qualname__}.Config must be a dataclass")
         params = getattr(cfg, "__dataclass_params__", None)
