@@ -52,6 +52,8 @@ def parse_args():
     p.add_argument("--opt-state", default="fp32", choices=["fp32", "bf16"])
     p.add_argument("--ac", default="selective")
     p.add_argument("--skip-e2e", action="store_true")
+    p.add_argument("--converters", default="", help="comma-separated model converters, e.g. mxfp8 (a separate, "
+                   "lower-precision measurement: the headline stays bf16)")
     return p.parse_args()
 
 
@@ -175,6 +177,8 @@ def main() -> None:
     )
     cfg.debug.seed = 0
     cfg.debug.enable_structured_logging = False
+    if args.converters:
+        cfg.model.converters = [c for c in args.converters.split(",") if c]
     trainer = cfg.build()
     trainer.model.single_document = True
     dev = trainer.device
@@ -266,7 +270,8 @@ def main() -> None:
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * dev_s / args.steps,
             "higher_is_better": True, "scaling": "weak",
             "vs_baseline": tokens_per_s / world / BASELINE_TOKENS_PER_SEC_PER_GPU,
-            "dtype": "bf16", "data": "synthetic uniform-random tokens, random-init weights",
+            "dtype": "bf16" if not args.converters else f"{args.converters} linears, bf16 elsewhere",
+            "data": "synthetic uniform-random tokens, random-init weights",
             "impl": "native",
             "tokens_per_sec_per_gpu": tokens_per_s / world,
             "mfu_pct": 100.0 * flops_per_token * tokens_per_s / world / 2.25e15,
