@@ -110,3 +110,28 @@ def test_byte_tokenizer_round_trip():
     t = ByteTokenizer()
     ids = t.encode("héllo")
     assert t.decode(ids) == "héllo" and ids[0] == t.bos_id
+
+
+def test_concat_and_mix_datasets(tok):
+    from torchtitan_b200.components.data.text import DATASETS, ConcatSource, MixSource, parse_composite
+
+    assert parse_composite("mix:c4_test=0.75,sft_test=0.25") == ("mix", ["c4_test", "sft_test"], [0.75, 0.25])
+    a, b = DATASETS["c4_test"].make_source(None), DATASETS["sft_test"].make_source(None)
+    cat = ConcatSource([a, b])
+    assert len(cat) == len(a) + len(b) and cat[0]["__dataset__"] == 0 and cat[len(a)]["__dataset__"] == 1
+    assert "text" in cat[0] and "question" in cat[len(a)]
+    mix = MixSource([a, b], [0.75, 0.25], seed=3)
+    picks = [mix[i]["__dataset__"] for i in range(len(mix))]
+    assert 0 < sum(picks) < len(picks)                     # both datasets appear
+    assert picks == [MixSource([a, b], [0.75, 0.25], seed=3)[i]["__dataset__"] for i in range(len(mix))]
+    # through the loader: SFT samples carry masked prompts, plain text does not
+    for name in ("concat:c4_test,sft_test", "mix:c4_test=0.5,sft_test=0.5"):
+        it = iter(_loader(tok, dataset=name, shuffle=True))
+        seen_masked = False
+        for _ in range(12):
+            inp, lab = next(it)
+            assert inp["input"].shape == (256,)
+            seen_masked |= bool(((lab == -100) & (inp["positions"] > 0)).any())
+        assert seen_masked
+    with pytest.raises(ValueError):
+        _loader(tok, dataset="mix:c4_test=1,nope=1")

@@ -32,7 +32,7 @@ from torchtitan_b200.utils.logging import logger
 from .loader import BaseDataLoader
 
 __all__ = ["TextDataLoader", "DATASETS", "DatasetSpec", "JsonlSource", "HuggingFaceSource", "TextProcessor",
-           "ChatProcessor", "register_dataset"]
+           "ChatProcessor", "register_dataset", "ConcatSource", "MixSource"]
 
 _ASSETS = os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))),
                        "tests", "assets")
@@ -175,6 +175,72 @@ def register_dataset(name: str, spec: DatasetSpec) -> None:
 
 
 # ----------------------------------------------------------------------------
+# composite datasets
+# ----------------------------------------------------------------------------
+class ConcatSource:
+    """Several random-access sources end to end; samples carry the index of their dataset so
+    that each goes through its own processor."""
+
+    random_access = True
+
+    def __init__(self, sources: list):
+        if not all(getattr(s, "random_access", True) for s in sources):
+            raise ValueError("composite datasets need random-access (non-streaming) sources")
+        self.sources = sources
+        self.starts = [0]
+        for src in sources:
+            self.starts.append(self.starts[-1] + len(src))
+
+    def __len__(self) -> int:
+        return self.starts[-1]
+
+    def __getitem__(self, i: int) -> dict:
+        import bisect
+
+        k = bisect.bisect_right(self.starts, i) - 1
+        return {"__dataset__": k, **self.sources[k][i - self.starts[k]]}
+
+
+class MixSource(ConcatSource):
+    """Weighted interleave: position i of the (virtual) epoch draws its dataset from the
+    normalised weights with a fixed seed and takes that dataset's next sample, wrapping around a
+    dataset that is exhausted (small datasets repeat, large ones are subsampled).  The epoch has
+    as many positions as all datasets together."""
+
+    def __init__(self, sources: list, weights: list[float], seed: int = 0):
+        super().__init__(sources)
+        if len(weights) != len(sources) or min(weights) <= 0:
+            raise ValueError("a dataset mix needs one positive weight per dataset")
+        n = self.starts[-1]
+        g = torch.Generator().manual_seed(seed)
+        pick = torch.multinomial(torch.tensor(weights, dtype=torch.float64), n, replacement=True, generator=g)
+        self.pick = pick.tolist()
+        counts = [0] * len(sources)
+        self.local = []
+        for k in self.pick:
+            self.local.append(counts[k] % len(sources[k]))
+            counts[k] += 1
+
+    def __getitem__(self, i: int) -> dict:
+        k = self.pick[i]
+        return {"__dataset__": k, **self.sources[k][self.local[i]]}
+
+
+def parse_composite(name: str):
+    """``concat:a,b`` -> ("concat", [a, b], None);  ``mix:a=0.7,b=0.3`` -> ("mix", [a, b], [0.7, 0.3])."""
+    kind, _, rest = name.partition(":")
+    parts = [x for x in rest.split(",") if x]
+    if kind == "concat":
+        return kind, parts, None
+    names, weights = [], []
+    for part in parts:
+        n, _, w = part.partition("=")
+        names.append(n)
+        weights.append(float(w) if w else 1.0)
+    return kind, names, weights
+
+
+# ----------------------------------------------------------------------------
 # loader
 # ----------------------------------------------------------------------------
 class TextDataLoader(BaseDataLoader):
@@ -182,13 +248,25 @@ class TextDataLoader(BaseDataLoader):
                  num_tokens_per_batch: int = 2048, max_context_length: int = 2048, vocab_size: int = 0,
                  tokenizer=None, **_):
         self.config = config
-        if config.dataset not in DATASETS:
-            raise ValueError(f"unknown dataset '{config.dataset}' (registered: {sorted(DATASETS)})")
         if tokenizer is None:
             raise ValueError("a tokenizer is required for text datasets")
-        spec = DATASETS[config.dataset]
-        self.source = spec.make_source(config.dataset_path)
-        self.process = spec.make_processor(tokenizer)
+        if config.dataset.startswith(("mix:", "concat:")):
+            # composite: ``concat:a,b`` or ``mix:a=0.7,b=0.3`` over registered datasets
+            # (parity: DatasetConcatConfig / DatasetMixConfig of torchtitan/components/data/dataset.py:197-309)
+            kind, names, weights = parse_composite(config.dataset)
+            unknown = [n for n in names if n not in DATASETS]
+            if unknown or not names:
+                raise ValueError(f"unknown dataset(s) {unknown} in '{config.dataset}' (registered: {sorted(DATASETS)})")
+            sources = [DATASETS[n].make_source(None) for n in names]
+            procs = [DATASETS[n].make_processor(tokenizer) for n in names]
+            self.source = ConcatSource(sources) if kind == "concat" else MixSource(sources, weights, seed=config.seed)
+            self.process = lambda sample: procs[sample["__dataset__"]](sample)
+        else:
+            if config.dataset not in DATASETS:
+                raise ValueError(f"unknown dataset '{config.dataset}' (registered: {sorted(DATASETS)})")
+            spec = DATASETS[config.dataset]
+            self.source = spec.make_source(config.dataset_path)
+            self.process = spec.make_processor(tokenizer)
         self.dp_world_size, self.dp_rank = dp_world_size, dp_rank
         self.T, self.ctx = num_tokens_per_batch, min(max_context_length, num_tokens_per_batch)
         self.epoch = 0

@@ -233,20 +233,23 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         tmem_ld_wait();
         const int c0 = (j_lo + i) * kBN;
         const bool edge = (c0 + kBN - 1 > hi) || (c0 < lo);
-        float m_tile = -INFINITY;
+        // Row maximum of the raw scores (the scale is positive, so it commutes with max): four
+        // independent partial maxima keep the dependent chain at 32 instead of 128 instructions.
+        if (edge) {
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
+          for (int c = 0; c < 4; ++c)
 #pragma unroll
-          for (int e = 0; e < 32; ++e) {
-            float x = __uint_as_float(r[c][e]) * p.scale_log2;
-            if (edge) {
+            for (int e = 0; e < 32; ++e) {
               const int col = c0 + c * 32 + e;
-              if (col > hi || col < lo) x = -INFINITY;
+              if (col > hi || col < lo) r[c][e] = __float_as_uint(-INFINITY);
             }
-            r[c][e] = __float_as_uint(x);
-            m_tile = fmaxf(m_tile, x);
-          }
         }
+        float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+#pragma unroll
+          for (int e = 0; e < 32; ++e) mx[e & 3] = fmaxf(mx[e & 3], __uint_as_float(r[c][e]));
+        const float m_tile = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * p.scale_log2;
         const float m_new = fmaxf(m_used, m_tile);
         if (__any_sync(0xffffffffu, m_new > m_used + kRescaleThreshold)) {
           // every row of this warp moves to its own new maximum; O and l are rescaled
@@ -265,19 +268,22 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
           }
           m_used = m_new;
         }
-        const float m_eff = (m_used == -INFINITY) ? 0.f : m_used;
+        // P = exp2(S scale - m): one FFMA and one MUFU per element; four partial row sums
+        const float neg_m = (m_used == -INFINITY) ? 0.f : -m_used;
+        float ls[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
           uint32_t pk[16];
 #pragma unroll
           for (int e = 0; e < 16; ++e) {
-            const float p0 = exp2f(__uint_as_float(r[c][2 * e]) - m_eff);
-            const float p1 = exp2f(__uint_as_float(r[c][2 * e + 1]) - m_eff);
-            l += p0 + p1;
+            const float p0 = exp2f(fmaf(__uint_as_float(r[c][2 * e]), p.scale_log2, neg_m));
+            const float p1 = exp2f(fmaf(__uint_as_float(r[c][2 * e + 1]), p.scale_log2, neg_m));
+            ls[e & 3] += p0 + p1;
             pk[e] = pack_bf16(p0, p1);
           }
           tmem_st16(s_t + c * 16, pk);
         }
+        l += (ls[0] + ls[1]) + (ls[2] + ls[3]);
         tmem_st_wait();
         tc_fence_before();
         __syncwarp();
