@@ -153,3 +153,31 @@ def test_quant_grouped_linear_padded_layout():
         want_dw = fq(ge, 0).float().t() @ fq(xe, 0).float()
         for got, want in ((y[lo:hi], want_y), (x.grad[lo:hi], want_dx), (w.grad[e], want_dw)):
             assert (got.float() - want).abs().max().item() <= 1e-2 * want.abs().max().item() + 1e-3
+
+
+def test_mx_grouped_linear_block_scaled_matches_emulated():
+    """Grouped expert GEMMs on the block-scaled kernel against the emulated (exact fp8 in bf16) path."""
+    from torchtitan_b200.components.quantization.grouped import quant_grouped_linear
+
+    ext.require()
+    torch.manual_seed(6)
+    E, N, K = 4, 256, 384
+    starts = [0, 128, 128, 512, 768]            # expert 1 is empty; 128 rows of tail padding
+    R = 896
+    offs = torch.tensor(starts, dtype=torch.int32, device="cuda")
+    outs = []
+    for block_scaled in (True, False):
+        g = torch.Generator(device="cuda").manual_seed(9)
+        x = torch.randn(R, K, device="cuda", generator=g).bfloat16()
+        x[starts[-1]:] = 0
+        x.requires_grad_()
+        w = (torch.randn(E, N, K, device="cuda", generator=g) * 0.1).bfloat16().requires_grad_()
+        y = quant_grouped_linear(x, w, offs, "mxfp8", True, block_scaled=block_scaled)
+        gy = torch.randn(y.shape, device="cuda", generator=g).bfloat16()
+        gy[starts[-1]:] = 0
+        y.backward(gy)
+        outs.append((y.detach().float()[:starts[-1]], x.grad.float()[:starts[-1]], w.grad.float()))
+    assert ext.require().gemm_status(True) == 0
+    for a, b in zip(*outs):
+        assert (a - b).abs().max().item() <= 1e-2 * b.abs().max().item() + 1e-3
+    assert float(outs[0][2][1].abs().max()) == 0.0      # the empty expert gets a zero gradient

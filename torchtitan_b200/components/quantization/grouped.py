@@ -8,8 +8,9 @@ layout every expert's rows start on a multiple of 128, so 32-row scale blocks ne
 experts and one column-wise quantiser call covers all experts; in the unpadded (sorted rows)
 layout the token-axis quantisation runs per expert.
 
-The GEMMs run on the operands' exact fp8 values held in bf16 (tcgen05 grouped GEMM on a GPU,
-PyTorch loops on CPU).  Parity: torchtitan/components/quantization/mx.py:104-206
+With ``mxfp8`` on a GPU, in the padded layout and with 128-multiple sizes, the three GEMMs run on
+the block-scaled tensor-core kernel (``gemm_mxfp8_grouped``); otherwise on the operands' exact fp8
+values held in bf16 (tcgen05 grouped GEMM on a GPU, PyTorch loops on CPU).  Parity: torchtitan/components/quantization/mx.py:104-206
 (``MXFP8GroupedExpertsConverter``: torchao ``_quantize_then_scaled_grouped_mm``, recipe
 ``mxfp8_rceil``) and float8.py:216-266 (``Float8GroupedExpertsConverter``).
 """
@@ -68,6 +69,52 @@ def _fq_tokens(t: torch.Tensor, recipe: str, offs, padded: bool) -> torch.Tensor
     return out
 
 
+def _mx_native(x: torch.Tensor, w: torch.Tensor, recipe: str, padded: bool) -> bool:
+    """The block-scaled grouped GEMM takes the padded layout and 128-multiples everywhere."""
+    return (recipe == "mxfp8" and _native(x, padded) and w.shape[1] % 128 == 0 and w.shape[2] % 128 == 0
+            and x.shape[0] % 128 == 0 and x.shape[0] > 0)
+
+
+class _MXGroupedLinearFn(torch.autograd.Function):
+    """All three grouped GEMMs on ``tcgen05.mma.kind::mxf8f6f4.block_scale`` (``gemm_mxfp8_grouped``)."""
+
+    @staticmethod
+    def forward(ctx, x, w, offs):
+        from torchtitan_b200.ops import ext, functional as OF
+
+        ops = ext.require()
+        E, N, K = w.shape
+        xq, xs = ops.mxfp8_quantize_tiled(x.contiguous())
+        wq, ws = ops.mxfp8_quantize_tiled(w.reshape(E * N, K).contiguous())
+        OF._count(3)
+        ctx.save_for_backward(x, w, offs)
+        return ops.gemm_mxfp8_grouped(xq, xs, wq, ws, offs, 1)
+
+    @staticmethod
+    def backward(ctx, dy):
+        from torchtitan_b200.ops import ext, functional as OF
+
+        ops = ext.require()
+        x, w, offs = ctx.saved_tensors
+        E, N, K = w.shape
+        dy = dy.contiguous()
+        dx = dw = None
+        if ctx.needs_input_grad[0]:
+            # contraction over the output features: every expert matrix transposed, then stacked [E K, N]
+            gq, gs = ops.mxfp8_quantize_tiled(dy)
+            wt = w.transpose(1, 2).contiguous().view(E * K, N)
+            tq, ts = ops.mxfp8_quantize_tiled(wt)
+            OF._count(3)
+            dx = ops.gemm_mxfp8_grouped(gq, gs, tq, ts, offs, 1)
+        if w.requires_grad:
+            # contraction over each expert's tokens: both operands transposed by the quantiser
+            gq, gs = ops.mxfp8_quantize_tiled_t(dy)
+            xq, xs = ops.mxfp8_quantize_tiled_t(x.contiguous())
+            OF._count(3)
+            dw = OF._deliver_wgrad(w, ops.gemm_mxfp8_grouped(gq, gs, xq, xs, offs, 2).view(E, N, K))
+        return dx, dw, None
+
+
 class _QuantGroupedLinearFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, w, offs, recipe, padded):
@@ -97,9 +144,12 @@ class _QuantGroupedLinearFn(torch.autograd.Function):
         return dx, dw, None, None, None
 
 
-def quant_grouped_linear(x: torch.Tensor, w: torch.Tensor, offs: torch.Tensor, recipe: str, padded: bool) -> torch.Tensor:
+def quant_grouped_linear(x: torch.Tensor, w: torch.Tensor, offs: torch.Tensor, recipe: str, padded: bool,
+                         block_scaled: bool = True) -> torch.Tensor:
     if w.shape[1] % 32 or w.shape[2] % 32:
         raise ValueError("quantised grouped experts need feature dimensions that are multiples of 32")
+    if block_scaled and _mx_native(x, w, recipe, padded):
+        return _MXGroupedLinearFn.apply(x, w, offs)
     return _QuantGroupedLinearFn.apply(x, w, offs, recipe, padded)
 
 

@@ -65,6 +65,8 @@ at::Tensor mxfp8_fake_quant(const at::Tensor& x, int64_t axis);
 std::tuple<at::Tensor, at::Tensor> mxfp8_quantize_tiled(const at::Tensor& x);
 at::Tensor gemm_mxfp8(const at::Tensor& a, const at::Tensor& sfa, const at::Tensor& b, const at::Tensor& sfb);
 void gemm_mx_set_variant(int64_t v);
+at::Tensor gemm_mxfp8_grouped(const at::Tensor& a, const at::Tensor& sfa, const at::Tensor& b, const at::Tensor& sfb,
+                              const at::Tensor& offs, int64_t mode);
 void gemm_mx_set_debug(int64_t v);
 std::tuple<at::Tensor, at::Tensor> mxfp8_quantize_tiled_t(const at::Tensor& x);
 at::Tensor mxfp8_dequantize(const at::Tensor& data, const at::Tensor& scales, int64_t axis);
@@ -111,6 +113,7 @@ TORCH_LIBRARY(tb200, m) {
   m.def("mxfp8_quantize_tiled(Tensor x) -> (Tensor, Tensor)", &tb200::mxfp8_quantize_tiled);
   m.def("gemm_mxfp8(Tensor a, Tensor sfa, Tensor b, Tensor sfb) -> Tensor", &tb200::gemm_mxfp8);
   m.def("gemm_mx_set_variant(int v) -> ()", &tb200::gemm_mx_set_variant);
+  m.def("gemm_mxfp8_grouped(Tensor a, Tensor sfa, Tensor b, Tensor sfb, Tensor offs, int mode) -> Tensor", &tb200::gemm_mxfp8_grouped);
   m.def("gemm_mx_set_debug(int v) -> ()", &tb200::gemm_mx_set_debug);
   m.def("mxfp8_quantize_tiled_t(Tensor x) -> (Tensor, Tensor)", &tb200::mxfp8_quantize_tiled_t);
   m.def("mxfp8_dequantize(Tensor data, Tensor scales, int axis) -> Tensor", &tb200::mxfp8_dequantize);

@@ -41,6 +41,14 @@ struct Params {
   const uint8_t* sfb;     // tiled scales of B
   int* status;
   int debug;              // timing switches: 1 = no loads (barriers only), 2 = no scale copies
+  // grouped forms (one-CTA kernel).  mode 1: rows of A / C are grouped (padded expert-major layout,
+  // every group starts on a multiple of 128), group g multiplies with rows [g * b_group_rows, ...)
+  // of B.  mode 2: the contraction dimension is grouped (weight gradients): group g contracts
+  // columns [offs[g], offs[g+1]) of A and B and writes rows [g * M, (g + 1) * M) of C.
+  int group_mode;
+  int num_groups;
+  int b_group_rows;
+  const int* group_offs;  // [num_groups + 1], multiples of 128
 };
 
 // Instruction descriptor of the block-scaled kinds: e4m3 x e4m3, ue8m0 scales, fp32 accumulate.
@@ -103,6 +111,44 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
     tn = r / gsz;
   };
 
+  // Every role derives the same description of a tile (and skips the same tiles).
+  struct TileInfo { int skip, tm, tn, a_tile, b_tile, kb0, nkb, c_row; };
+  const int tiles_per_group = num_m * num_n;
+  const int total_tiles = p.group_mode == 2 ? tiles_per_group * p.num_groups : num_tiles;
+  auto tile_info = [&](int t) {
+    TileInfo ti;
+    int e = 0;
+    if (p.group_mode == 2) {
+      e = t / tiles_per_group;
+      t -= e * tiles_per_group;
+    }
+    tile_coord(t, ti.tm, ti.tn);
+    ti.skip = 0;
+    ti.a_tile = ti.tm;
+    ti.b_tile = ti.tn;
+    ti.kb0 = 0;
+    ti.nkb = num_kb;
+    ti.c_row = ti.tm * BM;
+    if (p.group_mode == 1) {
+      const int m0 = ti.tm * BM;
+      if (m0 >= p.group_offs[p.num_groups]) {
+        ti.skip = 1;
+      } else {
+        int lo = 0, hi = p.num_groups;     // largest g with group_offs[g] <= m0
+        while (hi - lo > 1) {
+          const int mid = (lo + hi) >> 1;
+          if (p.group_offs[mid] <= m0) lo = mid; else hi = mid;
+        }
+        ti.b_tile = lo * (p.b_group_rows / BN) + ti.tn;
+      }
+    } else if (p.group_mode == 2) {
+      ti.kb0 = p.group_offs[e] / BK;
+      ti.nkb = (p.group_offs[e + 1] - p.group_offs[e]) / BK;
+      ti.c_row = e * p.M + ti.tm * BM;
+    }
+    return ti;
+  };
+
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
       mbar_init(full_bar(s), 1);
@@ -131,18 +177,19 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
     if (lane == 0) {
       uint32_t it = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-        int tm, tn;
-        tile_coord(tile, tm, tn);
-        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+        const TileInfo ti = tile_info(tile);
+        if (ti.skip) continue;
+        for (int kk = 0; kk < ti.nkb; ++kk, ++it) {
+          const int kb = ti.kb0 + kk;
           const int s = it % kStages;
           if (!mbar_wait(empty_bar(s), ((it / kStages) & 1u) ^ 1u, abort_flag)) { ok = false; break; }
           const uint32_t sa = base + s * kStageBytes, sb = sa + kABytes, ssf = sb + kBBytes;
           mbar_expect_tx(full_bar(s), kStageBytes);
-          tma_load_2d(sa, &tmap_a, full_bar(s), kb * BK, tm * BM);
-          tma_load_2d(sb, &tmap_b, full_bar(s), kb * BK, tn * BN);
-          bulk_load(ssf, p.sfa + ((int64_t)tm * num_kb + kb) * kSfBytes, kSfBytes, full_bar(s));
-          bulk_load(ssf + kSfBytes, p.sfb + ((int64_t)tn * num_kb + kb) * kSfBytes, kSfBytes, full_bar(s));
+          tma_load_2d(sa, &tmap_a, full_bar(s), kb * BK, ti.a_tile * BM);
+          tma_load_2d(sb, &tmap_b, full_bar(s), kb * BK, ti.b_tile * BN);
+          bulk_load(ssf, p.sfa + ((int64_t)ti.a_tile * num_kb + kb) * kSfBytes, kSfBytes, full_bar(s));
+          bulk_load(ssf + kSfBytes, p.sfb + ((int64_t)ti.b_tile * num_kb + kb) * kSfBytes, kSfBytes, full_bar(s));
         }
       }
     }
@@ -150,12 +197,20 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
     if (lane == 0) {
       uint32_t it = 0, tcount = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++tcount) {
+      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+        const TileInfo ti = tile_info(tile);
+        if (ti.skip) continue;
         const int acc = tcount & 1;
-        if (!mbar_wait(tempty_bar(acc), ((tcount >> 1) & 1u) ^ 1u, abort_flag)) { ok = false; break; }
+        const uint32_t acc_parity = ((tcount >> 1) & 1u) ^ 1u;
+        ++tcount;
+        if (!mbar_wait(tempty_bar(acc), acc_parity, abort_flag)) { ok = false; break; }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
-        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+        if (ti.nkb == 0) {          // an empty group: nothing to multiply, the epilogue writes zeros
+          mbar_arrive(tfull_bar(acc));
+          continue;
+        }
+        for (int kb = 0; kb < ti.nkb; ++kb, ++it) {
           const int s = it % kStages;
           if (!mbar_wait(full_bar(s), (it / kStages) & 1u, abort_flag)) { ok = false; break; }
           tc_fence_after();
@@ -176,21 +231,29 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
     const int q = warp & 3;
     uint32_t tcount = 0, sbuf = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++tcount) {
+    const int c_rows = p.group_mode == 2 ? p.M * p.num_groups : p.M;
+    for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+      const TileInfo ti = tile_info(tile);
+      if (ti.skip) continue;
       const int acc = tcount & 1;
-      int tm, tn;
-      tile_coord(tile, tm, tn);
-      const int m0 = tm * BM, n0 = tn * BN;
-      if (!mbar_wait(tfull_bar(acc), (tcount >> 1) & 1u, abort_flag)) { ok = false; break; }
+      const uint32_t acc_parity = (tcount >> 1) & 1u;
+      ++tcount;
+      const int m0 = ti.c_row, n0 = ti.tn * BN;
+      if (!mbar_wait(tfull_bar(acc), acc_parity, abort_flag)) { ok = false; break; }
       tc_fence_after();
       const uint32_t stage0 = epi_base + (uint32_t)(warp - 2) * 8192u;
 #pragma unroll 1
       for (int c = 0; c < BN / 64; ++c) {
         uint32_t r0[32], r1[32];
         const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN + c * 64);
-        tmem_ld32(taddr, r0);
-        tmem_ld32(taddr + 32, r1);
-        tmem_ld_wait();
+        if (ti.nkb > 0) {
+          tmem_ld32(taddr, r0);
+          tmem_ld32(taddr + 32, r1);
+          tmem_ld_wait();
+        } else {
+#pragma unroll
+          for (int e = 0; e < 32; ++e) r0[e] = r1[e] = 0u;
+        }
         if (lane == 0) tma_store_wait_read<1>();
         __syncwarp();
         const uint32_t buf = stage0 + (sbuf ? 4096u : 0u);
@@ -211,7 +274,7 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
         fence_proxy_async_smem();
         __syncwarp();
         const int col0 = n0 + c * 64;
-        if (lane == 0 && col0 < p.N && m0 + q * 32 < p.M) {
+        if (lane == 0 && col0 < p.N && m0 + q * 32 < c_rows) {
           tma_store_2d(&tmap_c, buf, col0, m0 + q * 32);
           tma_store_commit();
         }
@@ -555,6 +618,7 @@ at::Tensor gemm_mxfp8(const at::Tensor& a, const at::Tensor& sfa, const at::Tens
   if (!status.defined()) status = at::zeros({1}, a.options().dtype(at::kInt));
   p.status = status.data_ptr<int>();
   p.debug = g_mx_debug;
+  p.group_mode = 0; p.num_groups = 0; p.b_group_rows = 0; p.group_offs = nullptr;
   const bool use_pair = g_mx_variant == 2 || (g_mx_variant == 0 && M >= 512 && N >= 256);
   if (use_pair) {
     const CUtensorMap tb2 = make_tmap_2d_t(b.data_ptr(), CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, K, N, BK, pair::BN2 / 2);
@@ -598,6 +662,65 @@ at::Tensor gemm_mxfp8(const at::Tensor& a, const at::Tensor& sfa, const at::Tens
   }
   const int tiles = (int)(((M + BM - 1) / BM) * ((N + BN - 1) / BN));
   gemm_mxfp8_kernel<<<std::min(tiles, num_sms()), kThreads, kSmemBytes, at::cuda::getCurrentCUDAStream()>>>(ta, tb, tcm, p);
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+  return c;
+}
+
+// Grouped MXFP8 GEMMs of the expert layers (one-CTA kernel, 128 x 128 tiles).
+//   mode 1: a [R, K] rows in the padded expert-major layout (offs[E + 1], multiples of 128),
+//           b [E * N, K] the stacked expert matrices (N % 128 == 0)  ->  C [R, N];
+//           rows at or beyond offs[E] are not written.
+//   mode 2: a [M, R], b [N, R] with the contraction dimension R grouped by offs
+//           (M % 128 == 0)  ->  C [E * M, N], zeros for an empty group.
+at::Tensor gemm_mxfp8_grouped(const at::Tensor& a, const at::Tensor& sfa, const at::Tensor& b, const at::Tensor& sfb,
+                              const at::Tensor& offs, int64_t mode) {
+  using namespace gemm_mx;
+  TORCH_CHECK(mode == 1 || mode == 2, "gemm_mxfp8_grouped: mode 1 (rows grouped) or 2 (contraction grouped)");
+  TORCH_CHECK(a.is_cuda() && b.is_cuda() && a.scalar_type() == at::kByte && b.scalar_type() == at::kByte);
+  TORCH_CHECK(a.dim() == 2 && b.dim() == 2 && a.is_contiguous() && b.is_contiguous() && a.size(1) == b.size(1));
+  TORCH_CHECK(offs.is_cuda() && offs.scalar_type() == at::kInt && offs.is_contiguous() && offs.numel() >= 2);
+  const int64_t E = offs.numel() - 1;
+  const int64_t K = a.size(1);
+  TORCH_CHECK(K % BK == 0, "gemm_mxfp8_grouped: the contraction dimension must be a multiple of 128");
+  const int64_t kt = K / BK;
+  int64_t M, N, c_rows;
+  if (mode == 1) {
+    TORCH_CHECK(b.size(0) % E == 0 && (b.size(0) / E) % BN == 0, "gemm_mxfp8_grouped: b must stack E matrices of N % 128 == 0 rows");
+    M = a.size(0); N = b.size(0) / E; c_rows = M;
+  } else {
+    TORCH_CHECK(a.size(0) % BM == 0 && b.size(0) % 8 == 0, "gemm_mxfp8_grouped: mode 2 needs M % 128 == 0 and N % 8 == 0");
+    M = a.size(0); N = b.size(0); c_rows = E * M;
+  }
+  TORCH_CHECK(sfa.is_cuda() && sfa.scalar_type() == at::kByte && sfa.is_contiguous() &&
+              sfa.numel() == (a.size(0) + 127) / 128 * kt * 512, "gemm_mxfp8_grouped: sfa has the wrong size");
+  TORCH_CHECK(sfb.is_cuda() && sfb.scalar_type() == at::kByte && sfb.is_contiguous() &&
+              sfb.numel() == (b.size(0) + 127) / 128 * kt * 512, "gemm_mxfp8_grouped: sfb has the wrong size");
+  c10::cuda::CUDAGuard guard(a.device());
+  C10_CUDA_CHECK(cudaSetDevice(a.device().index()));
+  // mode 1 leaves the rows behind the last group untouched: they read as zeros
+  auto c = mode == 1 ? at::zeros({c_rows, N}, a.options().dtype(at::kBFloat16))
+                     : at::empty({c_rows, N}, a.options().dtype(at::kBFloat16));
+  if (c_rows == 0 || N == 0) return c;
+  const CUtensorMap ta = make_tmap_2d_t(a.data_ptr(), CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, K, a.size(0), BK, BM);
+  const CUtensorMap tb = make_tmap_2d_t(b.data_ptr(), CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, K, b.size(0), BK, BN);
+  const CUtensorMap tcm = make_tmap_2d_t(c.data_ptr(), CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, N, c_rows, 64, 32);
+  Params p;
+  p.M = (int)M; p.N = (int)N; p.K = (int)K;
+  p.sfa = sfa.data_ptr<uint8_t>();
+  p.sfb = sfb.data_ptr<uint8_t>();
+  static at::Tensor status;
+  if (!status.defined()) status = at::zeros({1}, a.options().dtype(at::kInt));
+  p.status = status.data_ptr<int>();
+  p.debug = 0;
+  p.group_mode = (int)mode; p.num_groups = (int)E; p.b_group_rows = (int)N; p.group_offs = offs.data_ptr<int>();
+  static bool attr_set = false;
+  if (!attr_set) {
+    C10_CUDA_CHECK(cudaFuncSetAttribute(gemm_mxfp8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
+    attr_set = true;
+  }
+  const int64_t tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN) * (mode == 2 ? E : 1);
+  gemm_mxfp8_kernel<<<(int)std::min<int64_t>(tiles, num_sms()), kThreads, kSmemBytes, at::cuda::getCurrentCUDAStream()>>>(
+      ta, tb, tcm, p);
   C10_CUDA_KERNEL_LAUNCH_CHECK();
   return c;
 }
