@@ -58,3 +58,29 @@ def test_activation_tracer_finds_first_divergence():
         net(x)
     rep = compare_traces([r for r in a.records if r["kind"] == "out"], c)
     assert "first divergence" in rep and ": 2 (" in rep
+
+
+def test_download_asset_selection():
+    from torchtitan_b200.scripts.download_hf_assets import select_files
+
+    files = ["config.json", "tokenizer.json", "model-00001-of-00002.safetensors", "model.safetensors.index.json",
+             "original/consolidated.pth", "README.md"]
+    assert select_files(files, ["tokenizer", "config"], []) == ["config.json", "tokenizer.json"]
+    assert select_files(files, ["index", "safetensors"], ["original/*"]) == [
+        "model-00001-of-00002.safetensors", "model.safetensors.index.json", "original/consolidated.pth"]
+
+
+def test_checkpoint_compat_script_same_revision(tmp_path):
+    """Saving and resuming with the working tree itself must reproduce the uninterrupted run."""
+    from torchtitan_b200.scripts import checkpoint_compat_test as cc
+
+    args = ("--module llama3 --config llama3_debugmodel --training.num_tokens_per_microbatch_per_dp_rank 128 "
+            "--training.max_context_length 64 --training.mixed_precision_param float32")
+    import os
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    a = cc.run(root, args, str(tmp_path / "r"), 2, 1)
+    resumed = cc.run(root, args, str(tmp_path / "r"), 4, 1)
+    straight = cc.run(root, args, str(tmp_path / "s"), 4, 1)
+    assert [s for s, _ in a] == [1, 2] and [s for s, _ in resumed] == [3, 4]
+    assert resumed == straight[2:]
