@@ -224,3 +224,39 @@ def test_cuda_graph_step_matches_eager(tmp_path):
     eager, graph = run(False), run(True)
     assert all(abs(a - b) < 2e-2 for a, b in zip(eager, graph)), (eager, graph)
     assert graph[-1] < graph[0]
+
+
+def test_optimizer_state_offload_is_bit_identical():
+    """Pinned-host optimizer state streamed through the GPU gives the same parameters as resident state."""
+    from tests.test_engine import T, _batches, _small_model_cfg
+    from torchtitan_b200.components.optimizer import OptimizersContainer, clip_grad_norm_
+    from torchtitan_b200.ops import functional as OF
+    from torchtitan_b200.parallel.parallel_dims import ParallelDims
+    from torchtitan_b200.parallel.parallelize import parallelize_decoder
+    from torchtitan_b200.trainer import Trainer
+
+    dev = torch.device("cuda", 0)
+    results = []
+    for offload in (False, True):
+        cfg = Trainer.Config()
+        cfg.training.num_tokens_per_microbatch_per_dp_rank = T
+        cfg.training.max_context_length = T
+        cfg.training.enable_cpu_offload = offload
+        pdims = ParallelDims(world_size=1)
+        with torch.device("meta"):
+            model = _small_model_cfg(2).build()
+        eng = parallelize_decoder(model, pdims=pdims, job_config=cfg, device=dev, seed=3)
+        assert eng.offload_optimizer == offload
+        opt = OptimizersContainer(OptimizersContainer.Config(lr=1e-2), engines=[eng])
+        pos = torch.arange(T, device=dev)
+        for tok, lab in _batches(3):
+            opt.zero_grad()
+            h = model(tok.to(dev), pos, return_hidden=True)
+            OF.linear_cross_entropy(h, model.lm_head.weight, lab.to(dev), torch.tensor(1.0 / T, device=dev), 2).backward()
+            eng.finish_backward()
+            clip_grad_norm_([eng], 1.0, pdims, optimizers=opt)
+            opt.step()
+        if offload:
+            assert all(not u.master.is_cuda and u.master.is_pinned() and not u.exp_avg.is_cuda for u in eng.units)
+        results.append(torch.cat([u.flat_param[:u.numel].float() for u in eng.units]).cpu())
+    assert torch.equal(results[0], results[1])

@@ -44,6 +44,8 @@ class TrainingConfig:
     max_norm: float = 1.0
     steps: int = 10000
     enable_cpu_offload: bool = False
+    """Keep the sharded optimizer state (fp32 master weights, both moments: 12 bytes per parameter
+    and rank) in pinned host memory; the optimizer step streams it through the GPU unit by unit."""
     disable_cuda_graphs: bool = True
     dtype: Literal["bfloat16", "float32"] = "float32"
     """Dtype of the master parameters."""

@@ -119,8 +119,11 @@ class ShardedModel:
     def __init__(self, model: nn.Module, units: list[UnitSpec], *, pdims, device: torch.device,
                  param_dtype: torch.dtype = torch.bfloat16, master_dtype: torch.dtype = torch.float32,
                  state_dtype: torch.dtype = torch.float32, seed: int = 0, comm: str = "nccl",
-                 grad_accum_steps: int = 1, fqn_prefix: str = "", tp=None):
+                 grad_accum_steps: int = 1, fqn_prefix: str = "", tp=None, offload_optimizer: bool = False):
         self.model = model
+        # optimizer state (fp32 master weights and both moments) lives in pinned host memory and is
+        # streamed through the GPU one unit at a time during the optimizer step
+        self.offload_optimizer = bool(offload_optimizer) and device.type == "cuda"
         self.pdims = pdims
         self.device = device
         self.param_dtype = param_dtype
@@ -215,7 +218,10 @@ class ShardedModel:
             else:
                 u.flat_param = torch.zeros(u.padded, dtype=pd, device=dev)
                 u.flat_grad = torch.zeros(u.padded, dtype=pd, device=dev)
-            u.master = torch.zeros(u.shard_numel, dtype=torch.float32, device=dev)
+            if self.offload_optimizer:
+                u.master = torch.zeros(u.shard_numel, dtype=torch.float32, pin_memory=True)
+            else:
+                u.master = torch.zeros(u.shard_numel, dtype=torch.float32, device=dev)
             u.sumsq = torch.zeros(2, dtype=torch.float32, device=dev)
             # A separate fp32 gradient shard is needed whenever gradients are summed across
             # ranks or across microbatches; a lone owner with one microbatch lets the
@@ -452,8 +458,9 @@ class ShardedModel:
     def ensure_state(self) -> None:
         for u in self.units:
             if u.exp_avg is None:
-                u.exp_avg = torch.zeros(u.shard_numel, dtype=self.state_dtype, device=self.device)
-                u.exp_avg_sq = torch.zeros(u.shard_numel, dtype=self.state_dtype, device=self.device)
+                kw = dict(pin_memory=True) if self.offload_optimizer else dict(device=self.device)
+                u.exp_avg = torch.zeros(u.shard_numel, dtype=self.state_dtype, **kw)
+                u.exp_avg_sq = torch.zeros(u.shard_numel, dtype=self.state_dtype, **kw)
 
     @torch.no_grad()
     def adamw_step(self, groups: list[dict], grad_scale: torch.Tensor | float = 1.0) -> None:
@@ -464,9 +471,15 @@ class ShardedModel:
         fused_ag = self._symm is not None
         if fused_ag and not isinstance(grad_scale, torch.Tensor):
             grad_scale = torch.full((1,), float(grad_scale), dtype=torch.float32, device=self.device)
+        host_state = None
         for u in self.units:
+            if host_state is not None:      # previous unit: updated state back to its pinned host buffers
+                self._unstage_state(*host_state)
+                host_state = None
             if not u.grad_shard_valid:
                 continue
+            if self.offload_optimizer:
+                host_state = self._stage_state(u)
             g = self._grad_of(u)
             runs = _group_runs(u)
             if any(groups[gi].get("optimizer_name") == "DistMuon" for gi, _a, _b in runs) or any(
@@ -493,10 +506,26 @@ class ShardedModel:
                     weight_decay=h["weight_decay"], step=step, grad_scale=grad_scale,
                 )
             u.grad_shard_valid = False
+        if host_state is not None:
+            self._unstage_state(*host_state)
+        if self.offload_optimizer:
+            torch.cuda.current_stream(self.device).synchronize()   # host buffers are complete before anyone reads them
         if fused_ag:
             self._symm.barrier_all()  # peers' stores into our parameter buffers have landed
         else:
             self._all_gather_params()
+
+    def _stage_state(self, u: FlatUnit):
+        """Offloaded optimizer state of one unit -> device copies (the unit's attributes point at
+        them while it is updated)."""
+        host = (u.master, u.exp_avg, u.exp_avg_sq)
+        u.master, u.exp_avg, u.exp_avg_sq = (t.to(self.device, non_blocking=True) for t in host)
+        return u, host
+
+    def _unstage_state(self, u: FlatUnit, host) -> None:
+        for h, d in zip(host, (u.master, u.exp_avg, u.exp_avg_sq)):
+            h.copy_(d, non_blocking=True)
+        u.master, u.exp_avg, u.exp_avg_sq = host
 
     def check_status(self) -> None:
         """Raise if a bounded device-side wait expired (host sync; call at logging points)."""

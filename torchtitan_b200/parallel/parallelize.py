@@ -104,7 +104,7 @@ def parallelize_decoder(model: nn.Module, *, pdims, job_config, device: torch.de
     engine = ShardedModel(
         model, decoder_units(model, pdims), pdims=pdims, device=device, param_dtype=param_dtype,
         state_dtype=state_dtype, seed=seed, comm=par.fsdp_comm, grad_accum_steps=grad_accum_steps,
-        fqn_prefix=fqn_prefix, tp=tp,
+        fqn_prefix=fqn_prefix, tp=tp, offload_optimizer=bool(getattr(tr, "enable_cpu_offload", False)),
     )
     if materialize:
         engine.materialize()
