@@ -194,3 +194,35 @@ def test_flux_autoencoder_and_sampling(tmp_path):
     import os
 
     assert os.path.exists(out) or os.path.exists(out[:-4] + ".ppm")
+
+
+def test_every_registered_config_builds_its_model_on_meta():
+    """Each config-registry function returns a config whose model flavor exists and builds on the
+    meta device with a parameter count that matches its accounting."""
+    import importlib
+    import inspect
+
+    from torchtitan_b200.models.spec import SUPPORTED_MODELS
+
+    n = 0
+    for fam in SUPPORTED_MODELS:
+        if fam == "flux":
+            continue
+        reg = importlib.import_module(f"torchtitan_b200.models.{fam}.config_registry")
+        for name, fn in inspect.getmembers(reg, inspect.isfunction):
+            if name.startswith("_") or fn.__module__ != reg.__name__ or inspect.signature(fn).parameters:
+                continue
+            cfg = fn()
+            spec = get_model_spec(cfg.model.name, cfg.model.flavor)
+            if "debug" in cfg.model.flavor:
+                from torchtitan_b200.components.quantization import apply_converters
+
+                apply_converters(spec.model, cfg.model.converters)
+                with torch.device("meta"):
+                    model = spec.model.build()
+                assert sum(p.numel() for p in model.parameters()) > 0
+            else:
+                total, flops = count_params_and_flops(spec.model, None, 4096)
+                assert total > 1e8 and flops > 0, (fam, name, total)
+            n += 1
+    assert n >= 50

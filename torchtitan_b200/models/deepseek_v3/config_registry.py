@@ -55,3 +55,30 @@ def deepseek_v3_236b() -> Trainer.Config:
 
 def deepseek_v3_671b() -> Trainer.Config:
     return _full("671B", 4 * 4096, 4096, 2.2e-4, 10000, expert_parallel_degree=8)
+
+
+def deepseek_v3_debugmodel_mxfp8() -> Trainer.Config:
+    """Block-scaled MXFP8 for the dense linears and the grouped expert GEMMs."""
+    cfg = deepseek_v3_debugmodel()
+    cfg.model.converters = ["mxfp8", "mxfp8_experts"]
+    return cfg
+
+
+def deepseek_v3_debugmodel_minimal_async_ep() -> Trainer.Config:
+    """Expert parallelism with direct peer-memory row copies: no host sync, CUDA-graph capturable."""
+    cfg = deepseek_v3_debugmodel()
+    cfg.parallelism.expert_parallel_degree = 2
+    cfg.parallelism.ep_comm = "nvlink"
+    return cfg
+
+
+def deepseek_v3_16b_minimal_async_ep() -> Trainer.Config:
+    cfg = deepseek_v3_16b()
+    cfg.parallelism.ep_comm = "nvlink"
+    return cfg
+
+
+def deepseek_v3_671b_float8() -> Trainer.Config:
+    cfg = deepseek_v3_671b()
+    cfg.model.converters = ["float8", "float8_experts"]
+    return cfg

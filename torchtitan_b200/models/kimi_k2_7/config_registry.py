@@ -75,3 +75,11 @@ def kimi_k2() -> Trainer.Config:
     cfg.model.name = "kimi_k2_7"
     cfg.optimizer = kimi_muon_optimizer("kimi_k2", 2e-4)
     return cfg
+
+
+def kimi_vl_a3b() -> Trainer.Config:
+    """Moonlight text decoder behind the vision tower, interleaved text / image data."""
+    cfg = kimi_moonlight()
+    cfg.model.flavor = "kimi_vl_a3b"
+    cfg.dataloader.dataset = "mm_jsonl"
+    return cfg

@@ -106,3 +106,45 @@ def sft_debugmodel() -> Trainer.Config:
     cfg = llama3_debugmodel()
     cfg.dataloader = BaseDataLoader.Config(dataset="sft_test")
     return cfg
+
+
+def llama3_debugmodel_varlen_attn() -> Trainer.Config:
+    """Packed documents of varying length through the native flash kernel (document starts from positions)."""
+    cfg = llama3_debugmodel()
+    cfg.dataloader = BaseDataLoader.Config(dataset="synthetic", synthetic_doc_len=512)
+    return cfg
+
+
+def llama3_debugmodel_dist_gemm() -> Trainer.Config:
+    """Tensor + sequence parallel with the all-gather / reduce-scatter fused into the GEMM kernels."""
+    cfg = llama3_debugmodel()
+    cfg.parallelism.tensor_parallel_degree = 2
+    cfg.parallelism.enable_sequence_parallel = True
+    cfg.parallelism.tp_comm = "nvlink"
+    return cfg
+
+
+def llama3_debugmodel_nvfp4() -> Trainer.Config:
+    cfg = llama3_debugmodel()
+    cfg.model.converters = ["nvfp4"]
+    return cfg
+
+
+def llama3_debugmodel_first_85_pct_layers_nvfp4() -> Trainer.Config:
+    """NVFP4 for the leading 85 % of the layers, the tail stays bf16."""
+    cfg = llama3_debugmodel()
+    cfg.model.converters = ["nvfp4:tail=0.15"]
+    return cfg
+
+
+def llama3_debugmodel_ce_loss() -> Trainer.Config:
+    """Plain cross entropy on materialised logits instead of the chunked fused lm_head + loss."""
+    cfg = llama3_debugmodel()
+    cfg.loss.name = "cross_entropy"
+    return cfg
+
+
+def llama3_8b_first_85_pct_layers_nvfp4() -> Trainer.Config:
+    cfg = llama3_8b()
+    cfg.model.converters = ["nvfp4:tail=0.15"]
+    return cfg

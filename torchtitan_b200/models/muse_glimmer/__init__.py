@@ -83,6 +83,8 @@ muse_glimmer_configs = {
                                                     window_pattern=[128, 128, 128, 0], output_multiplier=1.0),
     "debugmodel_mm": lambda: _mm(muse_glimmer_configs["debugmodel"](), dim=64, heads=2, mlp=128, layers=2, patch=4,
                                  image_token_id=2047),
+    "30B_mm": lambda: _mm(muse_glimmer_configs["30B"](), dim=1152, heads=16, mlp=4304, layers=27, patch=14,
+                          image_token_id=202047),
     "30B": lambda: build_muse_glimmer_config(dim=6656, n_layers=52, n_heads=32, n_kv_heads=2, head_dim=128,
                                              vocab_size=202048, max_context_length=16384,
                                              window_pattern=[2048, 2048, 2048, 0], output_multiplier=0.19611613513),

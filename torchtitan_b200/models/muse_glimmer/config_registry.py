@@ -42,3 +42,10 @@ def muse_glimmer_30b() -> Trainer.Config:
         checkpoint=CheckpointManager.Config(interval=500),
         activation_checkpoint=ActivationCheckpointConfig(mode="full"),
     )
+
+
+def muse_glimmer_30b_mm() -> Trainer.Config:
+    cfg = muse_glimmer_30b()
+    cfg.model.flavor = "30B_mm"
+    cfg.dataloader.dataset = "mm_jsonl"
+    return cfg

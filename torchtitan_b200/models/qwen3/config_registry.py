@@ -86,3 +86,40 @@ def qwen3_30b_a3b_ep8() -> Trainer.Config:
 
 def qwen3_235b_a22b() -> Trainer.Config:
     return _full("235B-A22B", 4 * 4096, 4096, 8e-4, ac="full", expert_parallel_degree=8, tensor_parallel_degree=1)
+
+
+def qwen3_debugmodel_nvfp4() -> Trainer.Config:
+    cfg = qwen3_debugmodel()
+    cfg.model.converters = ["nvfp4"]
+    return cfg
+
+
+def qwen3_debugmodel_first_85_pct_layers_nvfp4() -> Trainer.Config:
+    cfg = qwen3_debugmodel()
+    cfg.model.converters = ["nvfp4:tail=0.15"]
+    return cfg
+
+
+def qwen3_8b_first_85_pct_layers_nvfp4() -> Trainer.Config:
+    cfg = qwen3_8b()
+    cfg.model.converters = ["nvfp4:tail=0.15"]
+    return cfg
+
+
+def qwen3_moe_nvlink_ep() -> Trainer.Config:
+    """MoE debug model with expert parallelism over NVLink peer stores (no all-to-all, no host sync)."""
+    cfg = qwen3_moe_debug()
+    cfg.parallelism.expert_parallel_degree = 2
+    cfg.parallelism.ep_comm = "nvlink"
+    return cfg
+
+
+def sft_qwen3_8b_math() -> Trainer.Config:
+    """Single-turn supervised fine-tuning (prompt tokens masked) of the 8B model on a question / answer set."""
+    from torchtitan_b200.components.data import BaseDataLoader
+
+    cfg = qwen3_8b()
+    cfg.dataloader = BaseDataLoader.Config(dataset="sft_test", packing="first_fit")
+    cfg.optimizer.lr = 1e-5
+    cfg.training.steps = 500
+    return cfg
