@@ -725,3 +725,30 @@ class CheckpointManager(Configurable):
         if self._purge_q is not None:
             self._purge_q.put(None)
             self._purge_t.join(timeout=60)
+
+
+class TorchCheckpointingManager(CheckpointManager):
+    """Same policy surface (intervals, retention, async modes, model-only export, resume rules) on an
+    external ``torch_checkpointing`` storage engine instead of DCP files.  The storage engine is
+    not part of this package: ``_save`` / ``_load`` raise until one is plugged in by a subclass.
+    Parity: torchtitan/components/checkpointer/torch_checkpointing.py:121-222 (a skeleton there as
+    well)."""
+
+    Config = CheckpointManager.Config
+
+    def _save(self, state: dict, path: str) -> None:
+        raise NotImplementedError("no torch_checkpointing storage engine is available: subclass and implement _save")
+
+    def _load(self, state: dict, path: str) -> None:
+        raise NotImplementedError("no torch_checkpointing storage engine is available: subclass and implement _load")
+
+    def save(self, curr_step: int, last_step: bool = False) -> None:
+        if not self.config.enable:
+            return
+        self._save({}, os.path.join(self.folder, f"step-{curr_step}"))
+
+    def load(self, step: int = -1) -> bool:
+        if not self.config.enable:
+            return False
+        self._load({}, self.folder)
+        return True

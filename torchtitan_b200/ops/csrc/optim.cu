@@ -105,6 +105,85 @@ __global__ void __launch_bounds__(256) adamw_vec_kernel(float* __restrict__ mast
   }
 }
 
+
+// 4 elements per access: a warp reads 512 contiguous bytes of every fp32 stream per instruction
+// (each 32-byte sector is requested once), two independent groups per iteration for memory-level
+// parallelism, streaming cache hints (nothing is reused).
+template <typename T>
+__device__ __forceinline__ void load4(const T* p, float (&f)[4]);
+template <>
+__device__ __forceinline__ void load4<float>(const float* p, float (&f)[4]) {
+  const float4 a = __ldcs(reinterpret_cast<const float4*>(p));
+  f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w;
+}
+template <>
+__device__ __forceinline__ void load4<__nv_bfloat16>(const __nv_bfloat16* p, float (&f)[4]) {
+  const uint2 a = __ldcs(reinterpret_cast<const uint2*>(p));
+  const float2 lo = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&a.x));
+  const float2 hi = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&a.y));
+  f[0] = lo.x; f[1] = lo.y; f[2] = hi.x; f[3] = hi.y;
+}
+template <typename T>
+__device__ __forceinline__ void store4(T* p, const float (&f)[4]);
+template <>
+__device__ __forceinline__ void store4<float>(float* p, const float (&f)[4]) {
+  __stcs(reinterpret_cast<float4*>(p), make_float4(f[0], f[1], f[2], f[3]));
+}
+template <>
+__device__ __forceinline__ void store4<__nv_bfloat16>(__nv_bfloat16* p, const float (&f)[4]) {
+  __nv_bfloat162 lo = __floats2bfloat162_rn(f[0], f[1]), hi = __floats2bfloat162_rn(f[2], f[3]);
+  uint2 w;
+  w.x = *reinterpret_cast<uint32_t*>(&lo);
+  w.y = *reinterpret_cast<uint32_t*>(&hi);
+  *reinterpret_cast<uint2*>(p) = w;       // the low-precision weights are read by the next forward: default policy
+}
+
+template <typename G, typename S, typename P>
+__global__ void __launch_bounds__(256) adamw_vec4_kernel(float* __restrict__ master, const G* __restrict__ grad,
+                                                         S* __restrict__ m, S* __restrict__ v, P* __restrict__ lowp,
+                                                         const float* __restrict__ grad_scale, int64_t nvec, float lr,
+                                                         float beta1, float beta2, float eps, float wd, float bc1,
+                                                         float bc2_sqrt) {
+  const float gs = *grad_scale;
+  if (!isfinite(gs)) return;
+  const float step_size = lr / bc1;
+  const float decay = 1.f - lr * wd;
+  const float inv_bc2 = 1.f / bc2_sqrt;
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t i0 = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i0 < nvec; i0 += 2 * stride) {
+    float g[2][4], mm[2][4], vv[2][4], p[2][4];
+    bool live[2];
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+      const int64_t o = (i0 + u * stride) * 4;
+      live[u] = i0 + u * stride < nvec;
+      if (live[u]) {
+        load4<G>(grad + o, g[u]);
+        load4<S>(m + o, mm[u]);
+        load4<S>(v + o, vv[u]);
+        load4<float>(master + o, p[u]);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+      if (!live[u]) continue;
+      const int64_t o = (i0 + u * stride) * 4;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float gj = g[u][j] * gs;
+        mm[u][j] = beta1 * mm[u][j] + (1.f - beta1) * gj;
+        vv[u][j] = beta2 * vv[u][j] + (1.f - beta2) * gj * gj;
+        const float denom = sqrtf(vv[u][j]) * inv_bc2 + eps;
+        p[u][j] = p[u][j] * decay - step_size * (mm[u][j] / denom);
+      }
+      store4<float>(master + o, p[u]);
+      store4<S>(m + o, mm[u]);
+      store4<S>(v + o, vv[u]);
+      if (lowp != nullptr) store4<P>(lowp + o, p[u]);
+    }
+  }
+}
+
 static inline bool is_aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 template <typename G, typename S, typename P>
@@ -115,11 +194,11 @@ static void launch_adamw(float* master, const G* grad, S* m, S* v, P* lowp, cons
                    (lowp == nullptr || is_aligned16(lowp));
   int64_t done = 0;
   if (vec && n >= 8) {
-    const int64_t nvec = n / 8;
-    const int grid = (int)std::max<int64_t>(1, std::min<int64_t>((nvec + threads - 1) / threads, (int64_t)num_sms() * 16));
-    adamw_vec_kernel<G, S, P><<<grid, threads, 0, stream>>>(master, grad, m, v, lowp, gs, nvec, lr, b1, b2, eps, wd,
-                                                            bc1, sqrtf(bc2));
-    done = nvec * 8;
+    const int64_t nvec = n / 4;
+    const int grid = (int)std::max<int64_t>(1, std::min<int64_t>((nvec + 2 * threads - 1) / (2 * threads), (int64_t)num_sms() * 8));
+    adamw_vec4_kernel<G, S, P><<<grid, threads, 0, stream>>>(master, grad, m, v, lowp, gs, nvec, lr, b1, b2, eps, wd,
+                                                             bc1, sqrtf(bc2));
+    done = nvec * 4;
   }
   if (done < n) {
     const int64_t rem = n - done;
