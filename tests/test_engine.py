@@ -173,3 +173,28 @@ def test_tensor_parallel_matches_single(tmp_path):
     pdims = ParallelDims(world_size=1)
     losses, _, _ = _engine_steps(_job(), pdims, [[x] for x in _batches(3)])
     assert torch.allclose(got, torch.tensor(losses), atol=2e-4), (got, losses)
+
+
+def test_activation_offload_hooks_preserve_gradients():
+    from torchtitan_b200.parallel.activation_offload import OffloadStats, offload_activations
+
+    torch.manual_seed(0)
+    lin1, lin2 = torch.nn.Linear(64, 256), torch.nn.Linear(256, 8)
+    x = torch.randn(128, 64)
+
+    def run(ctx):
+        for p in list(lin1.parameters()) + list(lin2.parameters()):
+            p.grad = None
+        with ctx:
+            y = lin2(torch.nn.functional.gelu(lin1(x))).square().sum()
+        y.backward()
+        return [p.grad.clone() for p in list(lin1.parameters()) + list(lin2.parameters())]
+
+    import contextlib
+
+    ref_grads = run(contextlib.nullcontext())
+    stats = OffloadStats()
+    got = run(offload_activations(min_bytes=1024, stats=stats, force=True))
+    assert stats.tensors >= 2 and stats.bytes >= 128 * 256 * 4        # the hidden activations went through the hooks
+    for a, b in zip(ref_grads, got):
+        assert torch.equal(a, b)

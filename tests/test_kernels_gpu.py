@@ -263,3 +263,29 @@ def test_optimizer_state_offload_matches_resident_state():
     d = (results[0] - results[1]).abs()
     assert float(d.max()) <= 5e-2 and float(d.mean()) <= 1e-4, (float(d.max()), float(d.mean()))
     assert float((results[0] - results[0].mean()).abs().mean()) > 1e-3
+
+
+def test_activation_offload_on_gpu_matches_resident():
+    from torchtitan_b200.parallel.activation_offload import OffloadStats, offload_activations
+
+    torch.manual_seed(0)
+    dev = torch.device("cuda", 0)
+    lin1, lin2 = torch.nn.Linear(512, 2048).to(dev), torch.nn.Linear(2048, 64).to(dev)
+    x = torch.randn(4096, 512, device=dev)
+    import contextlib
+
+    def run(ctx):
+        for p in list(lin1.parameters()) + list(lin2.parameters()):
+            p.grad = None
+        with ctx:
+            y = lin2(torch.nn.functional.gelu(lin1(x))).square().sum()
+        y.backward()
+        torch.cuda.synchronize()
+        return [p.grad.clone() for p in list(lin1.parameters()) + list(lin2.parameters())]
+
+    ref_grads = run(contextlib.nullcontext())
+    stats = OffloadStats()
+    got = run(offload_activations(min_bytes=1 << 20, stats=stats))
+    assert stats.tensors >= 2
+    for a, b in zip(ref_grads, got):
+        assert torch.allclose(a, b, rtol=1e-5, atol=1e-5)

@@ -144,6 +144,9 @@ class ActivationCheckpointConfig:
     debug: bool = False
     force_recompute_mm_shapes_by_fqns: list[str] = field(default_factory=lambda: ["moe.router.gate"])
     memory_budget: float = 0.5
+    cpu_offload: bool = False
+    """Move activations saved for backward to pinned host memory on a side stream."""
+    cpu_offload_min_bytes: int = 1 << 20
     visualize_memory_budget_pareto: bool = False
 
 

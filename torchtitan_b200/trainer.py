@@ -253,6 +253,7 @@ class Trainer(Configurable):
         self._graph_runner = None
         self._mb_index = 0
         if (not c.training.disable_cuda_graphs and self.device.type == "cuda" and not pd.pp_enabled
+                and not c.activation_checkpoint.cpu_offload   # host copies cannot be captured
                 and not (pd.ep_enabled and c.parallelism.ep_comm == "nccl")):
             from torchtitan_b200.parallel.cudagraph import CUDAGraphRunner
 
@@ -327,7 +328,16 @@ class Trainer(Configurable):
 
     def _fwd_bwd_tensors(self, tokens, positions, labels, global_valid, q_pos=None) -> torch.Tensor:
         model = self.model
-        with sl.span("fwd_bwd"):
+        ac = self.config.activation_checkpoint
+        if ac.cpu_offload:
+            from torchtitan_b200.parallel.activation_offload import offload_activations
+
+            offload = offload_activations(min_bytes=ac.cpu_offload_min_bytes)
+        else:
+            import contextlib
+
+            offload = contextlib.nullcontext()
+        with sl.span("fwd_bwd"), offload:
             ctx = model.build_context(positions, q_pos)
             extra = getattr(self, "_extra_inputs", None) or {}
             if self.loss_fn.needs_hidden:
