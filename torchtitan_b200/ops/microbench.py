@@ -186,6 +186,32 @@ def bench_gemm_mx(args) -> None:
               f"{fl / t_bf / 1e9:.0f} | quantize x {t_q:.3f} ms{lib}", flush=True)
 
 
+def bench_gemm_mx_grouped(args) -> None:
+    """Grouped (expert) GEMMs: MXFP8 block-scaled kernel vs the bf16 grouped kernel, Qwen3-30B-A3B expert shapes
+    (128 experts, dim 2048, hidden 768, 8192 tokens x top-8 -> 512 rows per expert, padded layout)."""
+    ops = torch.ops.tb200
+    timer = Timer()
+    E, rows = (8, 512) if args.case == "small" else (128, 512)
+    R = E * rows
+    offs = torch.arange(0, R + 1, rows, dtype=torch.int32, device="cuda")
+    for name, K, N in (("w1/w3", 2048, 768), ("w2", 768, 2048)):
+        x = torch.randn(R, K, device="cuda").bfloat16()
+        w = (torch.randn(E, N, K, device="cuda") * 0.05).bfloat16()
+        y = torch.empty(R, N, device="cuda", dtype=torch.bfloat16)
+        xq, xs = ops.mxfp8_quantize_tiled(x)
+        wq, ws = ops.mxfp8_quantize_tiled(w.view(E * N, K))
+        if args.once:
+            ops.gemm_mxfp8_grouped(xq, xs, wq, ws, offs, 1)
+            torch.cuda.synchronize()
+            continue
+        t_mx = timer(lambda: ops.gemm_mxfp8_grouped(xq, xs, wq, ws, offs, 1))
+        t_bf = timer(lambda: ops.gemm_grouped_bf16(x, w, y, offs, 0, 128, False))
+        t_q = timer(lambda: ops.mxfp8_quantize_tiled(x))
+        fl = 2 * R * N * K
+        print(f"grouped {name:6s} E{E} rows/expert {rows} K{K} N{N}: mxfp8 {t_mx:.3f} ms {fl / t_mx / 1e9:.0f} TFLOPS | "
+              f"bf16 {t_bf:.3f} ms {fl / t_bf / 1e9:.0f} | quantize x {t_q:.3f} ms", flush=True)
+
+
 def bench_tp(args) -> None:
     """Fused tensor-parallel GEMMs vs NCCL collective + cuBLAS; run under torchrun with >= 2 ranks:
     ``python -m torch.distributed.run --nproc-per-node 2 --master-addr 127.0.0.1 -m torchtitan_b200.ops.microbench tp``."""
@@ -244,7 +270,7 @@ def bench_tp(args) -> None:
 
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser()
-    ap.add_argument("kernel", choices=["gemm", "gemm_mx", "attention", "elementwise", "tp"])
+    ap.add_argument("kernel", choices=["gemm", "gemm_mx", "gemm_mx_grouped", "attention", "elementwise", "tp"])
     ap.add_argument("--case", default="8b", choices=["small", "8b"])
     ap.add_argument("--variant", type=int, default=0, help="GEMM tiling: 0 auto, 1 single CTA, 2 CTA pair")
     ap.add_argument("--once", action="store_true", help="one launch per shape, no library arm (profiler form)")
@@ -253,7 +279,7 @@ def main(argv=None) -> int:
 
     assert torch.cuda.is_available(), "microbench needs a GPU"
     ext.require()
-    {"gemm": bench_gemm, "attention": bench_attention, "elementwise": bench_elementwise, "tp": bench_tp, "gemm_mx": bench_gemm_mx}[args.kernel](args)
+    {"gemm": bench_gemm, "attention": bench_attention, "elementwise": bench_elementwise, "tp": bench_tp, "gemm_mx": bench_gemm_mx, "gemm_mx_grouped": bench_gemm_mx_grouped}[args.kernel](args)
     return 0
 
 
