@@ -309,3 +309,47 @@ def test_expert_parallel_nvlink_matches_nccl(tmp_path):
     r = torch.load(out)
     assert r[-1] == 0, "a bounded wait expired"
     assert (r[:-1] < 3e-2).all(), r
+
+
+def _cp_nvlink(rank, world, out_path):
+    """Context-parallel KV exchange by peer loads against the NCCL collectives, forward and backward."""
+    import torch.distributed as dist
+
+    from torchtitan_b200.parallel.context_parallel import CPContext, _CPAllGather
+    from torchtitan_b200.parallel.cp_nvlink import CPNvlink
+
+    dev = torch.device("cuda", rank)
+    group = dist.new_group(list(range(world)))
+    nv = CPNvlink(group, dev, nbytes=8 << 20)
+    torch.manual_seed(10 + rank)
+    x = torch.randn(256, 8, 128, device=dev).bfloat16()
+    got = nv.all_gather(x)
+    want = torch.empty(world * 256, 8, 128, device=dev, dtype=torch.bfloat16)
+    dist.all_gather_into_tensor(want, x, group=group)
+    ok = torch.equal(got, want)
+    full = torch.randn(world * 256, 8, 128, device=dev).bfloat16()
+    rs = nv.reduce_scatter(full)
+    ref = torch.empty(256, 8, 128, device=dev, dtype=torch.float32)
+    dist.reduce_scatter_tensor(ref, full.float(), group=group)
+    ok = ok and torch.allclose(rs.float(), ref, atol=2e-2, rtol=2e-2)
+    # through the autograd function both ways
+    outs = []
+    for transport in (None, nv):
+        cp = CPContext(group=group, size=world, rank=rank, nvlink=transport)
+        xi = x.clone().requires_grad_()
+        y = _CPAllGather.apply(xi, cp)
+        (y.float() * torch.arange(y.shape[0], device=dev)[:, None, None]).sum().backward()
+        outs.append((y.detach(), xi.grad))
+    ok = ok and torch.equal(outs[0][0], outs[1][0]) and torch.allclose(outs[0][1].float(), outs[1][1].float(), rtol=2e-2, atol=1.0)
+    nv.check_status()
+    flag = torch.tensor([1 if ok else 0], device=dev)
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+    if rank == 0:
+        torch.save({"ok": int(flag.item())}, out_path)
+
+
+@pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
+def test_context_parallel_nvlink_exchange(tmp_path):
+    out = str(tmp_path / "cp.pt")
+    run_distributed(_cp_nvlink, 2, out, backend="nccl")
+    assert torch.load(out)["ok"] == 1

@@ -88,6 +88,10 @@ class ParallelismConfig:
     tp_symm_bytes: int = 2 << 30
     """Symmetric memory reserved per tensor-parallel group for gather / staging buffers."""
     cp_comm: Literal["allgather", "ring"] = "allgather"
+    cp_transport: Literal["nccl", "nvlink"] = "nccl"
+    """``nvlink``: the all-gather of K / V (and its reduce-scatter in backward) runs as peer loads over
+    symmetric memory instead of NCCL."""
+    cp_symm_bytes: int = 256 << 20
     ep_comm: Literal["nccl", "nvlink"] = "nccl"
     """``nvlink``: token dispatch / combine as in-kernel peer stores / loads over symmetric memory."""
     ep_capacity_factor: float = 0.0

@@ -38,6 +38,7 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor> flash_bwd(const at::Tensor& d_o, 
 int64_t flash_status(bool clear);
 void flash_set_debug(int64_t v);
 void symm_barrier(at::IntArrayRef flag_ptrs, int64_t my_rank, int64_t epoch, at::Tensor status, int64_t max_cycles);
+void all_gather_pull(at::IntArrayRef src_ptrs, int64_t my_rank, int64_t nbytes, at::Tensor out);
 void reduce_scatter_pull(at::IntArrayRef grad_ptrs, int64_t my_rank, int64_t offset, at::Tensor out, bool grad_is_bf16,
                          bool accumulate);
 void adamw_allgather_(at::Tensor master, const at::Tensor& grad, at::Tensor exp_avg, at::Tensor exp_avg_sq,
@@ -128,6 +129,7 @@ TORCH_LIBRARY(tb200, m) {
   m.def("moe_combine_bwd(Tensor dout, Tensor y, Tensor dest, Tensor wts) -> (Tensor, Tensor)", &tb200::moe_combine_bwd);
   m.def("symm_barrier(int[] flag_ptrs, int my_rank, int epoch, Tensor(a!) status, int max_cycles) -> ()",
         &tb200::symm_barrier);
+  m.def("all_gather_pull(int[] src_ptrs, int my_rank, int nbytes, Tensor(a!) out) -> ()", &tb200::all_gather_pull);
   m.def("reduce_scatter_pull(int[] grad_ptrs, int my_rank, int offset, Tensor(a!) out, bool grad_is_bf16, "
         "bool accumulate) -> ()", &tb200::reduce_scatter_pull);
   m.def("adamw_allgather_(Tensor(a!) master, Tensor grad, Tensor(b!) exp_avg, Tensor(c!) exp_avg_sq, int[] param_ptrs, "

@@ -168,6 +168,37 @@ void reduce_scatter_pull(at::IntArrayRef grad_ptrs, int64_t my_rank, int64_t off
   C10_CUDA_KERNEL_LAUNCH_CHECK();
 }
 
+// out[q * n16 + i] = peers[q][i] for every rank q (16-byte units): an all-gather by peer loads.
+// Rank order is rotated per block so that the ranks do not all read the same peer at once.
+__global__ void __launch_bounds__(256) all_gather_pull_kernel(PeerPtrs peers, int nranks, int my_rank, int64_t n16,
+                                                              uint4* __restrict__ out) {
+  const int64_t total = n16 * nranks;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int slot = (int)(i / n16);
+    const int64_t off = i - (int64_t)slot * n16;
+    const int q = (my_rank + slot) % nranks;
+    out[(int64_t)q * n16 + off] = reinterpret_cast<const uint4*>(peers.p[q])[off];
+  }
+}
+
+// Gather `nbytes` (a multiple of 16) from the same symmetric buffer of every rank into `out`
+// ([nranks * nbytes], rank-major).
+void all_gather_pull(at::IntArrayRef src_ptrs, int64_t my_rank, int64_t nbytes, at::Tensor out) {
+  TORCH_CHECK(out.is_cuda() && out.is_contiguous());
+  const int nr = (int)src_ptrs.size();
+  TORCH_CHECK(nbytes % 16 == 0 && (int64_t)out.numel() * out.element_size() == nbytes * nr,
+              "all_gather_pull: the output must hold nranks * nbytes and nbytes must be a multiple of 16");
+  TORCH_CHECK((reinterpret_cast<uintptr_t>(out.data_ptr()) & 15u) == 0, "all_gather_pull: unaligned output");
+  if (nbytes == 0) return;
+  c10::cuda::CUDAGuard guard(out.device());
+  const PeerPtrs pp = make_peers(src_ptrs);
+  const int64_t n16 = nbytes / 16;
+  const int grid = (int)std::max<int64_t>(1, std::min<int64_t>((n16 * nr + 255) / 256, (int64_t)num_sms() * 8));
+  all_gather_pull_kernel<<<grid, 256, 0, at::cuda::getCurrentCUDAStream()>>>(pp, nr, (int)my_rank, n16,
+                                                                              reinterpret_cast<uint4*>(out.data_ptr()));
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+}
+
 // AdamW on this rank's shard; the updated low-precision weights are stored into every peer's
 // parameter buffer at `offset` (the all-gather).
 template <typename G, typename S, typename P>

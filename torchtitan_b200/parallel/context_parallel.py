@@ -39,6 +39,7 @@ class CPContext:
     rank: int
     mode: str = "allgather"  # allgather | ring
     load_balancer: str = "headtail"  # headtail | none
+    nvlink: object | None = None  # parallel.cp_nvlink.CPNvlink: KV exchange by peer loads instead of NCCL
 
 
 def cp_chunk_ids(cp: CPContext, rank: int | None = None) -> list[int]:
@@ -77,7 +78,10 @@ class _CPAllGather(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, cp):
         ctx.cp = cp
-        full = tp_ops.all_gather_raw(x, cp.group, cp.size)
+        if cp.nvlink is not None and x.is_cuda:
+            full = cp.nvlink.all_gather(x)
+        else:
+            full = tp_ops.all_gather_raw(x, cp.group, cp.size)
         T = full.shape[0]
         order = torch.cat([_local_index(cp, T, x.device, r) for r in range(cp.size)])
         ctx.order = order
@@ -89,6 +93,8 @@ class _CPAllGather(torch.autograd.Function):
     def backward(ctx, dy):
         cp = ctx.cp
         rank_major = dy.index_select(0, ctx.order).contiguous()
+        if cp.nvlink is not None and dy.is_cuda:
+            return cp.nvlink.reduce_scatter(rank_major), None
         return tp_ops.reduce_scatter_raw(rank_major, cp.group, cp.size), None
 
 

@@ -92,6 +92,12 @@ def parallelize_decoder(model: nn.Module, *, pdims, job_config, device: torch.de
 
         model.cp = CPContext(group=pdims.group("cp"), size=pdims.cp, rank=pdims.local_rank("cp"),
                              mode=par.cp_comm, load_balancer=par.context_parallel_load_balancer or "none")
+        if getattr(par, "cp_transport", "nccl") == "nvlink" and device.type == "cuda":
+            from .cp_nvlink import CPNvlink
+            from .symm import symm_available
+
+            if symm_available():
+                model.cp.nvlink = CPNvlink(model.cp.group, device, nbytes=int(par.cp_symm_bytes))
     apply_activation_checkpointing(model, job_config.activation_checkpoint)
 
     param_dtype = torch.bfloat16 if tr.mixed_precision_param == "bfloat16" else torch.float32
