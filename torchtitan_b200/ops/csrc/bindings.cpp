@@ -43,7 +43,7 @@ void reduce_scatter_pull(at::IntArrayRef grad_ptrs, int64_t my_rank, int64_t off
                          bool accumulate);
 void adamw_allgather_(at::Tensor master, const at::Tensor& grad, at::Tensor exp_avg, at::Tensor exp_avg_sq,
                       at::IntArrayRef param_ptrs, int64_t my_rank, int64_t offset, bool param_is_bf16,
-                      const at::Tensor& grad_scale, double lr, double beta1, double beta2, double eps,
+                      int64_t multicast_ptr, const at::Tensor& grad_scale, double lr, double beta1, double beta2, double eps,
                       double weight_decay, double bc1, double bc2);
 std::tuple<at::Tensor, at::Tensor, at::Tensor> moe_router_fwd(const at::Tensor& logits, const c10::optional<at::Tensor>& bias,
                                                               int64_t top_k, bool sigmoid, bool route_norm,
@@ -133,6 +133,6 @@ TORCH_LIBRARY(tb200, m) {
   m.def("reduce_scatter_pull(int[] grad_ptrs, int my_rank, int offset, Tensor(a!) out, bool grad_is_bf16, "
         "bool accumulate) -> ()", &tb200::reduce_scatter_pull);
   m.def("adamw_allgather_(Tensor(a!) master, Tensor grad, Tensor(b!) exp_avg, Tensor(c!) exp_avg_sq, int[] param_ptrs, "
-        "int my_rank, int offset, bool param_is_bf16, Tensor grad_scale, float lr, float beta1, float beta2, float eps, "
+        "int my_rank, int offset, bool param_is_bf16, int multicast_ptr, Tensor grad_scale, float lr, float beta1, float beta2, float eps, "
         "float weight_decay, float bc1, float bc2) -> ()", &tb200::adamw_allgather_);
 }

@@ -199,12 +199,36 @@ void all_gather_pull(at::IntArrayRef src_ptrs, int64_t my_rank, int64_t nbytes, 
   C10_CUDA_KERNEL_LAUNCH_CHECK();
 }
 
+// 8 elements to a multicast address (multimem.st: the switch replicates the store to all ranks).
+__device__ __forceinline__ void mc_st16(void* p, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};"
+               ::"l"(p), "f"(__uint_as_float(a)), "f"(__uint_as_float(b)), "f"(__uint_as_float(c)), "f"(__uint_as_float(d))
+               : "memory");
+}
+template <typename T>
+__device__ __forceinline__ void mc_st8(T* p, const float (&f)[8]);
+template <>
+__device__ __forceinline__ void mc_st8<float>(float* p, const float (&f)[8]) {
+  mc_st16(p, __float_as_uint(f[0]), __float_as_uint(f[1]), __float_as_uint(f[2]), __float_as_uint(f[3]));
+  mc_st16(p + 4, __float_as_uint(f[4]), __float_as_uint(f[5]), __float_as_uint(f[6]), __float_as_uint(f[7]));
+}
+template <>
+__device__ __forceinline__ void mc_st8<__nv_bfloat16>(__nv_bfloat16* p, const float (&f)[8]) {
+  uint32_t w[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    __nv_bfloat162 h = __floats2bfloat162_rn(f[2 * j], f[2 * j + 1]);
+    w[j] = *reinterpret_cast<uint32_t*>(&h);
+  }
+  mc_st16(p, w[0], w[1], w[2], w[3]);
+}
+
 // AdamW on this rank's shard; the updated low-precision weights are stored into every peer's
 // parameter buffer at `offset` (the all-gather).
 template <typename G, typename S, typename P>
 __global__ void __launch_bounds__(256) adamw_allgather_kernel(float* __restrict__ master, const G* __restrict__ grad,
                                                               S* __restrict__ m, S* __restrict__ v, PeerPtrs params,
-                                                              int nranks, int my_rank, int64_t offset,
+                                                              P* __restrict__ mc_params, int nranks, int my_rank, int64_t offset,
                                                               const float* __restrict__ grad_scale, int64_t nvec,
                                                               float lr, float beta1, float beta2, float eps, float wd,
                                                               float bc1, float bc2_sqrt) {
@@ -231,16 +255,21 @@ __global__ void __launch_bounds__(256) adamw_allgather_kernel(float* __restrict_
     st8<float>(master + o, p);
     st8<S>(m + o, mm);
     st8<S>(v + o, vv);
-    for (int q = 0; q < nranks; ++q) {
-      const int dst = (my_rank + q) % nranks;
-      st8<P>(reinterpret_cast<P*>(params.p[dst]) + offset + o, p);
+    if (mc_params != nullptr) {
+      // one store through the NVSwitch multicast object reaches the buffer of every rank (this one included)
+      mc_st8<P>(mc_params + offset + o, p);
+    } else {
+      for (int q = 0; q < nranks; ++q) {
+        const int dst = (my_rank + q) % nranks;
+        st8<P>(reinterpret_cast<P*>(params.p[dst]) + offset + o, p);
+      }
     }
   }
 }
 
 void adamw_allgather_(at::Tensor master, const at::Tensor& grad, at::Tensor exp_avg, at::Tensor exp_avg_sq,
                       at::IntArrayRef param_ptrs, int64_t my_rank, int64_t offset, bool param_is_bf16,
-                      const at::Tensor& grad_scale, double lr, double beta1, double beta2, double eps,
+                      int64_t multicast_ptr, const at::Tensor& grad_scale, double lr, double beta1, double beta2, double eps,
                       double weight_decay, double bc1, double bc2) {
   TORCH_CHECK(master.is_cuda() && master.scalar_type() == at::kFloat && master.is_contiguous());
   const int64_t n = master.numel();
@@ -260,7 +289,8 @@ void adamw_allgather_(at::Tensor master, const at::Tensor& grad, at::Tensor exp_
 #define TB_AG(S, P)                                                                                             \
   adamw_allgather_kernel<float, S, P><<<grid, 256, 0, stream>>>(                                                  \
       master.data_ptr<float>(), grad.data_ptr<float>(), reinterpret_cast<S*>(exp_avg.data_ptr()),                 \
-      reinterpret_cast<S*>(exp_avg_sq.data_ptr()), pp, nr, (int)my_rank, offset, grad_scale.data_ptr<float>(), nvec, \
+      reinterpret_cast<S*>(exp_avg_sq.data_ptr()), pp, reinterpret_cast<P*>(multicast_ptr), nr, (int)my_rank, offset, \
+      grad_scale.data_ptr<float>(), nvec,                                                                          \
       (float)lr, (float)beta1, (float)beta2, (float)eps, (float)weight_decay, (float)bc1, sqrtf((float)bc2))
   using bf16 = __nv_bfloat16;
   if (sb && param_is_bf16) TB_AG(bf16, bf16);

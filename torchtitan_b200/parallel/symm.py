@@ -55,6 +55,18 @@ class _GroupArena:
         self.buf = symm_mem.empty(total, dtype=torch.uint8, device=device)
         self.handle = symm_mem.rendezvous(self.buf, gname)
         self.base_ptrs = [int(p) for p in self.handle.buffer_ptrs]
+        # NVSwitch multicast address of the same buffer (0 when the fabric or the driver has none);
+        # used only when TB200_MULTICAST=1 asks for it
+        self.mc_base = 0
+        if os.environ.get("TB200_MULTICAST", "0") == "1":
+            try:
+                self.mc_base = int(getattr(self.handle, "multicast_ptr", 0) or 0)
+            except Exception:
+                self.mc_base = 0
+            if self.rank == 0:
+                from torchtitan_b200.utils.logging import logger
+
+                logger.info(f"symmetric arena of group {gname}: multicast stores {'on' if self.mc_base else 'unavailable'}")
         self.flags = symm_mem.empty(_FLAG_SLOTS * self.size, dtype=torch.int32, device=device)
         self.flags.zero_()
         self.flag_handle = symm_mem.rendezvous(self.flags, gname)
@@ -144,8 +156,11 @@ class SymmetricArena:
             h = groups[gi]
             b1, b2 = h["betas"]
             _count()
+            mc = 0
+            if arena.mc_base:
+                mc = arena.mc_base + (ptrs[arena.rank] - arena.base_ptrs[arena.rank])   # same offset inside the arena
             ops.adamw_allgather_(unit.master[a:b], grad[a:b], unit.exp_avg[a:b], unit.exp_avg_sq[a:b], ptrs,
-                                 arena.rank, unit.shard_start + a, bf16, grad_scale, float(h["lr"]), float(b1),
+                                 arena.rank, unit.shard_start + a, bf16, mc, grad_scale, float(h["lr"]), float(b1),
                                  float(b2), float(h["eps"]), float(h["weight_decay"]), 1.0 - b1 ** step,
                                  1.0 - b2 ** step)
 
