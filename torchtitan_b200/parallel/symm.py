@@ -56,9 +56,9 @@ class _GroupArena:
         self.handle = symm_mem.rendezvous(self.buf, gname)
         self.base_ptrs = [int(p) for p in self.handle.buffer_ptrs]
         # NVSwitch multicast address of the same buffer (0 when the fabric or the driver has none);
-        # used only when TB200_MULTICAST=1 asks for it
+        # TB200_MULTICAST=0 keeps every store on plain peer addresses
         self.mc_base = 0
-        if os.environ.get("TB200_MULTICAST", "0") == "1":
+        if os.environ.get("TB200_MULTICAST", "1") != "0":
             try:
                 self.mc_base = int(getattr(self.handle, "multicast_ptr", 0) or 0)
             except Exception:
