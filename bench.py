@@ -112,32 +112,21 @@ class ClockSampler:
 
 
 def reference_arm(args) -> None:
-    """Run the unmodified reference from ``baseline/_ref`` through its own Trainer."""
-    ref_dir = os.path.join(ROOT, "baseline", "_ref")
-    out = {"impl": "reference"}
-    if not os.path.isdir(os.path.join(ref_dir, "torchtitan")):
-        out["unavailable"] = "baseline/_ref is empty: the reference was not installed on this box"
-        print(json.dumps(out))
-        return
-    sys.path.insert(0, ref_dir)
-    try:
-        import torchtitan.trainer  # noqa: F401  (the reference's public training API)
-    except Exception as e:  # ImportError on spmd_types / grain / torch-nightly FSDP symbols
-        out["unavailable"] = (
-            "reference installed with --no-deps but its trainer cannot be imported here: "
-            f"{type(e).__name__}: {str(e)[:160]} (needs spmd_types, grain, torchao and a PyTorch nightly; none "
-            "are in the offline wheelhouse)")
-        print(json.dumps(out))
-        return
-    out["unavailable"] = "reference trainer imported but no launch recipe is wired for this environment"
-    print(json.dumps(out))
+    """Run the unmodified upstream torchtitan through its own Trainer (see baseline/reference_arm.py)."""
+    import importlib.util
+
+    spec = importlib.util.spec_from_file_location("tb200_reference_arm", os.path.join(ROOT, "baseline", "reference_arm.py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    if ROOT in sys.path:
+        sys.path.remove(ROOT)  # nothing of this repo's package is importable on the reference path
+    mod.run(args, ROOT, ClockSampler)
 
 
 def main() -> None:
     args = parse_args()
     if args.impl == "reference":
-        if int(os.environ.get("RANK", "0")) == 0:
-            reference_arm(args)
+        reference_arm(args)
         return
     os.environ.setdefault("PYTORCH_CUDA_ALLOC_CONF", "expandable_segments:True")
     os.environ.setdefault("PYTORCH_ALLOC_CONF", "expandable_segments:True")
@@ -263,7 +252,11 @@ def main() -> None:
     tokens_per_s = T * world * args.steps / dev_s
     peak = torch.cuda.max_memory_allocated(dev) / (1 << 30)
     flops_per_token = trainer.metrics_processor.num_flops_per_token
-    loss = float(trainer._last_loss)
+    loss_t = trainer._last_loss.detach().float().reshape(1).clone()
+    lg = trainer.pdims.group("loss")
+    if lg is not None:
+        dist.all_reduce(loss_t, group=lg)   # every rank holds its share of the global mean
+    loss = float(loss_t)
     if rank == 0:
         line = {
             "metric": "tokens_per_sec", "value": tokens_per_s, "unit": "tokens/s", "n_gpus": world,
@@ -280,6 +273,10 @@ def main() -> None:
                        "seq_len": args.seq_len, "parallelism": f"fsdp{world}", "activation_checkpoint": args.ac,
                        "optimizer": f"AdamW fp32 master, {args.opt_state} moments", "fsdp_comm": trainer.engines[0].comm if trainer.engines[0]._symm is None else "nvlink",
                        "gemm": args.gemm, "attention": args.attention,
+                       "doc_mask": "skipped (every synthetic sequence is a single document)",
+                       "ac_policy": "selective = GEMM and attention outputs kept, norm outputs and SwiGLU activations "
+                                    "recomputed in backward (no GEMM is recomputed)",
+                       "param_layout": trainer.engines[0].param_layout(),
                        "l2": "per-step working set >> 126 MB L2 (no flush needed)"},
             "clocks": clocks, "e2e": e2e, "gpu_launches": launches,
             "peak_mem_gib": peak, "engine_mem_gib": mem, "loss": loss,

@@ -21,9 +21,11 @@ def test_bounded_wait_reports_timeout_without_trapping():
     a = torch.zeros(64, dtype=torch.int32, device="cuda")
     b = torch.zeros(64, dtype=torch.int32, device="cuda")
     status = torch.zeros(1, dtype=torch.int32, device="cuda")
-    torch.ops.tb200.symm_barrier([a.data_ptr(), b.data_ptr()], 0, 1, status, 2_000_000)  # ~1 ms of cycles
+    epoch = torch.zeros(1, dtype=torch.int32, device="cuda")
+    torch.ops.tb200.symm_barrier([a.data_ptr(), b.data_ptr()], 0, epoch, status, 2_000_000, None)  # ~1 ms of cycles
     torch.cuda.synchronize()
     assert int(status.item()) & 4
+    assert int(epoch.item()) == 1  # the kernel advanced the device-side epoch
     assert int(b[0].item()) == 1  # our own arrival was published to the "peer"
     # the context is still healthy
     assert float(torch.ones(4, device="cuda").sum()) == 4.0
@@ -120,6 +122,65 @@ def test_reduce_scatter_pull(tmp_path):
     run_distributed(_rs_ag, 2, out, backend="nccl")
     r = torch.load(out)
     assert r["ok1"] and r["ok2"]
+
+
+def _adamw_ag(rank, world, out_path):
+    """The fused AdamW + all-gather kernel on raw buffers; with TB200_MULTICAST=1 in the environment
+    the refreshed weights travel as multimem stores through the switch, else as per-peer stores."""
+    import torch.distributed as dist
+
+    from torchtitan_b200.parallel.fsdp import FlatUnit
+    from torchtitan_b200.parallel.parallel_dims import ParallelDims
+    from torchtitan_b200.parallel.symm import SymmetricArena
+
+    dev = torch.device("cuda", rank)
+    pdims = ParallelDims(world_size=world, rank=rank).build()
+    g = pdims.group("fsdp")
+    n = 1 << 18
+    arena = SymmetricArena(pdims, dev)
+    arena.reserve(g, 2 * n * 2)
+    unit = FlatUnit("u", [], g, world, rank)
+    unit.padded, unit.shard_numel = n, n // world
+    unit.flat_param = arena.alloc(n, torch.bfloat16, g)
+    unit.flat_param.zero_()
+    S = n // world
+    gen = torch.Generator(device=dev).manual_seed(7 + rank)
+    unit.master = torch.randn(S, device=dev, generator=gen)
+    unit.exp_avg = torch.zeros(S, device=dev)
+    unit.exp_avg_sq = torch.zeros(S, device=dev)
+    grad = torch.randn(S, device=dev, generator=gen)
+    ref_master = unit.master.clone()
+    groups = [dict(lr=1e-2, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1)]
+    arena.barrier_all()
+    arena.adamw_allgather(unit, [(0, 0, S)], groups, 1, torch.ones(1, device=dev), grad)
+    arena.barrier_all()
+    torch.cuda.synchronize()
+    # reference: AdamW step 1 on the shard, then all-gather of the bf16 weights
+    m = 0.1 * grad
+    v = 0.05 * grad * grad
+    upd = (m / (1 - 0.9)) / ((v / (1 - 0.95)).sqrt() + 1e-8)
+    exp_shard = (ref_master * (1 - 1e-2 * 0.1) - 1e-2 * upd).bfloat16()
+    want = torch.empty(n, dtype=torch.bfloat16, device=dev)
+    dist.all_gather_into_tensor(want, exp_shard)
+    err = (unit.flat_param.float() - want.float()).abs().max()
+    used_mc = 1.0 if next(iter(arena._arenas.values())).mc_base else 0.0
+    st = float(next(iter(arena._arenas.values())).status.item())
+    t = torch.stack([err, torch.tensor(st, device=dev), torch.tensor(used_mc, device=dev)])
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    if rank == 0:
+        torch.save(t.cpu(), out_path)
+
+
+@pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
+def test_adamw_allgather_multicast_matches_peer_stores(tmp_path):
+    """The only test that binds memory to an NVSwitch multicast object: multimem.st against per-peer stores."""
+    a, b = str(tmp_path / "peer.pt"), str(tmp_path / "mc.pt")
+    run_distributed(_adamw_ag, 2, a, backend="nccl")
+    run_distributed(_adamw_ag, 2, b, backend="nccl", env={"TB200_MULTICAST": "1", "TORCH_SYMM_MEM_DISABLE_MULTICAST": "0"})
+    ra, rb = torch.load(a), torch.load(b)
+    assert ra[1] == 0 and rb[1] == 0, "a bounded wait expired"
+    assert ra[2] == 0, "the default test environment must not use multicast"
+    assert ra[0] <= 1e-2 and rb[0] <= 1e-2, (ra, rb)
 
 
 def _fused_tp(rank, world, out_path):

@@ -39,7 +39,7 @@ def _call(lib, dy, x, w, rstd, dx, dw):
 
 
 @pytest.mark.parametrize("dtype,rows,dim", [(torch.bfloat16, 1000, 4096), (torch.float32, 37, 1024),
-                                            (torch.bfloat16, 3, 8192)])
+                                            (torch.bfloat16, 3, 8192), (torch.float32, 129, 8192)])
 def test_noalloc_matches_allocating_operator_twice(dtype, rows, dim):
     lib = _lib()
     torch.manual_seed(0)
@@ -58,6 +58,22 @@ def test_noalloc_matches_allocating_operator_twice(dtype, rows, dim):
         assert torch.cuda.memory_allocated() == before
         assert torch.allclose(dx.float(), dx_ref.float(), atol=tol, rtol=tol)
         assert torch.allclose(dw, dw_ref, atol=1e-2 * rows ** 0.5 if dtype == torch.bfloat16 else 1e-3, rtol=1e-3)
+
+
+def test_noalloc_with_no_rows_writes_a_zero_weight_gradient():
+    lib = _lib()
+    dim = 2048
+    x = torch.ones(1, dim, device="cuda", dtype=torch.bfloat16)   # valid pointers; zero rows are passed below
+    w = torch.ones(dim, device="cuda", dtype=torch.bfloat16)
+    rstd = torch.ones(1, device="cuda")
+    stream = torch.cuda.current_stream().cuda_stream
+    for _ in range(2):
+        dw = torch.full((dim,), 7.0, device="cuda")
+        rc = lib.tb200_rmsnorm_bwd_noalloc(x.data_ptr(), x.data_ptr(), w.data_ptr(), rstd.data_ptr(), x.data_ptr(),
+                                           dw.data_ptr(), 0, dim, 0, ctypes.c_void_p(stream))
+        assert rc == 0, lib.tb200_noalloc_strerror(rc).decode()
+        torch.cuda.synchronize()
+        assert float(dw.abs().max()) == 0.0
 
 
 def test_noalloc_rejects_rows_longer_than_the_static_scratch():

@@ -55,6 +55,9 @@ def build_llama_config(*, dim: int, n_layers: int, n_heads: int, n_kv_heads: int
 llama3_configs = {
     "debugmodel": lambda: build_llama_config(dim=256, n_layers=6, n_heads=16, n_kv_heads=None, vocab_size=2048,
                                              multiple_of=256),
+    # head dimension 128 with grouped queries: the shape the tcgen05 attention kernels are built for
+    "debugmodel_hd128": lambda: build_llama_config(dim=512, n_layers=4, n_heads=4, n_kv_heads=2, vocab_size=2048,
+                                                   multiple_of=256),
     "debugmodel_gqa": lambda: build_llama_config(dim=256, n_layers=4, n_heads=8, n_kv_heads=2, vocab_size=2048,
                                                  multiple_of=256),
     "1B": lambda: build_llama_config(dim=2048, n_layers=16, n_heads=32, n_kv_heads=8, vocab_size=128256,

@@ -29,6 +29,13 @@ def llama3_debugmodel() -> Trainer.Config:
     )
 
 
+def llama3_debugmodel_hd128() -> Trainer.Config:
+    """Debug model whose attention has head dimension 128 (runs the flash-attention kernels)."""
+    cfg = llama3_debugmodel()
+    cfg.model.flavor = "debugmodel_hd128"
+    return cfg
+
+
 def llama3_debugmodel_c4() -> Trainer.Config:
     cfg = llama3_debugmodel()
     cfg.dataloader = BaseDataLoader.Config(dataset="c4_test")

@@ -19,7 +19,7 @@ void gemm_bf16(const at::Tensor& a, const at::Tensor& b, at::Tensor c, int64_t m
 void gemm_grouped_bf16(const at::Tensor& a, const at::Tensor& b, at::Tensor c, const at::Tensor& offs, int64_t mode,
                        int64_t align, bool accumulate);
 void gemm_allgather_bf16(const at::Tensor& a_gather, const at::Tensor& b, at::Tensor c, at::IntArrayRef peer_ptrs,
-                         int64_t rank, at::Tensor flags, int64_t epoch, int64_t mode);
+                         int64_t rank, at::Tensor flags, const at::Tensor& epoch, int64_t mode);
 void gemm_scatter_bf16(const at::Tensor& a, const at::Tensor& b, at::IntArrayRef staging_ptrs, int64_t rank, int64_t mode);
 at::Tensor sum_slots(const at::Tensor& staging);
 int64_t gemm_status(bool clear);
@@ -37,7 +37,8 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor> flash_bwd(const at::Tensor& d_o, 
                                                          const c10::optional<at::Tensor>& dv_out);
 int64_t flash_status(bool clear);
 void flash_set_debug(int64_t v);
-void symm_barrier(at::IntArrayRef flag_ptrs, int64_t my_rank, int64_t epoch, at::Tensor status, int64_t max_cycles);
+void symm_barrier(at::IntArrayRef flag_ptrs, int64_t my_rank, at::Tensor epoch, at::Tensor status, int64_t max_cycles,
+                  const c10::optional<at::Tensor>& bump);
 void all_gather_pull(at::IntArrayRef src_ptrs, int64_t my_rank, int64_t nbytes, at::Tensor out);
 void reduce_scatter_pull(at::IntArrayRef grad_ptrs, int64_t my_rank, int64_t offset, at::Tensor out, bool grad_is_bf16,
                          bool accumulate);
@@ -91,7 +92,7 @@ TORCH_LIBRARY(tb200, m) {
   m.def("gemm_grouped_bf16(Tensor a, Tensor b, Tensor(a!) c, Tensor offs, int mode, int align, bool accumulate) -> ()",
         &tb200::gemm_grouped_bf16);
   m.def("gemm_allgather_bf16(Tensor(a!) a_gather, Tensor b, Tensor(b!) c, int[] peer_ptrs, int rank, Tensor(c!) flags, "
-        "int epoch, int mode) -> ()", &tb200::gemm_allgather_bf16);
+        "Tensor epoch, int mode) -> ()", &tb200::gemm_allgather_bf16);
   m.def("gemm_scatter_bf16(Tensor a, Tensor b, int[] staging_ptrs, int rank, int mode) -> ()", &tb200::gemm_scatter_bf16);
   m.def("sum_slots(Tensor staging) -> Tensor", &tb200::sum_slots);
   m.def("gemm_status(bool clear) -> int", &tb200::gemm_status);
@@ -127,7 +128,7 @@ TORCH_LIBRARY(tb200, m) {
   m.def("moe_permute_rows(Tensor x, Tensor dest, int rows) -> Tensor", &tb200::moe_permute_rows);
   m.def("moe_combine_rows(Tensor y, Tensor dest, Tensor? wts) -> Tensor", &tb200::moe_combine_rows);
   m.def("moe_combine_bwd(Tensor dout, Tensor y, Tensor dest, Tensor wts) -> (Tensor, Tensor)", &tb200::moe_combine_bwd);
-  m.def("symm_barrier(int[] flag_ptrs, int my_rank, int epoch, Tensor(a!) status, int max_cycles) -> ()",
+  m.def("symm_barrier(int[] flag_ptrs, int my_rank, Tensor(a!) epoch, Tensor(b!) status, int max_cycles, Tensor(c!)? bump=None) -> ()",
         &tb200::symm_barrier);
   m.def("all_gather_pull(int[] src_ptrs, int my_rank, int nbytes, Tensor(a!) out) -> ()", &tb200::all_gather_pull);
   m.def("reduce_scatter_pull(int[] grad_ptrs, int my_rank, int offset, Tensor(a!) out, bool grad_is_bf16, "

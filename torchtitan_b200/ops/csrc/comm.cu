@@ -44,10 +44,22 @@ __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
   return v;
 }
 
-// flags[q] on rank r holds the latest epoch published by rank q.
-__global__ void symm_barrier_kernel(PeerPtrs flags, int nranks, int my_rank, uint32_t epoch, int* status,
-                                    long long max_cycles) {
+// flags[q] on rank r holds the latest epoch published by rank q.  The epoch is a device-side
+// counter that the kernel itself advances: every rank runs the same sequence of barriers on an
+// arena, so the counters stay equal across ranks, and a barrier replayed from a CUDA graph
+// publishes a fresh epoch on every replay (a host-side counter would be frozen into the graph).
+// `bump`, when given, is a second counter advanced by one in the same launch (the fused
+// all-gather GEMM that follows reads it as its own epoch).
+__global__ void symm_barrier_kernel(PeerPtrs flags, int nranks, int my_rank, uint32_t* epoch_counter, uint32_t* bump,
+                                    int* status, long long max_cycles) {
+  __shared__ uint32_t s_epoch;
   const int t = threadIdx.x;
+  if (t == 0) {
+    s_epoch = atomicAdd(epoch_counter, 1u) + 1u;
+    if (bump != nullptr) atomicAdd(bump, 1u);
+  }
+  __syncthreads();
+  const uint32_t epoch = s_epoch;
   if (t >= nranks) return;
   __threadfence_system();
   st_release_sys(reinterpret_cast<uint32_t*>(flags.p[t]) + my_rank, epoch);
@@ -64,13 +76,22 @@ __global__ void symm_barrier_kernel(PeerPtrs flags, int nranks, int my_rank, uin
   }
 }
 
-void symm_barrier(at::IntArrayRef flag_ptrs, int64_t my_rank, int64_t epoch, at::Tensor status, int64_t max_cycles) {
+void symm_barrier(at::IntArrayRef flag_ptrs, int64_t my_rank, at::Tensor epoch, at::Tensor status, int64_t max_cycles,
+                  const c10::optional<at::Tensor>& bump) {
   TORCH_CHECK(status.is_cuda() && status.scalar_type() == at::kInt && status.numel() >= 1);
+  TORCH_CHECK(epoch.is_cuda() && epoch.scalar_type() == at::kInt && epoch.numel() == 1, "symm_barrier: epoch is an int32[1] device tensor");
+  TORCH_CHECK((int)flag_ptrs.size() <= 32, "symm_barrier: at most 32 ranks");
+  uint32_t* bp = nullptr;
+  if (bump.has_value() && bump->defined()) {
+    TORCH_CHECK(bump->is_cuda() && bump->scalar_type() == at::kInt && bump->numel() == 1);
+    bp = reinterpret_cast<uint32_t*>(bump->data_ptr<int>());
+  }
   c10::cuda::CUDAGuard guard(status.device());
   const PeerPtrs pp = make_peers(flag_ptrs);
   auto stream = at::cuda::getCurrentCUDAStream();
-  symm_barrier_kernel<<<1, 32, 0, stream>>>(pp, (int)flag_ptrs.size(), (int)my_rank, (uint32_t)epoch,
-                                            status.data_ptr<int>(), (long long)max_cycles);
+  symm_barrier_kernel<<<1, 32, 0, stream>>>(pp, (int)flag_ptrs.size(), (int)my_rank,
+                                            reinterpret_cast<uint32_t*>(epoch.data_ptr<int>()), bp, status.data_ptr<int>(),
+                                            (long long)max_cycles);
   C10_CUDA_KERNEL_LAUNCH_CHECK();
 }
 

@@ -24,6 +24,7 @@
 // All mbarrier waits are bounded; on a timeout every role leaves its loop, TMEM is released and
 // kStatusWaitTimedOut is set in the status word.  TMA loads are plain tile loads.
 #include <ATen/ATen.h>
+#include <cstdlib>
 #include <ATen/cuda/CUDAContext.h>
 #include <c10/cuda/CUDAGuard.h>
 #include <cuda.h>
@@ -922,7 +923,14 @@ static CUtensorMap make_tmap_thd(const at::Tensor& t, uint32_t rows) {
 }
 
 static int g_flash_debug = 0;
-void flash_set_debug(int64_t v) { g_flash_debug = (int)v; }
+// Timing diagnostics that make the kernel skip part of its work (results are garbage by design).
+// Refused unless the process was started with TB200_KERNEL_TIMING_DEBUG=1, so that no training
+// job can switch them on by accident.
+void flash_set_debug(int64_t v) {
+  TORCH_CHECK(v == 0 || std::getenv("TB200_KERNEL_TIMING_DEBUG") != nullptr,
+              "flash_set_debug: set TB200_KERNEL_TIMING_DEBUG=1 in the environment to enable the timing switches");
+  g_flash_debug = (int)v;
+}
 
 static at::Tensor& flash_status_tensor(const at::Device& dev) {
   static std::vector<at::Tensor> per_device(64);

@@ -34,6 +34,7 @@
 // kStatusWaitTimedOut in the status word.  TMA loads are plain tile loads: the CTA pair uses the
 // cta_group::2 form only so that both CTAs can report bytes to the barrier of CTA 0.
 #include <ATen/ATen.h>
+#include <cstdlib>
 #include <ATen/cuda/CUDAContext.h>
 #include <c10/cuda/CUDAGuard.h>
 #include <cuda.h>
@@ -93,7 +94,8 @@ struct Params {
   // GEMM -> reduce-scatter: the epilogue stores each tile into the staging buffer of the rank that
   // owns those rows (slot = this rank) with TMA stores to peer memory; rows of the next ranks first.
   uint32_t* a_flags;          // [ranks * shard_rows / 128], value = epoch once the block is local
-  uint32_t a_epoch;
+  const uint32_t* a_epoch;     // device counter: the value it holds when the kernel starts is this launch's epoch
+                               // (kept on the device so that a replayed CUDA graph sees a fresh epoch each time)
   int m_rotate;               // row tiles are visited from this tile index on (wrapping)
   int gather_ranks, gather_rank, gather_shard_rows, gather_row_bytes;
   const uint8_t* gather_src[8];
@@ -231,10 +233,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         if (kComm && p.a_flags != nullptr && m0 < p.M && m0 / p.gather_shard_rows != p.gather_rank) {
           // rows of another rank: wait (bounded) until the copy threads have brought this block in
           const uint32_t* f = p.a_flags + m0 / BM;
+          const uint32_t epoch = *p.a_epoch;
           uint32_t seen = 0, spins = 0;
           while (true) {
             asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(f) : "memory");
-            if ((int32_t)(seen - p.a_epoch) >= 0) break;
+            if ((int32_t)(seen - epoch) >= 0) break;
             if (++spins > kSpinLimit || *abort_flag) { *abort_flag = 1; ok = false; break; }
           }
           if (!ok) break;
@@ -338,6 +341,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       const int per_shard = p.gather_shard_rows / BM;
       const int total = (p.gather_ranks - 1) * per_shard;
       const int n16 = BM * p.gather_row_bytes / 16;
+      const uint32_t epoch = *p.a_epoch;
       for (int c = (int)blockIdx.x; c < total; c += (int)gridDim.x) {
         const int src = (p.gather_rank + 1 + c / per_shard) % p.gather_ranks;
         const int blk = src * per_shard + c % per_shard;
@@ -355,7 +359,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         }
         __threadfence();
         asm volatile("bar.sync 1, %0;" ::"n"(kCommThreads) : "memory");   // the four copy warps (no waits inside this loop)
-        if (ct == 0) asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p.a_flags + blk), "r"(p.a_epoch) : "memory");
+        if (ct == 0) asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p.a_flags + blk), "r"(epoch) : "memory");
       }
     }
   } else {
@@ -480,7 +484,14 @@ static at::Tensor& gemm_status_tensor(const at::Device& dev) {
 }
 
 static int g_gemm_debug = 0;
-void gemm_set_debug(int64_t v) { g_gemm_debug = (int)v; }
+// Timing diagnostics that make the kernel skip part of its work (results are garbage by design).
+// Refused unless the process was started with TB200_KERNEL_TIMING_DEBUG=1, so that no training
+// job can switch them on by accident.
+void gemm_set_debug(int64_t v) {
+  TORCH_CHECK(v == 0 || std::getenv("TB200_KERNEL_TIMING_DEBUG") != nullptr,
+              "gemm_set_debug: set TB200_KERNEL_TIMING_DEBUG=1 in the environment to enable the timing switches");
+  g_gemm_debug = (int)v;
+}
 static int g_gemm_variant = 0;  // 0 = choose by shape, 1 = single CTA tiles, 2 = CTA-pair tiles
 
 void gemm_set_variant(int64_t v) {
@@ -532,7 +543,7 @@ static void launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const CUte
 }
 
 static void clear_comm(gemm::Params& p) {
-  p.a_flags = nullptr; p.a_epoch = 0; p.m_rotate = 0;
+  p.a_flags = nullptr; p.a_epoch = nullptr; p.m_rotate = 0;
   p.gather_ranks = 0; p.gather_rank = 0; p.gather_shard_rows = 1; p.gather_row_bytes = 0; p.gather_dst = nullptr;
   for (auto& g : p.gather_src) g = nullptr;
   p.scatter_ranks = 0; p.scatter_rank = 0; p.scatter_shard_rows = 1;
@@ -654,11 +665,13 @@ void gemm_grouped_bf16(const at::Tensor& a, const at::Tensor& b, at::Tensor c, c
 // All-gather -> GEMM.  `a_gather` is this rank's gather buffer [ranks * shard_rows, K] in symmetric
 // memory with the rank's own rows already in place; `peer_ptrs[r]` is the address of rank r's
 // gather buffer; `flags` (uint32 [ranks * shard_rows / 128], zero-initialised once) and the
-// monotonically increasing `epoch` tell the GEMM which row blocks have arrived.  Every rank must
-// have passed a barrier after writing its own rows and before this call.
+// monotonically increasing `epoch` (a one-element int32 device tensor that the caller increments in
+// stream order before each call, e.g. through the `bump` argument of symm_barrier) tell the GEMM
+// which row blocks have arrived.  Every rank must have passed a barrier after writing its own rows
+// and before this call.
 //   mode 0: c = gathered . b^T (b [N, K]);  mode 1: c = gathered . b (b [K, N]).
 void gemm_allgather_bf16(const at::Tensor& a_gather, const at::Tensor& b, at::Tensor c, at::IntArrayRef peer_ptrs,
-                         int64_t rank, at::Tensor flags, int64_t epoch, int64_t mode) {
+                         int64_t rank, at::Tensor flags, const at::Tensor& epoch, int64_t mode) {
   using namespace gemm;
   check_bf16_2d(a_gather, "a_gather"); check_bf16_2d(b, "b"); check_bf16_2d(c, "c");
   TORCH_CHECK(mode == 0 || mode == 1, "gemm_allgather_bf16: mode 0 (NT) or 1 (NN)");
@@ -670,6 +683,7 @@ void gemm_allgather_bf16(const at::Tensor& a_gather, const at::Tensor& b, at::Te
   TORCH_CHECK(M % R == 0 && (M / R) % 256 == 0, "gemm_allgather_bf16: the shard must be a multiple of 256 rows");
   TORCH_CHECK(K % 8 == 0 && N % 8 == 0);
   TORCH_CHECK(flags.is_cuda() && flags.scalar_type() == at::kInt && flags.numel() >= M / BM && flags.is_contiguous());
+  TORCH_CHECK(epoch.is_cuda() && epoch.scalar_type() == at::kInt && epoch.numel() == 1, "gemm_allgather_bf16: epoch is an int32[1] device tensor");
   c10::cuda::CUDAGuard guard(a_gather.device());
   C10_CUDA_CHECK(cudaSetDevice(a_gather.device().index()));
   const bool b_mn = mode == 1;
@@ -686,7 +700,7 @@ void gemm_allgather_bf16(const at::Tensor& a_gather, const at::Tensor& b, at::Te
   clear_comm(p);
   const int shard = (int)(M / R);
   p.a_flags = reinterpret_cast<uint32_t*>(flags.data_ptr<int>());
-  p.a_epoch = (uint32_t)epoch;
+  p.a_epoch = reinterpret_cast<const uint32_t*>(epoch.data_ptr<int>());
   p.m_rotate = (int)rank * (shard / (2 * BM));
   p.gather_ranks = R; p.gather_rank = (int)rank; p.gather_shard_rows = shard; p.gather_row_bytes = (int)(K * 2);
   for (int r = 0; r < R; ++r) p.gather_src[r] = reinterpret_cast<const uint8_t*>(static_cast<uintptr_t>(peer_ptrs[r]));

@@ -13,6 +13,7 @@
 // pipeline (A 16 KB + B 16 KB + scales 1 KB per stage), two TMEM accumulators of 128 columns and
 // 8 columns of scale factors per stage.  Roles and the bounded waits are those of the bf16 GEMM.
 #include <ATen/ATen.h>
+#include <cstdlib>
 #include <ATen/cuda/CUDAContext.h>
 #include <c10/cuda/CUDAGuard.h>
 #include <cuda.h>
@@ -581,7 +582,14 @@ static CUtensorMap make_tmap_sf(const void* ptr, uint64_t row_tiles, uint64_t k_
 }
 
 static int g_mx_debug = 0;
-void gemm_mx_set_debug(int64_t v) { g_mx_debug = (int)v; }
+// Timing diagnostics that make the kernel skip part of its work (results are garbage by design).
+// Refused unless the process was started with TB200_KERNEL_TIMING_DEBUG=1, so that no training
+// job can switch them on by accident.
+void gemm_mx_set_debug(int64_t v) {
+  TORCH_CHECK(v == 0 || std::getenv("TB200_KERNEL_TIMING_DEBUG") != nullptr,
+              "gemm_mx_set_debug: set TB200_KERNEL_TIMING_DEBUG=1 in the environment to enable the timing switches");
+  g_mx_debug = (int)v;
+}
 static int g_mx_variant = 0;   // 0: by shape, 1: one CTA per tile, 2: CTA pairs
 void gemm_mx_set_variant(int64_t v) {
   TORCH_CHECK(v >= 0 && v <= 2, "gemm_mx_set_variant: 0 (auto), 1 (single CTA) or 2 (CTA pair)");

@@ -1,6 +1,7 @@
 // Allocation-free RMSNorm backward: see noalloc.h for the contract.
 #include <cuda_runtime.h>
 
+#include <atomic>
 #include <mutex>
 
 #include "common.cuh"
@@ -111,7 +112,7 @@ __global__ void __launch_bounds__(256) reduce_partials_kernel(const float* __res
 constexpr int kMaxDevices = 64;
 std::mutex g_mu;
 float* g_scratch_ptr[kMaxDevices] = {nullptr};
-int g_last_cuda_error = 0;
+std::atomic<int> g_last_cuda_error{0};   // written by any host thread, outside the set-up mutex too
 
 // Device address of g_partials for the current device; looked up once per device.
 int scratch_for_current_device(float** out) {
@@ -199,4 +200,4 @@ extern "C" const char* tb200_noalloc_strerror(int code) {
   }
 }
 
-extern "C" int tb200_noalloc_last_cuda_error(void) { return g_last_cuda_error; }
+extern "C" int tb200_noalloc_last_cuda_error(void) { return g_last_cuda_error.load(); }

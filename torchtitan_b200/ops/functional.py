@@ -2,8 +2,12 @@
 
 Every operator has one CUDA implementation (the in-tree sm_100a extension,
 ``torch.ops.tb200``) and one plain-PyTorch implementation used for CPU tensors.
-A CUDA tensor never takes the PyTorch path: if the extension is missing the call
-raises.
+If the extension is missing, a call with CUDA tensors raises.  Two library paths remain for
+CUDA tensors and are counted in ``settings.library_fallbacks``: a bf16 GEMM whose inner
+dimensions are not multiples of 8 elements (a TMA row must be a multiple of 16 bytes) runs on
+``torch.mm``, as does any GEMM when ``kernels.gemm = "cublas"`` selects the library arm; and
+attention shapes outside the flash kernel's instantiations run the blocked PyTorch fallback of
+:func:`attention`.
 
 Memory policy.  The fused functions below are where op-level selective
 recomputation lives: ``norm_linear`` keeps only the un-normalised input and the
@@ -42,6 +46,7 @@ class _Settings:
     recompute: bool = True  # fused functions recompute norm / SwiGLU activations in backward
     launches: int = 0  # count of launches of this package's own kernels
     count_launches: bool = False
+    library_fallbacks: int = 0  # CUDA calls that went to a library / PyTorch path (see the module docstring)
 
 
 settings = _Settings()
@@ -106,9 +111,8 @@ def gemm_tn(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None = None, a
 
 
 def _tc_gemm(a, b, mode, out, accumulate):
-    """Hand-written tcgen05 GEMM; returns None when the shape is not supported."""
-    if not (a.is_contiguous() and b.is_contiguous()):
-        return None
+    """Hand-written tcgen05 GEMM; returns None (library path, counted) when a row is not a multiple of 16 bytes."""
+    a, b = a.contiguous(), b.contiguous()
     if mode == 0:
         M, K = a.shape
         N = b.shape[0]
@@ -119,11 +123,13 @@ def _tc_gemm(a, b, mode, out, accumulate):
         K, M = a.shape
         N = b.shape[1]
     if (N % 8) or K == 0 or ((M % 8) if mode == 2 else (K % 8)):
+        settings.library_fallbacks += 1
         return None
     if out is None:
         out = torch.empty(M, N, dtype=torch.bfloat16, device=a.device)
         accumulate = False
     elif not (out.is_contiguous() and out.dtype == torch.bfloat16):
+        settings.library_fallbacks += 1
         return None
     torch.ops.tb200.gemm_bf16(a, b, out, mode, accumulate)
     _count()

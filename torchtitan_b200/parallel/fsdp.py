@@ -563,6 +563,13 @@ class ShardedModel:
             for s in u.slots:
                 yield u, s
 
+    def param_layout(self) -> str:
+        """One-line description of where parameters and gradients live (reported by the benchmark)."""
+        if all(u.size == 1 for u in self.units):
+            return "single rank: bf16 parameters and gradients, fp32 master weights and moments"
+        return ("bf16 parameters and gradients replicated on every rank (resident, refreshed once per step by the "
+                "optimizer kernel), fp32 master weights and moments sharded 1/N")
+
     def memory_summary(self) -> dict[str, float]:
         gib = 1 << 30
         tot = {"flat_param": 0, "flat_grad": 0, "master": 0, "grad_shard": 0, "opt_state": 0}

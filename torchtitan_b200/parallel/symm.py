@@ -9,9 +9,13 @@ use of symmetric memory for FSDP and MinimalAsyncEP, torchtitan/distributed/fsdp
 torchtitan/distributed/minimal_async_ep/api.py:174-295, re-designed around in-kernel
 transfers).
 
-Synchronisation is a flag barrier with monotonically increasing epochs.  Waits are bounded
-(``TB200_SYMM_TIMEOUT_S``, default 30 s): on expiry the kernel sets a bit in a status word
-and returns; :meth:`check_status` raises on the host.  Nothing traps the device.
+Synchronisation is a flag barrier with monotonically increasing epochs.  The epoch lives in
+device memory and is advanced by the barrier kernel itself, so a barrier captured into a CUDA
+graph publishes a new epoch on every replay.  Waits are bounded (``TB200_SYMM_TIMEOUT_S``,
+default 30 s): on expiry the kernel sets a bit in a status word and returns.  Every arena
+registers its status word with :class:`StatusMonitor`; the trainer polls the monitor every step
+(an asynchronous copy to pinned memory, checked one step later, no synchronisation) and raises
+when any word is non-zero.  Nothing traps the device.
 """
 
 from __future__ import annotations
@@ -24,7 +28,69 @@ import torch.distributed as dist
 from torchtitan_b200.ops import ext
 from torchtitan_b200.ops.functional import _count
 
-__all__ = ["SymmetricArena", "symm_available"]
+__all__ = ["SymmetricArena", "StatusMonitor", "status_monitor", "symm_available"]
+
+
+class StatusMonitor:
+    """Collects the status words of every bounded-wait path and checks them without stalling the GPU.
+
+    ``poll()`` queues a device-to-pinned-host copy of all registered words on the current stream and
+    examines the copy queued by the previous ``poll()`` if its event has completed (it always has
+    one step later); ``check()`` synchronises and examines the current values.  Both raise
+    ``RuntimeError`` naming the path whose wait expired."""
+
+    def __init__(self):
+        self._words: list[tuple[str, torch.Tensor]] = []
+        self._inflight: tuple | None = None
+
+    def register(self, name: str, word: torch.Tensor) -> None:
+        self._words.append((name, word))
+
+    def clear(self) -> None:
+        self._words.clear()
+        self._inflight = None
+
+    def _raise_if_set(self, values: list[int], names: list[str]) -> None:
+        bad = [(n, v) for n, v in zip(names, values) if v]
+        if bad:
+            for _, w in self._words:
+                w.zero_()
+            desc = ", ".join(f"{n} (status {v:#x})" for n, v in bad)
+            raise RuntimeError(
+                f"a bounded device wait expired in: {desc}. A peer did not arrive within the timeout "
+                "(TB200_SYMM_TIMEOUT_S); the data exchanged in that step is incomplete, so training stops here")
+
+    def poll(self) -> None:
+        if not self._words:
+            return
+        if self._inflight is not None:
+            host, ev, names = self._inflight
+            if ev is None or ev.query():
+                self._inflight = None
+                self._raise_if_set([int(x) for x in host.tolist()], names)
+            else:
+                return   # the previous copy has not landed yet: look again next step
+        words = [w.reshape(-1)[:1] for _, w in self._words]
+        names = [n for n, _ in self._words]
+        dev = torch.cat(words)
+        if dev.is_cuda:
+            host = torch.empty(dev.numel(), dtype=dev.dtype, pin_memory=True)
+            host.copy_(dev, non_blocking=True)
+            ev = torch.cuda.Event()
+            ev.record()
+        else:
+            host, ev = dev.clone(), None
+        self._inflight = (host, ev, names)
+
+    def check(self) -> None:
+        if not self._words:
+            return
+        self._inflight = None
+        vals = [int(w.reshape(-1)[0].item()) for _, w in self._words]
+        self._raise_if_set(vals, [n for n, _ in self._words])
+
+
+status_monitor = StatusMonitor()
 
 _FLAG_SLOTS = 64
 
@@ -72,9 +138,10 @@ class _GroupArena:
         self.flag_handle = symm_mem.rendezvous(self.flags, gname)
         self.flag_ptrs = [int(p) for p in self.flag_handle.buffer_ptrs]
         self.cursor = 0
-        self.epoch = 0
+        self.epoch = torch.zeros(1, dtype=torch.int32, device=device)   # advanced by the barrier kernel
         self.status = torch.zeros(1, dtype=torch.int32, device=device)
-        clock_hz = 1.9e9
+        status_monitor.register(f"symmetric arena of group {gname}", self.status)
+        clock_hz = 1e3 * float(getattr(torch.cuda.get_device_properties(device), "clock_rate", 1.9e6) or 1.9e6)
         self.max_cycles = int(float(os.environ.get("TB200_SYMM_TIMEOUT_S", "30")) * clock_hz)
         torch.cuda.synchronize(device)
         dist.barrier(group=group)
@@ -93,11 +160,11 @@ class _GroupArena:
         t.set_(self.buf.untyped_storage(), (self.buf.storage_offset() + off) // es, (numel,), (1,))
         return t, off
 
-    def barrier(self) -> None:
-        """Cross-rank barrier on the current stream (bounded wait)."""
-        self.epoch += 1
+    def barrier(self, bump: torch.Tensor | None = None) -> None:
+        """Cross-rank barrier on the current stream (bounded wait).  ``bump``: an int32[1] device
+        counter advanced by one in the same launch."""
         _count()
-        ext.require().symm_barrier(self.flag_ptrs, self.rank, self.epoch, self.status, self.max_cycles)
+        ext.require().symm_barrier(self.flag_ptrs, self.rank, self.epoch, self.status, self.max_cycles, bump)
 
 
 class SymmetricArena:

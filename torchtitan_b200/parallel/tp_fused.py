@@ -38,7 +38,7 @@ class FusedTP:
         self.arena = _GroupArena(group, device, nbytes)
         self._bufs: dict[tuple, list] = {}
         self._turn: dict[tuple, int] = {}
-        self.epoch = 0
+        self.epoch = torch.zeros(1, dtype=torch.int32, device=device)   # device counter, advanced with each gather barrier
 
     def supported(self, rows: int, *dims: int) -> bool:
         return rows % (256 * self.size) == 0 and all(d % 8 == 0 for d in dims)
@@ -66,10 +66,9 @@ class FusedTP:
         T = S * self.size
         buf, ptrs, flags = self._pair("gather", T, K)
         buf[self.rank * S:(self.rank + 1) * S].copy_(x_shard)
-        self.arena.barrier()
+        self.arena.barrier(bump=self.epoch)
         N = b.shape[0] if mode == 0 else b.shape[1]
         out = torch.empty(T, N, dtype=x_shard.dtype, device=x_shard.device)
-        self.epoch += 1
         _count()
         ext.require().gemm_allgather_bf16(buf, b, out, ptrs, self.rank, flags, self.epoch, mode)
         return out, buf

@@ -120,6 +120,9 @@ class Trainer(Configurable):
         self.config = config
         c = config
         config.validate()
+        from torchtitan_b200.parallel.symm import status_monitor
+
+        status_monitor.clear()   # arenas of an earlier trainer in this process are gone
         self.device = get_local_device()
         if self.device.type == "cuda":
             torch.cuda.set_device(self.device)
@@ -254,7 +257,7 @@ class Trainer(Configurable):
         self._mb_index = 0
         if (not c.training.disable_cuda_graphs and self.device.type == "cuda" and not pd.pp_enabled
                 and not c.activation_checkpoint.cpu_offload   # host copies cannot be captured
-                and not (pd.ep_enabled and c.parallelism.ep_comm == "nccl")):
+                and not pd.ep_enabled):   # both expert-parallel dispatchers read split sizes on the host
             from torchtitan_b200.parallel.cudagraph import CUDAGraphRunner
 
             eng = self.engines[0]
@@ -262,7 +265,6 @@ class Trainer(Configurable):
                 self._fwd_bwd_tensors,
                 snapshot=lambda: [u.grad_shard_valid for u in eng.units],
                 after_replay=lambda st: [setattr(u, "grad_shard_valid", v) for u, v in zip(eng.units, st)])
-        self._status_pending: list[tuple[int, torch.Tensor]] = []
         self._inv_tokens_cache = None
         logger.info(
             f"Trainer ready: tokens/microbatch/dp-rank {tok_mb}, grad accumulation {self.gradient_accumulation_steps}, "
@@ -405,9 +407,11 @@ class Trainer(Configurable):
             self.optimizers.step()
             self.lr_schedulers.step()
         self._last_loss, self._last_grad_norm = loss, grad_norm
+        self._poll_device_status(sync=False)
 
         if not self.metrics_processor.should_log(self.step):
             return
+        self._poll_device_status(sync=True)
         with sl.span("collect_dist_metrics"):
             lg = pd.group("loss")
             stats = torch.stack([loss.float().reshape(()), grad_norm.float().reshape(())])
@@ -428,6 +432,27 @@ class Trainer(Configurable):
         extra = {"n_tokens_seen": self.ntokens_seen}
         extra.update(self.lr_schedulers.get_metrics())
         self.metrics_processor.log(self.step, global_avg, global_max, gn, extra_metrics=extra)
+
+    def _poll_device_status(self, sync: bool) -> None:
+        """Raise when a bounded device-side wait of an NVLink path or of a kernel pipeline expired.
+
+        Every step queues an asynchronous copy of the arenas' status words and examines the copy of
+        the step before (no stall); logging steps, which synchronise anyway, read the current
+        values of the arenas and of the kernels' own status words."""
+        from torchtitan_b200.parallel.symm import status_monitor
+
+        if not sync:
+            status_monitor.poll()
+            return
+        status_monitor.check()
+        from torchtitan_b200.ops import ext
+
+        if self.device.type == "cuda" and ext.available():
+            ops = ext.require()
+            bits = int(ops.status(True)) | int(ops.gemm_status(True)) | int(ops.flash_status(True))
+            if bits & 4:
+                raise RuntimeError(f"a bounded wait inside a kernel pipeline expired (status {bits:#x}): results of this "
+                                   "step are incomplete")
 
     # ------------------------------------------------------------------
     def train(self) -> None:
