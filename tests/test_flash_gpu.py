@@ -10,7 +10,7 @@ from torchtitan_b200.ops import ext
 pytestmark = pytest.mark.gpu
 
 
-def _reference(q, k, v, scale, causal, offset, kv_first):
+def _reference(q, k, v, scale, causal, offset, kv_first, window=0, sinks=None):
     """fp32 attention with explicit masks; returns (o [Tq,Hq,D], lse [Hq,Tq])."""
     Tq, Hq, D = q.shape
     Tk, Hkv, _ = k.shape
@@ -26,9 +26,16 @@ def _reference(q, k, v, scale, causal, offset, kv_first):
         mask &= cols <= rows + offset
     if kv_first is not None:
         mask &= cols >= kv_first.long()[:, None]
+    if window:
+        mask &= cols > rows + offset - window
     s = s.masked_fill(~mask[None], float("-inf"))
-    lse = torch.logsumexp(s, dim=-1)
-    p = torch.softmax(s, dim=-1)
+    if sinks is not None:
+        s_ext = torch.cat([s, sinks.float()[:, None, None].expand(Hq, Tq, 1)], dim=-1)
+        lse = torch.logsumexp(s_ext, dim=-1)
+        p = torch.softmax(s_ext, dim=-1)[..., :-1]
+    else:
+        lse = torch.logsumexp(s, dim=-1)
+        p = torch.softmax(s, dim=-1)
     return torch.matmul(p, vf).transpose(0, 1), lse
 
 
@@ -58,8 +65,18 @@ CASES = [
 ]
 
 
+@pytest.fixture(params=[0, 1, 2, 3, 4], ids=lambda v: f"fwd{v}")
+def fwd_variant(request):
+    """Every forward kernel: 0 = whole-tile steps, 1..4 = the half-tile pipelined kernel (plain / packed fp32
+    instructions / a quarter / a half of the exponentials on the FMA pipe)."""
+    ops = ext.require()
+    ops.flash_set_fwd_variant(request.param)
+    yield request.param
+    ops.flash_set_fwd_variant(3)
+
+
 @pytest.mark.parametrize("Tq,Tk,Hq,Hkv,causal,offset,docs,packed", CASES)
-def test_flash_forward(Tq, Tk, Hq, Hkv, causal, offset, docs, packed):
+def test_flash_forward(Tq, Tk, Hq, Hkv, causal, offset, docs, packed, fwd_variant):
     ops = ext.require()
     q, k, v = _inputs(Tq, Tk, Hq, Hkv, seed=Tq + Hq, packed=packed)
     kv_first = None
@@ -118,3 +135,52 @@ def test_flash_backward_into_packed_gradient():
     assert torch.allclose(packed[:, :Hq].float(), ref[0].float(), atol=2e-2, rtol=2e-2)
     assert torch.equal(packed[:, Hq:Hq + Hkv], ref[1])
     assert torch.equal(packed[:, Hq + Hkv:], ref[2])
+
+
+WINDOW_CASES = [
+    # Tq, Tk, Hq, Hkv, offset, window, docs, sinks
+    (1024, 1024, 4, 2, 0, 128, False, False),
+    (1024, 1024, 4, 2, 0, 200, True, False),       # window and packed documents together
+    (777, 777, 2, 2, 0, 64, False, True),          # ragged, one head per CTA, sinks
+    (256, 768, 4, 2, 512, 300, False, False),      # queries are the tail of the keys
+    (512, 512, 8, 2, 0, 0, False, True),           # sinks only
+]
+
+
+def _docs_kv_first(Tq):
+    starts = torch.tensor([0, 130, 131, 517, 900], device="cuda")
+    pos = torch.arange(Tq, device="cuda")
+    return starts[torch.searchsorted(starts, pos, right=True) - 1].int()
+
+
+@pytest.mark.parametrize("Tq,Tk,Hq,Hkv,offset,window,docs,use_sinks", WINDOW_CASES)
+def test_flash_window_and_sinks(Tq, Tk, Hq, Hkv, offset, window, docs, use_sinks):
+    """Sliding window and attention sinks, forward and backward, through the autograd front-end."""
+    from torchtitan_b200.ops.flash import flash_attention_lse
+
+    q, k, v = _inputs(Tq, Tk, Hq, Hkv, seed=Tq + window)
+    kv_first = _docs_kv_first(Tq) if docs else None
+    sinks = None
+    if use_sinks:
+        sinks = (torch.randn(Hq, device="cuda") * 2.0).requires_grad_()
+    scale = 1.0 / math.sqrt(128)
+    qg, kg, vg = (t.detach().clone().requires_grad_() for t in (q, k, v))
+    o, lse = flash_attention_lse(qg, kg, vg, scale, causal=True, causal_offset=offset, kv_first=kv_first,
+                                 window=window, sinks=sinks)
+    d_o = torch.randn(Tq, Hq, 128, device="cuda").bfloat16()
+    o.backward(d_o)
+    torch.cuda.synchronize()
+    assert ext.require().flash_status(True) == 0
+    qr, kr, vr = (t.detach().float().requires_grad_() for t in (q, k, v))
+    sr = sinks.detach().clone().requires_grad_() if use_sinks else None
+    o_ref, lse_ref = _reference(qr, kr, vr, scale, True, offset, kv_first, window, sr)
+    o_ref.backward(d_o.float())
+    assert (o.float() - o_ref).abs().max().item() < 2e-2
+    assert (lse - lse_ref).abs().max().item() < 2e-2
+    for name, got, ref in (("dq", qg.grad, qr.grad), ("dk", kg.grad, kr.grad), ("dv", vg.grad, vr.grad)):
+        err = (got.float() - ref).abs().max().item()
+        tol = 2e-2 * ref.abs().max().item() + 2e-2
+        assert err <= tol, (name, err, tol)
+    if use_sinks:
+        err = (sinks.grad - sr.grad).abs().max().item()
+        assert err <= 2e-2 * sr.grad.abs().max().item() + 2e-2, (err, sr.grad)

@@ -27,14 +27,16 @@ void gemm_set_variant(int64_t v);
 void gemm_set_debug(int64_t v);
 std::tuple<at::Tensor, at::Tensor> flash_fwd(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v, double scale,
                                              bool causal, int64_t causal_offset,
-                                             const c10::optional<at::Tensor>& kv_first);
+                                             const c10::optional<at::Tensor>& kv_first, int64_t window,
+                                             const c10::optional<at::Tensor>& sinks);
+void flash_set_fwd_variant(int64_t v);
 std::tuple<at::Tensor, at::Tensor, at::Tensor> flash_bwd(const at::Tensor& d_o, const at::Tensor& q, const at::Tensor& k,
                                                          const at::Tensor& v, const at::Tensor& o, const at::Tensor& lse,
                                                          double scale, bool causal, int64_t causal_offset,
                                                          const c10::optional<at::Tensor>& kv_first,
                                                          const c10::optional<at::Tensor>& dq_out,
                                                          const c10::optional<at::Tensor>& dk_out,
-                                                         const c10::optional<at::Tensor>& dv_out);
+                                                         const c10::optional<at::Tensor>& dv_out, int64_t window);
 int64_t flash_status(bool clear);
 void flash_set_debug(int64_t v);
 void symm_barrier(at::IntArrayRef flag_ptrs, int64_t my_rank, at::Tensor epoch, at::Tensor status, int64_t max_cycles,
@@ -98,8 +100,9 @@ TORCH_LIBRARY(tb200, m) {
   m.def("gemm_status(bool clear) -> int", &tb200::gemm_status);
   m.def("gemm_set_variant(int v) -> ()", &tb200::gemm_set_variant);
   m.def("gemm_set_debug(int v) -> ()", &tb200::gemm_set_debug);
-  m.def("flash_fwd(Tensor q, Tensor k, Tensor v, float scale, bool causal, int causal_offset, Tensor? kv_first) -> "
-        "(Tensor, Tensor)", &tb200::flash_fwd);
+  m.def("flash_fwd(Tensor q, Tensor k, Tensor v, float scale, bool causal, int causal_offset, Tensor? kv_first, "
+        "int window=0, Tensor? sinks=None) -> (Tensor, Tensor)", &tb200::flash_fwd);
+  m.def("flash_set_fwd_variant(int v) -> ()", &tb200::flash_set_fwd_variant);
   m.def("flash_bwd(Tensor d_o, Tensor q, Tensor k, Tensor v, Tensor o, Tensor lse, float scale, bool causal, "
         "int causal_offset, Tensor? kv_first, Tensor(a!)? dq_out, Tensor(b!)? dk_out, Tensor(c!)? dv_out) -> "
         "(Tensor, Tensor, Tensor)", &tb200::flash_bwd);

@@ -57,6 +57,8 @@ struct FwdParams {
   int lse_stride;
   int debug;               // timing diagnostics: bit 0 skips the softmax math, bit 1 skips the MMAs (results are garbage)
   int* status;
+  int window;              // > 0: query row i sees only keys j > i + causal_offset - window (sliding window; pipelined kernel only)
+  const float* sinks;      // [Hq] per-head sink logit that joins the softmax denominator, or nullptr (pipelined kernel only)
 };
 
 __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t* r) {
@@ -343,6 +345,402 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
 }
 
 
+// -----------------------------------------------------------------------------------------
+// Forward, software-pipelined over half tiles (the default forward).
+//
+// Same roles, shared-memory and tensor-memory layout as flash_fwd_kernel, but each 128-key tile is
+// processed as two halves of 64 keys, each with its own S accumulator (64 TMEM columns), its own
+// packed P (the first 32 of those columns) and its own pair of barriers.  Per slot the chain
+// S -> softmax -> P.V of one half overlaps with the other half's: while the slot's softmax warps
+// work on half h, the tensor pipe runs P.V of half 1-h and the next tile's S for it, so the softmax
+// warps (the exponentials) run back to back instead of waiting for the MMAs of their own slot.
+//
+// Rescaling O when the running maximum grows (rare: the threshold is 2^8) touches an accumulator
+// that a P.V MMA of the other half may still be adding to.  The MMA warp follows every P.V with
+// the next S of the same half and a commit on that half's S_FULL barrier (a bare commit after the
+// last tile), so "S_FULL of the next work item is complete" implies "every P.V issued so far for
+// this slot is complete"; a row that must rescale waits for that barrier first.
+//
+// kEmu of every 8 exponentials are evaluated on the FMA pipe (round-to-nearest range reduction,
+// cubic polynomial, exponent patched in with an integer add; relative error 1e-4, below bf16
+// rounding of P), which takes load off the 16-per-clock MUFU unit that otherwise bounds the loop.
+// kPacked uses the two-wide fp32 instructions (fma.rn.f32x2 / add.f32x2) for the scale-and-shift
+// and the row sums.
+__device__ __forceinline__ uint64_t pack2(float lo, float hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void unpack2(uint64_t v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("add.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+__device__ __forceinline__ float ex2_mufu(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+// 2^x for x in [-126, 127] on the FMA pipe.
+__device__ __forceinline__ float ex2_poly(float x) {
+  x = fmaxf(x, -126.f);
+  const float fl = x + 12582912.f;                 // 1.5 * 2^23: the integer nearest to x sits in the low mantissa bits
+  const float f = x - (fl - 12582912.f);           // in [-0.5, 0.5]
+  float y = fmaf(f, 0.05500866f, 0.24221057f);
+  y = fmaf(y, f, 0.69328291f);
+  y = fmaf(y, f, 1.0f);
+  return __uint_as_float(__float_as_uint(y) + (__float_as_uint(fl) << 23));
+}
+
+template <int kEmu, bool kPacked>
+__global__ void __launch_bounds__(kThreadsFwd, 1)
+flash_fwd_pipe_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
+                      const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_o,
+                      const FwdParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  uint8_t* gen_base = smem_raw + (base - raw);
+  const uint32_t q_smem = base;
+  const uint32_t k_smem = base + 2 * kTileBytes;
+  const uint32_t v_smem = base + 4 * kTileBytes;
+  const uint32_t bar_base = base + 6 * kTileBytes;
+  // S_FULL / P_READY: index = slot * 2 + half
+  enum { Q_FULL = 0, K_FULL = 1, K_EMPTY = 3, V_FULL = 5, V_EMPTY = 7, S_FULL = 9, P_READY = 13, O_FULL = 17, O_STAGED = 18,
+         NBAR = 20 };
+  auto bar = [&](int i) { return bar_base + 8u * i; };
+  uint32_t* tmem_ptr_smem = reinterpret_cast<uint32_t*>(gen_base + 6 * kTileBytes + 8 * NBAR);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_ptr_smem + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  constexpr int kHN = kBN / 2;   // keys per half tile
+
+  const int num_q_tiles = (p.Tq + kBM - 1) / kBM;
+  const int per_tile = p.Hkv * p.ctas_per_kv_head;
+  const int q_tile = num_q_tiles - 1 - (int)blockIdx.x / per_tile;
+  const int rem = (int)blockIdx.x % per_tile;
+  const int kv_head = rem / p.ctas_per_kv_head;
+  const int group = p.Hq / p.Hkv;
+  const int head0 = kv_head * group + (rem % p.ctas_per_kv_head) * p.slots;
+  const int q0 = q_tile * kBM;
+  const int num_k_tiles = (p.Tk + kBN - 1) / kBN;
+  int j_hi = num_k_tiles - 1;
+  if (p.causal) j_hi = min(j_hi, (min(q0 + kBM - 1, p.Tq - 1) + p.causal_offset) / kBN);
+  int first_key = 0;                                                   // lowest key any row of this block sees
+  if (p.kv_first != nullptr) first_key = max(0, p.kv_first[q0]);      // kv_first is non-decreasing
+  if (p.window > 0) first_key = max(first_key, q0 + p.causal_offset - p.window + 1);
+  const int j_lo = first_key / kBN;
+  const int n_tiles = j_hi - j_lo + 1;                                 // may be <= 0: nothing visible
+  const int n_items = 2 * n_tiles;
+
+  if (threadIdx.x == 0) {
+    mbar_init(bar(Q_FULL), 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(bar(K_FULL + s), 1);
+      mbar_init(bar(K_EMPTY + s), 1);
+      mbar_init(bar(V_FULL + s), 1);
+      mbar_init(bar(V_EMPTY + s), 1);
+      mbar_init(bar(O_STAGED + s), 4);
+    }
+    for (int s = 0; s < 4; ++s) {
+      mbar_init(bar(S_FULL + s), 1);
+      mbar_init(bar(P_READY + s), 4);      // one arrival per warp (lane 0 after __syncwarp)
+    }
+    mbar_init(bar(O_FULL), 1);
+    *abort_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&tmap_q);
+    tma_prefetch_desc(&tmap_k);
+    tma_prefetch_desc(&tmap_v);
+    tma_prefetch_desc(&tmap_o);
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(tmem_ptr_smem), 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_ptr_smem;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0 && n_tiles > 0) {
+      mbar_expect_tx(bar(Q_FULL), (uint32_t)p.slots * kTileBytes);
+      for (int s = 0; s < p.slots; ++s)
+        for (int h = 0; h < 2; ++h)
+          tma_load_3d(q_smem + s * kTileBytes + h * kHalfBytes, &tmap_q, bar(Q_FULL), h * 64, head0 + s, q0);
+      for (int i = 0; i < n_tiles; ++i) {
+        const int st = i & 1;
+        const uint32_t parity = ((i >> 1) & 1u) ^ 1u;
+        const int k0 = (j_lo + i) * kBN;
+        if (!mbar_wait(bar(K_EMPTY + st), parity, abort_flag)) break;
+        mbar_expect_tx(bar(K_FULL + st), kTileBytes);
+        for (int h = 0; h < 2; ++h)
+          tma_load_3d(k_smem + st * kTileBytes + h * kHalfBytes, &tmap_k, bar(K_FULL + st), h * 64, kv_head, k0);
+        if (!mbar_wait(bar(V_EMPTY + st), parity, abort_flag)) break;
+        mbar_expect_tx(bar(V_FULL + st), kTileBytes);
+        for (int h = 0; h < 2; ++h)
+          tma_load_3d(v_smem + st * kTileBytes + h * kHalfBytes, &tmap_v, bar(V_FULL + st), h * 64, kv_head, k0);
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0 && n_tiles > 0) {
+      const uint32_t idesc_s = make_idesc(false, false, kBM, kHN);   // Q, K both K-major; 64 keys per instruction
+      const uint32_t idesc_pv = make_idesc(false, true, kBM, kD);    // V is [keys, head dim]: MN-major B
+      auto issue_s = [&](int slot, int half, int st) {
+        if (p.debug & 2) return;
+        const uint32_t qa = q_smem + slot * kTileBytes;
+        const uint32_t ka = k_smem + st * kTileBytes + (uint32_t)half * (kHN * 128u);   // key rows [64 half, 64 half + 64)
+#pragma unroll
+        for (int k = 0; k < kD / 16; ++k) {
+          const uint32_t off = (uint32_t)(k >> 2) * kHalfBytes + (uint32_t)(k & 3) * 32u;
+          umma_bf16<1>(tmem_base + slot * 256 + half * kHN, make_desc(qa + off, 16, 1024), make_desc(ka + off, 16, 1024),
+                       idesc_s, k != 0 ? 1u : 0u);
+        }
+      };
+      auto issue_pv = [&](int slot, int half, int st, bool accumulate) {
+        if (p.debug & 2) return;
+        const uint32_t va = v_smem + st * kTileBytes + (uint32_t)half * (kHN / 16) * 2048u;
+#pragma unroll
+        for (int k = 0; k < kHN / 16; ++k)   // 16 keys per step: 8 packed columns of P, 16 rows (2048 B) of V
+          umma_bf16_ts(tmem_base + slot * 256 + 128, tmem_base + slot * 256 + half * kHN + k * 8,
+                       make_desc(va + k * 2048, kHalfBytes, 1024), idesc_pv, (accumulate || k != 0) ? 1u : 0u);
+      };
+      bool ok = mbar_wait(bar(Q_FULL), 0, abort_flag) && mbar_wait(bar(K_FULL), 0, abort_flag);
+      if (ok) {
+        tc_fence_after();
+        for (int h = 0; h < 2; ++h)
+          for (int s = 0; s < p.slots; ++s) {
+            issue_s(s, h, 0);
+            umma_commit(bar(S_FULL + s * 2 + h));
+          }
+        umma_commit(bar(K_EMPTY));
+      }
+      for (int w = 0; w < n_items && ok; ++w) {
+        const int i = w >> 1, h = w & 1, st = i & 1;
+        if (h == 0 && !mbar_wait(bar(V_FULL + st), (i >> 1) & 1u, abort_flag)) { ok = false; break; }
+        for (int s = 0; s < p.slots && ok; ++s) {
+          if (!mbar_wait(bar(P_READY + s * 2 + h), i & 1u, abort_flag)) { ok = false; break; }
+          tc_fence_after();
+          issue_pv(s, h, st, w > 0);
+          if (h == 1 && s == p.slots - 1) umma_commit(bar(V_EMPTY + st));
+          if (i + 1 < n_tiles) {
+            const int st1 = (i + 1) & 1;
+            if (s == 0 && h == 0 && !mbar_wait(bar(K_FULL + st1), ((i + 1) >> 1) & 1u, abort_flag)) { ok = false; break; }
+            tc_fence_after();
+            issue_s(s, h, st1);
+            umma_commit(bar(S_FULL + s * 2 + h));
+            if (h == 1 && s == p.slots - 1) umma_commit(bar(K_EMPTY + st1));
+          } else {
+            umma_commit(bar(S_FULL + s * 2 + h));   // no next S: the commit still tells a rescaling row that this P.V is done
+          }
+        }
+      }
+      if (ok) umma_commit(bar(O_FULL));
+    }
+  } else {
+    // ------------------------------------------------------------------ softmax + epilogue
+    const int slot = (warp - 2) >> 2;
+    const int quarter = warp & 3;
+    if (slot < p.slots) {
+      const int row_in_tile = quarter * 32 + lane;
+      const int row = q0 + row_in_tile;
+      const uint32_t s_t = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(slot * 256);
+      const uint32_t o_t = s_t + 128;
+      int lo = p.kv_first != nullptr ? p.kv_first[min(row, p.Tq - 1)] : 0;                // first visible key
+      const int hi = min(p.Tk - 1, p.causal ? row + p.causal_offset : p.Tk - 1);           // last visible key
+      if (p.window > 0) lo = max(lo, row + p.causal_offset - p.window + 1);
+      float m_used = -INFINITY, l = 0.f;
+      bool ok = true;
+      for (int w = 0; w < n_items; ++w) {
+        const int i = w >> 1, h = w & 1;
+        if (!mbar_wait(bar(S_FULL + slot * 2 + h), i & 1u, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+        if (p.debug & 1) { tc_fence_before(); __syncwarp(); if (lane == 0) mbar_arrive(bar(P_READY + slot * 2 + h)); continue; }
+        uint32_t r[2][32];
+        tmem_ld32(s_t + h * kHN, r[0]);
+        tmem_ld32(s_t + h * kHN + 32, r[1]);
+        tmem_ld_wait();
+        const int c0 = (j_lo + i) * kBN + h * kHN;
+        const bool edge = (c0 + kHN - 1 > hi) || (c0 < lo);
+        if (edge) {
+#pragma unroll
+          for (int c = 0; c < 2; ++c)
+#pragma unroll
+            for (int e = 0; e < 32; ++e) {
+              const int col = c0 + c * 32 + e;
+              if (col > hi || col < lo) r[c][e] = __float_as_uint(-INFINITY);
+            }
+        }
+        // row maximum of the raw scores: four independent chains of three-input maxima
+        float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+        for (int c = 0; c < 2; ++c)
+#pragma unroll
+          for (int e = 0; e < 32; e += 2)
+            mx[(e >> 1) & 3] = max3(mx[(e >> 1) & 3], __uint_as_float(r[c][e]), __uint_as_float(r[c][e + 1]));
+        const float m_tile = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * p.scale_log2;
+        const float m_new = fmaxf(m_used, m_tile);
+        if (__any_sync(0xffffffffu, m_new > m_used + kRescaleThreshold)) {
+          // every row of this warp moves to its own new maximum; O and l are rescaled once all P.V MMAs issued
+          // so far for this slot have completed (see the header comment)
+          if (w > 0) {
+            if (!mbar_wait(bar(S_FULL + slot * 2 + (1 - h)), ((w + 1) >> 1) & 1u, abort_flag)) { ok = false; break; }
+            tc_fence_after();
+          }
+          const float alpha = (m_used == -INFINITY) ? 0.f : ex2_mufu(m_used - m_new);
+          l *= alpha;
+          if (w > 0) {
+#pragma unroll 1
+            for (int c = 0; c < 4; ++c) {
+              uint32_t o[32];
+              tmem_ld32(o_t + c * 32, o);
+              tmem_ld_wait();
+#pragma unroll
+              for (int e = 0; e < 32; ++e) o[e] = __float_as_uint(__uint_as_float(o[e]) * alpha);
+              tmem_st32(o_t + c * 32, o);
+            }
+          }
+          m_used = m_new;
+        }
+        // P = exp2(S scale - m)
+        const float neg_m = (m_used == -INFINITY) ? 0.f : -m_used;
+        float lsum;
+        if constexpr (kPacked) {
+          const uint64_t sc2 = pack2(p.scale_log2, p.scale_log2), nm2 = pack2(neg_m, neg_m);
+          uint64_t ls2[2] = {pack2(0.f, 0.f), pack2(0.f, 0.f)};
+#pragma unroll
+          for (int c = 0; c < 2; ++c) {
+            uint32_t pk[16];
+#pragma unroll
+            for (int e = 0; e < 16; ++e) {
+              float x0, x1;
+              unpack2(fma2(pack2(__uint_as_float(r[c][2 * e]), __uint_as_float(r[c][2 * e + 1])), sc2, nm2), x0, x1);
+              float p0, p1;
+              if (!edge && (e & 3) < kEmu / 2) {
+                p0 = ex2_poly(x0);
+                p1 = ex2_poly(x1);
+              } else {
+                p0 = ex2_mufu(x0);
+                p1 = ex2_mufu(x1);
+              }
+              ls2[e & 1] = add2(ls2[e & 1], pack2(p0, p1));
+              pk[e] = pack_bf16(p0, p1);
+            }
+            tmem_st16(s_t + h * kHN + c * 16, pk);
+          }
+          float a0, a1, b0, b1;
+          unpack2(ls2[0], a0, a1);
+          unpack2(ls2[1], b0, b1);
+          lsum = (a0 + a1) + (b0 + b1);
+        } else {
+          float ls[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+          for (int c = 0; c < 2; ++c) {
+            uint32_t pk[16];
+#pragma unroll
+            for (int e = 0; e < 16; ++e) {
+              const float x0 = fmaf(__uint_as_float(r[c][2 * e]), p.scale_log2, neg_m);
+              const float x1 = fmaf(__uint_as_float(r[c][2 * e + 1]), p.scale_log2, neg_m);
+              float p0, p1;
+              if (!edge && (e & 3) < kEmu / 2) {
+                p0 = ex2_poly(x0);
+                p1 = ex2_poly(x1);
+              } else {
+                p0 = ex2_mufu(x0);
+                p1 = ex2_mufu(x1);
+              }
+              ls[e & 3] += p0 + p1;
+              pk[e] = pack_bf16(p0, p1);
+            }
+            tmem_st16(s_t + h * kHN + c * 16, pk);
+          }
+          lsum = (ls[0] + ls[1]) + (ls[2] + ls[3]);
+        }
+        l += lsum;
+        tmem_st_wait();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(P_READY + slot * 2 + h));
+      }
+      // ---- epilogue: O / l -> bf16 -> swizzled staging tile (the slot's Q buffer) -> TMA store
+      if (ok && n_tiles > 0) ok = mbar_wait(bar(O_FULL), 0, abort_flag);
+      if (ok) {
+        tc_fence_after();
+        // an attention sink adds exp(sink) to the denominator and nothing to the numerator
+        float l_tot = l;
+        const float sink2 = p.sinks != nullptr ? p.sinks[head0 + slot] * 1.4426950408889634f : -INFINITY;
+        float m_fin = m_used;
+        if (p.sinks != nullptr) {
+          if (m_used == -INFINITY) { m_fin = sink2; l_tot = 1.f; }
+          else l_tot = l + ex2_mufu(sink2 - m_used);
+        }
+        const float inv = (l > 0.f) ? 1.f / l_tot : 0.f;
+        const uint32_t stage = q_smem + slot * kTileBytes;
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+          uint32_t o[32];
+          if (n_tiles > 0) {
+            tmem_ld32(o_t + c * 32, o);
+            tmem_ld_wait();
+          } else {
+#pragma unroll
+            for (int e = 0; e < 32; ++e) o[e] = 0u;
+          }
+#pragma unroll
+          for (int jj = 0; jj < 4; ++jj) {
+            uint32_t wv[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e)
+              wv[e] = pack_bf16(__uint_as_float(o[jj * 8 + 2 * e]) * inv, __uint_as_float(o[jj * 8 + 2 * e + 1]) * inv);
+            const int chunk = (c & 1) * 4 + jj;
+            const uint32_t dst = stage + (uint32_t)(c >> 1) * kHalfBytes + (uint32_t)row_in_tile * 128u +
+                                 (uint32_t)((chunk ^ (row_in_tile & 7)) << 4);
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(wv[0]), "r"(wv[1]), "r"(wv[2]), "r"(wv[3])
+                         : "memory");
+          }
+        }
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(O_STAGED + slot));                               // the four warps of this slot
+        if (quarter == 0 && lane == 0 && mbar_wait(bar(O_STAGED + slot), 0, abort_flag)) {
+          for (int h = 0; h < 2; ++h) tma_store_3d(&tmap_o, stage + h * kHalfBytes, h * 64, head0 + slot, q0);
+          tma_store_commit();
+          tma_store_wait<0>();
+        }
+        if (row < p.Tq)
+          p.lse[(int64_t)(head0 + slot) * p.lse_stride + row] =
+              l_tot > 0.f ? (m_fin + log2f(l_tot)) * 0.6931471805599453f : -INFINITY;
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+  if (threadIdx.x == 0 && *abort_flag && p.status != nullptr) atomicOr(p.status, kStatusWaitTimedOut);
+}
+
+
 // =========================================================================================
 // Backward, in two kernels that share no memory traffic besides their inputs, so that nothing
 // is accumulated through global memory (an earlier single kernel that reduced dQ partials with
@@ -379,6 +777,7 @@ struct BwdParams {
   int debug;               // timing diagnostics: bit 0 skips the warps' math, bit 1 skips the MMAs (results are garbage)
   int stat_stride;         // a multiple of 64 floats, so that 64-row slices can be fetched with bulk copies
   int* status;
+  int window;              // > 0: query row i sees only keys j > i + causal_offset - window
 };
 
 __global__ void __launch_bounds__(kThreadsBwd, 1)
@@ -431,6 +830,8 @@ flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
     // query rows that can see this key block: [q_lo, q_hi)
     int q_lo = 0, q_hi = p.Tq;
     if (p.causal) q_lo = max(0, k0 - p.causal_offset);
+    // sliding window: the last key of this block is visible up to query row last_key - offset + window - 1
+    if (p.window > 0) q_hi = max(0, min(q_hi, min(k0 + kBN, p.Tk) - p.causal_offset + p.window - 1));
     if (p.kv_first != nullptr) {
       // kv_first is non-decreasing: rows from the first one whose first key lies beyond this block see nothing
       int a = 0, b = p.Tq;
@@ -439,7 +840,7 @@ flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
         const int mid = (a + b) >> 1;
         if (p.kv_first[mid] <= last_key) a = mid + 1; else b = mid;
       }
-      q_hi = a;
+      q_hi = min(q_hi, a);
     }
     q_lo = (q_lo / kBQ) * kBQ;
     q_range[0] = q_lo;
@@ -552,7 +953,8 @@ flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
       if (!mbar_wait(bar(R_FULL + t % kRing), (t / kRing) & 1u, abort_flag)) { ok = false; break; }
       const uint32_t stat = stat_smem + (uint32_t)(t % kRing) * 512u + (uint32_t)grp * 64u;
       const bool edge = p.kv_first != nullptr || qc0 + 16 > p.Tq || k0 + kBN > p.Tk ||
-                        (p.causal && qc0 + p.causal_offset < k0 + kBN - 1);
+                        (p.causal && qc0 + p.causal_offset < k0 + kBN - 1) ||
+                        (p.window > 0 && qc0 + 15 + p.causal_offset - p.window + 1 > k0);
       uint32_t pk[8], dk[8];
 #pragma unroll
       for (int g = 0; g < 4; ++g) {
@@ -570,6 +972,7 @@ flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
             const int qi = qc0 + i;
             bool vis = qi < p.Tq && kv_idx < p.Tk;
             if (p.causal) vis = vis && kv_idx <= qi + p.causal_offset;
+            if (p.window > 0) vis = vis && kv_idx > qi + p.causal_offset - p.window;
             if (p.kv_first != nullptr) vis = vis && kv_idx >= p.kv_first[min(qi, p.Tq - 1)];
             if (!vis) pe = 0.f;
           }
@@ -681,8 +1084,10 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
   const int num_k_tiles = (p.Tk + kBN - 1) / kBN;
   int j_hi = num_k_tiles - 1;
   if (p.causal) j_hi = min(j_hi, (min(q0 + kBM - 1, p.Tq - 1) + p.causal_offset) / kBN);
-  int j_lo = 0;
-  if (p.kv_first != nullptr) j_lo = max(0, p.kv_first[q0]) / kBN;
+  int first_key = 0;
+  if (p.kv_first != nullptr) first_key = max(0, p.kv_first[q0]);
+  if (p.window > 0) first_key = max(first_key, q0 + p.causal_offset - p.window + 1);
+  const int j_lo = first_key / kBN;
   const int n_tiles = j_hi - j_lo + 1;
 
   if (threadIdx.x == 0) {
@@ -802,7 +1207,8 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
     const bool row_ok = row < p.Tq;
     const float l2 = row_ok ? p.lse[(int64_t)head * p.stat_stride + row] * 1.4426950408889634f : INFINITY;
     const float dl = (row_ok ? p.delta[(int64_t)head * p.stat_stride + row] : 0.f) * p.scale;
-    const int lo = p.kv_first != nullptr ? p.kv_first[min(row, p.Tq - 1)] : 0;
+    int lo = p.kv_first != nullptr ? p.kv_first[min(row, p.Tq - 1)] : 0;
+    if (p.window > 0) lo = max(lo, row + p.causal_offset - p.window + 1);
     const int hi = min(p.Tk - 1, p.causal ? row + p.causal_offset : p.Tk - 1);
     bool ok = true;
     for (int i = 0; i < n_tiles; ++i) {
@@ -939,11 +1345,29 @@ static at::Tensor& flash_status_tensor(const at::Device& dev) {
   return t;
 }
 
+// Forward kernel selection: 0 = one 128-key tile per step (flash_fwd_kernel); 1..4 = the half-tile
+// pipelined kernel with <kEmu, kPacked> = <0,false>, <0,true>, <2,true>, <4,true>.
+static int g_flash_fwd_variant = -1;
+void flash_set_fwd_variant(int64_t v) {
+  TORCH_CHECK(v >= 0 && v <= 4, "flash_set_fwd_variant: 0..4");
+  g_flash_fwd_variant = (int)v;
+}
+static int flash_fwd_variant() {
+  if (g_flash_fwd_variant < 0) {
+    const char* e = std::getenv("TB200_FLASH_FWD");
+    g_flash_fwd_variant = (e != nullptr && e[0] >= '0' && e[0] <= '4' && e[1] == 0) ? e[0] - '0' : 3;
+  }
+  return g_flash_fwd_variant;
+}
+
 // q [Tq, Hq, 128], k / v [Tk, Hkv, 128] (bf16, last dimension contiguous) -> (o [Tq, Hq, 128], lse [Hq, Tq]).
-// Query row i attends to keys kv_first[i] <= j <= i + causal_offset (causal) or all keys >= kv_first[i].
+// Query row i attends to keys max(kv_first[i], i + causal_offset - window + 1) <= j <= i + causal_offset
+// (causal; window 0 = unlimited) or to all keys >= kv_first[i].  `sinks` [Hq] fp32: one extra logit per head
+// that joins the softmax denominator only (its share of the probability mass is dropped); lse includes it.
 std::tuple<at::Tensor, at::Tensor> flash_fwd(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v, double scale,
                                              bool causal, int64_t causal_offset,
-                                             const c10::optional<at::Tensor>& kv_first) {
+                                             const c10::optional<at::Tensor>& kv_first, int64_t window,
+                                             const c10::optional<at::Tensor>& sinks) {
   using namespace flash;
   TORCH_CHECK(q.is_cuda() && k.is_cuda() && v.is_cuda());
   TORCH_CHECK(q.scalar_type() == at::kBFloat16 && k.scalar_type() == at::kBFloat16 && v.scalar_type() == at::kBFloat16);
@@ -977,30 +1401,58 @@ std::tuple<at::Tensor, at::Tensor> flash_fwd(const at::Tensor& q, const at::Tens
   p.lse_stride = (int)Tpad;
   p.debug = g_flash_debug;
   p.status = flash_status_tensor(q.device()).data_ptr<int>();
+  p.window = 0;
+  p.sinks = nullptr;
+  TORCH_CHECK(window >= 0, "flash_fwd: window must be >= 0");
+  int variant = flash_fwd_variant();
+  if (window > 0) {
+    TORCH_CHECK(causal, "flash_fwd: a sliding window needs causal attention");
+    p.window = (int)window;
+  }
+  if (sinks.has_value() && sinks->defined()) {
+    TORCH_CHECK(sinks->is_cuda() && sinks->scalar_type() == at::kFloat && sinks->numel() == Hq && sinks->is_contiguous(),
+                "flash_fwd: sinks must be a float32 [Hq] CUDA tensor");
+    p.sinks = sinks->data_ptr<float>();
+  }
+  if ((p.window > 0 || p.sinks != nullptr) && variant == 0) variant = 3;   // only the pipelined kernel has them
   const CUtensorMap tq = make_tmap_thd(q, kBM), tk = make_tmap_thd(k, kBN), tv = make_tmap_thd(v, kBN),
                     to = make_tmap_thd(o, kBM);
   constexpr uint32_t smem = 6 * kTileBytes + 1024 + 256;
   static bool attr_set = false;
   if (!attr_set) {
     C10_CUDA_CHECK(cudaFuncSetAttribute(flash_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    C10_CUDA_CHECK(cudaFuncSetAttribute(flash_fwd_pipe_kernel<0, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    C10_CUDA_CHECK(cudaFuncSetAttribute(flash_fwd_pipe_kernel<0, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    C10_CUDA_CHECK(cudaFuncSetAttribute(flash_fwd_pipe_kernel<2, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    C10_CUDA_CHECK(cudaFuncSetAttribute(flash_fwd_pipe_kernel<4, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     attr_set = true;
   }
   const int num_q_tiles = (int)((Tq + kBM - 1) / kBM);
   const int grid = num_q_tiles * (int)Hkv * p.ctas_per_kv_head;
-  flash_fwd_kernel<<<grid, kThreadsFwd, smem, at::cuda::getCurrentCUDAStream()>>>(tq, tk, tv, to, p);
+  auto stream = at::cuda::getCurrentCUDAStream();
+  switch (variant) {
+    case 0: flash_fwd_kernel<<<grid, kThreadsFwd, smem, stream>>>(tq, tk, tv, to, p); break;
+    case 1: flash_fwd_pipe_kernel<0, false><<<grid, kThreadsFwd, smem, stream>>>(tq, tk, tv, to, p); break;
+    case 2: flash_fwd_pipe_kernel<0, true><<<grid, kThreadsFwd, smem, stream>>>(tq, tk, tv, to, p); break;
+    case 4: flash_fwd_pipe_kernel<4, true><<<grid, kThreadsFwd, smem, stream>>>(tq, tk, tv, to, p); break;
+    default: flash_fwd_pipe_kernel<2, true><<<grid, kThreadsFwd, smem, stream>>>(tq, tk, tv, to, p); break;
+  }
   C10_CUDA_KERNEL_LAUNCH_CHECK();
   return {o, lse};
 }
 
 // (dO [Tq, Hq, 128] contiguous, q, k, v, o, lse from the forward) -> (dq, dk, dv).  The three
 // outputs may be given as views (last dimension contiguous), e.g. slices of one packed gradient.
+// With attention sinks nothing changes here: lse from the forward already contains the sink, so
+// exp(s - lse) are the probabilities of the real keys; the caller derives the sink's own gradient
+// from lse and delta.
 std::tuple<at::Tensor, at::Tensor, at::Tensor> flash_bwd(const at::Tensor& d_o, const at::Tensor& q, const at::Tensor& k,
                                                          const at::Tensor& v, const at::Tensor& o, const at::Tensor& lse,
                                                          double scale, bool causal, int64_t causal_offset,
                                                          const c10::optional<at::Tensor>& kv_first,
                                                          const c10::optional<at::Tensor>& dq_out,
                                                          const c10::optional<at::Tensor>& dk_out,
-                                                         const c10::optional<at::Tensor>& dv_out) {
+                                                         const c10::optional<at::Tensor>& dv_out, int64_t window) {
   using namespace flash;
   TORCH_CHECK(d_o.is_cuda() && q.is_cuda() && k.is_cuda() && v.is_cuda() && o.is_cuda() && lse.is_cuda());
   TORCH_CHECK(d_o.scalar_type() == at::kBFloat16 && q.scalar_type() == at::kBFloat16 && k.scalar_type() == at::kBFloat16 &&
@@ -1052,6 +1504,8 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor> flash_bwd(const at::Tensor& d_o, 
   p.stat_stride = (int)Tpad;
   p.debug = g_flash_debug;
   p.status = flash_status_tensor(q.device()).data_ptr<int>();
+  TORCH_CHECK(window >= 0 && (window == 0 || causal), "flash_bwd: a sliding window needs causal attention");
+  p.window = (int)window;
   {
     const CUtensorMap tq = make_tmap_thd(q, kBQ), tdo = make_tmap_thd(d_o, kBQ), tk = make_tmap_thd(k, kBN),
                       tv = make_tmap_thd(v, kBN), tdk = make_tmap_thd(dk, kBN), tdv = make_tmap_thd(dv, kBN);

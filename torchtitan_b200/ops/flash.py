@@ -5,9 +5,12 @@ contiguous last dimension are fine, e.g. slices of a packed QKV projection) and 
 ``o[Tq,Hq,128]``; ``flash_attention_lse`` also returns the log-sum-exp ``[Hq,Tq]`` so that
 partial results over different key ranges can be merged (context parallelism).
 
-Masks: causal with an offset (row ``i`` sees keys ``j <= i + causal_offset``) and an optional
+Masks: causal with an offset (row ``i`` sees keys ``j <= i + causal_offset``), an optional
 ``kv_first[Tq]`` (int32, non-decreasing): the first key each query may see, which is how
-packed documents are separated.  The library counterpart in the reference is flex / varlen
+packed documents are separated, and an optional sliding ``window`` (row ``i`` sees the last
+``window`` keys up to ``i + causal_offset``).  ``sinks[Hq]`` adds one learned logit per head to the
+softmax denominator (GPT-OSS attention sinks, torchtitan/models/gpt_oss/model.py:34-47); its
+gradient is ``-sum_i exp(sink - lse_i) * delta_i``.  The library counterpart in the reference is flex / varlen
 attention (torchtitan/models/common/attention.py:109-362).
 """
 
@@ -31,20 +34,24 @@ def supported(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor) -> bool:
 
 class _FlashFn(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, q, k, v, scale, causal, causal_offset, kv_first, packed_grad):
+    def forward(ctx, q, k, v, scale, causal, causal_offset, kv_first, packed_grad, window=0, sinks=None):
         ops = ext.require()
-        o, lse = ops.flash_fwd(q, k, v, scale, causal, causal_offset, kv_first)
-        ctx.save_for_backward(q, k, v, o, lse, kv_first if kv_first is not None else torch.empty(0))
+        sinks_f = sinks.detach().float().contiguous() if sinks is not None else None
+        o, lse = ops.flash_fwd(q, k, v, scale, causal, causal_offset, kv_first, window, sinks_f)
+        ctx.save_for_backward(q, k, v, o, lse, kv_first if kv_first is not None else torch.empty(0),
+                              sinks_f if sinks_f is not None else torch.empty(0))
         ctx.has_first = kv_first is not None
-        ctx.args = (scale, causal, causal_offset)
+        ctx.has_sinks = sinks is not None
+        ctx.sink_dtype = sinks.dtype if sinks is not None else None
+        ctx.args = (scale, causal, causal_offset, window)
         ctx.packed_grad = packed_grad
         ctx.mark_non_differentiable(lse)
         return o, lse
 
     @staticmethod
     def backward(ctx, d_o, _d_lse):
-        q, k, v, o, lse, kv_first = ctx.saved_tensors
-        scale, causal, causal_offset = ctx.args
+        q, k, v, o, lse, kv_first, sinks_f = ctx.saved_tensors
+        scale, causal, causal_offset, window = ctx.args
         ops = ext.require()
         if not d_o.is_contiguous():
             d_o = d_o.contiguous()
@@ -56,8 +63,12 @@ class _FlashFn(torch.autograd.Function):
             packed = torch.empty(T, hq + 2 * hkv, q.shape[2], dtype=q.dtype, device=q.device)
             dq, dk, dv = packed[:, :hq], packed[:, hq:hq + hkv], packed[:, hq + hkv:]
         dq, dk, dv = ops.flash_bwd(d_o, q, k, v, o, lse, scale, causal, causal_offset,
-                                   kv_first if ctx.has_first else None, dq, dk, dv)
-        return dq, dk, dv, None, None, None, None, None
+                                   kv_first if ctx.has_first else None, dq, dk, dv, window)
+        d_sinks = None
+        if ctx.has_sinks and ctx.needs_input_grad[9]:
+            delta = (d_o.float() * o.float()).sum(-1)                                   # [Tq, Hq]
+            d_sinks = -(torch.exp(sinks_f[None, :] - lse.t()) * delta).sum(0).to(ctx.sink_dtype)
+        return dq, dk, dv, None, None, None, None, None, None, d_sinks
 
 
 def _same_packed_storage(q, k, v) -> bool:
@@ -74,10 +85,14 @@ def _same_packed_storage(q, k, v) -> bool:
 
 
 def flash_attention_lse(q, k, v, scale: float, *, causal: bool = True, causal_offset: int = 0,
-                        kv_first: torch.Tensor | None = None):
-    return _FlashFn.apply(q, k, v, float(scale), bool(causal), int(causal_offset), kv_first, True)
+                        kv_first: torch.Tensor | None = None, window: int | None = None,
+                        sinks: torch.Tensor | None = None):
+    return _FlashFn.apply(q, k, v, float(scale), bool(causal), int(causal_offset), kv_first, True,
+                          int(window or 0), sinks)
 
 
 def flash_attention(q, k, v, scale: float, *, causal: bool = True, causal_offset: int = 0,
-                    kv_first: torch.Tensor | None = None) -> torch.Tensor:
-    return flash_attention_lse(q, k, v, scale, causal=causal, causal_offset=causal_offset, kv_first=kv_first)[0]
+                    kv_first: torch.Tensor | None = None, window: int | None = None,
+                    sinks: torch.Tensor | None = None) -> torch.Tensor:
+    return flash_attention_lse(q, k, v, scale, causal=causal, causal_offset=causal_offset, kv_first=kv_first,
+                               window=window, sinks=sinks)[0]

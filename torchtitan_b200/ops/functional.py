@@ -449,11 +449,14 @@ def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, scale: float
     if scale is None:
         scale = 1.0 / math.sqrt(q.shape[-1])
     simple = window is None and sinks is None and q_pos is None and k_pos is None and causal
-    if simple and (doc_ids is None or kv_first is not None) and _native_attention_ok(q, k, v):
+    if (causal and q_pos is None and k_pos is None and (doc_ids is None or kv_first is not None)
+            and _native_attention_ok(q, k, v)):
         from .flash import flash_attention
 
         _count(4)  # forward + (delta, backward, dq cast)
-        return flash_attention(q, k, v, scale, causal=True, kv_first=kv_first)
+        return flash_attention(q, k, v, scale, causal=True, kv_first=kv_first, window=window, sinks=sinks)
+    if _cuda(q):
+        settings.library_fallbacks += 1
     if simple and doc_ids is None and q.shape[-1] == v.shape[-1]:
         return _sdpa_causal(q, k, v, scale)
     return _masked_attention(q, k, v, scale, causal, doc_ids, window, sinks, q_pos, k_pos)

@@ -93,7 +93,11 @@ def bench_attention(args) -> None:
                 ops.flash_bwd(do, q, k, v, o, lse, scale, True, 0, None, None, None, None)
             torch.cuda.synchronize()
             continue
-        tf = timer(lambda: ops.flash_fwd(q, k, v, scale, True, 0, None))
+        for variant in (0, 1, 2, 4, 3):   # every forward kernel; the last one (the default) stays selected
+            ops.flash_set_fwd_variant(variant)
+            tf = timer(lambda: ops.flash_fwd(q, k, v, scale, True, 0, None))
+            print(f"attention tcgen05 T{Tn} H{H}/{Hkv} D{D} forward kernel {variant}: {tf:.3f} ms {fl_f / tf / 1e9:.0f} TFLOPS",
+                  flush=True)
         line = f"attention tcgen05 T{Tn} H{H}/{Hkv} D{D}: fwd {tf:.3f} ms {fl_f / tf / 1e9:.0f} TFLOPS"
         if has_bwd:
             o, lse = ops.flash_fwd(q, k, v, scale, True, 0, None)
