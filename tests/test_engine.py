@@ -198,3 +198,35 @@ def test_activation_offload_hooks_preserve_gradients():
     assert stats.tensors >= 2 and stats.bytes >= 128 * 256 * 4        # the hidden activations went through the hooks
     for a, b in zip(ref_grads, got):
         assert torch.equal(a, b)
+
+
+def _reshard_fn(rank, world, policy, accum, out_path):
+    import torch.distributed as dist
+
+    cfg = _job(accum_tokens=accum * T * world, fsdp_reshard_after_forward=policy)
+    pdims = ParallelDims(world_size=world, rank=rank).build()
+    b = _batches(4 * accum * world, seed=3)
+    data = [[b[(s * accum + a) * world + rank] for a in range(accum)] for s in range(4)]
+    losses, model, eng = _engine_steps(cfg, pdims, data, accum=accum, steps=4)
+    assert eng.sharded_params == (policy == "always")
+    if policy == "always":
+        # a rank holds its shards plus two gather slots and two gradient slots, never every unit in full
+        assert all(u.param_shard is not None and u.param_shard.numel() == u.shard_numel for u in eng.units)
+        assert len(eng._pools) == 1
+    t = torch.tensor(losses)
+    dist.all_reduce(t)
+    masters = torch.cat([u.master for u in eng.units])
+    if rank == 0:
+        torch.save({"losses": t, "master": masters}, out_path)
+
+
+@pytest.mark.parametrize("accum", [1, 2])
+def test_sharded_parameter_layout_matches_resident(tmp_path, accum):
+    """fsdp_reshard_after_forward = always (parameters gathered per unit, freed after use) trains exactly like
+    the resident layout: same reductions, same optimizer, only the place of the all-gather differs."""
+    a, b = str(tmp_path / "never.pt"), str(tmp_path / "always.pt")
+    run_distributed(_reshard_fn, 2, "never", accum, a)
+    run_distributed(_reshard_fn, 2, "always", accum, b)
+    ra, rb = torch.load(a), torch.load(b)
+    assert torch.equal(ra["losses"], rb["losses"]), (ra["losses"], rb["losses"])
+    assert torch.equal(ra["master"], rb["master"])

@@ -31,7 +31,7 @@ def test_bounded_wait_reports_timeout_without_trapping():
     assert float(torch.ones(4, device="cuda").sum()) == 4.0
 
 
-def _train(rank, world, comm, out_path):
+def _train(rank, world, comm, out_path, reshard="never"):
     import torch.distributed as dist
 
     from tests.test_engine import T, _batches, _small_model_cfg
@@ -46,6 +46,7 @@ def _train(rank, world, comm, out_path):
     cfg.training.num_tokens_per_microbatch_per_dp_rank = T
     cfg.training.max_context_length = T
     cfg.parallelism.fsdp_comm = comm
+    cfg.parallelism.fsdp_reshard_after_forward = reshard
     pdims = ParallelDims(world_size=world, rank=rank).build()
     mc = _small_model_cfg(3)
     with torch.device("meta"):
@@ -68,7 +69,8 @@ def _train(rank, world, comm, out_path):
     eng.check_status()
     t = torch.stack(losses)
     dist.all_reduce(t)
-    full = torch.cat([u.flat_param[:u.numel].float() for u in eng.units])
+    assert eng.sharded_params == (reshard == "always")
+    full = torch.cat([u.master for u in eng.units])    # this rank's fp32 shards
     if rank == 0:
         torch.save({"losses": t.cpu(), "params": full.cpu()}, out_path)
 
@@ -84,6 +86,20 @@ def test_nvlink_engine_matches_nccl(tmp_path):
     # up to one learning rate per step for single elements: bound the maximum loosely, the mean tightly
     d = (ra["params"] - rb["params"]).abs()
     assert float(d.max()) <= 0.1 and float(d.mean()) <= 1e-3, (float(d.max()), float(d.mean()))
+
+
+@pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
+@pytest.mark.parametrize("comm", ["nccl", "nvlink"])
+def test_sharded_parameters_match_resident(tmp_path, comm):
+    """fsdp_reshard_after_forward = always (per-unit gathers into rotating slots, prefetch on the communication
+    stream) against the resident layout, over NCCL and over the peer-load kernels."""
+    a, b = str(tmp_path / "never.pt"), str(tmp_path / "always.pt")
+    run_distributed(_train, 2, comm, a, "never", backend="nccl")
+    run_distributed(_train, 2, comm, b, "always", backend="nccl")
+    ra, rb = torch.load(a), torch.load(b)
+    assert torch.allclose(ra["losses"], rb["losses"], atol=1e-3), (ra["losses"], rb["losses"])
+    d = (ra["params"] - rb["params"]).abs()
+    assert float(d.max()) <= 2e-2 and float(d.mean()) <= 1e-4, (float(d.max()), float(d.mean()))
 
 
 def _rs_ag(rank, world, out_path):

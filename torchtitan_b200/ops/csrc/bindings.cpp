@@ -104,8 +104,8 @@ TORCH_LIBRARY(tb200, m) {
         "int window=0, Tensor? sinks=None) -> (Tensor, Tensor)", &tb200::flash_fwd);
   m.def("flash_set_fwd_variant(int v) -> ()", &tb200::flash_set_fwd_variant);
   m.def("flash_bwd(Tensor d_o, Tensor q, Tensor k, Tensor v, Tensor o, Tensor lse, float scale, bool causal, "
-        "int causal_offset, Tensor? kv_first, Tensor(a!)? dq_out, Tensor(b!)? dk_out, Tensor(c!)? dv_out) -> "
-        "(Tensor, Tensor, Tensor)", &tb200::flash_bwd);
+        "int causal_offset, Tensor? kv_first, Tensor(a!)? dq_out, Tensor(b!)? dk_out, Tensor(c!)? dv_out, "
+        "int window=0) -> (Tensor, Tensor, Tensor)", &tb200::flash_bwd);
   m.def("flash_status(bool clear) -> int", &tb200::flash_status);
   m.def("flash_set_debug(int v) -> ()", &tb200::flash_set_debug);
   m.def("ep_scatter_rows(Tensor x, Tensor dest_rank, Tensor dest_row, Tensor? wts, int[] peer_ptrs) -> ()", &tb200::ep_scatter_rows);

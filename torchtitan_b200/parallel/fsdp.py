@@ -5,10 +5,22 @@ final norm + lm_head -- the same unit structure the reference gives FSDP2,
 torchtitan/distributed/fsdp.py:168-381).  Per unit there are
 
 * ``flat_param``  full-size buffer in the compute dtype (bf16); module parameters
-  are views into it.  With 180 GB of HBM the bf16 weights of every target model
-  stay resident, so there is no all-gather on the forward critical path: the
-  gathered weights are refreshed once per optimizer step.  (``reshard`` mode for
-  models that do not fit re-gathers units on demand.)
+  are views into it.  Two layouts, chosen by ``parallelism.fsdp_reshard_after_forward``
+  (reference: torchtitan/distributed/fsdp.py:112-166):
+
+  - *resident* (``never``; also ``default`` while the replicated bf16 weights and
+    gradients take less than a third of the device memory): every unit keeps its own
+    full-size ``flat_param`` and ``flat_grad``.  With 180 GB of HBM the weights of the
+    8B - 70B models stay resident, so there is no all-gather on the forward critical
+    path: the gathered weights are refreshed once per optimizer step.
+  - *sharded* (``always``, and ``default`` for models that do not fit): a rank keeps
+    only its 1/N ``param_shard`` of every unit between uses (ZeRO-3 / FSDP2).  The
+    full-size buffers come from two rotating slots per sharding group, sized for the
+    largest unit; unit k+1 is gathered into the other slot on the communication stream
+    while unit k computes (forward order in forward, reverse order in backward), and
+    gradients are reduce-scattered out of two rotating gradient slots.  Parameter
+    shards change only in the optimizer, so the gathers need no cross-rank barrier
+    besides the one that ends the optimizer step.
 * ``flat_grad``   full-size local gradient buffer (compute dtype).  The linear
   backward writes weight gradients straight into it (``main_grad`` views).
 * ``master`` / ``exp_avg`` / ``exp_avg_sq`` / ``grad_shard``: this rank's 1/N slice
@@ -93,6 +105,11 @@ class FlatUnit:
         self.pending = False  # gradients written, reduction not yet launched
         self.grad_shard_valid = False
         self.sumsq: torch.Tensor | None = None  # [2]: (tp-replicated part, rest)
+        # sharded-parameter layout only
+        self.param_shard: torch.Tensor | None = None   # this rank's 1/N of the parameters, compute dtype
+        self.pool: "_SlotPool | None" = None
+        self.slot = 0
+        self.gather_dst: torch.Tensor | None = None    # alias of flat_param with its own version counter
 
     # shard geometry -----------------------------------------------------
     @property
@@ -119,8 +136,16 @@ class ShardedModel:
     def __init__(self, model: nn.Module, units: list[UnitSpec], *, pdims, device: torch.device,
                  param_dtype: torch.dtype = torch.bfloat16, master_dtype: torch.dtype = torch.float32,
                  state_dtype: torch.dtype = torch.float32, seed: int = 0, comm: str = "nccl",
-                 grad_accum_steps: int = 1, fqn_prefix: str = "", tp=None, offload_optimizer: bool = False):
+                 grad_accum_steps: int = 1, fqn_prefix: str = "", tp=None, offload_optimizer: bool = False,
+                 reshard_after_forward: str = "never"):
         self.model = model
+        if reshard_after_forward not in ("default", "always", "never"):
+            raise ValueError("fsdp_reshard_after_forward must be 'default', 'always' or 'never'")
+        self.reshard_policy = reshard_after_forward
+        self.sharded_params = False     # decided in materialize()
+        self._pools: dict[int, _SlotPool] = {}
+        self._order: list[FlatUnit] = []   # units with sharded parameters, in execution order
+        self._in_backward = False
         # optimizer state (fp32 master weights and both moments) lives in pinned host memory and is
         # streamed through the GPU one unit at a time during the optimizer step
         self.offload_optimizer = bool(offload_optimizer) and device.type == "cuda"
@@ -202,15 +227,62 @@ class ShardedModel:
         if missing:
             raise ValueError(f"parameters not assigned to any sharding unit: {missing[:5]} ...")
 
+    def _decide_layout(self, pd: torch.dtype) -> bool:
+        """True when parameters are kept sharded between uses (see the module docstring)."""
+        multi = [u for u in self.units if u.size > 1]
+        if not multi or self.reshard_policy == "never":
+            return False
+        if self.reshard_policy == "always":
+            return True
+        if self.device.type != "cuda":
+            return False
+        es = torch.empty(0, dtype=pd).element_size()
+        replicated = sum(2 * u.padded * es for u in multi)
+        return replicated > torch.cuda.get_device_properties(self.device).total_memory // 3
+
     def materialize(self, init: bool = True) -> None:
         """Allocate buffers, point module parameters at them, initialise the fp32 master shards."""
         dev, pd = self.device, self.param_dtype
+        self.sharded_params = self._decide_layout(pd)
         use_symm = self.comm in ("nvlink", "auto") and dev.type == "cuda" and any(u.size > 1 for u in self.units)
         if use_symm:
             use_symm = self._setup_symmetric(pd)
+        if self.sharded_params:
+            # two parameter slots and two gradient slots per sharding group, each as large as the group's largest unit
+            biggest: dict[int, int] = {}
+            for u in self.units:
+                if u.size > 1:
+                    biggest[id(u.group)] = max(biggest.get(id(u.group), 0), u.padded)
+            seen: dict[int, int] = {}
+            for u in self.units:
+                if u.size == 1:
+                    continue
+                key = id(u.group)
+                if key not in self._pools:
+                    n = biggest[key]
+                    if use_symm:
+                        grads = [self._symm.alloc(n, pd, u.group, tag=f"grad_slot{i}") for i in range(2)]
+                    else:
+                        grads = [torch.zeros(n, dtype=pd, device=dev) for _ in range(2)]
+                    for g in grads:
+                        g.zero_()
+                    self._pools[key] = _SlotPool([torch.zeros(n, dtype=pd, device=dev) for _ in range(2)], grads)
+                u.pool = self._pools[key]
+                u.slot = seen.get(key, 0) % 2
+                seen[key] = seen.get(key, 0) + 1
+                self._order.append(u)
         replaced: dict[int, nn.Parameter] = {}
         for u in self.units:
-            if use_symm and u.size > 1:
+            if u.pool is not None:
+                u.flat_param = _alias(u.pool.param[u.slot], u.padded)
+                u.gather_dst = _alias(u.pool.param[u.slot], u.padded)
+                u.flat_grad = _alias(u.pool.grad[u.slot], u.padded)
+                if use_symm:
+                    u.param_shard = self._symm.alloc(u.shard_numel, pd, u.group, tag=f"{u.name}.param_shard")
+                    u.param_shard.zero_()
+                else:
+                    u.param_shard = torch.zeros(u.shard_numel, dtype=pd, device=dev)
+            elif use_symm and u.size > 1:
                 u.flat_param = self._symm.alloc(u.padded, pd, u.group, tag=f"{u.name}.param")
                 u.flat_grad = self._symm.alloc(u.padded, pd, u.group, tag=f"{u.name}.grad")
                 u.flat_param.zero_()
@@ -260,10 +332,17 @@ class ShardedModel:
             arena = symm.SymmetricArena(self.pdims, self.device)
             es = torch.empty(0, dtype=pd).element_size()
             groups = {}
+            biggest: dict[int, int] = {}
             for u in self.units:
                 if u.size > 1:
-                    arena.reserve(u.group, 2 * u.padded * es)
                     groups[id(u.group)] = u.group
+                    if self.sharded_params:   # the unit's parameter shard; the gradient slots are reserved below
+                        arena.reserve(u.group, u.shard_numel * es)
+                        biggest[id(u.group)] = max(biggest.get(id(u.group), 0), u.padded)
+                    else:
+                        arena.reserve(u.group, 2 * u.padded * es)
+            for key, n in biggest.items():
+                arena.reserve(groups[key], 2 * n * es + 1024)
             for g in groups.values():
                 arena._arena(g)
             self._symm = arena
@@ -315,13 +394,88 @@ class ShardedModel:
     def publish_params(self) -> None:
         """master shard -> compute-dtype flat_param (own slice) -> all ranks."""
         for u in self.units:
-            u.shard_view(u.flat_param).copy_(u.master)
+            if u.pool is not None:
+                u.param_shard.copy_(u.master)
+            else:
+                u.shard_view(u.flat_param).copy_(u.master)
         self._all_gather_params()
 
     def _all_gather_params(self) -> None:
         for u in self.units:
-            if u.size > 1:
+            if u.size > 1 and u.pool is None:
                 dist.all_gather_into_tensor(u.flat_param, u.shard_view(u.flat_param), group=u.group)
+        self._shards_changed()
+
+    # ------------------------------------------------------------------
+    # sharded-parameter layout: gathering units into their slots
+    # ------------------------------------------------------------------
+    def _shards_changed(self) -> None:
+        """Parameter shards were rewritten (optimizer step, checkpoint load): nothing gathered is valid any more,
+        and on the NVLink path every rank must have finished writing before anyone pulls."""
+        if not self._pools:
+            return
+        for pool in self._pools.values():
+            pool.owner = [None, None]
+        if self._symm is not None:
+            self._symm.barrier_all()
+
+    def _issue_gather(self, u: FlatUnit) -> None:
+        """All-gather ``u`` into its slot on the communication stream (after everything queued so far on the
+        compute stream, which includes the last use of the slot's previous occupant)."""
+        pool, k = u.pool, u.slot
+        cs = self._comm_stream
+
+        def gather():
+            if self._symm is not None:
+                self._symm.all_gather_shards(u.param_shard, u.gather_dst)
+            else:
+                dist.all_gather_into_tensor(u.gather_dst, u.param_shard, group=u.group)
+
+        if cs is not None:
+            cs.wait_stream(torch.cuda.current_stream(self.device))
+            with torch.cuda.stream(cs):
+                gather()
+                ev = torch.cuda.Event()
+                ev.record(cs)
+            pool.ready[k] = ev
+        else:
+            gather()
+            pool.ready[k] = None
+        pool.owner[k] = u
+
+    def _acquire(self, u: FlatUnit) -> None:
+        """Make sure the unit's full parameters are in its slot before the compute stream goes on."""
+        pool, k = u.pool, u.slot
+        if pool.owner[k] is not u:
+            self._issue_gather(u)
+        if pool.ready[k] is not None:
+            torch.cuda.current_stream(self.device).wait_event(pool.ready[k])
+
+    def _neighbour(self, u: FlatUnit, step: int) -> FlatUnit | None:
+        i = self._order.index(u) + step
+        return self._order[i] if 0 <= i < len(self._order) else None
+
+    def _pre_forward(self, u: FlatUnit) -> None:
+        if u.pool is None:
+            return
+        self._acquire(u)
+        if self._in_backward:      # a recomputed forward inside backward: the backward order prefetches
+            return
+        nxt = self._neighbour(u, +1)
+        if nxt is not None and nxt.pool.owner[nxt.slot] is not nxt:
+            self._issue_gather(nxt)                     # overlaps with this unit's forward
+
+    def _pre_backward(self, u: FlatUnit) -> None:
+        if u.pool is None:
+            return
+        self._in_backward = True
+        self._acquire(u)
+        ev = u.pool.grad_free[u.slot]
+        if ev is not None:                               # the reduce-scatter that last read this gradient slot
+            torch.cuda.current_stream(self.device).wait_event(ev)
+        prv = self._neighbour(u, -1)
+        if prv is not None and prv.pool.owner[prv.slot] is not prv:
+            self._issue_gather(prv)                     # overlaps with this unit's backward
 
     # ------------------------------------------------------------------
     # backward-time gradient reduction
@@ -330,6 +484,8 @@ class ShardedModel:
         """Fire the unit's gradient reduction when the gradient reaches the unit's input."""
         for unit, module in unit_modules:
             module.register_forward_pre_hook(_make_pre_hook(self, unit), with_kwargs=True)
+            if unit.pool is not None:
+                module.register_forward_hook(_make_post_hook(self, unit))
 
     def _on_unit_backward_done(self, unit: FlatUnit) -> None:
         self._collect_autograd_grads(unit)
@@ -366,6 +522,10 @@ class ShardedModel:
             cs.wait_stream(torch.cuda.current_stream(self.device))
             with torch.cuda.stream(cs):
                 self._reduce_unit(unit)
+                if unit.pool is not None:
+                    ev = torch.cuda.Event()
+                    ev.record(cs)
+                    unit.pool.grad_free[unit.slot] = ev
         else:
             self._reduce_unit(unit)
 
@@ -424,6 +584,7 @@ class ShardedModel:
         for u in self.units:
             u.pending = False
         self._callback_queued = False
+        self._in_backward = False
 
     # ------------------------------------------------------------------
     # optimizer-side API
@@ -487,17 +648,20 @@ class ShardedModel:
                 # Muon needs whole matrices: owner-computes over the unit's group (parallel/muon.py)
                 from .muon import muon_unit_step
 
+                if u.pool is not None:
+                    raise NotImplementedError("DistMuon needs the resident parameter layout "
+                                              "(parallelism.fsdp_reshard_after_forward = never)")
                 muon_unit_step(self, u, groups, runs, step, grad_scale)
                 if fused_ag and u.size > 1:
                     dist.all_gather_into_tensor(u.flat_param, u.shard_view(u.flat_param).clone(), group=u.group)
                 u.grad_shard_valid = False
                 continue
-            if fused_ag and u.size > 1:
+            if fused_ag and u.size > 1 and u.pool is None:
                 # update + all-gather in one kernel: refreshed weights are stored to every peer
                 self._symm.adamw_allgather(u, _group_runs(u), groups, step, grad_scale.reshape(1), g)
                 u.grad_shard_valid = False
                 continue
-            lowp = u.shard_view(u.flat_param)
+            lowp = u.param_shard if u.pool is not None else u.shard_view(u.flat_param)
             for gi, a, b in _group_runs(u):
                 h = groups[gi]
                 optim_ops.adamw_(
@@ -511,7 +675,10 @@ class ShardedModel:
         if self.offload_optimizer:
             torch.cuda.current_stream(self.device).synchronize()   # host buffers are complete before anyone reads them
         if fused_ag:
-            self._symm.barrier_all()  # peers' stores into our parameter buffers have landed
+            if not self._pools:
+                self._symm.barrier_all()  # peers' stores into our parameter buffers have landed
+            else:
+                self._shards_changed()    # (includes the barrier)
         else:
             self._all_gather_params()
 
@@ -567,21 +734,52 @@ class ShardedModel:
         """One-line description of where parameters and gradients live (reported by the benchmark)."""
         if all(u.size == 1 for u in self.units):
             return "single rank: bf16 parameters and gradients, fp32 master weights and moments"
+        if self._pools:
+            return ("bf16 parameters sharded 1/N between uses (two gather slots and two gradient slots per group, next "
+                    "unit prefetched on the communication stream), fp32 master weights and moments sharded 1/N")
         return ("bf16 parameters and gradients replicated on every rank (resident, refreshed once per step by the "
                 "optimizer kernel), fp32 master weights and moments sharded 1/N")
 
     def memory_summary(self) -> dict[str, float]:
         gib = 1 << 30
         tot = {"flat_param": 0, "flat_grad": 0, "master": 0, "grad_shard": 0, "opt_state": 0}
+        for pool in self._pools.values():
+            tot["flat_param"] += sum(t.numel() * t.element_size() for t in pool.param)
+            tot["flat_grad"] += sum(t.numel() * t.element_size() for t in pool.grad)
         for u in self.units:
-            tot["flat_param"] += u.flat_param.numel() * u.flat_param.element_size()
-            tot["flat_grad"] += u.flat_grad.numel() * u.flat_grad.element_size()
+            if u.pool is not None:
+                tot["flat_param"] += u.param_shard.numel() * u.param_shard.element_size()
+            else:
+                tot["flat_param"] += u.flat_param.numel() * u.flat_param.element_size()
+                tot["flat_grad"] += u.flat_grad.numel() * u.flat_grad.element_size()
             tot["master"] += u.master.numel() * 4
             if u.grad_shard is not None:
                 tot["grad_shard"] += u.grad_shard.numel() * 4
             if u.exp_avg is not None:
                 tot["opt_state"] += 2 * u.exp_avg.numel() * u.exp_avg.element_size()
         return {k: v / gib for k, v in tot.items()}
+
+
+class _SlotPool:
+    """Two rotating full-size parameter buffers and two gradient buffers shared by the units of one sharding
+    group (sharded-parameter layout).  ``owner[k]`` is the unit whose gathered parameters slot ``k`` holds,
+    ``ready[k]`` the event of that gather, ``grad_free[k]`` the event of the last reduce-scatter out of
+    gradient slot ``k``."""
+
+    def __init__(self, param: list[torch.Tensor], grad: list[torch.Tensor]):
+        self.param, self.grad = param, grad
+        self.owner: list = [None, None]
+        self.ready: list = [None, None]
+        self.grad_free: list = [None, None]
+
+
+def _alias(t: torch.Tensor, numel: int) -> torch.Tensor:
+    """A fresh tensor over the first ``numel`` elements of ``t``'s storage.  It shares memory but not the
+    autograd version counter, so gathering into it does not invalidate tensors that autograd saved from a
+    sibling alias (the values are the same before and after a re-gather)."""
+    out = torch.empty(0, dtype=t.dtype, device=t.device)
+    out.set_(t.untyped_storage(), t.storage_offset(), (numel,), (1,))
+    return out
 
 
 def _group_runs(u: FlatUnit):
@@ -620,8 +818,45 @@ class _UnitBackwardEnd(torch.autograd.Function):
         return (None, None) + grads
 
 
+class _UnitBackwardStart(torch.autograd.Function):
+    """Identity on the unit's outputs whose backward re-gathers the unit's parameters (sharded layout)."""
+
+    @staticmethod
+    def forward(ctx, engine, unit, *tensors):
+        ctx.engine, ctx.unit = engine, unit
+        return tuple(t.view_as(t) for t in tensors)
+
+    @staticmethod
+    def backward(ctx, *grads):
+        ctx.engine._pre_backward(ctx.unit)
+        return (None, None) + grads
+
+
+def _make_post_hook(engine: ShardedModel, unit: FlatUnit):
+    def hook(module, args, output):
+        if not torch.is_grad_enabled():
+            return None
+        if isinstance(output, torch.Tensor):
+            if not output.requires_grad:
+                return None
+            return _UnitBackwardStart.apply(engine, unit, output)[0]
+        if isinstance(output, tuple):
+            idx = [i for i, o in enumerate(output) if isinstance(o, torch.Tensor) and o.requires_grad]
+            if not idx:
+                return None
+            outs = _UnitBackwardStart.apply(engine, unit, *[output[i] for i in idx])
+            res = list(output)
+            for i, o in zip(idx, outs):
+                res[i] = o
+            return tuple(res)
+        return None
+
+    return hook
+
+
 def _make_pre_hook(engine: ShardedModel, unit: FlatUnit):
     def hook(module, args, kwargs):
+        engine._pre_forward(unit)
         if not torch.is_grad_enabled():
             return None
         if not engine._callback_queued:

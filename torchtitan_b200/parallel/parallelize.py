@@ -111,11 +111,17 @@ def parallelize_decoder(model: nn.Module, *, pdims, job_config, device: torch.de
         model, decoder_units(model, pdims), pdims=pdims, device=device, param_dtype=param_dtype,
         state_dtype=state_dtype, seed=seed, comm=par.fsdp_comm, grad_accum_steps=grad_accum_steps,
         fqn_prefix=fqn_prefix, tp=tp, offload_optimizer=bool(getattr(tr, "enable_cpu_offload", False)),
+        reshard_after_forward=getattr(par, "fsdp_reshard_after_forward", "never") or "never",
     )
     if materialize:
         engine.materialize()
         hooks = []
         by_name = {u.name: u for u in engine.units}
+        if engine.sharded_params and model.tok_embeddings is not None:
+            # the embedding must be gathered before its lookup (it sits in the output unit when tied)
+            emb_unit = by_name.get("tok_embeddings") or by_name.get("output")
+            if emb_unit is not None:
+                hooks.append((emb_unit, model.tok_embeddings))
         for name, blk in model.layers.items():
             for key in (f"layers.{name}", f"layers.{name}.experts"):
                 if key in by_name:

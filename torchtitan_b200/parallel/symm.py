@@ -231,6 +231,15 @@ class SymmetricArena:
                                  float(b2), float(h["eps"]), float(h["weight_decay"]), 1.0 - b1 ** step,
                                  1.0 - b2 ** step)
 
+    def all_gather_shards(self, shard: torch.Tensor, out: torch.Tensor) -> None:
+        """``out[r * n:(r + 1) * n] = rank r's shard`` for every rank, by 16-byte peer loads (``shard`` is a
+        symmetric allocation, ``out`` local).  No barrier: the caller guarantees that no rank is writing its
+        shard (parameter shards change only inside the optimizer step, which ends with a barrier)."""
+        arena, ptrs = self.peer_ptrs(shard)
+        nbytes = shard.numel() * shard.element_size()
+        _count()
+        ext.require().all_gather_pull(ptrs, arena.rank, nbytes, out)
+
     def barrier_all(self) -> None:
         for arena in self._arenas.values():
             arena.barrier()
