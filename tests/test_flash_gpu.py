@@ -72,7 +72,7 @@ def fwd_variant(request):
     ops = ext.require()
     ops.flash_set_fwd_variant(request.param)
     yield request.param
-    ops.flash_set_fwd_variant(3)
+    ops.flash_set_fwd_variant(0)
 
 
 @pytest.mark.parametrize("Tq,Tk,Hq,Hkv,causal,offset,docs,packed", CASES)

@@ -30,6 +30,7 @@ std::tuple<at::Tensor, at::Tensor> flash_fwd(const at::Tensor& q, const at::Tens
                                              const c10::optional<at::Tensor>& kv_first, int64_t window,
                                              const c10::optional<at::Tensor>& sinks);
 void flash_set_fwd_variant(int64_t v);
+void attn_merge_(at::Tensor acc_o, at::Tensor acc_lse, const at::Tensor& o, const at::Tensor& lse);
 std::tuple<at::Tensor, at::Tensor, at::Tensor> flash_bwd(const at::Tensor& d_o, const at::Tensor& q, const at::Tensor& k,
                                                          const at::Tensor& v, const at::Tensor& o, const at::Tensor& lse,
                                                          double scale, bool causal, int64_t causal_offset,
@@ -103,6 +104,7 @@ TORCH_LIBRARY(tb200, m) {
   m.def("flash_fwd(Tensor q, Tensor k, Tensor v, float scale, bool causal, int causal_offset, Tensor? kv_first, "
         "int window=0, Tensor? sinks=None) -> (Tensor, Tensor)", &tb200::flash_fwd);
   m.def("flash_set_fwd_variant(int v) -> ()", &tb200::flash_set_fwd_variant);
+  m.def("attn_merge_(Tensor(a!) acc_o, Tensor(b!) acc_lse, Tensor o, Tensor lse) -> ()", &tb200::attn_merge_);
   m.def("flash_bwd(Tensor d_o, Tensor q, Tensor k, Tensor v, Tensor o, Tensor lse, float scale, bool causal, "
         "int causal_offset, Tensor? kv_first, Tensor(a!)? dq_out, Tensor(b!)? dk_out, Tensor(c!)? dv_out, "
         "int window=0) -> (Tensor, Tensor, Tensor)", &tb200::flash_bwd);

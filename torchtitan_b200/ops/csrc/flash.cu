@@ -772,8 +772,8 @@ struct BwdParams {
   int causal, causal_offset;
   float scale, scale_log2;
   const int* kv_first;     // [Tq] or nullptr
-  const float* lse;        // [Hq, Tq], row stride `stat_stride`
-  const float* delta;      // [Hq, Tq] rowsum(dO * O), row stride `stat_stride`
+  const float* lse;        // [Hq, Tq]: -lse log2(e) (pre-scaled by flash_delta_kernel), row stride `stat_stride`
+  const float* delta;      // [Hq, Tq]: -rowsum(dO * O) scale, row stride `stat_stride`
   int debug;               // timing diagnostics: bit 0 skips the warps' math, bit 1 skips the MMAs (results are garbage)
   int stat_stride;         // a multiple of 64 floats, so that 64-row slices can be fetched with bulk copies
   int* status;
@@ -938,51 +938,59 @@ flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
     const int kv_idx = k0 + r;
     const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
     bool ok = true;
+    const uint64_t sc2 = pack2(p.scale_log2, p.scale_log2), scl2 = pack2(p.scale, p.scale);
+    int sub = 0, st = 0;                           // t % n_sub and t % kRing, kept without divisions
+    uint32_t ring_par = 0;                         // (t / kRing) & 1
     for (int t = 0; t < n_iter; ++t) {
       const int b = t & 1;
-      const int qc0 = q_lo + (t % n_sub) * kBQ + grp * 16;    // first query column of this thread
+      const int qc0 = q_lo + sub * kBQ + grp * 16;    // first query column of this thread
       if (!mbar_wait(bar(ST_FULL + b), (t >> 1) & 1u, abort_flag)) { ok = false; break; }
       tc_fence_after();
-      if (p.debug & 1) { tc_fence_before(); __syncwarp(); if (lane == 0) mbar_arrive(bar(PS_READY + b)); continue; }
+      if (p.debug & 1) {
+        tc_fence_before(); __syncwarp(); if (lane == 0) mbar_arrive(bar(PS_READY + b));
+        if (++sub == n_sub) sub = 0;
+        if (++st == kRing) { st = 0; ring_par ^= 1u; }
+        continue;
+      }
       uint32_t sv[16], dv[16];
       tmem_ld16(tmem_base + lane_addr + T_ST + b * 64 + grp * 16, sv);
       tmem_ld16(tmem_base + lane_addr + T_DPT + b * 64 + grp * 16, dv);
       tmem_ld_wait();
-      // lse and delta of the 64 query rows of this step were staged next to Q / dO by the producer
-      // (the stage's barrier has completed long ago: the MMAs that filled S^T waited on it)
-      if (!mbar_wait(bar(R_FULL + t % kRing), (t / kRing) & 1u, abort_flag)) { ok = false; break; }
-      const uint32_t stat = stat_smem + (uint32_t)(t % kRing) * 512u + (uint32_t)grp * 64u;
+      // -lse log2(e) and -delta scale of the 64 query rows of this step were staged next to Q / dO by the
+      // producer (the stage's barrier has completed long ago: the MMAs that filled S^T waited on it)
+      if (!mbar_wait(bar(R_FULL + st), ring_par, abort_flag)) { ok = false; break; }
+      const uint32_t stat = stat_smem + (uint32_t)st * 512u + (uint32_t)grp * 64u;
       const bool edge = p.kv_first != nullptr || qc0 + 16 > p.Tq || k0 + kBN > p.Tk ||
                         (p.causal && qc0 + p.causal_offset < k0 + kBN - 1) ||
                         (p.window > 0 && qc0 + 15 + p.causal_offset - p.window + 1 > k0);
       uint32_t pk[8], dk[8];
 #pragma unroll
       for (int g = 0; g < 4; ++g) {
-        float l4[4], d4[4];
-        asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];"
-                     : "=f"(l4[0]), "=f"(l4[1]), "=f"(l4[2]), "=f"(l4[3]) : "r"(stat + g * 16));
-        asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];"
-                     : "=f"(d4[0]), "=f"(d4[1]), "=f"(d4[2]), "=f"(d4[3]) : "r"(stat + 256 + g * 16));
-        float pv[4], ds[4];
+        // two packed pairs of each statistic, ready to be the addend of a two-wide FMA
+        uint64_t nl[2], nd[2];
+        asm volatile("ld.shared.v2.b64 {%0, %1}, [%2];" : "=l"(nl[0]), "=l"(nl[1]) : "r"(stat + g * 16));
+        asm volatile("ld.shared.v2.b64 {%0, %1}, [%2];" : "=l"(nd[0]), "=l"(nd[1]) : "r"(stat + 256 + g * 16));
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const int i = g * 4 + e;
-          float pe = exp2f(fmaf(__uint_as_float(sv[i]), p.scale_log2, -l4[e] * 1.4426950408889634f));
+        for (int h2 = 0; h2 < 2; ++h2) {
+          const int i = g * 4 + h2 * 2;
+          float x0, x1, d0, d1;
+          unpack2(fma2(pack2(__uint_as_float(sv[i]), __uint_as_float(sv[i + 1])), sc2, nl[h2]), x0, x1);
+          unpack2(fma2(pack2(__uint_as_float(dv[i]), __uint_as_float(dv[i + 1])), scl2, nd[h2]), d0, d1);
+          float p0 = ex2_mufu(x0), p1 = ex2_mufu(x1);
           if (edge) {
-            const int qi = qc0 + i;
-            bool vis = qi < p.Tq && kv_idx < p.Tk;
-            if (p.causal) vis = vis && kv_idx <= qi + p.causal_offset;
-            if (p.window > 0) vis = vis && kv_idx > qi + p.causal_offset - p.window;
-            if (p.kv_first != nullptr) vis = vis && kv_idx >= p.kv_first[min(qi, p.Tq - 1)];
-            if (!vis) pe = 0.f;
+#pragma unroll
+            for (int u = 0; u < 2; ++u) {
+              const int qi = qc0 + i + u;
+              bool vis = qi < p.Tq && kv_idx < p.Tk;
+              if (p.causal) vis = vis && kv_idx <= qi + p.causal_offset;
+              if (p.window > 0) vis = vis && kv_idx > qi + p.causal_offset - p.window;
+              if (p.kv_first != nullptr) vis = vis && kv_idx >= p.kv_first[min(qi, p.Tq - 1)];
+              if (!vis) { if (u == 0) p0 = 0.f; else p1 = 0.f; }
+            }
           }
-          pv[e] = pe;
-          ds[e] = pe * fmaf(__uint_as_float(dv[i]), p.scale, -d4[e] * p.scale);
+          pk[2 * g + h2] = pack_bf16(p0, p1);
+          dk[2 * g + h2] = pack_bf16(p0 * d0, p1 * d1);
         }
-        pk[2 * g] = pack_bf16(pv[0], pv[1]);
-        pk[2 * g + 1] = pack_bf16(pv[2], pv[3]);
-        dk[2 * g] = pack_bf16(ds[0], ds[1]);
-        dk[2 * g + 1] = pack_bf16(ds[2], ds[3]);
       }
       // packed P^T / dS^T of this group's 16 columns go to the first 8 of its own 16 TMEM columns
       tmem_st8(tmem_base + lane_addr + T_ST + b * 64 + grp * 16, pk);
@@ -991,6 +999,8 @@ flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar(PS_READY + b));
+      if (++sub == n_sub) sub = 0;
+      if (++st == kRing) { st = 0; ring_par ^= 1u; }
     }
     if (ok && n_iter > 0) ok = mbar_wait(bar(ALL_DONE), 0, abort_flag);
     // ---- dK, dV: tensor memory -> bf16 -> swizzled staging tiles (the Q / dO ring) -> TMA store
@@ -1047,12 +1057,16 @@ flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
 // those rows can see (the forward's loop).  Per key block:
 //     S = Q . K^T,  dP = dO . V^T             (tcgen05.mma, shared-memory operands)
 //     dS = exp2(S c - lse) (dP - delta) scale  (16 warps: one query row, 32 keys per thread),
-//          written over S as packed bf16
+//          written as packed bf16 into its own tensor-memory columns
 //     dQ += dS . K                             (A operand from tensor memory)
-// dP is double buffered, so the dP MMA of the next block runs during the warps' math.
+// The warps read S and dP of block i into registers and release both accumulators at once
+// (SDP_FREE); the S and dP MMAs of block i+1 then run while the warps do the math of block i, so
+// the exponentials run back to back and the tensor pipe stays fed.  dS has one buffer: the dQ MMA
+// of block i is followed by a commit on DQ_DONE, which the warps wait for before they store dS of
+// block i+1 (by then it has long completed).
 //   warp 0 TMA producer (Q, dO once; K and V through two-stage rings), warp 1 MMA, warps 2..17 math
 //   (lane quarter = warp % 4, group of 32 keys = (warp - 2) / 4)
-// Tensor memory: S / dS [0,128)   dP [128,256) [256,384)   dQ [384,512)
+// Tensor memory: S [0,128)   dP [128,256)   dS (packed bf16) [256,320)   dQ [384,512)
 __global__ void __launch_bounds__(kThreadsBwd, 1)
 flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_do,
                     const __grid_constant__ CUtensorMap tmap_k, const __grid_constant__ CUtensorMap tmap_v,
@@ -1068,8 +1082,8 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
   const uint32_t v_smem = base + 4 * kTileBytes;
   constexpr uint32_t kBarOff = 6 * kTileBytes;
   const uint32_t bar_base = base + kBarOff;
-  enum { Q_FULL = 0, K_FULL = 1, K_EMPTY = 3, V_FULL = 5, V_EMPTY = 7, S_FULL = 9, DP_FULL = 10, DS_READY = 12, DQ_FULL = 13,
-         OUT_STAGED = 14, NBAR = 15 };
+  enum { Q_FULL = 0, K_FULL = 1, K_EMPTY = 3, V_FULL = 5, V_EMPTY = 7, S_FULL = 9, DP_FULL = 10, DS_READY = 11, DQ_FULL = 12,
+         OUT_STAGED = 13, SDP_FREE = 14, DQ_DONE = 15, NBAR = 16 };
   auto bar = [&](int i) { return bar_base + 8u * i; };
   uint32_t* tmem_ptr_smem = reinterpret_cast<uint32_t*>(gen_base + kBarOff + 8 * NBAR);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_ptr_smem + 1);
@@ -1097,9 +1111,11 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
       mbar_init(bar(K_EMPTY + s), 1);
       mbar_init(bar(V_FULL + s), 1);
       mbar_init(bar(V_EMPTY + s), 1);
-      mbar_init(bar(DP_FULL + s), 1);
     }
     mbar_init(bar(S_FULL), 1);
+    mbar_init(bar(DP_FULL), 1);
+    mbar_init(bar(SDP_FREE), 4 * kMathGroups);
+    mbar_init(bar(DQ_DONE), 1);
     mbar_init(bar(DS_READY), 4 * kMathGroups);
     mbar_init(bar(DQ_FULL), 1);
     mbar_init(bar(OUT_STAGED), 4 * kMathGroups);
@@ -1118,7 +1134,7 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_ptr_smem;
-  constexpr uint32_t T_S = 0, T_DP = 128, T_DQ = 384;
+  constexpr uint32_t T_S = 0, T_DP = 128, T_DS = 256, T_DQ = 384;
 
   if (warp == 0) {
     if (lane == 0 && n_tiles > 0) {
@@ -1145,25 +1161,24 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
     if (lane == 0 && n_tiles > 0) {
       const uint32_t idesc_s = make_idesc(false, false, kBM, kBN);
       const uint32_t idesc_dq = make_idesc(false, true, kBM, kD);     // A = dS from TMEM, B = K as [key, head dim]
-      auto issue_nt = [&](uint32_t d_col, uint32_t a_smem, uint32_t b_smem) {
+      // S and dP of one block: the two accumulators alternate, so that consecutive MMAs do not depend on each other
+      auto issue_scores = [&](uint32_t k_tile, uint32_t v_tile) {
         if (p.debug & 2) return;
 #pragma unroll
         for (int k = 0; k < kD / 16; ++k) {
           const uint32_t off = (uint32_t)(k >> 2) * kHalfBytes + (uint32_t)(k & 3) * 32u;
-          umma_bf16<1>(tmem_base + d_col, make_desc(a_smem + off, 16, 1024), make_desc(b_smem + off, 16, 1024), idesc_s,
+          umma_bf16<1>(tmem_base + T_S, make_desc(q_smem + off, 16, 1024), make_desc(k_tile + off, 16, 1024), idesc_s,
+                       k != 0 ? 1u : 0u);
+          umma_bf16<1>(tmem_base + T_DP, make_desc(do_smem + off, 16, 1024), make_desc(v_tile + off, 16, 1024), idesc_s,
                        k != 0 ? 1u : 0u);
         }
       };
-      bool ok = mbar_wait(bar(Q_FULL), 0, abort_flag) && mbar_wait(bar(K_FULL), 0, abort_flag);
+      bool ok = mbar_wait(bar(Q_FULL), 0, abort_flag) && mbar_wait(bar(K_FULL), 0, abort_flag) &&
+                mbar_wait(bar(V_FULL), 0, abort_flag);
       if (ok) {
         tc_fence_after();
-        issue_nt(T_S, q_smem, k_smem);
+        issue_scores(k_smem, v_smem);
         umma_commit(bar(S_FULL));
-        ok = mbar_wait(bar(V_FULL), 0, abort_flag);
-      }
-      if (ok) {
-        tc_fence_after();
-        issue_nt(T_DP, do_smem, v_smem);
         umma_commit(bar(DP_FULL));
         umma_commit(bar(V_EMPTY));
       }
@@ -1171,30 +1186,26 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
         const int st = i & 1;
         if (i + 1 < n_tiles) {
           const int s1 = (i + 1) & 1;
+          // the warps hold S and dP of block i in registers: both accumulators take the next block now
+          if (!mbar_wait(bar(SDP_FREE), i & 1u, abort_flag)) { ok = false; break; }
+          if (!mbar_wait(bar(K_FULL + s1), ((i + 1) >> 1) & 1u, abort_flag)) { ok = false; break; }
           if (!mbar_wait(bar(V_FULL + s1), ((i + 1) >> 1) & 1u, abort_flag)) { ok = false; break; }
           tc_fence_after();
-          issue_nt(T_DP + s1 * 128, do_smem, v_smem + s1 * kTileBytes);
-          umma_commit(bar(DP_FULL + s1));
+          issue_scores(k_smem + s1 * kTileBytes, v_smem + s1 * kTileBytes);
+          umma_commit(bar(S_FULL));
+          umma_commit(bar(DP_FULL));
           umma_commit(bar(V_EMPTY + s1));
         }
         if (!mbar_wait(bar(DS_READY), i & 1u, abort_flag)) { ok = false; break; }
         tc_fence_after();
         if (!(p.debug & 2))
 #pragma unroll
-        for (int ks = 0; ks < kBN / 16; ++ks) {
-          const uint32_t a_col = (uint32_t)(ks >> 1) * 32u + (uint32_t)(ks & 1) * 8u;
-          umma_bf16_ts(tmem_base + T_DQ, tmem_base + T_S + a_col,
+        for (int ks = 0; ks < kBN / 16; ++ks)   // 16 keys per step: 8 packed columns of dS, 16 rows (2048 B) of K
+          umma_bf16_ts(tmem_base + T_DQ, tmem_base + T_DS + (uint32_t)ks * 8u,
                        make_desc(k_smem + st * kTileBytes + ks * 2048, kHalfBytes, 1024), idesc_dq,
                        (i > 0 || ks > 0) ? 1u : 0u);
-        }
         umma_commit(bar(K_EMPTY + st));
-        if (i + 1 < n_tiles) {
-          const int s1 = (i + 1) & 1;
-          if (!mbar_wait(bar(K_FULL + s1), ((i + 1) >> 1) & 1u, abort_flag)) { ok = false; break; }
-          tc_fence_after();
-          issue_nt(T_S, q_smem, k_smem + s1 * kTileBytes);
-          umma_commit(bar(S_FULL));
-        }
+        umma_commit(bar(DQ_DONE));
       }
       if (ok) umma_commit(bar(DQ_FULL));
     }
@@ -1205,42 +1216,66 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
     const int row = q0 + row_in_tile;
     const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
     const bool row_ok = row < p.Tq;
-    const float l2 = row_ok ? p.lse[(int64_t)head * p.stat_stride + row] * 1.4426950408889634f : INFINITY;
-    const float dl = (row_ok ? p.delta[(int64_t)head * p.stat_stride + row] : 0.f) * p.scale;
+    const float l2 = row_ok ? -p.lse[(int64_t)head * p.stat_stride + row] : INFINITY;   // lse log2(e)
+    const float dl = row_ok ? -p.delta[(int64_t)head * p.stat_stride + row] : 0.f;       // delta scale
     int lo = p.kv_first != nullptr ? p.kv_first[min(row, p.Tq - 1)] : 0;
     if (p.window > 0) lo = max(lo, row + p.causal_offset - p.window + 1);
     const int hi = min(p.Tk - 1, p.causal ? row + p.causal_offset : p.Tk - 1);
     bool ok = true;
+    const uint64_t sc2 = pack2(p.scale_log2, p.scale_log2), nl2 = pack2(-l2, -l2);
+    const uint64_t scl2 = pack2(p.scale, p.scale), ndl2 = pack2(-dl, -dl);
     for (int i = 0; i < n_tiles; ++i) {
-      if (!mbar_wait(bar(S_FULL), i & 1u, abort_flag) || !mbar_wait(bar(DP_FULL + (i & 1)), (i >> 1) & 1u, abort_flag)) {
+      if (!mbar_wait(bar(S_FULL), i & 1u, abort_flag) || !mbar_wait(bar(DP_FULL), i & 1u, abort_flag)) {
         ok = false;
         break;
       }
       tc_fence_after();
-      if (p.debug & 1) { tc_fence_before(); __syncwarp(); if (lane == 0) mbar_arrive(bar(DS_READY)); continue; }
+      if (p.debug & 1) {
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(SDP_FREE));
+        if (i > 0 && !mbar_wait(bar(DQ_DONE), (i - 1) & 1u, abort_flag)) { ok = false; break; }
+        if (lane == 0) mbar_arrive(bar(DS_READY));
+        continue;
+      }
       const int c0 = (j_lo + i) * kBN + grp * 32;
       const bool edge = (c0 + 31 > hi) || (c0 < lo);
       uint32_t sv[32], dv[32], out[16];
       tmem_ld32(tmem_base + lane_addr + T_S + grp * 32, sv);
-      tmem_ld32(tmem_base + lane_addr + T_DP + (i & 1) * 128 + grp * 32, dv);
+      tmem_ld32(tmem_base + lane_addr + T_DP + grp * 32, dv);
       tmem_ld_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(SDP_FREE));
+      if (edge) {
 #pragma unroll
-      for (int e = 0; e < 16; ++e) {
-        float ds2[2];
+        for (int e = 0; e < 16; ++e) {
+          float ds2[2];
 #pragma unroll
-        for (int u = 0; u < 2; ++u) {
-          const int idx = 2 * e + u;
-          float pe = exp2f(fmaf(__uint_as_float(sv[idx]), p.scale_log2, -l2));
-          if (edge) {
+          for (int u = 0; u < 2; ++u) {
+            const int idx = 2 * e + u;
             const int col = c0 + idx;
+            float pe = ex2_mufu(fmaf(__uint_as_float(sv[idx]), p.scale_log2, -l2));
             if (col > hi || col < lo) pe = 0.f;
+            ds2[u] = pe * fmaf(__uint_as_float(dv[idx]), p.scale, -dl);
           }
-          ds2[u] = pe * fmaf(__uint_as_float(dv[idx]), p.scale, -dl);
+          out[e] = pack_bf16(ds2[0], ds2[1]);
         }
-        out[e] = pack_bf16(ds2[0], ds2[1]);
+      } else {
+#pragma unroll
+        for (int e = 0; e < 16; ++e) {
+          float x0, x1, d0, d1;
+          unpack2(fma2(pack2(__uint_as_float(sv[2 * e]), __uint_as_float(sv[2 * e + 1])), sc2, nl2), x0, x1);
+          unpack2(fma2(pack2(__uint_as_float(dv[2 * e]), __uint_as_float(dv[2 * e + 1])), scl2, ndl2), d0, d1);
+          out[e] = pack_bf16(ex2_mufu(x0) * d0, ex2_mufu(x1) * d1);
+        }
       }
-      // this thread's S columns are in registers: the packed dS overwrites the first half of them
-      tmem_st16(tmem_base + lane_addr + T_S + grp * 32, out);
+      // dS has a single buffer: the dQ MMA of the previous block must have read it
+      if (i > 0) {
+        if (!mbar_wait(bar(DQ_DONE), (i - 1) & 1u, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+      }
+      tmem_st16(tmem_base + lane_addr + T_DS + grp * 16, out);
       tmem_st_wait();
       tc_fence_before();
       __syncwarp();
@@ -1290,9 +1325,12 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
   if (threadIdx.x == 0 && *abort_flag && p.status != nullptr) atomicOr(p.status, kStatusWaitTimedOut);
 }
 
-// delta[h, t] = sum_d dO[t, h, d] * O[t, h, d]: one warp per (token, head).
+// The per-row statistics of the backward kernels, already in the form their inner loops add:
+//   ndelta[h, t] = -scale sum_d dO[t, h, d] O[t, h, d]      nlse2[h, t] = -lse[h, t] log2(e)
+// One warp per (token, head).
 __global__ void flash_delta_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ d_o,
-                                   float* __restrict__ delta, int T, int H, int stride) {
+                                   const float* __restrict__ lse, int lse_stride, float* __restrict__ ndelta,
+                                   float* __restrict__ nlse2, int T, int H, int stride, float scale) {
   const int64_t w = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
   if (w >= (int64_t)T * H) return;
@@ -1304,7 +1342,42 @@ __global__ void flash_delta_kernel(const __nv_bfloat16* __restrict__ o, const __
   const float2 b0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&b.x));
   const float2 b1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&b.y));
   const float s = warp_sum(a0.x * b0.x + a0.y * b0.y + a1.x * b1.x + a1.y * b1.y);
-  if (lane == 0) delta[(int64_t)h * stride + t] = s;
+  if (lane == 0) {
+    ndelta[(int64_t)h * stride + t] = -s * scale;
+    nlse2[(int64_t)h * stride + t] = -lse[(int64_t)h * lse_stride + t] * 1.4426950408889634f;
+  }
+}
+
+// Online-softmax merge of one block's normalised attention output into a running fp32 pair:
+//   lse' = log(exp(lse_a) + exp(lse_b));  o' = o_a exp(lse_a - lse') + o_b exp(lse_b - lse').
+// One warp per (token, head), four head-dim elements per lane; -inf (no visible key) contributes nothing.
+__global__ void attn_merge_kernel(float* __restrict__ acc_o, float* __restrict__ acc_lse, const __nv_bfloat16* __restrict__ o,
+                                  const float* __restrict__ lse, int T, int H, int acc_lse_stride, int lse_stride) {
+  const int64_t w = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (w >= (int64_t)T * H) return;
+  const int t = (int)(w / H), h = (int)(w % H);
+  const float la = acc_lse[(int64_t)h * acc_lse_stride + t];
+  const float lb = lse[(int64_t)h * lse_stride + t];
+  const float mx = fmaxf(la, lb);
+  float wa = 0.f, wb = 0.f, ln = -INFINITY;
+  if (mx > -INFINITY) {
+    const float ea = __expf(la - mx), eb = __expf(lb - mx);   // exp(-inf) = 0
+    ln = mx + __logf(ea + eb);
+    wa = ea / (ea + eb);
+    wb = eb / (ea + eb);
+  }
+  float4 a = *reinterpret_cast<const float4*>(acc_o + w * kD + lane * 4);
+  const uint2 b = *reinterpret_cast<const uint2*>(o + w * kD + lane * 4);
+  const float2 b0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&b.x));
+  const float2 b1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&b.y));
+  a.x = a.x * wa + b0.x * wb;
+  a.y = a.y * wa + b0.y * wb;
+  a.z = a.z * wa + b1.x * wb;
+  a.w = a.w * wa + b1.y * wb;
+  *reinterpret_cast<float4*>(acc_o + w * kD + lane * 4) = a;
+  __syncwarp();
+  if (lane == 0) acc_lse[(int64_t)h * acc_lse_stride + t] = ln;
 }
 
 }  // namespace flash
@@ -1355,7 +1428,7 @@ void flash_set_fwd_variant(int64_t v) {
 static int flash_fwd_variant() {
   if (g_flash_fwd_variant < 0) {
     const char* e = std::getenv("TB200_FLASH_FWD");
-    g_flash_fwd_variant = (e != nullptr && e[0] >= '0' && e[0] <= '4' && e[1] == 0) ? e[0] - '0' : 3;
+    g_flash_fwd_variant = (e != nullptr && e[0] >= '0' && e[0] <= '4' && e[1] == 0) ? e[0] - '0' : 0;
   }
   return g_flash_fwd_variant;
 }
@@ -1414,7 +1487,7 @@ std::tuple<at::Tensor, at::Tensor> flash_fwd(const at::Tensor& q, const at::Tens
                 "flash_fwd: sinks must be a float32 [Hq] CUDA tensor");
     p.sinks = sinks->data_ptr<float>();
   }
-  if ((p.window > 0 || p.sinks != nullptr) && variant == 0) variant = 3;   // only the pipelined kernel has them
+  if ((p.window > 0 || p.sinks != nullptr) && variant == 0) variant = 2;   // only the pipelined kernel has them
   const CUtensorMap tq = make_tmap_thd(q, kBM), tk = make_tmap_thd(k, kBN), tv = make_tmap_thd(v, kBN),
                     to = make_tmap_thd(o, kBM);
   constexpr uint32_t smem = 6 * kTileBytes + 1024 + 256;
@@ -1472,19 +1545,16 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor> flash_bwd(const at::Tensor& d_o, 
   TORCH_CHECK(dv.dim() == 3 && dv.size(0) == Tk && dv.size(1) == Hkv && dv.size(2) == kD);
   if (Tq == 0 || Tk == 0) return {dq, dk, dv};
   const int64_t Tpad = (Tq + 63) / 64 * 64;
-  // lse as returned by flash_fwd has padded rows; anything else is copied into that layout
-  at::Tensor lse_p = lse;
-  if (!(lse.stride(1) == 1 && lse.stride(0) == Tpad && (reinterpret_cast<uintptr_t>(lse.data_ptr()) & 15) == 0)) {
-    lse_p = at::zeros({Hq, Tpad}, lse.options()).narrow(1, 0, Tq);
-    lse_p.copy_(lse);
-  }
-  auto delta = at::zeros({Hq, Tpad}, lse.options());
+  TORCH_CHECK(lse.stride(1) == 1, "flash_bwd: lse rows must be contiguous");
+  // rows padded to a multiple of 64 floats (zero filled): the dK/dV kernel fetches 64-row slices with bulk copies
+  auto stats = at::zeros({2, Hq, Tpad}, lse.options());
   {
     const int64_t warps = Tq * Hq;
     const int threads = 256;
     flash_delta_kernel<<<(unsigned)((warps * 32 + threads - 1) / threads), threads, 0, stream>>>(
         reinterpret_cast<const __nv_bfloat16*>(o.data_ptr()), reinterpret_cast<const __nv_bfloat16*>(d_o.data_ptr()),
-        delta.data_ptr<float>(), (int)Tq, (int)Hq, (int)Tpad);
+        lse.data_ptr<float>(), (int)lse.stride(0), stats[0].data_ptr<float>(), stats[1].data_ptr<float>(), (int)Tq, (int)Hq,
+        (int)Tpad, (float)scale);
     C10_CUDA_KERNEL_LAUNCH_CHECK();
   }
   BwdParams p;
@@ -1499,8 +1569,8 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor> flash_bwd(const at::Tensor& d_o, 
                 kv_first->is_contiguous(), "flash_bwd: kv_first must be an int32 [Tq] CUDA tensor");
     p.kv_first = kv_first->data_ptr<int>();
   }
-  p.lse = lse_p.data_ptr<float>();
-  p.delta = delta.data_ptr<float>();
+  p.delta = stats[0].data_ptr<float>();
+  p.lse = stats[1].data_ptr<float>();
   p.stat_stride = (int)Tpad;
   p.debug = g_flash_debug;
   p.status = flash_status_tensor(q.device()).data_ptr<int>();
@@ -1533,6 +1603,27 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor> flash_bwd(const at::Tensor& d_o, 
     C10_CUDA_KERNEL_LAUNCH_CHECK();
   }
   return {dq, dk, dv};
+}
+
+// acc_o [T, H, 128] fp32 contiguous, acc_lse [H, T] fp32 (row stride arbitrary), o [T, H, 128] bf16 contiguous,
+// lse [H, T] fp32 (row stride arbitrary, e.g. the padded rows flash_fwd returns): merges (o, lse) into the pair.
+void attn_merge_(at::Tensor acc_o, at::Tensor acc_lse, const at::Tensor& o, const at::Tensor& lse) {
+  using namespace flash;
+  TORCH_CHECK(acc_o.is_cuda() && acc_o.scalar_type() == at::kFloat && acc_o.is_contiguous() && acc_o.dim() == 3 &&
+              acc_o.size(2) == kD, "attn_merge_: acc_o must be a contiguous fp32 [T, H, 128] tensor");
+  TORCH_CHECK(o.scalar_type() == at::kBFloat16 && o.is_contiguous() && o.sizes() == acc_o.sizes());
+  const int64_t T = acc_o.size(0), H = acc_o.size(1);
+  TORCH_CHECK(acc_lse.scalar_type() == at::kFloat && lse.scalar_type() == at::kFloat && acc_lse.dim() == 2 && lse.dim() == 2 &&
+              acc_lse.size(0) == H && acc_lse.size(1) == T && lse.size(0) == H && lse.size(1) == T &&
+              acc_lse.stride(1) == 1 && lse.stride(1) == 1);
+  if (T * H == 0) return;
+  c10::cuda::CUDAGuard guard(acc_o.device());
+  const int64_t warps = T * H;
+  const int threads = 256;
+  attn_merge_kernel<<<(unsigned)((warps * 32 + threads - 1) / threads), threads, 0, at::cuda::getCurrentCUDAStream()>>>(
+      acc_o.data_ptr<float>(), acc_lse.data_ptr<float>(), reinterpret_cast<const __nv_bfloat16*>(o.data_ptr()),
+      lse.data_ptr<float>(), (int)T, (int)H, (int)acc_lse.stride(0), (int)lse.stride(0));
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
 }
 
 int64_t flash_status(bool clear) {

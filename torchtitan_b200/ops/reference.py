@@ -170,6 +170,73 @@ def adamw_step(master: torch.Tensor, grad: torch.Tensor, exp_avg: torch.Tensor, 
 
 
 # -------------------------------------------------------------- attention
+def _block_mask(Tq: int, Tk: int, device, causal: bool, causal_offset: int, kv_first, window: int) -> torch.Tensor:
+    """The flash kernels' mask in local indices: row i sees keys max(kv_first[i], i + offset - window + 1) <= j <= i + offset."""
+    rows = torch.arange(Tq, device=device)[:, None]
+    cols = torch.arange(Tk, device=device)[None, :]
+    mask = torch.ones(Tq, Tk, dtype=torch.bool, device=device)
+    if causal:
+        mask &= cols <= rows + causal_offset
+    if kv_first is not None:
+        mask &= cols >= kv_first.long()[:, None]
+    if window:
+        mask &= cols > rows + causal_offset - window
+    return mask
+
+
+def block_attention_fwd(q, k, v, scale: float, causal: bool = True, causal_offset: int = 0, kv_first=None, window: int = 0):
+    """Dense-math counterpart of ``flash_fwd``: ``(o [Tq, Hq, D] in q's dtype, lse [Hq, Tq] fp32)``; rows that see no
+    key get ``o = 0`` and ``lse = -inf``."""
+    Tq, Hq, _ = q.shape
+    Tk, Hkv, _ = k.shape
+    rep = Hq // Hkv
+    qf = q.float().transpose(0, 1)
+    kf = k.float().transpose(0, 1).repeat_interleave(rep, dim=0)
+    vf = v.float().transpose(0, 1).repeat_interleave(rep, dim=0)
+    s = torch.matmul(qf, kf.transpose(1, 2)) * scale
+    mask = _block_mask(Tq, Tk, q.device, causal, causal_offset, kv_first, window)
+    s = s.masked_fill(~mask[None], float("-inf"))
+    lse = torch.logsumexp(s, dim=-1)
+    safe = torch.where(torch.isinf(lse), torch.zeros_like(lse), lse)
+    p = torch.where(mask[None], torch.exp(s - safe[..., None]), torch.zeros_like(s))
+    return torch.matmul(p, vf).transpose(0, 1).to(q.dtype), lse
+
+
+def block_attention_bwd(d_o, q, k, v, o, lse, scale: float, causal: bool = True, causal_offset: int = 0, kv_first=None,
+                        window: int = 0):
+    """Dense-math counterpart of ``flash_bwd``.  ``o`` and ``lse`` may be the *merged* result over several key
+    blocks: with ``P = exp(s - lse)`` and ``delta = rowsum(dO * O)`` the returned ``dq`` is this block's share
+    and ``dk`` / ``dv`` are exact for this block's keys."""
+    Tq, Hq, _ = q.shape
+    Tk, Hkv, _ = k.shape
+    rep = Hq // Hkv
+    qf = q.float().transpose(0, 1)
+    kf = k.float().transpose(0, 1).repeat_interleave(rep, dim=0)
+    vf = v.float().transpose(0, 1).repeat_interleave(rep, dim=0)
+    dof = d_o.float().transpose(0, 1)
+    s = torch.matmul(qf, kf.transpose(1, 2)) * scale
+    mask = _block_mask(Tq, Tk, q.device, causal, causal_offset, kv_first, window)
+    safe = torch.where(torch.isinf(lse), torch.zeros_like(lse), lse)
+    p = torch.where(mask[None], torch.exp(s - safe[..., None]), torch.zeros_like(s))
+    delta = (d_o.float() * o.float()).sum(-1).transpose(0, 1)              # [Hq, Tq]
+    dp = torch.matmul(dof, vf.transpose(1, 2))
+    ds = p * (dp - delta[..., None]) * scale
+    dq = torch.matmul(ds, kf).transpose(0, 1)
+    dk = torch.matmul(ds.transpose(1, 2), qf).view(Hkv, rep, Tk, -1).sum(1).transpose(0, 1)
+    dv = torch.matmul(p.transpose(1, 2), dof).view(Hkv, rep, Tk, -1).sum(1).transpose(0, 1)
+    return dq.to(q.dtype), dk.to(k.dtype), dv.to(v.dtype)
+
+
+def attention_merge_(acc_o: torch.Tensor, acc_lse: torch.Tensor, o: torch.Tensor, lse: torch.Tensor) -> None:
+    """In place: fold one block's normalised output ``o [T, H, D]`` / ``lse [H, T]`` into the fp32 running pair."""
+    new = torch.logaddexp(acc_lse, lse)
+    safe = torch.where(torch.isinf(new), torch.zeros_like(new), new)
+    wa = torch.where(torch.isinf(acc_lse), torch.zeros_like(new), torch.exp(acc_lse - safe)).transpose(0, 1)[..., None]
+    wb = torch.where(torch.isinf(lse), torch.zeros_like(new), torch.exp(lse - safe)).transpose(0, 1)[..., None]
+    acc_o.mul_(wa).add_(o.float() * wb)
+    acc_lse.copy_(new)
+
+
 def attention_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, scale: float, causal: bool = True,
                   doc_ids: torch.Tensor | None = None, window: int | None = None,
                   q_pos: torch.Tensor | None = None, k_pos: torch.Tensor | None = None,
