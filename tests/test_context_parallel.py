@@ -6,7 +6,7 @@ import torch
 from tests.dist_utils import run_distributed
 
 
-def _cp_fn(rank, world, mode, with_docs, out_path):
+def _cp_fn(rank, world, mode, with_docs, out_path, window=None, use_sinks=False):
     import torch.distributed as dist
 
     from torchtitan_b200.models.common.attention import AttentionContext
@@ -21,16 +21,22 @@ def _cp_fn(rank, world, mode, with_docs, out_path):
     if with_docs:
         doc = torch.tensor([1] * 10 + [2] * 15 + [3] * 7, dtype=torch.int32)
     qf, kf, vf = (t.clone().requires_grad_() for t in (q, k, v))
-    ref = OF.attention(qf, kf, vf, doc_ids=doc)
+    sinks_ref = torch.tensor([0.3, -0.5, 1.0, 0.0]).requires_grad_() if use_sinks else None
+    ref = OF.attention(qf, kf, vf, doc_ids=doc, window=window, sinks=sinks_ref)
     ref.backward(g)
 
     cp = CPContext(group=dist.group.WORLD, size=world, rank=rank, mode=mode)
     idx = shard_for_cp(cp, torch.arange(T), torch.arange(T), torch.arange(T))[3]
     ql, kl, vl = (t[idx].clone().requires_grad_() for t in (q, k, v))
     ctx = AttentionContext(doc_ids=None if doc is None else doc[idx], q_pos=idx, cp=cp)
-    out = cp_attention(ql, kl, vl, ctx)
+    sinks = sinks_ref.detach().clone().requires_grad_() if use_sinks else None
+    out = cp_attention(ql, kl, vl, ctx, window=window, sinks=sinks)
     out.backward(g[idx])
     ok = torch.allclose(out, ref[idx].detach(), atol=1e-5)
+    if use_sinks:
+        gs = sinks.grad.clone()
+        dist.all_reduce(gs)
+        ok = ok and torch.allclose(gs, sinks_ref.grad, atol=1e-5)
     ok = ok and torch.allclose(ql.grad, qf.grad[idx], atol=1e-5)
     ok = ok and torch.allclose(kl.grad, kf.grad[idx], atol=1e-5)
     ok = ok and torch.allclose(vl.grad, vf.grad[idx], atol=1e-5)
@@ -47,6 +53,13 @@ def _cp_fn(rank, world, mode, with_docs, out_path):
 def test_cp_attention_matches_full(tmp_path, mode, with_docs):
     out = str(tmp_path / "cp.pt")
     run_distributed(_cp_fn, 2, mode, with_docs, out)
+    assert float(torch.load(out)) == 1.0
+
+
+@pytest.mark.parametrize("mode", ["allgather", "ring"])
+def test_cp_attention_window_documents_and_sinks(tmp_path, mode):
+    out = str(tmp_path / "cpw.pt")
+    run_distributed(_cp_fn, 2, mode, True, out, 6, True)
     assert float(torch.load(out)) == 1.0
 
 

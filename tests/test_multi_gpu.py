@@ -430,3 +430,106 @@ def test_context_parallel_nvlink_exchange(tmp_path):
     out = str(tmp_path / "cp.pt")
     run_distributed(_cp_nvlink, 2, out, backend="nccl")
     assert torch.load(out)["ok"] == 1
+
+
+def _cp_flash(rank, world, mode, transport, out_path):
+    """Context-parallel attention on the flash kernels (blocks with offsets, LSE merge) against the same
+    kernels run on the whole sequence by one GPU: packed documents, a sliding window and sinks included."""
+    import torch.distributed as dist
+
+    from torchtitan_b200.models.common.attention import AttentionContext
+    from torchtitan_b200.ops import functional as OF
+    from torchtitan_b200.parallel.context_parallel import CPContext, cp_attention, shard_for_cp
+
+    dev = torch.device("cuda", rank)
+    T, Hq, Hkv, D = 2048, 4, 2, 128
+    g = torch.Generator(device=dev).manual_seed(5)
+    q = torch.randn(T, Hq, D, device=dev, generator=g).bfloat16()
+    k = torch.randn(T, Hkv, D, device=dev, generator=g).bfloat16()
+    v = torch.randn(T, Hkv, D, device=dev, generator=g).bfloat16()
+    d_o = torch.randn(T, Hq, D, device=dev, generator=g).bfloat16()
+    starts = torch.tensor([0, 300, 301, 1100, 1900], device=dev)
+    pos = torch.arange(T, device=dev)
+    doc_start = starts[torch.searchsorted(starts, pos, right=True) - 1]
+    errs = []
+    cp = CPContext(group=dist.group.WORLD, size=world, rank=rank, mode=mode)
+    if transport == "nvlink":
+        from torchtitan_b200.parallel.cp_nvlink import CPNvlink
+
+        cp.nvlink = CPNvlink(dist.group.WORLD, dev, nbytes=16 << 20)
+    idx = shard_for_cp(cp, pos, pos, pos)[3]
+    for docs, window, use_sinks in ((False, None, False), (True, None, False), (True, 256, True)):
+        kv_first = doc_start.int() if docs else None
+        sinks_ref = torch.linspace(-1, 1, Hq, device=dev).requires_grad_() if use_sinks else None
+        qf, kf, vf = (t.clone().requires_grad_() for t in (q, k, v))
+        ref = OF.attention(qf, kf, vf, causal=True, kv_first=kv_first, doc_ids=None if not docs else doc_start,
+                           window=window, sinks=sinks_ref)
+        ref.backward(d_o)
+        ql, kl, vl = (t[idx].clone().requires_grad_() for t in (q, k, v))
+        ctx = AttentionContext(doc_ids=None if not docs else doc_start[idx].int(), q_pos=idx, cp=cp,
+                               kv_first=None if not docs else doc_start[idx].int())
+        sinks = sinks_ref.detach().clone().requires_grad_() if use_sinks else None
+        out = cp_attention(ql, kl, vl, ctx, window=window, sinks=sinks)
+        out.backward(d_o[idx])
+        for got, want in ((out, ref[idx]), (ql.grad, qf.grad[idx]), (kl.grad, kf.grad[idx]), (vl.grad, vf.grad[idx])):
+            errs.append((got.float() - want.float()).abs().max().item() / (want.float().abs().max().item() + 1e-6))
+    torch.cuda.synchronize()
+    st = int(torch.ops.tb200.flash_status(True))
+    if cp.nvlink is not None:
+        st |= int(cp.nvlink.arena.status.item())
+    t = torch.tensor(errs + [float(st), float(OF.settings.library_fallbacks)], device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    if rank == 0:
+        torch.save(t.cpu(), out_path)
+
+
+@pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
+@pytest.mark.parametrize("mode,transport", [("allgather", "nccl"), ("ring", "nccl"), ("allgather", "nvlink")])
+def test_context_parallel_attention_on_flash_kernels(tmp_path, mode, transport):
+    out = str(tmp_path / "cpf.pt")
+    run_distributed(_cp_flash, 2, mode, transport, out, backend="nccl")
+    r = torch.load(out)
+    assert r[-2] == 0, "a bounded wait expired"
+    assert r[-1] == 0, "attention left the flash kernels"
+    assert (r[:-2] < 3e-2).all(), r
+
+
+def _graph_train(rank, world, graphs, out_path, folder):
+    """A few trainer steps on 2 GPUs over the NVLink FSDP path, forward + backward eager or replayed from a
+    CUDA graph (the flag barriers inside the graph must publish a fresh epoch on every replay)."""
+    from torchtitan_b200.config import ConfigManager
+
+    args = ["--module", "llama3", "--config", "llama3_debugmodel", "--training.steps", "6",
+            "--training.num_tokens_per_microbatch_per_dp_rank", "512", "--training.max_context_length", "256",
+            "--debug.seed", "0", "--dump_folder", folder, "--debug.no-enable_structured_logging",
+            "--checkpoint.no-enable", "--metrics.log_freq", "1", "--parallelism.fsdp_comm", "nvlink"]
+    if graphs:
+        args += ["--training.no-disable_cuda_graphs"]
+    tr = ConfigManager().parse_args(args).build()
+    assert tr.engines[0]._symm is not None
+    losses = []
+    it = tr.batch_generator(tr.dataloader)
+    for _ in range(6):
+        tr.step += 1
+        tr.train_step(it)
+        losses.append(tr._last_loss.detach().float().reshape(1).clone())
+    if graphs:
+        assert tr._graph_runner is not None and len(tr._graph_runner._graphs) >= 1
+    t = torch.cat(losses)
+    import torch.distributed as dist
+
+    dist.all_reduce(t)
+    tr.engines[0].check_status()
+    if rank == 0:
+        torch.save(t.cpu(), out_path)
+    tr.close()
+
+
+@pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
+def test_cuda_graph_replay_over_nvlink_matches_eager(tmp_path):
+    a, b = str(tmp_path / "eager.pt"), str(tmp_path / "graph.pt")
+    run_distributed(_graph_train, 2, False, a, str(tmp_path / "e"), backend="nccl")
+    run_distributed(_graph_train, 2, True, b, str(tmp_path / "g"), backend="nccl")
+    ra, rb = torch.load(a), torch.load(b)
+    assert torch.allclose(ra, rb, atol=2e-2), (ra, rb)
+    assert rb[-1] < rb[0]

@@ -47,10 +47,10 @@ def build_attention_context(positions: torch.Tensor, *, assume_single_document: 
         return AttentionContext(None, q_pos, cp)
     starts = (positions == 0).to(torch.int32)
     doc_ids = torch.cumsum(starts, dim=0, dtype=torch.int32)
-    kv_first = None
-    if cp is None:
-        # a document starts where positions == 0, so token i's document starts at i - positions[i]
-        kv_first = (torch.arange(positions.shape[0], device=positions.device) - positions).to(torch.int32)
+    # a document starts where positions == 0, so token i's document starts at (global index of i) - positions[i];
+    # under context parallelism the rows are sharded and ``q_pos`` holds their global indices
+    index = q_pos if (cp is not None and q_pos is not None) else torch.arange(positions.shape[0], device=positions.device)
+    kv_first = (index - positions).to(torch.int32)
     return AttentionContext(doc_ids, q_pos, cp, kv_first=kv_first)
 
 

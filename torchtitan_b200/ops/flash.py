@@ -96,3 +96,52 @@ def flash_attention(q, k, v, scale: float, *, causal: bool = True, causal_offset
                     sinks: torch.Tensor | None = None) -> torch.Tensor:
     return flash_attention_lse(q, k, v, scale, causal=causal, causal_offset=causal_offset, kv_first=kv_first,
                                window=window, sinks=sinks)[0]
+
+
+# ---------------------------------------------------------------------------------------------
+# Block-level entry points without autograd: one query block against one key block, the pieces
+# that context-parallel attention merges.  CUDA tensors of a supported shape run the tcgen05
+# kernels, everything else the dense fp32 reference with the same local-index mask semantics.
+def _use_kernels(q, k, v) -> bool:
+    from . import functional as OF
+
+    return OF.settings.attention == "native" and supported(q, k, v)
+
+
+def block_fwd(q, k, v, scale: float, *, causal: bool = True, causal_offset: int = 0, kv_first=None, window: int = 0):
+    """``(o [Tq, Hq, D], lse [Hq, Tq] fp32)``; rows without a visible key give ``o = 0``, ``lse = -inf``."""
+    if _use_kernels(q, k, v):
+        from .functional import _count
+
+        _count()
+        return ext.require().flash_fwd(q, k, v, float(scale), bool(causal), int(causal_offset), kv_first, int(window), None)
+    from . import reference as ref
+
+    return ref.block_attention_fwd(q, k, v, scale, causal, causal_offset, kv_first, window)
+
+
+def block_bwd(d_o, q, k, v, o, lse, scale: float, *, causal: bool = True, causal_offset: int = 0, kv_first=None,
+              window: int = 0):
+    """Gradients of one block given the (possibly merged) output ``o`` and ``lse`` of the whole row."""
+    if _use_kernels(q, k, v):
+        from .functional import _count
+
+        _count(3)
+        return ext.require().flash_bwd(d_o.contiguous(), q, k, v, o.contiguous(), lse, float(scale), bool(causal),
+                                       int(causal_offset), kv_first, None, None, None, int(window))
+    from . import reference as ref
+
+    return ref.block_attention_bwd(d_o, q, k, v, o, lse, scale, causal, causal_offset, kv_first, window)
+
+
+def merge_(acc_o: torch.Tensor, acc_lse: torch.Tensor, o: torch.Tensor, lse: torch.Tensor) -> None:
+    """Fold a block's ``(o, lse)`` into the running fp32 pair ``acc_o [T, H, D]``, ``acc_lse [H, T]`` (in place)."""
+    if acc_o.is_cuda and o.dtype == torch.bfloat16 and o.shape[-1] == 128 and ext.available():
+        from .functional import _count
+
+        _count()
+        ext.require().attn_merge_(acc_o, acc_lse, o.contiguous(), lse)
+        return
+    from . import reference as ref
+
+    ref.attention_merge_(acc_o, acc_lse, o, lse)

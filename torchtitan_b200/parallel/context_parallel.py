@@ -6,14 +6,15 @@ Sharding.  The ``T`` tokens of a microbatch are cut into ``2*cp`` chunks; with t
 positions are sharded identically; RoPE uses the (sharded) positions, the causal /
 document mask uses the global token index ``q_pos`` of each local row.
 
-Exchange modes
+Exchange modes (both run every block on the flash-attention kernels, see ``_CPAttentionFn``)
 * ``allgather`` (the reference's scheme, decoder_sharding.py:263-302): K and V are
   all-gathered over cp (backward: reduce-scatter of dK, dV), re-ordered into sequence order,
   and each local query chunk attends to its causal prefix with a bottom-right aligned
-  causal mask.
-* ``ring``: K/V blocks travel around the cp ring (``batch_isend_irecv``) while each rank
-  accumulates blockwise attention with the online-softmax (max / log-sum-exp) merge; only
-  one remote block is resident at a time.  The output equals gathered-KV attention.
+  causal mask (offset), the documents' first-key index and the sliding window.
+* ``ring``: the K/V chunks of one rank at a time travel around the cp ring
+  (``batch_isend_irecv``); every (query chunk, key chunk) block is attention with an offset,
+  and the partial results are merged by their log-sum-exp (a small CUDA kernel); only one
+  remote block is resident at a time.  The output equals gathered-KV attention.
 """
 
 from __future__ import annotations
@@ -98,74 +99,161 @@ class _CPAllGather(torch.autograd.Function):
         return tp_ops.reduce_scatter_raw(rank_major, cp.group, cp.size), None
 
 
-def _prefix_attention(q, k, v, n_prefix: int, scale: float):
-    """One query chunk (the last ``Tq`` rows of the prefix) against ``k[:n_prefix]`` with a
-    bottom-right aligned causal mask."""
-    Tq = q.shape[0]
-    kk, vv = k[:n_prefix], v[:n_prefix]
-    if OF._native_attention_ok(q, kk, vv):
-        # tcgen05 flash kernel: query row i sees keys j <= i + (n_prefix - Tq)
-        from torchtitan_b200.ops.flash import flash_attention
-
-        OF._count(4)
-        return flash_attention(q, kk, vv, scale, causal=True, causal_offset=n_prefix - Tq)
-    if q.is_cuda:
-        from torch.nn.attention.bias import causal_lower_right
-
-        qh, kh, vh = (t.transpose(0, 1).unsqueeze(0) for t in (q, kk, vv))
-        out = F.scaled_dot_product_attention(qh, kh, vh, attn_mask=causal_lower_right(Tq, n_prefix), scale=scale,
-                                             enable_gqa=(q.shape[1] != k.shape[1]))
-        return out.squeeze(0).transpose(0, 1)
-    q_pos = torch.arange(n_prefix - Tq, n_prefix, device=q.device)
-    return OF._masked_attention(q, kk, vv, scale, True, None, None, None, q_pos, None)
+def _gather_sequence(x: torch.Tensor, cp: CPContext):
+    """All ranks' rows in sequence order, and the index that maps rank-major rows to it."""
+    if cp.nvlink is not None and x.is_cuda:
+        full = cp.nvlink.all_gather(x)
+    else:
+        full = tp_ops.all_gather_raw(x, cp.group, cp.size)
+    T = full.shape[0]
+    order = torch.cat([_local_index(cp, T, x.device, r) for r in range(cp.size)])
+    out = torch.empty_like(full)
+    out[order] = full
+    return out, order
 
 
-def _block_attention_lse(q, k, v, scale, q_pos, k_pos, q_doc, k_doc, window):
-    """Dense differentiable attention of a query block against one K/V block; returns the
-    un-normalised pieces needed for the online-softmax merge: ``(out, lse)`` with
-    ``lse = -inf`` for fully masked rows."""
-    Hq, Hkv = q.shape[1], k.shape[1]
-    rep = Hq // Hkv
-    qh = q.transpose(0, 1).float()
-    kh = k.transpose(0, 1).float()
-    vh = v.transpose(0, 1).float()
-    if rep > 1:
-        kh, vh = kh.repeat_interleave(rep, 0), vh.repeat_interleave(rep, 0)
-    s = torch.matmul(qh, kh.transpose(1, 2)) * scale
-    mask = q_pos[:, None] >= k_pos[None, :]
-    if window:
-        mask &= (q_pos[:, None] - k_pos[None, :]) < window
-    if q_doc is not None:
-        mask &= q_doc[:, None] == k_doc[None, :]
-    s = s.masked_fill(~mask[None], float("-inf"))
-    lse = torch.logsumexp(s, dim=-1)  # [H, Tq]
-    safe = torch.where(torch.isinf(lse), torch.zeros_like(lse), lse)
-    p = torch.exp(s - safe[..., None])
-    p = torch.where(mask[None], p, torch.zeros_like(p))
-    return torch.matmul(p, vh), lse  # out [H, Tq, D]
+def _scatter_sequence_grad(d_full: torch.Tensor, order: torch.Tensor, cp: CPContext, dtype) -> torch.Tensor:
+    """Sum a sequence-ordered gradient over the cp group and keep this rank's rows."""
+    rank_major = d_full.index_select(0, order).contiguous()
+    if cp.nvlink is not None and rank_major.is_cuda:
+        return cp.nvlink.reduce_scatter(rank_major.to(dtype)).to(dtype)
+    return tp_ops.reduce_scatter_raw(rank_major, cp.group, cp.size).to(dtype)
 
 
-def _merge(out_a, lse_a, out_b, lse_b):
-    lse = torch.logaddexp(lse_a, lse_b)
-    safe = torch.where(torch.isinf(lse), torch.zeros_like(lse), lse)
-    wa = torch.exp(lse_a - safe)[..., None]
-    wb = torch.exp(lse_b - safe)[..., None]
-    wa = torch.where(torch.isinf(lse_a)[..., None], torch.zeros_like(wa), wa)
-    wb = torch.where(torch.isinf(lse_b)[..., None], torch.zeros_like(wb), wb)
-    return out_a * wa + out_b * wb, lse
+def _apply_sinks(o32: torch.Tensor, lse: torch.Tensor, sinks: torch.Tensor):
+    """A sink logit per head joins the denominator: ``lse' = logaddexp(lse, sink)``, ``o' = o exp(lse - lse')``."""
+    lse2 = torch.logaddexp(lse, sinks.float()[:, None])
+    w = torch.where(torch.isinf(lse), torch.zeros_like(lse), torch.exp(lse - lse2))
+    return o32 * w.transpose(0, 1)[..., None], lse2
 
 
-class _RingExchange(torch.autograd.Function):
-    """Send ``x`` to the next rank of the ring and receive the previous rank's tensor."""
+class _CPAttentionFn(torch.autograd.Function):
+    """Context-parallel attention as a sum over (query chunk, key chunk) blocks.
+
+    The local queries are ``2`` chunks of ``C`` consecutive tokens (global chunk ids ``cp_chunk_ids``); keys
+    come in chunks of ``C`` consecutive tokens as well, so every block is plain causal attention with an offset:
+    query ``i`` of chunk ``c`` sees key ``j`` of chunk ``c'`` iff ``j <= i + (c - c') C``.  Documents shift the
+    per-row first visible key by ``c' C``; a sliding window keeps its meaning.  Blocks run on the flash kernels
+    (``ops.flash.block_fwd``) and are merged by their log-sum-exp; the backward runs the flash backward of
+    every block against the merged output and log-sum-exp, which is exact.
+
+    ``allgather``: K/V are gathered into sequence order once and each query chunk attends to its prefix in one
+    block (no merge).  ``ring``: the K/V chunks of one rank at a time travel around the ring together with their
+    gradient accumulators."""
 
     @staticmethod
-    def forward(ctx, x, cp):
-        ctx.cp = cp
-        return _ring_shift(x, cp, +1)
+    def forward(ctx, q, k, v, sinks, cp, scale, window, kv_first, mode):
+        from torchtitan_b200.ops import flash as FL
+
+        Tl, Hq, D = q.shape
+        C = Tl // 2
+        ids = cp_chunk_ids(cp)
+        window = int(window or 0)
+        o32 = torch.zeros(Tl, Hq, D, dtype=torch.float32, device=q.device)
+        lse = torch.full((Hq, Tl), float("-inf"), dtype=torch.float32, device=q.device)
+        saved_kv = None
+        if mode == "allgather":
+            kf, order = _gather_sequence(k, cp)
+            vf, _ = _gather_sequence(v, cp)
+            for j, c in enumerate(ids):
+                n = (c + 1) * C
+                o, l = FL.block_fwd(q[j * C:(j + 1) * C], kf[:n], vf[:n], scale, causal=True, causal_offset=c * C,
+                                    kv_first=None if kv_first is None else kv_first[j * C:(j + 1) * C].contiguous(),
+                                    window=window)
+                o32[j * C:(j + 1) * C] = o.float()
+                lse[:, j * C:(j + 1) * C] = l
+            saved_kv = (kf, vf, order)
+        else:
+            k_blk, v_blk = k.contiguous(), v.contiguous()
+            for step in range(cp.size):
+                src_ids = cp_chunk_ids(cp, (cp.rank - step) % cp.size)
+                _ring_blocks(FL.block_fwd, q, k_blk, v_blk, ids, src_ids, C, scale, window, kv_first,
+                             lambda j, o, l: FL.merge_(o32[j * C:(j + 1) * C], lse[:, j * C:(j + 1) * C], o, l))
+                if step + 1 < cp.size:
+                    k_blk, v_blk = _ring_shift(k_blk, cp, +1), _ring_shift(v_blk, cp, +1)
+        if sinks is not None:
+            o32, lse = _apply_sinks(o32, lse, sinks)
+        o = o32.to(q.dtype)
+        ctx.save_for_backward(q, k, v, o, lse, kv_first if kv_first is not None else torch.empty(0),
+                              sinks if sinks is not None else torch.empty(0), *(saved_kv or ()))
+        ctx.meta = (cp, scale, window, kv_first is not None, sinks is not None, mode)
+        return o
+
 
     @staticmethod
-    def backward(ctx, dy):
-        return _ring_shift(dy, ctx.cp, -1), None
+    def backward(ctx, d_o):
+        from torchtitan_b200.ops import flash as FL
+
+        cp, scale, window, has_first, has_sinks, mode = ctx.meta
+        q, k, v, o, lse, kv_first, sinks = ctx.saved_tensors[:7]
+        kv_first = kv_first if has_first else None
+        Tl, Hq, D = q.shape
+        C = Tl // 2
+        ids = cp_chunk_ids(cp)
+        d_o = d_o.contiguous()
+        dq = torch.zeros(Tl, Hq, D, dtype=torch.float32, device=q.device)
+        d_sinks = None
+        if has_sinks:
+            delta = (d_o.float() * o.float()).sum(-1)                                        # [Tl, Hq]
+            d_sinks = -(torch.exp(sinks.float()[None, :] - lse.t()) * delta).sum(0).to(sinks.dtype)
+
+        def chunk(t, j):
+            return t[j * C:(j + 1) * C]
+
+        if mode == "allgather":
+            kf, vf, order = ctx.saved_tensors[7:10]
+            dkf = torch.zeros(kf.shape, dtype=torch.float32, device=q.device)
+            dvf = torch.zeros(vf.shape, dtype=torch.float32, device=q.device)
+            for j, c in enumerate(ids):
+                n = (c + 1) * C
+                g = FL.block_bwd(chunk(d_o, j), chunk(q, j), kf[:n], vf[:n], chunk(o, j), lse[:, j * C:(j + 1) * C], scale,
+                                 causal=True, causal_offset=c * C,
+                                 kv_first=None if kv_first is None else chunk(kv_first, j).contiguous(), window=window)
+                dq[j * C:(j + 1) * C] = g[0].float()
+                dkf[:n] += g[1].float()
+                dvf[:n] += g[2].float()
+            dk = _scatter_sequence_grad(dkf, order, cp, k.dtype)
+            dv = _scatter_sequence_grad(dvf, order, cp, v.dtype)
+            return dq.to(q.dtype), dk, dv, d_sinks, None, None, None, None, None
+        # ring: the K/V chunks travel again, their gradient accumulators with them; one more hop brings
+        # every accumulator home
+        k_blk, v_blk = k.contiguous(), v.contiguous()
+        dk_acc = torch.zeros(k.shape, dtype=torch.float32, device=q.device)
+        dv_acc = torch.zeros(v.shape, dtype=torch.float32, device=q.device)
+        for step in range(cp.size):
+            src_ids = cp_chunk_ids(cp, (cp.rank - step) % cp.size)
+
+            for j, c in enumerate(ids):
+                for jj, c2 in enumerate(src_ids):
+                    if c2 > c:
+                        continue
+                    kvf = None
+                    if kv_first is not None:
+                        kvf = (chunk(kv_first, j) - c2 * C).clamp_(min=0).to(torch.int32).contiguous()
+                    g = FL.block_bwd(chunk(d_o, j), chunk(q, j), chunk(k_blk, jj), chunk(v_blk, jj), chunk(o, j),
+                                     lse[:, j * C:(j + 1) * C], scale, causal=True, causal_offset=(c - c2) * C,
+                                     kv_first=kvf, window=window)
+                    dq[j * C:(j + 1) * C] += g[0].float()
+                    dk_acc[jj * C:(jj + 1) * C] += g[1].float()
+                    dv_acc[jj * C:(jj + 1) * C] += g[2].float()
+            if step + 1 < cp.size:
+                k_blk, v_blk = _ring_shift(k_blk, cp, +1), _ring_shift(v_blk, cp, +1)
+            dk_acc, dv_acc = _ring_shift(dk_acc, cp, +1), _ring_shift(dv_acc, cp, +1)
+        return dq.to(q.dtype), dk_acc.to(k.dtype), dv_acc.to(v.dtype), d_sinks, None, None, None, None, None
+
+
+def _ring_blocks(block_fwd, q, k_blk, v_blk, ids, src_ids, C, scale, window, kv_first, sink):
+    """Forward of every visible (local query chunk, held key chunk) block; ``sink(j, o, lse)`` merges it."""
+    for j, c in enumerate(ids):
+        for jj, c2 in enumerate(src_ids):
+            if c2 > c:            # keys of a later chunk: nothing visible
+                continue
+            kvf = None
+            if kv_first is not None:
+                kvf = (kv_first[j * C:(j + 1) * C] - c2 * C).clamp_(min=0).to(torch.int32).contiguous()
+            o, l = block_fwd(q[j * C:(j + 1) * C], k_blk[jj * C:(jj + 1) * C], v_blk[jj * C:(jj + 1) * C], scale,
+                             causal=True, causal_offset=(c - c2) * C, kv_first=kvf, window=window)
+            sink(j, o, l)
 
 
 def _ring_shift(x, cp: CPContext, direction: int):
@@ -180,47 +268,27 @@ def _ring_shift(x, cp: CPContext, direction: int):
     return out
 
 
+def _global_kv_first(cp: CPContext, ctx, T: int, device) -> torch.Tensor | None:
+    """Global index of the first token of each local query's document (``None`` = one document)."""
+    if getattr(ctx, "kv_first", None) is not None:
+        return ctx.kv_first.to(torch.int32)
+    if ctx.doc_ids is None:
+        return None
+    # document ids are non-decreasing along the sequence: the first position holding a query's id
+    full = unshard_from_cp(cp, ctx.doc_ids.contiguous())
+    return torch.searchsorted(full.contiguous(), ctx.doc_ids.contiguous(), right=False).to(torch.int32)
+
+
 def cp_attention(q, k, v, ctx, *, scale: float | None = None, window: int | None = None, sinks=None):
-    """Attention of the local queries against the keys/values of the whole cp group."""
+    """Attention of the local queries against the keys/values of the whole cp group (causal; packed documents,
+    sliding window and attention sinks supported in both exchange modes)."""
     cp: CPContext = ctx.cp
     if scale is None:
         scale = 1.0 / math.sqrt(q.shape[-1])
-    if sinks is not None:
-        raise NotImplementedError("attention sinks are not supported under context parallelism")
     Tl = q.shape[0]
-    T = Tl * cp.size
-    C = T // (2 * cp.size)
-    q_pos = ctx.q_pos if ctx.q_pos is not None else _local_index(cp, T, q.device)
-    plain = ctx.doc_ids is None and not window and cp.load_balancer == "headtail"
-
-    if cp.mode == "allgather":
-        kf = _CPAllGather.apply(k, cp)
-        vf = _CPAllGather.apply(v, cp)
-        if plain:
-            outs = []
-            for j, c in enumerate(cp_chunk_ids(cp)):
-                outs.append(_prefix_attention(q[j * C:(j + 1) * C], kf, vf, (c + 1) * C, scale))
-            return torch.cat(outs, dim=0)
-        k_doc = None
-        if ctx.doc_ids is not None:
-            k_doc = unshard_from_cp(cp, ctx.doc_ids)
-        k_pos = torch.arange(T, device=q.device)
-        doc = None if k_doc is None else (ctx.doc_ids, k_doc)
-        return OF._masked_attention(q, kf, vf, scale, True, doc, window, None, q_pos, k_pos)
-
-    # ---- ring: blockwise accumulation while K/V circulate -------------------------------
-    k_blk, v_blk = k, v
-    pos_blk = q_pos
-    doc_blk = ctx.doc_ids
-    out = lse = None
-    for step in range(cp.size):
-        o, l = _block_attention_lse(q, k_blk, v_blk, scale, q_pos, pos_blk, ctx.doc_ids, doc_blk, window)
-        out, lse = (o, l) if out is None else _merge(out, lse, o, l)
-        if step + 1 < cp.size:
-            k_blk = _RingExchange.apply(k_blk, cp)
-            v_blk = _RingExchange.apply(v_blk, cp)
-            with torch.no_grad():
-                pos_blk = _ring_shift(pos_blk, cp, +1)
-                if doc_blk is not None:
-                    doc_blk = _ring_shift(doc_blk, cp, +1)
-    return out.transpose(0, 1).to(q.dtype)
+    if Tl % 2:
+        raise ValueError("context parallelism needs an even number of local tokens (two chunks per rank)")
+    with torch.no_grad():
+        kv_first = _global_kv_first(cp, ctx, Tl * cp.size, q.device)
+    mode = "allgather" if cp.mode == "allgather" else "ring"
+    return _CPAttentionFn.apply(q, k, v, sinks, cp, float(scale), window, kv_first, mode)
