@@ -63,3 +63,50 @@ def test_router_kernel_matches_reference_selection():
         assert torch.equal(sel.long().sort(dim=-1).values, rsel.sort(dim=-1).values)
         assert torch.equal(counts, rcounts)
         assert torch.allclose(top.sort(dim=-1).values, rtop.sort(dim=-1).values, atol=1e-5, rtol=1e-4)
+
+
+def _layout_reference(selected, all_counts, me, align=128):
+    """The expert-parallel layout in plain tensor ops: rows of an expert start at a multiple of ``align``,
+    lower source ranks first, token order inside a source rank."""
+    n, E = all_counts.shape
+    El = E // n
+    T, K = selected.shape
+    tot = all_counts.sum(0)
+    padded = ((tot + align - 1) // align * align).view(n, El)
+    offs = torch.zeros(n, El + 1, dtype=torch.int64)
+    offs[:, 1:] = torch.cumsum(padded, 1)
+    base = offs[:, :-1].reshape(-1) + all_counts[:me].sum(0)
+    flat = selected.reshape(-1).long()
+    order = torch.argsort(flat, stable=True)
+    e_sorted = flat[order]
+    c = all_counts[me]
+    start = torch.cumsum(c, 0) - c
+    pos = torch.arange(T * K) - start[e_sorted]
+    dest_row = torch.empty(T * K, dtype=torch.int64)
+    dest_row[order] = base[e_sorted] + pos
+    return (flat // El).view(T, K), dest_row.view(T, K), offs[me], tot.view(n, El)[me]
+
+
+def test_ep_layout_kernel_matches_reference():
+    """Device-side layout of two emulated ranks (the count table is filled by hand) against tensor ops."""
+    ops = ext.require()
+    torch.manual_seed(3)
+    n, E, T, K = 2, 16, 3000, 4
+    sels = [torch.stack([torch.randperm(E)[:K] for _ in range(T)]).int() for _ in range(n)]
+    all_counts = torch.stack([torch.bincount(s.reshape(-1).long(), minlength=E) for s in sels])
+    table = all_counts.int().cuda()
+    for me in range(n):
+        status = torch.zeros(1, dtype=torch.int32, device="cuda")
+        got = ops.ep_layout(sels[me].cuda(), table, me, 1 << 20, 128, status)
+        want = _layout_reference(sels[me], all_counts, me)
+        torch.cuda.synchronize()
+        assert int(status.item()) == 0
+        for g, w in zip(got, want):
+            assert torch.equal(g.cpu().long(), w.long())
+    # a capacity that is too small: the slots that do not fit are dropped (row -1) and the status word says so
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    cap = 4096
+    dest_rank, dest_row, my_offs, _ = ops.ep_layout(sels[0].cuda(), table, 0, cap, 128, status)
+    torch.cuda.synchronize()
+    assert int(status.item()) & 8
+    assert int(dest_row.max()) < cap and int((dest_row < 0).sum()) > 0 and int(my_offs[-1]) <= cap

@@ -64,6 +64,10 @@ std::tuple<at::Tensor, at::Tensor> ep_gather_rows(at::IntArrayRef peer_ptrs, con
                                                   const at::Tensor& dest_row, const c10::optional<at::Tensor>& wts,
                                                   int64_t D, bool keep_rows, const at::Tensor& like);
 void moe_zero_pad_rows(at::Tensor buf, const at::Tensor& offs, const at::Tensor& counts);
+void ep_publish_counts(const at::Tensor& counts, at::IntArrayRef table_ptrs, int64_t my_rank);
+std::tuple<at::Tensor, at::Tensor, at::Tensor, at::Tensor> ep_layout(const at::Tensor& selected, const at::Tensor& table,
+                                                                     int64_t my_rank, int64_t cap, int64_t align,
+                                                                     at::Tensor status);
 at::Tensor moe_slot_dot(const at::Tensor& dout, const at::Tensor& rows, int64_t K);
 std::tuple<at::Tensor, at::Tensor> mxfp8_quantize(const at::Tensor& x, int64_t axis);
 at::Tensor mxfp8_fake_quant(const at::Tensor& x, int64_t axis);
@@ -114,6 +118,9 @@ TORCH_LIBRARY(tb200, m) {
   m.def("ep_gather_rows(int[] peer_ptrs, Tensor dest_rank, Tensor dest_row, Tensor? wts, int D, bool keep_rows, Tensor like) -> "
         "(Tensor, Tensor)", &tb200::ep_gather_rows);
   m.def("moe_zero_pad_rows(Tensor(a!) buf, Tensor offs, Tensor counts) -> ()", &tb200::moe_zero_pad_rows);
+  m.def("ep_publish_counts(Tensor counts, int[] table_ptrs, int my_rank) -> ()", &tb200::ep_publish_counts);
+  m.def("ep_layout(Tensor selected, Tensor table, int my_rank, int cap, int align, Tensor(a!) status) -> "
+        "(Tensor, Tensor, Tensor, Tensor)", &tb200::ep_layout);
   m.def("moe_slot_dot(Tensor dout, Tensor rows, int K) -> Tensor", &tb200::moe_slot_dot);
   m.def("mxfp8_quantize(Tensor x, int axis) -> (Tensor, Tensor)", &tb200::mxfp8_quantize);
   m.def("mxfp8_fake_quant(Tensor x, int axis) -> Tensor", &tb200::mxfp8_fake_quant);

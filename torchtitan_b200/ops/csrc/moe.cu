@@ -527,4 +527,146 @@ at::Tensor moe_slot_dot(const at::Tensor& dout, const at::Tensor& rows, int64_t 
   return dw;
 }
 
+// ---------------------------------------------------------------------------------------------
+// Expert-parallel layout, entirely on the device (no host read, no library collective).
+//
+// ep_publish_counts: every rank stores its per-expert token counts into row `my_rank` of the
+// symmetric count table of every peer (plain peer stores).  After a flag barrier each rank holds
+// the full table counts[n_ranks][E].
+//
+// ep_layout: from that table each rank derives, for every routing slot (token t, choice k), the rank
+// that hosts the chosen expert and the row of that rank's receive buffer reserved for the slot.  The
+// receive buffer is expert-major; the rows of one expert start at a multiple of `align`, rows of lower
+// source ranks come first, and within a source rank the slots keep token order (stable, hence
+// deterministic).  One block per expert: it recomputes the prefix of padded group sizes of the owner
+// rank, then walks over all slots in order with a block-wide exclusive scan of "slot chose this
+// expert".  A slot whose row would fall outside the static capacity gets row -1 (the scatter / gather
+// kernels skip it) and kStatusEpOverflow is set in the status word.
+constexpr int kLayoutThreads = 1024;
+constexpr int kLayoutPerThread = 8;
+constexpr int kStatusEpOverflow = 1 << 3;
+
+__global__ void ep_publish_counts_kernel(const float* __restrict__ counts, EpPeers tables, int n_ranks, int my_rank, int E) {
+  for (int i = threadIdx.x; i < n_ranks * E; i += blockDim.x) {
+    const int q = i / E, e = i % E;
+    reinterpret_cast<int*>(tables.p[q])[my_rank * E + e] = (int)counts[e];
+  }
+}
+
+__global__ void __launch_bounds__(kLayoutThreads)
+ep_layout_kernel(const int* __restrict__ selected, const int* __restrict__ table, int n_ranks, int my_rank, int E,
+                 int64_t slots, int cap, int align, int* __restrict__ dest_rank, int* __restrict__ dest_row,
+                 int* __restrict__ my_offs, int* __restrict__ my_counts, int* __restrict__ status) {
+  const int e = blockIdx.x;
+  const int El = E / n_ranks;
+  const int owner = e / El, e_loc = e % El;
+  __shared__ int s_warp[kLayoutThreads / 32];
+  __shared__ int s_base, s_running, s_limit;
+  if (threadIdx.x == 0) {
+    // first row of expert e in the owner's buffer, then the rows of lower source ranks
+    int start = 0;
+    for (int j = 0; j < e_loc; ++j) {
+      int tot = 0;
+      for (int r = 0; r < n_ranks; ++r) tot += table[r * E + owner * El + j];
+      start += (tot + align - 1) / align * align;
+    }
+    int before = 0;
+    for (int r = 0; r < my_rank; ++r) before += table[r * E + e];
+    s_base = start + before;
+    s_running = 0;
+    s_limit = cap;
+    if (owner == my_rank) {
+      int tot = 0;
+      for (int r = 0; r < n_ranks; ++r) tot += table[r * E + e];
+      my_offs[e_loc] = start;
+      my_counts[e_loc] = tot;
+      if (e_loc == El - 1) {
+        const int end = start + (tot + align - 1) / align * align;
+        my_offs[El] = min(end, cap / align * align);
+        if (end > cap) atomicOr(status, kStatusEpOverflow);
+      }
+    }
+  }
+  __syncthreads();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  for (int64_t chunk = 0; chunk < slots; chunk += (int64_t)kLayoutThreads * kLayoutPerThread) {
+    const int64_t i0 = chunk + (int64_t)threadIdx.x * kLayoutPerThread;
+    int hit[kLayoutPerThread];
+    int mine = 0;
+#pragma unroll
+    for (int u = 0; u < kLayoutPerThread; ++u) {
+      hit[u] = (i0 + u < slots && selected[i0 + u] == e) ? 1 : 0;
+      mine += hit[u];
+    }
+    // exclusive scan of `mine` over the block
+    int incl = mine;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int v = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += v;
+    }
+    if (lane == 31) s_warp[warp] = incl;
+    __syncthreads();
+    if (warp == 0) {
+      int w = s_warp[lane];
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int v = __shfl_up_sync(0xffffffffu, w, o);
+        if (lane >= o) w += v;
+      }
+      s_warp[lane] = w;   // inclusive scan of the warp totals
+    }
+    __syncthreads();
+    const int running = s_running;
+    int pos = s_base + running + (warp > 0 ? s_warp[warp - 1] : 0) + incl - mine;
+#pragma unroll
+    for (int u = 0; u < kLayoutPerThread; ++u) {
+      if (hit[u]) {
+        const bool fits = pos < s_limit;
+        dest_rank[i0 + u] = owner;
+        dest_row[i0 + u] = fits ? pos : -1;
+        if (!fits) atomicOr(status, kStatusEpOverflow);
+        ++pos;
+      }
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) s_running = running + s_warp[kLayoutThreads / 32 - 1];
+    __syncthreads();
+  }
+}
+
+void ep_publish_counts(const at::Tensor& counts, at::IntArrayRef table_ptrs, int64_t my_rank) {
+  TORCH_CHECK(counts.is_cuda() && counts.scalar_type() == at::kFloat && counts.is_contiguous());
+  c10::cuda::CUDAGuard guard(counts.device());
+  const EpPeers pp = make_ep_peers(table_ptrs);
+  ep_publish_counts_kernel<<<1, 256, 0, at::cuda::getCurrentCUDAStream()>>>(counts.data_ptr<float>(), pp, (int)table_ptrs.size(),
+                                                                             (int)my_rank, (int)counts.numel());
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+}
+
+// selected [T, K] int32, table [n_ranks, E] int32 (this rank's copy) -> (dest_rank [T, K], dest_row [T, K],
+// my_offs [E / n_ranks + 1], my_counts [E / n_ranks]); `status` collects kStatusEpOverflow.
+std::tuple<at::Tensor, at::Tensor, at::Tensor, at::Tensor> ep_layout(const at::Tensor& selected, const at::Tensor& table,
+                                                                     int64_t my_rank, int64_t cap, int64_t align,
+                                                                     at::Tensor status) {
+  TORCH_CHECK(selected.is_cuda() && selected.scalar_type() == at::kInt && selected.is_contiguous() && selected.dim() == 2);
+  TORCH_CHECK(table.is_cuda() && table.scalar_type() == at::kInt && table.is_contiguous() && table.dim() == 2);
+  TORCH_CHECK(status.is_cuda() && status.scalar_type() == at::kInt && status.numel() >= 1);
+  const int n = (int)table.size(0), E = (int)table.size(1);
+  TORCH_CHECK(E % n == 0 && my_rank >= 0 && my_rank < n && align > 0 && cap >= align);
+  c10::cuda::CUDAGuard guard(selected.device());
+  auto iopt = selected.options();
+  auto dest_rank = at::empty_like(selected);
+  auto dest_row = at::empty_like(selected);
+  auto my_offs = at::zeros({E / n + 1}, iopt);
+  auto my_counts = at::zeros({E / n}, iopt);
+  if (selected.numel() > 0 || true)
+    ep_layout_kernel<<<E, kLayoutThreads, 0, at::cuda::getCurrentCUDAStream()>>>(
+        selected.data_ptr<int>(), table.data_ptr<int>(), n, (int)my_rank, E, selected.numel(), (int)cap, (int)align,
+        dest_rank.data_ptr<int>(), dest_row.data_ptr<int>(), my_offs.data_ptr<int>(), my_counts.data_ptr<int>(),
+        status.data_ptr<int>());
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+  return {dest_rank, dest_row, my_offs, my_counts};
+}
+
 }  // namespace tb200

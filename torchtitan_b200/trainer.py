@@ -257,7 +257,7 @@ class Trainer(Configurable):
         self._mb_index = 0
         if (not c.training.disable_cuda_graphs and self.device.type == "cuda" and not pd.pp_enabled
                 and not c.activation_checkpoint.cpu_offload   # host copies cannot be captured
-                and not pd.ep_enabled):   # both expert-parallel dispatchers read split sizes on the host
+                and not (pd.ep_enabled and c.parallelism.ep_comm == "nccl")):   # the all-to-all dispatcher reads split sizes on the host
             from torchtitan_b200.parallel.cudagraph import CUDAGraphRunner
 
             eng = self.engines[0]
