@@ -110,6 +110,7 @@ class FlatUnit:
         self.pool: "_SlotPool | None" = None
         self.slot = 0
         self.gather_dst: torch.Tensor | None = None    # alias of flat_param with its own version counter
+        self.private_grad = False                      # gradients in an own buffer instead of a rotating slot
 
     # shard geometry -----------------------------------------------------
     @property
@@ -276,7 +277,18 @@ class ShardedModel:
             if u.pool is not None:
                 u.flat_param = _alias(u.pool.param[u.slot], u.padded)
                 u.gather_dst = _alias(u.pool.param[u.slot], u.padded)
-                u.flat_grad = _alias(u.pool.grad[u.slot], u.padded)
+                if u is self._order[0]:
+                    # The first unit in execution order (the embedding on a first stage) may have no input that
+                    # carries a gradient, so the end of its backward is only known when the whole backward has
+                    # finished; its gradients get a buffer of their own instead of a rotating slot.
+                    if use_symm:
+                        u.flat_grad = self._symm.alloc(u.padded, pd, u.group, tag=f"{u.name}.grad")
+                        u.flat_grad.zero_()
+                    else:
+                        u.flat_grad = torch.zeros(u.padded, dtype=pd, device=dev)
+                    u.private_grad = True
+                else:
+                    u.flat_grad = _alias(u.pool.grad[u.slot], u.padded)
                 if use_symm:
                     u.param_shard = self._symm.alloc(u.shard_numel, pd, u.group, tag=f"{u.name}.param_shard")
                     u.param_shard.zero_()
@@ -343,6 +355,10 @@ class ShardedModel:
                         arena.reserve(u.group, 2 * u.padded * es)
             for key, n in biggest.items():
                 arena.reserve(groups[key], 2 * n * es + 1024)
+            if self.sharded_params:
+                first = next((u for u in self.units if u.size > 1), None)
+                if first is not None:   # the first unit's own gradient buffer
+                    arena.reserve(first.group, first.padded * es)
             for g in groups.values():
                 arena._arena(g)
             self._symm = arena
@@ -459,6 +475,11 @@ class ShardedModel:
         if u.pool is None:
             return
         self._acquire(u)
+        ev = u.pool.grad_free[u.slot]
+        if ev is not None:
+            # the fused loss writes the output unit's weight gradients during the forward: the last reduce-scatter
+            # out of this gradient slot (an earlier microbatch) must be over
+            torch.cuda.current_stream(self.device).wait_event(ev)
         if self._in_backward:      # a recomputed forward inside backward: the backward order prefetches
             return
         nxt = self._neighbour(u, +1)
@@ -489,7 +510,9 @@ class ShardedModel:
 
     def _on_unit_backward_done(self, unit: FlatUnit) -> None:
         self._collect_autograd_grads(unit)
-        if not self.defer_reduce:
+        # sharded layout: the gradient slot is reused by the unit after next, so every microbatch is reduced into
+        # the fp32 shard at once, also on pipeline stages (which otherwise keep local gradients until the flush)
+        if not self.defer_reduce or (unit.pool is not None and not unit.private_grad):
             self._launch_reduce(unit)
 
     def _collect_autograd_grads(self, unit: FlatUnit) -> None:
@@ -522,12 +545,14 @@ class ShardedModel:
             cs.wait_stream(torch.cuda.current_stream(self.device))
             with torch.cuda.stream(cs):
                 self._reduce_unit(unit)
-                if unit.pool is not None:
+                if unit.pool is not None and not unit.private_grad:
                     ev = torch.cuda.Event()
                     ev.record(cs)
                     unit.pool.grad_free[unit.slot] = ev
         else:
             self._reduce_unit(unit)
+        if unit.pool is not None and not unit.private_grad and self.defer_reduce:
+            unit.pending = False     # the next microbatch of this pipeline step reduces again
 
     @torch.no_grad()
     def _reduce_unit(self, u: FlatUnit) -> None:
