@@ -42,19 +42,47 @@ def parse_args():
     p.add_argument("--steps", type=int, default=5)
     p.add_argument("--warmup", type=int, default=3)
     p.add_argument("--impl", default="native", choices=["native", "reference"])
-    p.add_argument("--model", default="llama3")
-    p.add_argument("--flavor", default="8B")
-    p.add_argument("--seq-len", type=int, default=8192)
-    p.add_argument("--local-batch", type=int, default=1)
+    p.add_argument("--model", default=None)           # explicit values win over the preset's
+    p.add_argument("--flavor", default=None)
+    p.add_argument("--seq-len", type=int, default=None)
+    p.add_argument("--local-batch", type=int, default=None)
     p.add_argument("--fsdp-comm", default=os.environ.get("TB200_FSDP_COMM", "auto"))
     p.add_argument("--gemm", default=os.environ.get("TB200_GEMM", "tcgen05"))
     p.add_argument("--attention", default=os.environ.get("TB200_ATTENTION", "native"))
-    p.add_argument("--opt-state", default="fp32", choices=["fp32", "bf16"])
-    p.add_argument("--ac", default="selective")
+    p.add_argument("--opt-state", default=None, choices=["fp32", "bf16"])
+    p.add_argument("--ac", default=None)
     p.add_argument("--skip-e2e", action="store_true")
-    p.add_argument("--converters", default="", help="comma-separated model converters, e.g. mxfp8 (a separate, "
+    p.add_argument("--converters", default=None, help="comma-separated model converters, e.g. mxfp8 (a separate, "
                    "lower-precision measurement: the headline stays bf16)")
+    p.add_argument("--preset", default="fsdp", choices=sorted(PRESETS),
+                   help="fsdp = the headline (Llama-3 8B, FSDP over all ranks); the others are the multi-dimensional "
+                        "configurations listed in PRESETS")
+    p.add_argument("--comm", default="default", choices=["default", "nvlink", "nccl"],
+                   help="nvlink / nccl switch every collective path of the preset together (FSDP, TP, CP, EP) between the "
+                        "in-kernel NVLink transport and the NCCL arm; default keeps each path's default")
+    p.add_argument("--reshard", default=None, choices=["default", "always", "never"],
+                   help="parallelism.fsdp_reshard_after_forward")
+    p.add_argument("--par", action="append", default=[], metavar="KEY=VALUE",
+                   help="override one field of the parallelism section (repeatable), e.g. --par tensor_parallel_degree=1")
     return p.parse_args()
+
+
+# Multi-dimensional benchmark configurations (8 GPUs unless noted).  Each entry: model, flavor, sequence length,
+# sequences per microbatch, parallelism overrides, converters, optimizer state dtype, activation checkpointing.
+PRESETS = {
+    "fsdp": {},
+    # Llama-3.1 8B, FSDP x async TP 2 x CP 2, 32k tokens, MXFP8 linears
+    "3d_mxfp8_32k": dict(model="llama3", flavor="8B", seq_len=32768, local_batch=1, converters="mxfp8", ac="selective",
+                         par=dict(tensor_parallel_degree=2, context_parallel_degree=2)),
+    # Qwen3-30B-A3B-shaped MoE, expert parallel over all ranks, FSDP on the rest
+    "moe_ep8": dict(model="qwen3", flavor="30B-A3B", seq_len=4096, local_batch=2, ac="selective",
+                    par=dict(expert_parallel_degree=-1, ep_capacity_factor=2.0)),
+    # Llama-3.1 70B, PP 2 (interleaved 1F1B, two virtual stages per rank) x TP 2 x FSDP, bf16 optimizer states, full AC
+    "70b_pp2tp2": dict(model="llama3", flavor="70B", seq_len=8192, local_batch=1, opt_state="bf16", ac="full",
+                       par=dict(pipeline_parallel_degree=2, tensor_parallel_degree=2,
+                                pipeline_parallel_schedule="Interleaved1F1B", pipeline_parallel_layers_per_stage=20,
+                                num_pp_microbatches=8)),
+}
 
 
 class ClockSampler:
@@ -120,11 +148,47 @@ def reference_arm(args) -> None:
     spec.loader.exec_module(mod)
     if ROOT in sys.path:
         sys.path.remove(ROOT)  # nothing of this repo's package is importable on the reference path
+    if args.preset != "fsdp":
+        if int(os.environ.get("RANK", "0")) == 0:
+            print(json.dumps({"impl": "reference", "unavailable": "the reference arm covers the FSDP headline only; the image's "
+                              "torchtitan 0.1.0 has no counterpart wired for preset " + args.preset}), flush=True)
+        return
     mod.run(args, ROOT, ClockSampler)
+
+
+def apply_preset(args) -> dict:
+    """Fold the preset into ``args``; returns the parallelism overrides."""
+    pre = PRESETS[args.preset]
+    base = dict(model="llama3", flavor="8B", seq_len=8192, local_batch=1, opt_state="fp32", ac="selective")
+    for key, default in base.items():
+        if getattr(args, key) is None:
+            setattr(args, key, pre.get(key, default))
+    if args.converters is None:
+        args.converters = pre.get("converters", "")
+    par = dict(pre.get("par", {}))
+    if par.get("expert_parallel_degree") == -1:
+        par["expert_parallel_degree"] = args.gpus
+    if args.comm != "default":
+        par.update(fsdp_comm=args.comm, tp_comm=args.comm, cp_transport=args.comm, ep_comm=args.comm)
+    else:
+        par.setdefault("fsdp_comm", args.fsdp_comm)
+    if args.reshard is not None:
+        par["fsdp_reshard_after_forward"] = args.reshard
+    for item in args.par:
+        key, _, val = item.partition("=")
+        try:
+            par[key] = int(val)
+        except ValueError:
+            try:
+                par[key] = float(val)
+            except ValueError:
+                par[key] = val
+    return par
 
 
 def main() -> None:
     args = parse_args()
+    par_overrides = apply_preset(args)
     if args.impl == "reference":
         reference_arm(args)
         return
@@ -159,7 +223,7 @@ def main() -> None:
         lr_scheduler=LRSchedulersContainer.Config(warmup_steps=2),
         training=TrainingConfig(num_tokens_per_microbatch_per_dp_rank=T, max_context_length=args.seq_len,
                                 steps=steps_total, gc_freq=10 ** 6),
-        parallelism=ParallelismConfig(data_parallel_shard_degree=-1, fsdp_comm=args.fsdp_comm),
+        parallelism=ParallelismConfig(data_parallel_shard_degree=-1, **par_overrides),
         checkpoint=CheckpointManager.Config(enable=False),
         activation_checkpoint=ActivationCheckpointConfig(mode=args.ac),
         kernels=KernelConfig(gemm=args.gemm, attention=args.attention),
@@ -169,7 +233,12 @@ def main() -> None:
     if args.converters:
         cfg.model.converters = [c for c in args.converters.split(",") if c]
     trainer = cfg.build()
-    trainer.model.single_document = True
+    for part in trainer.model_parts:
+        part.single_document = True
+    pd = trainer.pdims
+    tokens_per_step = trainer.tokens_per_step_per_dp_rank * pd.dp_degree    # global tokens per optimizer step
+    tokens_per_rank_step = trainer.tokens_per_step_per_dp_rank              # host -> device per step on a data rank
+    layout = f"pp{pd.pp} dp_replicate{pd.dp_replicate} dp_shard{pd.dp_shard} cp{pd.cp} tp{pd.tp} ep{pd.ep}"
     dev = trainer.device
     mem = trainer.engines[0].memory_summary()
 
@@ -208,9 +277,9 @@ def main() -> None:
         barrier()
         wall = time.perf_counter() - t0
         e2e_s = max_over_ranks(max(wall, ev0.elapsed_time(ev1) / 1e3))
-        h2d = 3 * T * 8  # input ids, positions, labels: int64 each
+        h2d = 3 * tokens_per_rank_step * 8  # input ids, positions, labels: int64 each
         d2h = 4
-        e2e = {"value": T * world * args.steps / e2e_s, "unit": "tokens/s", "h2d_bytes_per_step": h2d,
+        e2e = {"value": tokens_per_step * args.steps / e2e_s, "unit": "tokens/s", "h2d_bytes_per_step": h2d,
                "d2h_bytes_per_step": d2h, "ms_per_step": 1e3 * e2e_s / args.steps, "last_loss": loss_host}
 
     # ------------------------------------------------------------ device-timed
@@ -249,7 +318,7 @@ def main() -> None:
     OF.settings.count_launches = False
     launches = OF.settings.launches
     dev_s = max_over_ranks(ev0.elapsed_time(ev1) / 1e3)
-    tokens_per_s = T * world * args.steps / dev_s
+    tokens_per_s = tokens_per_step * args.steps / dev_s
     peak = torch.cuda.max_memory_allocated(dev) / (1 << 30)
     flops_per_token = trainer.metrics_processor.num_flops_per_token
     loss_t = trainer._last_loss.detach().float().reshape(1).clone()
@@ -262,15 +331,19 @@ def main() -> None:
             "metric": "tokens_per_sec", "value": tokens_per_s, "unit": "tokens/s", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * dev_s / args.steps,
             "higher_is_better": True, "scaling": "weak",
-            "vs_baseline": tokens_per_s / world / BASELINE_TOKENS_PER_SEC_PER_GPU,
+            # the published number is the bf16 FSDP headline; other presets have no published counterpart
+            "vs_baseline": (tokens_per_s / world / BASELINE_TOKENS_PER_SEC_PER_GPU
+                            if args.preset == "fsdp" and not args.converters and args.flavor == "8B" else None),
             "dtype": "bf16" if not args.converters else f"{args.converters} linears, bf16 elsewhere",
             "data": "synthetic uniform-random tokens, random-init weights",
             "impl": "native",
             "tokens_per_sec_per_gpu": tokens_per_s / world,
             "mfu_pct": 100.0 * flops_per_token * tokens_per_s / world / 2.25e15,
             "tflops_per_gpu": flops_per_token * tokens_per_s / world / 1e12,
-            "config": {"model": f"{args.model}-{args.flavor}", "global_batch": args.local_batch * world,
-                       "seq_len": args.seq_len, "parallelism": f"fsdp{world}", "activation_checkpoint": args.ac,
+            "config": {"model": f"{args.model}-{args.flavor}", "global_batch": tokens_per_step // args.seq_len,
+                       "seq_len": args.seq_len, "parallelism": f"fsdp{world}" if args.preset == "fsdp" else layout,
+                       "preset": args.preset, "comm": args.comm, "tokens_per_step": tokens_per_step,
+                       "activation_checkpoint": args.ac,
                        "optimizer": f"AdamW fp32 master, {args.opt_state} moments", "fsdp_comm": trainer.engines[0].comm if trainer.engines[0]._symm is None else "nvlink",
                        "gemm": args.gemm, "attention": args.attention,
                        "doc_mask": "skipped (every synthetic sequence is a single document)",

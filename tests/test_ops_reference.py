@@ -154,3 +154,29 @@ def test_router_topk_counts():
     top, sel, counts = ref.router_topk(logits, 2, "softmax", None, True, 1.0)
     assert torch.allclose(top.sum(-1), torch.ones(20), atol=1e-5)
     assert counts.sum() == 40 and sel.shape == (20, 2)
+
+
+def test_chunked_attention_fallback_matches_dense_autograd(monkeypatch):
+    """The memory-bounded fallback (query blocks, probabilities recomputed in backward) against dense autograd math,
+    with documents, a window, sinks and grouped heads; the block size is forced small so several blocks run."""
+    import torch
+
+    from torchtitan_b200.ops import functional as OF
+    from torchtitan_b200.ops import reference as ref
+
+    torch.manual_seed(0)
+    T, Hq, Hkv, D = 70, 4, 2, 8
+    q, k, v = torch.randn(T, Hq, D), torch.randn(T, Hkv, D), torch.randn(T, Hkv, D)
+    doc = torch.tensor([0] * 20 + [1] * 33 + [2] * 17)
+    sinks = torch.tensor([0.5, -1.0, 0.0, 2.0])
+    g = torch.randn(T, Hq, D)
+    monkeypatch.setattr(OF, "_DENSE_SCORE_BYTES", 4 * Hq * T * 16)     # 16 query rows per block
+    a = [t.clone().requires_grad_() for t in (q, k, v, sinks)]
+    out = OF._masked_attention(a[0], a[1], a[2], 0.3, True, doc, 9, a[3], None, None)
+    out.backward(g)
+    b = [t.clone().requires_grad_() for t in (q, k, v, sinks)]
+    want, _ = ref.attention_fwd(b[0], b[1], b[2], scale=0.3, causal=True, doc_ids=doc, window=9, sinks=b[3])
+    want.backward(g)
+    assert torch.allclose(out, want, atol=1e-5)
+    for x, y in zip(a, b):
+        assert torch.allclose(x.grad, y.grad, atol=1e-4), (x.grad - y.grad).abs().max()

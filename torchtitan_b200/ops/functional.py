@@ -497,34 +497,103 @@ def attention_packed(qkv3: torch.Tensor, hq: int, hkv: int, scale: float, *, doc
     return attention(q, k, v, scale=scale, causal=True, doc_ids=doc_ids, kv_first=kv_first)
 
 
-def _masked_attention(q, k, v, scale, causal, doc_ids, window, sinks, q_pos, k_pos):
-    """General masks (documents, windows, sinks): dense-mask SDPA with autograd."""
-    Tq, Hq, _ = q.shape
-    Tk, Hkv, _ = k.shape
-    dev = q.device
-    qp = torch.arange(Tq, device=dev) if q_pos is None else q_pos
-    kp = torch.arange(Tk, device=dev) if k_pos is None else k_pos
-    mask = torch.ones(Tq, Tk, dtype=torch.bool, device=dev)
+_DENSE_SCORE_BYTES = 256 << 20   # largest fp32 score block the PyTorch fallback materialises at a time
+
+
+def _mask_block(qp, kp, causal, window, qd, kd):
+    mask = torch.ones(qp.numel(), kp.numel(), dtype=torch.bool, device=qp.device)
     if causal:
         mask &= qp[:, None] >= kp[None, :]
     if window is not None and window > 0:
         mask &= (qp[:, None] - kp[None, :]) < window
+    if qd is not None:
+        mask &= qd[:, None] == kd[None, :]
+    return mask
+
+
+class _ChunkedAttentionFn(torch.autograd.Function):
+    """PyTorch fallback for shapes and masks outside the flash kernels (general masks through positions, documents,
+    windows, sinks; any head dimension).  Queries are processed in blocks sized so that one fp32 score block
+    ``[Hq, Bq, Tk]`` stays under ``_DENSE_SCORE_BYTES``; nothing of size ``T x T`` is kept for the backward, which
+    recomputes each block's probabilities from the saved log-sum-exp."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, sinks, scale, causal, window, qp, kp, qd, kd):
+        Tq, Hq, _ = q.shape
+        Tk, Hkv, Dv = v.shape
+        rep = Hq // Hkv
+        kf = k.float().transpose(0, 1)
+        vf = v.float().transpose(0, 1)
+        if rep > 1:
+            kf, vf = kf.repeat_interleave(rep, 0), vf.repeat_interleave(rep, 0)
+        bq = max(16, min(Tq, _DENSE_SCORE_BYTES // max(1, 4 * Hq * Tk)))
+        out = torch.empty(Tq, Hq, Dv, dtype=q.dtype, device=q.device)
+        lse = torch.empty(Hq, Tq, dtype=torch.float32, device=q.device)
+        for a in range(0, Tq, bq):
+            b = min(Tq, a + bq)
+            s_ = torch.matmul(q[a:b].float().transpose(0, 1), kf.transpose(1, 2)) * scale
+            mask = _mask_block(qp[a:b], kp, causal, window, None if qd is None else qd[a:b], kd)
+            s_ = s_.masked_fill(~mask[None], float("-inf"))
+            if sinks is not None:
+                l = torch.logsumexp(torch.cat([s_, sinks.float()[:, None, None].expand(Hq, b - a, 1)], dim=-1), dim=-1)
+            else:
+                l = torch.logsumexp(s_, dim=-1)
+            safe = torch.where(torch.isinf(l), torch.zeros_like(l), l)
+            p = torch.where(mask[None], torch.exp(s_ - safe[..., None]), torch.zeros_like(s_))
+            out[a:b] = torch.matmul(p, vf).transpose(0, 1).to(q.dtype)
+            lse[:, a:b] = l
+        ctx.save_for_backward(q, k, v, out, lse, qp, kp, *(t for t in (sinks, qd, kd) if t is not None))
+        ctx.meta = (scale, causal, window, bq, sinks is not None, qd is not None)
+        return out
+
+    @staticmethod
+    def backward(ctx, d_o):
+        scale, causal, window, bq, has_sinks, has_docs = ctx.meta
+        q, k, v, out, lse, qp, kp, *rest = ctx.saved_tensors
+        sinks = rest.pop(0) if has_sinks else None
+        qd, kd = (rest[0], rest[1]) if has_docs else (None, None)
+        Tq, Hq, _ = q.shape
+        Tk, Hkv, Dv = v.shape
+        rep = Hq // Hkv
+        kf = k.float().transpose(0, 1)
+        vf = v.float().transpose(0, 1)
+        if rep > 1:
+            kf, vf = kf.repeat_interleave(rep, 0), vf.repeat_interleave(rep, 0)
+        dq = torch.empty_like(q)
+        dk = torch.zeros(Hq, Tk, k.shape[2], dtype=torch.float32, device=q.device)
+        dv = torch.zeros(Hq, Tk, Dv, dtype=torch.float32, device=q.device)
+        d_sinks = torch.zeros(Hq, dtype=torch.float32, device=q.device) if has_sinks else None
+        for a in range(0, Tq, bq):
+            b = min(Tq, a + bq)
+            qf = q[a:b].float().transpose(0, 1)
+            dof = d_o[a:b].float().transpose(0, 1)
+            s_ = torch.matmul(qf, kf.transpose(1, 2)) * scale
+            mask = _mask_block(qp[a:b], kp, causal, window, None if qd is None else qd[a:b], kd)
+            l = lse[:, a:b]
+            safe = torch.where(torch.isinf(l), torch.zeros_like(l), l)
+            p = torch.where(mask[None], torch.exp(s_ - safe[..., None]), torch.zeros_like(s_))
+            delta = (dof * out[a:b].float().transpose(0, 1)).sum(-1)                    # [Hq, Bq]
+            ds = p * (torch.matmul(dof, vf.transpose(1, 2)) - delta[..., None]) * scale
+            dq[a:b] = torch.matmul(ds, kf).transpose(0, 1).to(q.dtype)
+            dk += torch.matmul(ds.transpose(1, 2), qf)
+            dv += torch.matmul(p.transpose(1, 2), dof)
+            if has_sinks:
+                d_sinks -= (torch.exp(sinks.float()[:, None] - safe) * delta).masked_fill(torch.isinf(l), 0.0).sum(-1)
+        dk = dk.view(Hkv, rep, Tk, -1).sum(1).transpose(0, 1).to(k.dtype)
+        dv = dv.view(Hkv, rep, Tk, -1).sum(1).transpose(0, 1).to(v.dtype)
+        return dq, dk, dv, (d_sinks.to(sinks.dtype) if has_sinks else None), None, None, None, None, None, None, None
+
+
+def _masked_attention(q, k, v, scale, causal, doc_ids, window, sinks, q_pos, k_pos):
+    """General masks (documents, windows, sinks, explicit positions): memory-bounded PyTorch fallback."""
+    Tq, Tk = q.shape[0], k.shape[0]
+    dev = q.device
+    qp = torch.arange(Tq, device=dev) if q_pos is None else q_pos
+    kp = torch.arange(Tk, device=dev) if k_pos is None else k_pos
+    qd = kd = None
     if doc_ids is not None:
         qd, kd = doc_ids if isinstance(doc_ids, tuple) else (doc_ids, doc_ids)
-        mask &= qd[:, None] == kd[None, :]
-    rep = Hq // Hkv
-    qh = q.transpose(0, 1)
-    kh = k.transpose(0, 1).repeat_interleave(rep, dim=0) if rep > 1 else k.transpose(0, 1)
-    vh = v.transpose(0, 1).repeat_interleave(rep, dim=0) if rep > 1 else v.transpose(0, 1)
-    s = torch.matmul(qh.float(), kh.float().transpose(1, 2)) * scale
-    s = s.masked_fill(~mask[None], float("-inf"))
-    if sinks is not None:
-        s_ext = torch.cat([s, sinks.float()[:, None, None].expand(Hq, Tq, 1)], dim=-1)
-        p = torch.softmax(s_ext, dim=-1)[..., :-1]
-    else:
-        p = torch.softmax(s, dim=-1)
-    p = torch.nan_to_num(p, nan=0.0)
-    return torch.matmul(p, vh.float()).transpose(0, 1).to(q.dtype)
+    return _ChunkedAttentionFn.apply(q, k, v, sinks, float(scale), bool(causal), window, qp, kp, qd, kd)
 
 
 # =====================================================================
