@@ -136,6 +136,8 @@ def _row_maps(slot, slices_of_param):
 
 def _entries_for_flat(engine, pick_flat, dtype=None, key_fmt="{}") -> dict[str, ShardedEntry]:
     """Build ``{checkpoint_fqn: ShardedEntry}`` from per-unit flat shard tensors."""
+    if hasattr(engine, "wait_optimizer"):
+        engine.wait_optimizer()        # an optimizer step overlapped with the next forward must have finished
     slices = _global_slices(engine)
     out: dict[str, ShardedEntry] = {}
     for u in engine.units:

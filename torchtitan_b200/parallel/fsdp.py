@@ -43,6 +43,7 @@ and ``nvlink`` (peer loads / stores from our own kernels over symmetric memory,
 
 from __future__ import annotations
 
+import contextlib
 import math
 import re
 from dataclasses import dataclass, field
@@ -111,6 +112,8 @@ class FlatUnit:
         self.slot = 0
         self.gather_dst: torch.Tensor | None = None    # alias of flat_param with its own version counter
         self.private_grad = False                      # gradients in an own buffer instead of a rotating slot
+        self.ready = None                              # event of the optimizer step still refreshing this unit
+        self.hooked = False                            # a forward pre-hook of this unit exists
 
     # shard geometry -----------------------------------------------------
     @property
@@ -147,6 +150,8 @@ class ShardedModel:
         self._pools: dict[int, _SlotPool] = {}
         self._order: list[FlatUnit] = []   # units with sharded parameters, in execution order
         self._in_backward = False
+        self._optimizer_inflight = False
+        self._rs_unfenced = False     # reduce-scatters launched without their own trailing barrier in this pass
         # optimizer state (fp32 master weights and both moments) lives in pinned host memory and is
         # streamed through the GPU one unit at a time during the optimizer step
         self.offload_optimizer = bool(offload_optimizer) and device.type == "cuda"
@@ -409,6 +414,7 @@ class ShardedModel:
     @torch.no_grad()
     def publish_params(self) -> None:
         """master shard -> compute-dtype flat_param (own slice) -> all ranks."""
+        self.wait_optimizer()
         for u in self.units:
             if u.pool is not None:
                 u.param_shard.copy_(u.master)
@@ -472,6 +478,9 @@ class ShardedModel:
         return self._order[i] if 0 <= i < len(self._order) else None
 
     def _pre_forward(self, u: FlatUnit) -> None:
+        if u.ready is not None:        # the optimizer step that refreshes this unit may still be running
+            torch.cuda.current_stream(self.device).wait_event(u.ready)
+            u.ready = None
         if u.pool is None:
             return
         self._acquire(u)
@@ -504,6 +513,7 @@ class ShardedModel:
     def attach_hooks(self, unit_modules: list[tuple[FlatUnit, nn.Module]]) -> None:
         """Fire the unit's gradient reduction when the gradient reaches the unit's input."""
         for unit, module in unit_modules:
+            unit.hooked = True
             module.register_forward_pre_hook(_make_pre_hook(self, unit), with_kwargs=True)
             if unit.pool is not None:
                 module.register_forward_hook(_make_post_hook(self, unit))
@@ -571,7 +581,12 @@ class ShardedModel:
             else:
                 u.grad_shard.add_(src)
         elif self._symm is not None:
-            self._symm.reduce_scatter_accumulate(u.flat_grad, u.grad_shard, u.group, accumulate=not first)
+            # a rotating gradient slot is rewritten two units later: its readers are fenced off right here; a unit's
+            # own gradient buffer is next written one backward pass later, after the barrier of finish_backward
+            slot_backed = u.pool is not None and not u.private_grad
+            self._symm.reduce_scatter_accumulate(u.flat_grad, u.grad_shard, u.group, accumulate=not first,
+                                                 trailing_barrier=slot_backed)
+            self._rs_unfenced = self._rs_unfenced or not slot_backed
         else:
             tmp = self._get_fp32_tmp(u.padded)
             tmp.copy_(u.flat_grad)
@@ -604,6 +619,12 @@ class ShardedModel:
             return
         for u in self.units:
             self._launch_reduce(u)
+        if self._rs_unfenced and self._symm is not None:
+            # one barrier for all reduce-scatters of this pass: every rank has finished pulling from every gradient buffer
+            cs = self._comm_stream
+            with torch.cuda.stream(cs) if cs is not None else contextlib.nullcontext():
+                self._symm.barrier_all()
+            self._rs_unfenced = False
         if self._comm_stream is not None:
             torch.cuda.current_stream(self.device).wait_stream(self._comm_stream)
         for u in self.units:
@@ -642,6 +663,7 @@ class ShardedModel:
         return total
 
     def ensure_state(self) -> None:
+        self.wait_optimizer()
         for u in self.units:
             if u.exp_avg is None:
                 kw = dict(pin_memory=True) if self.offload_optimizer else dict(device=self.device)
@@ -657,6 +679,9 @@ class ShardedModel:
         fused_ag = self._symm is not None
         if fused_ag and not isinstance(grad_scale, torch.Tensor):
             grad_scale = torch.full((1,), float(grad_scale), dtype=torch.float32, device=self.device)
+        if self._overlap_ok(groups):
+            self._adamw_step_overlapped(groups, grad_scale, step)
+            return
         host_state = None
         for u in self.units:
             if host_state is not None:      # previous unit: updated state back to its pinned host buffers
@@ -706,6 +731,64 @@ class ShardedModel:
                 self._shards_changed()    # (includes the barrier)
         else:
             self._all_gather_params()
+
+    # -- optimizer overlapped with the next forward ---------------------------------------
+    def _overlap_ok(self, groups: list[dict]) -> bool:
+        """The update (and weight refresh) of unit k only has to be finished when the next forward reaches unit k.
+        Resident layout on CUDA, plain AdamW, state on the device; ``TB200_OVERLAP_OPTIMIZER=0`` switches it off."""
+        import os
+
+        return (self._comm_stream is not None and not self._pools and not self.offload_optimizer
+                and os.environ.get("TB200_OVERLAP_OPTIMIZER", "1") != "0"
+                and not any(g.get("optimizer_name") == "DistMuon" for g in groups))
+
+    def _adamw_step_overlapped(self, groups: list[dict], grad_scale, step: int) -> None:
+        """Units are updated in forward order on the communication stream; each unit records an event once its
+        refreshed weights are in place on every rank (after the unit's flag barrier or NCCL all-gather), and the
+        unit's forward pre-hook makes the compute stream wait for exactly that event.  The rest of the optimizer
+        therefore runs under the first layers of the next forward."""
+        cs = self._comm_stream
+        main = torch.cuda.current_stream(self.device)
+        fused_ag = self._symm is not None
+        if isinstance(grad_scale, torch.Tensor):
+            grad_scale.record_stream(cs)
+        cs.wait_stream(main)
+        with torch.cuda.stream(cs):
+            for u in self.units:
+                if u.grad_shard_valid:
+                    g = self._grad_of(u)
+                    if fused_ag and u.size > 1:
+                        self._symm.adamw_allgather(u, _group_runs(u), groups, step, grad_scale.reshape(1), g)
+                        self._symm.barrier_group(u.group)      # every rank's stores into this unit have landed
+                    else:
+                        lowp = u.shard_view(u.flat_param)
+                        for gi, a, b in _group_runs(u):
+                            h = groups[gi]
+                            optim_ops.adamw_(
+                                u.master[a:b], g[a:b], u.exp_avg[a:b], u.exp_avg_sq[a:b], lowp[a:b],
+                                lr=h["lr"], beta1=h["betas"][0], beta2=h["betas"][1], eps=h["eps"],
+                                weight_decay=h["weight_decay"], step=step, grad_scale=grad_scale,
+                            )
+                        if u.size > 1:
+                            dist.all_gather_into_tensor(u.flat_param, lowp, group=u.group)
+                    u.grad_shard_valid = False
+                ev = torch.cuda.Event()
+                ev.record(cs)
+                u.ready = ev
+        for u in self.units:
+            if not u.hooked:          # no forward hook will wait for it
+                main.wait_event(u.ready)
+                u.ready = None
+        self._optimizer_inflight = True
+
+    def wait_optimizer(self) -> None:
+        """Make the current stream wait for an optimizer step that is still running on the communication stream
+        (before anything outside the units' forward hooks reads parameters or optimizer state)."""
+        if self._optimizer_inflight:
+            torch.cuda.current_stream(self.device).wait_stream(self._comm_stream)
+            for u in self.units:
+                u.ready = None
+            self._optimizer_inflight = False
 
     def _stage_state(self, u: FlatUnit):
         """Offloaded optimizer state of one unit -> device copies (the unit's attributes point at

@@ -117,8 +117,9 @@ def parallelize_decoder(model: nn.Module, *, pdims, job_config, device: torch.de
         engine.materialize()
         hooks = []
         by_name = {u.name: u for u in engine.units}
-        if engine.sharded_params and model.tok_embeddings is not None:
-            # the embedding must be gathered before its lookup (it sits in the output unit when tied)
+        if model.tok_embeddings is not None:
+            # the embedding's forward hook: waits for the optimizer step that refreshes it and, in the sharded layout,
+            # gathers it before the lookup (it sits in the output unit when tied)
             emb_unit = by_name.get("tok_embeddings") or by_name.get("output")
             if emb_unit is not None:
                 hooks.append((emb_unit, model.tok_embeddings))

@@ -205,14 +205,19 @@ class SymmetricArena:
 
     # -- collectives -----------------------------------------------------------
     def reduce_scatter_accumulate(self, flat_grad: torch.Tensor, grad_shard: torch.Tensor, group,
-                                  accumulate: bool) -> None:
-        """``grad_shard (+)= sum over ranks of flat_grad[my slice]`` by pulling from peers."""
+                                  accumulate: bool, trailing_barrier: bool = True) -> None:
+        """``grad_shard (+)= sum over ranks of flat_grad[my slice]`` by pulling from peers.
+
+        The barrier in front makes every rank's local gradients complete.  A second barrier after the pull keeps a
+        rank from overwriting a gradient buffer that a peer still reads; the caller may leave it out when a later
+        barrier of the same arena on the same stream is certain to follow before the buffer is written again."""
         arena, ptrs = self.peer_ptrs(flat_grad)
-        arena.barrier()  # every rank's local gradients are complete
+        arena.barrier()
         _count()
         ext.require().reduce_scatter_pull(ptrs, arena.rank, arena.rank * grad_shard.numel(), grad_shard,
                                           flat_grad.dtype == torch.bfloat16, accumulate)
-        arena.barrier()  # every rank has finished reading before buffers are reused
+        if trailing_barrier:
+            arena.barrier()
 
     def adamw_allgather(self, unit, runs, groups, step: int, grad_scale: torch.Tensor, grad: torch.Tensor) -> None:
         """AdamW on this rank's shard with the weight all-gather fused in (peer stores)."""
@@ -239,6 +244,9 @@ class SymmetricArena:
         nbytes = shard.numel() * shard.element_size()
         _count()
         ext.require().all_gather_pull(ptrs, arena.rank, nbytes, out)
+
+    def barrier_group(self, group) -> None:
+        self._arenas[id(group)].barrier()
 
     def barrier_all(self) -> None:
         for arena in self._arenas.values():

@@ -322,6 +322,7 @@ class Trainer(Configurable):
         if self.pdims.pp_enabled:
             return self.pp_forward_backward_step(tokens, positions, labels, q_pos, global_valid)
         if self._graph_runner is not None and q_pos is None and not self._extra_inputs:
+            self.engines[0].wait_optimizer()   # a replayed graph has no per-unit waits on the previous optimizer step
             key = (min(self._mb_index, 1), tuple(tokens.shape))
             self._mb_index += 1
             with sl.span("fwd_bwd"):
