@@ -62,6 +62,67 @@ def test_generator_and_buffer_fold():
     assert torch.allclose(lp[mask.bool()], old[mask.bool()], atol=1e-4)
 
 
+def _tiny_llama(seed=0, layers=2):
+    from torchtitan_b200.models import get_model_spec
+
+    spec = get_model_spec("llama3", "debugmodel")
+    spec.model.layers = spec.model.layers[:layers]
+    spec.model.n_layers = layers
+    model = spec.model.build()
+    model.init_states(seed=seed)
+    return spec, model
+
+
+def test_cached_generator_matches_prefix_recomputation_and_weight_sync():
+    from torchtitan_b200.experiments.rl import CachedGenerator, SamplingGenerator, WeightSync
+
+    _, model = _tiny_llama(seed=0)
+    prompt = torch.tensor([5, 9, 11, 4])
+    slow = SamplingGenerator(model, temperature=0.0).generate(prompt, 8)
+    fast = CachedGenerator(model, temperature=0.0).generate(prompt, 8)
+    assert torch.equal(slow.response, fast.response)
+    assert torch.allclose(slow.logprobs, fast.logprobs, atol=1e-4)
+    # a generator with its own (stale) copy acts differently until the trainer's weights are pushed
+    _, other = _tiny_llama(seed=1)
+    gen = CachedGenerator(other, temperature=0.0)
+    assert not torch.equal(gen.generate(prompt, 8).response, fast.response)
+    sync = WeightSync()
+    assert sync.push(model, gen) == 1 and gen.policy_version == 1
+    assert torch.equal(gen.generate(prompt, 8).response, fast.response)
+
+
+def test_rl_controller_improves_a_toy_reward():
+    """DAPO with the cached generator on the debug model: the reward (share of answer tokens from the lower half of
+    the vocabulary) rises within a few iterations; dynamic sampling drops groups without signal."""
+    from torchtitan_b200.components.optimizer import OptimizersContainer
+    from torchtitan_b200.config import ConfigManager
+    from torchtitan_b200.experiments.rl import CachedGenerator, RLConfig, RLController
+    from torchtitan_b200.parallel.parallel_dims import ParallelDims
+    from torchtitan_b200.parallel.parallelize import parallelize_decoder
+    from torchtitan_b200.trainer import Trainer
+
+    spec, _ = _tiny_llama()
+    cfg = Trainer.Config()
+    cfg.training.mixed_precision_param = "float32"
+    cfg.training.num_tokens_per_microbatch_per_dp_rank = 64
+    cfg.training.max_context_length = 64
+    pdims = ParallelDims(world_size=1)
+    with torch.device("meta"):
+        model = spec.model.build()
+    eng = parallelize_decoder(model, pdims=pdims, job_config=cfg, device=torch.device("cpu"), seed=3)
+    opt = OptimizersContainer(OptimizersContainer.Config(lr=2e-2, weight_decay=0.0), engines=[eng])
+    reward = lambda prompt, resp: float((resp < 1024).float().mean())      # noqa: E731
+    gen = CachedGenerator(model, temperature=1.0, seed=0)
+    ctl = RLController(model, eng, opt, gen, reward, RLConfig(group_size=6, max_new_tokens=8, loss="dapo",
+                                                               dynamic_sampling=True), pdims=pdims)
+    prompts = [torch.tensor([3, 1, 4]), torch.tensor([1, 5, 9, 2])]
+    hist = [ctl.step(prompts) for _ in range(12)]
+    first = sum(h["reward_mean"] for h in hist[:3]) / 3
+    last = sum(h["reward_mean"] for h in hist[-3:]) / 3
+    assert last > first, (first, last)
+    assert gen.policy_version == ctl.sync.version >= 1
+
+
 def test_hf_backend_trains():
     transformers = pytest.importorskip("transformers")
     from torchtitan_b200.experiments.transformers_backend import HFCausalLM, hf_train_steps

@@ -27,7 +27,7 @@ from torchtitan_b200.parallel import tp_ops
 from .layers import Linear, RMSNorm, RoPE, TPContext
 from .module import InitSpec, Module, set_init
 
-__all__ = ["GQAttention", "AttentionContext", "build_attention_context"]
+__all__ = ["GQAttention", "AttentionContext", "KVCache", "build_attention_context"]
 
 
 @dataclass
@@ -38,6 +38,38 @@ class AttentionContext:
     max_doc_len: int | None = None
     kv_first: torch.Tensor | None = None  # [T_local] int32: index of the first token of each token's document
     rope_positions: torch.Tensor | None = None  # [3, T_local] multimodal rotary positions (overrides ``positions``)
+    kv_cache: "KVCache | None" = None  # incremental decoding: keys / values of earlier tokens, per attention layer
+
+
+class KVCache:
+    """Keys and values of the tokens seen so far, one pair of buffers per attention layer (incremental decoding
+    with the training model itself; the reference's generator keeps its cache inside vLLM,
+    torchtitan/experiments/rl).  Buffers grow in chunks; ``update`` appends the new rows and returns views of
+    everything cached."""
+
+    def __init__(self, chunk: int = 256):
+        self.chunk = chunk
+        self._k: dict[int, torch.Tensor] = {}
+        self._v: dict[int, torch.Tensor] = {}
+        self._len: dict[int, int] = {}
+
+    def length(self, layer) -> int:
+        return self._len.get(id(layer), 0)
+
+    def update(self, layer, k: torch.Tensor, v: torch.Tensor):
+        key = id(layer)
+        n0, n = self._len.get(key, 0), k.shape[0]
+        if key not in self._k or self._k[key].shape[0] < n0 + n:
+            cap = (n0 + n + self.chunk - 1) // self.chunk * self.chunk
+            nk = k.new_empty((cap,) + tuple(k.shape[1:]))
+            nv = v.new_empty((cap,) + tuple(v.shape[1:]))
+            if n0:
+                nk[:n0], nv[:n0] = self._k[key][:n0], self._v[key][:n0]
+            self._k[key], self._v[key] = nk, nv
+        self._k[key][n0:n0 + n] = k
+        self._v[key][n0:n0 + n] = v
+        self._len[key] = n0 + n
+        return self._k[key][:n0 + n], self._v[key][:n0 + n]
 
 
 def build_attention_context(positions: torch.Tensor, *, assume_single_document: bool = False,
@@ -168,7 +200,16 @@ class GQAttention(Module):
         else:
             q, k, v = qkv[:, :hq], qkv[:, hq:hq + hkv], qkv[:, hq + hkv:]
         ctx = ctx or AttentionContext()
-        if ctx.cp is not None:
+        if ctx.kv_cache is not None:
+            # incremental decoding (no autograd): the new queries attend to everything cached plus themselves
+            from torchtitan_b200.ops import flash as FL
+
+            kc, vc = ctx.kv_cache.update(self, k.detach(), v.detach())
+            o, lse = FL.block_fwd(q.contiguous(), kc, vc, self.scale, causal=True, causal_offset=kc.shape[0] - T,
+                                  window=int(self.window or 0))
+            if self.sinks is not None:
+                o = (o.float() * torch.sigmoid(lse - self.sinks.float()[:, None]).t()[..., None]).to(q.dtype)
+        elif ctx.cp is not None:
             from torchtitan_b200.parallel.context_parallel import cp_attention
 
             o = cp_attention(q, k, v, ctx, scale=self.scale, window=self.window, sinks=self.sinks)

@@ -47,6 +47,7 @@ class _Settings:
     launches: int = 0  # count of launches of this package's own kernels
     count_launches: bool = False
     library_fallbacks: int = 0  # CUDA calls that went to a library / PyTorch path (see the module docstring)
+    strict_native: bool = False  # batch-invariant mode: a CUDA call that would take a library path raises instead
 
 
 settings = _Settings()
@@ -55,6 +56,14 @@ settings = _Settings()
 def _count(n: int = 1) -> None:
     if settings.count_launches:
         settings.launches += n
+
+
+def _library_fallback(what: str) -> None:
+    """Book-keeping for a CUDA call that leaves the hand-written kernels."""
+    settings.library_fallbacks += 1
+    if settings.strict_native:
+        raise RuntimeError(f"{what} would run on a library / PyTorch path, which is not batch-invariant "
+                           "(debug.batch_invariant is on)")
 
 
 def _cuda(t: torch.Tensor) -> bool:
@@ -123,13 +132,13 @@ def _tc_gemm(a, b, mode, out, accumulate):
         K, M = a.shape
         N = b.shape[1]
     if (N % 8) or K == 0 or ((M % 8) if mode == 2 else (K % 8)):
-        settings.library_fallbacks += 1
+        _library_fallback(f"a bf16 GEMM with M={M} N={N} K={K}")
         return None
     if out is None:
         out = torch.empty(M, N, dtype=torch.bfloat16, device=a.device)
         accumulate = False
     elif not (out.is_contiguous() and out.dtype == torch.bfloat16):
-        settings.library_fallbacks += 1
+        _library_fallback("a bf16 GEMM into a strided or non-bf16 output")
         return None
     torch.ops.tb200.gemm_bf16(a, b, out, mode, accumulate)
     _count()
@@ -456,7 +465,7 @@ def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, scale: float
         _count(4)  # forward + (delta, backward, dq cast)
         return flash_attention(q, k, v, scale, causal=True, kv_first=kv_first, window=window, sinks=sinks)
     if _cuda(q):
-        settings.library_fallbacks += 1
+        _library_fallback(f"attention with head dimension {q.shape[-1]}")
     if simple and doc_ids is None and q.shape[-1] == v.shape[-1]:
         return _sdpa_causal(q, k, v, scale)
     return _masked_attention(q, k, v, scale, causal, doc_ids, window, sinks, q_pos, k_pos)

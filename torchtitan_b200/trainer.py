@@ -147,6 +147,11 @@ class Trainer(Configurable):
                                                c.debug.deterministic_warn_only)
         OF.settings.gemm = c.kernels.gemm
         OF.settings.attention = c.kernels.attention
+        OF.settings.strict_native = False
+        if c.debug.batch_invariant:
+            from torchtitan_b200.experiments.rl.batch_invariance import enable_batch_invariant_mode
+
+            enable_batch_invariant_mode(True)
 
         # ---- model ------------------------------------------------------
         spec: ModelSpec = c.model_spec or get_model_spec(c.model.name, c.model.flavor)
