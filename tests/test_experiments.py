@@ -240,3 +240,54 @@ def test_diloco_outer_step():
     assert algo.step()
     # pseudo-gradient = global - local = 0.75; outer SGD with lr 1 moves the global weights onto the local ones
     assert torch.allclose(p.detach(), torch.full((3,), 0.25))
+
+
+def _hf_engine(rank, world, reshard, out_path):
+    import transformers
+
+    from torchtitan_b200.experiments.transformers_backend import HFCausalLM, hf_engine_train_steps, parallelize_hf
+    from torchtitan_b200.parallel.parallel_dims import ParallelDims
+    from torchtitan_b200.trainer import Trainer
+
+    cfg = transformers.LlamaConfig(vocab_size=128, hidden_size=32, intermediate_size=64, num_hidden_layers=3,
+                                   num_attention_heads=4, num_key_value_heads=2, max_position_embeddings=64,
+                                   tie_word_embeddings=False)
+    torch.manual_seed(0)
+    model = HFCausalLM(cfg)
+    job = Trainer.Config()
+    job.training.mixed_precision_param = "float32"
+    job.parallelism.fsdp_reshard_after_forward = reshard
+    pdims = ParallelDims(world_size=world, rank=rank).build()
+    eng = parallelize_hf(model, pdims=pdims, job_config=job, device=torch.device("cpu"))
+    g = torch.Generator().manual_seed(1)
+    batches = []
+    for s in range(4):
+        per_rank = []
+        for r in range(2):
+            toks = torch.randint(0, 128, (33,), generator=g)
+            per_rank.append((toks[:-1], torch.arange(32), toks[1:]))
+        batches.append(per_rank)
+    mine = [b[rank] for b in batches] if world == 2 else None
+    if world == 2:
+        losses = hf_engine_train_steps(model, eng, mine, pdims=pdims, lr=3e-3)
+    else:   # one rank sees both sequences of a step as one packed batch
+        packed = [(torch.cat([a[0], b[0]]), torch.cat([a[1], b[1]]), torch.cat([a[2], b[2]])) for a, b in batches]
+        losses = hf_engine_train_steps(model, eng, packed, pdims=pdims, lr=3e-3)
+    if rank == 0:
+        torch.save(torch.tensor(losses), out_path)
+
+
+def test_hf_model_on_the_sharded_engine(tmp_path):
+    """A Hugging Face Llama under the flat-buffer FSDP engine: 2 ranks (resident and sharded layout) reproduce the
+    single-rank losses on the same global batch."""
+    pytest.importorskip("transformers")
+    from tests.dist_utils import run_distributed
+
+    outs = {}
+    for name, world, reshard in (("one", 1, "never"), ("resident", 2, "never"), ("sharded", 2, "always")):
+        path = str(tmp_path / f"{name}.pt")
+        run_distributed(_hf_engine, world, reshard, path)
+        outs[name] = torch.load(path)
+    assert torch.allclose(outs["one"], outs["resident"], atol=2e-4), outs
+    assert torch.allclose(outs["one"], outs["sharded"], atol=2e-4), outs
+    assert outs["one"][-1] < outs["one"][0]

@@ -4,7 +4,12 @@ interface, loss and data pipeline (parity: torchtitan/experiments/transformers_m
 ``HFCausalLM(config_or_name)`` builds the architecture from a ``transformers`` config (random
 init) and exposes ``forward(tokens[T], positions[T]) -> logits[T, V]``; documents are kept apart by
 passing ``position_ids`` that restart per document together with a block-diagonal causal mask.
-``hf_train_steps`` is a minimal data-parallel loop (gradient averaging over the world group)."""
+``hf_train_steps`` is a minimal data-parallel loop (gradient averaging over the world group), the oracle of the
+tests.  ``parallelize_hf`` puts the same module under this framework's sharded data-parallel engine (units =
+embedding, every decoder layer, final norm + lm_head; resident or sharded parameter layout, NCCL or NVLink
+transport, fp32 master weights and sharded AdamW: parity with parallelize.py of the reference's backend, which
+applies FSDP to the HF layers), and ``hf_engine_train_steps`` is the training loop on it.  Tensor and pipeline
+parallel plans for HF modules are not built."""
 
 from __future__ import annotations
 
@@ -12,7 +17,7 @@ import torch
 import torch.distributed as dist
 import torch.nn as nn
 
-__all__ = ["HFCausalLM", "hf_train_steps"]
+__all__ = ["HFCausalLM", "hf_train_steps", "parallelize_hf", "hf_engine_train_steps"]
 
 
 class HFCausalLM(nn.Module):
@@ -54,3 +59,76 @@ def hf_train_steps(model: HFCausalLM, batches, *, lr: float = 3e-4, max_norm: fl
         opt.step()
         losses.append(float(loss.detach()))
     return losses
+
+
+def _hf_units(model: HFCausalLM):
+    from torchtitan_b200.parallel.fsdp import UnitSpec
+
+    base = model.hf.model
+    layers = list(base.layers)
+    tied = model.hf.lm_head.weight is base.embed_tokens.weight
+    units, hooks = [], []
+    if not tied:
+        units.append(UnitSpec("embed_tokens", [base.embed_tokens]))
+        hooks.append(("embed_tokens", base.embed_tokens))
+    for i, layer in enumerate(layers):
+        units.append(UnitSpec(f"layers.{i}", [layer]))
+        hooks.append((f"layers.{i}", layer))
+    tail = ([base.embed_tokens] if tied else []) + [base.norm, model.hf.lm_head]
+    units.append(UnitSpec("output", tail))
+    hooks.append(("output", base.embed_tokens if tied else base.norm))
+    if tied:
+        hooks.append(("output", base.norm))
+    rest = [m for n, m in base.named_children() if n not in ("embed_tokens", "layers", "norm")]
+    if any(True for m in rest for _ in m.parameters()):
+        units.append(UnitSpec("extras", rest))
+    return units, hooks
+
+
+def parallelize_hf(model: HFCausalLM, *, pdims, job_config, device: torch.device, seed: int = 0):
+    """Shard an ``HFCausalLM`` with the flat-buffer engine, keeping the values the HF initialiser gave it."""
+    from torchtitan_b200.parallel.fsdp import ShardedModel
+
+    par, tr = job_config.parallelism, job_config.training
+    values = {n: p.detach().float().cpu().clone() for n, p in model.named_parameters()}
+    units, hooks = _hf_units(model)
+    param_dtype = torch.bfloat16 if tr.mixed_precision_param == "bfloat16" else torch.float32
+    engine = ShardedModel(model, units, pdims=pdims, device=device, param_dtype=param_dtype, seed=seed,
+                          comm=par.fsdp_comm, reshard_after_forward=par.fsdp_reshard_after_forward or "never")
+    model.to(device)          # buffers (rotary tables); parameters are replaced by views of the flat buffers below
+    engine.materialize(init=False)
+    with torch.no_grad():
+        for u in engine.units:
+            for slot, pstart, sstart, n in u.slot_pieces():
+                u.master[sstart:sstart + n].copy_(values[slot.fqn].reshape(-1)[pstart:pstart + n])
+    engine.publish_params()
+    by_name = {u.name: u for u in engine.units}
+    engine.attach_hooks([(by_name[name], module) for name, module in hooks if name in by_name])
+    return engine
+
+
+def hf_engine_train_steps(model: HFCausalLM, engine, batches, *, pdims, lr: float = 3e-4, max_norm: float = 1.0) -> list[float]:
+    """Like ``hf_train_steps`` on the sharded engine: the loss is divided by the global token count, gradients are
+    reduce-scattered per unit during backward, AdamW runs on the fp32 shards."""
+    from torchtitan_b200.components.optimizer import OptimizersContainer, clip_grad_norm_
+
+    opt = OptimizersContainer(OptimizersContainer.Config(lr=lr), engines=[engine])
+    losses = []
+    for tokens, positions, labels in batches:
+        dev = engine.device
+        tokens, positions, labels = tokens.to(dev), positions.to(dev), labels.to(dev)
+        n = (labels != -100).sum().float()
+        if dist.is_initialized() and dist.get_world_size() > 1:
+            dist.all_reduce(n)
+        opt.zero_grad()
+        logits = model(tokens, positions)
+        loss = nn.functional.cross_entropy(logits.float(), labels, ignore_index=-100, reduction="sum") / n
+        loss.backward()
+        engine.finish_backward()
+        clip_grad_norm_([engine], max_norm, pdims, optimizers=opt)
+        opt.step()
+        losses.append(loss.detach())
+    out = torch.stack(losses)
+    if dist.is_initialized() and dist.get_world_size() > 1:
+        dist.all_reduce(out)
+    return out.tolist()
