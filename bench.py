@@ -76,7 +76,7 @@ PRESETS = {
                          par=dict(tensor_parallel_degree=2, context_parallel_degree=2)),
     # Qwen3-30B-A3B-shaped MoE, expert parallel over all ranks, FSDP on the rest
     "moe_ep8": dict(model="qwen3", flavor="30B-A3B", seq_len=4096, local_batch=2, ac="selective",
-                    par=dict(expert_parallel_degree=-1, ep_capacity_factor=2.0)),
+                    par=dict(expert_parallel_degree=-1, ep_capacity_factor=1.25)),
     # Llama-3.1 70B, PP 2 (interleaved 1F1B, two virtual stages per rank) x TP 2 x FSDP, bf16 optimizer states, full AC
     "70b_pp2tp2": dict(model="llama3", flavor="70B", seq_len=8192, local_batch=1, opt_state="bf16", ac="full",
                        par=dict(pipeline_parallel_degree=2, tensor_parallel_degree=2,
