@@ -291,3 +291,27 @@ def test_hf_model_on_the_sharded_engine(tmp_path):
     assert torch.allclose(outs["one"], outs["resident"], atol=2e-4), outs
     assert torch.allclose(outs["one"], outs["sharded"], atol=2e-4), outs
     assert outs["one"][-1] < outs["one"][0]
+
+
+def test_graph_trainer_passes_map_to_engine_settings(tmp_path):
+    from torchtitan_b200.config import ConfigManager
+    from torchtitan_b200.experiments.graph_trainer import GraphTrainer, apply_passes
+
+    cfg = ConfigManager().parse_args([
+        "--module", "llama3", "--config", "llama3_debugmodel", "--training.num_tokens_per_microbatch_per_dp_rank", "64",
+        "--training.max_context_length", "64", "--training.steps", "2", "--training.mixed_precision_param", "float32",
+        "--dump_folder", str(tmp_path), "--debug.no-enable_structured_logging"])
+    done = apply_passes(cfg, ["fsdp_reshard", "async_tp", "ep_overlap", "full_remat", "regional_inductor"])
+    assert done == ["fsdp_reshard", "async_tp", "ep_overlap", "full_remat"]
+    assert cfg.parallelism.fsdp_reshard_after_forward == "always" and cfg.parallelism.tp_comm == "nvlink"
+    assert cfg.parallelism.ep_comm == "nvlink" and cfg.activation_checkpoint.mode == "full"
+    with pytest.raises(ValueError):
+        apply_passes(cfg, ["no_such_pass"])
+    with pytest.raises(ValueError):
+        apply_passes(cfg, ["cudagraph", "cpu_offload"])
+    cfg.training.disable_cuda_graphs = True
+    cfg.activation_checkpoint.cpu_offload = False
+    t = GraphTrainer(cfg, passes=["selective_remat", "fsdp_overlap"])
+    t.train()
+    assert t.step == 2 and t.applied_passes == ["selective_remat", "fsdp_overlap"]
+    t.close()
