@@ -195,27 +195,68 @@ def engine_model_state(engine, dtype: torch.dtype | None = None) -> dict[str, Sh
     return _entries_for_flat(engine, lambda u: u.master, dtype)
 
 
+_GROUP_KEYS = ("lr", "betas", "eps", "weight_decay", "initial_lr")
+# torch.optim.AdamW fields that the reference's flattened optimizer dict also carries; constant here
+_GROUP_CONSTANTS = {"amsgrad": False, "maximize": False, "foreach": None, "capturable": False, "differentiable": False,
+                    "fused": True}
+
+
+def _checkpoint_names(engine) -> list[tuple[str, int]]:
+    """``(checkpoint fqn, optimizer group index)`` of every parameter of the engine, whichever rank holds its rows."""
+    slices = _global_slices(engine)
+    out = []
+    for u in engine.units:
+        for slot in u.slots:
+            for _l0, _l1, name, _g0, _cshape in _row_maps(slot, slices.get(slot.fqn, [])):
+                out.append((name, slot.group_idx))
+    return out
+
+
 def engine_optimizer_state(engine, param_groups: list[dict]) -> dict[str, Any]:
+    """The optimizer state in the key scheme of the reference's flattened DCP optimizer dict
+    (``get_optimizer_state_dict(..., flatten_optimizer_state_dict=True)``, torchtitan/components/optimizer.py):
+    ``state.{fqn}.exp_avg`` / ``exp_avg_sq`` / ``step`` and ``param_groups.{fqn}.{field}`` per parameter."""
     engine.ensure_state()
     out: dict[str, Any] = {}
     out.update(_entries_for_flat(engine, lambda u: u.exp_avg, key_fmt="state.{}.exp_avg"))
     out.update(_entries_for_flat(engine, lambda u: u.exp_avg_sq, key_fmt="state.{}.exp_avg_sq"))
-    out["step"] = engine.step_count
-    for i, g in enumerate(param_groups):
-        for k in ("lr", "betas", "eps", "weight_decay", "initial_lr"):
+    step = torch.tensor(float(engine.step_count))
+    for name, gi in _checkpoint_names(engine):
+        out[f"state.{name}.step"] = step.clone()
+        g = param_groups[gi] if gi < len(param_groups) else param_groups[-1]
+        for k in _GROUP_KEYS:
             if k in g:
-                out[f"param_groups.{i}.{k}"] = list(g[k]) if isinstance(g[k], tuple) else g[k]
+                out[f"param_groups.{name}.{k}"] = list(g[k]) if isinstance(g[k], tuple) else g[k]
+        for k, v in _GROUP_CONSTANTS.items():
+            out[f"param_groups.{name}.{k}"] = v
     return out
 
 
 def load_engine_optimizer_state(engine, sd: dict[str, Any], param_groups: list[dict]) -> None:
-    # tensors were loaded in place through the ShardedEntry views
-    if "step" in sd:
-        engine.step_count = int(sd["step"])
-    for i, g in enumerate(param_groups):
-        for k in ("lr", "betas", "eps", "weight_decay", "initial_lr"):
-            key = f"param_groups.{i}.{k}"
+    """Moments were loaded in place through the ShardedEntry views; the step and the group fields come from the
+    per-parameter keys (or from the single ``step`` / index-keyed ``param_groups.{i}.*`` of earlier checkpoints)."""
+    names = _checkpoint_names(engine)
+    step = sd.get("step")
+    for name, _ in names:
+        if f"state.{name}.step" in sd:
+            step = sd[f"state.{name}.step"]
+            break
+    if step is not None:
+        engine.step_count = int(step.item() if isinstance(step, torch.Tensor) else step)
+    seen: set[int] = set()
+    for name, gi in names:
+        if gi in seen or gi >= len(param_groups):
+            continue
+        g = param_groups[gi]
+        for k in _GROUP_KEYS:
+            key = f"param_groups.{name}.{k}"
             if key in sd:
+                g[k] = tuple(sd[key]) if k == "betas" else sd[key]
+                seen.add(gi)
+    for i, g in enumerate(param_groups):
+        for k in _GROUP_KEYS:
+            key = f"param_groups.{i}.{k}"
+            if i not in seen and key in sd:
                 g[k] = tuple(sd[key]) if k == "betas" else sd[key]
 
 
