@@ -184,3 +184,31 @@ def test_flash_window_and_sinks(Tq, Tk, Hq, Hkv, offset, window, docs, use_sinks
     if use_sinks:
         err = (sinks.grad - sr.grad).abs().max().item()
         assert err <= 2e-2 * sr.grad.abs().max().item() + 2e-2, (err, sr.grad)
+
+
+@pytest.mark.parametrize("D,window,use_sinks", [(64, 0, False), (64, 128, True), (16, 0, False), (96, 0, False)])
+def test_small_head_dims_run_on_the_padded_kernels(D, window, use_sinks):
+    """Head dimensions below 128 (GPT-OSS 64, debug models 16): zero-padded heads through the 128-wide kernels."""
+    from torchtitan_b200.ops import functional as OF
+
+    T, Hq, Hkv = 640, 4, 2
+    g = torch.Generator(device="cuda").manual_seed(D)
+    q = torch.randn(T, Hq, D, device="cuda", generator=g).bfloat16()
+    k = torch.randn(T, Hkv, D, device="cuda", generator=g).bfloat16()
+    v = torch.randn(T, Hkv, D, device="cuda", generator=g).bfloat16()
+    d_o = torch.randn(T, Hq, D, device="cuda", generator=g).bfloat16()
+    sinks = torch.linspace(-1, 1, Hq, device="cuda").requires_grad_() if use_sinks else None
+    scale = 1.0 / math.sqrt(D)
+    before = OF.settings.library_fallbacks
+    qg, kg, vg = (t.clone().requires_grad_() for t in (q, k, v))
+    o = OF.attention(qg, kg, vg, scale=scale, causal=True, window=window or None, sinks=sinks)
+    o.backward(d_o)
+    assert OF.settings.library_fallbacks == before, "the call left the flash kernels"
+    qr, kr, vr = (t.float().requires_grad_() for t in (q, k, v))
+    sr = sinks.detach().clone().requires_grad_() if use_sinks else None
+    o_ref, _ = _reference(qr, kr, vr, scale, True, 0, None, window, sr)
+    o_ref.backward(d_o.float())
+    assert o.shape == (T, Hq, D)
+    assert (o.float() - o_ref).abs().max().item() < 2e-2
+    for got, ref in ((qg.grad, qr.grad), (kg.grad, kr.grad), (vg.grad, vr.grad)):
+        assert (got.float() - ref).abs().max().item() <= 2e-2 * ref.abs().max().item() + 2e-2

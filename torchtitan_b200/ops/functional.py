@@ -464,6 +464,20 @@ def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, scale: float
 
         _count(4)  # forward + (delta, backward, dq cast)
         return flash_attention(q, k, v, scale, causal=True, kv_first=kv_first, window=window, sinks=sinks)
+    D = q.shape[-1]
+    if (settings.attention == "native" and _cuda(q) and causal and q_pos is None and k_pos is None
+            and (doc_ids is None or kv_first is not None) and D < 128 and v.shape[-1] == D
+            and q.dtype == torch.bfloat16 and q.shape[1] % k.shape[1] == 0):
+        # Smaller head dimensions run on the 128-wide kernels with zero-padded heads: the padded columns add
+        # nothing to q . k and produce zero output columns, which are cut off again (twice the attention FLOPs of a
+        # dedicated instantiation, still tensor-core attention without a T x T intermediate).
+        from .flash import flash_attention
+
+        pad = (0, 128 - D)
+        _count(4)
+        o = flash_attention(F.pad(q, pad), F.pad(k, pad), F.pad(v, pad), scale, causal=True, kv_first=kv_first,
+                            window=window, sinks=sinks)
+        return o[..., :D]
     if _cuda(q):
         _library_fallback(f"attention with head dimension {q.shape[-1]}")
     if simple and doc_ids is None and q.shape[-1] == v.shape[-1]:
