@@ -87,6 +87,18 @@ def test_mxfp8_tiled_quantisers(R, C):
     assert torch.equal(dt, d0.t().contiguous()) and torch.equal(_untile(st, Ct, Rt), s0.t().contiguous())
 
 
+@pytest.mark.parametrize("R,C", [(128, 128), (384, 256), (1024, 640)])
+def test_mxfp8_dual_quantiser_equals_the_two_single_ones(R, C):
+    """One read, both forms: row-wise and transposed outputs are bit-identical to the separate kernels."""
+    ops = ext.require()
+    x = _input(R, C, seed=R + C)
+    d_row, s_row, d_t, s_t = ops.mxfp8_quantize_tiled_both(x)
+    rd, rs = ops.mxfp8_quantize_tiled(x)
+    td, ts = ops.mxfp8_quantize_tiled_t(x)
+    assert torch.equal(d_row, rd) and torch.equal(s_row, rs)
+    assert torch.equal(d_t, td) and torch.equal(s_t, ts)
+
+
 @pytest.mark.parametrize("variant", [1, 2])
 @pytest.mark.parametrize("M,N,K", [(128, 128, 128), (512, 256, 256), (1000, 520, 1024), (2048, 768, 512)])
 def test_gemm_mxfp8_block_scaled(M, N, K, variant):

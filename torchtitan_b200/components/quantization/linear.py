@@ -67,17 +67,40 @@ def _mx_gemm(a: torch.Tensor, a_rows_contracted: bool, b: torch.Tensor, b_rows_c
     return ops.gemm_mxfp8(qa[0], qa[1], qb[0], qb[1])
 
 
+def _both_ok(t: torch.Tensor) -> bool:
+    return t.shape[0] % 128 == 0 and t.shape[1] % 128 == 0
+
+
 class _QuantLinearFn(torch.autograd.Function):
+    """``y = x w^T`` with all three GEMMs on quantised operands.  On the block-scaled path an operand that two GEMMs
+    contract over different dimensions (``x``: features in the forward, tokens in the weight gradient; ``dy``:
+    output features in the input gradient, tokens in the weight gradient) is quantised in both forms by one kernel
+    from one read; the forward then keeps the transposed fp8 form of ``x`` for the backward instead of bf16 ``x``."""
+
     @staticmethod
     def forward(ctx, x, weight, recipe, hp_wgrad, block_scaled=True):
         x2 = x.reshape(-1, x.shape[-1])
         if not x2.is_contiguous():
             x2 = x2.contiguous()
+        ctx.x_t = None
+        saved_x = x2
         if _mx_native(recipe, block_scaled, x2.shape[1], weight.shape[0], x2, weight):
-            y = _mx_gemm(x2, False, weight, False)
+            ops = ext.require()
+            wgrad_native = (weight.requires_grad and not hp_wgrad and _both_ok(x2)
+                            and _mx_native(recipe, block_scaled, x2.shape[0], weight.shape[1], x2))
+            qw = ops.mxfp8_quantize_tiled(weight)
+            if wgrad_native:
+                qx = ops.mxfp8_quantize_tiled_both(x2)
+                ctx.x_t = (qx[2], qx[3])          # [features, tokens] fp8 + scales: the weight gradient's operand
+                saved_x = x2.new_empty(0)
+                OF._count(3)
+            else:
+                qx = ops.mxfp8_quantize_tiled(x2)
+                OF._count(3)
+            y = ops.gemm_mxfp8(qx[0], qx[1], qw[0], qw[1])
         else:
             y = OF.gemm_nt(fake_quant(x2, recipe, 1), fake_quant(weight, recipe, 1))
-        ctx.save_for_backward(x2, weight)
+        ctx.save_for_backward(saved_x, weight)
         ctx.recipe, ctx.hp_wgrad, ctx.xshape, ctx.block_scaled = recipe, hp_wgrad, x.shape, block_scaled
         return y if x.dim() == 2 else y.view(*x.shape[:-1], weight.shape[0])
 
@@ -90,17 +113,34 @@ class _QuantLinearFn(torch.autograd.Function):
             dy2 = dy2.contiguous()
         dx = None
         bs = ctx.block_scaled
-        if ctx.needs_input_grad[0]:
+        ops = ext.require() if dy2.is_cuda else None
+        x_t = ctx.x_t
+        ctx.x_t = None
+        need_dx = ctx.needs_input_grad[0]
+        dgrad_native = need_dx and _mx_native(r, bs, weight.shape[0], weight.shape[1], dy2, weight)
+        wgrad_native = weight.requires_grad and not ctx.hp_wgrad and x_t is not None
+        q_dy = None
+        if dgrad_native and wgrad_native and _both_ok(dy2):
+            q_dy = ops.mxfp8_quantize_tiled_both(dy2)     # one read of dy for both gradients
+            OF._count()
+        if need_dx:
             # contraction over the output features: dy along its columns, w along its rows
-            if _mx_native(r, bs, weight.shape[0], weight.shape[1], dy2, weight):
-                dx = _mx_gemm(dy2, False, weight, True).view(ctx.xshape)
+            if dgrad_native:
+                qa = (q_dy[0], q_dy[1]) if q_dy is not None else ops.mxfp8_quantize_tiled(dy2)
+                qb = ops.mxfp8_quantize_tiled_t(weight)
+                OF._count(3)
+                dx = ops.gemm_mxfp8(qa[0], qa[1], qb[0], qb[1]).view(ctx.xshape)
             else:
                 dx = OF.gemm_nn(fake_quant(dy2, r, 1), fake_quant(weight, r, 0)).view(ctx.xshape)
         dw = None
         if weight.requires_grad:
             if ctx.hp_wgrad:
                 dw = OF._wgrad(dy2, x2, weight)
-            elif _mx_native(r, bs, dy2.shape[0], weight.shape[1], dy2, x2):   # contraction over the tokens
+            elif wgrad_native:                                            # contraction over the tokens
+                qa = (q_dy[2], q_dy[3]) if q_dy is not None else ops.mxfp8_quantize_tiled_t(dy2)
+                OF._count(2)
+                dw = OF._deliver_wgrad(weight, ops.gemm_mxfp8(qa[0], qa[1], x_t[0], x_t[1]))
+            elif _mx_native(r, bs, dy2.shape[0], weight.shape[1], dy2, x2):
                 dw = OF._deliver_wgrad(weight, _mx_gemm(dy2, True, x2, True))
             else:
                 dw = OF._wgrad(fake_quant(dy2, r, 0), fake_quant(x2, r, 0), weight)

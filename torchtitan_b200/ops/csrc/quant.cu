@@ -132,10 +132,14 @@ __global__ void mx_colwise_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* 
 // memory (16-byte chunks, XOR-swizzled by the row block so that the column reads below do not
 // collide); thread (c, b) then owns column c over row block b and writes 32 contiguous bytes, the
 // four threads of a column one 128-byte line.
+// kBoth: the same tile also yields the row-wise form (data_row [R, C] scaled along C, tiled scales over rows = R,
+// contraction = C), so an operand that two GEMMs contract over different dimensions is read from memory once:
+// thread (r, h) owns the 32 columns of half h of tile row r.
 constexpr int kTqRows = 128, kTqCols = 64;
+template <bool kBoth>
 __global__ void __launch_bounds__(256)
 mx_transpose_tiled_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* __restrict__ data, uint8_t* __restrict__ scales,
-                          int R, int C) {
+                          uint8_t* __restrict__ data_row, uint8_t* __restrict__ scales_row, int R, int C) {
   __shared__ __align__(16) uint8_t tile[kTqRows * kTqCols * 2];
   const int r0 = blockIdx.y * kTqRows, c0 = blockIdx.x * kTqCols;
   // load: 1024 chunks of 8 elements, 4 per thread (row = chunk / 8)
@@ -148,6 +152,33 @@ mx_transpose_tiled_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* __restri
     *reinterpret_cast<uint4*>(tile + r * 128 + ((cc ^ ((r >> 5) * 2)) << 4)) = v;
   }
   __syncthreads();
+  if (kBoth) {
+    const int r = threadIdx.x >> 1, h = threadIdx.x & 1;
+    if (c0 + h * 32 < C) {
+      float v[32];
+      float amax = 0.f;
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const int cc = h * 4 + q;
+        const uint4 raw = *reinterpret_cast<const uint4*>(tile + r * 128 + ((cc ^ ((r >> 5) * 2)) << 4));
+        unpack8(*reinterpret_cast<const bf16x8*>(&raw), *reinterpret_cast<float(*)[8]>(v + q * 8));
+      }
+#pragma unroll
+      for (int i = 0; i < 32; ++i) amax = fmaxf(amax, fabsf(v[i]));
+      const uint32_t e = e8m0_rceil(amax);
+      const float inv = e8m0_inverse(e);
+      uint32_t w[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) w[i] = to_e4m3x4(v[4 * i] * inv, v[4 * i + 1] * inv, v[4 * i + 2] * inv, v[4 * i + 3] * inv);
+      uint4* dst = reinterpret_cast<uint4*>(data_row + (int64_t)(r0 + r) * C + c0 + h * 32);
+      dst[0] = make_uint4(w[0], w[1], w[2], w[3]);
+      dst[1] = make_uint4(w[4], w[5], w[6], w[7]);
+      const int row = r0 + r;
+      const int blk = (c0 >> 5) + h;
+      const int64_t atom = (int64_t)(row >> 7) * (C >> 7) + (blk >> 2);
+      scales_row[atom * 512 + (row & 31) * 16 + ((row & 127) >> 5) * 4 + (blk & 3)] = (uint8_t)e;
+    }
+  }
   const int b = threadIdx.x & 3, c = threadIdx.x >> 2;
   if (c0 + c >= C) return;
   const int cc = (c >> 3) ^ (b * 2);
@@ -298,12 +329,34 @@ std::tuple<at::Tensor, at::Tensor> mxfp8_quantize_tiled_t(const at::Tensor& x) {
   auto scales = C % 128 == 0 ? at::empty({n_sf}, x.options().dtype(at::kByte)) : at::zeros({n_sf}, x.options().dtype(at::kByte));
   if (R > 0 && C > 0) {
     dim3 grid((unsigned)((C + kTqCols - 1) / kTqCols), (unsigned)(R / kTqRows));
-    mx_transpose_tiled_kernel<<<grid, 256, 0, at::cuda::getCurrentCUDAStream()>>>(
-        reinterpret_cast<const __nv_bfloat16*>(x.data_ptr()), data.data_ptr<uint8_t>(), scales.data_ptr<uint8_t>(), (int)R,
-        (int)C);
+    mx_transpose_tiled_kernel<false><<<grid, 256, 0, at::cuda::getCurrentCUDAStream()>>>(
+        reinterpret_cast<const __nv_bfloat16*>(x.data_ptr()), data.data_ptr<uint8_t>(), scales.data_ptr<uint8_t>(), nullptr,
+        nullptr, (int)R, (int)C);
     C10_CUDA_KERNEL_LAUNCH_CHECK();
   }
   return {data, scales};
+}
+
+// Both MXFP8 forms of x [R, C] from one read: (row-wise data [R, C], its tiled scales, transposed data [C, R] scaled
+// along R, its tiled scales), i.e. mxfp8_quantize_tiled(x) and mxfp8_quantize_tiled_t(x).  R % 128 == 0, C % 128 == 0.
+std::tuple<at::Tensor, at::Tensor, at::Tensor, at::Tensor> mxfp8_quantize_tiled_both(const at::Tensor& x) {
+  check_q_input(x, 0);
+  TORCH_CHECK(x.size(0) % 128 == 0 && x.size(1) % 128 == 0, "mxfp8_quantize_tiled_both: both dimensions must be multiples of 128");
+  c10::cuda::CUDAGuard guard(x.device());
+  const int64_t R = x.size(0), C = x.size(1);
+  auto bopt = x.options().dtype(at::kByte);
+  auto data_row = at::empty({R, C}, bopt);
+  auto scales_row = at::empty({R / 128 * (C / 128) * 512}, bopt);
+  auto data_t = at::empty({C, R}, bopt);
+  auto scales_t = at::empty({C / 128 * (R / 128) * 512}, bopt);
+  if (R > 0 && C > 0) {
+    dim3 grid((unsigned)(C / kTqCols), (unsigned)(R / kTqRows));
+    mx_transpose_tiled_kernel<true><<<grid, 256, 0, at::cuda::getCurrentCUDAStream()>>>(
+        reinterpret_cast<const __nv_bfloat16*>(x.data_ptr()), data_t.data_ptr<uint8_t>(), scales_t.data_ptr<uint8_t>(),
+        data_row.data_ptr<uint8_t>(), scales_row.data_ptr<uint8_t>(), (int)R, (int)C);
+    C10_CUDA_KERNEL_LAUNCH_CHECK();
+  }
+  return {data_row, scales_row, data_t, scales_t};
 }
 
 at::Tensor mxfp8_fake_quant(const at::Tensor& x, int64_t axis) {
