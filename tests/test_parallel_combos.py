@@ -50,3 +50,30 @@ def test_pipeline_stages_with_sharded_parameters(tmp_path):
     run_distributed(_run, 4, pp + ["--parallelism.fsdp_reshard_after_forward", "always"], b, 256, timeout=400)
     ra, rb = torch.load(a), torch.load(b)
     assert torch.allclose(ra, rb, atol=1e-5), (ra, rb)
+
+
+def test_local_tensor_mode_validates_the_sharding_plan():
+    """comm.mode = local_tensor: one process walks over 8 emulated ranks (dp_shard 4 x tp 2) and checks that their
+    shards tile every parameter exactly once; a plan with a hole is reported."""
+    from torchtitan_b200.config import ConfigManager
+    from torchtitan_b200.parallel import local_plan
+
+    cfg = ConfigManager().parse_args([
+        "--module", "llama3", "--config", "llama3_debugmodel", "--training.num_tokens_per_microbatch_per_dp_rank", "64",
+        "--training.max_context_length", "64", "--parallelism.tensor_parallel_degree", "2", "--comm.mode", "local_tensor"])
+    covered = local_plan.validate_plan(cfg, world=8)
+    assert any("wqkv" in k for k in covered) and all(v > 0 for v in covered.values())
+    orig = local_plan._rank_plan
+
+    def broken(config, world, rank):
+        owned, total = orig(config, world, rank)
+        if rank == 3:
+            owned.pop(next(iter(owned)))
+        return owned, total
+
+    local_plan._rank_plan = broken
+    try:
+        with pytest.raises(RuntimeError, match="does not tile"):
+            local_plan.validate_plan(cfg, world=8)
+    finally:
+        local_plan._rank_plan = orig

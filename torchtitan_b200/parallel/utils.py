@@ -37,6 +37,9 @@ def init_distributed(comm_config, device: torch.device, *, dump_folder: str = ".
         world = int(os.environ.get("NGPU", os.environ.get("WORLD_SIZE", "1")))
         dist.init_process_group("fake", rank=rank, world_size=world, store=FakeStore())
         return world
+    if mode == "torchcomms":
+        logger.warning("comm.mode = torchcomms: the torchcomms package is not part of this build; using the default "
+                       "torch.distributed process groups (NCCL / gloo)")
     if world == 1 and "MASTER_ADDR" not in os.environ:
         return 1
 

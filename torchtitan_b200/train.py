@@ -26,6 +26,12 @@ def main(argv: list[str] | None = None) -> None:
     debug = getattr(config, "debug", None)
     sl.init_structured_logger("training", getattr(config, "dump_folder", "./outputs"),
                               enable=bool(debug and debug.enable_structured_logging))
+    if getattr(getattr(config, "comm", None), "mode", "default") == "local_tensor":
+        # one process emulates every rank and checks the sharding plan; nothing is trained (as in the reference)
+        from torchtitan_b200.parallel.local_plan import validate_plan
+
+        validate_plan(config)
+        return
     trainer = None
     seed_ckpt = bool(getattr(getattr(config, "checkpoint", None), "create_seed_checkpoint", False))
     try:
