@@ -82,6 +82,12 @@ def test_nvlink_engine_matches_nccl(tmp_path):
     run_distributed(_train, 2, "nvlink", b, backend="nccl")
     ra, rb = torch.load(a), torch.load(b)
     assert torch.allclose(ra["losses"], rb["losses"], atol=2e-2), (ra["losses"], rb["losses"])
+    # race detection: with the gradient buffers poisoned (NaN) as soon as every rank has finished reading them, a
+    # stale read anywhere in the step would turn the losses into NaN; they must stay what they were
+    c = str(tmp_path / "canary.pt")
+    run_distributed(_train, 2, "nvlink", c, backend="nccl", env={"TB200_SYMM_CANARY": "1"})
+    rc = torch.load(c)
+    assert torch.isfinite(rc["losses"]).all() and torch.allclose(rb["losses"], rc["losses"], atol=1e-3), rc["losses"]
     # AdamW's g / (|g| + eps) turns last-bit differences of near-zero gradients (reduction order) into
     # up to one learning rate per step for single elements: bound the maximum loosely, the mean tightly
     d = (ra["params"] - rb["params"]).abs()
@@ -121,11 +127,15 @@ def _rs_ag(rank, world, out_path):
     torch.manual_seed(100 + rank)
     grad.copy_(torch.randn(n, device=dev))
     shard = torch.zeros(n // world, dtype=torch.float32, device=dev)
+    if rank == 1:
+        torch.cuda._sleep(400_000_000)     # arrival skew: this rank reaches the collective ~0.2 s late
     arena.reduce_scatter_accumulate(grad, shard, g, accumulate=False)
     gathered = [torch.empty(n, dtype=torch.bfloat16, device=dev) for _ in range(world)]
     dist.all_gather(gathered, grad)
     exp = sum(t.float() for t in gathered)[rank * (n // world):(rank + 1) * (n // world)]
     ok1 = torch.allclose(shard, exp, atol=1e-5)
+    if rank == 0:
+        torch.cuda._sleep(400_000_000)     # and the other rank late for the second one
     arena.reduce_scatter_accumulate(grad, shard, g, accumulate=True)
     ok2 = torch.allclose(shard, 2 * exp, atol=1e-4)
     for a in arena._arenas.values():

@@ -624,6 +624,12 @@ class ShardedModel:
             cs = self._comm_stream
             with torch.cuda.stream(cs) if cs is not None else contextlib.nullcontext():
                 self._symm.barrier_all()
+                from . import symm as _symm_mod
+
+                if _symm_mod._CANARY:      # race detection aid: nobody may read these gradients any more
+                    for u in self.units:
+                        if u.size > 1 and (u.pool is None or u.private_grad):
+                            u.flat_grad.fill_(float("nan"))
             self._rs_unfenced = False
         if self._comm_stream is not None:
             torch.cuda.current_stream(self.device).wait_stream(self._comm_stream)

@@ -93,6 +93,8 @@ class StatusMonitor:
 status_monitor = StatusMonitor()
 
 _FLAG_SLOTS = 64
+# TB200_SYMM_CANARY=1: symmetric gradient buffers are filled with NaN once every rank has finished reading them
+_CANARY = os.environ.get("TB200_SYMM_CANARY", "0") == "1"
 
 
 def symm_available() -> bool:
@@ -218,6 +220,10 @@ class SymmetricArena:
                                           flat_grad.dtype == torch.bfloat16, accumulate)
         if trailing_barrier:
             arena.barrier()
+            if _CANARY:
+                # race detection aid: after the fence nobody may read these gradients again; poison them so that a
+                # stale read (a missing barrier, a wrong buffer) shows up as NaN in the loss instead of going unnoticed
+                flat_grad.fill_(float("nan"))
 
     def adamw_allgather(self, unit, runs, groups, step: int, grad_scale: torch.Tensor, grad: torch.Tensor) -> None:
         """AdamW on this rank's shard with the weight all-gather fused in (peer stores)."""
