@@ -84,3 +84,25 @@ def test_checkpoint_compat_script_same_revision(tmp_path):
     straight = cc.run(root, args, str(tmp_path / "s"), 4, 1)
     assert [s for s, _ in a] == [1, 2] and [s for s, _ in resumed] == [3, 4]
     assert resumed == straight[2:]
+
+
+def test_operator_tracer_and_html_report(tmp_path):
+    import torch
+
+    from torchtitan_b200.tools.numerics import OperatorTracer, html_report
+
+    torch.manual_seed(0)
+    net = torch.nn.Sequential(torch.nn.Linear(8, 16), torch.nn.GELU(), torch.nn.Linear(16, 4))
+    x = torch.randn(5, 8)
+    with OperatorTracer(net) as a:
+        net(x).sum().backward()
+    with torch.no_grad():
+        net[2].weight.mul_(1.5)
+    with OperatorTracer(net) as b:
+        net(x).sum().backward()
+    assert any("addmm" in r["name"] or "mm" in r["name"] for r in a.records)
+    assert any(r["name"].startswith("2::") for r in a.records)          # tagged with the executing module
+    out = tmp_path / "report.html"
+    n = html_report(a, b, str(out))
+    text = out.read_text()
+    assert n > 0 and "class='diff'" in text and "class='same'" in text
