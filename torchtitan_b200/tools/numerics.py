@@ -29,7 +29,7 @@ def tensor_record(t: torch.Tensor) -> dict:
     f = t.detach().float()
     fin = torch.isfinite(f)
     ok = f[fin] if not bool(fin.all()) else f
-    raw = t.detach().contiguous().cpu()
+    raw = t.detach().contiguous().cpu().reshape(-1)     # (0-d tensors cannot be viewed as bytes)
     digest = hashlib.sha1(raw.view(torch.uint8).numpy().tobytes() if raw.numel() else b"").hexdigest()[:16]
     return {"shape": list(t.shape), "dtype": str(t.dtype).replace("torch.", ""),
             "mean": float(ok.mean()) if ok.numel() else 0.0, "std": float(ok.std()) if ok.numel() > 1 else 0.0,
