@@ -39,7 +39,7 @@ def test_float8_rowwise():
     ops = ext.require()
     x = _input(200, 320, seed=3)
     fq = ops.float8_rowwise_fake_quant(x)
-    expect = ref.float8_rowwise_fake_quant(x.cpu()).cuda()
+    expect = ref.float8_rowwise_fake_quant(x.cpu(), pow2=False).cuda()
     # same fp32 quotient on both sides; allow one e4m3 step in a vanishing fraction of elements
     row_max = expect.float().abs().amax(dim=1, keepdim=True)
     assert ((fq.float() - expect.float()).abs() <= row_max * 2 ** -3).all()
@@ -120,13 +120,33 @@ def test_gemm_mxfp8_block_scaled(M, N, K, variant):
     assert (err <= 1e-2 * want.abs() + 1e-3 * want.abs().max()).all(), err.max().item()
 
 
-def test_quant_linear_block_scaled_matches_emulated():
+def test_float8_pow2_quantisers_match_reference():
+    """Row-wise float8 with power-of-two scales in the block-scaled operand format: data and exponents against the
+    PyTorch restatement, for both operand orientations."""
+    ops = ext.require()
+    x = _input(256, 384, seed=9)
+    e_row = ref.float8_pow2_exponents(x.float().abs().amax(dim=1)).contiguous()
+    d, s_ = ops.float8_pow2_quantize_tiled(x, e_row)
+    scale = torch.exp2(e_row.float() - 127.0)[:, None]
+    want = (x.float() / scale).clamp(-448, 448).to(torch.float8_e4m3fn)
+    assert torch.equal(d.view(torch.float8_e4m3fn).float(), want.float())
+    assert torch.equal(_untile(s_, 256, 384), e_row[:, None].expand(256, 384 // 32))
+    e_col = ref.float8_pow2_exponents(x.float().abs().amax(dim=0)).contiguous()
+    dt, st = ops.float8_pow2_quantize_tiled_t(x, e_col)
+    scale_c = torch.exp2(e_col.float() - 127.0)[None, :]
+    want_t = (x.float() / scale_c).clamp(-448, 448).to(torch.float8_e4m3fn).float().t()
+    assert torch.equal(dt.view(torch.float8_e4m3fn).float(), want_t)
+    assert torch.equal(_untile(st, 384, 256), e_col[:, None].expand(384, 256 // 32))
+
+
+@pytest.mark.parametrize("recipe", ["mxfp8", "float8_rowwise"])
+def test_quant_linear_block_scaled_matches_emulated(recipe):
     from torchtitan_b200.components.quantization.linear import QuantLinear
 
     ext.require()
     outs = []
     for block_scaled in (True, False):
-        lin = QuantLinear.Config(in_features=256, out_features=384, recipe="mxfp8", block_scaled=block_scaled).build()
+        lin = QuantLinear.Config(in_features=256, out_features=384, recipe=recipe, block_scaled=block_scaled).build()
         lin.init_states(seed=0)
         lin = lin.cuda().bfloat16()
         g = torch.Generator(device="cuda").manual_seed(5)

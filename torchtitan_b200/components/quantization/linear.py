@@ -15,6 +15,9 @@ on e4m3 bytes and e8m0 scales; the operands that are contracted over their rows 
 transposing kernel so that both arrive K-major).  Otherwise, and for ``float8_rowwise``, the GEMM
 runs on the operands' *exact* fp8 values held in bf16 (every e4m3 x 2^e product is representable
 in bf16) on the tcgen05 bf16 GEMM with fp32 accumulation: the same numerics at bf16 throughput.
+``float8_rowwise`` uses power-of-two row scales (the reference recipe's ``round_scales_to_power_of_2``), which are
+e8m0 scales that are equal along a row: on a GPU its GEMMs therefore run on the same block-scaled kernel, with the
+quantisers taking the per-row exponents as an input (``float8_pow2_quantize_tiled`` / ``_t``).
 On CPU the same math runs in PyTorch (``ops.reference``), which is also the oracle of the kernel
 tests.  ``block_scaled = False`` in the layer's config forces the emulated path.
 """
@@ -40,11 +43,7 @@ def fake_quant(x: torch.Tensor, recipe: str, axis: int) -> torch.Tensor:
         return ref.mxfp8_fake_quant(x, axis)
     if recipe == "float8_rowwise":
         xt = x if axis == 1 else x.t()
-        if x.is_cuda and x.dtype == torch.bfloat16 and xt.shape[1] % 8 == 0:
-            OF._count()
-            out = ext.require().float8_rowwise_fake_quant(xt.contiguous())
-        else:
-            out = ref.float8_rowwise_fake_quant(xt)
+        out = ref.float8_rowwise_fake_quant(xt)      # power-of-two row scales (tensor ops; the emulated path only)
         return out if axis == 1 else out.t()
     raise ValueError(f"unknown quantisation recipe '{recipe}'")
 
@@ -65,6 +64,31 @@ def _mx_gemm(a: torch.Tensor, a_rows_contracted: bool, b: torch.Tensor, b_rows_c
     qa = ops.mxfp8_quantize_tiled_t(a) if a_rows_contracted else ops.mxfp8_quantize_tiled(a)
     qb = ops.mxfp8_quantize_tiled_t(b) if b_rows_contracted else ops.mxfp8_quantize_tiled(b)
     return ops.gemm_mxfp8(qa[0], qa[1], qb[0], qb[1])
+
+
+def _f8_native(recipe: str, block_scaled: bool, contraction: int, n_out: int, *ts: torch.Tensor) -> bool:
+    """Whether a float8 row-wise GEMM can run on the block-scaled tensor-core kernel (power-of-two row scales are
+    e8m0 scales that happen to be equal along a row)."""
+    return (block_scaled and recipe == "float8_rowwise" and contraction > 0 and contraction % 128 == 0 and n_out % 8 == 0
+            and all(t.is_cuda and t.dtype == torch.bfloat16 and t.shape[1] % 8 == 0 for t in ts) and ext.available())
+
+
+def _f8_operand(t: torch.Tensor, rows_contracted: bool):
+    """Quantise ``t`` for a float8 row-wise GEMM: one power-of-two scale per output row, i.e. per row of ``t`` when it
+    is given as [rows, contraction] and per column when it is given as [contraction, rows]."""
+    ops = ext.require()
+    OF._count(2)
+    if rows_contracted:
+        exps = ref.float8_pow2_exponents(t.abs().amax(dim=0))
+        return ops.float8_pow2_quantize_tiled_t(t, exps.contiguous())
+    exps = ref.float8_pow2_exponents(t.abs().amax(dim=1))
+    return ops.float8_pow2_quantize_tiled(t, exps.contiguous())
+
+
+def _f8_gemm(a: torch.Tensor, a_rows_contracted: bool, b: torch.Tensor, b_rows_contracted: bool) -> torch.Tensor:
+    qa, qb = _f8_operand(a, a_rows_contracted), _f8_operand(b, b_rows_contracted)
+    OF._count()
+    return ext.require().gemm_mxfp8(qa[0], qa[1], qb[0], qb[1])
 
 
 def _both_ok(t: torch.Tensor) -> bool:
@@ -98,6 +122,8 @@ class _QuantLinearFn(torch.autograd.Function):
                 qx = ops.mxfp8_quantize_tiled(x2)
                 OF._count(3)
             y = ops.gemm_mxfp8(qx[0], qx[1], qw[0], qw[1])
+        elif _f8_native(recipe, block_scaled, x2.shape[1], weight.shape[0], x2, weight):
+            y = _f8_gemm(x2, False, weight, False)
         else:
             y = OF.gemm_nt(fake_quant(x2, recipe, 1), fake_quant(weight, recipe, 1))
         ctx.save_for_backward(saved_x, weight)
@@ -130,6 +156,8 @@ class _QuantLinearFn(torch.autograd.Function):
                 qb = ops.mxfp8_quantize_tiled_t(weight)
                 OF._count(3)
                 dx = ops.gemm_mxfp8(qa[0], qa[1], qb[0], qb[1]).view(ctx.xshape)
+            elif _f8_native(r, bs, weight.shape[0], weight.shape[1], dy2, weight):
+                dx = _f8_gemm(dy2, False, weight, True).view(ctx.xshape)
             else:
                 dx = OF.gemm_nn(fake_quant(dy2, r, 1), fake_quant(weight, r, 0)).view(ctx.xshape)
         dw = None
@@ -142,6 +170,8 @@ class _QuantLinearFn(torch.autograd.Function):
                 dw = OF._deliver_wgrad(weight, ops.gemm_mxfp8(qa[0], qa[1], x_t[0], x_t[1]))
             elif _mx_native(r, bs, dy2.shape[0], weight.shape[1], dy2, x2):
                 dw = OF._deliver_wgrad(weight, _mx_gemm(dy2, True, x2, True))
+            elif _f8_native(r, bs, dy2.shape[0], weight.shape[1], dy2, x2):
+                dw = OF._deliver_wgrad(weight, _f8_gemm(dy2, True, x2, True))
             else:
                 dw = OF._wgrad(fake_quant(dy2, r, 0), fake_quant(x2, r, 0), weight)
         return dx, dw, None, None, None

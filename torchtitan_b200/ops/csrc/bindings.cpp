@@ -79,6 +79,8 @@ at::Tensor gemm_mxfp8_grouped(const at::Tensor& a, const at::Tensor& sfa, const 
 void gemm_mx_set_debug(int64_t v);
 std::tuple<at::Tensor, at::Tensor> mxfp8_quantize_tiled_t(const at::Tensor& x);
 std::tuple<at::Tensor, at::Tensor, at::Tensor, at::Tensor> mxfp8_quantize_tiled_both(const at::Tensor& x);
+std::tuple<at::Tensor, at::Tensor> float8_pow2_quantize_tiled(const at::Tensor& x, const at::Tensor& exps);
+std::tuple<at::Tensor, at::Tensor> float8_pow2_quantize_tiled_t(const at::Tensor& x, const at::Tensor& exps);
 at::Tensor mxfp8_dequantize(const at::Tensor& data, const at::Tensor& scales, int64_t axis);
 std::tuple<at::Tensor, at::Tensor> float8_rowwise_quantize(const at::Tensor& x);
 at::Tensor float8_rowwise_fake_quant(const at::Tensor& x);
@@ -132,6 +134,8 @@ TORCH_LIBRARY(tb200, m) {
   m.def("gemm_mx_set_debug(int v) -> ()", &tb200::gemm_mx_set_debug);
   m.def("mxfp8_quantize_tiled_t(Tensor x) -> (Tensor, Tensor)", &tb200::mxfp8_quantize_tiled_t);
   m.def("mxfp8_quantize_tiled_both(Tensor x) -> (Tensor, Tensor, Tensor, Tensor)", &tb200::mxfp8_quantize_tiled_both);
+  m.def("float8_pow2_quantize_tiled(Tensor x, Tensor exps) -> (Tensor, Tensor)", &tb200::float8_pow2_quantize_tiled);
+  m.def("float8_pow2_quantize_tiled_t(Tensor x, Tensor exps) -> (Tensor, Tensor)", &tb200::float8_pow2_quantize_tiled_t);
   m.def("mxfp8_dequantize(Tensor data, Tensor scales, int axis) -> Tensor", &tb200::mxfp8_dequantize);
   m.def("float8_rowwise_quantize(Tensor x) -> (Tensor, Tensor)", &tb200::float8_rowwise_quantize);
   m.def("float8_rowwise_fake_quant(Tensor x) -> Tensor", &tb200::float8_rowwise_fake_quant);

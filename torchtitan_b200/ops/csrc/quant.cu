@@ -47,7 +47,8 @@ __device__ __forceinline__ float from_e4m3(uint32_t byte) {
 // through tcgen05.cp: byte (r % 32) * 16 + (r / 32) * 4 + b inside atom (row tile, k tile).
 template <bool kFake, bool kTiled = false>
 __global__ void mx_rowwise_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* __restrict__ data,
-                                  uint8_t* __restrict__ scales, __nv_bfloat16* __restrict__ fake, int64_t n_vec, int C) {
+                                  uint8_t* __restrict__ scales, __nv_bfloat16* __restrict__ fake, int64_t n_vec, int C,
+                                  const uint8_t* __restrict__ row_exp = nullptr) {
   const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;   // vector of 8 elements
   const bool live = i < n_vec;
   float v[8] = {0, 0, 0, 0, 0, 0, 0, 0};
@@ -58,7 +59,8 @@ __global__ void mx_rowwise_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* 
   amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
   amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
   if (!live) return;
-  const uint32_t e = e8m0_rceil(amax);
+  // row_exp: one given exponent per row (float8 row-wise scaling with power-of-two scales) instead of one per block
+  const uint32_t e = row_exp != nullptr ? (uint32_t)row_exp[(i * 8) / C] : e8m0_rceil(amax);
   const float inv = e8m0_inverse(e);
   const uint32_t lo = to_e4m3x4(v[0] * inv, v[1] * inv, v[2] * inv, v[3] * inv);
   const uint32_t hi = to_e4m3x4(v[4] * inv, v[5] * inv, v[6] * inv, v[7] * inv);
@@ -139,7 +141,8 @@ constexpr int kTqRows = 128, kTqCols = 64;
 template <bool kBoth>
 __global__ void __launch_bounds__(256)
 mx_transpose_tiled_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* __restrict__ data, uint8_t* __restrict__ scales,
-                          uint8_t* __restrict__ data_row, uint8_t* __restrict__ scales_row, int R, int C) {
+                          uint8_t* __restrict__ data_row, uint8_t* __restrict__ scales_row, int R, int C,
+                          const uint8_t* __restrict__ col_exp = nullptr) {
   __shared__ __align__(16) uint8_t tile[kTqRows * kTqCols * 2];
   const int r0 = blockIdx.y * kTqRows, c0 = blockIdx.x * kTqCols;
   // load: 1024 chunks of 8 elements, 4 per thread (row = chunk / 8)
@@ -190,7 +193,8 @@ mx_transpose_tiled_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* __restri
     v[i] = __bfloat162float(*reinterpret_cast<const __nv_bfloat16*>(src + i * 128));
     amax = fmaxf(amax, fabsf(v[i]));
   }
-  const uint32_t e = e8m0_rceil(amax);
+  // col_exp: one given exponent per column of x, i.e. per output row (float8 row-wise scaling, power-of-two scales)
+  const uint32_t e = col_exp != nullptr ? (uint32_t)col_exp[c0 + c] : e8m0_rceil(amax);
   const float inv = e8m0_inverse(e);
   uint32_t w[8];
 #pragma unroll
@@ -357,6 +361,46 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor, at::Tensor> mxfp8_quantize_tiled_
     C10_CUDA_KERNEL_LAUNCH_CHECK();
   }
   return {data_row, scales_row, data_t, scales_t};
+}
+
+// Float8 row-wise scaling with power-of-two scales, in the operand format of the block-scaled GEMM: every 32-element
+// block of a row carries the row's exponent `exps[row]` (e8m0).  x [R, C], C % 128 == 0.
+std::tuple<at::Tensor, at::Tensor> float8_pow2_quantize_tiled(const at::Tensor& x, const at::Tensor& exps) {
+  check_q_input(x, 1);
+  const int64_t R = x.size(0), C = x.size(1);
+  TORCH_CHECK(C % 128 == 0, "float8_pow2_quantize_tiled: the contraction dimension must be a multiple of 128");
+  TORCH_CHECK(exps.is_cuda() && exps.scalar_type() == at::kByte && exps.is_contiguous() && exps.numel() == R);
+  c10::cuda::CUDAGuard guard(x.device());
+  auto data = at::empty({R, C}, x.options().dtype(at::kByte));
+  const int64_t n_sf = (R + 127) / 128 * (C / 128) * 512;
+  auto scales = R % 128 == 0 ? at::empty({n_sf}, x.options().dtype(at::kByte)) : at::zeros({n_sf}, x.options().dtype(at::kByte));
+  const int64_t n_vec = R * C / 8;
+  if (n_vec > 0)
+    mx_rowwise_kernel<false, true><<<(unsigned)((n_vec + 255) / 256), 256, 0, at::cuda::getCurrentCUDAStream()>>>(
+        reinterpret_cast<const __nv_bfloat16*>(x.data_ptr()), data.data_ptr<uint8_t>(), scales.data_ptr<uint8_t>(), nullptr,
+        n_vec, (int)C, exps.data_ptr<uint8_t>());
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+  return {data, scales};
+}
+
+// The same for an operand contracted over its rows: x [R, C] -> data [C, R], output row c scaled by exps[c]; R % 128 == 0.
+std::tuple<at::Tensor, at::Tensor> float8_pow2_quantize_tiled_t(const at::Tensor& x, const at::Tensor& exps) {
+  check_q_input(x, 0);
+  const int64_t R = x.size(0), C = x.size(1);
+  TORCH_CHECK(R % 128 == 0, "float8_pow2_quantize_tiled_t: the contraction dimension (rows) must be a multiple of 128");
+  TORCH_CHECK(exps.is_cuda() && exps.scalar_type() == at::kByte && exps.is_contiguous() && exps.numel() == C);
+  c10::cuda::CUDAGuard guard(x.device());
+  auto data = at::empty({C, R}, x.options().dtype(at::kByte));
+  const int64_t n_sf = (C + 127) / 128 * (R / 128) * 512;
+  auto scales = C % 128 == 0 ? at::empty({n_sf}, x.options().dtype(at::kByte)) : at::zeros({n_sf}, x.options().dtype(at::kByte));
+  if (R > 0 && C > 0) {
+    dim3 grid((unsigned)((C + kTqCols - 1) / kTqCols), (unsigned)(R / kTqRows));
+    mx_transpose_tiled_kernel<false><<<grid, 256, 0, at::cuda::getCurrentCUDAStream()>>>(
+        reinterpret_cast<const __nv_bfloat16*>(x.data_ptr()), data.data_ptr<uint8_t>(), scales.data_ptr<uint8_t>(), nullptr,
+        nullptr, (int)R, (int)C, exps.data_ptr<uint8_t>());
+    C10_CUDA_KERNEL_LAUNCH_CHECK();
+  }
+  return {data, scales};
 }
 
 at::Tensor mxfp8_fake_quant(const at::Tensor& x, int64_t axis) {

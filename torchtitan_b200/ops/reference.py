@@ -339,7 +339,22 @@ def mxfp8_fake_quant(x: torch.Tensor, axis: int) -> torch.Tensor:
     return out.to(x.dtype)
 
 
-def float8_rowwise_fake_quant(x: torch.Tensor) -> torch.Tensor:
+def float8_pow2_exponents(amax: torch.Tensor) -> torch.Tensor:
+    """e8m0 byte of the smallest power of two >= amax / 448 (uint8; 1 for an all-zero row)."""
+    v = (amax.float() / 448.0).clamp_min(2.0 ** -126)
+    m, e = torch.frexp(v)                          # v = m * 2^e, m in [0.5, 1)
+    e = torch.where(m == 0.5, e - 1, e)            # exact powers of two keep their exponent
+    return (e + 127).clamp(1, 254).to(torch.uint8)
+
+
+def float8_rowwise_fake_quant(x: torch.Tensor, pow2: bool = True) -> torch.Tensor:
+    """Row-wise float8 (e4m3) round trip.  ``pow2`` rounds each row's scale up to a power of two, the default of the
+    reference's row-wise recipe (torchao ``round_scales_to_power_of_2``); it makes the scaled values exactly
+    representable products, which is what lets the GEMM run on the block-scaled tensor-core kernel."""
     xf = x.float()
-    scale = xf.abs().amax(dim=1, keepdim=True).clamp_min(1e-12) / 448.0
+    amax = xf.abs().amax(dim=1, keepdim=True)
+    if pow2:
+        scale = torch.exp2(float8_pow2_exponents(amax).float() - 127.0)
+    else:
+        scale = amax.clamp_min(1e-12) / 448.0
     return ((xf / scale).clamp(-448.0, 448.0).to(torch.float8_e4m3fn).float() * scale).to(x.dtype)
