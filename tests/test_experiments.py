@@ -315,3 +315,69 @@ def test_graph_trainer_passes_map_to_engine_settings(tmp_path):
     t.train()
     assert t.step == 2 and t.applied_passes == ["selective_remat", "fsdp_overlap"]
     t.close()
+
+
+def _ft_replica(rid, n, port, die_at, out, folder):
+    """A replica group = one single-process trainer; replica ``n - 1`` leaves between steps at ``die_at``."""
+    from datetime import timedelta
+
+    from torch.distributed import TCPStore
+
+    from torchtitan_b200.config import ConfigManager
+    from torchtitan_b200.experiments.ft import FaultToleranceConfig, FaultTolerantTrainer
+
+    store = TCPStore("127.0.0.1", port, world_size=n, is_master=(rid == 0), timeout=timedelta(seconds=60),
+                     wait_for_workers=True)
+    cfg = ConfigManager().parse_args([
+        "--module", "llama3", "--config", "llama3_debugmodel", "--training.num_tokens_per_microbatch_per_dp_rank", "64",
+        "--training.max_context_length", "64", "--training.mixed_precision_param", "float32", "--debug.seed", "0",
+        "--dump_folder", f"{folder}/r{rid}", "--debug.no-enable_structured_logging", "--checkpoint.no-enable",
+        "--dataloader.seed", str(10 + rid), "--metrics.log_freq", "100"])
+    ft = FaultToleranceConfig(enable=True, replica_id=rid, group_size=n, heartbeat_timeout_s=1.0, quorum_timeout_s=5.0)
+    t = FaultTolerantTrainer(cfg, fault_tolerance=ft, store=store)
+    it = t.batch_generator(t.dataloader)
+    members, losses = [], []
+    for step in range(6):
+        if rid == n - 1 and step == die_at:
+            return                                          # leaves between steps
+        t.step += 1
+        t.train_step(it)
+        t.checkpointer.save(t.step)
+        members.append(list(t.manager.members))
+        losses.append(float(t._last_loss))
+    w = torch.cat([u.master for e in t.engines for u in e.units])
+    torch.save({"members": members, "losses": losses, "w": w, "skipped": t.optimizers.skipped}, out.format(rid))
+    assert os.path.exists(os.path.join(cfg.dump_folder, f"ft-replica-{rid}", "dataloader.pt"))
+    if rid == 0:
+        time.sleep(1.0)
+    t.close()
+
+
+def test_fault_tolerant_trainer_survives_a_lost_replica(tmp_path):
+    """Two replica groups average gradients through the FT manager; one leaves after step 3, the other goes on alone
+    (its quorum shrinks) and keeps training."""
+    import torch.multiprocessing as mp
+
+    from tests.dist_utils import _free_port
+
+    port = _free_port()
+    out = str(tmp_path / "ft{}.pt")
+    ctx = mp.get_context("spawn")
+    procs = [ctx.Process(target=_ft_replica, args=(r, 2, port, 3, out, str(tmp_path))) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(240)
+        assert p.exitcode == 0
+    r0 = torch.load(out.format(0))
+    assert r0["members"][:3] == [[0, 1]] * 3 and r0["members"][-1] == [0]
+    assert all(l == l for l in r0["losses"]) and r0["skipped"] == 0
+
+
+def test_fragment_llm_covers_every_parameter_once():
+    from torchtitan_b200.experiments.ft import fragment_llm
+
+    _, model = _tiny_llama(layers=4)
+    frags = fragment_llm(model, 3)
+    ids = [id(p) for f in frags for p in f]
+    assert len(ids) == len(set(ids)) == len(list(model.parameters())) and len(frags) >= 2

@@ -56,11 +56,31 @@ class FTManager:
         self._errored = False
         self._comm = None
         self._t0 = clock()
+        self._hb_thread = None
         self.heartbeat()
 
     # -- liveness ------------------------------------------------------------------------
     def heartbeat(self) -> None:
         self.store.set(f"hb/{self.id}", repr(self.clock()))
+
+    def start_heartbeat_thread(self) -> None:
+        """Beat from a daemon thread, so that a replica busy inside a long training step is not taken for dead.
+        The thread ends with the process: a replica that exits (or is killed) stops beating."""
+        import threading
+
+        if self._hb_thread is not None:
+            return
+
+        def loop():
+            while True:
+                try:
+                    self.heartbeat()
+                except Exception:
+                    return
+                time.sleep(max(0.05, self.hb_timeout / 4))
+
+        self._hb_thread = threading.Thread(target=loop, daemon=True)
+        self._hb_thread.start()
 
     def _alive(self, rid: int) -> bool:
         if rid == self.id:
@@ -123,7 +143,12 @@ class FTManager:
     def _store_average(self, tensors, tag) -> None:
         buf = io.BytesIO()
         torch.save([t.detach().cpu() for t in tensors], buf)
-        self.store.set(f"ar/{self.step}/{tag}/{self.id}", buf.getvalue())
+        blob = buf.getvalue()
+        # the store is a control-plane service: large payloads travel in 1 MiB parts, the part count last
+        parts = [blob[i:i + (1 << 20)] for i in range(0, len(blob), 1 << 20)] or [b""]
+        for i, part in enumerate(parts):
+            self.store.set(f"ar/{self.step}/{tag}/{self.id}/{i}", part)
+        self.store.set(f"ar/{self.step}/{tag}/{self.id}", str(len(parts)))
         acc = None
         deadline = self.clock() + self.q_timeout
         for r in self.members:
@@ -134,7 +159,9 @@ class FTManager:
                     raise RuntimeError(f"replica {r} left during the average of step {self.step}")
                 self.heartbeat()
                 time.sleep(0.005)
-            vals = torch.load(io.BytesIO(self.store.get(key)))
+            n_parts = int(self.store.get(key).decode())
+            data = b"".join(self.store.get(f"{key}/{i}") for i in range(n_parts))
+            vals = torch.load(io.BytesIO(data))
             acc = vals if acc is None else [a + v for a, v in zip(acc, vals)]
         for t, a in zip(tensors, acc):
             t.copy_((a / len(self.members)).to(t.dtype))
