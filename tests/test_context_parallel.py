@@ -6,7 +6,7 @@ import torch
 from tests.dist_utils import run_distributed
 
 
-def _cp_fn(rank, world, mode, with_docs, out_path, window=None, use_sinks=False):
+def _cp_fn(rank, world, mode, with_docs, out_path, window=None, use_sinks=False, balancer="headtail"):
     import torch.distributed as dist
 
     from torchtitan_b200.models.common.attention import AttentionContext
@@ -25,7 +25,13 @@ def _cp_fn(rank, world, mode, with_docs, out_path, window=None, use_sinks=False)
     ref = OF.attention(qf, kf, vf, doc_ids=doc, window=window, sinks=sinks_ref)
     ref.backward(g)
 
-    cp = CPContext(group=dist.group.WORLD, size=world, rank=rank, mode=mode)
+    cp = CPContext(group=dist.group.WORLD, size=world, rank=rank, mode=mode, load_balancer=balancer)
+    if balancer == "ptrr":
+        from torchtitan_b200.parallel.context_parallel import ptrr_assignment
+
+        positions = torch.cat([torch.arange(10), torch.arange(15), torch.arange(7)]) if with_docs else torch.arange(T)
+        cp.assignment = ptrr_assignment(positions, world, chunks_per_rank=4)
+        assert sorted(c for a in cp.assignment for c in a) == list(range(4 * world))
     idx = shard_for_cp(cp, torch.arange(T), torch.arange(T), torch.arange(T))[3]
     ql, kl, vl = (t[idx].clone().requires_grad_() for t in (q, k, v))
     ctx = AttentionContext(doc_ids=None if doc is None else doc[idx], q_pos=idx, cp=cp)
@@ -61,6 +67,25 @@ def test_cp_attention_window_documents_and_sinks(tmp_path, mode):
     out = str(tmp_path / "cpw.pt")
     run_distributed(_cp_fn, 2, mode, True, out, 6, True)
     assert float(torch.load(out)) == 1.0
+
+
+@pytest.mark.parametrize("mode", ["allgather", "ring"])
+def test_cp_attention_with_ptrr_balancer(tmp_path, mode):
+    out = str(tmp_path / "cpp.pt")
+    run_distributed(_cp_fn, 2, mode, True, out, None, False, "ptrr")
+    assert float(torch.load(out)) == 1.0
+
+
+def test_ptrr_assignment_balances_uneven_documents():
+    from torchtitan_b200.parallel.context_parallel import ptrr_assignment
+
+    # one long document followed by many short ones: head-tail pairing would overload the ranks holding the long one
+    pos = torch.cat([torch.arange(4096)] + [torch.arange(64)] * 64)
+    a = ptrr_assignment(pos, 4, chunks_per_rank=8)
+    work = (pos.double() + 1).view(32, -1).sum(1)
+    loads = [sum(float(work[c]) for c in chunks) for chunks in a]
+    assert max(loads) / min(loads) < 1.15
+    assert all(len(c) == 8 for c in a)
 
 
 def test_headtail_chunks():

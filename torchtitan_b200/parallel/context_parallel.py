@@ -1,8 +1,9 @@
 """Context parallelism: tokens sharded over the cp group, K/V exchanged inside attention.
 
 Sharding.  The ``T`` tokens of a microbatch are cut into ``2*cp`` chunks; with the
-``headtail`` balancer rank r owns chunks ``r`` and ``2cp-1-r`` so causal work is even
-(parity: torchtitan/distributed/context_parallel/api.py:137-226).  Inputs, labels and
+``headtail`` balancer rank r owns chunks ``r`` and ``2cp-1-r`` so causal work is even; the ``ptrr``
+balancer cuts finer chunks and deals them by the work the batch's documents imply
+(``ptrr_assignment``; parity: torchtitan/distributed/context_parallel/api.py:137-226).  Inputs, labels and
 positions are sharded identically; RoPE uses the (sharded) positions, the causal /
 document mask uses the global token index ``q_pos`` of each local row.
 
@@ -30,7 +31,7 @@ from torchtitan_b200.ops import functional as OF
 
 from . import tp_ops
 
-__all__ = ["CPContext", "shard_for_cp", "cp_attention", "cp_chunk_ids", "unshard_from_cp"]
+__all__ = ["CPContext", "shard_for_cp", "cp_attention", "cp_chunk_ids", "unshard_from_cp", "ptrr_assignment"]
 
 
 @dataclass
@@ -39,22 +40,50 @@ class CPContext:
     size: int
     rank: int
     mode: str = "allgather"  # allgather | ring
-    load_balancer: str = "headtail"  # headtail | none
+    load_balancer: str = "headtail"  # headtail | ptrr | none
     nvlink: object | None = None  # parallel.cp_nvlink.CPNvlink: KV exchange by peer loads instead of NCCL
+    assignment: list | None = None  # ptrr: chunk ids per rank for the current batch (``ptrr_assignment``)
 
 
 def cp_chunk_ids(cp: CPContext, rank: int | None = None) -> list[int]:
     r = cp.rank if rank is None else rank
-    if cp.load_balancer == "headtail":
+    if cp.assignment is not None:
+        return list(cp.assignment[r])
+    if cp.load_balancer in ("headtail", "ptrr"):
         return [r, 2 * cp.size - 1 - r]
     return [2 * r, 2 * r + 1]
 
 
+def _num_chunks(cp: CPContext) -> int:
+    return cp.size * len(cp_chunk_ids(cp, 0))
+
+
 def _local_index(cp: CPContext, T: int, device, rank: int | None = None) -> torch.Tensor:
-    if T % (2 * cp.size):
-        raise ValueError(f"token count {T} must be divisible by 2*cp = {2 * cp.size}")
-    C = T // (2 * cp.size)
+    n = _num_chunks(cp)
+    if T % n:
+        raise ValueError(f"token count {T} must be divisible by the number of context-parallel chunks ({n})")
+    C = T // n
     return torch.cat([torch.arange(c * C, (c + 1) * C, device=device) for c in cp_chunk_ids(cp, rank)])
+
+
+def ptrr_assignment(positions: torch.Tensor, cp_size: int, chunks_per_rank: int = 4) -> list[list[int]]:
+    """Processing-time round-robin: cut the sequence into ``cp_size * chunks_per_rank`` chunks, estimate each chunk's
+    attention work from the document structure (a token at position ``p`` of its document attends to ``p + 1``
+    keys), sort the chunks by work and deal them to the ranks in snake order, heaviest first.  With packed documents
+    of uneven length this balances better than the fixed head-tail pairing, which assumes one long causal sequence
+    (parity: the reference's "ptrr" balancer, torchtitan/config/configs.py:246-255, built from the batch's mask).
+    ``positions``: the batch's per-token positions ``[T]`` (host tensor); every rank computes the same answer."""
+    T = positions.shape[-1]
+    n = cp_size * chunks_per_rank
+    if T % n:
+        raise ValueError(f"token count {T} must be divisible by cp * chunks_per_rank = {n}")
+    work = (positions.reshape(-1)[:T].to(torch.float64) + 1.0).view(n, T // n).sum(1)
+    order = torch.argsort(work, descending=True, stable=True).tolist()
+    out: list[list[int]] = [[] for _ in range(cp_size)]
+    for i, c in enumerate(order):
+        rnd, k = divmod(i, cp_size)
+        out[k if rnd % 2 == 0 else cp_size - 1 - k].append(c)
+    return [sorted(x) for x in out]
 
 
 def shard_for_cp(cp: CPContext, tokens, positions, labels):
@@ -146,8 +175,8 @@ class _CPAttentionFn(torch.autograd.Function):
         from torchtitan_b200.ops import flash as FL
 
         Tl, Hq, D = q.shape
-        C = Tl // 2
         ids = cp_chunk_ids(cp)
+        C = Tl // len(ids)
         window = int(window or 0)
         o32 = torch.zeros(Tl, Hq, D, dtype=torch.float32, device=q.device)
         lse = torch.full((Hq, Tl), float("-inf"), dtype=torch.float32, device=q.device)
@@ -188,8 +217,8 @@ class _CPAttentionFn(torch.autograd.Function):
         q, k, v, o, lse, kv_first, sinks = ctx.saved_tensors[:7]
         kv_first = kv_first if has_first else None
         Tl, Hq, D = q.shape
-        C = Tl // 2
         ids = cp_chunk_ids(cp)
+        C = Tl // len(ids)
         d_o = d_o.contiguous()
         dq = torch.zeros(Tl, Hq, D, dtype=torch.float32, device=q.device)
         d_sinks = None
@@ -286,8 +315,8 @@ def cp_attention(q, k, v, ctx, *, scale: float | None = None, window: int | None
     if scale is None:
         scale = 1.0 / math.sqrt(q.shape[-1])
     Tl = q.shape[0]
-    if Tl % 2:
-        raise ValueError("context parallelism needs an even number of local tokens (two chunks per rank)")
+    if Tl % len(cp_chunk_ids(cp)):
+        raise ValueError("the local token count must be a multiple of the number of chunks per rank")
     with torch.no_grad():
         kv_first = _global_kv_first(cp, ctx, Tl * cp.size, q.device)
     mode = "allgather" if cp.mode == "allgather" else "ring"

@@ -316,8 +316,12 @@ class Trainer(Configurable):
         if self.pdims.cp_enabled:
             if self._extra_inputs:
                 raise NotImplementedError("multimodal batches are not supported with context parallelism")
-            from torchtitan_b200.parallel.context_parallel import shard_for_cp
+            from torchtitan_b200.parallel.context_parallel import ptrr_assignment, shard_for_cp
 
+            if model.cp.load_balancer == "ptrr":
+                # the balancer is built from this batch's documents (host copy of the positions; same on every cp rank)
+                host_pos = inputs["positions"] if not inputs["positions"].is_cuda else inputs["positions"].cpu()
+                model.cp.assignment = ptrr_assignment(host_pos, model.cp.size)
             tokens, positions, labels, q_pos = shard_for_cp(model.cp, tokens, positions, labels)
         return tokens, positions, labels, q_pos
 
