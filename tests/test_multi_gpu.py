@@ -516,7 +516,8 @@ def _cp_flash(rank, world, mode, transport, out_path):
 
 
 @pytest.mark.skipif(_ngpu() < 2, reason="needs 2 GPUs")
-@pytest.mark.parametrize("mode,transport", [("allgather", "nccl"), ("ring", "nccl"), ("allgather", "nvlink")])
+@pytest.mark.parametrize("mode,transport", [("allgather", "nccl"), ("ring", "nccl"), ("allgather", "nvlink"),
+                                            ("ring", "nvlink")])
 def test_context_parallel_attention_on_flash_kernels(tmp_path, mode, transport):
     out = str(tmp_path / "cpf.pt")
     run_distributed(_cp_flash, 2, mode, transport, out, backend="nccl")

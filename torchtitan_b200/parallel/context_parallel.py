@@ -193,13 +193,10 @@ class _CPAttentionFn(torch.autograd.Function):
                 lse[:, j * C:(j + 1) * C] = l
             saved_kv = (kf, vf, order)
         else:
-            k_blk, v_blk = k.contiguous(), v.contiguous()
-            for step in range(cp.size):
+            for step, k_blk, v_blk in _ring_walk(cp, k, v):
                 src_ids = cp_chunk_ids(cp, (cp.rank - step) % cp.size)
                 _ring_blocks(FL.block_fwd, q, k_blk, v_blk, ids, src_ids, C, scale, window, kv_first,
                              lambda j, o, l: FL.merge_(o32[j * C:(j + 1) * C], lse[:, j * C:(j + 1) * C], o, l))
-                if step + 1 < cp.size:
-                    k_blk, v_blk = _ring_shift(k_blk, cp, +1), _ring_shift(v_blk, cp, +1)
         if sinks is not None:
             o32, lse = _apply_sinks(o32, lse, sinks)
         o = o32.to(q.dtype)
@@ -244,14 +241,21 @@ class _CPAttentionFn(torch.autograd.Function):
             dk = _scatter_sequence_grad(dkf, order, cp, k.dtype)
             dv = _scatter_sequence_grad(dvf, order, cp, v.dtype)
             return dq.to(q.dtype), dk, dv, d_sinks, None, None, None, None, None
-        # ring: the K/V chunks travel again, their gradient accumulators with them; one more hop brings
-        # every accumulator home
-        k_blk, v_blk = k.contiguous(), v.contiguous()
-        dk_acc = torch.zeros(k.shape, dtype=torch.float32, device=q.device)
-        dv_acc = torch.zeros(v.shape, dtype=torch.float32, device=q.device)
-        for step in range(cp.size):
-            src_ids = cp_chunk_ids(cp, (cp.rank - step) % cp.size)
-
+        # ring: the K/V chunks come by again.  Over NCCL their gradient accumulators travel with them (one more hop
+        # brings every accumulator home); over NVLink each rank keeps a full-size accumulator, indexed by source rank,
+        # and one reduce-scatter by peer loads delivers every rank's rows.
+        nv = cp.nvlink if (cp.nvlink is not None and k.is_cuda) else None
+        n = cp.size
+        if nv is not None:
+            dk_all = torch.zeros((n,) + tuple(k.shape), dtype=torch.float32, device=q.device)
+            dv_all = torch.zeros((n,) + tuple(v.shape), dtype=torch.float32, device=q.device)
+        else:
+            dk_acc = torch.zeros(k.shape, dtype=torch.float32, device=q.device)
+            dv_acc = torch.zeros(v.shape, dtype=torch.float32, device=q.device)
+        for step, k_blk, v_blk in _ring_walk(cp, k, v):
+            src = (cp.rank - step) % n
+            src_ids = cp_chunk_ids(cp, src)
+            dk_t, dv_t = (dk_all[src], dv_all[src]) if nv is not None else (dk_acc, dv_acc)
             for j, c in enumerate(ids):
                 for jj, c2 in enumerate(src_ids):
                     if c2 > c:
@@ -263,12 +267,56 @@ class _CPAttentionFn(torch.autograd.Function):
                                      lse[:, j * C:(j + 1) * C], scale, causal=True, causal_offset=(c - c2) * C,
                                      kv_first=kvf, window=window)
                     dq[j * C:(j + 1) * C] += g[0].float()
-                    dk_acc[jj * C:(jj + 1) * C] += g[1].float()
-                    dv_acc[jj * C:(jj + 1) * C] += g[2].float()
-            if step + 1 < cp.size:
-                k_blk, v_blk = _ring_shift(k_blk, cp, +1), _ring_shift(v_blk, cp, +1)
-            dk_acc, dv_acc = _ring_shift(dk_acc, cp, +1), _ring_shift(dv_acc, cp, +1)
+                    dk_t[jj * C:(jj + 1) * C] += g[1].float()
+                    dv_t[jj * C:(jj + 1) * C] += g[2].float()
+            if nv is None:
+                dk_acc, dv_acc = _ring_shift(dk_acc, cp, +1), _ring_shift(dv_acc, cp, +1)
+        if nv is not None:
+            dk_acc = nv.reduce_scatter(dk_all.view((n * k.shape[0],) + tuple(k.shape[1:])))
+            dv_acc = nv.reduce_scatter(dv_all.view((n * v.shape[0],) + tuple(v.shape[1:])))
         return dq.to(q.dtype), dk_acc.to(k.dtype), dv_acc.to(v.dtype), d_sinks, None, None, None, None, None
+
+
+def _ring_walk(cp: CPContext, k: torch.Tensor, v: torch.Tensor):
+    """Yields ``(step, k_block, v_block)``: at step ``s`` the K / V of rank ``rank - s``.
+
+    NCCL: the blocks are passed around the ring with ``batch_isend_irecv``.  NVLink (``cp.nvlink``): every rank
+    stages its K / V once in symmetric memory; the block of the next step is copied out of its owner's buffer on a
+    side stream (a peer-to-peer copy, no SM involved) while the attention kernels work on the current block."""
+    n = cp.size
+    k_blk, v_blk = k.contiguous(), v.contiguous()
+    nv = cp.nvlink if (cp.nvlink is not None and k.is_cuda) else None
+    if nv is None:
+        for step in range(n):
+            yield step, k_blk, v_blk
+            if step + 1 < n:
+                k_blk, v_blk = _ring_shift(k_blk, cp, +1), _ring_shift(v_blk, cp, +1)
+        return
+    nv.stage_pair(k_blk, v_blk)
+    main = torch.cuda.current_stream(k.device)
+    side = getattr(nv, "_side_stream", None)
+    if side is None:
+        side = nv._side_stream = torch.cuda.Stream(k.device)
+    nxt = None
+    for step in range(n):
+        if step + 1 < n:
+            src = (cp.rank - step - 1) % n
+            side.wait_stream(main)
+            with torch.cuda.stream(side):
+                pk, pv = nv.peer_pair(src, k_blk, v_blk)
+                nk, nv_ = torch.empty_like(k_blk), torch.empty_like(v_blk)
+                nk.copy_(pk)
+                nv_.copy_(pv)
+                ev = torch.cuda.Event()
+                ev.record(side)
+            nk.record_stream(main)
+            nv_.record_stream(main)
+            nxt = (nk, nv_, ev)
+        yield step, k_blk, v_blk
+        if step + 1 < n:
+            main.wait_event(nxt[2])
+            k_blk, v_blk = nxt[0], nxt[1]
+    nv.release()
 
 
 def _ring_blocks(block_fwd, q, k_blk, v_blk, ids, src_ids, C, scale, window, kv_first, sink):

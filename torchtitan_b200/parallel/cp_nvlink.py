@@ -65,6 +65,31 @@ class CPNvlink:
         self.arena.barrier()
         return out.view((n,) + tuple(full.shape[1:])).to(full.dtype)
 
+    # -- ring mode: staged K / V, peers copy a rank's block straight out of its symmetric buffer ------------------
+    def stage_pair(self, k: torch.Tensor, v: torch.Tensor) -> None:
+        """Put this rank's K and V where the peers can read them (two halves of the symmetric buffer) and fence."""
+        half = self.capacity // 2
+        for slot, t in enumerate((k, v)):
+            t = t.contiguous()
+            nbytes = t.numel() * t.element_size()
+            if nbytes > half:
+                raise ValueError(f"cp nvlink ring: {nbytes} bytes per tensor exceed half the staging buffer ({half})")
+            self.stage[slot * half: slot * half + nbytes].view(t.dtype).view(t.shape).copy_(t)
+        self.arena.barrier()
+
+    def peer_pair(self, rank: int, like_k: torch.Tensor, like_v: torch.Tensor):
+        """Views of rank ``rank``'s staged K and V (peer memory; read them with copies or plain loads only)."""
+        half = self.capacity // 2
+        out = []
+        for slot, t in enumerate((like_k, like_v)):
+            es = t.element_size()
+            out.append(self.arena.handle.get_buffer(rank, tuple(t.shape), t.dtype, (slot * half) // es))
+        return out
+
+    def release(self) -> None:
+        """Every rank has finished reading the staged tensors (before they are staged again)."""
+        self.arena.barrier()
+
     def check_status(self) -> None:
         v = int(self.arena.status.item())
         if v:
