@@ -6,21 +6,20 @@ stores every parameter as flat element ranges cut at arbitrary shard boundaries.
 unit therefore runs as
 
 1. momentum update and Nesterov blend on this rank's flat shard (element-wise);
-2. all-gather of the blended bf16 shard, so that every rank of the unit's group sees whole
-   matrices;
+2. a packed all-to-all sends every piece of the blended bf16 shard to the owner of its matrix (split sizes
+   from a static plan, no host read);
 3. owner-computes: every matrix (a 2-D parameter, one ``block_rows`` x C row block of it, or one
    expert of a 3-D stack) has one owner rank, chosen by longest-processing-time-first balancing of
    the Newton-Schulz cost ``steps * short^2 * (2 long + short)``; the owner runs the iteration on
-   the tensor-core GEMMs and writes the direction in place, every other rank writes zeros;
-4. reduce-scatter (bf16 sum of one value and zeros: exact) brings each rank the directions of its
-   own flat shard;
+   the tensor-core GEMMs;
+4. the reverse all-to-all brings each rank the directions of its own flat shard;
 5. decoupled weight decay and the update, with the learning rate adjusted to the matrix shape,
    on the fp32 master shard; the compute-dtype copy is refreshed for the parameter all-gather.
 
 Parity: torchtitan/distributed/flex_shard/dist_muon.py:252-640 (optimizer), :1810-1916 (the
 learning-rate adjustment, momentum preparation, update and Newton-Schulz math).  The reference
-moves matrices to their owners with a bucketed redistribution planner; here two collectives of the
-unit's size (the sizes FSDP already moves every step) do the same job on the flat layout.
+moves matrices to their owners with a bucketed redistribution planner (:1889-1920); here the flat layout makes the
+plan a list of contiguous pieces per (source, owner) pair.
 """
 
 from __future__ import annotations
@@ -130,6 +129,83 @@ def _plan_unit(u, groups: list[dict]) -> list[_Item]:
     return items
 
 
+def _a2a_plan(u, items):
+    """Static exchange plan of a unit: which pieces of which rank's flat shard belong to matrices of which owner.
+
+    ``send[o]``: ``(offset in my shard, length)`` pieces that go to owner ``o``; ``recv[s]``: ``(offset in my buffer of
+    owned matrices, length)`` pieces that arrive from rank ``s``.  Both sides walk the matrices in flat order, so the
+    pieces of a (source, owner) pair line up without any index exchange."""
+    S = u.shard_numel
+    owned_off, total = {}, 0
+    for it in items:
+        if it.owner == u.rank:
+            owned_off[it.offset] = total
+            total += it.rows * it.cols
+    send = [[] for _ in range(u.size)]
+    recv = [[] for _ in range(u.size)]
+    for it in items:
+        a0, b0 = it.offset, it.offset + it.rows * it.cols
+        for s_ in range(a0 // S, min(u.size - 1, (b0 - 1) // S) + 1):
+            a, b = max(a0, s_ * S), min(b0, (s_ + 1) * S)
+            if a >= b:
+                continue
+            if s_ == u.rank:
+                send[it.owner].append((a - s_ * S, b - a))
+            if it.owner == u.rank:
+                recv[s_].append((owned_off[it.offset] + (a - a0), b - a))
+    return send, recv, owned_off, total
+
+
+def _owner_compute_all_to_all(engine, u, items, groups, shard: torch.Tensor) -> torch.Tensor:
+    """Matrices travel to their owners and the directions travel back with two packed all-to-alls: every element
+    crosses the network once each way (an all-gather would deliver every matrix to every rank).  The split sizes come
+    from the static plan, so nothing is read back to the host.  Parity: the packed all-to-all reshard of
+    torchtitan/distributed/flex_shard/dist_muon.py:1889-1920."""
+    plans = engine.__dict__.setdefault("_muon_a2a", {})
+    if u.name not in plans:
+        plans[u.name] = _a2a_plan(u, items)
+    send, recv, owned_off, total = plans[u.name]
+    dev = shard.device
+    in_splits = [sum(n for _, n in send[o]) for o in range(u.size)]
+    out_splits = [sum(n for _, n in recv[s_]) for s_ in range(u.size)]
+    sendbuf = torch.empty(sum(in_splits), dtype=shard.dtype, device=dev)
+    pos = 0
+    for o in range(u.size):
+        for off, n in send[o]:
+            sendbuf[pos:pos + n].copy_(shard[off:off + n])
+            pos += n
+    recvbuf = torch.empty(sum(out_splits), dtype=shard.dtype, device=dev)
+    dist.all_to_all_single(recvbuf, sendbuf, output_split_sizes=out_splits, input_split_sizes=in_splits, group=u.group)
+    owned = torch.empty(total, dtype=shard.dtype, device=dev)
+    pos = 0
+    for s_ in range(u.size):
+        for off, n in recv[s_]:
+            owned[off:off + n].copy_(recvbuf[pos:pos + n])
+            pos += n
+    for it in items:
+        if it.owner != u.rank:
+            continue
+        h = groups[it.group_idx]
+        o0 = owned_off[it.offset]
+        mat = owned[o0:o0 + it.rows * it.cols].view(it.rows, it.cols)
+        mat.copy_(newton_schulz(mat, ns_coefficients=tuple(h["ns_coefficients"]), ns_steps=int(h["ns_steps"]),
+                                eps=float(h["eps"])))
+    # the way back: same pieces, roles swapped
+    pos = 0
+    for s_ in range(u.size):
+        for off, n in recv[s_]:
+            recvbuf[pos:pos + n].copy_(owned[off:off + n])
+            pos += n
+    dist.all_to_all_single(sendbuf, recvbuf, output_split_sizes=in_splits, input_split_sizes=out_splits, group=u.group)
+    dshard = torch.zeros(u.shard_numel, dtype=shard.dtype, device=dev)
+    pos = 0
+    for o in range(u.size):
+        for off, n in send[o]:
+            dshard[off:off + n].copy_(sendbuf[pos:pos + n])
+            pos += n
+    return dshard
+
+
 @torch.no_grad()
 def muon_unit_step(engine, u, groups: list[dict], runs, step: int, grad_scale) -> None:
     """One optimizer step of a unit that holds Muon parameters (its AdamW runs included)."""
@@ -169,23 +245,13 @@ def muon_unit_step(engine, u, groups: list[dict], runs, step: int, grad_scale) -
         shard[a:b].copy_(torch.lerp(gg, m_new, beta) if h["nesterov"] else m_new)
 
     if u.size > 1:
-        dist.all_gather_into_tensor(full, shard.clone(), group=u.group)
-    results = []
-    for it in items:
-        if it.owner != u.rank:
-            continue
-        h = groups[it.group_idx]
-        mat = full[it.offset:it.offset + it.rows * it.cols].view(it.rows, it.cols)
-        results.append((it, newton_schulz(mat, ns_coefficients=tuple(h["ns_coefficients"]), ns_steps=int(h["ns_steps"]),
-                                          eps=float(h["eps"]))))
-    if u.size > 1:
-        full.zero_()
-    for it, d in results:
-        full[it.offset:it.offset + it.rows * it.cols].view(it.rows, it.cols).copy_(d)
-    if u.size > 1:
-        dshard = torch.empty(u.shard_numel, dtype=torch.bfloat16, device=dev)
-        dist.reduce_scatter_tensor(dshard, full, group=u.group)
+        dshard = _owner_compute_all_to_all(engine, u, items, groups, shard)
     else:
+        for it in items:
+            h = groups[it.group_idx]
+            mat = full[it.offset:it.offset + it.rows * it.cols].view(it.rows, it.cols)
+            mat.copy_(newton_schulz(mat, ns_coefficients=tuple(h["ns_coefficients"]), ns_steps=int(h["ns_steps"]),
+                                    eps=float(h["eps"])))
         dshard = full
 
     lo = u.shard_start
