@@ -106,3 +106,30 @@ def test_operator_tracer_and_html_report(tmp_path):
     n = html_report(a, b, str(out))
     text = out.read_text()
     assert n > 0 and "class='diff'" in text and "class='same'" in text
+
+
+def test_memory_plan_of_large_registry_configs():
+    """Meta-device memory plans: Llama-3 405B and Qwen3 235B-A22B fit a 180 GB GPU only with sharded parameters;
+    the 8B headline at 8 GPUs keeps at most its shards plus four unit-sized slots in the sharded layout."""
+    from torchtitan_b200.config import ConfigManager
+    from torchtitan_b200.tools.memory_plan import plan_memory
+
+    def cfg(module, name, *extra):
+        return ConfigManager().parse_args(["--module", module, "--config", name, *extra])
+
+    c = cfg("llama3", "llama3_405b", "--parallelism.tensor_parallel_degree", "8", "--parallelism.pipeline_parallel_degree", "1",
+            "--parallelism.fsdp_reshard_after_forward", "default")
+    big = plan_memory(c, world=512)
+    assert big.layout == "sharded parameters" and big.fits(), str(big)
+    c.parallelism.fsdp_reshard_after_forward = "never"
+    assert not plan_memory(c, world=512).fits()
+    moe = plan_memory(cfg("qwen3", "qwen3_235b_a22b", "--parallelism.fsdp_reshard_after_forward", "always",
+                          "--parallelism.expert_parallel_degree", "8", "--parallelism.pipeline_parallel_degree", "1",
+                          "--parallelism.tensor_parallel_degree", "1"), world=128)
+    assert moe.fits(), str(moe)
+    small = cfg("llama3", "llama3_8b", "--parallelism.fsdp_reshard_after_forward", "always")
+    p8 = plan_memory(small, world=8)
+    full_bf16 = 8.03e9 * 2 / (1 << 30)
+    assert p8.params_gib <= full_bf16 / 8 + 2 * p8.largest_unit_gib + 0.1, str(p8)
+    resident = plan_memory(cfg("llama3", "llama3_8b", "--parallelism.fsdp_reshard_after_forward", "never"), world=8)
+    assert resident.params_gib > 0.95 * full_bf16
