@@ -289,3 +289,24 @@ def test_activation_offload_on_gpu_matches_resident():
     assert stats.tensors >= 2
     for a, b in zip(ref_grads, got):
         assert torch.allclose(a, b, rtol=1e-5, atol=1e-5)
+
+
+def test_gemm_and_norm_are_batch_invariant():
+    """A row's result does not depend on how many other rows are in the batch (no split-K, fixed tile walk)."""
+    from torchtitan_b200.experiments.rl.batch_invariance import batch_invariant
+    from torchtitan_b200.ops import functional as OF
+
+    g = torch.Generator(device="cuda").manual_seed(0)
+    x = torch.randn(4096, 1024, device="cuda", generator=g).bfloat16()
+    w = (torch.randn(2048, 1024, device="cuda", generator=g) * 0.05).bfloat16()
+    nw = torch.ones(1024, device="cuda", dtype=torch.bfloat16)
+    with batch_invariant():
+        big = OF.gemm_nt(x, w)
+        for rows in (128, 256, 1000 // 8 * 8):
+            small = OF.gemm_nt(x[:rows].contiguous(), w)
+            assert torch.equal(big[:rows], small), rows
+        nb = OF.rms_norm(x, nw, 1e-5)
+        ns = OF.rms_norm(x[:8].contiguous(), nw, 1e-5)
+        assert torch.equal(nb[:8], ns)
+        with pytest.raises(RuntimeError, match="batch-invariant"):
+            OF.gemm_nt(torch.randn(64, 36, device="cuda").bfloat16(), torch.randn(16, 36, device="cuda").bfloat16())

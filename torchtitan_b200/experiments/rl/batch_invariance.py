@@ -4,9 +4,11 @@ torchtitan/experiments/rl/batch_invariance.py:25-60, torchtitan/distributed/util
 fixed-order reduction kernels and pin NCCL algorithms).
 
 The hand-written kernels of this package are batch-invariant by construction: the GEMM walks K in one fixed
-order per output tile (no split-K, tile shape independent of M), attention walks the key tiles of a row in
-order, norms and the cross entropy reduce inside one row, and the NVLink reduce-scatter sums ranks in rank
-order.  What is not invariant are the library paths (cuBLAS picks kernels by shape), so this mode makes every
+order per output tile (no split-K, tile shape independent of M), norms and the cross entropy reduce inside one
+row, and the NVLink reduce-scatter sums ranks in rank order.  Attention walks the key tiles of a row in order: a
+sequence's result does not depend on the other sequences of a packed batch as long as it starts on a multiple of
+the 128-token tile (pad prompts accordingly); at other offsets the same products are grouped into different
+partial sums.  What is not invariant are the library paths (cuBLAS picks kernels by shape), so this mode makes every
 silent library route an error instead."""
 
 from __future__ import annotations

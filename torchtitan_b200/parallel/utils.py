@@ -16,8 +16,25 @@ import torch.distributed as dist
 
 from torchtitan_b200.utils.logging import logger
 
-__all__ = ["init_distributed", "set_determinism", "dist_sum", "dist_max", "dist_mean", "dist_min",
+__all__ = ["pin_nccl_for_batch_invariance", "init_distributed", "set_determinism", "dist_sum", "dist_max", "dist_mean", "dist_min",
            "set_pg_timeouts", "destroy", "world_info"]
+
+
+def pin_nccl_for_batch_invariance() -> dict[str, str]:
+    """Fix every NCCL choice that may depend on load or message size, so that reductions add in one order (must run
+    before the process group is created; values already present in the environment win).  Parity:
+    torchtitan/distributed/utils.py:345-370."""
+    pins = {
+        "NCCL_LAUNCH_MODE": "GROUP", "NCCL_COLLNET_ENABLE": "0", "NCCL_NVLS_ENABLE": "0", "NCCL_P2P_NET_DISABLE": "1",
+        "NCCL_MIN_NCHANNELS": "4", "NCCL_MAX_NCHANNELS": "4", "NCCL_PROTO": "Simple", "NCCL_ALGO": "Ring",
+        "NCCL_NTHREADS": "512",
+    }
+    applied = {}
+    for k, v in pins.items():
+        if k not in os.environ:
+            os.environ[k] = v
+            applied[k] = v
+    return applied
 
 
 def world_info() -> tuple[int, int, int]:

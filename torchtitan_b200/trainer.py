@@ -126,6 +126,9 @@ class Trainer(Configurable):
         self.device = get_local_device()
         if self.device.type == "cuda":
             torch.cuda.set_device(self.device)
+        if c.debug.batch_invariant:
+            pinned = dist_utils.pin_nccl_for_batch_invariance()
+            logger.info(f"batch-invariant mode: NCCL pinned with {pinned}")
         with sl.span("torch_distributed_init"):
             world = dist_utils.init_distributed(c.comm, self.device, dump_folder=c.dump_folder,
                                                 enable_cpu_backend=c.training.enable_cpu_offload)
