@@ -7,10 +7,10 @@ import torch
 from tests.dist_utils import run_distributed
 
 
-def _run(rank, world, extra, out_path, global_tokens):
+def _run(rank, world, extra, out_path, global_tokens, module="llama3", config="llama3_debugmodel"):
     from torchtitan_b200.config import ConfigManager
 
-    args = ["--module", "llama3", "--config", "llama3_debugmodel", "--training.steps", "3",
+    args = ["--module", module, "--config", config, "--training.steps", "3",
             "--training.num_tokens_per_microbatch_per_dp_rank", "64", "--training.max_context_length", "64",
             "--training.mixed_precision_param", "float32", "--debug.seed", "0", "--dump_folder", out_path + "_d",
             "--debug.no-enable_structured_logging", "--metrics.log_freq", "1",
@@ -52,6 +52,24 @@ def test_pipeline_stages_with_sharded_parameters(tmp_path):
     assert torch.allclose(ra, rb, atol=1e-5), (ra, rb)
 
 
+def test_expert_tensor_parallel_matches_data_parallel(tmp_path):
+    """Expert tensor parallelism (tp 2, expert parallelism off: w1 / w3 split over the hidden dimension, w2 over its
+    input, the layer's output a partial sum reduced over tp; reference plan: models/common/moe_sharding.py:50-68)
+    and tp 2 x ep 2 (experts split over ep, tokens stay split over tp) train a mixture-of-experts model like two
+    data-parallel ranks on the same global batch (data-parallel degree 2 in all three)."""
+    moe = ("qwen3", "qwen3_moe_tiny")
+    a, b, c = (str(tmp_path / n) for n in ("dp.pt", "etp.pt", "tp_ep.pt"))
+    run_distributed(_run, 2, ["--parallelism.data_parallel_shard_degree", "2"], a, 256, *moe, timeout=400)
+    run_distributed(_run, 4, ["--parallelism.tensor_parallel_degree", "2", "--parallelism.data_parallel_shard_degree", "2"],
+                    b, 256, *moe, timeout=400)
+    ra, rb = torch.load(a), torch.load(b)
+    assert torch.allclose(ra, rb, atol=3e-4), (ra, rb)
+    run_distributed(_run, 4, ["--parallelism.tensor_parallel_degree", "2", "--parallelism.expert_parallel_degree", "2",
+                              "--parallelism.data_parallel_shard_degree", "2"], c, 256, *moe, timeout=400)
+    rc = torch.load(c)
+    assert torch.allclose(ra, rc, atol=3e-4), (ra, rc)
+
+
 def test_local_tensor_mode_validates_the_sharding_plan():
     """comm.mode = local_tensor: one process walks over 8 emulated ranks (dp_shard 4 x tp 2) and checks that their
     shards tile every parameter exactly once; a plan with a hole is reported."""
@@ -77,3 +95,54 @@ def test_local_tensor_mode_validates_the_sharding_plan():
             local_plan.validate_plan(cfg, world=8)
     finally:
         local_plan._rank_plan = orig
+
+
+def test_declarative_sharding_contracts_drive_the_slices():
+    """Every tensor-parallel module declares its contract (parameter placements, input / output placement pairs);
+    the slices the modules hold are cut from those declarations, and the boundary collectives follow from the
+    (source, destination) pairs.  Reference: protocols/sharding.py:69-168, models/common/decoder_sharding.py."""
+    from types import SimpleNamespace
+
+    from torchtitan_b200.models import get_model_spec
+    from torchtitan_b200.models.common.layers import TPContext
+    from torchtitan_b200.parallel import sharding as shd
+
+    assert shd.redistribution(shd.Shard(0), shd.Replicate()) == "all_gather_rows"
+    assert shd.redistribution(shd.Partial(), shd.Shard(0)) == "reduce_scatter_rows"
+    assert shd.redistribution(shd.Partial(), shd.Replicate()) == "all_reduce"
+    assert shd.redistribution(shd.Replicate(), shd.Replicate()) == "copy"
+    with pytest.raises(ValueError):
+        shd.redistribution(shd.Shard(1), shd.Replicate())
+    with pytest.raises(ValueError):
+        shd.SpmdLayout(model_parallel=shd.Shard(0))
+    lay = shd.SpmdLayout(tp=shd.Shard(0), dp_shard=shd.Shard(0))
+    assert shd.resolve_placements(lay, [("dp_shard", 4), ("cp", 2), ("tp", 1)]) == (shd.Shard(0), shd.Replicate(), shd.Replicate())
+
+    for module, flavor in (("llama3", "debugmodel"), ("qwen3", "debugmodel_moe_tiny")):
+        with torch.device("meta"):
+            model = get_model_spec(module, flavor).model.build()
+        tp = TPContext(group=None, size=2, rank=1)
+        par = SimpleNamespace(tensor_parallel_degree=2, disable_sequence_parallel=False, tp_comm="nccl", enable_loss_parallel=True)
+        model.tok_embeddings.shard_(tp)
+        for blk in model.layers.values():
+            blk.attention.shard_(tp)
+            if blk.feed_forward is not None:
+                blk.feed_forward.shard_(tp)
+            if blk.moe is not None:
+                blk.moe.shard_tp_(tp)
+        model.lm_head.shard_("colwise", tp)
+        table = shd.sharding_table(model)
+        assert table["tok_embeddings"]["state"]["weight"] == {"tp": "S(0)"}
+        assert table["tok_embeddings"]["out"] == [{"tp": "P"}, {"tp": "S(0)"}]
+        assert table["layers.0.attention.wo"]["state"]["weight"] == {"tp": "S(1)"}
+        assert table["layers.0.attention_norm"]["state"]["weight"] == {"tp": "R"}
+        if module == "qwen3":
+            ex = table["layers.0.moe.routed_experts.inner_experts"]
+            assert ex["state"]["w2_EDF"] == {"tp": "S(2)"} and ex["out"][0] == {"tp": "P"}
+        n = shd.check_against_slices(model, "tp")
+        assert n > 10
+        # a slice that contradicts the declaration is reported
+        wo = model.layers["0"].attention.wo
+        wo.weight._tp_slices = (0,) + wo.weight._tp_slices[1:]
+        with pytest.raises(RuntimeError, match="declared S\\(1\\)"):
+            shd.check_against_slices(model, "tp")

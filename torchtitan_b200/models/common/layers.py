@@ -21,6 +21,7 @@ import torch.nn as nn
 
 from torchtitan_b200.ops import functional as OF
 from torchtitan_b200.ops import reference as ref
+from torchtitan_b200.parallel import sharding as shd
 from torchtitan_b200.parallel import tp_ops
 
 from .module import InitSpec, Module, set_init
@@ -84,31 +85,28 @@ class Linear(Module):
         self.tp_mode: str | None = None
 
     def shard_(self, mode: Literal["colwise", "rowwise"], tp: TPContext) -> None:
-        """Keep only this rank's slice (meta device): colwise = output rows, rowwise = input columns."""
+        """Keep only this rank's slice (meta device): colwise = output rows, rowwise = input columns.  The slice
+        dimension comes from the declared contract (``self.sharding``)."""
         self.tp_mode = mode
-        w = self.weight
-        spec = w._init_spec
+        full = (self.out_features, self.in_features)
         if mode == "colwise":
-            rows = _block_slices(self.row_blocks, tp.size, tp.rank)
-            n = sum(b - a for a, b in rows)
-            new = nn.Parameter(torch.empty(n, self.in_features, device=w.device, dtype=w.dtype))
-            new._tp_slices = (0, rows, (self.out_features, self.in_features))
-            self.row_blocks = [b - a for a, b in rows]
-            if self.bias is not None:
-                nb = nn.Parameter(torch.empty(n, device=w.device, dtype=w.dtype))
-                nb._tp_slices = (0, rows, (self.out_features,))
-                set_init(nb, self.bias._init_spec)
-                self.bias = nb
-            self.out_features = n
+            self.sharding = shd.colwise_linear(tp.sequence_parallel, blocks=len(self.row_blocks) > 1,
+                                               bias=self.bias is not None)
         else:
             if self.in_features % tp.size:
                 raise ValueError("rowwise shard needs in_features divisible by tp")
-            k = self.in_features // tp.size
-            new = nn.Parameter(torch.empty(self.out_features, k, device=w.device, dtype=w.dtype))
-            new._tp_slices = (1, [(tp.rank * k, (tp.rank + 1) * k)], (self.out_features, self.in_features))
-            self.in_features = k
-        set_init(new, spec)
-        self.weight = new
+            self.sharding = shd.rowwise_linear(tp.sequence_parallel)
+        place = self.sharding.state_shardings["weight"].on("tp")
+        blocks = self.row_blocks if place.dim == 0 else None
+        self.weight = shd.shard_parameter(self.weight, place, tp.size, tp.rank, blocks=blocks, full_shape=full)
+        if place.dim == 0:
+            if self.bias is not None:
+                self.bias = shd.shard_parameter(self.bias, self.sharding.state_shardings["bias"].on("tp"), tp.size, tp.rank,
+                                                blocks=self.row_blocks, full_shape=(self.out_features,))
+            self.row_blocks = [b - a for a, b in self.weight._tp_slices[1]]
+            self.out_features = self.weight.shape[0]
+        else:
+            self.in_features = self.weight.shape[1]
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         return OF.linear(x, self.weight, self.bias)
@@ -133,14 +131,10 @@ class Embedding(Module):
         """Vocabulary-parallel: rank r owns a contiguous range of rows."""
         if self.num_embeddings % tp.size:
             raise ValueError("vocab size must divide by tp for a vocab-parallel embedding")
-        n = self.num_embeddings // tp.size
-        w = self.weight
-        new = nn.Parameter(torch.empty(n, self.embedding_dim, device=w.device, dtype=w.dtype))
-        new._tp_slices = (0, [(tp.rank * n, (tp.rank + 1) * n)], (self.num_embeddings, self.embedding_dim))
-        set_init(new, w._init_spec)
-        self.weight = new
+        self.sharding = shd.vocab_parallel_embedding(tp.sequence_parallel)
+        self.weight = shd.shard_parameter(self.weight, self.sharding.state_shardings["weight"].on("tp"), tp.size, tp.rank)
         self.tp = tp
-        self.vocab_start = tp.rank * n
+        self.vocab_start = self.weight._tp_slices[1][0][0]
 
     def forward(self, tokens: torch.Tensor) -> torch.Tensor:
         if self.tp is None:
@@ -150,9 +144,8 @@ class Embedding(Module):
         mine = (local >= 0) & (local < n)
         out = OF.embedding(local.clamp(0, n - 1), self.weight)
         out = out * mine.unsqueeze(-1).to(out.dtype)
-        if self.tp.sequence_parallel:
-            return tp_ops.reduce_scatter_rows(out, self.tp)
-        return tp_ops.all_reduce(out, self.tp)
+        return shd.redistribute(out, self.sharding.out_src_shardings.on("tp"), self.sharding.out_dst_shardings.on("tp"),
+                                self.tp)
 
 
 class RMSNorm(Module):
@@ -170,6 +163,7 @@ class RMSNorm(Module):
             self.weight = nn.Parameter(torch.empty(config.dim))
             set_init(self.weight, InitSpec(kind="ones"))
             self.weight._replicated_over_tp = True
+            self.sharding = shd.sequence_parallel_norm()
         else:
             self.register_parameter("weight", None)
 

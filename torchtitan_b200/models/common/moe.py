@@ -89,30 +89,27 @@ class GroupedExperts(Module):
         E = self.num_experts
         if E % ep_size:
             raise ValueError(f"num_experts={E} must divide by ep={ep_size}")
-        n = E // ep_size
-        for name in ("w1_EFD", "w2_EDF", "w3_EFD"):
-            p = getattr(self, name)
-            new = nn.Parameter(torch.empty(n, *p.shape[1:], device=p.device, dtype=p.dtype))
-            new._tp_slices = (0, [(ep_rank * n, (ep_rank + 1) * n)], tuple(p.shape))
+        from torchtitan_b200.parallel import sharding as shd
+
+        self.sharding = shd.expert_parallel()
+        for name, layout in self.sharding.state_shardings.items():
+            new = shd.shard_parameter(getattr(self, name), layout.on("ep"), ep_size, ep_rank)
             new._is_expert = True
-            set_init(new, p._init_spec)
             setattr(self, name, new)
-        self.num_experts = n
+        self.num_experts = E // ep_size
 
     def shard_tp_(self, tp: TPContext) -> None:
         """Expert tensor parallel (EP off): hidden dim split, w1/w3 on dim 1, w2 on dim 2."""
-        for name, dim in (("w1_EFD", 1), ("w3_EFD", 1), ("w2_EDF", 2)):
+        from torchtitan_b200.parallel import sharding as shd
+
+        self.sharding = shd.expert_tensor_parallel(tp.sequence_parallel)
+        for name, layout in self.sharding.state_shardings.items():
+            place = layout.on("tp")
             p = getattr(self, name)
-            full = p.shape[dim]
-            if full % tp.size:
+            if p.shape[place.dim] % tp.size:
                 raise ValueError("expert hidden dim must divide by tp")
-            k = full // tp.size
-            shape = list(p.shape)
-            shape[dim] = k
-            new = nn.Parameter(torch.empty(*shape, device=p.device, dtype=p.dtype))
-            new._tp_slices = (dim, [(tp.rank * k, (tp.rank + 1) * k)], tuple(p.shape))
+            new = shd.shard_parameter(p, place, tp.size, tp.rank)
             new._is_expert = True
-            set_init(new, p._init_spec)
             setattr(self, name, new)
 
     def native_ok(self, x: torch.Tensor) -> bool:
@@ -326,9 +323,10 @@ class MoE(Module):
         tp = getattr(self, "tp", None)
         gather = tp is not None and self.routed_experts.ep is None
         if gather:
-            from torchtitan_b200.parallel import tp_ops
+            from torchtitan_b200.parallel import sharding as shd
 
-            x = tp_ops.all_gather_rows(x, tp) if tp.sequence_parallel else tp_ops.copy_to_tp(x, tp)
+            plan = self.routed_experts.inner_experts.sharding
+            x = shd.redistribute(x, plan.in_src_shardings["x"].on("tp"), plan.in_dst_shardings["x"].on("tp"), tp)
         top, sel, counts = self.router(x, self.expert_bias_E)
         with torch.no_grad():
             self.tokens_per_expert_E.add_(counts)
@@ -337,7 +335,5 @@ class MoE(Module):
             se = self.shared_experts
             out = out + OF.swiglu_linear(se.w13(x), se.w2.weight)
         if gather:
-            from torchtitan_b200.parallel import tp_ops
-
-            return tp_ops.reduce_scatter_rows(out, tp) if tp.sequence_parallel else tp_ops.all_reduce(out, tp)
+            return shd.redistribute(out, plan.out_src_shardings.on("tp"), plan.out_dst_shardings.on("tp"), tp)
         return out

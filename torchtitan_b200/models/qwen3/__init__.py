@@ -59,6 +59,8 @@ qwen3_configs = {
     "32B": lambda: build_qwen3_config(dim=5120, n_layers=64, n_heads=64, n_kv_heads=8, hidden_dim=25600),
     "debugmodel_moe": lambda: build_qwen3_config(dim=256, n_layers=8, n_heads=16, n_kv_heads=8, vocab_size=2048,
                                                  moe_hidden_dim=768, num_experts=64, top_k=8),
+    "debugmodel_moe_tiny": lambda: build_qwen3_config(dim=64, n_layers=2, n_heads=4, n_kv_heads=2, head_dim=16, vocab_size=512,
+                                                      moe_hidden_dim=32, num_experts=8, top_k=2, max_context_length=256),
     "30B-A3B": lambda: build_qwen3_config(dim=2048, n_layers=48, n_heads=32, n_kv_heads=4, moe_hidden_dim=768,
                                           num_experts=128, top_k=8, max_context_length=4096),
     "235B-A22B": lambda: build_qwen3_config(dim=4096, n_layers=94, n_heads=64, n_kv_heads=4, moe_hidden_dim=1536,

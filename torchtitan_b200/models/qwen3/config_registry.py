@@ -32,6 +32,11 @@ def qwen3_moe_debug() -> Trainer.Config:
     return _debug("debugmodel_moe")
 
 
+def qwen3_moe_tiny() -> Trainer.Config:
+    """Two layers of eight experts at width 64: the mixture-of-experts model of the CPU multi-rank tests."""
+    return _debug("debugmodel_moe_tiny")
+
+
 def qwen3_moe_debug_param_groups() -> Trainer.Config:
     cfg = _debug("debugmodel_moe")
     cfg.optimizer.param_groups = [

@@ -12,6 +12,7 @@ import torch
 import torch.nn as nn
 
 from torchtitan_b200.models.common.layers import TPContext
+from torchtitan_b200.utils.logging import logger
 
 from .activation_checkpoint import apply_activation_checkpointing
 from .fsdp import ShardedModel, UnitSpec
@@ -86,6 +87,13 @@ def parallelize_decoder(model: nn.Module, *, pdims, job_config, device: torch.de
         par._tokens_per_rank = tr.num_tokens_per_microbatch_per_dp_rank // max(1, pdims.tp * pdims.cp)
         apply_expert_parallel(model, pdims, par)
     tp = apply_tensor_parallel(model, pdims, par)
+    if tp is not None or pdims.ep_enabled:
+        # the slices the modules hold must be the ones their declared contracts name
+        from . import sharding as shd
+
+        if tp is not None:
+            shd.check_against_slices(model, "tp")
+        logger.debug("sharding contracts: %s", shd.sharding_table(model))
 
     if pdims.cp_enabled:
         from .context_parallel import CPContext
