@@ -76,11 +76,11 @@ PRESETS = {
                          par=dict(tensor_parallel_degree=2, context_parallel_degree=2)),
     # Qwen3-30B-A3B-shaped MoE, expert parallel over all ranks, FSDP on the rest
     "moe_ep8": dict(model="qwen3", flavor="30B-A3B", seq_len=4096, local_batch=2, ac="selective",
-                    par=dict(expert_parallel_degree=-1, ep_capacity_factor=1.25)),
+                    par=dict(expert_parallel_degree=-1, ep_capacity_factor=2.0)),
     # Llama-3.1 70B, PP 2 (interleaved 1F1B, two virtual stages per rank) x TP 2 x FSDP, bf16 optimizer states, full AC
     "70b_pp2tp2": dict(model="llama3", flavor="70B", seq_len=8192, local_batch=1, opt_state="bf16", ac="full",
                        par=dict(pipeline_parallel_degree=2, tensor_parallel_degree=2,
-                                pipeline_parallel_schedule="Interleaved1F1B", pipeline_parallel_layers_per_stage=20,
+                                pipeline_parallel_schedule="Interleaved1F1B", pipeline_parallel_layers_per_stage=21,
                                 num_pp_microbatches=8)),
 }
 
@@ -234,7 +234,9 @@ def main() -> None:
         cfg.model.converters = [c for c in args.converters.split(",") if c]
     trainer = cfg.build()
     for part in trainer.model_parts:
-        part.single_document = True
+        # one sequence per microbatch is one document: no document mask is needed; with several sequences per
+        # microbatch the positions restart and attention is masked per document
+        part.single_document = args.local_batch == 1
     pd = trainer.pdims
     tokens_per_step = trainer.tokens_per_step_per_dp_rank * pd.dp_degree    # global tokens per optimizer step
     tokens_per_rank_step = trainer.tokens_per_step_per_dp_rank              # host -> device per step on a data rank
@@ -346,7 +348,8 @@ def main() -> None:
                        "activation_checkpoint": args.ac,
                        "optimizer": f"AdamW fp32 master, {args.opt_state} moments", "fsdp_comm": trainer.engines[0].comm if trainer.engines[0]._symm is None else "nvlink",
                        "gemm": args.gemm, "attention": args.attention,
-                       "doc_mask": "skipped (every synthetic sequence is a single document)",
+                       "doc_mask": ("skipped (the microbatch is one sequence = one document)" if args.local_batch == 1 else
+                                    f"on ({args.local_batch} sequences per microbatch, attention masked per document)"),
                        "ac_policy": "selective = GEMM and attention outputs kept, norm outputs and SwiGLU activations "
                                     "recomputed in backward (no GEMM is recomputed)",
                        "param_layout": trainer.engines[0].param_layout(),

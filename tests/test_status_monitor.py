@@ -21,7 +21,10 @@ def test_monitor_poll_reports_one_call_later_and_clears():
     assert int(b[0]) == 0           # the words are cleared when the error is raised
     mon.check()
     a[0] = 4
-    with pytest.raises(RuntimeError, match="path a"):
+    with pytest.raises(RuntimeError, match="path a.*wait expired"):
+        mon.check()
+    a[0] = 8                        # the bits are decoded: an overflowing expert-parallel receive buffer
+    with pytest.raises(RuntimeError, match="ep_capacity_factor"):
         mon.check()
 
 

@@ -31,7 +31,27 @@ class ModelSpec:
         yield from self.model.walk(config_cls, prefix="model", **kw)
 
 
+def _truncate_layers(spec: ModelSpec, n: int) -> ModelSpec:
+    cfg = spec.model
+    layers = getattr(cfg, "layers", None)
+    if not isinstance(layers, list) or not 0 < n <= len(layers):
+        raise ValueError(f"cannot keep {n} layers of {spec.name} {spec.flavor}")
+    cfg.layers = layers[-n:] if n < len(layers) else layers   # the last layers: the mixture-of-experts ones of mixed stacks
+    for i, blk in enumerate(cfg.layers):
+        if hasattr(blk, "layer_id"):
+            blk.layer_id = i
+    if hasattr(cfg, "n_layers"):
+        cfg.n_layers = n
+    spec.flavor = f"{spec.flavor}@{n}"
+    return spec
+
+
 def get_model_spec(name: str, flavor: str) -> ModelSpec:
+    """``flavor`` may end in ``@N``: the architecture with only N of its layers (per-layer cost of a large model on
+    a few GPUs: profiling and benchmarks; not a registered training recipe)."""
+    if "@" in flavor:
+        base, n = flavor.rsplit("@", 1)
+        return _truncate_layers(get_model_spec(name, base), int(n))
     for root in ("torchtitan_b200.models", "torchtitan_b200.experiments"):
         try:
             mod = importlib.import_module(f"{root}.{name}")

@@ -559,9 +559,10 @@ struct GroupArgs {
 
 // Shared launcher.  a / b / c are the 2-D row-major views described by (rows, cols); the logical
 // problem is M x N x K with A stored [K, M] when a_mn and B stored [K, N] when b_mn.
+// lda / ldb / ldc: row strides in elements (negative: the operand is dense, stride = its column count).
 static void run_gemm(const at::Tensor& ref, const void* a, int64_t a_rows, int64_t a_cols, const void* b, int64_t b_rows,
                      int64_t b_cols, void* c, int64_t c_rows, int64_t M, int64_t N, int64_t K, bool a_mn, bool b_mn,
-                     bool accumulate, const GroupArgs& g) {
+                     bool accumulate, const GroupArgs& g, int64_t lda = -1, int64_t ldb = -1, int64_t ldc = -1) {
   using namespace gemm;
   c10::cuda::CUDAGuard guard(ref.device());
   // The tensor-map encoder is a driver-API call and needs the primary context current on this
@@ -577,11 +578,14 @@ static void run_gemm(const at::Tensor& ref, const void* a, int64_t a_rows, int64
   if (g.mode == 2) TORCH_CHECK(M % (pair ? 256 : 128) == 0 && g.align % 64 == 0, "grouped gemm: M must be a multiple of the row tile");
   const uint32_t b_box_rows = pair ? Cfg<2>::kBRows : Cfg<1>::kBRows;
   // K-major: inner = K, box {64, rows};  MN-major: inner = MN extent, box {64, 64 k-rows}
-  const CUtensorMap ta = a_mn ? make_tmap_2d(a, a_cols, a_rows, a_cols * 2, 64, BK)
-                              : make_tmap_2d(a, a_cols, a_rows, a_cols * 2, BK, BM);
-  const CUtensorMap tb = b_mn ? make_tmap_2d(b, b_cols, b_rows, b_cols * 2, 64, BK)
-                              : make_tmap_2d(b, b_cols, b_rows, b_cols * 2, BK, b_box_rows);
-  const CUtensorMap tcm = make_tmap_2d(c, N, c_rows, N * 2, 64, 32);   // store tiles: 64 columns x 32 rows
+  if (lda < 0) lda = a_cols;
+  if (ldb < 0) ldb = b_cols;
+  if (ldc < 0) ldc = N;
+  const CUtensorMap ta = a_mn ? make_tmap_2d(a, a_cols, a_rows, lda * 2, 64, BK)
+                              : make_tmap_2d(a, a_cols, a_rows, lda * 2, BK, BM);
+  const CUtensorMap tb = b_mn ? make_tmap_2d(b, b_cols, b_rows, ldb * 2, 64, BK)
+                              : make_tmap_2d(b, b_cols, b_rows, ldb * 2, BK, b_box_rows);
+  const CUtensorMap tcm = make_tmap_2d(c, N, c_rows, ldc * 2, 64, 32);   // store tiles: 64 columns x 32 rows
   Params p;
   p.M = (int)M; p.N = (int)N; p.K = (int)K;
   p.a_mn_major = a_mn; p.b_mn_major = b_mn; p.accumulate = accumulate ? 1 : 0;
@@ -628,9 +632,21 @@ void gemm_bf16(const at::Tensor& a, const at::Tensor& b, at::Tensor c, int64_t m
 //   mode 1: c[rows of g] = a[rows of g] . b[g]        a [R, K], b [G, K, N], c [R, N]
 //   mode 2: c[g] = a[rows of g]^T . b[rows of g]      a [R, M], b [R, N],    c [G, M, N]
 // Rows of c at or beyond offs[G] (modes 0, 1) are not written.
+// A row-major 2-D operand whose rows may be strided (a column slice of a wider buffer): unit column stride, row
+// stride and base address multiples of 16 bytes (the tensor-map rules).
+static void check_bf16_rows(const at::Tensor& t, const char* name) {
+  TORCH_CHECK(t.is_cuda() && t.scalar_type() == at::kBFloat16 && t.dim() == 2 && (t.size(1) == 1 || t.stride(1) == 1) &&
+                  t.stride(0) >= t.size(1) && (t.stride(0) * 2) % 16 == 0,
+              "gemm: ", name, " must be a 2-D CUDA bf16 tensor with contiguous rows and a 16-byte multiple row stride");
+  TORCH_CHECK((reinterpret_cast<uintptr_t>(t.data_ptr()) & 15) == 0, "gemm: ", name, " must be 16-byte aligned");
+}
+
 void gemm_grouped_bf16(const at::Tensor& a, const at::Tensor& b, at::Tensor c, const at::Tensor& offs, int64_t mode,
                        int64_t align, bool accumulate) {
-  check_bf16_2d(a, "a"); check_bf16_2d(b, "b"); check_bf16_2d(c, "c");
+  // the row-indexed operands (a, and c in modes 0 / 1, b in mode 2) may be column slices of wider buffers
+  check_bf16_rows(a, "a");
+  if (mode == 2) { check_bf16_rows(b, "b"); check_bf16_2d(c, "c"); }
+  else { check_bf16_2d(b, "b"); check_bf16_rows(c, "c"); }
   TORCH_CHECK(offs.is_cuda() && offs.scalar_type() == at::kInt && offs.is_contiguous() && offs.numel() >= 2,
               "gemm_grouped_bf16: offs must be an int32 CUDA tensor of G + 1 entries");
   const int G = (int)offs.numel() - 1;
@@ -651,13 +667,14 @@ void gemm_grouped_bf16(const at::Tensor& a, const at::Tensor& b, at::Tensor c, c
     g.mode = 1;
     g.b_group_rows = (int)(mode == 0 ? N : K);
     run_gemm(a, a.data_ptr(), R, K, b.data_ptr(), (int64_t)G * b.size(1), b.size(2), c.data_ptr(), R, R, N, K, false,
-             mode == 1, accumulate, g);
+             mode == 1, accumulate, g, a.stride(0), -1, c.stride(0));
   } else {
     TORCH_CHECK(mode == 2 && b.dim() == 2 && b.size(0) == R && c.dim() == 3 && c.size(0) == G);
     const int64_t M = a.size(1), N = b.size(1);
     TORCH_CHECK(c.size(1) == M && c.size(2) == N && M % 8 == 0 && N % 8 == 0);
     g.mode = 2;
-    run_gemm(a, a.data_ptr(), R, M, b.data_ptr(), R, N, c.data_ptr(), (int64_t)G * M, M, N, R, true, true, accumulate, g);
+    run_gemm(a, a.data_ptr(), R, M, b.data_ptr(), R, N, c.data_ptr(), (int64_t)G * M, M, N, R, true, true, accumulate, g,
+             a.stride(0), b.stride(0), -1);
   }
 }
 

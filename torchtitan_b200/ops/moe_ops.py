@@ -191,15 +191,11 @@ class _GroupedSwiGLUExpertsFn(torch.autograd.Function):
     def forward(ctx, x, w1, w3, w2, offs):
         R = x.shape[0]
         F_ = w1.shape[1]
+        # the two projections write the column halves of one [R, 2F] buffer (strided output rows), the layout the
+        # SwiGLU kernel takes
         gu = torch.empty(R, 2 * F_, dtype=x.dtype, device=x.device)
-        # the two projections write the halves of one [R, 2F] buffer, the layout the SwiGLU kernel takes
-        h = torch.empty(R, F_, dtype=x.dtype, device=x.device)
-        u = torch.empty(R, F_, dtype=x.dtype, device=x.device)
-        _gg(x, w1, h, offs, 0)
-        _gg(x, w3, u, offs, 0)
-        gu[:, :F_] = h
-        gu[:, F_:] = u
-        del h, u
+        _gg(x, w1, gu[:, :F_], offs, 0)
+        _gg(x, w3, gu[:, F_:], offs, 0)
         # rows at or beyond offs[-1] hold whatever the allocator returned; they are never consumed
         a = ext.require().swiglu_fwd(gu)
         _count()
@@ -216,24 +212,22 @@ class _GroupedSwiGLUExpertsFn(torch.autograd.Function):
         F_ = w1.shape[1]
         a = ops.swiglu_fwd(gu)
         dw2 = _grouped_wgrad(dy, a, w2, offs) if w2.requires_grad else None
-        da = torch.zeros_like(a)
+        # rows at or beyond offs[-1] of da / dgu / dx are never written nor consumed (the grouped GEMMs only visit
+        # the padded groups), so none of these buffers needs clearing
+        da = torch.empty_like(a)
         del a
         _gg(dy, w2, da, offs, 1)
         dgu = ops.swiglu_bwd(gu, da)
         _count(2)
         del da
-        dh = dgu[:, :F_].contiguous()
-        du = dgu[:, F_:].contiguous()
-        del dgu
+        dh, du = dgu[:, :F_], dgu[:, F_:]        # column halves, read in place through strided tensor maps
         dw1 = _grouped_wgrad(dh, x, w1, offs) if w1.requires_grad else None
         dw3 = _grouped_wgrad(du, x, w3, offs) if w3.requires_grad else None
         dx = None
         if ctx.needs_input_grad[0]:
-            dx = torch.zeros_like(x)
+            dx = torch.empty_like(x)
             _gg(dh, w1, dx, offs, 1)
-            dx2 = torch.zeros_like(x)
-            _gg(du, w3, dx2, offs, 1)
-            dx += dx2
+            _gg(du, w3, dx, offs, 1, accumulate=True)
         return dx, dw1, dw3, dw2, None
 
 

@@ -50,15 +50,22 @@ class StatusMonitor:
         self._words.clear()
         self._inflight = None
 
+    # bits of a status word (ops/csrc/common.cuh, moe.cu)
+    _BITS = ((1, "a RoPE position outside the table"), (2, "a label outside the vocabulary"),
+             (4, "a bounded device wait expired: a peer did not arrive within the timeout (TB200_SYMM_TIMEOUT_S), the "
+                 "data exchanged in that step is incomplete"),
+             (8, "an expert-parallel receive buffer overflowed: more rows were routed to this rank than "
+                 "parallelism.ep_capacity_factor allows, the rows that did not fit were dropped (raise the factor, or "
+                 "set it to 0 for the worst-case capacity)"))
+
     def _raise_if_set(self, values: list[int], names: list[str]) -> None:
         bad = [(n, v) for n, v in zip(names, values) if v]
         if bad:
             for _, w in self._words:
                 w.zero_()
-            desc = ", ".join(f"{n} (status {v:#x})" for n, v in bad)
-            raise RuntimeError(
-                f"a bounded device wait expired in: {desc}. A peer did not arrive within the timeout "
-                "(TB200_SYMM_TIMEOUT_S); the data exchanged in that step is incomplete, so training stops here")
+            desc = "; ".join(f"{n} (status {v:#x}): " + ", ".join(text for bit, text in self._BITS if v & bit)
+                             for n, v in bad)
+            raise RuntimeError(f"device status set in {desc}; training stops here")
 
     def poll(self) -> None:
         if not self._words:

@@ -34,7 +34,9 @@ def main(argv=None) -> int:
         "--metrics.log_freq", "1000000", "--debug.seed", "0", "--debug.no-enable_structured_logging",
         "--checkpoint.no-enable", "--dump_folder", "/tmp/tb200_step_profile"] + extra)
     trainer = cfg.build()
-    trainer.model.single_document = True
+    tr = cfg.training
+    # one sequence per microbatch is one document; several sequences keep their per-document attention mask
+    trainer.model.single_document = tr.num_tokens_per_microbatch_per_dp_rank <= tr.max_context_length
     it = trainer.batch_generator(trainer.dataloader)
     for _ in range(args.warmup):
         trainer.step += 1
@@ -46,6 +48,9 @@ def main(argv=None) -> int:
         torch.cuda.synchronize()
     rows = sorted(prof.key_averages(), key=lambda e: -e.device_time_total)
     total = sum(e.device_time_total for e in rows)
+    if int(os.environ.get("RANK", "0")) != 0:     # under torchrun every rank profiles its own step; rank 0 reports
+        trainer.close()
+        return 0
     print(f"total device time {total / 1e3:.1f} ms over {sum(e.count for e in rows)} launches")
     for e in rows[: args.top]:
         print(f"{e.device_time_total / 1e3:9.2f} ms {100 * e.device_time_total / total:5.1f}% n={e.count:5d}  {e.key[:110]}")
