@@ -286,21 +286,23 @@ def main() -> None:
 
     # ------------------------------------------------------------ device-timed
     class _Resident:
-        """Feeds the same device-resident batch every step (inputs never leave the GPU)."""
+        """Feeds device-resident batches (inputs never leave the GPU): a different batch every step, so the loss
+        stays that of unseen random tokens instead of a memorised batch."""
 
-        def __init__(self, batch):
-            inp, lab = batch
-            self.inp = {k: v.to(dev) for k, v in inp.items()}
-            self.lab = lab.to(dev)
-            self.host_lab = lab
+        def __init__(self, batches):
+            self.batches = [({k: v.to(dev) for k, v in inp.items()}, lab.to(dev)) for inp, lab in batches]
+            self.i = 0
 
         def __iter__(self):
             return self
 
         def __next__(self):
-            return self.inp, self.lab
+            b = self.batches[self.i % len(self.batches)]
+            self.i += 1
+            return b
 
-    resident = _Resident(next(it))
+    per_step = trainer.gradient_accumulation_steps * (cfg.parallelism.num_pp_microbatches if pd.pp_enabled else 1)
+    resident = _Resident([next(it) for _ in range(min(64, (args.warmup + args.steps) * per_step))])
     for _ in range(args.warmup):
         trainer.step += 1
         trainer.train_step(resident)
@@ -337,7 +339,7 @@ def main() -> None:
             "vs_baseline": (tokens_per_s / world / BASELINE_TOKENS_PER_SEC_PER_GPU
                             if args.preset == "fsdp" and not args.converters and args.flavor == "8B" else None),
             "dtype": "bf16" if not args.converters else f"{args.converters} linears, bf16 elsewhere",
-            "data": "synthetic uniform-random tokens, random-init weights",
+            "data": "synthetic uniform-random tokens (a new batch every step), random-init weights",
             "impl": "native",
             "tokens_per_sec_per_gpu": tokens_per_s / world,
             "mfu_pct": 100.0 * flops_per_token * tokens_per_s / world / 2.25e15,

@@ -230,3 +230,41 @@ def test_sharded_parameter_layout_matches_resident(tmp_path, accum):
     ra, rb = torch.load(a), torch.load(b)
     assert torch.equal(ra["losses"], rb["losses"]), (ra["losses"], rb["losses"])
     assert torch.equal(ra["master"], rb["master"])
+
+
+def test_per_op_selective_checkpoint_keeps_every_second_gemm():
+    """``selective_ac_option = op_half_mm``: blocks are recomputed in backward except the GEMM outputs the save list
+    keeps (1st, 3rd, ... of a block; forced shapes never): same losses and gradients as keeping everything, and the
+    recompute really skips the kept GEMMs (reference policy: distributed/activation_checkpoint.py:186-287)."""
+    from torchtitan_b200.parallel.activation_checkpoint import forced_recompute_shapes, half_mm_policy
+
+    pdims = ParallelDims(world_size=1)
+    mbs = [[x] for x in _batches(2)]
+    cfg_a = _job()
+    cfg_a.activation_checkpoint.mode = "selective"
+    cfg_a.activation_checkpoint.selective_ac_option = "op"
+    cfg_b = _job()
+    cfg_b.activation_checkpoint.mode = "selective"
+    cfg_b.activation_checkpoint.selective_ac_option = "op_half_mm"
+    la, _, ea = _engine_steps(cfg_a, pdims, mbs, steps=2)
+    lb, mb_, eb = _engine_steps(cfg_b, pdims, mbs, steps=2)
+    assert torch.allclose(torch.tensor(la), torch.tensor(lb), atol=1e-6), (la, lb)
+    for ua, ub in zip(ea.units, eb.units):
+        assert torch.allclose(ua.master, ub.master, atol=1e-6)
+    blk = next(iter(mb_.layers.values()))
+    s = blk._last_sac_session
+    # a llama block has four forward GEMMs: wqkv (rotated in place afterwards, so given up), wo (kept), w13 (run
+    # again), w2 (kept)
+    assert (s.saved, s.recomputed) == (2, 2), (s.saved, s.recomputed)
+    assert not s.store                                     # every kept output was handed back and released
+    # forced shapes are recomputed and do not take part in the count
+    forced = forced_recompute_shapes(blk, ["attention.wo"])
+    assert forced == {(blk.attention.wo.weight.shape[1], blk.attention.wo.weight.shape[0])}
+    pol = half_mm_policy(forced)
+
+    class S:
+        mm_count = 0
+    st = S()
+    wo = next(iter(forced))
+    assert [pol("mm", (1, 2), st), pol("mm", wo, st), pol("mm", (3, 4), st), pol("mm", (5, 6), st)] == [True, False, False, True]
+    assert pol("attention", None, st)

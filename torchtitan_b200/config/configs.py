@@ -137,7 +137,10 @@ class ActivationCheckpointConfig:
 
     ``selective`` keeps GEMM and attention outputs and recomputes the
     bandwidth-bound ops (norms, RoPE, SwiGLU) inside the fused autograd
-    functions; ``full`` recomputes whole blocks; ``none`` keeps everything.
+    functions (``selective_ac_option = "op"``); ``"op_half_mm"`` recomputes
+    whole blocks except attention and every second GEMM (the per-op save
+    list of the reference), a number N recomputes every N-th block;
+    ``full`` recomputes whole blocks; ``none`` keeps everything.
     Parity: torchtitan/distributed/activation_checkpoint.py:112-337.
     """
 

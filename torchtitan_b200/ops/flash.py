@@ -37,7 +37,10 @@ class _FlashFn(torch.autograd.Function):
     def forward(ctx, q, k, v, scale, causal, causal_offset, kv_first, packed_grad, window=0, sinks=None):
         ops = ext.require()
         sinks_f = sinks.detach().float().contiguous() if sinks is not None else None
-        o, lse = ops.flash_fwd(q, k, v, scale, causal, causal_offset, kv_first, window, sinks_f)
+        from .functional import _sac_run
+
+        o, lse = _sac_run("attention", None,
+                          lambda: ops.flash_fwd(q, k, v, scale, causal, causal_offset, kv_first, window, sinks_f))
         ctx.save_for_backward(q, k, v, o, lse, kv_first if kv_first is not None else torch.empty(0),
                               sinks_f if sinks_f is not None else torch.empty(0))
         ctx.has_first = kv_first is not None

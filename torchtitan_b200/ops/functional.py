@@ -48,9 +48,82 @@ class _Settings:
     count_launches: bool = False
     library_fallbacks: int = 0  # CUDA calls that went to a library / PyTorch path (see the module docstring)
     strict_native: bool = False  # batch-invariant mode: a CUDA call that would take a library path raises instead
+    sac: object | None = None  # the SacSession of the checkpointed block whose forward (or recompute) is running
 
 
 settings = _Settings()
+
+
+class SacSession:
+    """Per-op selective checkpointing inside a block that is otherwise recomputed in backward: the outputs of the
+    ops the policy selects (attention, every second GEMM, ...) are kept from the first forward and handed back,
+    in call order, when the block's forward runs again for the backward pass; everything else is recomputed.
+
+    ``policy(kind, shape, session) -> bool`` decides at the first forward whether the output of the op is kept
+    (``kind``: "mm" with ``shape = (in_features, out_features)``, or "attention").  Parity with the save-list
+    policy of torchtitan/distributed/activation_checkpoint.py:186-287, acting on this package's own ops."""
+
+    def __init__(self, policy):
+        self.policy = policy
+        self.store: dict[int, object] = {}
+        self.kinds: dict[int, str] = {}
+        self.replaying = False
+        self.index = 0
+        self.mm_count = 0
+        self.saved = 0
+        self.recomputed = 0
+
+    def begin(self, replaying: bool) -> None:
+        self.replaying = replaying
+        self.index = 0
+
+    @staticmethod
+    def _tensors(out):
+        return [t for t in (out if isinstance(out, (tuple, list)) else (out,)) if isinstance(t, torch.Tensor)]
+
+    def run(self, kind: str, shape, compute):
+        i = self.index
+        self.index += 1
+        if self.replaying:
+            kept = self.store.pop(i, None)
+            if kept is not None:
+                out, versions = kept
+                # an output that was written in place after it was kept no longer holds the op's result
+                if [t._version for t in self._tensors(out)] == versions:
+                    return out
+            self.recomputed += 1
+            return compute()
+        out = compute()
+        if self.policy(kind, shape, self):
+            self.store[i] = (out, [t._version for t in self._tensors(out)])
+            self.kinds[i] = kind
+            self.saved += 1
+        return out
+
+    def written_in_place(self, t: torch.Tensor) -> None:
+        """An op is about to overwrite ``t``: a kept output that shares its memory is given up (it will be
+        recomputed), and a GEMM that is given up hands its place in the every-second count to the next one."""
+        if self.replaying:
+            return
+        ptr = t.untyped_storage().data_ptr()
+        for i in [i for i, (out, _) in self.store.items()
+                  if any(x.untyped_storage().data_ptr() == ptr for x in self._tensors(out))]:
+            del self.store[i]
+            self.saved -= 1
+            if self.kinds.pop(i, None) == "mm":
+                self.mm_count -= 1
+
+
+def _sac_run(kind: str, shape, compute):
+    s = settings.sac
+    return compute() if s is None else s.run(kind, shape, compute)
+
+
+def _fwd_gemm_nt(a: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    """The forward GEMM of a linear layer (``a @ w^T``), subject to the running per-op checkpoint session."""
+    if settings.sac is None:
+        return gemm_nt(a, w)
+    return settings.sac.run("mm", (w.shape[1], w.shape[0]), lambda: gemm_nt(a, w))
 
 
 def _count(n: int = 1) -> None:
@@ -224,7 +297,7 @@ class _LinearFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, weight, bias):
         x2 = x.reshape(-1, x.shape[-1])
-        y = gemm_nt(x2, weight)
+        y = _fwd_gemm_nt(x2, weight)
         if bias is not None:
             y = y + bias
         ctx.save_for_backward(x2, weight)
@@ -257,7 +330,7 @@ class _NormLinearFn(torch.autograd.Function):
     def forward(ctx, x, norm_w, weight, eps):
         x2 = x.reshape(-1, x.shape[-1])
         xn, rstd = _rms_fwd(x2, norm_w, eps)
-        y = gemm_nt(xn, weight)
+        y = _fwd_gemm_nt(xn, weight)
         ctx.save_for_backward(x2, norm_w, weight, rstd)
         ctx.eps = eps
         ctx.xshape = x.shape
@@ -333,7 +406,7 @@ class _SwiGLULinearFn(torch.autograd.Function):
     def forward(ctx, gu, weight):
         gu2 = gu.reshape(-1, gu.shape[-1])
         a = _swiglu_fwd(gu2)
-        y = gemm_nt(a, weight)
+        y = _fwd_gemm_nt(a, weight)
         ctx.save_for_backward(gu2, weight)
         ctx.shape = gu.shape
         return y if gu.dim() == 2 else y.view(*gu.shape[:-1], weight.shape[0])
@@ -400,6 +473,8 @@ class _RopeQKInplaceFn(torch.autograd.Function):
         ctx.interleaved = interleaved
         ctx.n_rot, ctx.hd = n_rot_heads, head_dim
         ctx.mark_dirty(qkv)
+        if settings.sac is not None:
+            settings.sac.written_in_place(qkv)
         v = qkv.view(qkv.shape[0], -1, head_dim)
         _rope_inplace(v[:, :n_rot_heads], table, positions, interleaved, False)
         return qkv
@@ -493,7 +568,7 @@ class _PackedFlashFn(torch.autograd.Function):
     def forward(ctx, qkv3, hq, hkv, scale, kv_first):
         ops = ext.require()
         q, k, v = qkv3[:, :hq], qkv3[:, hq:hq + hkv], qkv3[:, hq + hkv:]
-        o, lse = ops.flash_fwd(q, k, v, scale, True, 0, kv_first)
+        o, lse = _sac_run("attention", None, lambda: ops.flash_fwd(q, k, v, scale, True, 0, kv_first))
         ctx.save_for_backward(qkv3, o, lse, kv_first if kv_first is not None else torch.empty(0))
         ctx.meta = (hq, hkv, scale, kv_first is not None)
         return o
