@@ -146,3 +146,15 @@ def test_declarative_sharding_contracts_drive_the_slices():
         wo.weight._tp_slices = (0,) + wo.weight._tp_slices[1:]
         with pytest.raises(RuntimeError, match="declared S\\(1\\)"):
             shd.check_against_slices(model, "tp")
+
+
+def test_tensor_parallel_without_sequence_parallel_matches_single_rank(tmp_path):
+    """tp 2 with replicated activations between the blocks: the block norms then hold their complete gradient on every
+    rank (not summed over tp), q / k norms and other replicated parameters inside a parallel region still hold parts;
+    losses and gradient norms equal the single-rank run."""
+    a, b = str(tmp_path / "one.pt"), str(tmp_path / "tp.pt")
+    run_distributed(_run, 1, [], a, 128, timeout=400)
+    run_distributed(_run, 2, ["--parallelism.tensor_parallel_degree", "2", "--parallelism.no-enable_sequence_parallel"],
+                    b, 128, timeout=400)
+    ra, rb = torch.load(a), torch.load(b)
+    assert torch.allclose(ra, rb, atol=2e-4), (ra, rb)

@@ -47,6 +47,12 @@ class TransformerBlock(Module):
         self.moe = config.moe.build() if config.moe is not None else None
         if (self.feed_forward is None) == (self.moe is None):
             raise ValueError("a block needs exactly one of feed_forward / moe")
+        # Tensor parallelism without sequence parallelism: the block norms act on the replicated residual stream,
+        # before the activation enters a parallel region, so every rank already holds their complete gradient
+        # (with sequence parallelism each rank holds the part of its sequence shard and the parts are summed).
+        for norm in (self.attention_norm, self.ffn_norm):
+            for p in norm.parameters():
+                p._tp_grad_complete_without_sp = True
 
     def forward(self, x: torch.Tensor, positions: torch.Tensor, ctx: AttentionContext | None = None) -> torch.Tensor:
         h = x + self.attention(x, positions, ctx, norm=self.attention_norm)
@@ -99,6 +105,8 @@ class Decoder(Module):
         self.tok_embeddings = c.tok_embeddings.build()
         self.layers = ModuleDict({str(i): blk.build() for i, blk in enumerate(c.layers)})
         self.norm = c.norm.build()
+        for p in self.norm.parameters():
+            p._tp_grad_complete_without_sp = True     # as for the block norms
         self.lm_head = c.lm_head.build()
         if c.enable_weight_tying:
             self.lm_head.weight = self.tok_embeddings.weight

@@ -164,6 +164,8 @@ class GatedDeltaNet(Module):
         self.tp = tp
         for p in self.parameters():
             p._replicated_over_tp = True
+            # without sequence parallelism every rank runs the whole layer on the whole sequence
+            p._tp_grad_complete_without_sp = True
 
     def forward(self, x: torch.Tensor, positions: torch.Tensor, ctx: AttentionContext | None = None,
                 norm: RMSNorm | None = None) -> torch.Tensor:

@@ -103,6 +103,7 @@ class FlatUnit:
         self.exp_avg: torch.Tensor | None = None
         self.exp_avg_sq: torch.Tensor | None = None
         self.rep_numel = 0  # leading elements that are replicated across tensor-parallel ranks
+        self.rep_reduce_numel = 0  # the part of them whose gradients are per-rank parts to be summed over tp
         self.pending = False  # gradients written, reduction not yet launched
         self.grad_shard_valid = False
         self.sumsq: torch.Tensor | None = None  # [2]: (tp-replicated part, rest)
@@ -200,11 +201,20 @@ class ShardedModel:
                     self.frozen[n] = p
             if not trainable:
                 continue
-            # tensor-parallel-replicated parameters first: their gradients need one
-            # all-reduce over the leading range of the flat buffer
-            trainable.sort(key=lambda np_: 0 if getattr(np_[1], "_replicated_over_tp", False) else 1)
+            # tensor-parallel-replicated parameters first: the ones whose gradient is a per-rank part (summed with
+            # one all-reduce over the leading range of the flat buffer), then the ones whose gradient is already
+            # complete on every rank (no reduction; both kinds are counted once in the gradient norm)
+            sp = self.tp is None or self.tp.sequence_parallel
+
+            def _tp_class(p) -> int:
+                if not getattr(p, "_replicated_over_tp", False):
+                    return 2
+                return 1 if (not sp and getattr(p, "_tp_grad_complete_without_sp", False)) else 0
+
+            trainable.sort(key=lambda np_: _tp_class(np_[1]))
             off = 0
             rep = 0
+            rep_reduce = 0
             for n, p in trainable:
                 slot = ParamSlot(
                     fqn=n, param=p, shape=tuple(p.shape), numel=p.numel(), offset=off,
@@ -216,6 +226,8 @@ class ShardedModel:
                 off += (p.numel() + 7) // 8 * 8  # keep every parameter 16-byte aligned
                 if slot.tp_replicated:
                     rep = off
+                    if _tp_class(p) == 0:
+                        rep_reduce = off
             # compact numel accounting: last slot's padding is part of unit padding
             gname = spec.group_name
             group = self.pdims.group(gname)
@@ -228,6 +240,7 @@ class ShardedModel:
             unit.padded = max(quantum, (off + quantum - 1) // quantum * quantum)
             unit.shard_numel = unit.padded // gsize
             unit.rep_numel = rep if (self.tp is not None and self.tp.size > 1) else 0
+            unit.rep_reduce_numel = rep_reduce if (self.tp is not None and self.tp.size > 1) else 0
             self.units.append(unit)
         missing = [n for i, n in fqn_of.items() if i not in claimed]
         if missing:
@@ -567,8 +580,8 @@ class ShardedModel:
     @torch.no_grad()
     def _reduce_unit(self, u: FlatUnit) -> None:
         tp = self.tp
-        if u.rep_numel and tp is not None and tp.size > 1:
-            dist.all_reduce(u.flat_grad[:u.rep_numel], group=tp.group)
+        if u.rep_reduce_numel and tp is not None and tp.size > 1:
+            dist.all_reduce(u.flat_grad[:u.rep_reduce_numel], group=tp.group)
         if u.grad_shard is None:
             # single shard owner, no accumulation: the optimizer reads flat_grad directly
             u.grad_shard_valid = True
