@@ -293,6 +293,59 @@ def test_hf_model_on_the_sharded_engine(tmp_path):
     assert outs["one"][-1] < outs["one"][0]
 
 
+def _hf_tp(rank, world, tp, out_path):
+    import transformers
+
+    from torchtitan_b200.experiments.transformers_backend import HFCausalLM, hf_engine_train_steps, parallelize_hf
+    from torchtitan_b200.parallel.parallel_dims import ParallelDims
+    from torchtitan_b200.trainer import Trainer
+
+    cfg = transformers.Qwen3Config(vocab_size=128, hidden_size=32, intermediate_size=64, num_hidden_layers=2,
+                                   num_attention_heads=4, num_key_value_heads=2, head_dim=8, max_position_embeddings=64,
+                                   tie_word_embeddings=False)
+    torch.manual_seed(0)
+    model = HFCausalLM(cfg)
+    job = Trainer.Config()
+    job.training.mixed_precision_param = "float32"
+    pdims = ParallelDims(world_size=world, rank=rank, tp=tp).build()
+    eng = parallelize_hf(model, pdims=pdims, job_config=job, device=torch.device("cpu"))
+    if tp > 1:
+        q = model.hf.model.layers[0].self_attn.q_proj
+        assert q.weight.shape == (32 // tp, 32) and q.weight._tp_slices[0] == 0
+        assert model.hf.model.layers[0].mlp.down_proj.weight.shape == (32, 64 // tp)
+    g = torch.Generator().manual_seed(1)
+    batches = []
+    for s in range(4):
+        per_rank = []
+        for r in range(2):
+            toks = torch.randint(0, 128, (33,), generator=g)
+            per_rank.append((toks[:-1], torch.arange(32), toks[1:]))
+        batches.append(per_rank)
+    if pdims.dp_degree == 2:
+        mine = [b[pdims.dp_rank] for b in batches]
+    else:   # one data rank sees both sequences of a step as one packed batch
+        mine = [(torch.cat([a[0], b[0]]), torch.cat([a[1], b[1]]), torch.cat([a[2], b[2]])) for a, b in batches]
+    losses = hf_engine_train_steps(model, eng, mine, pdims=pdims, lr=3e-3)
+    gn = float(sum((u.master.double() ** 2).sum() for u in eng.units))
+    if rank == 0:
+        torch.save(torch.tensor(losses + [gn]), out_path)
+
+
+def test_hf_model_tensor_parallel(tmp_path):
+    """A Hugging Face Qwen3 (per-head q / k norms) with its projections split over tp 2, alone and under dp 2 x tp 2:
+    the losses of the single-rank run."""
+    pytest.importorskip("transformers")
+    from tests.dist_utils import run_distributed
+
+    outs = {}
+    for name, world, tp in (("one", 1, 1), ("tp2", 2, 2), ("dp2tp2", 4, 2)):
+        path = str(tmp_path / f"{name}.pt")
+        run_distributed(_hf_tp, world, tp, path)
+        outs[name] = torch.load(path)
+    assert torch.allclose(outs["one"][:-1], outs["tp2"][:-1], atol=2e-4), outs
+    assert torch.allclose(outs["one"][:-1], outs["dp2tp2"][:-1], atol=2e-4), outs
+
+
 def test_graph_trainer_passes_map_to_engine_settings(tmp_path):
     from torchtitan_b200.config import ConfigManager
     from torchtitan_b200.experiments.graph_trainer import GraphTrainer, apply_passes

@@ -8,8 +8,10 @@ passing ``position_ids`` that restart per document together with a block-diagona
 tests.  ``parallelize_hf`` puts the same module under this framework's sharded data-parallel engine (units =
 embedding, every decoder layer, final norm + lm_head; resident or sharded parameter layout, NCCL or NVLink
 transport, fp32 master weights and sharded AdamW: parity with parallelize.py of the reference's backend, which
-applies FSDP to the HF layers), and ``hf_engine_train_steps`` is the training loop on it.  Tensor and pipeline
-parallel plans for HF modules are not built."""
+applies FSDP to the HF layers), and ``hf_engine_train_steps`` is the training loop on it.  With a tensor-parallel
+degree in ``pdims`` the attention and MLP projections of every decoder layer are split first (``apply_hf_tensor_parallel``:
+q / k / v / gate / up column-wise, o / down row-wise with an all-reduce, activations replicated between the layers;
+parity: hf_sharding.py of the reference's backend).  A pipeline plan for HF modules is not built."""
 
 from __future__ import annotations
 
@@ -17,7 +19,7 @@ import torch
 import torch.distributed as dist
 import torch.nn as nn
 
-__all__ = ["HFCausalLM", "hf_train_steps", "parallelize_hf", "hf_engine_train_steps"]
+__all__ = ["HFCausalLM", "hf_train_steps", "parallelize_hf", "hf_engine_train_steps", "apply_hf_tensor_parallel"]
 
 
 class HFCausalLM(nn.Module):
@@ -61,6 +63,72 @@ def hf_train_steps(model: HFCausalLM, batches, *, lr: float = 3e-4, max_norm: fl
     return losses
 
 
+_COLWISE = ("q_proj", "k_proj", "v_proj", "gate_proj", "up_proj")
+_ROWWISE = ("o_proj", "down_proj")
+
+
+class _TPLinear(nn.Module):
+    """A projection of an HF layer split over the tensor-parallel group.  ``colwise``: this rank's output features,
+    the (replicated) input passes through an identity whose backward sums the input gradient over the group.
+    ``rowwise``: this rank's input features, the partial products are summed with an all-reduce, the bias added once."""
+
+    def __init__(self, lin: nn.Linear, mode: str, tp):
+        super().__init__()
+        self.mode, self.tp = mode, tp
+        out_f, in_f = lin.weight.shape
+        dim = 0 if mode == "colwise" else 1
+        full = out_f if dim == 0 else in_f
+        if full % tp.size:
+            raise ValueError(f"{mode} projection of {full} features does not divide by tp={tp.size}")
+        n = full // tp.size
+        lo, hi = tp.rank * n, (tp.rank + 1) * n
+        w = lin.weight.detach()[lo:hi] if dim == 0 else lin.weight.detach()[:, lo:hi]
+        self.weight = nn.Parameter(w.clone().contiguous())
+        self.weight._tp_slices = (dim, [(lo, hi)], (out_f, in_f))
+        self.bias = None
+        if lin.bias is not None:
+            if dim == 0:
+                self.bias = nn.Parameter(lin.bias.detach()[lo:hi].clone())
+                self.bias._tp_slices = (0, [(lo, hi)], (out_f,))
+            else:
+                self.bias = nn.Parameter(lin.bias.detach().clone())
+                self.bias._replicated_over_tp = True
+                self.bias._tp_grad_complete_without_sp = True
+
+    def forward(self, x):
+        from torchtitan_b200.parallel import tp_ops
+
+        if self.mode == "colwise":
+            return nn.functional.linear(tp_ops.copy_to_tp(x, self.tp), self.weight, self.bias)
+        y = tp_ops.all_reduce(nn.functional.linear(x, self.weight), self.tp)
+        return y if self.bias is None else y + self.bias
+
+
+def apply_hf_tensor_parallel(model: HFCausalLM, tp) -> int:
+    """Split the attention / MLP projections of every decoder layer over ``tp`` (a ``TPContext`` with
+    ``sequence_parallel = False``); every other parameter stays replicated.  Returns the number of projections split."""
+    if tp.sequence_parallel:
+        raise ValueError("HF modules run with replicated activations: build the TPContext with sequence_parallel=False")
+    n = 0
+    inside = set()
+    for layer in model.hf.model.layers:
+        for parent in layer.modules():
+            for name, child in list(parent.named_children()):
+                if isinstance(child, nn.Linear) and name in _COLWISE + _ROWWISE:
+                    setattr(parent, name, _TPLinear(child, "colwise" if name in _COLWISE else "rowwise", tp))
+                    n += 1
+        attn = getattr(layer, "self_attn", None)
+        if attn is not None:
+            # per-head norms (q_norm / k_norm) act on this rank's heads: their gradients are per-rank parts
+            inside.update(id(p) for name, m in attn.named_children() if "norm" in name for p in m.parameters())
+    for p in model.parameters():
+        if getattr(p, "_tp_slices", None) is None:
+            p._replicated_over_tp = True
+            if id(p) not in inside:
+                p._tp_grad_complete_without_sp = True    # seen after the all-reduce: complete on every rank
+    return n
+
+
 def _hf_units(model: HFCausalLM):
     from torchtitan_b200.parallel.fsdp import UnitSpec
 
@@ -90,10 +158,16 @@ def parallelize_hf(model: HFCausalLM, *, pdims, job_config, device: torch.device
     from torchtitan_b200.parallel.fsdp import ShardedModel
 
     par, tr = job_config.parallelism, job_config.training
+    tp = None
+    if pdims.tp_enabled:
+        from torchtitan_b200.models.common.layers import TPContext
+
+        tp = TPContext(group=pdims.group("tp"), size=pdims.tp, rank=pdims.local_rank("tp"), sequence_parallel=False)
+        apply_hf_tensor_parallel(model, tp)
     values = {n: p.detach().float().cpu().clone() for n, p in model.named_parameters()}
     units, hooks = _hf_units(model)
     param_dtype = torch.bfloat16 if tr.mixed_precision_param == "bfloat16" else torch.float32
-    engine = ShardedModel(model, units, pdims=pdims, device=device, param_dtype=param_dtype, seed=seed,
+    engine = ShardedModel(model, units, pdims=pdims, device=device, param_dtype=param_dtype, seed=seed, tp=tp,
                           comm=par.fsdp_comm, reshard_after_forward=par.fsdp_reshard_after_forward or "never")
     model.to(device)          # buffers (rotary tables); parameters are replaced by views of the flat buffers below
     engine.materialize(init=False)
@@ -114,12 +188,14 @@ def hf_engine_train_steps(model: HFCausalLM, engine, batches, *, pdims, lr: floa
 
     opt = OptimizersContainer(OptimizersContainer.Config(lr=lr), engines=[engine])
     losses = []
+    # token counts and losses are summed over the ranks that hold different data (tensor-parallel ranks share a batch)
+    loss_group = pdims.group("loss") if (dist.is_initialized() and pdims.world_size > 1 and pdims.dp_degree > 1) else None
     for tokens, positions, labels in batches:
         dev = engine.device
         tokens, positions, labels = tokens.to(dev), positions.to(dev), labels.to(dev)
         n = (labels != -100).sum().float()
-        if dist.is_initialized() and dist.get_world_size() > 1:
-            dist.all_reduce(n)
+        if loss_group is not None:
+            dist.all_reduce(n, group=loss_group)
         opt.zero_grad()
         logits = model(tokens, positions)
         loss = nn.functional.cross_entropy(logits.float(), labels, ignore_index=-100, reduction="sum") / n
@@ -129,6 +205,6 @@ def hf_engine_train_steps(model: HFCausalLM, engine, batches, *, pdims, lr: floa
         opt.step()
         losses.append(loss.detach())
     out = torch.stack(losses)
-    if dist.is_initialized() and dist.get_world_size() > 1:
-        dist.all_reduce(out)
+    if loss_group is not None:
+        dist.all_reduce(out, group=loss_group)
     return out.tolist()
