@@ -74,9 +74,12 @@ PRESETS = {
     # Llama-3.1 8B, FSDP x async TP 2 x CP 2, 32k tokens, MXFP8 linears
     "3d_mxfp8_32k": dict(model="llama3", flavor="8B", seq_len=32768, local_batch=1, converters="mxfp8", ac="selective",
                          par=dict(tensor_parallel_degree=2, context_parallel_degree=2)),
-    # Qwen3-30B-A3B-shaped MoE, expert parallel over all ranks, FSDP on the rest
-    "moe_ep8": dict(model="qwen3", flavor="30B-A3B", seq_len=4096, local_batch=2, ac="selective",
-                    par=dict(expert_parallel_degree=-1, ep_capacity_factor=2.0)),
+    # Qwen3-30B-A3B-shaped MoE, expert parallel over all ranks, FSDP on the rest.  A random-init router sends most
+    # tokens to a few experts (one rank can receive several times the balanced load), so throughput runs assign
+    # experts round-robin (debug.moe_force_load_balance, as the reference does for its throughput runs): the same
+    # rows and FLOPs per step on both arms, and the static receive buffers of the NVLink dispatcher fit.
+    "moe_ep8": dict(model="qwen3", flavor="30B-A3B", seq_len=4096, local_batch=2, ac="selective", force_balance=True,
+                    par=dict(expert_parallel_degree=-1, ep_capacity_factor=1.25)),
     # Llama-3.1 70B, PP 2 (interleaved 1F1B, two virtual stages per rank) x TP 2 x FSDP, bf16 optimizer states, full AC
     "70b_pp2tp2": dict(model="llama3", flavor="70B", seq_len=8192, local_batch=1, opt_state="bf16", ac="full",
                        par=dict(pipeline_parallel_degree=2, tensor_parallel_degree=2,
@@ -230,6 +233,8 @@ def main() -> None:
     )
     cfg.debug.seed = 0
     cfg.debug.enable_structured_logging = False
+    force_balance = bool(PRESETS[args.preset].get("force_balance", False))
+    cfg.debug.moe_force_load_balance = force_balance
     if args.converters:
         cfg.model.converters = [c for c in args.converters.split(",") if c]
     trainer = cfg.build()
@@ -329,6 +334,8 @@ def main() -> None:
     lg = trainer.pdims.group("loss")
     if lg is not None:
         dist.all_reduce(loss_t, group=lg)   # every rank holds its share of the global mean
+    if pd.pp_enabled:
+        dist.all_reduce(loss_t, group=pd.group("pp"))   # only the last pipeline stage holds the loss
     loss = float(loss_t)
     if rank == 0:
         line = {
@@ -352,6 +359,8 @@ def main() -> None:
                        "gemm": args.gemm, "attention": args.attention,
                        "doc_mask": ("skipped (the microbatch is one sequence = one document)" if args.local_batch == 1 else
                                     f"on ({args.local_batch} sequences per microbatch, attention masked per document)"),
+                       **({"moe_routing": "round-robin expert assignment (debug.moe_force_load_balance): balanced load on "
+                                          "every step, the router's scores still weight the outputs"} if force_balance else {}),
                        "ac_policy": "selective = GEMM and attention outputs kept, norm outputs and SwiGLU activations "
                                     "recomputed in backward (no GEMM is recomputed)",
                        "param_layout": trainer.engines[0].param_layout(),

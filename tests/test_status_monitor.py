@@ -26,6 +26,13 @@ def test_monitor_poll_reports_one_call_later_and_clears():
     a[0] = 8                        # the bits are decoded: an overflowing expert-parallel receive buffer
     with pytest.raises(RuntimeError, match="ep_capacity_factor"):
         mon.check()
+    mon.tolerated = 8               # parallelism.ep_overflow = "drop": logged, cleared, not raised
+    a[0] = 8
+    mon.check()
+    assert int(a[0]) == 0 and mon.tolerated_seen == 1
+    a[0] = 12                       # an expired wait next to it still stops training
+    with pytest.raises(RuntimeError, match="wait expired"):
+        mon.check()
 
 
 def test_trainer_raises_when_a_wait_timed_out(tmp_path):

@@ -96,6 +96,9 @@ class ParallelismConfig:
     """``nvlink``: token dispatch / combine as in-kernel peer stores / loads over symmetric memory."""
     ep_capacity_factor: float = 0.0
     """Rows of the nvlink receive buffer = factor * tokens * top_k (0 = the worst case, ep degree)."""
+    ep_overflow: Literal["error", "drop"] = "error"
+    """Routed rows beyond the receive buffer of their rank: ``error`` stops training at the next status poll,
+    ``drop`` leaves them out of the step (they contribute nothing to the layer output; a warning is logged)."""
     _tokens_per_rank: int = 0
 
 

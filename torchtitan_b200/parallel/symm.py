@@ -42,6 +42,8 @@ class StatusMonitor:
     def __init__(self):
         self._words: list[tuple[str, torch.Tensor]] = []
         self._inflight: tuple | None = None
+        self.tolerated = 0      # status bits that are logged instead of raised (8: dropped expert-parallel rows)
+        self.tolerated_seen = 0
 
     def register(self, name: str, word: torch.Tensor) -> None:
         self._words.append((name, word))
@@ -49,6 +51,8 @@ class StatusMonitor:
     def clear(self) -> None:
         self._words.clear()
         self._inflight = None
+        self.tolerated = 0
+        self.tolerated_seen = 0
 
     # bits of a status word (ops/csrc/common.cuh, moe.cu)
     _BITS = ((1, "a RoPE position outside the table"), (2, "a label outside the vocabulary"),
@@ -59,6 +63,18 @@ class StatusMonitor:
                  "set it to 0 for the worst-case capacity)"))
 
     def _raise_if_set(self, values: list[int], names: list[str]) -> None:
+        if self.tolerated and any(v & self.tolerated for v in values):
+            self.tolerated_seen += 1
+            if self.tolerated_seen in (1, 10, 100) or self.tolerated_seen % 1000 == 0:
+                from torchtitan_b200.utils.logging import logger
+
+                logger.warning("tolerated device status (seen %d times): %s", self.tolerated_seen, "; ".join(
+                    f"{n}: " + ", ".join(t for b, t in self._BITS if v & b & self.tolerated) for n, v in zip(names, values)
+                    if v & self.tolerated))
+            for (_, w), v in zip(self._words, values):
+                if v & self.tolerated and not v & ~self.tolerated:
+                    w.zero_()
+            values = [v & ~self.tolerated for v in values]
         bad = [(n, v) for n, v in zip(names, values) if v]
         if bad:
             for _, w in self._words:

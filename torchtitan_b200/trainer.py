@@ -123,6 +123,8 @@ class Trainer(Configurable):
         from torchtitan_b200.parallel.symm import status_monitor
 
         status_monitor.clear()   # arenas of an earlier trainer in this process are gone
+        if c.parallelism.ep_overflow == "drop":
+            status_monitor.tolerated |= 8
         self.device = get_local_device()
         if self.device.type == "cuda":
             torch.cuda.set_device(self.device)
