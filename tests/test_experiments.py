@@ -386,7 +386,7 @@ def _ft_replica(rid, n, port, die_at, out, folder):
         "--training.max_context_length", "64", "--training.mixed_precision_param", "float32", "--debug.seed", "0",
         "--dump_folder", f"{folder}/r{rid}", "--debug.no-enable_structured_logging", "--checkpoint.no-enable",
         "--dataloader.seed", str(10 + rid), "--metrics.log_freq", "100"])
-    ft = FaultToleranceConfig(enable=True, replica_id=rid, group_size=n, heartbeat_timeout_s=1.0, quorum_timeout_s=5.0)
+    ft = FaultToleranceConfig(enable=True, replica_id=rid, group_size=n, heartbeat_timeout_s=4.0, quorum_timeout_s=12.0)
     t = FaultTolerantTrainer(cfg, fault_tolerance=ft, store=store)
     it = t.batch_generator(t.dataloader)
     members, losses = [], []

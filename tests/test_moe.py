@@ -82,3 +82,19 @@ def test_expert_parallel_matches_local(tmp_path):
     out = str(tmp_path / "ep.pt")
     run_distributed(_ep_fn, 2, out)
     assert float(torch.load(out)) == 1.0
+
+
+def test_force_load_balance_flag_reaches_every_router(tmp_path):
+    """``debug.moe_force_load_balance`` assigns experts round-robin in every mixture-of-experts layer (balanced counts)."""
+    from torchtitan_b200.config import ConfigManager
+
+    cfg = ConfigManager().parse_args([
+        "--module", "qwen3", "--config", "qwen3_moe_tiny", "--debug.moe_force_load_balance",
+        "--training.num_tokens_per_microbatch_per_dp_rank", "64", "--training.max_context_length", "64",
+        "--debug.no-enable_structured_logging", "--dump_folder", str(tmp_path)])
+    t = cfg.build()
+    routers = [blk.moe.router for blk in t.model.layers.values() if blk.moe is not None]
+    assert routers and all(r.config._debug_force_load_balance for r in routers)
+    _, sel, counts = routers[0](torch.randn(64, 64), None)
+    assert torch.equal(counts, torch.full((8,), 16.0)) and sel.shape == (64, 2)
+    t.close()

@@ -183,51 +183,66 @@ def grouped_linear(x: torch.Tensor, w: torch.Tensor, offs: torch.Tensor) -> torc
     return _GroupedLinearFn.apply(x, w, offs)
 
 
+def swiglu_experts_fwd(x, w1, w3, w2, offs, out=None):
+    """``(silu(x w1^T) * (x w3^T)) w2^T`` per expert on the padded layout; returns ``(y, gu)`` with ``gu[R, 2F]`` the
+    two first GEMM outputs side by side (what the backward keeps).  ``out``: write ``y`` into this buffer."""
+    R = x.shape[0]
+    F_ = w1.shape[1]
+    # the two projections write the column halves of one [R, 2F] buffer (strided output rows), the layout the
+    # SwiGLU kernel takes
+    gu = torch.empty(R, 2 * F_, dtype=x.dtype, device=x.device)
+    _gg(x, w1, gu[:, :F_], offs, 0)
+    _gg(x, w3, gu[:, F_:], offs, 0)
+    # rows at or beyond offs[-1] hold whatever the allocator returned; they are never consumed
+    a = ext.require().swiglu_fwd(gu)
+    _count()
+    y = out if out is not None else torch.empty(R, w2.shape[1], dtype=x.dtype, device=x.device)
+    _gg(a, w2, y, offs, 0)
+    return y, gu
+
+
+def swiglu_experts_bwd(dy, x, gu, w1, w3, w2, offs, need_dx=True, dx_out=None):
+    """Backward of :func:`swiglu_experts_fwd`: the activation is recomputed from ``gu``; weight gradients go to the
+    parameters' ``main_grad`` buffers when they have them (then the returned ``dw`` is None).  ``dx_out``: write the
+    input gradient into this buffer.  Returns ``(dx, dw1, dw3, dw2)``."""
+    ops = ext.require()
+    dy = dy.contiguous()
+    F_ = w1.shape[1]
+    a = ops.swiglu_fwd(gu)
+    dw2 = _grouped_wgrad(dy, a, w2, offs) if w2.requires_grad else None
+    # rows at or beyond offs[-1] of da / dgu / dx are never written nor consumed (the grouped GEMMs only visit
+    # the padded groups), so none of these buffers needs clearing
+    da = torch.empty_like(a)
+    del a
+    _gg(dy, w2, da, offs, 1)
+    dgu = ops.swiglu_bwd(gu, da)
+    _count(2)
+    del da
+    dh, du = dgu[:, :F_], dgu[:, F_:]        # column halves, read in place through strided tensor maps
+    dw1 = _grouped_wgrad(dh, x, w1, offs) if w1.requires_grad else None
+    dw3 = _grouped_wgrad(du, x, w3, offs) if w3.requires_grad else None
+    dx = None
+    if need_dx:
+        dx = dx_out if dx_out is not None else torch.empty_like(x)
+        _gg(dh, w1, dx, offs, 1)
+        _gg(du, w3, dx, offs, 1, accumulate=True)
+    return dx, dw1, dw3, dw2
+
+
 class _GroupedSwiGLUExpertsFn(torch.autograd.Function):
-    """``(silu(x w1^T) * (x w3^T)) w2^T`` per expert, keeping ``x`` and the two first GEMM outputs;
-    the activation is recomputed in backward (same policy as the dense SwiGLU MLP)."""
+    """Autograd form of ``swiglu_experts_fwd`` / ``swiglu_experts_bwd``, keeping ``x`` and ``gu``; the activation is
+    recomputed in backward (same policy as the dense SwiGLU MLP)."""
 
     @staticmethod
     def forward(ctx, x, w1, w3, w2, offs):
-        R = x.shape[0]
-        F_ = w1.shape[1]
-        # the two projections write the column halves of one [R, 2F] buffer (strided output rows), the layout the
-        # SwiGLU kernel takes
-        gu = torch.empty(R, 2 * F_, dtype=x.dtype, device=x.device)
-        _gg(x, w1, gu[:, :F_], offs, 0)
-        _gg(x, w3, gu[:, F_:], offs, 0)
-        # rows at or beyond offs[-1] hold whatever the allocator returned; they are never consumed
-        a = ext.require().swiglu_fwd(gu)
-        _count()
-        y = torch.empty(R, w2.shape[1], dtype=x.dtype, device=x.device)
-        _gg(a, w2, y, offs, 0)
+        y, gu = swiglu_experts_fwd(x, w1, w3, w2, offs)
         ctx.save_for_backward(x, gu, w1, w3, w2, offs)
         return y
 
     @staticmethod
     def backward(ctx, dy):
         x, gu, w1, w3, w2, offs = ctx.saved_tensors
-        ops = ext.require()
-        dy = dy.contiguous()
-        F_ = w1.shape[1]
-        a = ops.swiglu_fwd(gu)
-        dw2 = _grouped_wgrad(dy, a, w2, offs) if w2.requires_grad else None
-        # rows at or beyond offs[-1] of da / dgu / dx are never written nor consumed (the grouped GEMMs only visit
-        # the padded groups), so none of these buffers needs clearing
-        da = torch.empty_like(a)
-        del a
-        _gg(dy, w2, da, offs, 1)
-        dgu = ops.swiglu_bwd(gu, da)
-        _count(2)
-        del da
-        dh, du = dgu[:, :F_], dgu[:, F_:]        # column halves, read in place through strided tensor maps
-        dw1 = _grouped_wgrad(dh, x, w1, offs) if w1.requires_grad else None
-        dw3 = _grouped_wgrad(du, x, w3, offs) if w3.requires_grad else None
-        dx = None
-        if ctx.needs_input_grad[0]:
-            dx = torch.empty_like(x)
-            _gg(dh, w1, dx, offs, 1)
-            _gg(du, w3, dx, offs, 1, accumulate=True)
+        dx, dw1, dw3, dw2 = swiglu_experts_bwd(dy, x, gu, w1, w3, w2, offs, need_dx=ctx.needs_input_grad[0])
         return dx, dw1, dw3, dw2, None
 
 

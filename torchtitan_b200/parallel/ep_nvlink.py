@@ -70,33 +70,49 @@ class EPNvlink:
         return dest_rank, dest_row, my_offs, my_counts
 
 
+def _plain_experts(experts) -> bool:
+    """Plain bf16 grouped SwiGLU experts: the exchange calls their forward / backward directly, with the symmetric
+    buffers as the GEMM outputs.  Anything else (quantised recipes, other expert classes) runs as a nested autograd
+    graph on copies."""
+    return (type(experts).__name__ == "GroupedExperts" and not getattr(experts, "quant_recipe", None)
+            and all(hasattr(experts, n) for n in ("w1_EFD", "w3_EFD", "w2_EDF")))
+
+
 class _EPNvlinkFn(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, top_scores, ep: EPNvlink, experts, dest_rank, dest_row, my_offs, my_counts):
+    def forward(ctx, x, top_scores, ep: EPNvlink, experts, dest_rank, dest_row, my_offs, my_counts, *weights):
         ops = ext.require()
         xbuf, xptrs = ep.bufs["x"]
         ybuf, yptrs = ep.bufs["y"]
         ops.ep_scatter_rows(x.contiguous(), dest_rank, dest_row, None, xptrs)
         ep.arena.barrier()
         ops.moe_zero_pad_rows(xbuf, my_offs, my_counts)
-        with torch.enable_grad():
-            # the whole static buffer: rows at or beyond my_offs[-1] are never read by the grouped GEMMs
-            x_loc = xbuf.clone().requires_grad_(True)
-            y_loc = experts.forward_padded(x_loc, my_offs)
-        ybuf.copy_(y_loc.detach())
+        # the whole static buffer is kept for the weight gradients (the next layer's dispatch overwrites xbuf): rows
+        # at or beyond my_offs[-1] are never read by the grouped GEMMs
+        ctx.plain = bool(weights)
+        if ctx.plain:
+            w1, w3, w2 = weights
+            x_loc = xbuf.clone()
+            _, gu = moe_ops.swiglu_experts_fwd(x_loc, w1, w3, w2, my_offs, out=ybuf)   # the last GEMM writes ybuf
+            ctx.local = (x_loc, gu)
+            ctx.weights = weights
+        else:
+            with torch.enable_grad():
+                x_loc = xbuf.clone().requires_grad_(True)
+                y_loc = experts.forward_padded(x_loc, my_offs)
+            ybuf.copy_(y_loc.detach())
+            ctx.local = (x_loc, y_loc)
         ep.arena.barrier()
         wts = top_scores.float().contiguous()
         out, keep = ops.ep_gather_rows(yptrs, dest_rank, dest_row, wts, x.shape[1], True, x)
         _count(4)
         ctx.save_for_backward(dest_rank, dest_row, my_offs, my_counts, wts, keep)
-        ctx.local = (x_loc, y_loc)
         ctx.ep = ep
         return out
 
     @staticmethod
     def backward(ctx, dout):
         dest_rank, dest_row, my_offs, my_counts, wts, keep = ctx.saved_tensors
-        x_loc, y_loc = ctx.local
         ep = ctx.ep
         ops = ext.require()
         dout = dout.contiguous()
@@ -106,13 +122,23 @@ class _EPNvlinkFn(torch.autograd.Function):
         ops.ep_scatter_rows(dout, dest_rank, dest_row, wts, dyptrs)
         ep.arena.barrier()
         ops.moe_zero_pad_rows(dybuf, my_offs, my_counts)
-        torch.autograd.backward(y_loc, dybuf)
-        dxbuf.copy_(x_loc.grad)
+        wgrads = ()
+        if ctx.plain:
+            x_loc, gu = ctx.local
+            w1, w3, w2 = ctx.weights
+            # the input-gradient GEMMs write dxbuf; weight gradients go to main_grad (or come back for autograd)
+            _, dw1, dw3, dw2 = moe_ops.swiglu_experts_bwd(dybuf, x_loc, gu, w1, w3, w2, my_offs, need_dx=True, dx_out=dxbuf)
+            wgrads = (dw1, dw3, dw2)
+            ctx.weights = None
+        else:
+            x_loc, y_loc = ctx.local
+            torch.autograd.backward(y_loc, dybuf)
+            dxbuf.copy_(x_loc.grad)
         ep.arena.barrier()
         dx, _ = ops.ep_gather_rows(dxptrs, dest_rank, dest_row, None, dout.shape[1], False, dout)
         _count(4)
         ctx.local = None
-        return dx, dw, None, None, None, None, None, None
+        return (dx, dw, None, None, None, None, None, None) + wgrads
 
 
 def ep_experts_nvlink(ep: EPNvlink, experts, x: torch.Tensor, top_scores: torch.Tensor, selected: torch.Tensor,
@@ -120,4 +146,5 @@ def ep_experts_nvlink(ep: EPNvlink, experts, x: torch.Tensor, top_scores: torch.
     """Dispatch, grouped experts and weighted combine for tokens ``x[T, D]``; returns ``[T, D]``."""
     with torch.no_grad():
         dest_rank, dest_row, my_offs, my_counts = ep.layout(selected, counts)
-    return _EPNvlinkFn.apply(x, top_scores, ep, experts, dest_rank, dest_row, my_offs, my_counts)
+    weights = (experts.w1_EFD, experts.w3_EFD, experts.w2_EDF) if _plain_experts(experts) else ()
+    return _EPNvlinkFn.apply(x, top_scores, ep, experts, dest_rank, dest_row, my_offs, my_counts, *weights)

@@ -170,7 +170,7 @@ class Trainer(Configurable):
             done = apply_overrides(model_cfg, c.override.imports)
             logger.info(f"applied overrides: {done}")
         if c.debug.moe_force_load_balance:
-            for ref in model_cfg.walk(object):
+            for ref in model_cfg.walk(object, descend_into_matches=True):
                 if hasattr(ref.config, "_debug_force_load_balance"):
                     ref.config._debug_force_load_balance = True
         self.model_config = model_cfg
