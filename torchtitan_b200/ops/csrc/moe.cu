@@ -379,16 +379,26 @@ __global__ void ep_scatter_rows_kernel(const __nv_bfloat16* __restrict__ x, cons
   if (row < 0) return;
   const bf16x8* src = reinterpret_cast<const bf16x8*>(x + (s / K) * D);
   bf16x8* dst = reinterpret_cast<bf16x8*>(out.p[dest_rank[s]] + (int64_t)row * D);
-  if (wts == nullptr) {
-    for (int i = lane; i < D / 8; i += 32) dst[i] = src[i];
-  } else {
-    const float w = wts[s];
-    for (int i = lane; i < D / 8; i += 32) {
-      float v[8];
-      unpack8(src[i], v);
+  const float w = wts == nullptr ? 1.f : wts[s];
+  // four 16-byte loads in flight per lane before the (possibly remote) stores go out
+  const int n = D / 8;
+  for (int base = lane; base < n; base += 128) {
+    bf16x8 r[4];
 #pragma unroll
-      for (int j = 0; j < 8; ++j) v[j] *= w;
-      dst[i] = pack8(v);
+    for (int j = 0; j < 4; ++j)
+      if (base + 32 * j < n) r[j] = src[base + 32 * j];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      if (base + 32 * j < n) {
+        if (wts != nullptr) {
+          float v[8];
+          unpack8(r[j], v);
+#pragma unroll
+          for (int q = 0; q < 8; ++q) v[q] *= w;
+          r[j] = pack8(v);
+        }
+        dst[base + 32 * j] = r[j];
+      }
     }
   }
 }
@@ -400,18 +410,37 @@ __global__ void ep_gather_rows_kernel(EpPeers y, const int* __restrict__ dest_ra
   const int64_t t = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
   if (t >= T) return;
+  // per 16-byte column all K rows of the token are fetched before they are summed (K independent peer loads in
+  // flight instead of a load -> accumulate chain)
+  constexpr int kMaxK = 8;
   for (int i = lane; i < D / 8; i += 32) {
     float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-    for (int k = 0; k < K; ++k) {
-      const int row = dest_row[t * K + k];
-      if (row < 0) continue;
-      const bf16x8 raw = reinterpret_cast<const bf16x8*>(y.p[dest_rank[t * K + k]] + (int64_t)row * D)[i];
-      if (keep != nullptr) reinterpret_cast<bf16x8*>(keep + (t * K + k) * D)[i] = raw;
-      float v[8];
-      unpack8(raw, v);
-      const float w = kWeighted ? wts[t * K + k] : 1.f;
+    for (int k0 = 0; k0 < K; k0 += kMaxK) {
+      bf16x8 raw[kMaxK];
+      bool live[kMaxK];
 #pragma unroll
-      for (int j = 0; j < 8; ++j) acc[j] += w * v[j];
+      for (int u = 0; u < kMaxK; ++u) {
+        const int k = k0 + u;
+        live[u] = false;
+        if (k < K) {
+          const int row = dest_row[t * K + k];
+          if (row >= 0) {
+            live[u] = true;
+            raw[u] = reinterpret_cast<const bf16x8*>(y.p[dest_rank[t * K + k]] + (int64_t)row * D)[i];
+          }
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < kMaxK; ++u) {
+        if (!live[u]) continue;
+        const int k = k0 + u;
+        if (keep != nullptr) reinterpret_cast<bf16x8*>(keep + (t * K + k) * D)[i] = raw[u];
+        float v[8];
+        unpack8(raw[u], v);
+        const float w = kWeighted ? wts[t * K + k] : 1.f;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[j] += w * v[j];
+      }
     }
     reinterpret_cast<bf16x8*>(out + t * D)[i] = pack8(acc);
   }
