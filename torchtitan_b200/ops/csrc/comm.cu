@@ -13,6 +13,7 @@
 //    all-gather happens inside the optimizer kernel.
 //
 // Peer memory is only touched with plain ld/st.global (no TMA, no multicast loads).
+#include <cstdlib>
 #include <ATen/ATen.h>
 #include <ATen/cuda/CUDAContext.h>
 #include <c10/cuda/CUDAGuard.h>
@@ -157,6 +158,18 @@ __global__ void __launch_bounds__(256) reduce_scatter_pull_kernel(PeerPtrs peers
   }
 }
 
+// Thread blocks per SM of the communication kernels that run on a side stream next to the GEMMs.  More blocks keep
+// more peer loads in flight; fewer leave more issue slots and memory bandwidth to the compute stream.  The environment
+// variable TB200_COMM_CTAS_PER_SM overrides the per-kernel default (read once).
+static int comm_ctas_per_sm(int dflt) {
+  static const int env = [] {
+    const char* e = std::getenv("TB200_COMM_CTAS_PER_SM");
+    const int v = e ? std::atoi(e) : 0;
+    return v > 0 && v <= 32 ? v : 0;
+  }();
+  return env ? env : dflt;
+}
+
 void reduce_scatter_pull(at::IntArrayRef grad_ptrs, int64_t my_rank, int64_t offset, at::Tensor out, bool grad_is_bf16,
                          bool accumulate) {
   TORCH_CHECK(out.is_cuda() && out.scalar_type() == at::kFloat && out.is_contiguous());
@@ -168,7 +181,7 @@ void reduce_scatter_pull(at::IntArrayRef grad_ptrs, int64_t my_rank, int64_t off
   const int nr = (int)grad_ptrs.size();
   auto stream = at::cuda::getCurrentCUDAStream();
   const int64_t nvec = n / 8;
-  const int grid = (int)std::max<int64_t>(1, std::min<int64_t>((nvec + 255) / 256, (int64_t)num_sms() * 8));
+  const int grid = (int)std::max<int64_t>(1, std::min<int64_t>((nvec + 255) / 256, (int64_t)num_sms() * comm_ctas_per_sm(8)));
   float* op = out.data_ptr<float>();
 #define TB_RS(G, NR) \
   reduce_scatter_pull_kernel<G, NR><<<grid, 256, 0, stream>>>(pp, nr, (int)my_rank, offset, nvec, op, accumulate ? 1 : 0)
@@ -304,7 +317,7 @@ void adamw_allgather_(at::Tensor master, const at::Tensor& grad, at::Tensor exp_
   const int nr = (int)param_ptrs.size();
   auto stream = at::cuda::getCurrentCUDAStream();
   const int64_t nvec = n / 8;
-  const int grid = (int)std::max<int64_t>(1, std::min<int64_t>((nvec + 255) / 256, (int64_t)num_sms() * 16));
+  const int grid = (int)std::max<int64_t>(1, std::min<int64_t>((nvec + 255) / 256, (int64_t)num_sms() * comm_ctas_per_sm(16)));
   const bool sb = exp_avg.scalar_type() == at::kBFloat16;
   TORCH_CHECK(sb || exp_avg.scalar_type() == at::kFloat);
 #define TB_AG(S, P)                                                                                             \
