@@ -226,6 +226,34 @@ def test_cuda_graph_step_matches_eager(tmp_path):
     assert graph[-1] < graph[0]
 
 
+def test_per_op_checkpoint_keeps_flash_outputs_on_gpu(tmp_path):
+    """``selective_ac_option = op_half_mm`` on the kernels: blocks are recomputed in backward, the flash-attention
+    output and every second GEMM output are handed back from the first forward; same losses as keeping everything,
+    and the attention kernel is not launched again in backward."""
+    from torchtitan_b200.config import ConfigManager
+
+    def run(opt: str):
+        args = ["--module", "llama3", "--config", "llama3_debugmodel_hd128", "--training.steps", "4",
+                "--training.num_tokens_per_microbatch_per_dp_rank", "512", "--training.max_context_length", "256",
+                "--debug.seed", "0", "--dump_folder", str(tmp_path / opt), "--debug.no-enable_structured_logging",
+                "--checkpoint.no-enable", "--metrics.log_freq", "1", "--activation_checkpoint.selective_ac_option", opt]
+        tr = ConfigManager().parse_args(args).build()
+        losses = []
+        it = tr.batch_generator(tr.dataloader)
+        for _ in range(4):
+            tr.step += 1
+            tr.train_step(it)
+            losses.append(float(tr._last_loss))
+        sess = getattr(next(iter(tr.model.layers.values())), "_last_sac_session", None)
+        tr.close()
+        return losses, sess
+
+    (keep_all, _), (half, sess) = run("op"), run("op_half_mm")
+    assert all(abs(a - b) < 2e-2 for a, b in zip(keep_all, half)), (keep_all, half)
+    # per block: attention + two of the four GEMMs kept (wqkv is rotated in place and given up), two GEMMs recomputed
+    assert sess is not None and (sess.saved, sess.recomputed) == (3, 2) and not sess.store
+
+
 def test_optimizer_state_offload_matches_resident_state():
     """Pinned-host optimizer state streamed through the GPU gives the same parameters as resident
     state (up to the run-to-run last-bit differences of the atomically summed gradient norm)."""
