@@ -338,3 +338,39 @@ def test_gemm_and_norm_are_batch_invariant():
         assert torch.equal(nb[:8], ns)
         with pytest.raises(RuntimeError, match="batch-invariant"):
             OF.gemm_nt(torch.randn(64, 36, device="cuda").bfloat16(), torch.randn(16, 36, device="cuda").bfloat16())
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("T,C,W,docs", [(300, 256, 4, True), (64, 64, 4, False), (1000, 136, 2, True), (5, 8, 3, True)])
+def test_causal_conv_silu_kernel(T, C, W, docs, dtype):
+    """The fused depthwise causal convolution + SiLU (forward, dx, dw) against the tap-by-tap PyTorch form in fp32,
+    with taps cut at document starts and row blocks that do not divide the sequence."""
+    from torchtitan_b200.models.qwen3_5 import gdn
+
+    g = torch.Generator(device="cuda").manual_seed(T + C)
+    x32 = torch.randn(T, C, device="cuda", generator=g)
+    w32 = torch.randn(C, W, device="cuda", generator=g) * 0.5
+    dy32 = torch.randn(T, C, device="cuda", generator=g)
+    pos = None
+    if docs:
+        starts = sorted({0, T // 3, T // 3 + 1, (2 * T) // 3})
+        idx = torch.arange(T, device="cuda")
+        st = torch.tensor(starts, device="cuda")
+        pos = idx - st[torch.searchsorted(st, idx, right=True) - 1]
+    x, w, dy = (t.to(dtype) for t in (x32, w32, dy32))
+    xr, wr = x.float().clone().requires_grad_(), w.float().clone().requires_grad_()
+    orig = gdn._conv_kernel_ok
+    gdn._conv_kernel_ok = lambda *_: False
+    try:
+        ref = gdn.causal_conv_silu(xr, wr, pos)
+        ref.backward(dy.float())
+    finally:
+        gdn._conv_kernel_ok = orig
+    xk, wk = x.detach().clone().requires_grad_(), w.detach().clone().requires_grad_()
+    assert gdn._conv_kernel_ok(xk, wk)
+    out = gdn.causal_conv_silu(xk, wk, pos)
+    out.backward(dy)
+    tol = 1e-5 if dtype == torch.float32 else 2e-2
+    for got, want in ((out, ref), (xk.grad, xr.grad), (wk.grad, wr.grad)):
+        err = (got.float() - want).abs().max().item()
+        assert err <= tol * (want.abs().max().item() + 1.0), (err, want.abs().max().item())

@@ -94,9 +94,47 @@ def chunk_gated_delta_rule(q, k, v, g, beta, chunk: int = 64):
     return o.transpose(0, 1).to(dt)
 
 
+class _ConvSiluFn(torch.autograd.Function):
+    """The convolution + SiLU as one kernel each way (``ops/csrc/conv.cu``): x is read once, the backward recomputes
+    the pre-activation and returns dx and the fp32 weight gradient."""
+
+    @staticmethod
+    def forward(ctx, x, weight, positions):
+        from torchtitan_b200.ops import ext
+        from torchtitan_b200.ops.functional import _count
+
+        w32 = weight.detach().float().contiguous()
+        pos = None if positions is None else positions.to(torch.int64).contiguous()
+        ctx.save_for_backward(x, w32, pos if pos is not None else torch.empty(0))
+        ctx.has_pos = pos is not None
+        ctx.weight = weight
+        _count()
+        return ext.require().conv_silu_fwd(x, w32, pos)
+
+    @staticmethod
+    def backward(ctx, dy):
+        from torchtitan_b200.ops import ext
+        from torchtitan_b200.ops.functional import _count, _deliver_wgrad
+
+        x, w32, pos = ctx.saved_tensors
+        _count()
+        dx, dw = ext.require().conv_silu_bwd(x, w32, pos if ctx.has_pos else None, dy.contiguous())
+        w = ctx.weight
+        return dx, _deliver_wgrad(w, dw.to(w.dtype)) if w.requires_grad else None, None
+
+
+def _conv_kernel_ok(x: torch.Tensor, weight: torch.Tensor) -> bool:
+    from torchtitan_b200.ops import ext
+
+    return (x.is_cuda and x.dim() == 2 and x.is_contiguous() and x.dtype in (torch.bfloat16, torch.float32)
+            and weight.shape[-1] <= 4 and x.shape[1] % (8 if x.dtype == torch.bfloat16 else 4) == 0 and ext.available())
+
+
 def causal_conv_silu(x: torch.Tensor, weight: torch.Tensor, positions: torch.Tensor | None) -> torch.Tensor:
     """Depthwise causal convolution over tokens + SiLU.  ``x [T, C]``, ``weight [C, W]``; taps that
     would reach before the start of the token's document (``positions``) contribute nothing."""
+    if _conv_kernel_ok(x, weight):
+        return _ConvSiluFn.apply(x, weight, positions)
     T, C = x.shape
     W = weight.shape[-1]
     y = x * weight[:, W - 1].to(x.dtype)

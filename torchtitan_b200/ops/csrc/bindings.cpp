@@ -9,6 +9,9 @@ std::tuple<at::Tensor, at::Tensor> rmsnorm_bwd(const at::Tensor& dy, const at::T
 void rope_(at::Tensor x, const at::Tensor& table, const at::Tensor& positions, bool interleaved, bool inverse);
 at::Tensor swiglu_fwd(const at::Tensor& gu);
 at::Tensor swiglu_bwd(const at::Tensor& gu, const at::Tensor& dout);
+at::Tensor conv_silu_fwd(const at::Tensor& x, const at::Tensor& w, const c10::optional<at::Tensor>& pos);
+std::tuple<at::Tensor, at::Tensor> conv_silu_bwd(const at::Tensor& x, const at::Tensor& w,
+                                                 const c10::optional<at::Tensor>& pos, const at::Tensor& dy);
 int64_t status(bool clear);
 at::Tensor cross_entropy_(at::Tensor logits, const at::Tensor& labels, const at::Tensor& scale);
 void adamw_(at::Tensor master, const at::Tensor& grad, at::Tensor exp_avg, at::Tensor exp_avg_sq,
@@ -92,6 +95,8 @@ TORCH_LIBRARY(tb200, m) {
   m.def("rope_(Tensor(a!) x, Tensor table, Tensor positions, bool interleaved, bool inverse) -> ()", &tb200::rope_);
   m.def("swiglu_fwd(Tensor gu) -> Tensor", &tb200::swiglu_fwd);
   m.def("swiglu_bwd(Tensor gu, Tensor dout) -> Tensor", &tb200::swiglu_bwd);
+  m.def("conv_silu_fwd(Tensor x, Tensor w, Tensor? pos) -> Tensor", &tb200::conv_silu_fwd);
+  m.def("conv_silu_bwd(Tensor x, Tensor w, Tensor? pos, Tensor dy) -> (Tensor, Tensor)", &tb200::conv_silu_bwd);
   m.def("status(bool clear) -> int", &tb200::status);
   m.def("cross_entropy_(Tensor(a!) logits, Tensor labels, Tensor scale) -> Tensor", &tb200::cross_entropy_);
   m.def("adamw_(Tensor(a!) master, Tensor grad, Tensor(b!) exp_avg, Tensor(c!) exp_avg_sq, Tensor(d!)? lowp, "
