@@ -368,12 +368,16 @@ def _ep_nvlink(rank, world, out_path):
 
     res = []
     models = {comm: make(comm) for comm in ("nccl", "nvlink")}
+    # a third model on the exact mode of the NVLink dispatcher (worst-case buffers, received row count read on the
+    # host per exchange, kept rows and activations of that size)
+    models["nvlink_exact"] = make("nvlink")
+    models["nvlink_exact"].routed_experts.ep.nvlink.exact = True
     for it in range(2):   # two rounds: the symmetric buffers are reused
         g = torch.Generator(device=dev).manual_seed(50 + 7 * it + rank)
         x = (torch.randn(T, dim, device=dev, generator=g) * 0.5).bfloat16()
         dy = (torch.randn(T, dim, device=dev, generator=g) * 0.1).bfloat16()
         outs = {}
-        for comm in ("nccl", "nvlink"):
+        for comm in ("nccl", "nvlink", "nvlink_exact"):
             m = models[comm]
             m.zero_grad()
             xi = x.clone().requires_grad_()
@@ -381,8 +385,9 @@ def _ep_nvlink(rank, world, out_path):
             y.backward(dy)
             outs[comm] = (y.detach().float(), xi.grad.float(), m.routed_experts.inner_experts.w1_EFD.grad.float(),
                           m.router.gate.weight.grad.float())
-        for a, b in zip(outs["nccl"], outs["nvlink"]):
-            res.append((a - b).abs().max().item() / (a.abs().max().item() + 1e-6))
+        for other in ("nvlink", "nvlink_exact"):
+            for a, b in zip(outs["nccl"], outs[other]):
+                res.append((a - b).abs().max().item() / (a.abs().max().item() + 1e-6))
     # the NVLink dispatcher has no host read and no library collective: the layer's forward can be captured in a
     # CUDA graph (a synchronisation during capture would raise) and the replay reproduces the eager result
     m = models["nvlink"]
@@ -405,6 +410,7 @@ def _ep_nvlink(rank, world, out_path):
         res.append((y_static.float() - y_eager).abs().max().item() / (y_eager.abs().max().item() + 1e-6))
     torch.cuda.synchronize()
     st = int(models["nvlink"].routed_experts.ep.nvlink.arena.status.item()) | int(torch.ops.tb200.gemm_status(True))
+    st |= int(models["nvlink_exact"].routed_experts.ep.nvlink.arena.status.item())
     t = torch.tensor(res + [float(st)], device=dev)
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
     if rank == 0:

@@ -95,7 +95,8 @@ class ParallelismConfig:
     ep_comm: Literal["nccl", "nvlink"] = "nccl"
     """``nvlink``: token dispatch / combine as in-kernel peer stores / loads over symmetric memory."""
     ep_capacity_factor: float = 0.0
-    """Rows of the nvlink receive buffer = factor * tokens * top_k (0 = the worst case, ep degree)."""
+    """Rows of the nvlink receive buffer = factor * tokens * top_k: static, no host read, CUDA-graph capturable.
+    0 (default): worst-case buffers and one host read of the received row count per exchange (any imbalance fits)."""
     ep_overflow: Literal["error", "drop"] = "error"
     """Routed rows beyond the receive buffer of their rank: ``error`` stops training at the next status poll,
     ``drop`` leaves them out of the step (they contribute nothing to the layer output; a warning is logged)."""

@@ -13,10 +13,12 @@ The backward mirrors it (scatter of ``w * dout``, local grouped backward, pull o
 layout is computed on the device as well: every rank stores its per-expert token counts into a small
 symmetric table of every peer, and after a flag barrier one kernel derives the destination rank and
 row of every routing slot and this rank's group offsets (``ep_publish_counts`` / ``ep_layout``).  There
-is no library collective, no sort and no host read anywhere in the exchange, so a MoE layer can be
-captured in a CUDA graph; buffers have a static capacity (``parallelism.ep_capacity_factor`` times the
-balanced load), and a slot that does not fit is dropped and reported through the arena's status word
-(bit 3), which the trainer polls.  (The reference's counterpart is its sync-free MinimalAsyncEP,
+is no library collective and no sort anywhere in the exchange.  With ``parallelism.ep_capacity_factor > 0`` the
+buffers have a static capacity (the factor times the balanced load) and nothing is read on the host, so a MoE layer
+can be captured in a CUDA graph; a slot that does not fit is dropped and reported through the arena's status word
+(bit 3), which the trainer polls (``parallelism.ep_overflow``).  With the default factor 0 the buffers hold the worst
+case and each exchange reads the number of rows this rank received on the host (the exact mode: any routing
+imbalance fits, e.g. a freshly initialised router; kept rows and expert activations have the received size).  (The reference's counterpart is its sync-free MinimalAsyncEP,
 torchtitan/distributed/minimal_async_ep/api.py:174-385; its all-to-all dispatcher reads split sizes on
 the host, torchtitan/models/common/token_dispatcher.py:245-370.)  Each exchange is fenced by the bounded
 flag barrier of the symmetric arena; buffer reuse across layers needs no extra barrier because a rank
@@ -37,7 +39,12 @@ __all__ = ["EPNvlink", "ep_experts_nvlink"]
 
 
 class EPNvlink:
-    def __init__(self, group, device: torch.device, capacity_rows: int, dim: int, num_experts: int):
+    def __init__(self, group, device: torch.device, capacity_rows: int, dim: int, num_experts: int, exact: bool = False):
+        """``exact``: the symmetric buffers hold the worst case (``capacity_rows`` = every routed row of every rank)
+        and each exchange reads the number of rows this rank really received on the host, so that the rows kept
+        for backward and the expert activations have that size: any routing imbalance fits, at the price of one
+        host read per layer (no CUDA-graph capture).  Otherwise the capacity is static and nothing is read."""
+        self.exact = exact
         self.group = group
         self.size = dist.get_world_size(group)
         self.rank = dist.get_rank(group)
@@ -86,6 +93,12 @@ class _EPNvlinkFn(torch.autograd.Function):
         ybuf, yptrs = ep.bufs["y"]
         ops.ep_scatter_rows(x.contiguous(), dest_rank, dest_row, None, xptrs)
         ep.arena.barrier()
+        R = ep.cap
+        if ep.exact:
+            # rows this rank received, padded per expert (the one host read of the exact mode)
+            R = max(moe_ops.ALIGN, min(ep.cap, int(my_offs[-1])))
+            xbuf, ybuf = xbuf[:R], ybuf[:R]
+        ctx.rows = R
         ops.moe_zero_pad_rows(xbuf, my_offs, my_counts)
         # the whole static buffer is kept for the weight gradients (the next layer's dispatch overwrites xbuf): rows
         # at or beyond my_offs[-1] are never read by the grouped GEMMs
@@ -121,6 +134,7 @@ class _EPNvlinkFn(torch.autograd.Function):
         dxbuf, dxptrs = ep.bufs["dx"]
         ops.ep_scatter_rows(dout, dest_rank, dest_row, wts, dyptrs)
         ep.arena.barrier()
+        dybuf, dxbuf = dybuf[:ctx.rows], dxbuf[:ctx.rows]
         ops.moe_zero_pad_rows(dybuf, my_offs, my_counts)
         wgrads = ()
         if ctx.plain:

@@ -43,12 +43,14 @@ def apply_expert_parallel(model, pdims, parallelism) -> None:
             if moes:
                 t = getattr(parallelism, "_tokens_per_rank", 0) or 8192
                 k, e_local = moes[0].config.top_k, moes[0].num_experts // ep.size
-                # rows a rank can receive: capacity factor x the balanced load (default: the worst case, every
-                # token of every rank) plus the alignment padding of its experts
+                # rows a rank can receive: capacity factor x the balanced load plus the alignment padding of its
+                # experts.  Factor 0 (the default): buffers for the worst case (every token of every rank) and the
+                # received row count read on the host per exchange, so that any imbalance fits
+                exact = not parallelism.ep_capacity_factor
                 factor = parallelism.ep_capacity_factor or float(ep.size)
                 cap = int(factor * t * k) + e_local * 128
                 ep.nvlink = EPNvlink(ep.group, torch.device("cuda", torch.cuda.current_device()), cap, moes[0].config.dim,
-                                     moes[0].num_experts)
+                                     moes[0].num_experts, exact=exact)
     for blk in model.layers.values():
         if blk.moe is not None:
             blk.moe.routed_experts.ep = ep

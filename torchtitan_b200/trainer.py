@@ -267,7 +267,8 @@ class Trainer(Configurable):
         self._mb_index = 0
         if (not c.training.disable_cuda_graphs and self.device.type == "cuda" and not pd.pp_enabled
                 and not c.activation_checkpoint.cpu_offload   # host copies cannot be captured
-                and not (pd.ep_enabled and c.parallelism.ep_comm == "nccl")):   # the all-to-all dispatcher reads split sizes on the host
+                # the all-to-all dispatcher and the exact mode of the NVLink dispatcher read row counts on the host
+                and not (pd.ep_enabled and (c.parallelism.ep_comm == "nccl" or not c.parallelism.ep_capacity_factor))):
             from torchtitan_b200.parallel.cudagraph import CUDAGraphRunner
 
             eng = self.engines[0]
