@@ -346,6 +346,56 @@ def test_hf_model_tensor_parallel(tmp_path):
     assert torch.allclose(outs["one"][:-1], outs["dp2tp2"][:-1], atol=2e-4), outs
 
 
+def _hf_pp(rank, world, out_path):
+    import transformers
+
+    from torchtitan_b200.experiments.transformers_backend import (HFCausalLM, hf_engine_train_steps, hf_pipeline_train_steps,
+                                                                  parallelize_hf, pipeline_hf)
+    from torchtitan_b200.parallel.parallel_dims import ParallelDims
+    from torchtitan_b200.trainer import Trainer
+
+    cfg = transformers.LlamaConfig(vocab_size=128, hidden_size=32, intermediate_size=64, num_hidden_layers=4,
+                                   num_attention_heads=4, num_key_value_heads=2, max_position_embeddings=64,
+                                   tie_word_embeddings=False)
+    torch.manual_seed(0)
+    model = HFCausalLM(cfg)
+    job = Trainer.Config()
+    job.training.mixed_precision_param = "float32"
+    job.parallelism.pipeline_parallel_schedule = "1F1B"
+    job.parallelism.num_pp_microbatches = 2
+    g = torch.Generator().manual_seed(1)
+    steps = []
+    for s in range(4):
+        toks = torch.randint(0, 128, (2, 33), generator=g)
+        steps.append((toks[:, :-1].contiguous(), torch.arange(32).expand(2, 32).contiguous(), toks[:, 1:].contiguous()))
+    if world == 1:
+        pdims = ParallelDims(world_size=1, rank=0).build()
+        eng = parallelize_hf(model, pdims=pdims, job_config=job, device=torch.device("cpu"))
+        packed = [(t.reshape(-1), p.reshape(-1), l.reshape(-1)) for t, p, l in steps]
+        losses = hf_engine_train_steps(model, eng, packed, pdims=pdims, lr=3e-3)
+    else:
+        pdims = ParallelDims(world_size=world, rank=rank, pp=2).build()
+        sched, stage, eng, first, last = pipeline_hf(model, pdims=pdims, job_config=job, device=torch.device("cpu"))
+        assert (stage.embed_tokens is not None) == (rank == 0) and (stage.lm_head is not None) == (rank == 1)
+        assert len(stage.layers) in (2, 3)
+        losses = hf_pipeline_train_steps(sched, eng, steps, pdims=pdims, has_first=first, has_last=last, lr=3e-3)
+    if rank == 0:
+        torch.save(torch.tensor(losses), out_path)
+
+
+def test_hf_model_pipeline_parallel(tmp_path):
+    """A Hugging Face Llama split into two pipeline stages (1F1B, two microbatches, each stage under the sharded
+    engine) reproduces the single-rank losses on the same batches."""
+    pytest.importorskip("transformers")
+    from tests.dist_utils import run_distributed
+
+    a, b = str(tmp_path / "one.pt"), str(tmp_path / "pp.pt")
+    run_distributed(_hf_pp, 1, a)
+    run_distributed(_hf_pp, 2, b)
+    ra, rb = torch.load(a), torch.load(b)
+    assert torch.allclose(ra, rb, atol=2e-4), (ra, rb)
+
+
 def test_graph_trainer_passes_map_to_engine_settings(tmp_path):
     from torchtitan_b200.config import ConfigManager
     from torchtitan_b200.experiments.graph_trainer import GraphTrainer, apply_passes

@@ -11,7 +11,9 @@ transport, fp32 master weights and sharded AdamW: parity with parallelize.py of 
 applies FSDP to the HF layers), and ``hf_engine_train_steps`` is the training loop on it.  With a tensor-parallel
 degree in ``pdims`` the attention and MLP projections of every decoder layer are split first (``apply_hf_tensor_parallel``:
 q / k / v / gate / up column-wise, o / down row-wise with an all-reduce, activations replicated between the layers;
-parity: hf_sharding.py of the reference's backend).  A pipeline plan for HF modules is not built."""
+parity: hf_sharding.py of the reference's backend).  ``pipeline_hf`` splits the decoder layers over the pipeline
+ranks (one stage per rank, GPipe / 1F1B, every stage under the sharded engine) and ``hf_pipeline_train_steps`` trains
+on the schedule."""
 
 from __future__ import annotations
 
@@ -19,7 +21,8 @@ import torch
 import torch.distributed as dist
 import torch.nn as nn
 
-__all__ = ["HFCausalLM", "hf_train_steps", "parallelize_hf", "hf_engine_train_steps", "apply_hf_tensor_parallel"]
+__all__ = ["HFCausalLM", "hf_train_steps", "parallelize_hf", "hf_engine_train_steps", "apply_hf_tensor_parallel",
+           "pipeline_hf", "hf_pipeline_train_steps"]
 
 
 class HFCausalLM(nn.Module):
@@ -208,3 +211,134 @@ def hf_engine_train_steps(model: HFCausalLM, engine, batches, *, pdims, lr: floa
     if loss_group is not None:
         dist.all_reduce(out, group=loss_group)
     return out.tolist()
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# pipeline parallelism for HF decoder stacks
+
+
+class _HFStage(nn.Module):
+    """A contiguous slice of an HF decoder stack in the schedule's calling convention: ``x`` is ``[1, T]`` token ids
+    on the first stage and ``[1, T, D]`` hidden states elsewhere; ``positions [1, T]`` reach every stage as a keyword
+    argument, so each stage derives its own rotary tables and per-document causal mask."""
+
+    def __init__(self, hf, layer_ids: list[int], first: bool, last: bool):
+        super().__init__()
+        base = hf.model
+        self.embed_tokens = base.embed_tokens if first else None
+        self.layers = nn.ModuleList([base.layers[i] for i in layer_ids])
+        self.rotary_emb = base.rotary_emb
+        self.norm = base.norm if last else None
+        self.lm_head = hf.lm_head if last else None
+
+    def forward(self, x, positions=None):
+        T = x.shape[1]
+        if positions is None:
+            positions = torch.arange(T, device=x.device)[None]
+        h = self.embed_tokens(x) if self.embed_tokens is not None else x
+        pos = positions[0]
+        doc = torch.cumsum((pos == 0).long(), 0)
+        allowed = (doc[:, None] == doc[None, :]) & torch.ones(T, T, dtype=torch.bool, device=x.device).tril()
+        mask = torch.zeros(T, T, device=x.device, dtype=h.dtype).masked_fill(~allowed, torch.finfo(h.dtype).min)
+        cos_sin = self.rotary_emb(h, positions)
+        for layer in self.layers:
+            out = layer(h, attention_mask=mask[None, None], position_ids=positions, position_embeddings=cos_sin)
+            h = out[0] if isinstance(out, tuple) else out
+        if self.norm is not None:
+            h = self.lm_head(self.norm(h))
+        return h
+
+
+class _HFPipelineLoss:
+    def __init__(self):
+        self.global_valid: torch.Tensor | float = 1.0
+
+    def __call__(self, logits, target):
+        return nn.functional.cross_entropy(logits[0].float(), target[0], ignore_index=-100, reduction="sum") / self.global_valid
+
+
+def pipeline_hf(model: HFCausalLM, *, pdims, job_config, device: torch.device, seed: int = 0):
+    """Split the decoder layers of an ``HFCausalLM`` over the pipeline ranks (embedding on the first stage, final
+    norm + lm_head on the last; parity: pipeline.py of the reference's backend) and put every stage under the sharded
+    engine.  Returns ``(schedule, stage module, engine, has_first, has_last)``; single-stage-per-rank schedules
+    (GPipe, 1F1B)."""
+    from torch.distributed.pipelining import PipelineStage
+    from torch.distributed.pipelining.schedules import PipelineScheduleSingle, get_schedule_class
+
+    from torchtitan_b200.parallel.fsdp import ShardedModel, UnitSpec
+    from torchtitan_b200.parallel.pipeline import stage_layer_assignment
+
+    par, tr = job_config.parallelism, job_config.training
+    if model.hf.lm_head.weight is model.hf.model.embed_tokens.weight:
+        raise ValueError("tied embeddings span the first and the last pipeline stage: not supported")
+    sched_cls = get_schedule_class(par.pipeline_parallel_schedule)
+    if not issubclass(sched_cls, PipelineScheduleSingle):
+        raise ValueError("the HF pipeline plan runs one stage per rank (GPipe or 1F1B)")
+    pp, sid = pdims.pp, pdims.local_rank("pp")
+    first, layer_ids, last = stage_layer_assignment(len(model.hf.model.layers), pp)[sid]
+    stage = _HFStage(model.hf, layer_ids, first, last)
+    values = {n: p.detach().float().cpu().clone() for n, p in stage.named_parameters()}
+    units, hooks = [], []
+    if first:
+        units.append(UnitSpec("embed_tokens", [stage.embed_tokens]))
+        hooks.append(("embed_tokens", stage.embed_tokens))
+    for i, layer in zip(layer_ids, stage.layers):
+        units.append(UnitSpec(f"layers.{i}", [layer]))
+        hooks.append((f"layers.{i}", layer))
+    if last:
+        units.append(UnitSpec("output", [stage.norm, stage.lm_head]))
+        hooks.append(("output", stage.norm))
+    param_dtype = torch.bfloat16 if tr.mixed_precision_param == "bfloat16" else torch.float32
+    engine = ShardedModel(stage, units, pdims=pdims, device=device, param_dtype=param_dtype, seed=seed,
+                          comm=par.fsdp_comm, reshard_after_forward="never", grad_accum_steps=2)
+    engine.defer_reduce = True        # gradients accumulate over the microbatches, one reduction per step
+    stage.to(device)
+    engine.materialize(init=False)
+    with torch.no_grad():
+        for u in engine.units:
+            for slot, pstart, sstart, n in u.slot_pieces():
+                u.master[sstart:sstart + n].copy_(values[slot.fqn].reshape(-1)[pstart:pstart + n])
+    engine.publish_params()
+    by_name = {u.name: u for u in engine.units}
+    engine.attach_hooks([(by_name[name], module) for name, module in hooks])
+    ploss = _HFPipelineLoss()
+    pstage = PipelineStage(stage, sid, pp, device, group=pdims.group("pp"))
+    schedule = sched_cls(pstage, n_microbatches=par.num_pp_microbatches, loss_fn=ploss, scale_grads=False)
+    schedule._tb200_loss = ploss
+    return schedule, stage, engine, first, last
+
+
+def hf_pipeline_train_steps(schedule, engine, batches, *, pdims, has_first: bool, has_last: bool, lr: float = 3e-4,
+                            max_norm: float = 1.0) -> list[float]:
+    """``batches``: per step ``(tokens [M, T], positions [M, T], labels [M, T])`` with M microbatches.  Returns the
+    per-step losses (summed over the pipeline group, so every rank returns them)."""
+    from torchtitan_b200.components.optimizer import OptimizersContainer, clip_grad_norm_
+
+    opt = OptimizersContainer(OptimizersContainer.Config(lr=lr), engines=[engine])
+    dev = engine.device
+    out = []
+    loss_group = pdims.group("loss") if (pdims.dp_degree > 1) else None
+    for tokens, positions, labels in batches:
+        tokens, positions, labels = tokens.to(dev), positions.to(dev), labels.to(dev)
+        n = (labels != -100).sum().float()
+        if loss_group is not None:
+            dist.all_reduce(n, group=loss_group)
+        schedule._tb200_loss.global_valid = n
+        opt.zero_grad()
+        losses: list[torch.Tensor] = []
+        target = labels if has_last else None
+        if has_first:
+            schedule.step(tokens, target=target, losses=losses, return_outputs=False, positions=positions)
+        else:
+            schedule.step(target=target, losses=losses, return_outputs=False, positions=positions)
+        engine.finish_backward(flush=True)
+        clip_grad_norm_([engine], max_norm, pdims, optimizers=opt)
+        opt.step()
+        step_loss = torch.stack([l.detach().reshape(()) for l in losses]).sum() if (has_last and losses) else \
+            torch.zeros((), device=dev)
+        out.append(step_loss)
+    res = torch.stack(out)
+    dist.all_reduce(res, group=pdims.group("pp"))       # only the last stage holds the loss
+    if loss_group is not None:
+        dist.all_reduce(res, group=loss_group)
+    return res.tolist()
