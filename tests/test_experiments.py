@@ -163,6 +163,39 @@ def test_forge_engine(tmp_path):
     eng.close()
 
 
+def test_forge_example_trainer_matches_the_trainer_and_resumes(tmp_path):
+    """The loop written on the engine's verbs (gradient accumulation over two microbatches) gives the Trainer's losses,
+    and a second run resumes from the checkpoint the first one wrote."""
+    from torchtitan_b200.config import ConfigManager
+    from torchtitan_b200.experiments.forge.example_train import main
+
+    def args(folder, steps, ckpt):
+        return ["--module", "llama3", "--config", "llama3_debugmodel", "--training.steps", str(steps),
+                "--training.num_tokens_per_microbatch_per_dp_rank", "64", "--training.max_context_length", "64",
+                "--training.num_tokens_per_train_step", "128", "--training.mixed_precision_param", "float32",
+                "--debug.seed", "0", "--dump_folder", str(folder), "--debug.no-enable_structured_logging",
+                "--metrics.log_freq", "1"] + (["--checkpoint.enable", "--checkpoint.interval", "2"] if ckpt else
+                                             ["--checkpoint.no-enable"])
+
+    got = main(args(tmp_path / "a", 4, False))
+    t = ConfigManager().parse_args(args(tmp_path / "b", 4, False)).build()
+    want = []
+    orig = t.metrics_processor.log
+
+    def log(step, avg, mx, gn, extra_metrics=None):
+        want.append(avg)
+        return orig(step, avg, mx, gn, extra_metrics=extra_metrics)
+
+    t.metrics_processor.log = log
+    t.train()
+    t.close()
+    assert torch.allclose(torch.tensor(got), torch.tensor(want), atol=1e-5), (got, want)
+    first = main(args(tmp_path / "c", 2, True))
+    rest = main(args(tmp_path / "c", 4, True))          # resumes at step 2
+    assert len(first) == 2 and len(rest) == 2
+    assert torch.allclose(torch.tensor(first + rest), torch.tensor(got), atol=1e-5), (first, rest, got)
+
+
 # ---------------------------------------------------------------------------------------------
 def _replica(rid, n, port, die_at, out):
     """A replica trains a least-squares model; replica ``n - 1`` stops between steps at ``die_at``."""
