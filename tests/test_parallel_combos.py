@@ -158,3 +158,17 @@ def test_tensor_parallel_without_sequence_parallel_matches_single_rank(tmp_path)
                     b, 128, timeout=400)
     ra, rb = torch.load(a), torch.load(b)
     assert torch.allclose(ra, rb, atol=2e-4), (ra, rb)
+
+
+def test_async_tensor_parallel_flag_selects_the_fused_gemms():
+    """``compile.enable_async_tensor_parallel`` (the reference's switch) maps to the GEMM kernels with the collective
+    inside; without sequence parallelism it is refused."""
+    from torchtitan_b200.config import ConfigManager
+
+    base = ["--module", "llama3", "--config", "llama3_debugmodel", "--parallelism.tensor_parallel_degree", "2",
+            "--compile.enable_async_tensor_parallel"]
+    cfg = ConfigManager().parse_args(base)
+    cfg.validate()
+    assert cfg.parallelism.tp_comm == "nvlink"
+    with pytest.raises(ValueError, match="sequence parallelism"):
+        ConfigManager().parse_args(base + ["--parallelism.no-enable_sequence_parallel"]).validate()

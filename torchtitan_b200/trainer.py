@@ -105,6 +105,14 @@ class Trainer(Configurable):
             if self.compile.enable:
                 logger.warning("compile.enable is accepted for compatibility; this framework runs hand-written "
                                "kernels and CUDA graphs instead of a tracing compiler")
+            if self.compile.enable_async_tensor_parallel and p.tensor_parallel_degree > 1 and p.tp_comm == "nccl":
+                # the reference's async TP overlaps the all-gather / reduce-scatter with the GEMM through the compiler
+                # (distributed/tensor_parallel.py:19-95); here it selects the GEMM kernels with the collective inside
+                if not p.enable_sequence_parallel:
+                    raise ValueError("async tensor parallelism needs sequence parallelism")
+                p.tp_comm = "nvlink"
+                logger.info("compile.enable_async_tensor_parallel: tensor-parallel collectives run inside the GEMM "
+                            "kernels (parallelism.tp_comm = nvlink)")
             if not t.disable_cuda_graphs and p.pipeline_parallel_degree > 1:
                 raise ValueError("CUDA graphs cannot be combined with pipeline parallelism")
             if self.checkpoint is not None and self.checkpoint.enable and self.checkpoint.keep_latest_k == 1:
