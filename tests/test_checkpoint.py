@@ -122,3 +122,15 @@ def test_adapter_qk_permutation_round_trip():
     # pairs (0,1),(2,3).. -> halves: first half holds even rows
     one = torch.arange(8.0)[:, None]
     assert pairs_to_halves(one, 1).flatten().tolist() == [0, 2, 4, 6, 1, 3, 5, 7]
+
+
+@pytest.mark.parametrize("module,flavor", [("llama3", "debugmodel_gqa"), ("qwen3", "debugmodel")])
+def test_logits_match_transformers_on_converted_weights(module, flavor):
+    """A freshly initialised Hugging Face model and the native model that received its weights through the family's
+    state-dict adapter give the same next-token distributions (RoPE convention and scaling, fused q/k/v and gate/up
+    splits, grouped queries, q/k norms, tied embeddings): mean KL below 1e-6."""
+    pytest.importorskip("transformers")
+    from torchtitan_b200.scripts.numerical_tests import main
+
+    res = main(["--module", module, "--flavor", flavor, "--random", "--seq-len", "48", "--num-seqs", "2"])
+    assert abs(res["kl_mean"]) < 1e-6 and res["max_abs_logit_diff"] < 1e-4, res

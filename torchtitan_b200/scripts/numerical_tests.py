@@ -1,0 +1,111 @@
+"""Numerical parity between a Hugging Face ``transformers`` model and this framework's model on the same weights.
+
+    python -m torchtitan_b200.scripts.numerical_tests --module llama3 --flavor 8B --hf-dir ./assets/hf/Llama-3.1-8B
+    python -m torchtitan_b200.scripts.numerical_tests --module qwen3 --flavor debugmodel --random
+
+The HF weights (a safetensors directory, or with ``--random`` a freshly initialised ``transformers`` model built from
+the flavor's architecture) go through the family's state-dict adapter into the native model; both models then score
+the same random token sequences and the script reports the mean KL divergence between their next-token
+distributions and the largest logit difference.  Parity: scripts/checkpoint_conversion/numerical_tests_example.py
+(same measure: KL divergence of the two logit sets).
+"""
+
+from __future__ import annotations
+
+import argparse
+
+import torch
+
+from torchtitan_b200.models import get_model_spec
+
+__all__ = ["hf_config_for", "load_native_from_hf_state", "compare_logits", "main"]
+
+
+def hf_config_for(module: str, cfg):
+    """A ``transformers`` config describing the same architecture as the native decoder config ``cfg``."""
+    import transformers
+
+    blk = cfg.layers[0]
+    att = blk.attention
+    rope = att.rope
+    common = dict(vocab_size=cfg.vocab_size, hidden_size=cfg.dim, num_hidden_layers=len(cfg.layers),
+                  num_attention_heads=att.n_heads, num_key_value_heads=att.n_kv_heads or att.n_heads,
+                  rms_norm_eps=blk.attention_norm.eps, rope_theta=rope.theta, tie_word_embeddings=cfg.enable_weight_tying,
+                  max_position_embeddings=min(cfg.max_context_length, 131072), attention_bias=False)
+    inter = blk.feed_forward.hidden_dim if blk.feed_forward is not None else 0
+    if module == "llama3":
+        scaling = None
+        if rope.scaling == "llama":
+            scaling = dict(rope_type="llama3", factor=rope.scaling_factor, low_freq_factor=rope.low_freq_factor,
+                           high_freq_factor=rope.high_freq_factor,
+                           original_max_position_embeddings=getattr(rope, "original_max_context_length", 8192))
+        return transformers.LlamaConfig(intermediate_size=inter, rope_scaling=scaling, head_dim=att.head_dim, **common)
+    if module == "qwen3":
+        if blk.moe is not None:
+            raise ValueError("the random Hugging Face stand-in covers dense Qwen3 flavors")
+        return transformers.Qwen3Config(intermediate_size=inter, head_dim=att.head_dim, **common)
+    raise ValueError(f"no Hugging Face config mapping for module '{module}'")
+
+
+def load_native_from_hf_state(spec, hf_state: dict[str, torch.Tensor], hf_dir: str | None = None):
+    """The native model (fp32, CPU) with the weights of ``hf_state`` (Hugging Face names)."""
+    from torchtitan_b200.models.common.module import iter_checkpoint_slices
+
+    adapter = spec.state_dict_adapter(spec.model, hf_dir)
+    native = adapter.from_hf(dict(hf_state))
+    model = spec.model.build()
+    fused = dict(iter_checkpoint_slices(model))
+    with torch.no_grad():
+        for k, p in model.named_parameters():
+            if k in fused:
+                for name, a, b in fused[k]:
+                    p[a:b].copy_(native[name].float())
+            else:
+                p.copy_(native[k].float())
+    model.init_buffers() if hasattr(model, "init_buffers") else None
+    return model.float().eval()
+
+
+@torch.no_grad()
+def compare_logits(native, hf_model, tokens: torch.Tensor) -> dict:
+    """``tokens [B, T]``: mean KL(hf || native) over positions and the largest absolute logit difference."""
+    kls, worst = [], 0.0
+    for row in tokens:
+        ours = native(row, torch.arange(row.shape[0])).float()
+        theirs = hf_model(input_ids=row[None]).logits[0].float()
+        lp, lq = torch.log_softmax(theirs, -1), torch.log_softmax(ours, -1)
+        kls.append(float((lp.exp() * (lp - lq)).sum(-1).mean()))
+        worst = max(worst, float((ours - theirs).abs().max()))
+    return {"kl_mean": sum(kls) / len(kls), "max_abs_logit_diff": worst}
+
+
+def main(argv=None) -> dict:
+    import transformers
+
+    ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    ap.add_argument("--module", required=True)
+    ap.add_argument("--flavor", required=True)
+    ap.add_argument("--hf-dir", default=None)
+    ap.add_argument("--random", action="store_true", help="compare on a freshly initialised transformers model")
+    ap.add_argument("--seq-len", type=int, default=64)
+    ap.add_argument("--num-seqs", type=int, default=4)
+    ap.add_argument("--seed", type=int, default=0)
+    args = ap.parse_args(argv)
+    if bool(args.hf_dir) == bool(args.random):
+        raise SystemExit("give exactly one of --hf-dir and --random")
+    spec = get_model_spec(args.module, args.flavor)
+    torch.manual_seed(args.seed)
+    if args.random:
+        hf_model = transformers.AutoModelForCausalLM.from_config(hf_config_for(args.module, spec.model)).float().eval()
+    else:
+        hf_model = transformers.AutoModelForCausalLM.from_pretrained(args.hf_dir, torch_dtype=torch.float32).eval()
+    native = load_native_from_hf_state(spec, hf_model.state_dict(), args.hf_dir)
+    g = torch.Generator().manual_seed(args.seed)
+    tokens = torch.randint(0, spec.model.vocab_size, (args.num_seqs, args.seq_len), generator=g)
+    res = compare_logits(native, hf_model, tokens)
+    print(f"{args.module} {args.flavor}: mean KL {res['kl_mean']:.3e}, largest logit difference {res['max_abs_logit_diff']:.3e}")
+    return res
+
+
+if __name__ == "__main__":
+    main()
