@@ -124,13 +124,17 @@ def test_adapter_qk_permutation_round_trip():
     assert pairs_to_halves(one, 1).flatten().tolist() == [0, 2, 4, 6, 1, 3, 5, 7]
 
 
-@pytest.mark.parametrize("module,flavor", [("llama3", "debugmodel_gqa"), ("qwen3", "debugmodel")])
-def test_logits_match_transformers_on_converted_weights(module, flavor):
+@pytest.mark.parametrize("module,flavor,seq", [
+    ("llama3", "debugmodel_gqa", 48), ("qwen3", "debugmodel", 48), ("qwen3", "debugmodel_moe_tiny", 48),
+    ("deepseek_v3", "debugmodel_v3routing", 48), ("gpt_oss", "debugmodel", 96)])
+def test_logits_match_transformers_on_converted_weights(module, flavor, seq):
     """A freshly initialised Hugging Face model and the native model that received its weights through the family's
-    state-dict adapter give the same next-token distributions (RoPE convention and scaling, fused q/k/v and gate/up
-    splits, grouped queries, q/k norms, tied embeddings): mean KL below 1e-6."""
+    state-dict adapter give the same next-token distributions: mean KL below 1e-6.  Covers the RoPE conventions and
+    their Llama / YaRN scalings, fused q/k/v and gate/up splits, grouped queries, q/k norms, tied embeddings, top-k
+    routers (softmax, and sigmoid with groups, bias and scaling), shared experts, multi-head latent attention, and
+    GPT-OSS's sinks, alternating sliding window (sequence longer than the window), biases and clamped SwiGLU."""
     pytest.importorskip("transformers")
     from torchtitan_b200.scripts.numerical_tests import main
 
-    res = main(["--module", module, "--flavor", flavor, "--random", "--seq-len", "48", "--num-seqs", "2"])
+    res = main(["--module", module, "--flavor", flavor, "--random", "--seq-len", str(seq), "--num-seqs", "2"])
     assert abs(res["kl_mean"]) < 1e-6 and res["max_abs_logit_diff"] < 1e-4, res

@@ -73,6 +73,12 @@ deepseek_v3_configs = {
     "debugmodel": lambda: build_deepseek_v3_config(
         vocab_size=2048, dim=256, inter_dim=1024, moe_inter_dim=256, n_layers=6, n_dense_layers=1, n_heads=16,
         n_routed_experts=8, n_shared_experts=2, n_activated_experts=3, route_scale=1.0),
+    # the routing of the released V3 models at toy size: sigmoid scores, normalised top-k inside two of four groups
+    "debugmodel_v3routing": lambda: build_deepseek_v3_config(
+        vocab_size=2048, dim=128, inter_dim=256, moe_inter_dim=64, n_layers=3, n_dense_layers=1, n_heads=4,
+        n_routed_experts=8, n_shared_experts=1, n_activated_experts=2, n_expert_groups=4, n_limited_groups=2,
+        score_func="sigmoid", route_norm=True, route_scale=2.5, kv_lora_rank=64, qk_nope_head_dim=32,
+        qk_rope_head_dim=16, v_head_dim=32, q_lora_rank=48, max_context_length=8192),
     "debugmodel_mtp": lambda: build_deepseek_v3_config(
         vocab_size=2048, dim=256, inter_dim=1024, moe_inter_dim=256, n_layers=3, n_dense_layers=1, n_heads=16,
         n_routed_experts=8, n_shared_experts=2, n_activated_experts=3, route_scale=1.0, n_mtp_layers=2),

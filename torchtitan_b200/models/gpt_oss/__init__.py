@@ -23,10 +23,16 @@ def build_gpt_oss_config(*, dim, n_layers, n_heads=64, n_kv_heads=8, head_dim=64
                          top_k=4, vocab_size=201088, sliding_window=128, rope_theta=150000.0, rope_factor=32.0,
                          original_seq_len=4096, max_context_length=4096) -> Decoder.Config:
     out_std = 0.02 / (2 * n_layers) ** 0.5
+    # YaRN's attention magnitude correction m = 0.1 ln(factor) + 1 scales q and k alike: it is folded into the softmax
+    # scale as m^2, the rotary table stays a pure rotation (parity: torchtitan/models/gpt_oss/model.py:74-78)
+    import math
+
+    mscale = 0.1 * math.log(rope_factor) + 1.0 if rope_factor > 1.0 else 1.0
+    softmax_scale = head_dim ** -0.5 * mscale * mscale
     layers = []
     for i in range(n_layers):
         attn = GQAttention.Config(
-            dim=dim, n_heads=n_heads, n_kv_heads=n_kv_heads, head_dim=head_dim,
+            dim=dim, n_heads=n_heads, n_kv_heads=n_kv_heads, head_dim=head_dim, softmax_scale=softmax_scale,
             wqkv=Linear.Config(init_std=0.02, bias=True), wo=Linear.Config(init_std=out_std, bias=True),
             rope=RoPE.Config(dim=head_dim, theta=rope_theta, style="cos_sin", scaling="yarn", rope_factor=rope_factor,
                              beta_fast=32.0, beta_slow=1.0, original_seq_len=original_seq_len, truncate=False,

@@ -18,7 +18,7 @@ import torch
 
 from torchtitan_b200.models import get_model_spec
 
-__all__ = ["hf_config_for", "load_native_from_hf_state", "compare_logits", "main"]
+__all__ = ["hf_config_for", "checkpoint_state", "load_native_from_hf_state", "compare_logits", "main"]
 
 
 def hf_config_for(module: str, cfg):
@@ -29,7 +29,7 @@ def hf_config_for(module: str, cfg):
     att = blk.attention
     rope = att.rope
     common = dict(vocab_size=cfg.vocab_size, hidden_size=cfg.dim, num_hidden_layers=len(cfg.layers),
-                  num_attention_heads=att.n_heads, num_key_value_heads=att.n_kv_heads or att.n_heads,
+                  num_attention_heads=att.n_heads, num_key_value_heads=getattr(att, "n_kv_heads", None) or att.n_heads,
                   rms_norm_eps=blk.attention_norm.eps, rope_theta=rope.theta, tie_word_embeddings=cfg.enable_weight_tying,
                   max_position_embeddings=min(cfg.max_context_length, 131072), attention_bias=False)
     inter = blk.feed_forward.hidden_dim if blk.feed_forward is not None else 0
@@ -42,9 +42,59 @@ def hf_config_for(module: str, cfg):
         return transformers.LlamaConfig(intermediate_size=inter, rope_scaling=scaling, head_dim=att.head_dim, **common)
     if module == "qwen3":
         if blk.moe is not None:
-            raise ValueError("the random Hugging Face stand-in covers dense Qwen3 flavors")
+            return transformers.Qwen3MoeConfig(
+                intermediate_size=blk.moe.hidden_dim, moe_intermediate_size=blk.moe.hidden_dim, head_dim=att.head_dim,
+                num_experts=blk.moe.num_experts, num_experts_per_tok=blk.moe.top_k, norm_topk_prob=blk.moe.router.route_norm,
+                decoder_sparse_step=1, mlp_only_layers=[], **common)
         return transformers.Qwen3Config(intermediate_size=inter, head_dim=att.head_dim, **common)
+    if module == "gpt_oss":
+        common.pop("attention_bias")
+        yarn = dict(rope_type="yarn", factor=rope.rope_factor, original_max_position_embeddings=rope.original_seq_len,
+                    beta_fast=rope.beta_fast, beta_slow=rope.beta_slow, truncate=False)
+        window = next(b.attention.sliding_window for b in cfg.layers if b.attention.sliding_window)
+        return transformers.GptOssConfig(
+            intermediate_size=blk.moe.hidden_dim, head_dim=att.head_dim, num_local_experts=blk.moe.num_experts,
+            num_experts_per_tok=blk.moe.top_k, sliding_window=window, rope_scaling=yarn, attention_bias=True,
+            layer_types=["sliding_attention" if b.attention.sliding_window else "full_attention" for b in cfg.layers],
+            **common)
+    if module == "deepseek_v3":
+        moe_blk = next(b for b in cfg.layers if b.moe is not None)
+        moe, router = moe_blk.moe, moe_blk.moe.router
+        if router.score_func != "sigmoid":
+            raise ValueError("the Hugging Face DeepSeek-V3 model routes with sigmoid scores: use a flavor that does")
+        n_dense = sum(1 for b in cfg.layers if b.moe is None)
+        yarn = dict(rope_type="yarn", factor=rope.rope_factor, original_max_position_embeddings=rope.original_seq_len,
+                    beta_fast=rope.beta_fast, beta_slow=rope.beta_slow, mscale=att.mscale, mscale_all_dim=att.mscale)
+        return transformers.DeepseekV3Config(
+            vocab_size=cfg.vocab_size, hidden_size=cfg.dim, num_hidden_layers=len(cfg.layers),
+            intermediate_size=next(b for b in cfg.layers if b.moe is None).feed_forward.hidden_dim,
+            moe_intermediate_size=moe.hidden_dim, num_attention_heads=att.n_heads, num_key_value_heads=att.n_heads,
+            n_shared_experts=moe.shared_hidden_dim // moe.hidden_dim, n_routed_experts=moe.num_experts,
+            routed_scaling_factor=router.route_scale, kv_lora_rank=att.kv_lora_rank, q_lora_rank=att.q_lora_rank or None,
+            qk_rope_head_dim=att.qk_rope_head_dim, v_head_dim=att.v_head_dim, qk_nope_head_dim=att.qk_nope_head_dim,
+            n_group=router.num_expert_groups or 1, topk_group=router.num_limited_groups or 1,
+            num_experts_per_tok=moe.top_k, first_k_dense_replace=n_dense, norm_topk_prob=router.route_norm,
+            rms_norm_eps=blk.attention_norm.eps, rope_theta=rope.theta, rope_scaling=yarn,
+            max_position_embeddings=cfg.max_context_length, tie_word_embeddings=False, attention_bias=False)
     raise ValueError(f"no Hugging Face config mapping for module '{module}'")
+
+
+def checkpoint_state(hf_model) -> dict[str, torch.Tensor]:
+    """The tensors of ``hf_model`` under their checkpoint names (``save_pretrained`` undoes the in-memory fusion of
+    expert weights that recent ``transformers`` releases apply on load)."""
+    import os
+    import tempfile
+
+    from safetensors import safe_open
+
+    out = {}
+    with tempfile.TemporaryDirectory() as d:
+        hf_model.save_pretrained(d, safe_serialization=True)
+        for fn in sorted(f for f in os.listdir(d) if f.endswith(".safetensors")):
+            with safe_open(os.path.join(d, fn), framework="pt", device="cpu") as f:
+                for k in f.keys():
+                    out[k] = f.get_tensor(k)
+    return out
 
 
 def load_native_from_hf_state(spec, hf_state: dict[str, torch.Tensor], hf_dir: str | None = None):
@@ -99,7 +149,7 @@ def main(argv=None) -> dict:
         hf_model = transformers.AutoModelForCausalLM.from_config(hf_config_for(args.module, spec.model)).float().eval()
     else:
         hf_model = transformers.AutoModelForCausalLM.from_pretrained(args.hf_dir, torch_dtype=torch.float32).eval()
-    native = load_native_from_hf_state(spec, hf_model.state_dict(), args.hf_dir)
+    native = load_native_from_hf_state(spec, checkpoint_state(hf_model), args.hf_dir)
     g = torch.Generator().manual_seed(args.seed)
     tokens = torch.randint(0, spec.model.vocab_size, (args.num_seqs, args.seq_len), generator=g)
     res = compare_logits(native, hf_model, tokens)
