@@ -126,15 +126,50 @@ def test_adapter_qk_permutation_round_trip():
 
 @pytest.mark.parametrize("module,flavor,seq", [
     ("llama3", "debugmodel_gqa", 48), ("qwen3", "debugmodel", 48), ("qwen3", "debugmodel_moe_tiny", 48),
-    ("deepseek_v3", "debugmodel_v3routing", 48), ("gpt_oss", "debugmodel", 96)])
+    ("deepseek_v3", "debugmodel_v3routing", 48), ("gpt_oss", "debugmodel", 96), ("qwen3_5", "debugmodel", 100),
+    ("qwen3_5", "debugmodel_moe", 80)])
 def test_logits_match_transformers_on_converted_weights(module, flavor, seq):
     """A freshly initialised Hugging Face model and the native model that received its weights through the family's
     state-dict adapter give the same next-token distributions: mean KL below 1e-6.  Covers the RoPE conventions and
     their Llama / YaRN scalings, fused q/k/v and gate/up splits, grouped queries, q/k norms, tied embeddings, top-k
     routers (softmax, and sigmoid with groups, bias and scaling), shared experts, multi-head latent attention, and
-    GPT-OSS's sinks, alternating sliding window (sequence longer than the window), biases and clamped SwiGLU."""
+    GPT-OSS's sinks, alternating sliding window (sequence longer than the window), biases and clamped SwiGLU, and
+    Qwen3.5's Gated DeltaNet layers (fused projections and convolution, chunked delta rule across chunk boundaries,
+    gated norm), gated partial-rotary attention, offset-gain norms and gated shared expert.  Norm gains, biases and
+    the other 1-D parameters are perturbed so that they matter."""
     pytest.importorskip("transformers")
     from torchtitan_b200.scripts.numerical_tests import main
 
-    res = main(["--module", module, "--flavor", flavor, "--random", "--seq-len", str(seq), "--num-seqs", "2"])
+    res = main(["--module", module, "--flavor", flavor, "--random", "--perturb", "0.1", "--seq-len", str(seq),
+                "--num-seqs", "2"])
     assert abs(res["kl_mean"]) < 1e-6 and res["max_abs_logit_diff"] < 1e-4, res
+
+
+def test_qwen3_5_adapter_round_trip():
+    """Native -> Hugging Face -> native is the identity for the Qwen3.5 layouts (fused DeltaNet projections and
+    convolution, query / gate interleaving, fused expert tensors), with either decoder prefix."""
+    from torchtitan_b200.models import get_model_spec
+    from torchtitan_b200.models.common.module import iter_checkpoint_slices
+
+    for flavor in ("debugmodel", "debugmodel_moe"):
+        spec = get_model_spec("qwen3_5", flavor)
+        model = spec.model.build()
+        model.init_states(seed=3)
+        fused = dict(iter_checkpoint_slices(model))
+        native = {}
+        for k, p in model.named_parameters():
+            if k in fused:
+                for name, a, b in fused[k]:
+                    native[name] = p.detach()[a:b].clone()
+            else:
+                native[k] = p.detach().clone()
+        ad = spec.state_dict_adapter(spec.model, None)
+        for prefix in ("model.language_model.", "model."):
+            ad.hf_prefix = prefix
+            hf = ad.to_hf(dict(native))
+            assert all(k.startswith(prefix) or k == "lm_head.weight" for k in hf), list(hf)[:3]
+            assert any(k.endswith("linear_attn.in_proj_qkv.weight") for k in hf)
+            back = ad.from_hf(hf)
+            assert set(back) == set(native), set(back) ^ set(native)
+            for k in native:
+                assert torch.equal(back[k], native[k]), k

@@ -180,7 +180,7 @@ class GQAttention(Module):
             else:
                 x = tp_ops.all_gather_rows(x, tp) if tp.sequence_parallel else tp_ops.copy_to_tp(x, tp)
                 qkv = self.wqkv(x)
-        elif norm is not None and type(self.wqkv) is Linear and norm.weight is not None and self.wqkv.bias is None:
+        elif type(norm) is RMSNorm and type(self.wqkv) is Linear and norm.weight is not None and self.wqkv.bias is None:
             qkv = OF.norm_linear(x, norm.weight, self.wqkv.weight, norm.eps)
         else:
             qkv = self.wqkv(norm(x) if norm is not None else x)

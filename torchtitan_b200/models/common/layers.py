@@ -311,7 +311,8 @@ class FeedForward(Module):
             gu = self.w13(x)
             y = OF.swiglu_linear(gu, self.w2.weight)
             return tp_ops.reduce_scatter_rows(y, tp) if tp.sequence_parallel else tp_ops.all_reduce(y, tp)
-        if norm is not None and type(self.w13) is Linear and norm.weight is not None:
+        # the fused norm + GEMM takes a plain RMSNorm; norm subclasses (offset gains ...) run as their own module
+        if type(norm) is RMSNorm and type(self.w13) is Linear and norm.weight is not None:
             gu = OF.norm_linear(x, norm.weight, self.w13.weight, norm.eps)
         else:
             gu = self.w13(norm(x) if norm is not None else x)

@@ -260,6 +260,8 @@ class MoE(Module):
         load_balance_coeff: float | None = 1e-3
         shared_hidden_dim: int = 0
         shared_experts: FeedForward.Config | None = None
+        shared_expert_gate: bool = False
+        """Scale the shared experts' output by ``sigmoid(x w_gate)`` per token (Qwen3.5 MoE)."""
 
     def __init__(self, config: "MoE.Config", **_):
         super().__init__(config)
@@ -274,6 +276,10 @@ class MoE(Module):
             sc = c.shared_experts or FeedForward.Config()
             sc.dim, sc.hidden_dim = c.dim, c.shared_hidden_dim
             self.shared_experts = sc.build()
+        self.shared_gate = None
+        if c.shared_expert_gate and self.shared_experts is not None:
+            self.shared_gate = Linear(Linear.Config(in_features=c.dim, out_features=1, init_std=0.02))
+            self.shared_gate.weight._replicated_over_tp = True
         self.load_balance_coeff = c.load_balance_coeff
         self.num_experts = c.num_experts
         if c.load_balance_coeff:
@@ -333,7 +339,10 @@ class MoE(Module):
         out = self.routed_experts(x, top, sel, counts)
         if self.shared_experts is not None:
             se = self.shared_experts
-            out = out + OF.swiglu_linear(se.w13(x), se.w2.weight)
+            shared = OF.swiglu_linear(se.w13(x), se.w2.weight)
+            if self.shared_gate is not None:
+                shared = shared * torch.sigmoid(self.shared_gate(x).float()).to(shared.dtype)
+            out = out + shared
         if gather:
             return shd.redistribute(out, plan.out_src_shardings.on("tp"), plan.out_dst_shardings.on("tp"), tp)
         return out

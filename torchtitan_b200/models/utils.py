@@ -49,6 +49,8 @@ def count_params_and_flops(cfg, model: nn.Module | None, seq_len: int) -> tuple[
             if getattr(m.router, "gate_bias", False):
                 router += m.num_experts
             shared = 3 * dim * m.shared_hidden_dim if m.shared_hidden_dim else 0
+            if shared and getattr(m, "shared_expert_gate", False):
+                shared += dim                     # the sigmoid gate of the shared experts
             layer += m.num_experts * per_expert + router + shared
             layer_active += m.top_k * per_expert + router + shared
         total += layer

@@ -25,6 +25,24 @@ def hf_config_for(module: str, cfg):
     """A ``transformers`` config describing the same architecture as the native decoder config ``cfg``."""
     import transformers
 
+    if module == "qwen3_5":
+        full = next(b for b in cfg.layers if hasattr(b.attention, "rope"))
+        lin = next(b for b in cfg.layers if not hasattr(b.attention, "rope"))
+        fa, la = full.attention, lin.attention
+        kw = dict(vocab_size=cfg.vocab_size, hidden_size=cfg.dim, num_hidden_layers=len(cfg.layers),
+                  num_attention_heads=fa.n_heads, num_key_value_heads=fa.n_kv_heads, head_dim=fa.head_dim,
+                  linear_conv_kernel_dim=la.conv_kernel_size, linear_key_head_dim=la.key_head_dim,
+                  linear_value_head_dim=la.value_head_dim, linear_num_key_heads=la.n_key_heads,
+                  linear_num_value_heads=la.n_value_heads, rms_norm_eps=full.attention_norm.eps,
+                  layer_types=["full_attention" if hasattr(b.attention, "rope") else "linear_attention" for b in cfg.layers],
+                  rope_parameters=dict(rope_type="default", rope_theta=fa.rope.theta,
+                                       partial_rotary_factor=fa.rope.dim / fa.head_dim),
+                  max_position_embeddings=cfg.max_context_length, tie_word_embeddings=cfg.enable_weight_tying)
+        if full.moe is not None:
+            return transformers.Qwen3_5MoeTextConfig(
+                moe_intermediate_size=full.moe.hidden_dim, shared_expert_intermediate_size=full.moe.shared_hidden_dim,
+                num_experts=full.moe.num_experts, num_experts_per_tok=full.moe.top_k, **kw)
+        return transformers.Qwen3_5TextConfig(intermediate_size=full.feed_forward.hidden_dim, **kw)
     blk = cfg.layers[0]
     att = blk.attention
     rope = att.rope
@@ -137,6 +155,9 @@ def main(argv=None) -> dict:
     ap.add_argument("--flavor", required=True)
     ap.add_argument("--hf-dir", default=None)
     ap.add_argument("--random", action="store_true", help="compare on a freshly initialised transformers model")
+    ap.add_argument("--perturb", type=float, default=0.0,
+                    help="with --random: noise added to every 1-D parameter (norm gains, biases, sinks, decay terms), "
+                         "which a fresh initialisation leaves at 0 or 1")
     ap.add_argument("--seq-len", type=int, default=64)
     ap.add_argument("--num-seqs", type=int, default=4)
     ap.add_argument("--seed", type=int, default=0)
@@ -147,6 +168,11 @@ def main(argv=None) -> dict:
     torch.manual_seed(args.seed)
     if args.random:
         hf_model = transformers.AutoModelForCausalLM.from_config(hf_config_for(args.module, spec.model)).float().eval()
+        if args.perturb:
+            with torch.no_grad():
+                for p in hf_model.parameters():
+                    if p.dim() == 1:
+                        p.add_(torch.randn_like(p) * args.perturb)
     else:
         hf_model = transformers.AutoModelForCausalLM.from_pretrained(args.hf_dir, torch_dtype=torch.float32).eval()
     native = load_native_from_hf_state(spec, checkpoint_state(hf_model), args.hf_dir)
