@@ -141,8 +141,10 @@ def test_logits_match_transformers_on_converted_weights(module, flavor, seq):
     from torchtitan_b200.scripts.numerical_tests import main
 
     res = main(["--module", module, "--flavor", flavor, "--random", "--perturb", "0.1", "--seq-len", str(seq),
-                "--num-seqs", "2"])
+                "--num-seqs", "2", "--grads"])
     assert abs(res["kl_mean"]) < 1e-6 and res["max_abs_logit_diff"] < 1e-4, res
+    # the backward of the native operators against transformers' autograd, parameter by parameter
+    assert res["grad_tensors_compared"] >= 20 and res["max_rel_grad_diff"] < 2e-3, res
 
 
 def test_qwen3_5_adapter_round_trip():

@@ -18,7 +18,7 @@ import torch
 
 from torchtitan_b200.models import get_model_spec
 
-__all__ = ["hf_config_for", "checkpoint_state", "load_native_from_hf_state", "compare_logits", "main"]
+__all__ = ["hf_config_for", "checkpoint_state", "load_native_from_hf_state", "compare_logits", "compare_grads", "main"]
 
 
 def hf_config_for(module: str, cfg):
@@ -147,6 +147,43 @@ def compare_logits(native, hf_model, tokens: torch.Tensor) -> dict:
     return {"kl_mean": sum(kls) / len(kls), "max_abs_logit_diff": worst}
 
 
+def compare_grads(spec, native, hf_model, tokens: torch.Tensor) -> dict:
+    """Gradients of the summed next-token cross entropy on ``tokens [B, T]``: the native gradients, renamed and
+    re-laid-out by the state-dict adapter, against ``transformers`` autograd.  Compares the parameters whose Hugging
+    Face checkpoint name is also an in-memory parameter name (fused expert tensors of recent releases are skipped)."""
+    from torchtitan_b200.models.common.module import iter_checkpoint_slices
+
+    for m in (native, hf_model):
+        m.zero_grad(set_to_none=True)
+        m.train(False)
+    for row in tokens:
+        inp, lab = row[:-1], row[1:]
+        torch.nn.functional.cross_entropy(native(inp, torch.arange(inp.shape[0])).float(), lab, reduction="sum").backward()
+        torch.nn.functional.cross_entropy(hf_model(input_ids=inp[None]).logits[0].float(), lab, reduction="sum").backward()
+    fused = dict(iter_checkpoint_slices(native))
+    grads = {}
+    for k, p in native.named_parameters():
+        if p.grad is None:
+            continue
+        if k in fused:
+            for name, a, b in fused[k]:
+                grads[name] = p.grad[a:b]
+        else:
+            grads[k] = p.grad
+    adapter = spec.state_dict_adapter(spec.model, None)
+    if hasattr(adapter, "hf_prefix"):
+        adapter.hf_prefix = "model."
+    as_hf = adapter.to_hf(grads)
+    theirs = {k: p.grad for k, p in hf_model.named_parameters() if p.grad is not None}
+    worst, n = 0.0, 0
+    for k, g in as_hf.items():
+        if k in theirs and theirs[k].shape == g.shape:
+            denom = float(theirs[k].abs().max()) + 1e-12
+            worst = max(worst, float((g - theirs[k]).abs().max()) / denom)
+            n += 1
+    return {"grad_tensors_compared": n, "max_rel_grad_diff": worst}
+
+
 def main(argv=None) -> dict:
     import transformers
 
@@ -158,6 +195,7 @@ def main(argv=None) -> dict:
     ap.add_argument("--perturb", type=float, default=0.0,
                     help="with --random: noise added to every 1-D parameter (norm gains, biases, sinks, decay terms), "
                          "which a fresh initialisation leaves at 0 or 1")
+    ap.add_argument("--grads", action="store_true", help="also compare the gradients of a cross-entropy loss")
     ap.add_argument("--seq-len", type=int, default=64)
     ap.add_argument("--num-seqs", type=int, default=4)
     ap.add_argument("--seed", type=int, default=0)
@@ -180,6 +218,9 @@ def main(argv=None) -> dict:
     tokens = torch.randint(0, spec.model.vocab_size, (args.num_seqs, args.seq_len), generator=g)
     res = compare_logits(native, hf_model, tokens)
     print(f"{args.module} {args.flavor}: mean KL {res['kl_mean']:.3e}, largest logit difference {res['max_abs_logit_diff']:.3e}")
+    if args.grads:
+        res.update(compare_grads(spec, native, hf_model, tokens))
+        print(f"gradients: {res['grad_tensors_compared']} tensors, largest relative difference {res['max_rel_grad_diff']:.3e}")
     return res
 
 
