@@ -142,6 +142,27 @@ def test_hf_backend_trains():
     assert losses[-1] < losses[0]
 
 
+@pytest.mark.parametrize("module,flavor", [("llama3", "debugmodel_gqa"), ("gpt_oss", "debugmodel")])
+def test_cached_generation_matches_transformers_greedy(module, flavor):
+    """Greedy decoding with the key / value cache (and, for GPT-OSS, a context longer than the sliding window, with
+    sinks) produces the tokens ``transformers.generate`` produces on the same weights, as does the cache-free sampler."""
+    transformers = pytest.importorskip("transformers")
+    from torchtitan_b200.experiments.rl.generator import CachedGenerator, SamplingGenerator
+    from torchtitan_b200.models import get_model_spec
+    from torchtitan_b200.scripts.numerical_tests import checkpoint_state, hf_config_for, load_native_from_hf_state
+
+    spec = get_model_spec(module, flavor)
+    torch.manual_seed(0)
+    hf = transformers.AutoModelForCausalLM.from_config(hf_config_for(module, spec.model)).float().eval()
+    native = load_native_from_hf_state(spec, checkpoint_state(hf))
+    prompt = torch.randint(0, 2048, (20,))
+    with torch.no_grad():
+        want = hf.generate(prompt[None], do_sample=False, max_new_tokens=70, pad_token_id=0)[0, 20:]
+    for cls in (CachedGenerator, SamplingGenerator):
+        got = cls(native, temperature=0.0).generate(prompt, 70).response
+        assert torch.equal(got, want), (cls.__name__, int((got != want).sum()))
+
+
 def test_forge_engine(tmp_path):
     from torchtitan_b200.config import ConfigManager
     from torchtitan_b200.experiments.forge import ForgeEngine
