@@ -157,9 +157,9 @@ def test_cached_generation_matches_transformers_greedy(module, flavor):
     native = load_native_from_hf_state(spec, checkpoint_state(hf))
     prompt = torch.randint(0, 2048, (20,))
     with torch.no_grad():
-        want = hf.generate(prompt[None], do_sample=False, max_new_tokens=70, pad_token_id=0)[0, 20:]
+        want = hf.generate(prompt[None], do_sample=False, max_new_tokens=50, pad_token_id=0)[0, 20:]
     for cls in (CachedGenerator, SamplingGenerator):
-        got = cls(native, temperature=0.0).generate(prompt, 70).response
+        got = cls(native, temperature=0.0).generate(prompt, 50).response
         assert torch.equal(got, want), (cls.__name__, int((got != want).sum()))
 
 
