@@ -11,7 +11,7 @@ from torchtitan_b200.models.utils import count_params_and_flops
 FAMILIES = [
     ("llama3", "llama3_debugmodel", "debugmodel"),
     ("qwen3", "qwen3_debugmodel", "debugmodel"),
-    ("qwen3", "qwen3_moe_debug", "debugmodel_moe"),
+    ("qwen3", "qwen3_moe_tiny", "debugmodel_moe_tiny"),
     ("deepseek_v3", "deepseek_v3_debugmodel", "debugmodel"),
     ("deepseek_v3", "deepseek_v3_debugmodel_mtp", "debugmodel_mtp"),
     ("gpt_oss", "gpt_oss_debugmodel", "debugmodel"),

@@ -110,7 +110,7 @@ def test_expert_converters_train(tmp_path):
     moe = next(b.moe for b in spec.model.layers if b.moe is not None)
     assert moe.routed_experts.inner_experts.quant_recipe == "mxfp8"
     cfg = ConfigManager().parse_args([
-        "--module", "qwen3", "--config", "qwen3_moe_debug", "--training.steps", "2",
+        "--module", "qwen3", "--config", "qwen3_moe_tiny", "--training.steps", "2",
         "--training.num_tokens_per_microbatch_per_dp_rank", "128", "--training.max_context_length", "64",
         "--training.mixed_precision_param", "float32", "--dump_folder", str(tmp_path), "--checkpoint.no-enable",
         "--debug.no-enable_structured_logging", "--model.converters", "float8_experts",
