@@ -374,3 +374,39 @@ def test_causal_conv_silu_kernel(T, C, W, docs, dtype):
     for got, want in ((out, ref), (xk.grad, xr.grad), (wk.grad, wr.grad)):
         err = (got.float() - want).abs().max().item()
         assert err <= tol * (want.abs().max().item() + 1.0), (err, want.abs().max().item())
+
+
+def test_mla_assemble_kernel_matches_separate_ops():
+    """The fused multi-head-latent-attention assembly (rotary q_pe / k_pe, [nope | pe] queries and keys, contiguous
+    values) and its backward against the separate rotary / concatenate / expand operators in fp32."""
+    from torchtitan_b200.models.common.mla import _MLAAssembleFn
+
+    T, H, dn, dr, dv, rank = 200, 4, 32, 16, 32, 64
+    g = torch.Generator(device="cuda").manual_seed(4)
+    q = torch.randn(T, H, dn + dr, device="cuda", generator=g).bfloat16()
+    kv = torch.randn(T, H, dn + dv, device="cuda", generator=g).bfloat16()
+    kv_a = torch.randn(T, rank + dr, device="cuda", generator=g).bfloat16()
+    table = ref.rope_table(dr, 512, 10000.0).cuda()
+    pos = torch.randint(0, 512, (T,), device="cuda")
+    grads = [torch.randn(T, H, dn + dr, device="cuda", generator=g).bfloat16(),
+             torch.randn(T, H, dn + dr, device="cuda", generator=g).bfloat16(),
+             torch.randn(T, H, dv, device="cuda", generator=g).bfloat16()]
+
+    def separate(q, kv, kv_a):
+        q_pe = ref.rope_apply(q[:, :, dn:], table, pos, True)
+        k_pe = ref.rope_apply(kv_a[:, rank:].reshape(T, 1, dr), table, pos, True)
+        return (torch.cat([q[:, :, :dn], q_pe], -1), torch.cat([kv[:, :, :dn], k_pe.expand(T, H, dr)], -1), kv[:, :, dn:])
+
+    a = [t.float().requires_grad_() for t in (q, kv, kv_a)]
+    want = separate(*a)
+    torch.autograd.backward(want, [x.float() for x in grads])
+    b = [t.clone().requires_grad_() for t in (q, kv, kv_a)]
+    got = _MLAAssembleFn.apply(b[0], b[1], b[2][:, rank:], table, pos, dn, dr, dv)
+    torch.autograd.backward(got, grads)
+    assert got[2].is_contiguous()
+    for x, y in zip(got, want):
+        assert (x.float() - y).abs().max().item() <= 2e-2 * y.abs().max().item() + 1e-3
+    for x, y in zip(b, a):
+        assert (x.grad.float() - y.grad).abs().max().item() <= 2e-2 * y.grad.abs().max().item() + 2e-2
+    assert (b[2].grad[:, :rank] == 0).all()
+    assert OF.settings is not None and torch.ops.tb200.status(True) == 0

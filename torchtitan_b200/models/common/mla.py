@@ -30,6 +30,43 @@ from .module import Module
 __all__ = ["MLAttention"]
 
 
+class _MLAAssembleFn(torch.autograd.Function):
+    """Rotary embedding of the decoupled query / key parts and assembly of ``qf``, ``kf``, ``v`` in one kernel
+    (``ops/csrc/mla.cu``); the backward is its transpose (the gradient of the shared rotary key sums over the heads)."""
+
+    @staticmethod
+    def forward(ctx, q, kv, k_pe, table, positions, dn, dr, dv):
+        from torchtitan_b200.ops import ext
+        from torchtitan_b200.ops.functional import _count
+
+        pos = positions.to(torch.int64).contiguous()
+        ctx.save_for_backward(table, pos)
+        ctx.dims = (dn, dr, dv)
+        _count()
+        return ext.require().mla_assemble_fwd(q.contiguous(), kv.contiguous(), k_pe, table, pos, dn, dr, dv)
+
+    @staticmethod
+    def backward(ctx, dqf, dkf, dv_):
+        from torchtitan_b200.ops import ext
+        from torchtitan_b200.ops.functional import _count
+
+        table, pos = ctx.saved_tensors
+        dn, dr, dv = ctx.dims
+        _count()
+        dq, dkv, dk_pe = ext.require().mla_assemble_bwd(dqf.contiguous(), dkf.contiguous(), dv_.contiguous(), table, pos,
+                                                        dn, dr, dv)
+        return dq, dkv, dk_pe, None, None, None, None, None
+
+
+def _assemble_kernel_ok(q, kv, kv_a, positions, rope, dn, dr, dv, rank) -> bool:
+    from torchtitan_b200.ops import ext
+
+    return (q.is_cuda and q.dtype == torch.bfloat16 and kv.dtype == torch.bfloat16 and positions.dim() == 1
+            and rope.interleaved and rope.cache.shape[1] == dr and rope.cache.dtype == torch.float32
+            and dn % 8 == 0 and dr % 8 == 0 and dv % 8 == 0 and rank % 8 == 0 and kv_a.shape[1] % 8 == 0
+            and ext.available())
+
+
 class MLAttention(Module):
     @dataclass(kw_only=True, slots=True)
     class Config(Module.Config):
@@ -106,13 +143,17 @@ class MLAttention(Module):
         H, dn, dr, dv = self.n_heads, c.qk_nope_head_dim, c.qk_rope_head_dim, c.v_head_dim
         q = self.wq_b(self.q_norm(self.wq_a(x))) if self.wq is None else self.wq(x)
         q = q.view(T, H, dn + dr)
-        q_pe = self.rope(q[:, :, dn:], positions)
         kv_a = self.wkv_a(x)
-        k_pe = self.rope(kv_a[:, c.kv_lora_rank:].reshape(T, 1, dr), positions)
         kv = self.wkv_b(self.kv_norm(kv_a[:, :c.kv_lora_rank])).view(T, H, dn + dv)
-        qf = torch.cat([q[:, :, :dn], q_pe], dim=-1)
-        kf = torch.cat([kv[:, :, :dn], k_pe.expand(T, H, dr)], dim=-1)
-        v = kv[:, :, dn:]
+        if _assemble_kernel_ok(q, kv, kv_a, positions, self.rope, dn, dr, dv, c.kv_lora_rank):
+            # one kernel: rotary embedding of q_pe and k_pe, [nope | pe] assembly of queries and keys, contiguous values
+            qf, kf, v = _MLAAssembleFn.apply(q, kv, kv_a[:, c.kv_lora_rank:], self.rope.cache, positions, dn, dr, dv)
+        else:
+            q_pe = self.rope(q[:, :, dn:], positions)
+            k_pe = self.rope(kv_a[:, c.kv_lora_rank:].reshape(T, 1, dr), positions)
+            qf = torch.cat([q[:, :, :dn], q_pe], dim=-1)
+            kf = torch.cat([kv[:, :, :dn], k_pe.expand(T, H, dr)], dim=-1)
+            v = kv[:, :, dn:]
         ctx = ctx or AttentionContext()
         if ctx.cp is not None:
             from torchtitan_b200.parallel.context_parallel import cp_attention

@@ -9,6 +9,12 @@ std::tuple<at::Tensor, at::Tensor> rmsnorm_bwd(const at::Tensor& dy, const at::T
 void rope_(at::Tensor x, const at::Tensor& table, const at::Tensor& positions, bool interleaved, bool inverse);
 at::Tensor swiglu_fwd(const at::Tensor& gu);
 at::Tensor swiglu_bwd(const at::Tensor& gu, const at::Tensor& dout);
+std::tuple<at::Tensor, at::Tensor, at::Tensor> mla_assemble_fwd(const at::Tensor& q, const at::Tensor& kv, const at::Tensor& k_pe,
+                                                                const at::Tensor& table, const at::Tensor& positions, int64_t dn,
+                                                                int64_t dr, int64_t dv);
+std::tuple<at::Tensor, at::Tensor, at::Tensor> mla_assemble_bwd(const at::Tensor& dqf, const at::Tensor& dkf, const at::Tensor& dv_,
+                                                                const at::Tensor& table, const at::Tensor& positions, int64_t dn,
+                                                                int64_t dr, int64_t dv);
 at::Tensor conv_silu_fwd(const at::Tensor& x, const at::Tensor& w, const c10::optional<at::Tensor>& pos);
 std::tuple<at::Tensor, at::Tensor> conv_silu_bwd(const at::Tensor& x, const at::Tensor& w,
                                                  const c10::optional<at::Tensor>& pos, const at::Tensor& dy);
@@ -95,6 +101,10 @@ TORCH_LIBRARY(tb200, m) {
   m.def("rope_(Tensor(a!) x, Tensor table, Tensor positions, bool interleaved, bool inverse) -> ()", &tb200::rope_);
   m.def("swiglu_fwd(Tensor gu) -> Tensor", &tb200::swiglu_fwd);
   m.def("swiglu_bwd(Tensor gu, Tensor dout) -> Tensor", &tb200::swiglu_bwd);
+  m.def("mla_assemble_fwd(Tensor q, Tensor kv, Tensor k_pe, Tensor table, Tensor positions, int dn, int dr, int dv) -> (Tensor, Tensor, Tensor)",
+        &tb200::mla_assemble_fwd);
+  m.def("mla_assemble_bwd(Tensor dqf, Tensor dkf, Tensor dv, Tensor table, Tensor positions, int dn, int dr, int dv) -> (Tensor, Tensor, Tensor)",
+        &tb200::mla_assemble_bwd);
   m.def("conv_silu_fwd(Tensor x, Tensor w, Tensor? pos) -> Tensor", &tb200::conv_silu_fwd);
   m.def("conv_silu_bwd(Tensor x, Tensor w, Tensor? pos, Tensor dy) -> (Tensor, Tensor)", &tb200::conv_silu_bwd);
   m.def("status(bool clear) -> int", &tb200::status);

@@ -562,6 +562,13 @@ at::Tensor swiglu_bwd(const at::Tensor& gu, const at::Tensor& dout) {
   return dgu;
 }
 
+// Address of the status word on the current device, for kernels of other translation units.
+int* status_word_ptr() {
+  int* p = nullptr;
+  C10_CUDA_CHECK(cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_status_word));
+  return p;
+}
+
 int64_t status(bool clear) {
   int v = 0;
   cudaMemcpyFromSymbol(&v, g_status_word, sizeof(int));
