@@ -73,3 +73,28 @@ def test_vision_encoder_is_block_diagonal_and_position_aware():
     r = rope_2d(x, torch.tensor([0, 0, 1, 1]), torch.tensor([0, 1, 0, 1]))
     assert torch.allclose(r[0], x[0]) and not torch.allclose(r[3], x[3])
     assert torch.allclose(r.norm(dim=-1), x.norm(dim=-1), atol=1e-5)
+
+
+def test_qwen3_5_vision_language_matches_transformers():
+    """The vision-language flavor on weights taken from a freshly initialised ``Qwen3_5ForConditionalGeneration``: the
+    ViT tower (two-frame patch embedding, interpolated position table, 2-D rotary attention, 2 x 2 merger), the
+    placeholder scatter, the three-axis position rule and the interleaved multimodal RoPE give transformers' logits
+    on text interleaved with two images; the adapter's visual names round-trip."""
+    import pytest
+
+    pytest.importorskip("transformers")
+    from torchtitan_b200.models import get_model_spec
+    from torchtitan_b200.scripts.numerical_tests import main
+
+    res = main(["--module", "qwen3_5", "--flavor", "debugmodel_vl", "--random", "--perturb", "0.1"])
+    assert abs(res["kl_mean"]) < 1e-6 and res["max_abs_logit_diff"] < 1e-4, res
+
+    spec = get_model_spec("qwen3_5", "debugmodel_vl")
+    model = spec.model.build()
+    model.init_states(seed=2)
+    ad = spec.state_dict_adapter(spec.model, None)
+    vis = {k: p.detach() for k, p in model.named_parameters() if k.startswith("vision_encoder.")}
+    hf = ad.to_hf(dict(vis))
+    assert hf["model.visual.patch_embed.proj.weight"].dim() == 5 and "model.visual.blocks.0.attn.qkv.weight" in hf
+    back = ad.from_hf(hf)
+    assert set(back) == set(vis) and all(torch.equal(back[k], vis[k]) for k in vis)

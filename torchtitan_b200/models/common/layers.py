@@ -198,6 +198,10 @@ class RoPE(Module):
         mrope_sections: tuple[int, ...] | None = None
         """Multimodal RoPE: how many of the ``dim / 2`` rotary frequencies follow the temporal,
         height and width position axis.  Positions are then ``[3, T]``."""
+        mrope_interleaved: bool = False
+        """Frequency f follows the height axis when ``f % 3 == 1`` and ``f < 3 * sections[1]``, the width axis when
+        ``f % 3 == 2`` and ``f < 3 * sections[2]``, else the temporal axis (Qwen3-VL / Qwen3.5); otherwise the axes own
+        contiguous runs of frequencies (Qwen2-VL)."""
 
     def __init__(self, config: "RoPE.Config", **_):
         super().__init__(config)
@@ -232,8 +236,14 @@ class RoPE(Module):
         if secs is None:
             raise ValueError("3-axis positions need RoPE.Config.mrope_sections")
         half = self.cache.shape[1] // 2
-        axis_of_freq = torch.repeat_interleave(torch.arange(len(secs), device=positions.device),
-                                               torch.tensor(secs, device=positions.device))          # [half]
+        if self.config.mrope_interleaved:
+            f = torch.arange(half, device=positions.device)
+            axis_of_freq = torch.zeros(half, dtype=torch.int64, device=positions.device)
+            axis_of_freq[(f % 3 == 1) & (f < 3 * secs[1])] = 1
+            axis_of_freq[(f % 3 == 2) & (f < 3 * secs[2])] = 2
+        else:
+            axis_of_freq = torch.repeat_interleave(torch.arange(len(secs), device=positions.device),
+                                                   torch.tensor(secs, device=positions.device))      # [half]
         pos_tf = positions.long()[axis_of_freq].t()                                                   # [T, half]
         f = torch.arange(half, device=positions.device)
         table = torch.cat([self.cache[pos_tf, f], self.cache[pos_tf, f + half]], dim=1).contiguous()

@@ -144,7 +144,7 @@ class MultimodalDecoder(Decoder):
 
 
 def to_multimodal(text_cfg: Decoder.Config, vision: VisionEncoder.Config, image_token_id: int,
-                  mrope_sections: tuple[int, ...] | None = None) -> "MultimodalDecoder.Config":
+                  mrope_sections: tuple[int, ...] | None = None, mrope_interleaved: bool = False) -> "MultimodalDecoder.Config":
     """A text decoder config with a vision tower in front; with ``mrope_sections`` every rotary
     attention layer switches to three-axis positions."""
     import dataclasses
@@ -155,5 +155,6 @@ def to_multimodal(text_cfg: Decoder.Config, vision: VisionEncoder.Config, image_
             rope = getattr(blk.attention, "rope", None)
             if rope is not None:
                 rope.mrope_sections = tuple(mrope_sections)
+                rope.mrope_interleaved = mrope_interleaved
     return MultimodalDecoder.Config(**kw, vision_encoder=vision, image_token_id=image_token_id,
                                     use_mrope=mrope_sections is not None)

@@ -97,6 +97,11 @@ class VisionEncoder(Module):
         mlp_dim: int = 0
         n_layers: int = 0
         spatial_merge: int = 2
+        temporal_patch_size: int = 1
+        """Frames per patch: a patch vector holds ``C * temporal_patch_size * P * P`` values (still images repeat the frame)."""
+        num_position_embeddings: int = 0
+        """Learned position table of ``sqrt(n) x sqrt(n)`` entries, bilinearly interpolated to every image's patch grid
+        and added to the patch embeddings (0: rotary positions only)."""
         out_dim: int = 0          # the language model's width
         norm_eps: float = 1e-6
         layers: list = field(default_factory=list)   # list[VisionBlock.Config], filled from the sizes when empty
@@ -111,13 +116,37 @@ class VisionEncoder(Module):
             c.layers = [VisionBlock.Config(dim=c.dim, num_heads=c.num_heads, mlp_dim=c.mlp_dim, norm_eps=c.norm_eps)
                         for _ in range(c.n_layers)]
         m2 = c.spatial_merge ** 2
-        c.patch_embed.in_features, c.patch_embed.out_features = c.in_channels * c.patch_size ** 2, c.dim
+        c.patch_embed.in_features = c.in_channels * c.temporal_patch_size * c.patch_size ** 2
+        c.patch_embed.out_features = c.dim
+        self.pos_embed = None
+        if c.num_position_embeddings:
+            side = int(round(c.num_position_embeddings ** 0.5))
+            if side * side != c.num_position_embeddings:
+                raise ValueError("num_position_embeddings must be a square")
+            self.pos_embed = nn.Parameter(torch.empty(c.num_position_embeddings, c.dim))
+            set_init(self.pos_embed, InitSpec(kind="normal", std=0.02))
         c.merger_fc1.in_features, c.merger_fc1.out_features = c.dim * m2, c.dim * m2
         c.merger_fc2.in_features, c.merger_fc2.out_features = c.dim * m2, c.out_dim
         self.patch_embed = c.patch_embed.build()
         self.layers = ModuleDict({str(i): b.build() for i, b in enumerate(c.layers)})
         self.norm = _layer_norm(c.dim, c.norm_eps)
         self.merger_fc1, self.merger_fc2 = c.merger_fc1.build(), c.merger_fc2.build()
+
+    def _interpolated_positions(self, h: int, w: int) -> torch.Tensor:
+        """The learned ``side x side`` table sampled bilinearly on an ``h x w`` grid that spans it corner to corner
+        (row-major ``[h * w, dim]``)."""
+        table = self.pos_embed
+        side = int(round(table.shape[0] ** 0.5))
+        dev = table.device
+        ys = torch.linspace(0, side - 1, h, device=dev)
+        xs = torch.linspace(0, side - 1, w, device=dev)
+        y0, x0 = ys.long(), xs.long()
+        y1, x1 = (y0 + 1).clamp(max=side - 1), (x0 + 1).clamp(max=side - 1)
+        dy, dx = (ys - y0)[:, None, None], (xs - x0)[None, :, None]
+        t = table.float().view(side, side, -1)
+        out = (t[y0][:, x0] * (1 - dy) * (1 - dx) + t[y0][:, x1] * (1 - dy) * dx
+               + t[y1][:, x0] * dy * (1 - dx) + t[y1][:, x1] * dy * dx)
+        return out.reshape(h * w, -1)
 
     def tokens_per_image(self, grid_hw: torch.Tensor) -> torch.Tensor:
         m = self.config.spatial_merge
@@ -139,7 +168,14 @@ class VisionEncoder(Module):
             o += h * w
         if o != patches.shape[0]:
             raise ValueError(f"grid_hw describes {o} patches, got {patches.shape[0]}")
+        per_frame = c.in_channels * c.patch_size ** 2
+        if c.temporal_patch_size > 1 and patches.shape[1] == per_frame:
+            # still images: the frame is repeated over the temporal extent of the patch ([C, frames, P, P] layout)
+            patches = patches.view(-1, c.in_channels, 1, c.patch_size ** 2).expand(-1, -1, c.temporal_patch_size, -1)
+            patches = patches.reshape(-1, per_frame * c.temporal_patch_size)
         x = self.patch_embed(patches.to(self.patch_embed.weight.dtype))
+        if self.pos_embed is not None:
+            x = x + torch.cat([self._interpolated_positions(h, w) for h, w in grid]).to(x.dtype)
         for blk in self.layers.values():
             x = blk(x, rows, cols, spans)
         x = self.norm(x)

@@ -9,7 +9,10 @@ Hugging Face files differ from the native layout in four places:
 * MoE experts: fused ``gate_up_proj [E, 2F, D]`` and ``down_proj [E, D, F]`` tensors (or one 2-D tensor per expert in
   older exports); natively ``w1 / w3 [E, F, D]`` and ``w2 [E, D, F]``; the shared expert has a sigmoid gate;
 * released multimodal checkpoints prefix the decoder with ``model.language_model.``, text-only exports with ``model.``:
-  both are read, ``to_hf`` writes the prefix given by ``hf_prefix``.
+  both are read, ``to_hf`` writes the prefix given by ``hf_prefix``;
+* the vision tower (``model.visual.*``, read when the native model has one): the patch embedding is a 3-D
+  convolution whose kernel equals the patch, natively a linear layer on the flattened patch; blocks are called
+  ``blocks`` / ``attn.qkv`` / ``mlp.linear_fc1`` there and ``layers`` / ``wqkv`` / ``fc1`` here.
 """
 
 from __future__ import annotations
@@ -21,6 +24,21 @@ import torch
 from torchtitan_b200.models.state_dict_adapter import StateDictAdapter
 
 __all__ = ["Qwen35StateDictAdapter"]
+
+
+_VISUAL = {
+    "patch_embed.proj.bias": "patch_embed.bias",
+    "pos_embed.weight": "pos_embed",
+    "merger.norm.weight": "norm.weight", "merger.norm.bias": "norm.bias",
+    "merger.linear_fc1.weight": "merger_fc1.weight", "merger.linear_fc1.bias": "merger_fc1.bias",
+    "merger.linear_fc2.weight": "merger_fc2.weight", "merger.linear_fc2.bias": "merger_fc2.bias",
+}
+_VISUAL_BLOCK = {
+    "norm1.weight": "norm1.weight", "norm1.bias": "norm1.bias", "norm2.weight": "norm2.weight", "norm2.bias": "norm2.bias",
+    "attn.qkv.weight": "wqkv.weight", "attn.qkv.bias": "wqkv.bias", "attn.proj.weight": "proj.weight",
+    "attn.proj.bias": "proj.bias", "mlp.linear_fc1.weight": "fc1.weight", "mlp.linear_fc1.bias": "fc1.bias",
+    "mlp.linear_fc2.weight": "fc2.weight", "mlp.linear_fc2.bias": "fc2.bias",
+}
 
 
 class Qwen35StateDictAdapter(StateDictAdapter):
@@ -66,8 +84,22 @@ class Qwen35StateDictAdapter(StateDictAdapter):
         for k, v in hf_state_dict.items():
             if k.startswith("model.language_model."):
                 k = "model." + k[len("model.language_model."):]
-            if k.startswith("model.visual.") or k.startswith("mtp."):
-                continue                                   # the vision tower and the MTP head are not part of the decoder
+            if k.startswith("model.visual."):
+                if getattr(self.model_config, "vision_encoder", None) is None:
+                    continue                               # a text-only native model: the tower is left out
+                name = k[len("model.visual."):]
+                mb = re.fullmatch(r"blocks\.(\d+)\.(.+)", name)
+                if name == "patch_embed.proj.weight":
+                    out["vision_encoder.patch_embed.weight"] = v.reshape(v.shape[0], -1)
+                elif mb and mb.group(2) in _VISUAL_BLOCK:
+                    out[f"vision_encoder.layers.{mb.group(1)}.{_VISUAL_BLOCK[mb.group(2)]}"] = v
+                elif name in _VISUAL:
+                    out["vision_encoder." + _VISUAL[name]] = v
+                else:
+                    raise KeyError(f"no native name for '{k}'")
+                continue
+            if k.startswith("mtp."):
+                continue                                   # the multi-token-prediction head is not part of the decoder
             m = re.fullmatch(r"model\.layers\.(\d+)\.(.+)", k)
             rest = m.group(2) if m else None
             if rest == "linear_attn.in_proj_qkv.weight":
@@ -112,6 +144,7 @@ class Qwen35StateDictAdapter(StateDictAdapter):
 
     def to_hf(self, state_dict):
         plain, out = {}, {}
+        visual: dict[str, torch.Tensor] = {}
         gdn: dict[str, dict[str, torch.Tensor]] = {}
         attn: dict[str, dict[str, torch.Tensor]] = {}
         moe: dict[str, dict[str, torch.Tensor]] = {}
@@ -129,6 +162,22 @@ class Qwen35StateDictAdapter(StateDictAdapter):
                 moe.setdefault(m.group(1), {})[m.group(2)] = v
                 continue
             if k.endswith("moe.expert_bias_E"):
+                continue
+            if k.startswith("vision_encoder."):
+                name = k[len("vision_encoder."):]
+                mb = re.fullmatch(r"layers\.(\d+)\.(.+)", name)
+                inv_b = {b: a for a, b in _VISUAL_BLOCK.items()}
+                inv = {b: a for a, b in _VISUAL.items()}
+                if name == "patch_embed.weight":
+                    vc = self.model_config.vision_encoder
+                    visual[f"model.visual.patch_embed.proj.weight"] = v.reshape(
+                        v.shape[0], vc.in_channels, vc.temporal_patch_size, vc.patch_size, vc.patch_size)
+                elif mb and mb.group(2) in inv_b:
+                    visual[f"model.visual.blocks.{mb.group(1)}.{inv_b[mb.group(2)]}"] = v
+                elif name in inv:
+                    visual["model.visual." + inv[name]] = v
+                else:
+                    raise KeyError(f"no Hugging Face name for '{k}'")
                 continue
             plain[k] = v
         if self.model_config.enable_weight_tying:
@@ -148,4 +197,5 @@ class Qwen35StateDictAdapter(StateDictAdapter):
             out[f"model.layers.{i}.mlp.experts.down_proj"] = d["w2_EDF"]
         if self.hf_prefix != "model.":
             out = {(self.hf_prefix + k[len("model."):] if k.startswith("model.") else k): v for k, v in out.items()}
+        out.update(visual)
         return out

@@ -60,7 +60,8 @@ def count_params_and_flops(cfg, model: nn.Module | None, seq_len: int) -> tuple[
     if vis is not None:     # vision tower: counted as parameters; its FLOPs depend on the images, not on seq_len
         d, mlp, dm = vis.dim, vis.mlp_dim, vis.dim * vis.spatial_merge ** 2
         n_blocks = len(vis.layers) or vis.n_layers
-        v = vis.in_channels * vis.patch_size ** 2 * d + d
+        v = vis.in_channels * getattr(vis, "temporal_patch_size", 1) * vis.patch_size ** 2 * d + d
+        v += getattr(vis, "num_position_embeddings", 0) * d
         v += n_blocks * (3 * d * d + 3 * d + d * d + d + d * mlp + mlp + mlp * d + d + 4 * d)
         v += 2 * d + dm * dm + dm + dm * dim + dim
         total += v

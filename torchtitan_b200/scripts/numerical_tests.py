@@ -18,7 +18,7 @@ import torch
 
 from torchtitan_b200.models import get_model_spec
 
-__all__ = ["hf_config_for", "checkpoint_state", "load_native_from_hf_state", "compare_logits", "compare_grads", "main"]
+__all__ = ["hf_config_for", "hf_multimodal_config_for", "compare_multimodal", "checkpoint_state", "load_native_from_hf_state", "compare_logits", "compare_grads", "main"]
 
 
 def hf_config_for(module: str, cfg):
@@ -112,6 +112,10 @@ def checkpoint_state(hf_model) -> dict[str, torch.Tensor]:
             with safe_open(os.path.join(d, fn), framework="pt", device="cpu") as f:
                 for k in f.keys():
                     out[k] = f.get_tensor(k)
+    if any(".language_model.language_model." in k for k in out):
+        # composite (vision + text) models built from a config: the name conversion of ``save_pretrained`` repeats the
+        # prefix; their in-memory names already are the released checkpoint names
+        return {k: v.detach().clone() for k, v in hf_model.state_dict().items()}
     return out
 
 
@@ -184,6 +188,58 @@ def compare_grads(spec, native, hf_model, tokens: torch.Tensor) -> dict:
     return {"grad_tensors_compared": n, "max_rel_grad_diff": worst}
 
 
+def hf_multimodal_config_for(module: str, cfg):
+    """The ``transformers`` config of a vision-language flavor (Qwen3.5: ViT tower + interleaved three-axis RoPE)."""
+    import transformers
+
+    if module != "qwen3_5":
+        raise ValueError(f"no Hugging Face multimodal mapping for module '{module}'")
+    text = hf_config_for(module, cfg)
+    full = next(b for b in cfg.layers if hasattr(b.attention, "rope"))
+    text.rope_parameters["mrope_section"] = list(full.attention.rope.mrope_sections)
+    text.rope_parameters["mrope_interleaved"] = True
+    vis = cfg.vision_encoder
+    vision = dict(depth=len(vis.layers) or vis.n_layers, hidden_size=vis.dim, intermediate_size=vis.mlp_dim,
+                  num_heads=vis.num_heads, in_channels=vis.in_channels, patch_size=vis.patch_size,
+                  spatial_merge_size=vis.spatial_merge, temporal_patch_size=vis.temporal_patch_size,
+                  out_hidden_size=cfg.dim, num_position_embeddings=vis.num_position_embeddings)
+    top = cfg.vocab_size
+    return transformers.Qwen3_5Config(text_config=text.to_dict(), vision_config=vision, image_token_id=cfg.image_token_id,
+                                      vision_start_token_id=top - 3, vision_end_token_id=top - 2, video_token_id=top - 4,
+                                      tie_word_embeddings=cfg.enable_weight_tying)
+
+
+@torch.no_grad()
+def compare_multimodal(spec, native, hf_model, grids=((4, 6), (2, 4)), seed: int = 0) -> dict:
+    """Logits on text interleaved with images of the given patch grids.  The native tower takes row-major single-frame
+    patches; ``transformers`` takes two-frame patches in merge-window order (what its processor emits)."""
+    cfg = spec.model
+    vis = cfg.vision_encoder
+    g = torch.Generator().manual_seed(seed)
+    m, P2 = vis.spatial_merge, vis.patch_size ** 2
+    start, end = cfg.vocab_size - 3, cfg.vocab_size - 2
+    low = cfg.vocab_size - 8
+
+    def window(x, h, w):
+        return x.view(h // m, m, w // m, m, -1).permute(0, 2, 1, 3, 4).reshape(h * w, -1)
+
+    parts, rowmajor, windowed = [torch.randint(0, low, (10,), generator=g)], [], []
+    for gh, gw in grids:
+        parts += [torch.tensor([start]), torch.full((gh * gw // (m * m),), cfg.image_token_id), torch.tensor([end]),
+                  torch.randint(0, low, (7,), generator=g)]
+        p = torch.randn(gh * gw, vis.in_channels * P2, generator=g)
+        rowmajor.append(p)
+        frames = p.view(-1, vis.in_channels, 1, P2).expand(-1, -1, vis.temporal_patch_size, -1).reshape(gh * gw, -1)
+        windowed.append(window(frames, gh, gw))
+    tok = torch.cat(parts)
+    theirs = hf_model(input_ids=tok[None], pixel_values=torch.cat(windowed),
+                      image_grid_thw=torch.tensor([[1, h, w] for h, w in grids]),
+                      mm_token_type_ids=(tok == cfg.image_token_id).long()[None]).logits[0].float()
+    ours = native(tok, torch.arange(tok.shape[0]), pixel_patches=torch.cat(rowmajor), grid_hw=torch.tensor(grids)).float()
+    lp, lq = torch.log_softmax(theirs, -1), torch.log_softmax(ours, -1)
+    return {"kl_mean": float((lp.exp() * (lp - lq)).sum(-1).mean()), "max_abs_logit_diff": float((ours - theirs).abs().max())}
+
+
 def main(argv=None) -> dict:
     import transformers
 
@@ -204,16 +260,28 @@ def main(argv=None) -> dict:
         raise SystemExit("give exactly one of --hf-dir and --random")
     spec = get_model_spec(args.module, args.flavor)
     torch.manual_seed(args.seed)
-    if args.random:
+    multimodal = getattr(spec.model, "vision_encoder", None) is not None
+    if args.random and multimodal:
+        hf_model = transformers.AutoModelForImageTextToText.from_config(
+            hf_multimodal_config_for(args.module, spec.model)).float().eval()
+    elif args.random:
         hf_model = transformers.AutoModelForCausalLM.from_config(hf_config_for(args.module, spec.model)).float().eval()
+    if args.random:
         if args.perturb:
             with torch.no_grad():
                 for p in hf_model.parameters():
                     if p.dim() == 1:
                         p.add_(torch.randn_like(p) * args.perturb)
+    elif multimodal:
+        hf_model = transformers.AutoModelForImageTextToText.from_pretrained(args.hf_dir, torch_dtype=torch.float32).eval()
     else:
         hf_model = transformers.AutoModelForCausalLM.from_pretrained(args.hf_dir, torch_dtype=torch.float32).eval()
     native = load_native_from_hf_state(spec, checkpoint_state(hf_model), args.hf_dir)
+    if multimodal:
+        res = compare_multimodal(spec, native, hf_model, seed=args.seed)
+        print(f"{args.module} {args.flavor} (text + images): mean KL {res['kl_mean']:.3e}, largest logit difference "
+              f"{res['max_abs_logit_diff']:.3e}")
+        return res
     g = torch.Generator().manual_seed(args.seed)
     tokens = torch.randint(0, spec.model.vocab_size, (args.num_seqs, args.seq_len), generator=g)
     res = compare_logits(native, hf_model, tokens)
