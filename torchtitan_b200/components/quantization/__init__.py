@@ -12,8 +12,7 @@ QUANT = ("mxfp8", "float8", "nvfp4", "mxfp8_experts", "float8_experts")
 
 
 def _registry():
-    from .mx import mxfp8_converter
-    from .float8 import float8_converter
+    from .utils import float8_converter, mxfp8_converter
     from torchtitan_b200.components.lora import lora_converter
 
     from .grouped import quantize_experts

@@ -56,3 +56,21 @@ def swap_linears(model_cfg, *, recipe: str, include=None, **extra) -> int:
     if n == 0:
         raise ValueError("the quantisation converter matched no Linear layer")
     return n
+
+
+def mxfp8_converter(model_cfg, arg, job_config) -> int:
+    """MXFP8: swaps the selected ``Linear`` configs for block-scaled fp8 linears (parity:
+    torchtitan/components/quantization/mx.py:50-98).  ``arg``: comma-separated FQN substrings to include (default: every
+    attention / MLP linear)."""
+    fqns = [a for a in (arg or "").split(",") if a and a != "emulate"]
+    return swap_linears(model_cfg, recipe="mxfp8", include=fqns or None)
+
+
+def float8_converter(model_cfg, arg, job_config) -> int:
+    """Float8 row-wise (parity: torchtitan/components/quantization/float8.py:53-173).  ``float8`` scales all three
+    GEMMs row-wise, ``float8:rowwise_with_gw_hp`` keeps the weight-gradient GEMM in bf16; ``emulate`` is accepted for
+    interface parity (the fp8 numerics are always reproduced exactly, see ``quantization.linear``)."""
+    opts = [a for a in (arg or "").split(",") if a]
+    hp = "rowwise_with_gw_hp" in opts
+    fqns = [a for a in opts if a not in ("emulate", "rowwise", "rowwise_with_gw_hp")]
+    return swap_linears(model_cfg, recipe="float8_rowwise", include=fqns or None, high_precision_wgrad=hp)
