@@ -2,6 +2,7 @@
 Hugging Face export/import, retention policy."""
 
 import os
+import shutil
 
 import pytest
 import torch
@@ -175,3 +176,27 @@ def test_qwen3_5_adapter_round_trip():
             assert set(back) == set(native), set(back) ^ set(native)
             for k in native:
                 assert torch.equal(back[k], native[k]), k
+
+
+def test_torch_save_storage_resumes_and_reshards(tmp_path):
+    """``checkpoint.storage = torch_save`` (one file per rank with global chunk offsets): a 2-rank job resumes exactly
+    from its own files, and its checkpoint loads on 1 rank (model and optimizer re-laid-out by box overlap) where the
+    next loss equals the one of loading the same step from DCP files."""
+    ts = ("--checkpoint.storage", "torch_save")
+    full, resumed, one_ts, one_dcp = (str(tmp_path / n) for n in ("full.pt", "res.pt", "one_ts.pt", "one_dcp.pt"))
+    run_distributed(_train, 2, str(tmp_path / "a"), 4, full, ts)
+    run_distributed(_train, 2, str(tmp_path / "b"), 2, str(tmp_path / "part.pt"), ts)
+    assert os.path.exists(tmp_path / "b" / "checkpoint" / "step-2" / "rank-1.pt")
+    run_distributed(_train, 2, str(tmp_path / "b"), 4, resumed, ts)
+    a, c = dict(torch.load(full)), dict(torch.load(resumed))
+    assert sorted(c) == [3, 4]
+    for s in (3, 4):
+        assert abs(a[s] - c[s]) < 1e-5, (s, a[s], c[s])
+    # the same two training steps written by both engines, then loaded on one rank
+    run_distributed(_train, 2, str(tmp_path / "d"), 2, str(tmp_path / "y.pt"))
+    skip = ("--checkpoint.exclude_from_loading", "dataloader")
+    shutil.rmtree(tmp_path / "b" / "checkpoint" / "step-4")            # folder b still holds the torch.save step 2
+    run_distributed(_train, 1, str(tmp_path / "b"), 3, one_ts, ts + skip)
+    run_distributed(_train, 1, str(tmp_path / "d"), 3, one_dcp, skip)
+    x, y = dict(torch.load(one_ts)), dict(torch.load(one_dcp))
+    assert list(x) == [3] and abs(x[3] - y[3]) < 1e-6, (x, y)

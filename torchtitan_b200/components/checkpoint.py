@@ -412,6 +412,14 @@ class CheckpointManager(Configurable):
         enable_first_step_checkpoint: bool = False
         create_seed_checkpoint: bool = False
         load_only: bool = False
+        storage: Literal["dcp", "torch_save"] = "dcp"
+        """``dcp``: torch.distributed.checkpoint files; ``torch_save``: one ``torch.save`` file per rank with global chunk
+        offsets (``TorchCheckpointingManager``); both load across layouts."""
+
+    def __new__(cls, config=None, **kw):
+        if cls is CheckpointManager and config is not None and getattr(config, "storage", "dcp") == "torch_save":
+            return object.__new__(TorchCheckpointingManager)
+        return object.__new__(cls)
 
     def __init__(self, config: "CheckpointManager.Config", *, trainer=None, dump_folder: str = "./outputs",
                  pdims=None, **_):
@@ -526,6 +534,12 @@ class CheckpointManager(Configurable):
             writer_filter = self.pdims.coords()["dp_replicate"] == 0
         dcp.save(state, checkpoint_id=path, planner=ChunkSavePlanner(writer_rank_filter=writer_filter),
                  process_group=group)
+
+    def _engine_load(self, state: dict[str, Any], path: str) -> None:
+        """Fill the tensors of ``state`` (this rank's chunks) and its plain entries from the files under ``path``."""
+        planner = ChunkLoadPlanner()
+        dcp.load(state, checkpoint_id=path, planner=planner)
+        _unflatten_into(state, planner.plain_state())
 
     def _save_last_step(self, step: int, path: str) -> None:
         c = self.config
@@ -746,9 +760,7 @@ class CheckpointManager(Configurable):
             if in_hf:
                 self._load_hf(path, {k: v for k, v in state.items() if isinstance(v, ShardedEntry)})
             else:
-                planner = ChunkLoadPlanner()
-                dcp.load(state, checkpoint_id=path, planner=planner)
-                _unflatten_into(state, planner.plain_state())
+                self._engine_load(state, path)
                 self._apply_plain(state)
             for e in self._engines():
                 e.publish_params()
@@ -770,28 +782,100 @@ class CheckpointManager(Configurable):
             self._purge_t.join(timeout=60)
 
 
+def _box_overlap(off_a, size_a, off_b, size_b):
+    """Intersection of two axis-aligned boxes: ``(offset, size)`` or None."""
+    lo = tuple(max(a, b) for a, b in zip(off_a, off_b))
+    hi = tuple(min(a + x, b + y) for a, x, b, y in zip(off_a, size_a, off_b, size_b))
+    if any(h <= l for l, h in zip(lo, hi)):
+        return None
+    return lo, tuple(h - l for l, h in zip(lo, hi))
+
+
 class TorchCheckpointingManager(CheckpointManager):
-    """Same policy surface (intervals, retention, async modes, model-only export, resume rules) on an
-    external ``torch_checkpointing`` storage engine instead of DCP files.  The storage engine is
-    not part of this package: ``_save`` / ``_load`` raise until one is plugged in by a subclass.
-    Parity: torchtitan/components/checkpointer/torch_checkpointing.py:121-222 (a skeleton there as
-    well)."""
+    """Same policy surface (intervals, retention, async modes, model-only export, resume rules) on plain
+    ``torch.save`` files instead of DCP: every writer rank stores its chunks (with their global offsets) and its
+    plain entries in ``rank-<r>.pt``, rank 0 adds ``.metadata`` with the rank count.  Loading reads the chunk index
+    of every rank file (memory-mapped) and copies the overlaps into this rank's chunks, so a checkpoint written with one
+    layout loads with another; no collective is used, writers only need a shared folder.  Parity: the interface of
+    torchtitan/components/checkpointer/torch_checkpointing.py:121-222 (whose ``_save`` / ``_load`` are not implemented
+    there)."""
 
     Config = CheckpointManager.Config
+    _META = ".metadata"
 
-    def _save(self, state: dict, path: str) -> None:
-        raise NotImplementedError("no torch_checkpointing storage engine is available: subclass and implement _save")
+    def _dcp_save(self, state: dict[str, Any], path: str, group=None) -> None:
+        import json
 
-    def _load(self, state: dict, path: str) -> None:
-        raise NotImplementedError("no torch_checkpointing storage engine is available: subclass and implement _load")
+        rank = dist.get_rank() if dist.is_initialized() else 0
+        world = dist.get_world_size() if dist.is_initialized() else 1
+        writer = not (self.pdims is not None and self.pdims.dp_replicate > 1 and self.pdims.coords()["dp_replicate"] != 0)
+        flat: dict[str, Any] = {}
+        _flatten("", state, flat)
+        payload = {"chunks": {}, "plain": {}}
+        for k, v in flat.items():
+            if isinstance(v, ShardedEntry):
+                if writer:
+                    payload["chunks"][k] = {"global_shape": tuple(v.global_shape), "dtype": v.dtype,
+                                            "pieces": [(tuple(o), tuple(z), t.detach().to(v.dtype).cpu().clone())
+                                                       for o, z, t in v.chunks]}
+            else:
+                payload["plain"][k] = v.detach().cpu() if isinstance(v, torch.Tensor) else v
+        os.makedirs(path, exist_ok=True)
+        tmp = os.path.join(path, f"rank-{rank}.pt.tmp")
+        torch.save(payload, tmp)
+        os.replace(tmp, os.path.join(path, f"rank-{rank}.pt"))
+        if dist.is_initialized() and world > 1:
+            dist.barrier(group=group)
+        if rank == 0:      # written last: a folder without it is an unfinished checkpoint
+            with open(os.path.join(path, self._META), "w") as f:
+                json.dump({"engine": "torch_save", "ranks": world}, f)
+        if dist.is_initialized() and world > 1:
+            dist.barrier(group=group)
 
-    def save(self, curr_step: int, last_step: bool = False) -> None:
-        if not self.config.enable:
-            return
-        self._save({}, os.path.join(self.folder, f"step-{curr_step}"))
+    def _engine_load(self, state: dict[str, Any], path: str) -> None:
+        import json
 
-    def load(self, step: int = -1) -> bool:
-        if not self.config.enable:
-            return False
-        self._load({}, self.folder)
-        return True
+        with open(os.path.join(path, self._META)) as f:
+            meta = json.load(f)
+        if meta.get("engine") != "torch_save":
+            raise ValueError(f"{path} was not written by the torch.save checkpoint engine")
+        flat: dict[str, Any] = {}
+        _flatten("", state, flat)
+        wanted = {k: v for k, v in flat.items() if isinstance(v, ShardedEntry)}
+        covered = {k: [0] * len(v.chunks) for k, v in wanted.items()}
+        plain: dict[str, Any] = {}
+        for r in range(int(meta["ranks"])):
+            data = torch.load(os.path.join(path, f"rank-{r}.pt"), map_location="cpu", mmap=True, weights_only=False)
+            for k, v in data["plain"].items():
+                plain.setdefault(k, v)
+            for k, ent in wanted.items():
+                saved = data["chunks"].get(k)
+                if saved is None:
+                    continue
+                if tuple(saved["global_shape"]) != tuple(ent.global_shape):
+                    raise ValueError(f"{k}: saved with global shape {saved['global_shape']}, the model has {ent.global_shape}")
+                for i, (off, size, dst) in enumerate(ent.chunks):
+                    for s_off, s_size, src in saved["pieces"]:
+                        box = _box_overlap(off, size, s_off, s_size)
+                        if box is None:
+                            continue
+                        lo, ext = box
+                        d = dst.view(size) if dst.dim() != len(size) else dst
+                        sl_d = tuple(slice(a - b, a - b + n) for a, b, n in zip(lo, off, ext))
+                        sl_s = tuple(slice(a - b, a - b + n) for a, b, n in zip(lo, s_off, ext))
+                        with torch.no_grad():
+                            d[sl_d].copy_(src.view(s_size)[sl_s].to(d.dtype))
+                        n = 1
+                        for e in ext:
+                            n *= e
+                        covered[k][i] += n
+        for k, ent in wanted.items():
+            for i, (_off, size, _t) in enumerate(ent.chunks):
+                n = 1
+                for e in size:
+                    n *= e
+                if covered[k][i] < n:
+                    raise KeyError(f"the checkpoint at {path} does not cover '{k}' (chunk {i}: {covered[k][i]} of {n} elements)")
+        _unflatten_into(state, {k: v for k, v in plain.items() if k in flat and k not in wanted})
+
+
