@@ -33,6 +33,7 @@ void gemm_scatter_bf16(const at::Tensor& a, const at::Tensor& b, at::IntArrayRef
 at::Tensor sum_slots(const at::Tensor& staging);
 int64_t gemm_status(bool clear);
 void gemm_set_variant(int64_t v);
+void gemm_set_mn3d(int64_t v);
 void gemm_set_debug(int64_t v);
 std::tuple<at::Tensor, at::Tensor> flash_fwd(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v, double scale,
                                              bool causal, int64_t causal_offset,
@@ -122,6 +123,7 @@ TORCH_LIBRARY(tb200, m) {
   m.def("sum_slots(Tensor staging) -> Tensor", &tb200::sum_slots);
   m.def("gemm_status(bool clear) -> int", &tb200::gemm_status);
   m.def("gemm_set_variant(int v) -> ()", &tb200::gemm_set_variant);
+  m.def("gemm_set_mn3d(int v) -> ()", &tb200::gemm_set_mn3d);
   m.def("gemm_set_debug(int v) -> ()", &tb200::gemm_set_debug);
   m.def("flash_fwd(Tensor q, Tensor k, Tensor v, float scale, bool causal, int causal_offset, Tensor? kv_first, "
         "int window=0, Tensor? sinks=None) -> (Tensor, Tensor)", &tb200::flash_fwd);
