@@ -66,8 +66,15 @@ def bench_gemm(args) -> None:
                2: (lambda: c.addmm_(a.t(), b)) if acc else (lambda: torch.mm(a.t(), b, out=c))}[mode]
         t1, t2 = timer(ours), timer(lib)
         fl = 2 * M * N * K
+        extra = ""
+        if args.mn_boxes and mode != 0:
+            # the same MN-major operands through one 2-D load per 64-column box instead of one 3-D load per stage
+            ops.gemm_set_mn3d(0)
+            t0 = timer(ours)
+            ops.gemm_set_mn3d(1)
+            extra = f" | 2-D boxes {t0:.3f} ms {fl / t0 / 1e9:.0f} TFLOPS"
         print(f"gemm {name:10s} mode{mode} M{M} N{N} K{K}: tcgen05 {t1:.3f} ms {fl / t1 / 1e9:.0f} TFLOPS | "
-              f"cuBLAS {t2:.3f} ms {fl / t2 / 1e9:.0f} TFLOPS | speedup {t2 / t1:.2f}", flush=True)
+              f"cuBLAS {t2:.3f} ms {fl / t2 / 1e9:.0f} TFLOPS | speedup {t2 / t1:.2f}{extra}", flush=True)
     print("gemm status word", ops.gemm_status(True))
 
 
@@ -278,6 +285,8 @@ def main(argv=None) -> int:
     ap.add_argument("--case", default="8b", choices=["small", "8b"])
     ap.add_argument("--variant", type=int, default=0, help="GEMM tiling: 0 auto, 1 single CTA, 2 CTA pair")
     ap.add_argument("--once", action="store_true", help="one launch per shape, no library arm (profiler form)")
+    ap.add_argument("--mn-boxes", action="store_true",
+                    help="gemm: also time MN-major operands staged with one 2-D load per 64-column box")
     args = ap.parse_args(argv)
     from . import ext
 
