@@ -22,7 +22,7 @@ import torch
 
 from .generator import SamplingGenerator, WeightSync
 from .losses import dapo_loss, group_advantages, grpo_loss, token_logprobs
-from .rollout import Rollout, RolloutBuffer
+from .rollout import SampledResponse, RolloutBuffer
 
 __all__ = ["RLConfig", "RLController"]
 
@@ -51,7 +51,7 @@ class RLController:
         self.buffer = RolloutBuffer(max_staleness=config.max_staleness)
         self.iteration = 0
 
-    def collect(self, prompts: list[torch.Tensor]) -> tuple[list[Rollout], torch.Tensor]:
+    def collect(self, prompts: list[torch.Tensor]) -> tuple[list[SampledResponse], torch.Tensor]:
         c = self.cfg
         rollouts, rewards = [], []
         self._all_rewards: list[float] = []

@@ -10,7 +10,7 @@ from __future__ import annotations
 
 import torch
 
-from .rollout import Rollout
+from .rollout import SampledResponse
 
 __all__ = ["SamplingGenerator", "CachedGenerator", "WeightSync"]
 
@@ -25,7 +25,7 @@ class SamplingGenerator:
         self.policy_version = 0
 
     @torch.no_grad()
-    def generate(self, prompt: torch.Tensor, max_new_tokens: int) -> Rollout:
+    def generate(self, prompt: torch.Tensor, max_new_tokens: int) -> SampledResponse:
         dev = next(self.model.parameters()).device
         seq = prompt.to(dev)
         lps = []
@@ -47,7 +47,7 @@ class SamplingGenerator:
             if self.eos_id is not None and int(nxt) == self.eos_id:
                 break
         n = len(lps)
-        return Rollout(prompt=prompt.cpu(), response=seq[-n:].cpu(), logprobs=torch.stack(lps).cpu(),
+        return SampledResponse(prompt=prompt.cpu(), response=seq[-n:].cpu(), logprobs=torch.stack(lps).cpu(),
                        policy_version=self.policy_version)
 
 
@@ -58,7 +58,7 @@ class CachedGenerator(SamplingGenerator):
     or process); ``WeightSync`` refreshes it and bumps ``policy_version``."""
 
     @torch.no_grad()
-    def generate(self, prompt: torch.Tensor, max_new_tokens: int) -> Rollout:
+    def generate(self, prompt: torch.Tensor, max_new_tokens: int) -> SampledResponse:
         from torchtitan_b200.models.common.attention import AttentionContext, KVCache
 
         dev = next(self.model.parameters()).device
@@ -81,7 +81,7 @@ class CachedGenerator(SamplingGenerator):
             if self.eos_id is not None and int(nxt) == self.eos_id:
                 break
         self.model.train(was_training)
-        return Rollout(prompt=prompt.cpu(), response=torch.stack(out_tokens).cpu(), logprobs=torch.stack(lps).cpu(),
+        return SampledResponse(prompt=prompt.cpu(), response=torch.stack(out_tokens).cpu(), logprobs=torch.stack(lps).cpu(),
                        policy_version=self.policy_version)
 
     def _sample(self, logits: torch.Tensor):

@@ -1,4 +1,4 @@
-"""Rollout records and a FIFO buffer that folds them into training batches."""
+"""SampledResponse records and a FIFO buffer that folds them into training batches."""
 
 from __future__ import annotations
 
@@ -7,11 +7,11 @@ from dataclasses import dataclass
 
 import torch
 
-__all__ = ["Rollout", "RolloutBuffer"]
+__all__ = ["SampledResponse", "RolloutBuffer"]
 
 
 @dataclass
-class Rollout:
+class SampledResponse:
     prompt: torch.Tensor       # [P] token ids
     response: torch.Tensor     # [R] token ids
     logprobs: torch.Tensor     # [R] behaviour-policy log-probabilities of the response tokens
@@ -21,7 +21,7 @@ class Rollout:
 
 class RolloutBuffer:
     def __init__(self, max_size: int = 4096, max_staleness: int = 1):
-        self.items: deque[Rollout] = deque(maxlen=max_size)
+        self.items: deque[SampledResponse] = deque(maxlen=max_size)
         self.max_staleness = max_staleness
 
     def add(self, rollouts) -> None:
@@ -33,7 +33,7 @@ class RolloutBuffer:
         self.items = deque(keep, maxlen=self.items.maxlen)
         return dropped
 
-    def fold(self, rollouts: list[Rollout], advantages: torch.Tensor):
+    def fold(self, rollouts: list[SampledResponse], advantages: torch.Tensor):
         """Concatenate samples into one token stream: ``(tokens, positions, labels, old_logp, adv, mask)``.
         Position restarts at every sample (document masking keeps samples apart); labels are the next
         token, prompt positions and the last token of each sample are masked out."""

@@ -27,7 +27,7 @@ from torchtitan_b200.parallel import tp_ops
 from .layers import Linear, RMSNorm, RoPE, TPContext
 from .module import InitSpec, Module, set_init
 
-__all__ = ["GQAttention", "AttentionContext", "KVCache", "build_attention_context"]
+__all__ = ["GQAttention", "AttentionContext", "KVCache", "BatchedKVCache", "build_attention_context"]
 
 
 @dataclass
@@ -38,7 +38,7 @@ class AttentionContext:
     max_doc_len: int | None = None
     kv_first: torch.Tensor | None = None  # [T_local] int32: index of the first token of each token's document
     rope_positions: torch.Tensor | None = None  # [3, T_local] multimodal rotary positions (overrides ``positions``)
-    kv_cache: "KVCache | None" = None  # incremental decoding: keys / values of earlier tokens, per attention layer
+    kv_cache: "KVCache | BatchedKVCache | None" = None  # incremental decoding: keys / values of earlier tokens, per attention layer
 
 
 class KVCache:
@@ -70,6 +70,16 @@ class KVCache:
         self._v[key][n0:n0 + n] = v
         self._len[key] = n0 + n
         return self._k[key][:n0 + n], self._v[key][:n0 + n]
+
+
+class BatchedKVCache:
+    """Several sequences decoded in one forward pass: the flat token stream holds ``rows[i]`` consecutive rows of
+    sequence ``i`` (its whole prompt at prefill, one row while decoding), each attending to its own ``caches[i]``.
+    The projections and feed-forward layers run once over all rows; only the attention core is per sequence."""
+
+    def __init__(self, caches: "list[KVCache]", rows: list[int]):
+        assert len(caches) == len(rows)
+        self.caches, self.rows = caches, rows
 
 
 def build_attention_context(positions: torch.Tensor, *, assume_single_document: bool = False,
@@ -204,11 +214,23 @@ class GQAttention(Module):
             # incremental decoding (no autograd): the new queries attend to everything cached plus themselves
             from torchtitan_b200.ops import flash as FL
 
-            kc, vc = ctx.kv_cache.update(self, k.detach(), v.detach())
-            o, lse = FL.block_fwd(q.contiguous(), kc, vc, self.scale, causal=True, causal_offset=kc.shape[0] - T,
-                                  window=int(self.window or 0))
-            if self.sinks is not None:
-                o = (o.float() * torch.sigmoid(lse - self.sinks.float()[:, None]).t()[..., None]).to(q.dtype)
+            def attend(cache, q_, k_, v_):
+                kc, vc = cache.update(self, k_.detach(), v_.detach())
+                o_, lse = FL.block_fwd(q_.contiguous(), kc, vc, self.scale, causal=True,
+                                       causal_offset=kc.shape[0] - q_.shape[0], window=int(self.window or 0))
+                if self.sinks is not None:
+                    o_ = (o_.float() * torch.sigmoid(lse - self.sinks.float()[:, None]).t()[..., None]).to(q_.dtype)
+                return o_
+
+            if isinstance(ctx.kv_cache, BatchedKVCache):
+                parts, r0 = [], 0
+                for cache, n in zip(ctx.kv_cache.caches, ctx.kv_cache.rows):
+                    parts.append(attend(cache, q[r0:r0 + n], k[r0:r0 + n], v[r0:r0 + n]))
+                    r0 += n
+                assert r0 == T, f"BatchedKVCache rows cover {r0} of {T} tokens"
+                o = torch.cat(parts)
+            else:
+                o = attend(ctx.kv_cache, q, k, v)
         elif ctx.cp is not None:
             from torchtitan_b200.parallel.context_parallel import cp_attention
 

@@ -142,6 +142,11 @@ class Decoder(Module):
             from torchtitan_b200.parallel import tp_ops
 
             h = tp_ops.all_gather_rows(h, self.tp)
+        return self.output_logits(h)
+
+    def output_logits(self, h: torch.Tensor) -> torch.Tensor:
+        """Output projection (with its multiplier and soft cap) of final-norm hidden states, e.g. of the rows a
+        generator samples from after ``forward(..., return_hidden=True)``."""
         logits = self.lm_head(h)
         if self.config.final_logit_multiplier != 1.0:
             logits = logits * self.config.final_logit_multiplier
