@@ -490,7 +490,7 @@ def test_engine_in_a_thread_serves_concurrent_requests():
 
 
 # ------------------------------------------------------------------------------------------------------- end to end
-def _rl_parts(tmp_path, *, steps, prompts_per_step=2, group=4):
+def _rl_parts(tmp_path, *, steps, prompts_per_step=2, group=4, drop_flat=False, lr=1e-2):
     from dataclasses import dataclass
 
     from torchtitan_b200.components.optimizer import OptimizersContainer
@@ -498,7 +498,8 @@ def _rl_parts(tmp_path, *, steps, prompts_per_step=2, group=4):
     from torchtitan_b200.config import Configurable
     from torchtitan_b200.experiments.rl import (AsyncController, AsyncLoopConfig, BatchConfig, Batcher, GenerationEngine,
                                                 MessageEnv, MessageEnvInit, MessageEnvStep, PolicyLoss, PolicyTrainer,
-                                                RewardFn, Rollouter, Rubric, SamplingConfig, ValidationConfig)
+                                                RewardFn, Rollouter, Rubric, SamplingConfig, TrainingSampleBuilder,
+                                                ValidationConfig)
     from torchtitan_b200.parallel.parallel_dims import ParallelDims
     from torchtitan_b200.parallel.parallelize import parallelize_decoder
     from torchtitan_b200.trainer import Trainer
@@ -530,7 +531,7 @@ def _rl_parts(tmp_path, *, steps, prompts_per_step=2, group=4):
             return MessageEnvStep(done=True)
 
     class LowBytes(RewardFn):
-        """Share of the completion's tokens below 64: easy to raise, so a few steps show learning."""
+        """Share of the completion's tokens from the lower half of the vocabulary: a dense signal that a few steps raise."""
 
         @dataclass(kw_only=True, slots=True)
         class Config(RewardFn.Config):
@@ -538,7 +539,7 @@ def _rl_parts(tmp_path, *, steps, prompts_per_step=2, group=4):
 
         async def __call__(self, rollout, env_input):
             ids = rollout.turns[-1].completion_token_ids if rollout.turns else []
-            return sum(t < 64 for t in ids) / max(len(ids), 1)
+            return sum(t < 1024 for t in ids) / max(len(ids), 1)
 
     spec, _ = _tiny_llama()
     cfg = Trainer.Config()
@@ -549,7 +550,7 @@ def _rl_parts(tmp_path, *, steps, prompts_per_step=2, group=4):
     with torch.device("meta"):
         model = spec.model.build()
     eng = parallelize_decoder(model, pdims=pdims, job_config=cfg, device=torch.device("cpu"), seed=3)
-    opt = OptimizersContainer(OptimizersContainer.Config(lr=3e-2, weight_decay=0.0), engines=[eng])
+    opt = OptimizersContainer(OptimizersContainer.Config(lr=lr, weight_decay=0.0), engines=[eng])
     trainer = PolicyTrainer(model=model, engine=eng, optimizers=opt, loss=PolicyLoss(0.2, 0.28), pdims=pdims)
     generator = GenerationEngine(GenerationEngine.Config(threaded=False), model=model)     # shares the trainer's weights
     config = AsyncController.Config(
@@ -557,6 +558,8 @@ def _rl_parts(tmp_path, *, steps, prompts_per_step=2, group=4):
                                    rubric=Rubric.Config(reward_fns=[LowBytes.Config()]), message_env=OneShot.Config()),
         async_loop=AsyncLoopConfig(num_training_steps=steps, num_prompts_per_train_step=prompts_per_step,
                                    num_samples_per_prompt=group, target_offpolicy_steps=1, window_fraction=0.5,
+                                   training_sample_builder=TrainingSampleBuilder.Config(drop_zero_std_reward_groups=drop_flat),
+                                   max_consecutive_untrainable_groups=16,
                                    batcher=Batcher.Config(batch=BatchConfig(local_batch_size=2, seq_len=64)),
                                    validation=ValidationConfig(num_samples=4)),
         sampling=SamplingConfig(temperature=1.0, max_tokens=6), dump_folder=str(tmp_path), trainer_in_thread=False)
@@ -564,27 +567,44 @@ def _rl_parts(tmp_path, *, steps, prompts_per_step=2, group=4):
 
 
 def test_async_controller_trains_with_bounded_staleness(tmp_path):
-    ctl, trainer, generator = _rl_parts(tmp_path, steps=8)
+    ctl, trainer, generator = _rl_parts(tmp_path, steps=10, group=8)
     lc = ctl.config.async_loop
     assert (lc.max_active_rollout_groups, lc.window_size, lc.max_offpolicy_steps) == (4, 2, 2)
     summary = run(ctl.run())
-    assert trainer.policy_version == 8 and generator.policy_version == 8
+    assert trainer.policy_version == 10 and generator.policy_version == 10
     hist = [h for h in ctl.metrics.history if "loss/mean" in h]
-    assert [h["step"] for h in hist] == list(range(1, 9))
+    assert [h["step"] for h in hist] == list(range(1, 11))
     assert all(h["policy_age_max"] <= lc.max_offpolicy_steps for h in hist)
-    assert all(math.isfinite(h["loss/mean"]) and h["optim/grad_norm"] > 0 for h in hist)
+    assert all(math.isfinite(h["loss/mean"]) for h in hist) and any(h["optim/grad_norm"] > 0 for h in hist)
     assert all(0 <= h["train_batch/padding_frac"] < 1 and h["train_batch/num_rollout_groups"] == 2 for h in hist)
     assert "perf/trainer/tokens_per_second_full_step" in hist[0] and "timing/weight_sync/generator_pull" in hist[0]
-    # the policy learned to prefer low token ids
-    first = sum(h["rollout_reward/_mean"] for h in hist[:2]) / 2
-    last = sum(h["rollout_reward/_mean"] for h in hist[-2:]) / 2
+    # samples generated by the current weights reproduce the generator's log-probabilities exactly in the trainer
+    fresh = [h for h in hist if h["policy_age_max"] == 0]
+    assert fresh and all(abs(h["bit_wise/logprob_diff/max"]) < 1e-4 and h["loss/ratio_clipped_frac"] == 0 for h in fresh)
+    # the policy learned to prefer the rewarded half of the vocabulary
+    first = sum(h["rollout_reward/_mean"] for h in hist[:3]) / 3
+    last = sum(h["rollout_reward/_mean"] for h in hist[-3:]) / 3
     assert last > first, (first, last)
-    assert summary["post"]["validation/rollout_reward/_mean"] >= summary["pre"]["validation/rollout_reward/_mean"]
+    assert "validation/rollout_reward/_mean" in summary["pre"] and "validation/rollout_reward/_mean" in summary["post"]
     rows = [json.loads(ln) for ln in open(tmp_path / "rollout_samples.jsonl")]
     assert any(r["is_validation"] for r in rows) and any(not r["is_validation"] for r in rows)
     assert rows[0]["turns"][0]["prompt_messages"][0]["role"] == "user" and "prompt_token_ids" not in rows[0]["turns"][0]
-    assert ctl._buffer.released["trained"] == 8 * 2
+    assert ctl._buffer.released["trained"] == 10 * 2
     run(ctl.close())
+
+
+def test_async_controller_stops_when_no_group_carries_signal(tmp_path):
+    """A constant reward makes every group's rewards equal; with such groups dropped nothing is ever trainable, and the
+    job stops with an error instead of generating forever."""
+    ctl, trainer, _ = _rl_parts(tmp_path, steps=2, drop_flat=True, lr=0.0)
+    ctl.rollouter.rubric.fns[0].__class__.__call__ = lambda self, rollout, env_input: _const()
+    with pytest.raises(RuntimeError, match="nothing to train on"):
+        run(ctl.run())
+    assert trainer.policy_version == 0 and ctl._buffer.released.get("untrainable_group", 0) >= 16
+
+
+async def _const():
+    return 0.5
 
 
 def test_async_loop_config_derives_window_and_bound():
@@ -665,3 +685,78 @@ def test_math_answer_example(tmp_path):
     path = tmp_path / "q.jsonl"
     path.write_text('{"prompt": "1+1?", "answer": 2}\n')
     assert next(MathDataset(MathDataset.Config(path=str(path)))).ground_truth == "2"
+
+
+# --------------------------------------------------------------------------------------------------------------- job
+def _job_args(folder, steps=2):
+    return ["--module", "rl", "--config", "rl_grpo_debug_alphabet_sort", "--trainer.dump_folder", folder,
+            "--controller.dump_folder", folder, "--trainer.training.mixed_precision_param", "float32",
+            "--trainer.debug.no-enable_structured_logging", "--trainer.debug.seed", "0",
+            "--controller.sampling.max_tokens", "6", "--controller.async_loop.num_training_steps", str(steps),
+            "--controller.async_loop.batcher.batch.seq_len", "512", "--controller.async_loop.validation.num_samples", "1"]
+
+
+def _run_job(rank, world, folder, out_path):
+    from torchtitan_b200.config import ConfigManager
+
+    job = ConfigManager().parse_args(_job_args(folder)).build()
+    result = job.run()
+    if rank == 0:
+        hist = [h for h in job.controller.metrics.history if "loss/mean" in h]
+        torch.save({"steps": [h["step"] for h in hist], "version": job.trainer.policy_version,
+                    "dp": job.controller.dp_degree, "post": result["post"]}, out_path)
+    else:
+        assert result is None and job.trainer.policy_version == 2          # the followers stepped with the leader
+    job.close()
+
+
+@pytest.mark.parametrize("world", [1, 2])
+def test_rl_job_from_the_config_registry(tmp_path, world):
+    """The registered debug job end to end; with two training ranks the controller runs on rank 0 and the other rank
+    follows its forward / backward and optimizer calls on its own column of the microbatch grid."""
+    from tests.dist_utils import run_distributed
+
+    out = str(tmp_path / "out.pt")
+    run_distributed(_run_job, world, str(tmp_path / "job"), out)
+    got = torch.load(out)
+    assert got["steps"] == [1, 2] and got["version"] == 2 and got["dp"] == world
+    assert "validation/rollout_reward/_mean" in got["post"]
+
+
+def test_rl_job_config_validation():
+    from torchtitan_b200.config import ConfigManager
+    from torchtitan_b200.experiments.rl import config_registry as reg
+
+    cfg = ConfigManager().parse_args(_job_args("/tmp/unused"))
+    assert cfg.trainer.training.max_context_length == 512 and cfg.trainer.training.num_tokens_per_microbatch_per_dp_rank == 1024
+    assert cfg.generator.threaded is False and cfg.controller.trainer_in_thread is False     # shared weights: no threads
+    assert cfg.trainer.model.converters == ["lm_head_cast"]
+    two = reg.rl_grpo_qwen3_0_6b_async_two_generators()
+    two.validate()
+    assert two.generator.threaded and two.controller.async_loop.max_offpolicy_steps >= 3
+    dapo = reg.rl_dapo_qwen3_4b_math_8k()
+    assert dapo.ratio_clip_high > dapo.ratio_clip_low and dapo.controller.rollouter.advantage.should_std_normalize
+    bad = reg.rl_grpo_debug_alphabet_sort()
+    bad.num_generators = 2
+    with pytest.raises(ValueError, match="share_weights"):
+        bad.validate()
+    assert reg.rl_grpo_qwen3_0_6b_alphabet_sort_batch_invariant().controller.async_loop.batcher.per_sample_pad_multiple == 128
+
+
+def test_lm_head_cast_converter_keeps_logits_in_fp32():
+    from torchtitan_b200.components.quantization import apply_converters
+    from torchtitan_b200.experiments.rl.cast_linear import CastLinear
+    from torchtitan_b200.models import get_model_spec
+
+    spec = get_model_spec("llama3", "debugmodel")
+    apply_converters(spec.model, ["lm_head_cast"])
+    model = spec.model.build()
+    model.init_states(seed=0)
+    casts = [n for n, x in model.named_modules() if isinstance(x, CastLinear)]
+    assert casts == ["lm_head"]
+    ref = model(torch.tensor([1, 2, 3]))
+    low = model.bfloat16()(torch.tensor([1, 2, 3]))
+    assert low.dtype == torch.float32 and model.lm_head.weight.dtype == torch.bfloat16
+    assert torch.allclose(low, ref, atol=0.15)
+    with pytest.raises(ValueError, match="lm_head"):
+        apply_converters(get_model_spec("llama3", "debugmodel").model.layers[0], ["lm_head_cast"])

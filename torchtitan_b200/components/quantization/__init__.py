@@ -18,12 +18,14 @@ def _registry():
     from .grouped import quantize_experts
     from .nvfp4 import nvfp4_converter
 
-    return {"mxfp8": mxfp8_converter, "float8": float8_converter, "lora": lora_converter, "nvfp4": nvfp4_converter,
+    from torchtitan_b200.experiments.rl.cast_linear import lm_head_cast_converter
+
+    return {"lm_head_cast": lm_head_cast_converter, "mxfp8": mxfp8_converter, "float8": float8_converter, "lora": lora_converter, "nvfp4": nvfp4_converter,
             "mxfp8_experts": lambda cfg, arg, job: quantize_experts(cfg, "mxfp8"),
             "float8_experts": lambda cfg, arg, job: quantize_experts(cfg, "float8_rowwise")}
 
 
-CONVERTERS = ("mxfp8", "float8", "nvfp4", "mxfp8_experts", "float8_experts", "lora")
+CONVERTERS = ("mxfp8", "float8", "nvfp4", "mxfp8_experts", "float8_experts", "lora", "lm_head_cast")
 
 
 def has_quantization(names) -> bool:

@@ -70,6 +70,10 @@ class AsyncLoopConfig(Configurable.Config):
     target_offpolicy_steps: int = 3
     window_fraction: float | None = 0.3
     """Share of the buffer the batcher may look ahead past an unfinished head; None: strict FIFO."""
+    max_consecutive_untrainable_groups: int | None = 4096
+    """Stop the job when this many prompt groups in a row yield nothing to train on (generation keeps failing, or
+    every group's rewards are all equal and such groups are dropped: a policy that always or never succeeds gives no
+    signal, and the trainer would wait forever).  None: keep waiting."""
     training_sample_builder: TrainingSampleBuilder.Config = field(default_factory=TrainingSampleBuilder.Config)
     batcher: Batcher.Config = field(default_factory=Batcher.Config)
     validation: ValidationConfig = field(default_factory=ValidationConfig)
@@ -105,8 +109,9 @@ class WeightSyncManager:
     before the next optimizer step (which overwrites the weights being read), the pull before the next push."""
 
     def __init__(self, *, trainer: PolicyTrainer, router: InterGeneratorRouter, buffer: RolloutGroupWorkBuffer,
-                 num_prompts_per_train_step: int):
+                 num_prompts_per_train_step: int, call_trainer=None):
         self._trainer, self._router, self._buffer, self._n = trainer, router, buffer, num_prompts_per_train_step
+        self._call = call_trainer or (lambda fn, *a: asyncio.to_thread(fn, *a))
         self._push = self._pull = None
         self.last_push_s = self.last_pull_s = 0.0
 
@@ -130,7 +135,7 @@ class WeightSyncManager:
 
     async def _do_push(self) -> None:
         t0 = time.perf_counter()
-        await asyncio.to_thread(self._trainer.push_model_state_dict)
+        await self._call(self._trainer.push_model_state_dict)
         self.last_push_s = time.perf_counter() - t0
 
     async def _do_pull(self, version: int, push: asyncio.Task) -> None:
@@ -171,12 +176,16 @@ class AsyncController(Configurable):
         self.sampling = dataclasses.replace(config.sampling, stop_sequences=[*config.sampling.stop_sequences, *stops])
         self.start_step = trainer.policy_version
         self._buffer: RolloutGroupWorkBuffer | None = None
+        self._trainer_lock = asyncio.Lock()
 
     # -- pieces ------------------------------------------------------------------------------------------------
     async def _call_trainer(self, fn, *args):
-        if self.config.trainer_in_thread:
-            return await asyncio.to_thread(fn, *args)
-        return fn(*args)
+        """One trainer call at a time (the background weight push included): a multi-rank trainer announces each call
+        to its other ranks, and two announcements must not interleave."""
+        async with self._trainer_lock:
+            if self.config.trainer_in_thread:
+                return await asyncio.to_thread(fn, *args)
+            return fn(*args)
 
     async def validate(self, *, step: int) -> list[m.Metric]:
         n = self.config.async_loop.validation.num_samples
@@ -224,10 +233,20 @@ class AsyncController(Configurable):
 
     async def _batcher_loop(self, buffer: RolloutGroupWorkBuffer, builder: TrainingSampleBuilder, batcher: Batcher,
                             queue: "asyncio.Queue[TrainingBatch | None]") -> None:
+        barren = 0
         while (group := await buffer.take_finalized()) is not None:
             samples = builder.build_from_group(rollout_group=group)
             if not samples.training_samples:
                 await buffer.release_active_groups(1, reason="untrainable_group")    # nothing of it will be trained
+                barren += 1
+                limit = self.config.async_loop.max_consecutive_untrainable_groups
+                if limit is not None and barren >= limit:
+                    raise RuntimeError(f"{barren} prompt groups in a row gave nothing to train on; stopping")
+                if barren % 32 == 0:
+                    logger.warning(f"{barren} prompt groups in a row gave nothing to train on (failed, empty, or all "
+                                   "rewards equal with drop_zero_std_reward_groups): the trainer is waiting")
+            else:
+                barren = 0
             batch = await asyncio.to_thread(batcher.add_training_samples, training_sample_group=samples)
             if batch is not None:
                 await queue.put(batch)
@@ -277,7 +296,7 @@ class AsyncController(Configurable):
         logger.info(f"async RL: {lc.max_active_rollout_groups} active groups, window {lc.window_size}, "
                     f"policy age <= {lc.max_offpolicy_steps}")
         sync = WeightSyncManager(trainer=self.trainer, router=self.router, buffer=buffer,
-                                 num_prompts_per_train_step=lc.num_prompts_per_train_step)
+                                 num_prompts_per_train_step=lc.num_prompts_per_train_step, call_trainer=self._call_trainer)
         batcher = lc.batcher.build(num_prompts_per_train_step=lc.num_prompts_per_train_step, dp_degree=self.dp_degree,
                                    pad_id=self.renderer.eos_token_id)
         queue: asyncio.Queue = asyncio.Queue(maxsize=1)

@@ -1,0 +1,207 @@
+"""One RL job: the training ranks, the generators and the controller, built from one config.
+
+``RLJob.Config`` holds a full ``Trainer.Config`` (model, parallelism, optimizer, schedule, checkpointing: the
+policy is trained by the same engine as pre-training, built through ``ForgeEngine``), the generation engine's
+config and the controller's.  Placement:
+
+* ``share_weights = True`` (default): one generation engine on the training model object itself.  In the resident
+  FSDP layout every rank holds the full bf16 weights, refreshed by the optimizer kernel, so nothing is copied for a
+  "weight sync"; generation and training alternate on the device.
+* ``share_weights = False``: ``num_generators`` engines, each with its own copy of the model on
+  ``generator_devices[i]`` (other GPUs of the node), running in worker threads while the trainer trains; a pull
+  copies the trainer's parameters device to device.
+
+With more than one training rank the controller lives on rank 0; it announces every trainer call to the other
+ranks (``_LeaderTrainer`` / ``follow``), which run the same call on their shard of the microbatch grid.
+
+Parity: torchtitan/experiments/rl/train.py:46-314 and controller.py:261-520 (setup: Monarch proc meshes for the
+trainer and each generator, TorchStore for the weights).
+"""
+
+from __future__ import annotations
+
+import asyncio
+import os
+from dataclasses import dataclass, field
+from typing import Any
+
+import torch
+import torch.distributed as dist
+
+from torchtitan_b200.config import Configurable
+from torchtitan_b200.trainer import Trainer
+from torchtitan_b200.utils.logging import logger
+
+from .async_controller import AsyncController
+from .engine import GenerationEngine
+from .losses import PolicyLoss
+from .policy_trainer import PolicyTrainer
+
+__all__ = ["RLJob"]
+
+
+def _announce(msg: Any) -> Any:
+    box = [msg]
+    dist.broadcast_object_list(box, src=0)
+    return box[0]
+
+
+class _LeaderTrainer(PolicyTrainer):
+    """Rank 0's trainer: every call is first announced to the follower ranks, which then join its collectives."""
+
+    def forward_backward(self, row, n):
+        _announce(("forward_backward", row, n))
+        return super().forward_backward(row, n)
+
+    def optim_step(self):
+        _announce(("optim_step",))
+        return super().optim_step()
+
+    def push_model_state_dict(self):
+        _announce(("push",))
+        return super().push_model_state_dict()
+
+    def save(self, forge, step, last):
+        _announce(("save", step, last))
+        forge.step = step
+        forge.save(step, last_step=last)
+
+
+def follow(trainer: PolicyTrainer, forge) -> None:
+    """The loop of every training rank but 0."""
+    while True:
+        op, *args = _announce(None)
+        if op == "stop":
+            return
+        if op == "forward_backward":
+            trainer.forward_backward(*args)
+        elif op == "optim_step":
+            trainer.optim_step()
+        elif op == "push":
+            trainer.push_model_state_dict()
+        elif op == "save":
+            forge.step = args[0]
+            forge.save(args[0], last_step=args[1])
+
+
+class RLJob(Configurable):
+    @dataclass(kw_only=True, slots=True)
+    class Config(Configurable.Config):
+        trainer: Trainer.Config
+        controller: AsyncController.Config
+        generator: GenerationEngine.Config = field(default_factory=GenerationEngine.Config)
+        num_generators: int = 1
+        share_weights: bool = True
+        generator_devices: list[str] = field(default_factory=list)
+        """Devices of the generator replicas when they hold their own weights (default: the trainer's device)."""
+        ratio_clip_low: float = 0.2
+        ratio_clip_high: float = 0.2
+        """Larger than ``ratio_clip_low``: DAPO's clip-higher."""
+        byte_tokenizer: bool = False
+        """Use the built-in byte tokenizer instead of the files under ``trainer.hf_assets_path``."""
+
+        def validate(self) -> None:
+            t = self.trainer
+            if self.num_generators < 1:
+                raise ValueError(f"num_generators must be >= 1, got {self.num_generators}")
+            if self.share_weights and self.num_generators != 1:
+                raise ValueError("share_weights runs exactly one generator on the training model")
+            if self.share_weights and t.parallelism.fsdp_reshard_after_forward == "always":
+                raise ValueError("share_weights needs the resident parameter layout (the generator reads full weights)")
+            if t.parallelism.pipeline_parallel_degree > 1 or t.parallelism.context_parallel_degree > 1:
+                raise ValueError("the RL trainer supports data and tensor parallelism")
+            b = self.controller.async_loop.batcher.batch
+            sp = t.parallelism.tensor_parallel_degree if t.parallelism.enable_sequence_parallel else 1
+            if b.seq_len * b.local_batch_size % max(sp, 1):
+                raise ValueError(f"tokens per microbatch ({b.seq_len * b.local_batch_size}) must divide by the "
+                                 f"sequence-parallel degree {sp}")
+            # the batcher's grid decides the training shapes
+            t.training.max_context_length = b.seq_len
+            t.training.num_tokens_per_microbatch_per_dp_rank = b.seq_len * b.local_batch_size
+            t.training.num_tokens_per_train_step = -1
+            t.dataloader.dataset = "synthetic"
+            if self.share_weights:
+                self.generator.threaded = False
+                self.controller.trainer_in_thread = False
+            if callable(getattr(t, "validate", None)):
+                t.validate()
+
+    def __init__(self, config: Config, **_):
+        from torchtitan_b200.experiments.forge import ForgeEngine
+
+        self.config = config
+        self.forge = forge = ForgeEngine(config.trainer)
+        self.rank = dist.get_rank() if dist.is_initialized() else 0
+        cls = _LeaderTrainer if dist.is_initialized() and dist.get_world_size() > 1 and self.rank == 0 else PolicyTrainer
+        self.trainer = cls(model=forge.model, engine=forge.engines[0], optimizers=forge.optimizers,
+                           lr_schedulers=forge.lr_schedulers, pdims=forge.pdims, max_norm=config.trainer.training.max_norm,
+                           loss=PolicyLoss(config.ratio_clip_low, config.ratio_clip_high))
+        if config.trainer.checkpoint.enable and forge.load():
+            self.trainer.policy_version = forge.step
+        self.controller = None
+        if self.rank != 0:
+            return
+        if config.byte_tokenizer or not os.path.isdir(config.trainer.hf_assets_path):
+            from torchtitan_b200.components.tokenizer import ByteTokenizer
+
+            tokenizer = ByteTokenizer()
+        else:
+            from torchtitan_b200.components.tokenizer import HuggingFaceTokenizer
+
+            tokenizer = HuggingFaceTokenizer(tokenizer_path=config.trainer.hf_assets_path)
+        if tokenizer.get_vocab_size() > forge.model_config.vocab_size:
+            raise ValueError(f"the tokenizer has {tokenizer.get_vocab_size()} tokens, the model {forge.model_config.vocab_size}")
+        self.generators = self._build_generators(tokenizer)
+        self.controller = AsyncController(config.controller, trainer=self.trainer, generators=self.generators,
+                                          tokenizer=tokenizer, dp_degree=forge.pdims.dp_degree)
+        self.controller.start_step = self.trainer.policy_version
+
+    def _build_generators(self, tokenizer) -> list[GenerationEngine]:
+        c, forge = self.config, self.forge
+        eos = int(tokenizer.eos_id) if tokenizer.eos_id is not None else None
+        if c.share_weights:
+            return [c.generator.build(model=forge.model, eos_id=eos)]
+        out = []
+        for i in range(c.num_generators):
+            dev = torch.device(c.generator_devices[i] if i < len(c.generator_devices) else forge.device)
+            copy = forge.model_config.build().to(device=dev, dtype=next(forge.model.parameters()).dtype)
+            out.append(c.generator.build(model=copy, eos_id=eos, weight_source=self._copy_weights))
+            self._copy_weights(out[-1])
+        return out
+
+    @torch.no_grad()
+    def _copy_weights(self, engine: GenerationEngine) -> None:
+        src = dict(self.forge.model.named_parameters())
+        for name, p in engine.model.named_parameters():
+            p.copy_(src[name].detach().to(p.device, p.dtype), non_blocking=True)
+        for name, b in engine.model.named_buffers():
+            s = dict(self.forge.model.named_buffers()).get(name)
+            if s is not None and s.shape == b.shape:
+                b.copy_(s.to(b.device, b.dtype))
+
+    def run(self) -> dict | None:
+        """Rank 0 returns the validation summaries; the other ranks return None when the leader says stop."""
+        if self.rank != 0:
+            follow(self.trainer, self.forge)
+            return None
+        try:
+            return asyncio.run(self._run())
+        finally:
+            if isinstance(self.trainer, _LeaderTrainer):
+                _announce(("stop",))
+
+    async def _run(self) -> dict:
+        out = await self.controller.run()
+        if self.config.trainer.checkpoint.enable:
+            step = self.trainer.policy_version
+            if isinstance(self.trainer, _LeaderTrainer):
+                self.trainer.save(self.forge, step, True)
+            else:
+                self.forge.step = step
+                self.forge.save(step, last_step=True)
+        await self.controller.close()
+        logger.info("RL job finished")
+        return out
+
+    def close(self) -> None:
+        self.forge.close()
