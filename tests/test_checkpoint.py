@@ -200,3 +200,39 @@ def test_torch_save_storage_resumes_and_reshards(tmp_path):
     run_distributed(_train, 1, str(tmp_path / "d"), 3, one_dcp, skip)
     x, y = dict(torch.load(one_ts)), dict(torch.load(one_dcp))
     assert list(x) == [3] and abs(x[3] - y[3]) < 1e-6, (x, y)
+
+
+def test_filesystem_helpers_local_and_fsspec(tmp_path):
+    from torchtitan_b200.utils import filesystem as fsys
+
+    for root in (str(tmp_path / "loc"), "memory://fs_helpers_test"):
+        assert fsys.is_remote(root) == root.startswith("memory://")
+        assert fsys.listdir(root) == [] and not fsys.exists(root)
+        d = fsys.join(root, "step-3")
+        fsys.makedirs(d)
+        with fsys.open_file(fsys.join(d, ".metadata"), "w") as f:
+            f.write("x")
+        assert fsys.isdir(d) and fsys.isfile(fsys.join(d, ".metadata")) and fsys.listdir(root) == ["step-3"]
+        assert fsys.listdir(d) == [".metadata"]
+        fsys.rmtree(d)
+        assert not fsys.exists(d)
+    assert not fsys.is_remote("file:///tmp/x") and not fsys.is_remote("C:/x") and fsys.is_remote("s3://b/k")
+    assert fsys.join("s3://b/run/", "/checkpoint/", "step-1") == "s3://b/run/checkpoint/step-1"
+
+
+def _train_remote(rank, world, folder, steps, out_path):
+    _train(rank, world, folder, steps, out_path, ("--checkpoint.folder", "memory://ckpt_remote_test", "--checkpoint.keep_latest_k", "2"))
+    from torchtitan_b200.utils import filesystem as fsys
+
+    if rank == 0:
+        torch.save(fsys.listdir("memory://ckpt_remote_test"), out_path + ".ls")
+
+
+def test_checkpoints_on_an_fsspec_uri(tmp_path):
+    """``checkpoint.folder`` as an fsspec URI (the in-process ``memory://`` filesystem here): DCP writes through its
+    fsspec storage, step discovery and the retention policy work on the URI."""
+    out = str(tmp_path / "o.pt")
+    run_distributed(_train_remote, 1, str(tmp_path / "r"), 6, out)
+    kept = torch.load(out + ".ls")
+    assert "step-6" in kept and "step-2" not in kept and len([k for k in kept if k.startswith("step-")]) <= 3, kept
+    assert not os.path.exists(tmp_path / "r" / "checkpoint")

@@ -98,3 +98,65 @@ def test_qwen3_5_vision_language_matches_transformers():
     assert hf["model.visual.patch_embed.proj.weight"].dim() == 5 and "model.visual.blocks.0.attn.qkv.weight" in hf
     back = ad.from_hf(hf)
     assert set(back) == set(vis) and all(torch.equal(back[k], vis[k]) for k in vis)
+
+
+def test_media_fit_to_grid_image_and_video(tmp_path):
+    """Sizes land on the patch grid inside the pixel budget; an image file and a video file written here decode, and a
+    JSONL sample with text, an image and a video becomes placeholder runs of the right lengths."""
+    import json
+
+    import numpy as np
+
+    from torchtitan_b200.components.data import media
+
+    for (h, w) in [(480, 640), (33, 1000), (2000, 3000), (20, 20)]:
+        H, W = media.fit_to_grid(h, w, factor=28, min_pixels=56 * 56, max_pixels=512 * 512)
+        assert H % 28 == 0 and W % 28 == 0 and 56 * 56 <= H * W <= 512 * 512 + 28 * 28 * 4
+    assert media.fit_to_grid(448, 448, factor=28, min_pixels=1, max_pixels=10 ** 9) == (448, 448)
+    with pytest.raises(ValueError):
+        media.fit_to_grid(1, 1000, factor=28, min_pixels=1, max_pixels=10 ** 6)
+    assert media.sample_frame_indices(100, 25.0, fps=2.0, min_frames=4, max_frames=768) == [0, 14, 28, 42, 57, 71, 85, 99]
+    assert media.sample_frame_indices(3, 30.0, min_frames=4) == [0, 1, 2]
+    assert len(media.sample_frame_indices(10000, 25.0, fps=2.0, max_frames=16)) == 16
+
+    from PIL import Image
+
+    rng = np.random.default_rng(0)
+    img_path = str(tmp_path / "a.png")
+    Image.fromarray(rng.integers(0, 255, (70, 90, 3), dtype=np.uint8)).save(img_path)
+    img = media.load_image(img_path)
+    assert img.shape == (3, 70, 90) and img.dtype == torch.uint8
+    out = media.process_image(img, patch_size=4, merge_size=2, min_pixels=64, max_pixels=48 * 48)
+    assert out.dtype == torch.float32 and out.shape[1] % 8 == 0 and out.shape[2] % 8 == 0 and out.abs().max() <= 1.0 + 1e-5
+
+    cv2 = pytest.importorskip("cv2")
+    vid_path = str(tmp_path / "v.avi")
+    wr = cv2.VideoWriter(vid_path, cv2.VideoWriter_fourcc(*"MJPG"), 10.0, (64, 48))
+    if not wr.isOpened():
+        pytest.skip("no MJPG encoder in this OpenCV build")
+    for i in range(20):
+        wr.write(np.full((48, 64, 3), i * 10, dtype=np.uint8))
+    wr.release()
+    clip = media.load_video(vid_path, fps=2.0, min_frames=4, max_frames=8)
+    assert clip is not None and clip.shape == (4, 48, 64, 3)          # 2 s at 2 fps, raised to the minimum of 4 frames
+    assert clip[0].float().mean() < clip[-1].float().mean()            # frames come in order
+    frames = media.process_video(clip, patch_size=4, merge_size=2, min_pixels=64, max_pixels=32 * 32)
+    assert frames.shape[0] == 4 and frames.shape[1] == 3 and frames.shape[2] % 8 == 0 and frames.shape[3] % 8 == 0
+    assert media.load_video(str(tmp_path / "missing.mp4")) is None
+
+    from torchtitan_b200.components.data import BaseDataLoader
+    from torchtitan_b200.components.data.multimodal import MultimodalDataLoader
+    from torchtitan_b200.components.tokenizer import ByteTokenizer
+
+    jl = tmp_path / "mm.jsonl"
+    jl.write_text(json.dumps({"segments": [{"text": "look:"}, {"image": img_path}, {"text": "then"},
+                                           {"video": vid_path, "max_frames": 4, "max_pixels": 32 * 32}]}) + "\n")
+    dl = MultimodalDataLoader(BaseDataLoader.Config(dataset="mm_jsonl", dataset_path=str(jl)), num_tokens_per_batch=4096,
+                              max_context_length=4096, tokenizer=ByteTokenizer(), patch_size=4, spatial_merge=2,
+                              image_token_id=300)
+    batch, labels = next(iter(dl))
+    grids = batch["grid_hw"]
+    assert grids.shape[0] >= 5                                          # one image and four frames (per packed sample)
+    n_slots = int((batch["input"] == 300).sum()) + int(batch["input"][0] == 300)
+    assert n_slots >= int((grids[:5, 0] * grids[:5, 1] // 4).sum()) - 1
+    assert batch["pixel_patches"].shape[1] == 3 * 4 * 4

@@ -29,7 +29,6 @@ import enum
 import os
 import queue
 import re
-import shutil
 import threading
 import time
 from dataclasses import dataclass, field
@@ -49,6 +48,7 @@ from torch.distributed.checkpoint.planner_helpers import create_read_items_for_c
 
 from torchtitan_b200.config import Configurable
 from torchtitan_b200.models.common.module import iter_checkpoint_slices
+from torchtitan_b200.utils import filesystem as fsys
 from torchtitan_b200.utils import structured_logger as sl
 from torchtitan_b200.utils.logging import logger
 
@@ -386,7 +386,7 @@ def _purge_worker(q: "queue.Queue[str | None]") -> None:
             return
         try:
             t = time.monotonic()
-            shutil.rmtree(path, ignore_errors=True)
+            fsys.rmtree(path, ignore_errors=True)
             logger.info(f"Checkpointer deleted {path} in {time.monotonic() - t:.2f}s")
         except Exception as e:  # the purge thread must survive failed deletes
             logger.warning(f"failed to delete {path}: {e}")
@@ -427,7 +427,8 @@ class CheckpointManager(Configurable):
         self.trainer = trainer
         self.pdims = pdims
         self.enable = config.enable
-        self.folder = os.path.join(dump_folder, config.folder)
+        # an fsspec URI as checkpoint.folder (s3://..., gs://..., memory://...) is used as it is
+        self.folder = config.folder if fsys.is_remote(config.folder) else fsys.join(dump_folder, config.folder)
         self.async_mode = AsyncMode(config.async_mode)
         self._bg: threading.Thread | None = None
         self._bg_error: BaseException | None = None
@@ -484,21 +485,18 @@ class CheckpointManager(Configurable):
 
     # -- paths -----------------------------------------------------------------
     def _step_dir(self, step: int) -> str:
-        return os.path.join(self.folder, f"step-{step}")
+        return fsys.join(self.folder, f"step-{step}")
 
     def _find_steps(self, folder: str | None = None) -> list[int]:
         folder = folder or self.folder
-        if not os.path.isdir(folder):
-            return []
         steps = []
-        for name in os.listdir(folder):
+        for name in fsys.listdir(folder):
             m = re.fullmatch(r"step-(\d+)", name)
             if not m:
                 continue
-            d = os.path.join(folder, name)
-            if os.path.exists(os.path.join(d, ".metadata")) or os.path.exists(
-                    os.path.join(d, "model.safetensors.index.json")) or any(
-                    f.endswith(".safetensors") for f in os.listdir(d)):
+            inside = fsys.listdir(fsys.join(folder, name))
+            if ".metadata" in inside or "model.safetensors.index.json" in inside or any(
+                    f.endswith(".safetensors") for f in inside):
                 steps.append(int(m.group(1)))
         return sorted(steps)
 
@@ -726,16 +724,16 @@ class CheckpointManager(Configurable):
                 raise FileNotFoundError(f"checkpoint.load_step={step} not found in {self.folder} (have {steps})")
             path = self._step_dir(step)
             model_only = step == 0
-            in_hf = not os.path.exists(os.path.join(path, ".metadata"))
+            in_hf = not fsys.exists(fsys.join(path, ".metadata"))
         elif c.initial_load_path:
             path = c.initial_load_path
-            if not os.path.isdir(path):
+            if not fsys.isdir(path):
                 raise FileNotFoundError(f"checkpoint.initial_load_path is invalid: {path}")
             model_only = c.initial_load_model_only
             in_hf = c.initial_load_in_hf
             sub = self._find_steps(path)
-            if sub and not os.path.exists(os.path.join(path, ".metadata")) and not in_hf:
-                path = os.path.join(path, f"step-{sub[-1]}")
+            if sub and not fsys.exists(fsys.join(path, ".metadata")) and not in_hf:
+                path = fsys.join(path, f"step-{sub[-1]}")
         elif c.initial_load_in_hf:
             path = self.trainer.config.hf_assets_path
             model_only = True

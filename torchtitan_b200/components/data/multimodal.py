@@ -11,7 +11,8 @@ Batch: ``({"input", "positions", "pixel_patches" [N, C p p], "grid_hw" [I, 2]}, 
 
 ``dataset = "synthetic_mm"`` draws random text and images, a pure function of
 ``(seed, dp rank, batch index)``.  ``dataset = "mm_jsonl"`` reads lines
-``{"segments": [{"text": ...} | {"image": "<path to .pt / .npy tensor>"}]}``.
+``{"segments": [{"text": ...} | {"image": "<.png / .jpg / ... or a .pt / .npy tensor>"} | {"video": "<file>",
+"fps": 2.0, "max_frames": 32}]}`` (``components/data/media.py`` decodes, resizes to the patch grid and normalises).
 Parity: torchtitan/hf_datasets/multimodal/mm_datasets.py and mm_collator.py (interleaved
 samples, patchification, placeholder expansion, padding to the batch length).
 """
@@ -25,6 +26,7 @@ import torch
 
 from torchtitan_b200.ops.reference import IGNORE_INDEX
 
+from . import media
 from .loader import BaseDataLoader
 
 __all__ = ["patchify", "MultimodalCollator", "MultimodalDataLoader"]
@@ -135,18 +137,30 @@ class MultimodalDataLoader(BaseDataLoader):
         segs: list = []
         for s in rec["segments"]:
             if "image" in s:
-                path = s["image"]
-                if path.endswith(".npy"):
-                    import numpy as np
-
-                    segs.append(torch.from_numpy(np.load(path)).float())
-                else:
-                    segs.append(torch.load(path).float())
+                segs.append(self._image(media.load_image(s["image"])))
+            elif "video" in s:
+                # every sampled frame becomes one image segment (its own patch grid); a tower with temporal patches
+                # repeats a single frame over the temporal extent, as for still images
+                clip = media.load_video(s["video"], fps=s.get("fps", 2.0), min_frames=s.get("min_frames", 4),
+                                        max_frames=s.get("max_frames", 32))
+                if clip is None:
+                    continue
+                q = self.collator.patch
+                frames = media.process_video(clip, patch_size=q, merge_size=self.collator.merge,
+                                             max_pixels=s.get("max_pixels", 256 * 256))
+                segs += list(frames)
             else:
                 if self.tokenizer is None:
                     raise ValueError("text segments need a tokenizer")
                 segs.append(self.tokenizer.encode(s["text"], add_bos=not segs, add_eos=False))
         return segs
+
+    def _image(self, image: torch.Tensor) -> torch.Tensor:
+        """Saved float tensors are taken as already prepared; decoded (uint8) images are fitted to the patch grid
+        and normalised."""
+        if image.dtype != torch.uint8:
+            return image.float()
+        return media.process_image(image, patch_size=self.collator.patch, merge_size=self.collator.merge)
 
     def _make(self, idx: int):
         g = torch.Generator()

@@ -17,7 +17,7 @@ import dataclasses
 from dataclasses import dataclass, fields, is_dataclass
 from typing import Any, Callable, ClassVar, Iterator
 
-__all__ = ["Configurable", "ConfigRef", "config_to_dict"]
+__all__ = ["Configurable", "ConfigRef", "config_to_dict", "Function"]
 
 
 def config_to_dict(value: Any) -> Any:
@@ -147,3 +147,19 @@ def replace_config(cfg, **changes):
 
 
 Factory = Callable[..., Any]
+
+
+class Function(Configurable):
+    """Any callable as a config node: ``Function.Config(fn=...).build()`` is itself callable.  For config fields
+    whose value is computed when the owner is built, e.g. a per-layer initialiser that depends on the depth
+    (parity: torchtitan/config/function.py:16-40)."""
+
+    @dataclass(kw_only=True, slots=True)
+    class Config(Configurable.Config):
+        fn: Callable[..., Any]
+
+    def __init__(self, config: "Function.Config", **_: Any):
+        self.fn = config.fn
+
+    def __call__(self, *args: Any, **kwargs: Any) -> Any:
+        return self.fn(*args, **kwargs)
