@@ -538,3 +538,75 @@ def test_fragment_llm_covers_every_parameter_once():
     frags = fragment_llm(model, 3)
     ids = [id(p) for f in frags for p in f]
     assert len(ids) == len(set(ids)) == len(list(model.parameters())) and len(frags) >= 2
+
+
+@pytest.mark.parametrize("family", ["qwen3_moe", "deepseek_v3"])
+def test_hf_backend_native_moe_replacement(family):
+    """The HF model with its expert blocks swapped for the native MoE layer gives the HF model's logits (softmax
+    top-k with renormalisation; sigmoid routing with groups, selection bias, scaling and shared experts), trains,
+    and the trained weights go back into the HF blocks."""
+    transformers = pytest.importorskip("transformers")
+    from torchtitan_b200.experiments.transformers_backend import HFCausalLM, hf_train_steps
+    from torchtitan_b200.experiments.transformers_backend.moe_replacement import (NativeMoEAdapter, probe_hf_moe_block,
+                                                                                  restore_hf_moe_state, swap_native_moe)
+
+    if family == "qwen3_moe":
+        cfg = transformers.Qwen3MoeConfig(vocab_size=128, hidden_size=32, intermediate_size=64, moe_intermediate_size=16,
+                                          num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2, head_dim=8,
+                                          num_experts=8, num_experts_per_tok=2, norm_topk_prob=True, decoder_sparse_step=1,
+                                          mlp_only_layers=[], max_position_embeddings=64)
+    else:
+        cfg = transformers.DeepseekV3Config(vocab_size=128, hidden_size=32, intermediate_size=64, moe_intermediate_size=16,
+                                            num_hidden_layers=3, num_attention_heads=4, num_key_value_heads=4,
+                                            n_routed_experts=8, n_shared_experts=2, num_experts_per_tok=3, n_group=4,
+                                            topk_group=2, routed_scaling_factor=2.5, norm_topk_prob=True,
+                                            first_k_dense_replace=1, q_lora_rank=16, kv_lora_rank=16, qk_nope_head_dim=8,
+                                            qk_rope_head_dim=8, v_head_dim=8, max_position_embeddings=64)
+    torch.manual_seed(0)
+    model = HFCausalLM(cfg)
+    with torch.no_grad():
+        for p in model.parameters():
+            if p.dim() >= 2:
+                p.normal_(0, 0.2)                               # the default init leaves routing nearly uniform
+        for name, b in model.named_buffers():
+            if name.endswith("e_score_correction_bias"):
+                b.normal_(0, 0.1)
+    toks = torch.randint(0, 128, (41,))
+    pos = torch.cat([torch.arange(25), torch.arange(16)])
+    with torch.no_grad():
+        want = model(toks, pos)
+    n_moe = sum(1 for layer in model.hf.model.layers if hasattr(layer.mlp, "experts"))
+    info = probe_hf_moe_block(next(layer.mlp for layer in model.hf.model.layers if hasattr(layer.mlp, "experts")))
+    assert info["num_experts"] == 8 and info["score_func"] == ("softmax" if family == "qwen3_moe" else "sigmoid")
+    assert swap_native_moe(model) == n_moe > 0 and swap_native_moe(model) == 0
+    assert sum(isinstance(layer.mlp, NativeMoEAdapter) for layer in model.hf.model.layers) == n_moe
+    with torch.no_grad():
+        got = model(toks, pos)
+    assert torch.allclose(got, want, atol=2e-4, rtol=1e-4), float((got - want).abs().max())
+    batch = (toks[:-1], pos[:-1], toks[1:])
+    losses = hf_train_steps(model, [batch] * 6, lr=3e-3)
+    assert losses[-1] < losses[0]
+    with torch.no_grad():
+        trained = model(toks, pos)
+    assert restore_hf_moe_state(model) == n_moe
+    assert not any(isinstance(layer.mlp, NativeMoEAdapter) for layer in model.hf.model.layers)
+    with torch.no_grad():
+        back = model(toks, pos)
+    assert torch.allclose(back, trained, atol=2e-4, rtol=1e-4) and not torch.allclose(back, want, atol=1e-3)
+
+
+def test_ft_config_registry_builds_the_fault_tolerant_trainer(tmp_path):
+    from torchtitan_b200.config import ConfigManager
+    from torchtitan_b200.experiments.ft import config_registry as reg
+
+    assert reg.llama3_ft_debugmodel_diloco().fault_tolerance.semi_sync_method == "diloco"
+    cfg = ConfigManager().parse_args([
+        "--module", "ft", "--config", "llama3_ft_debugmodel", "--fault_tolerance.replica_id", "1",
+        "--fault_tolerance.no-enable", "--training.steps", "1", "--training.num_tokens_per_microbatch_per_dp_rank", "64",
+        "--training.max_context_length", "64", "--training.mixed_precision_param", "float32", "--dump_folder", str(tmp_path),
+        "--debug.no-enable_structured_logging", "--checkpoint.no-enable"])
+    assert cfg.fault_tolerance.replica_id == 1 and cfg.fault_tolerance.group_size == 2 and cfg.model.flavor == "debugmodel"
+    t = cfg.build()
+    assert type(t).__name__ == "FaultTolerantTrainer" and t.manager is None       # disabled: a plain trainer
+    t.train()
+    t.close()

@@ -21,7 +21,7 @@ involved.
 from __future__ import annotations
 
 import os
-from dataclasses import dataclass
+from dataclasses import dataclass, field
 from datetime import timedelta
 
 import torch
@@ -120,9 +120,14 @@ def fragment_llm(model, num_fragments: int) -> list[list[torch.nn.Parameter]]:
 
 
 class FaultTolerantTrainer(Trainer):
-    def __init__(self, config: "Trainer.Config", *, fault_tolerance: FaultToleranceConfig, store=None, **kw):
+    @dataclass(kw_only=True, slots=True)
+    class Config(Trainer.Config):
+        """The trainer's config plus ``--fault_tolerance.*`` (parity: torchft/config/job_config.py:15-87)."""
+        fault_tolerance: FaultToleranceConfig = field(default_factory=FaultToleranceConfig)
+
+    def __init__(self, config: "Trainer.Config", *, fault_tolerance: FaultToleranceConfig | None = None, store=None, **kw):
         super().__init__(config, **kw)
-        ft = fault_tolerance
+        ft = fault_tolerance or getattr(config, "fault_tolerance", None) or FaultToleranceConfig()
         self.ft = ft
         self.manager = None
         self.semi_sync: list = []
