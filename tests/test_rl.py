@@ -472,6 +472,24 @@ def test_engine_batches_sequences_and_matches_single_sequence_decoding():
     run(go())
 
 
+def test_engine_step_failure_fails_the_requests_in_flight_and_the_engine_stays_up():
+    from torchtitan_b200.experiments.rl import GenerationEngine, SamplingConfig
+
+    _, model = _tiny_llama()
+    greedy = SamplingConfig(temperature=0.0, max_tokens=3)
+
+    async def go():
+        for threaded in (False, True):
+            eng = GenerationEngine(GenerationEngine.Config(threaded=threaded), model=model)
+            with pytest.raises(RuntimeError, match="generation failed"):
+                await asyncio.wait_for(eng.generate([5000], request_id="bad", sampling_config=greedy), timeout=20)   # id outside the vocabulary
+            ok = await asyncio.wait_for(eng.generate([5, 6], request_id="good", sampling_config=greedy), timeout=20)
+            assert len(ok.token_ids) == 3
+            await eng.close()
+
+    run(go())
+
+
 def test_engine_in_a_thread_serves_concurrent_requests():
     from torchtitan_b200.experiments.rl import GenerationEngine, SamplingConfig
 

@@ -180,11 +180,25 @@ class GenerationEngine(Configurable):
                 if not busy:
                     await self._wake.wait()
                     continue
-            if self.config.threaded:
-                await asyncio.to_thread(self.step)
-            else:
-                self.step()
-                await asyncio.sleep(0)
+            try:
+                if self.config.threaded:
+                    await asyncio.to_thread(self.step)
+                else:
+                    self.step()
+                    await asyncio.sleep(0)
+            except Exception as e:
+                # a failed forward leaves the caches of the sequences in flight in an unknown state: their requests
+                # fail with the error (instead of waiting forever), the engine stays up for new ones
+                logger.exception("generation engine step failed")
+                self._fail_inflight(e)
+
+    def _fail_inflight(self, error: Exception) -> None:
+        with self._lock:
+            hit, self._running = self._running, []
+        for seq in hit:
+            seq.cache = None
+            if not seq.future.done():
+                seq.future.set_exception(RuntimeError(f"{seq.request_id}: generation failed: {error!r}"))
 
     def _apply_pulls(self) -> None:
         with self._lock:
