@@ -778,3 +778,39 @@ def test_lm_head_cast_converter_keeps_logits_in_fp32():
     assert torch.allclose(low, ref, atol=0.15)
     with pytest.raises(ValueError, match="lm_head"):
         apply_converters(get_model_spec("llama3", "debugmodel").model.layers[0], ["lm_head_cast"])
+
+
+def test_generate_cli_and_hf_weight_loading(tmp_path):
+    """``load_hf_into`` fills a built model from a Hugging Face folder through the adapter, and the stand-alone
+    generator of a registered job decodes several samples of one prompt together."""
+    from safetensors.torch import save_file
+
+    from torchtitan_b200.experiments.rl.generate import generate
+    from torchtitan_b200.models import get_model_spec
+    from torchtitan_b200.models.common.module import iter_checkpoint_slices
+    from torchtitan_b200.scripts.convert_hf import load_hf_into
+
+    spec = get_model_spec("llama3", "debugmodel")
+    src = spec.model.build()
+    src.init_states(seed=5)
+    fused = dict(iter_checkpoint_slices(src))
+    native = {}
+    for k, p in src.named_parameters():
+        for name, a, b in fused.get(k, [(k, None, None)]):
+            native[name] = (p if a is None else p[a:b]).detach().clone()
+    hf = spec.state_dict_adapter(spec.model, None).to_hf(native)
+    save_file({k: v.contiguous() for k, v in hf.items()}, str(tmp_path / "model.safetensors"))
+    dst = spec.model.build()
+    dst.init_states(seed=6)
+    assert load_hf_into(dst, spec, str(tmp_path)) == len(native)
+    for (k, a), (_, b) in zip(src.named_parameters(), dst.named_parameters()):
+        assert torch.equal(a, b), k
+    with pytest.raises(FileNotFoundError):
+        load_hf_into(dst, spec, str(tmp_path / "nowhere") if (tmp_path / "nowhere").mkdir() is None else "")
+    texts = generate(["--config", "rl_grpo_debug_alphabet_sort", "--max-tokens", "5", "--num-samples", "3", "--temperature", "0",
+                      "--device", "cpu"])
+    assert len(texts) == 3 and texts[0] == texts[1] == texts[2]              # greedy: the samples agree
+    assert generate(["--config", "rl_grpo_debug_alphabet_sort", "--max-tokens", "4", "--raw-prompt", "--prompt", "abc",
+                     "--seed", "1", "--device", "cpu"]) != []
+    with pytest.raises(ValueError):
+        generate(["--config", "no_such_job"])

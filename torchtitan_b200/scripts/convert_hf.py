@@ -60,6 +60,33 @@ def from_hf(args) -> None:
     print(f"wrote {len(state)} tensors to {args.out}")
 
 
+@torch.no_grad()
+def load_hf_into(model, spec, hf_dir: str) -> int:
+    """Copy the ``*.safetensors`` weights of a Hugging Face folder into an already built native ``model`` (any device
+    or dtype) through the family's state-dict adapter; returns the number of native tensors written."""
+    from safetensors import safe_open
+
+    adapter = spec.state_dict_adapter(spec.model, hf_dir)
+    hf = {}
+    files = sorted(f for f in os.listdir(hf_dir) if f.endswith(".safetensors"))
+    if not files:
+        raise FileNotFoundError(f"{hf_dir}: no .safetensors files")
+    for fn in files:
+        with safe_open(os.path.join(hf_dir, fn), framework="pt", device="cpu") as f:
+            for k in f.keys():
+                hf[k] = f.get_tensor(k)
+    native = adapter.from_hf(hf)
+    fused = dict(iter_checkpoint_slices(model))
+    n = 0
+    for k, p in model.named_parameters():
+        for name, a, b in fused.get(k, [(k, None, None)]):
+            if name not in native:
+                raise KeyError(f"{hf_dir}: the checkpoint lacks '{name}'")
+            (p if a is None else p[a:b]).copy_(native[name].to(p.device, p.dtype))
+            n += 1
+    return n
+
+
 def to_hf(args) -> None:
     import torch.distributed.checkpoint as dcp
     from safetensors.torch import save_file
