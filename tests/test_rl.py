@@ -814,3 +814,60 @@ def test_generate_cli_and_hf_weight_loading(tmp_path):
                      "--seed", "1", "--device", "cpu"]) != []
     with pytest.raises(ValueError):
         generate(["--config", "no_such_job"])
+
+
+def test_search_qa_example_tool_calls_end_to_end(tmp_path):
+    """A scripted generator calls the search tool, reads the passages and answers: the renderer shows the tool schema
+    and parses the call, the environment retrieves in process, the rollout stays one growing-prefix sample, and the
+    exact-match reward tells searched from closed-book and from retrieval-only outcomes."""
+    from torchtitan_b200.components.tokenizer import ByteTokenizer
+    from torchtitan_b200.experiments.rl import (ChatRenderer, Completion, Rollouter, Rubric, TokenEnv,
+                                                TrainingSampleBuilder)
+    from torchtitan_b200.experiments.rl.examples.search_qa import (PassageIndex, RewardExactMatch, SearchDataset, SearchEnv,
+                                                                  normalize_answer)
+
+    (tmp_path / "p.tsv").write_text("Eiffel Tower\tA wrought-iron tower in Paris, France.\n"
+                                    "Great Wall\tA series of fortifications in northern China.\n"
+                                    "Paris\tThe capital of France.\n")
+    (tmp_path / "q.jsonl").write_text(json.dumps({"question": "Which city has the Eiffel Tower?", "golden_answers": ["Paris"]}) + "\n")
+    idx = PassageIndex.from_file(str(tmp_path / "p.tsv"))
+    assert idx.search("eiffel tower", 2)[0]["contents"].startswith("Eiffel Tower\n") and idx.search("zzz", 2) == []
+    assert normalize_answer("The  Paris!") == "paris"
+    with pytest.raises(ValueError):
+        SearchEnv.Config()
+    rend = ChatRenderer(tokenizer=ByteTokenizer())
+    scripts = {0: ['<tool_call>{"name": "search", "arguments": {"query": "Eiffel Tower city"}}</tool_call><|im_end|>', "Paris<|im_end|>"],
+               1: ["Paris<|im_end|>"],                                              # closed book
+               2: ['<tool_call>{"name": "search", "arguments": "{\\"query\\": \\"Eiffel Tower\\"}"}</tool_call><|im_end|>', "Lyon<|im_end|>"]}
+    seen_prompts = []
+
+    async def generate_fn(prompt_token_ids, *, request_id, routing_session_id=None, sampling_config=None):
+        rollout = int(request_id.split("rollout=")[1].split("/")[0])
+        turn = int(request_id.rsplit("turn=", 1)[1])
+        seen_prompts.append(ByteTokenizer().decode(prompt_token_ids))
+        ids = rend._encode(scripts[rollout][turn])
+        return Completion(request_id=request_id, token_ids=ids, token_logprobs=[-0.1] * len(ids), finish_reason="stop")
+
+    rollouter = Rollouter.Config(
+        train_dataset=SearchDataset.Config(path=str(tmp_path / "q.jsonl")), validation_dataset=SearchDataset.Config(path=str(tmp_path / "q.jsonl")),
+        rubric=Rubric.Config(reward_fns=[RewardExactMatch.Config(no_search_penalty=0.2, retrieval_score=0.1)]),
+        message_env=SearchEnv.Config(passages_path=str(tmp_path / "p.tsv"), topk=2),
+        token_env=TokenEnv.Config(max_num_turns=4)).build()
+    sample = rollouter.get_training_sample()
+    group = run(rollouter.run_group_rollouts(generate_fn=generate_fn, sample=sample, group_id=0, group_size=3, sampling=None,
+                                             renderer=rend))
+    r0, r1, r2 = group.rollouts
+    assert [len(r.turns) for r in group.rollouts] == [2, 1, 2] and all(r.status.value == "completed" for r in group.rollouts)
+    assert '"name": "search"' in seen_prompts[0] and "You may call these tools" in seen_prompts[0]
+    tool_msg = r0.turns[0].env_messages[0]
+    assert tool_msg["role"] == "tool" and "Doc 1(Title: Eiffel Tower)" in tool_msg["content"] and "Paris" in tool_msg["content"]
+    assert r2.turns[0].env_messages[0]["content"].startswith("Doc 1(Title: Eiffel Tower)")     # arguments given as a JSON string
+    assert [r.reward for r in group.rollouts] == [1.0, 0.8, 0.1]
+    assert sum(r.advantage for r in group.rollouts) == pytest.approx(0.0)
+    samples = TrainingSampleBuilder().build_from_group(rollout_group=group).training_samples
+    assert len(samples) == 3                                                          # every rollout stayed one growing prefix
+    two_turn = samples[0]
+    text = ByteTokenizer().decode(two_turn.token_ids)
+    assert text.count("<|im_start|>tool") == 1 and text.endswith("Paris<|im_end|>")
+    trained = ByteTokenizer().decode([t for t, m_ in zip(two_turn.token_ids, two_turn.loss_mask) if m_])
+    assert trained.startswith("<tool_call>") and trained.endswith("Paris<|im_end|>") and "Doc 1" not in trained

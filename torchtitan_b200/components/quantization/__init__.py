@@ -11,6 +11,13 @@ __all__ = ["apply_converters", "CONVERTERS", "has_quantization"]
 QUANT = ("mxfp8", "float8", "nvfp4", "mxfp8_experts", "float8_experts")
 
 
+def _lm_head_cast(cfg, arg, job):
+    # imported on use: the converter lives with the RL experiment, which the core must not load otherwise
+    from torchtitan_b200.experiments.rl.cast_linear import lm_head_cast_converter
+
+    return lm_head_cast_converter(cfg, arg, job)
+
+
 def _registry():
     from .utils import float8_converter, mxfp8_converter
     from torchtitan_b200.components.lora import lora_converter
@@ -18,9 +25,8 @@ def _registry():
     from .grouped import quantize_experts
     from .nvfp4 import nvfp4_converter
 
-    from torchtitan_b200.experiments.rl.cast_linear import lm_head_cast_converter
-
-    return {"lm_head_cast": lm_head_cast_converter, "mxfp8": mxfp8_converter, "float8": float8_converter, "lora": lora_converter, "nvfp4": nvfp4_converter,
+    return {"lm_head_cast": _lm_head_cast, "mxfp8": mxfp8_converter, "float8": float8_converter, "lora": lora_converter,
+            "nvfp4": nvfp4_converter,
             "mxfp8_experts": lambda cfg, arg, job: quantize_experts(cfg, "mxfp8"),
             "float8_experts": lambda cfg, arg, job: quantize_experts(cfg, "float8_rowwise")}
 
