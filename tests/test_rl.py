@@ -871,3 +871,28 @@ def test_search_qa_example_tool_calls_end_to_end(tmp_path):
     assert text.count("<|im_start|>tool") == 1 and text.endswith("Paris<|im_end|>")
     trained = ByteTokenizer().decode([t for t, m_ in zip(two_turn.token_ids, two_turn.loss_mask) if m_])
     assert trained.startswith("<tool_call>") and trained.endswith("Paris<|im_end|>") and "Doc 1" not in trained
+
+
+def test_rl_job_with_own_copy_generators_in_threads(tmp_path):
+    """Two generator replicas with their own weights decode in worker threads while the trainer trains in another; a
+    pull copies the trainer's parameters into each replica and stamps the version."""
+    from torchtitan_b200.config import ConfigManager
+
+    args = _job_args(str(tmp_path), steps=3) + ["--no-share_weights", "--num_generators", "2",
+                                                "--controller.async_loop.target_offpolicy_steps", "2"]
+    cfg = ConfigManager().parse_args(args)
+    assert cfg.generator.threaded and cfg.controller.trainer_in_thread
+    job = cfg.build()
+    gens = job.generators
+    assert len(gens) == 2 and gens[0].model is not job.forge.model and gens[0].model is not gens[1].model
+    out = job.run()
+    assert job.trainer.policy_version == 3 and [g.policy_version for g in gens] == [3, 3]
+    src = dict(job.forge.model.named_parameters())
+    for g in gens:                                          # after the last pull the replicas hold the trainer's weights
+        for name, p in g.model.named_parameters():
+            assert torch.equal(p, src[name].to(p.dtype)), name
+    assert all(g.steps > 0 for g in gens)                   # the router used both replicas
+    hist = [h for h in job.controller.metrics.history if "loss/mean" in h]
+    assert [h["step"] for h in hist] == [1, 2, 3] and all(h["policy_age_max"] <= cfg.controller.async_loop.max_offpolicy_steps for h in hist)
+    assert "validation/rollout_reward/_mean" in out["post"]
+    job.close()
