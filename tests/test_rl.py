@@ -879,14 +879,18 @@ def test_rl_job_with_own_copy_generators_in_threads(tmp_path):
     from torchtitan_b200.config import ConfigManager
 
     args = _job_args(str(tmp_path), steps=3) + ["--no-share_weights", "--num_generators", "2",
-                                                "--controller.async_loop.target_offpolicy_steps", "2"]
+                                                "--controller.async_loop.target_offpolicy_steps", "2",
+                                                # all rewards are 0 here (no gradient): weight decay still moves the weights
+                                                "--trainer.optimizer.weight_decay", "0.5", "--trainer.optimizer.lr", "1e-2"]
     cfg = ConfigManager().parse_args(args)
     assert cfg.generator.threaded and cfg.controller.trainer_in_thread
     job = cfg.build()
     gens = job.generators
     assert len(gens) == 2 and gens[0].model is not job.forge.model and gens[0].model is not gens[1].model
+    first = {n: p.detach().clone() for n, p in gens[1].model.named_parameters()}
     out = job.run()
     assert job.trainer.policy_version == 3 and [g.policy_version for g in gens] == [3, 3]
+    assert any(not torch.equal(p, first[n]) for n, p in gens[1].model.named_parameters())     # the pulls brought new weights
     src = dict(job.forge.model.named_parameters())
     for g in gens:                                          # after the last pull the replicas hold the trainer's weights
         for name, p in g.model.named_parameters():
