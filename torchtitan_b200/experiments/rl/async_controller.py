@@ -17,8 +17,8 @@ Four kinds of coroutines share one event loop::
 * the batcher turns finalised groups into training samples and, once ``num_prompts_per_train_step`` trainable groups
   are present, into the packed microbatch grid of one step;
 * the trainer loop runs forward / backward over the grid, steps the optimizer, and starts the weight transfer
-  (trainer push, then generator pull, then release of the slots just trained) in the background: it is awaited only
-  right before the weights change again.
+  (trainer push, then generator pull, then release of the slots just trained) in the background: it runs under the
+  next step's forward / backward and is awaited right before the weights change again.
 
 With ``P`` prompts per step and ``S = target_offpolicy_steps`` the buffer admits ``B = (S + 1) P`` groups; the
 batcher may look ``W = max(1, floor(window_fraction * B))`` groups past the oldest one, and a sample is never
@@ -105,8 +105,9 @@ class AsyncLoopConfig(Configurable.Config):
 
 
 class WeightSyncManager:
-    """Trainer push -> generator pull -> release of the trained slots, as background tasks.  The push is awaited
-    before the next optimizer step (which overwrites the weights being read), the pull before the next push."""
+    """Trainer push -> generator pull -> release of the trained slots, as background tasks that run under the next
+    step's forward / backward.  Both are awaited before the next optimizer step, which overwrites the weights the
+    generators are reading."""
 
     def __init__(self, *, trainer: PolicyTrainer, router: InterGeneratorRouter, buffer: RolloutGroupWorkBuffer,
                  num_prompts_per_train_step: int, call_trainer=None):
@@ -271,12 +272,15 @@ class AsyncController(Configurable):
                     fb = combine_microbatch_metrics(per_mb)
                 if not math.isfinite(fb["loss/mean"]):
                     raise FloatingPointError(f"step {step}: the policy loss is not finite")
+                # the generators copy from the trainer's live weights (there is no staging store in between), so the
+                # previous push AND pull must be over before the optimizer overwrites them; both overlapped with this
+                # step's forward / backward
                 with timer.record("timing/step/blocking_trainer_push"):
-                    push = await sync.wait_prev_push()           # the optimizer is about to overwrite what is read
+                    push = await sync.wait_prev_push()
+                with timer.record("timing/step/blocking_generator_pull"):
+                    pull = await sync.wait_prev_pull()
                 with timer.record("timing/step/optim"):
                     opt = await self._call_trainer(self.trainer.optim_step)
-                with timer.record("timing/step/blocking_generator_pull"):
-                    pull = await sync.wait_prev_pull()           # the next push replaces what the generators read
                 sync.start_async_push_pull(version=opt.policy_version)
             times = timer.flush()
             self.metrics.log(step=step, metrics=[
