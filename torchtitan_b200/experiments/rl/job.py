@@ -174,8 +174,9 @@ class RLJob(Configurable):
         src = dict(self.forge.model.named_parameters())
         for name, p in engine.model.named_parameters():
             p.copy_(src[name].detach().to(p.device, p.dtype), non_blocking=True)
+        src_buffers = dict(self.forge.model.named_buffers())      # e.g. the routers' selection bias
         for name, b in engine.model.named_buffers():
-            s = dict(self.forge.model.named_buffers()).get(name)
+            s = src_buffers.get(name)
             if s is not None and s.shape == b.shape:
                 b.copy_(s.to(b.device, b.dtype))
 
