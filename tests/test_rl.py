@@ -728,10 +728,10 @@ def _run_job(rank, world, folder, out_path):
     job.close()
 
 
-@pytest.mark.parametrize("world", [1, 2])
-def test_rl_job_from_the_config_registry(tmp_path, world):
-    """The registered debug job end to end; with two training ranks the controller runs on rank 0 and the other rank
-    follows its forward / backward and optimizer calls on its own column of the microbatch grid."""
+def test_rl_job_from_the_config_registry(tmp_path, world=2):
+    """The registered debug job end to end on two training ranks: the controller runs on rank 0 and the other rank
+    follows its forward / backward and optimizer calls on its own column of the microbatch grid.  (The single-rank
+    job is what ``test_rl_job_with_own_copy_generators_in_threads`` runs.)"""
     from tests.dist_utils import run_distributed
 
     out = str(tmp_path / "out.pt")
