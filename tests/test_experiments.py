@@ -142,7 +142,45 @@ def test_hf_backend_trains():
     assert losses[-1] < losses[0]
 
 
-@pytest.mark.parametrize("module,flavor", [("llama3", "debugmodel_gqa"), ("gpt_oss", "debugmodel")])
+@pytest.mark.parametrize("module,flavor", [("deepseek_v3", "debugmodel"), ("qwen3_5", "debugmodel_moe"), ("muse_glimmer", "debugmodel"),
+                                           ("kimi_k2_7", "debugmodel")])
+def test_cached_generation_covers_latent_attention_and_recurrent_layers(module, flavor):
+    """Incremental decoding equals prefix recomputation for latent attention (assembled keys / values cached), Gated
+    DeltaNet layers (state matrix and convolution tails carried) and the gated-attention subclass, one sequence at a
+    time and several sequences per pass in the engine."""
+    import asyncio
+
+    from torchtitan_b200.experiments.rl import GenerationEngine, SamplingConfig
+    from torchtitan_b200.experiments.rl.generator import CachedGenerator, SamplingGenerator
+    from torchtitan_b200.models import get_model_spec
+
+    spec = get_model_spec(module, flavor)
+    model = spec.model.build()
+    model.init_states(seed=1)
+    model.eval()
+    g = torch.Generator().manual_seed(0)
+    with torch.no_grad():
+        for p in model.parameters():
+            if p.dim() == 1:
+                p.add_(0.1 * torch.randn(p.shape, generator=g))
+    prompts = [torch.randint(0, 2000, (n,), generator=g) for n in (70, 5)]
+    want = [SamplingGenerator(model, temperature=0.0).generate(p, 10) for p in prompts]
+    for p, w in zip(prompts, want):
+        got = CachedGenerator(model, temperature=0.0).generate(p, 10)
+        assert torch.equal(got.response, w.response) and torch.allclose(got.logprobs, w.logprobs, atol=1e-4)
+
+    async def go():
+        eng = GenerationEngine(GenerationEngine.Config(threaded=False), model=model)
+        out = await asyncio.gather(*(eng.generate(p.tolist(), request_id=f"r{i}", sampling_config=SamplingConfig(
+            temperature=0.0, max_tokens=10)) for i, p in enumerate(prompts)))
+        await eng.close()
+        return out
+
+    for c, w in zip(asyncio.run(go()), want):
+        assert c.token_ids == w.response.tolist() and torch.allclose(torch.tensor(c.token_logprobs), w.logprobs, atol=1e-4)
+
+
+@pytest.mark.parametrize("module,flavor", [("llama3", "debugmodel_gqa"), ("gpt_oss", "debugmodel"), ("qwen3_5", "debugmodel")])
 def test_cached_generation_matches_transformers_greedy(module, flavor):
     """Greedy decoding with the key / value cache (and, for GPT-OSS, a context longer than the sliding window, with
     sinks) produces the tokens ``transformers.generate`` produces on the same weights, as does the cache-free sampler."""

@@ -101,14 +101,8 @@ class GenerationEngine(Configurable):
 
     def __init__(self, config: Config | None = None, *, model, eos_id: int | None = None,
                  weight_source: Callable[["GenerationEngine"], None] | None = None):
-        from torchtitan_b200.models.common.attention import GQAttention
-
         self.config = config or GenerationEngine.Config()
         self.model, self.eos_id, self.weight_source = model, eos_id, weight_source
-        for name, mod in model.named_modules():
-            if type(mod).__name__ in ("MLAttention", "GatedDeltaNet"):
-                raise NotImplementedError(f"{name}: cached decoding covers grouped-query attention layers only")
-        self._n_attn = sum(isinstance(x, GQAttention) for x in model.modules())
         self.policy_version = 0
         self._waiting: list[_Seq] = []
         self._running: list[_Seq] = []

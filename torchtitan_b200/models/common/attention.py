@@ -27,7 +27,7 @@ from torchtitan_b200.parallel import tp_ops
 from .layers import Linear, RMSNorm, RoPE, TPContext
 from .module import InitSpec, Module, set_init
 
-__all__ = ["GQAttention", "AttentionContext", "KVCache", "BatchedKVCache", "build_attention_context"]
+__all__ = ["GQAttention", "AttentionContext", "KVCache", "BatchedKVCache", "cached_attention", "build_attention_context"]
 
 
 @dataclass
@@ -56,6 +56,13 @@ class KVCache:
     def length(self, layer) -> int:
         return self._len.get(id(layer), 0)
 
+    def state(self, layer) -> dict:
+        """Free-form per-layer state for layers that are not attention (a recurrent layer's state matrix and the
+        tail of its convolution inputs)."""
+        if not hasattr(self, "_state"):
+            self._state = {}
+        return self._state.setdefault(id(layer), {})
+
     def update(self, layer, k: torch.Tensor, v: torch.Tensor):
         key = id(layer)
         n0, n = self._len.get(key, 0), k.shape[0]
@@ -80,6 +87,32 @@ class BatchedKVCache:
     def __init__(self, caches: "list[KVCache]", rows: list[int]):
         assert len(caches) == len(rows)
         self.caches, self.rows = caches, rows
+
+
+def cached_attention(layer, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, kv_cache, scale: float, *, window: int = 0,
+                     sinks: torch.Tensor | None = None) -> torch.Tensor:
+    """Append the new keys / values to ``layer``'s cache and attend the new queries to everything cached (causal
+    among the new rows).  ``kv_cache``: one ``KVCache`` (all rows belong to one sequence) or a ``BatchedKVCache``
+    (consecutive row blocks of several sequences).  Query / key and value head dimensions may differ (latent
+    attention); shapes the flash kernels do not cover run the PyTorch block attention."""
+    from torchtitan_b200.ops import flash as FL
+
+    def attend(cache, q_, k_, v_):
+        kc, vc = cache.update(layer, k_.detach(), v_.detach())
+        o_, lse = FL.block_fwd(q_.contiguous(), kc, vc, scale, causal=True, causal_offset=kc.shape[0] - q_.shape[0],
+                               window=window)
+        if sinks is not None:
+            o_ = (o_.float() * torch.sigmoid(lse - sinks.float()[:, None]).t()[..., None]).to(q_.dtype)
+        return o_
+
+    if not isinstance(kv_cache, BatchedKVCache):
+        return attend(kv_cache, q, k, v)
+    parts, r0 = [], 0
+    for cache, n in zip(kv_cache.caches, kv_cache.rows):
+        parts.append(attend(cache, q[r0:r0 + n], k[r0:r0 + n], v[r0:r0 + n]))
+        r0 += n
+    assert r0 == q.shape[0], f"BatchedKVCache rows cover {r0} of {q.shape[0]} tokens"
+    return torch.cat(parts)
 
 
 def build_attention_context(positions: torch.Tensor, *, assume_single_document: bool = False,
@@ -212,25 +245,7 @@ class GQAttention(Module):
         ctx = ctx or AttentionContext()
         if ctx.kv_cache is not None:
             # incremental decoding (no autograd): the new queries attend to everything cached plus themselves
-            from torchtitan_b200.ops import flash as FL
-
-            def attend(cache, q_, k_, v_):
-                kc, vc = cache.update(self, k_.detach(), v_.detach())
-                o_, lse = FL.block_fwd(q_.contiguous(), kc, vc, self.scale, causal=True,
-                                       causal_offset=kc.shape[0] - q_.shape[0], window=int(self.window or 0))
-                if self.sinks is not None:
-                    o_ = (o_.float() * torch.sigmoid(lse - self.sinks.float()[:, None]).t()[..., None]).to(q_.dtype)
-                return o_
-
-            if isinstance(ctx.kv_cache, BatchedKVCache):
-                parts, r0 = [], 0
-                for cache, n in zip(ctx.kv_cache.caches, ctx.kv_cache.rows):
-                    parts.append(attend(cache, q[r0:r0 + n], k[r0:r0 + n], v[r0:r0 + n]))
-                    r0 += n
-                assert r0 == T, f"BatchedKVCache rows cover {r0} of {T} tokens"
-                o = torch.cat(parts)
-            else:
-                o = attend(ctx.kv_cache, q, k, v)
+            o = cached_attention(self, q, k, v, ctx.kv_cache, self.scale, window=int(self.window or 0), sinks=self.sinks)
         elif ctx.cp is not None:
             from torchtitan_b200.parallel.context_parallel import cp_attention
 

@@ -155,7 +155,12 @@ class MLAttention(Module):
             kf = torch.cat([kv[:, :, :dn], k_pe.expand(T, H, dr)], dim=-1)
             v = kv[:, :, dn:]
         ctx = ctx or AttentionContext()
-        if ctx.cp is not None:
+        if ctx.kv_cache is not None:
+            # incremental decoding: the assembled per-head keys and values are cached
+            from .attention import cached_attention
+
+            o = cached_attention(self, qf, kf, v.contiguous(), ctx.kv_cache, self.scale)
+        elif ctx.cp is not None:
             from torchtitan_b200.parallel.context_parallel import cp_attention
 
             o = cp_attention(qf, kf, v, ctx, scale=self.scale, window=None, sinks=None)

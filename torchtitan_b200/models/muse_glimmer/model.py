@@ -74,8 +74,13 @@ class MuseAttention(GQAttention):
             rp = ctx.rope_positions if ctx is not None and ctx.rope_positions is not None else positions
             q, k = self.rope(q, rp), self.rope(k, rp)
         ctx = ctx or AttentionContext()
-        o = OF.attention(q, k, v, scale=self.scale, causal=True, doc_ids=ctx.doc_ids, window=self.window,
-                         kv_first=ctx.kv_first)
+        if ctx.kv_cache is not None:          # incremental decoding
+            from torchtitan_b200.models.common.attention import cached_attention
+
+            o = cached_attention(self, q, k, v, ctx.kv_cache, self.scale, window=int(self.window or 0))
+        else:
+            o = OF.attention(q, k, v, scale=self.scale, causal=True, doc_ids=ctx.doc_ids, window=self.window,
+                             kv_first=ctx.kv_first)
         o = o.reshape(T, hq * hd)
         if self.o_gate is not None:
             o = o * torch.sigmoid(self.o_gate(x))

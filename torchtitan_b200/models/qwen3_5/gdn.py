@@ -51,8 +51,10 @@ def recurrent_gated_delta_rule(q, k, v, g, beta):
     return torch.stack(out)
 
 
-def chunk_gated_delta_rule(q, k, v, g, beta, chunk: int = 64):
-    """Chunked evaluation of the gated delta rule (same signature as the recurrent oracle)."""
+def chunk_gated_delta_rule(q, k, v, g, beta, chunk: int = 64, *, initial_state=None, return_state: bool = False):
+    """Chunked evaluation of the gated delta rule (same signature as the recurrent oracle).  ``initial_state``
+    ``[H, dk, dv]`` continues an earlier call (incremental decoding); ``return_state`` also returns the state after
+    the last token (padding rows have zero keys, values and gates, so they leave it unchanged)."""
     T, H, dk = q.shape
     dv = v.shape[-1]
     dt = v.dtype
@@ -81,7 +83,7 @@ def chunk_gated_delta_rule(q, k, v, g, beta, chunk: int = 64):
     a = torch.stack(rows, dim=-2) + torch.eye(chunk, device=q.device)
     value = a @ v_beta
     k_cum = a @ (k_beta * torch.exp(gc)[..., None])
-    S = q.new_zeros(H, dk, dv)
+    S = q.new_zeros(H, dk, dv) if initial_state is None else initial_state.float()
     outs = []
     for i in range(N):
         qi, ki, vi, gi = q[:, i], k[:, i], value[:, i], gc[:, i]
@@ -91,6 +93,8 @@ def chunk_gated_delta_rule(q, k, v, g, beta, chunk: int = 64):
         outs.append(inter + attn @ v_new)
         S = S * torch.exp(gi[:, -1])[:, None, None] + (ki * torch.exp(gi[:, -1:] - gi)[..., None]).transpose(-1, -2) @ v_new
     o = torch.stack(outs, dim=1).reshape(H, N * chunk, dv)[:, :T]
+    if return_state:
+        return o.transpose(0, 1).to(dt), S
     return o.transpose(0, 1).to(dt)
 
 
@@ -214,19 +218,51 @@ class GatedDeltaNet(Module):
         if tp is not None and tp.sequence_parallel:
             x = tp_ops.all_gather_rows(x, tp)
         T = x.shape[0]
-        packed = ctx is not None and ctx.doc_ids is not None
+        cache = ctx.kv_cache if ctx is not None else None
+        packed = cache is None and ctx is not None and ctx.doc_ids is not None
         pos = positions if packed else None
-        q = causal_conv_silu(self.in_proj_q(x), self.conv_q, pos).view(T, c.n_key_heads, c.key_head_dim)
-        k = causal_conv_silu(self.in_proj_k(x), self.conv_k, pos).view(T, c.n_key_heads, c.key_head_dim)
-        v = causal_conv_silu(self.in_proj_v(x), self.conv_v, pos).view(T, c.n_value_heads, c.value_head_dim)
+        pq, pk, pv = self.in_proj_q(x), self.in_proj_k(x), self.in_proj_v(x)
         g = -torch.exp(self.A_log.float()) * F.softplus(self.in_proj_a(x).float() + self.dt_bias.float())
         beta = torch.sigmoid(self.in_proj_b(x).float())
         if packed:
             g = torch.where((positions == 0)[:, None], torch.full_like(g, _RESET), g)
         rep = c.n_value_heads // c.n_key_heads
-        if rep > 1:
-            q, k = q.repeat_interleave(rep, dim=1), k.repeat_interleave(rep, dim=1)
-        o = chunk_gated_delta_rule(q, k, v, g, beta, c.chunk_size)
+
+        def mix(pq_, pk_, pv_, g_, beta_, state: dict | None):
+            """Convolutions and the delta rule over one token range; ``state`` (incremental decoding) carries the last
+            ``W - 1`` convolution inputs and the state matrix from the range before."""
+            n = pq_.shape[0]
+
+            def conv(p, w, name):
+                if state is None:
+                    return causal_conv_silu(p, w, pos)
+                tail = state.get(name)
+                full = p if tail is None else torch.cat([tail, p])
+                state[name] = full[-(w.shape[-1] - 1):].detach().clone()
+                return causal_conv_silu(full.contiguous(), w, None)[-n:]
+
+            q = conv(pq_, self.conv_q, "q").view(n, c.n_key_heads, c.key_head_dim)
+            k = conv(pk_, self.conv_k, "k").view(n, c.n_key_heads, c.key_head_dim)
+            v = conv(pv_, self.conv_v, "v").view(n, c.n_value_heads, c.value_head_dim)
+            if rep > 1:
+                q, k = q.repeat_interleave(rep, dim=1), k.repeat_interleave(rep, dim=1)
+            if state is None:
+                return chunk_gated_delta_rule(q, k, v, g_, beta_, c.chunk_size)
+            o_, state["S"] = chunk_gated_delta_rule(q, k, v, g_, beta_, c.chunk_size, initial_state=state.get("S"),
+                                                    return_state=True)
+            return o_
+
+        if cache is None:
+            o = mix(pq, pk, pv, g, beta, None)
+        elif hasattr(cache, "caches"):          # several sequences in one pass: the token mixing is per sequence
+            parts, r0 = [], 0
+            for one, n in zip(cache.caches, cache.rows):
+                sl = slice(r0, r0 + n)
+                parts.append(mix(pq[sl], pk[sl], pv[sl], g[sl], beta[sl], one.state(self)))
+                r0 += n
+            o = torch.cat(parts)
+        else:
+            o = mix(pq, pk, pv, g, beta, cache.state(self))
         z = self.in_proj_z(x).view(T, c.n_value_heads, c.value_head_dim)
         of = o.float()
         of = of * torch.rsqrt(of.pow(2).mean(-1, keepdim=True) + c.norm_eps) * self.norm_weight.float()
