@@ -900,3 +900,30 @@ def test_rl_job_with_own_copy_generators_in_threads(tmp_path):
     assert [h["step"] for h in hist] == [1, 2, 3] and all(h["policy_age_max"] <= cfg.controller.async_loop.max_offpolicy_steps for h in hist)
     assert "validation/rollout_reward/_mean" in out["post"]
     job.close()
+
+
+def test_rl_job_checkpoints_and_resumes(tmp_path):
+    """Checkpoints at the trainer's interval carry the policy version and the datasets' positions: a second job on the
+    same folder continues at the saved version, draws the next prompts of the stream and only runs the steps left."""
+    from torchtitan_b200.config import ConfigManager
+
+    def build(steps):
+        return ConfigManager().parse_args(_job_args(str(tmp_path), steps=steps) + [
+            "--trainer.checkpoint.enable", "--trainer.checkpoint.interval", "1", "--trainer.checkpoint.no-last_save_model_only"]).build()
+
+    first = build(2)
+    first.run()
+    assert first.trainer.policy_version == 2
+    position = first.controller.rollouter.dataset_state()
+    first.close()
+    state = json.loads((tmp_path / "checkpoint" / "rl_state.json").read_text())
+    assert state["policy_version"] == 2 and "train" in state["datasets"]
+    assert (tmp_path / "checkpoint" / "step-2" / ".metadata").exists()
+    second = build(3)
+    assert second.trainer.policy_version == 2 and second.controller.start_step == 2 and second.generators[0].policy_version == 2
+    resumed_at = second.controller.rollouter.dataset_state()["train"]["rng_state"]
+    assert json.loads(json.dumps(resumed_at)) == json.loads(json.dumps(state["datasets"]["train"]["rng_state"]))
+    second.run()
+    hist = [h["step"] for h in second.controller.metrics.history if "loss/mean" in h]
+    assert hist == [3] and second.trainer.policy_version == 3 and position is not None
+    second.close()

@@ -164,9 +164,11 @@ class AsyncController(Configurable):
         Must be off when a generator shares its model object with the trainer."""
 
     def __init__(self, config: Config, *, trainer: PolicyTrainer, generators: Sequence[Any], tokenizer,
-                 dp_degree: int = 1, loggers: Sequence[Any] = ()):
+                 dp_degree: int = 1, loggers: Sequence[Any] = (), step_callback=None):
         self.config = config
         self.trainer = trainer
+        self.step_callback = step_callback
+        """``step_callback(step, last_step)`` runs after every optimizer step (the job saves checkpoints there)."""
         self.renderer = config.renderer.build(tokenizer=tokenizer)
         self.rollouter: Rollouter = config.rollouter.build()
         self.router: InterGeneratorRouter = config.generator_router.build(generators=list(generators))
@@ -288,6 +290,8 @@ class AsyncController(Configurable):
                 *[m.Metric(k, m.NoReduce(v)) for k, v in opt.metrics.items()], *self._buffer.metrics(), *times, *age,
                 *push, *pull, *compute_perf_ratio_metrics(num_global_valid_tokens=batch.num_global_valid_tokens,
                                                           time_metrics=times)])
+            if self.step_callback is not None:
+                await self._call_trainer(self.step_callback, step, step == loop_cfg.num_training_steps)
         await sync.wait_inflight_push_pull()
 
     # -- the whole run ------------------------------------------------------------------------------------------

@@ -21,6 +21,7 @@ trainer and each generator, TorchStore for the weights).
 from __future__ import annotations
 
 import asyncio
+import json
 import os
 from dataclasses import dataclass, field
 from typing import Any
@@ -136,7 +137,8 @@ class RLJob(Configurable):
         self.trainer = cls(model=forge.model, engine=forge.engines[0], optimizers=forge.optimizers,
                            lr_schedulers=forge.lr_schedulers, pdims=forge.pdims, max_norm=config.trainer.training.max_norm,
                            loss=PolicyLoss(config.ratio_clip_low, config.ratio_clip_high))
-        if config.trainer.checkpoint.enable and forge.load():
+        resumed = bool(config.trainer.checkpoint.enable and forge.load())
+        if resumed:
             self.trainer.policy_version = forge.step
         self.controller = None
         if self.rank != 0:
@@ -153,8 +155,34 @@ class RLJob(Configurable):
             raise ValueError(f"the tokenizer has {tokenizer.get_vocab_size()} tokens, the model {forge.model_config.vocab_size}")
         self.generators = self._build_generators(tokenizer)
         self.controller = AsyncController(config.controller, trainer=self.trainer, generators=self.generators,
-                                          tokenizer=tokenizer, dp_degree=forge.pdims.dp_degree)
+                                          tokenizer=tokenizer, dp_degree=forge.pdims.dp_degree,
+                                          step_callback=self._after_step if config.trainer.checkpoint.enable else None)
         self.controller.start_step = self.trainer.policy_version
+        for g in self.generators:
+            g.policy_version = self.trainer.policy_version
+        self._state_path = os.path.join(config.trainer.dump_folder, config.trainer.checkpoint.folder, "rl_state.json")
+        if resumed and os.path.exists(self._state_path):
+            with open(self._state_path) as f:
+                state = json.load(f)
+            if state.get("policy_version") == self.trainer.policy_version:
+                self.controller.rollouter.load_dataset_state(state.get("datasets", {}))
+                logger.info(f"RL job resumed at policy version {self.trainer.policy_version} with its dataset position")
+
+    def _after_step(self, step: int, last: bool) -> None:
+        """Checkpoint at the trainer's interval: model / optimizer / schedule through the regular checkpoint manager,
+        plus the datasets' positions (prompt groups still in flight at the save are regenerated after a resume)."""
+        c = self.config.trainer.checkpoint
+        if not (last or step % max(c.interval, 1) == 0):
+            return
+        if isinstance(self.trainer, _LeaderTrainer):
+            self.trainer.save(self.forge, step, last)
+        else:
+            self.forge.step = step
+            self.forge.save(step, last_step=last)
+        os.makedirs(os.path.dirname(self._state_path), exist_ok=True)
+        with open(self._state_path + ".tmp", "w") as f:
+            json.dump({"policy_version": step, "datasets": self.controller.rollouter.dataset_state()}, f)
+        os.replace(self._state_path + ".tmp", self._state_path)
 
     def _build_generators(self, tokenizer) -> list[GenerationEngine]:
         c, forge = self.config, self.forge
@@ -193,13 +221,6 @@ class RLJob(Configurable):
 
     async def _run(self) -> dict:
         out = await self.controller.run()
-        if self.config.trainer.checkpoint.enable:
-            step = self.trainer.policy_version
-            if isinstance(self.trainer, _LeaderTrainer):
-                self.trainer.save(self.forge, step, True)
-            else:
-                self.forge.step = step
-                self.forge.save(step, last_step=True)
         await self.controller.close()
         logger.info("RL job finished")
         return out
