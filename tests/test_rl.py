@@ -927,3 +927,33 @@ def test_rl_job_checkpoints_and_resumes(tmp_path):
     hist = [h["step"] for h in second.controller.metrics.history if "loss/mean" in h]
     assert hist == [3] and second.trainer.policy_version == 3 and position is not None
     second.close()
+
+
+def test_renderer_with_a_tokenizer_chat_template_rerenders_between_turns():
+    """With the tokenizer's own Jinja template the renderer cannot bridge turns as tokens: the token environment
+    re-renders the conversation, and a template that drops earlier reasoning breaks the prefix, so the rollout packs
+    into two training samples instead of one."""
+    from torchtitan_b200.components.tokenizer import ByteTokenizer
+    from torchtitan_b200.experiments.rl import ChatRenderer, TokenEnv, TrainingSampleBuilder
+
+    tok = ByteTokenizer()
+    tok.chat_template = ("{% for m in messages %}[{{ m['role'] }}]{{ m['content'] }}\\n{% endfor %}"
+                         "{% if add_generation_prompt %}[assistant]{% endif %}")
+    rend = ChatRenderer(tokenizer=tok)
+    ids = rend.render_ids(messages=[{"role": "user", "content": "hi"}])
+    assert tok.decode(ids) == "[user]hi\\n[assistant]"
+    assert rend.bridge_to_next_turn(previous_prompt_ids=ids, previous_completion_ids=[1], new_messages=[]) is None
+
+    async def go():
+        env = TokenEnv(message_env=_EchoEnv(turns=2), renderer=rend)
+        first = await env.init()
+        c1 = _completion(rend, "<think>secret</think>one")
+        second = await env.step(c1)
+        return first, c1, second
+
+    first, c1, second = run(go())
+    text = tok.decode(second.next_prompt_token_ids)
+    assert text == "[user]hi\\n[assistant]one\\n[user]again\\n[assistant]"          # the reasoning is not in the history
+    turns = [_turn(0, 0, 0, first.next_prompt_token_ids, c1.token_ids), _turn(0, 0, 1, second.next_prompt_token_ids, rend._encode("two"))]
+    samples = TrainingSampleBuilder().rollout_to_training_samples(_rollout(0, 0, turns, 1.0, 0.5))
+    assert len(samples) == 2 and samples[1].rollout_id.turn_id == 1
