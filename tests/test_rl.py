@@ -957,3 +957,24 @@ def test_renderer_with_a_tokenizer_chat_template_rerenders_between_turns():
     turns = [_turn(0, 0, 0, first.next_prompt_token_ids, c1.token_ids), _turn(0, 0, 1, second.next_prompt_token_ids, rend._encode("two"))]
     samples = TrainingSampleBuilder().rollout_to_training_samples(_rollout(0, 0, turns, 1.0, 0.5))
     assert len(samples) == 2 and samples[1].rollout_id.turn_id == 1
+
+
+def test_place_model_keeps_buffer_dtypes():
+    """Parameters go to bf16, the fp32 rotary tables stay fp32 (``model.to(dtype=...)`` would cast them and the kernels
+    that read them refuse that), and the engine decodes on the result."""
+    from torchtitan_b200.experiments.rl import GenerationEngine, SamplingConfig
+    from torchtitan_b200.experiments.rl.engine import place_model_
+
+    _, model = _tiny_llama()
+    place_model_(model, torch.device("cpu"), torch.bfloat16)
+    assert all(p.dtype == torch.bfloat16 for p in model.parameters())
+    tables = [b for n, b in model.named_buffers() if n.endswith("rope.cache")]
+    assert tables and all(b.dtype == torch.float32 for b in tables)
+
+    async def go():
+        eng = GenerationEngine(GenerationEngine.Config(threaded=False), model=model)
+        out = await eng.generate([3, 4, 5], request_id="x", sampling_config=SamplingConfig(temperature=0.0, max_tokens=4))
+        await eng.close()
+        return out
+
+    assert len(run(go()).token_ids) == 4

@@ -34,7 +34,19 @@ from torchtitan_b200.utils.logging import logger
 from . import metrics as m
 from .types import Completion
 
-__all__ = ["SamplingConfig", "GenerationEngine"]
+__all__ = ["SamplingConfig", "GenerationEngine", "place_model_"]
+
+
+def place_model_(model, device, param_dtype: torch.dtype | None = None):
+    """Move ``model`` to ``device`` and cast its floating-point *parameters* to ``param_dtype``.  Buffers keep their
+    dtype: the rotary tables (and the routers' selection bias) are fp32 by contract of the kernels that read them,
+    which ``model.to(dtype=...)`` would silently break."""
+    model.to(device)
+    if param_dtype is not None:
+        for p in model.parameters():
+            if p.is_floating_point() and p.dtype != param_dtype:
+                p.data = p.data.to(param_dtype)
+    return model
 
 
 @dataclass(kw_only=True, slots=True)

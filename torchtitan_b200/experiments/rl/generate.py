@@ -20,7 +20,7 @@ import time
 from torchtitan_b200.utils.logging import init_logger, logger
 
 from . import config_registry
-from .engine import GenerationEngine
+from .engine import GenerationEngine, place_model_
 from .renderer import ChatRenderer
 
 _DEFAULT_PROMPT = ("Sort these names alphabetically and put the final answer inside "
@@ -59,7 +59,7 @@ def generate(argv: list[str] | None = None) -> list[str]:
     device = torch.device(args.device or ("cuda" if torch.cuda.is_available() else "cpu"))
     model = spec.model.build()
     model.init_states(seed=t.debug.seed or 0)
-    model = model.to(device=device, dtype=torch.bfloat16 if device.type == "cuda" else torch.float32)
+    model = place_model_(model, device, torch.bfloat16 if device.type == "cuda" else torch.float32)
     if t.checkpoint.initial_load_path or t.checkpoint.initial_load_in_hf:
         from torchtitan_b200.scripts.convert_hf import load_hf_into
 

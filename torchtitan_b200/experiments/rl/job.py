@@ -34,7 +34,7 @@ from torchtitan_b200.trainer import Trainer
 from torchtitan_b200.utils.logging import logger
 
 from .async_controller import AsyncController
-from .engine import GenerationEngine
+from .engine import GenerationEngine, place_model_
 from .losses import PolicyLoss
 from .policy_trainer import PolicyTrainer
 
@@ -192,7 +192,9 @@ class RLJob(Configurable):
         out = []
         for i in range(c.num_generators):
             dev = torch.device(c.generator_devices[i] if i < len(c.generator_devices) else forge.device)
-            copy = forge.model_config.build().to(device=dev, dtype=next(forge.model.parameters()).dtype)
+            copy = place_model_(forge.model_config.build(), dev, next(forge.model.parameters()).dtype)
+            if hasattr(copy, "init_buffers"):
+                copy.init_buffers(dev)
             out.append(c.generator.build(model=copy, eos_id=eos, weight_source=self._copy_weights))
             self._copy_weights(out[-1])
         return out
