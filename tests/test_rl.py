@@ -246,7 +246,7 @@ def test_sample_builder_merges_growing_prefix_and_branches_where_it_breaks():
 
 def test_batcher_packs_rows_shifts_labels_and_deals_the_grid():
     from torchtitan_b200.experiments.rl import BatchConfig, Batcher, TrainingSample, TrainingSampleGroup
-    from torchtitan_b200.experiments.rl.types import RolloutTurnID
+    from torchtitan_b200.experiments.rl.records import RolloutTurnID
 
     def sample(g, toks, n_prompt, v=0):
         n = len(toks)

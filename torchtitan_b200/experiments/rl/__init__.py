@@ -25,7 +25,7 @@ from .rollout import RolloutBuffer, SampledResponse
 from .rollouter import AdvantageEstimator, RewardFn, Rollouter, Rubric, RubricOutput
 from .routing import (InterGeneratorRouter, IntraGeneratorRouter, LeastLoadedRoutingStrategy, RoundRobinRoutingStrategy,
                       RoutingContext, StickySessionRoutingStrategy)
-from .types import (Completion, Rollout, RolloutGroup, RolloutStatus, RolloutTurn, RolloutTurnID, TrainingBatch,
+from .records import (Completion, Rollout, RolloutGroup, RolloutStatus, RolloutTurn, RolloutTurnID, TrainingBatch,
                     TrainingMicrobatch, TrainingSample, TrainingSampleGroup)
 from .work_buffer import RolloutGroupWork, RolloutGroupWorkBuffer
 

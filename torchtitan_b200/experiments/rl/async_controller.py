@@ -50,7 +50,7 @@ from .recorder import (RolloutSampleRecorder, combine_microbatch_metrics, comput
 from .renderer import ChatRenderer
 from .rollouter import Rollouter
 from .routing import InterGeneratorRouter
-from .types import RolloutGroup, TrainingBatch
+from .records import RolloutGroup, TrainingBatch
 from .work_buffer import RolloutGroupWork, RolloutGroupWorkBuffer
 
 __all__ = ["ValidationConfig", "AsyncLoopConfig", "WeightSyncManager", "AsyncController"]

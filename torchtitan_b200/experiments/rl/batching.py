@@ -24,7 +24,7 @@ from torchtitan_b200.config import Configurable
 from torchtitan_b200.utils.logging import logger
 
 from . import metrics as m
-from .types import (Rollout, RolloutGroup, RolloutTurnID, TrainingBatch, TrainingMicrobatch, TrainingSample,
+from .records import (Rollout, RolloutGroup, RolloutTurnID, TrainingBatch, TrainingMicrobatch, TrainingSample,
                     TrainingSampleGroup)
 
 __all__ = ["TrainingSampleBuilder", "BatchConfig", "Batcher"]

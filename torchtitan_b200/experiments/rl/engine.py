@@ -32,7 +32,7 @@ from torchtitan_b200.config import Configurable
 from torchtitan_b200.utils.logging import logger
 
 from . import metrics as m
-from .types import Completion
+from .records import Completion
 
 __all__ = ["SamplingConfig", "GenerationEngine", "place_model_"]
 

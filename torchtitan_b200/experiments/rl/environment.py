@@ -17,7 +17,7 @@ from typing import Any
 from torchtitan_b200.config import Configurable
 from torchtitan_b200.utils.logging import logger
 
-from .types import Completion, Message, RolloutStatus
+from .records import Completion, Message, RolloutStatus
 
 __all__ = ["MessageEnvInit", "MessageEnvStep", "MessageEnv", "TokenEnvOutput", "TokenEnv"]
 

@@ -26,7 +26,7 @@ from torchtitan_b200.config import Configurable
 
 from ..environment import MessageEnv, MessageEnvInit, MessageEnvStep
 from ..rollouter import RewardFn
-from ..types import Message, Rollout
+from ..records import Message, Rollout
 
 __all__ = ["AlphabetSortSample", "AlphabetSortDataset", "AlphabetSortEnv", "RewardAlphabetSort", "score_sorted_list"]
 

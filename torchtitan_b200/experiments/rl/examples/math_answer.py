@@ -24,7 +24,7 @@ from torchtitan_b200.config import Configurable
 
 from ..environment import MessageEnv, MessageEnvInit, MessageEnvStep
 from ..rollouter import RewardFn
-from ..types import Message, Rollout
+from ..records import Message, Rollout
 
 __all__ = ["MathSample", "MathDataset", "MathEnv", "RewardMathAnswer", "score_math_response", "extract_final_answer",
            "normalize_answer"]

@@ -28,7 +28,7 @@ from torchtitan_b200.utils.logging import logger
 
 from ..environment import MessageEnv, MessageEnvInit, MessageEnvStep
 from ..rollouter import RewardFn
-from ..types import Message, Rollout
+from ..records import Message, Rollout
 
 __all__ = ["SearchSample", "SearchDataset", "PassageIndex", "SearchEnv", "RewardExactMatch", "SEARCH_TOOL", "normalize_answer"]
 

@@ -16,7 +16,7 @@ import torch
 import torch.distributed as dist
 
 from .losses import PolicyLoss
-from .types import OptimStepOutput, TrainingMicrobatch
+from .records import OptimStepOutput, TrainingMicrobatch
 
 __all__ = ["PolicyTrainer"]
 

@@ -17,7 +17,7 @@ from dataclasses import dataclass, field
 from torchtitan_b200.config import Configurable
 
 from . import metrics as m
-from .types import Rollout, RolloutGroup
+from .records import Rollout, RolloutGroup
 
 __all__ = ["KeepExtremeRewardsFilter", "RolloutSampleRecorder", "compute_rollout_metrics", "compute_policy_age_metrics",
            "compute_perf_ratio_metrics", "combine_microbatch_metrics"]

@@ -72,12 +72,15 @@ class RolloutStatus(str, Enum):
 
 @dataclass(kw_only=True, slots=True)
 class RolloutTurn:
+    """One generator call and the environment's answer to it."""
     rollout_id: RolloutTurnID
+    # token space (what training needs)
     prompt_token_ids: list[int]                 # the whole conversation up to this turn
     completion_token_ids: list[int]
-    completion_logprobs: list[float]
-    min_policy_version: int | None = None
+    completion_logprobs: list[float]            # behaviour policy, one per completion token
+    min_policy_version: int | None = None       # None: nothing was generated
     max_policy_version: int | None = None
+    # message space (what rubrics and the recorder read)
     prompt_messages: list[Message] = field(default_factory=list)
     completion_message: Message | None = None   # the environment's parse of the completion
     env_messages: list[Message] = field(default_factory=list)
@@ -88,12 +91,16 @@ class RolloutTurn:
 @dataclass(kw_only=True, slots=True)
 class Rollout:
     group_id: int
-    rollout_id: int
+    rollout_id: int                             # sibling index inside the group
     status: RolloutStatus
     turns: list[RolloutTurn] = field(default_factory=list)
     reward: float | None = None                 # filled by the rubric
     reward_breakdown: dict[str, float] = field(default_factory=dict)
     advantage: float | None = None              # filled by the advantage estimator
+
+    @property
+    def num_completion_tokens(self) -> int:
+        return sum(len(t.completion_token_ids) for t in self.turns)
 
 
 @dataclass(kw_only=True, slots=True)
@@ -105,15 +112,18 @@ class RolloutGroup:
 
 @dataclass(kw_only=True, slots=True)
 class TrainingSample:
-    """Packed ``prompt + completion (+ env reply + completion ...)``; the three per-token lists are zero / False
-    outside the completions."""
-    rollout_id: RolloutTurnID
-    min_policy_version: int
-    max_policy_version: int
+    """Packed ``prompt + completion (+ env reply + completion ...)``.  ``loss_mask`` is True on completion tokens;
+    ``logprobs`` and ``advantage`` are zero elsewhere.  All four lists have the same length."""
+    rollout_id: RolloutTurnID                   # turn_id: the turn at which this sample starts
     token_ids: list[int]
     loss_mask: list[bool]
     logprobs: list[float]
     advantage: list[float]
+    min_policy_version: int
+    max_policy_version: int
+
+    def __len__(self) -> int:
+        return len(self.token_ids)
 
 
 @dataclass(frozen=True, slots=True)

@@ -21,7 +21,7 @@ from typing import Any
 
 from torchtitan_b200.config import Configurable
 
-from .types import Message
+from .records import Message
 
 __all__ = ["ChatRenderer", "ParsedResponse", "BridgedPrompt"]
 

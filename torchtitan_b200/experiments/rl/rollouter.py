@@ -23,7 +23,7 @@ from torchtitan_b200.config import Configurable
 from torchtitan_b200.utils.logging import logger
 
 from .environment import MessageEnv, TokenEnv
-from .types import Completion, Rollout, RolloutGroup, RolloutStatus, RolloutTurn, RolloutTurnID
+from .records import Completion, Rollout, RolloutGroup, RolloutStatus, RolloutTurn, RolloutTurnID
 
 __all__ = ["RewardFn", "RubricOutput", "Rubric", "AdvantageEstimator", "Rollouter", "GenerateFn"]
 

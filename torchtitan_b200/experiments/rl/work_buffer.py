@@ -25,7 +25,7 @@ from typing import Any
 from torchtitan_b200.config import Configurable
 
 from . import metrics as m
-from .types import RolloutGroup
+from .records import RolloutGroup
 
 __all__ = ["RolloutGroupWork", "RolloutGroupWorkBuffer"]
 
