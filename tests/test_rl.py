@@ -978,3 +978,31 @@ def test_place_model_keeps_buffer_dtypes():
         return out
 
     assert len(run(go()).token_ids) == 4
+
+
+def test_data_parallel_engine_spreads_requests_and_keeps_sessions_together():
+    from torchtitan_b200.experiments.rl import (DataParallelEngine, GenerationEngine, InterGeneratorRouter,
+                                                IntraGeneratorRouter, LeastLoadedRoutingStrategy, SamplingConfig)
+
+    _, model = _tiny_llama()
+    greedy = SamplingConfig(temperature=0.0, max_tokens=3)
+
+    async def go():
+        ranks = [GenerationEngine(GenerationEngine.Config(threaded=False), model=model) for _ in range(2)]
+        dp = DataParallelEngine(ranks, IntraGeneratorRouter.Config(strategy=LeastLoadedRoutingStrategy.Config()))
+        out = await asyncio.gather(*(dp.generate([i + 1, 2], request_id=f"q{i}", sampling_config=greedy) for i in range(6)))
+        assert all(len(c.token_ids) == 3 for c in out) and dp.router.loads() == [0, 0]
+        assert ranks[0].tokens_generated > 0 and ranks[1].tokens_generated > 0
+        sticky = DataParallelEngine([GenerationEngine(GenerationEngine.Config(threaded=False), model=model) for _ in range(2)])
+        for turn in range(3):
+            await sticky.generate([7, 8, turn + 1], request_id=f"s/turn={turn}", routing_session_id="s", sampling_config=greedy)
+        assert sorted(e.tokens_generated for e in sticky.engines) == [0, 9]          # one rank served the whole session
+        front = InterGeneratorRouter(generators=[dp, sticky])                          # layer one in front of layer two
+        await front.generate([3, 4], request_id="f0", sampling_config=greedy)
+        await front.pull_model_state_dict(4)
+        assert dp.policy_version == 4 and all(e.policy_version == 4 for e in sticky.engines)
+        await front.close_generators()
+
+    run(go())
+    with pytest.raises(ValueError):
+        DataParallelEngine([GenerationEngine(model=model)])

@@ -14,7 +14,7 @@ from .async_controller import AsyncController, AsyncLoopConfig, ValidationConfig
 from .batch_invariance import batch_invariant, enable_batch_invariant_mode
 from .batching import BatchConfig, Batcher, TrainingSampleBuilder
 from .controller import RLConfig, RLController
-from .engine import GenerationEngine, SamplingConfig
+from .engine import DataParallelEngine, GenerationEngine, SamplingConfig
 from .environment import MessageEnv, MessageEnvInit, MessageEnvStep, TokenEnv, TokenEnvOutput
 from .generator import CachedGenerator, SamplingGenerator, WeightSync
 from .losses import PolicyLoss, dapo_loss, group_advantages, grpo_loss, token_logprobs
@@ -32,7 +32,7 @@ from .work_buffer import RolloutGroupWork, RolloutGroupWorkBuffer
 __all__ = [
     "token_logprobs", "grpo_loss", "dapo_loss", "group_advantages", "PolicyLoss", "SamplingGenerator", "CachedGenerator",
     "WeightSync", "SampledResponse", "RolloutBuffer", "RLConfig", "RLController", "batch_invariant",
-    "enable_batch_invariant_mode", "metrics", "GenerationEngine", "SamplingConfig", "ChatRenderer", "MessageEnv",
+    "enable_batch_invariant_mode", "metrics", "GenerationEngine", "DataParallelEngine", "SamplingConfig", "ChatRenderer", "MessageEnv",
     "MessageEnvInit", "MessageEnvStep", "TokenEnv", "TokenEnvOutput", "RewardFn", "Rubric", "RubricOutput",
     "AdvantageEstimator", "Rollouter", "TrainingSampleBuilder", "BatchConfig", "Batcher", "RolloutGroupWork",
     "RolloutGroupWorkBuffer", "RoutingContext", "RoundRobinRoutingStrategy", "LeastLoadedRoutingStrategy",

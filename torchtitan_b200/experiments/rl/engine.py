@@ -34,7 +34,7 @@ from torchtitan_b200.utils.logging import logger
 from . import metrics as m
 from .records import Completion
 
-__all__ = ["SamplingConfig", "GenerationEngine", "place_model_"]
+__all__ = ["SamplingConfig", "GenerationEngine", "DataParallelEngine", "place_model_"]
 
 
 def place_model_(model, device, param_dtype: torch.dtype | None = None):
@@ -297,3 +297,38 @@ class GenerationEngine(Configurable):
             s.loop.call_soon_threadsafe(lambda: s.future.done() or s.future.set_result(done))
         except RuntimeError:                        # the request's event loop is gone
             logger.warning(f"{s.request_id}: completion dropped, its event loop is closed")
+
+
+class DataParallelEngine:
+    """One generator made of several engines holding the same weights (one per GPU): layer two of the routing
+    design.  Each request is placed on a data-parallel rank by an ``IntraGeneratorRouter`` (sticky sessions by
+    default, so the turns of one rollout reuse one rank) and released when it completes; weight pulls and ``close``
+    fan out to every rank.  It has the interface of a single engine, so an ``InterGeneratorRouter`` can sit in front
+    of several of them."""
+
+    def __init__(self, engines: list[GenerationEngine], router_config=None):
+        from .routing import IntraGeneratorRouter
+
+        if len(engines) < 2:
+            raise ValueError("DataParallelEngine needs at least two engines (use the engine itself otherwise)")
+        self.engines = list(engines)
+        self.router = IntraGeneratorRouter(router_config, dp_degree=len(engines))
+
+    @property
+    def policy_version(self) -> int:
+        return min(e.policy_version for e in self.engines)
+
+    async def generate(self, prompt_token_ids: list[int], *, request_id: str, routing_session_id: str | None = None,
+                       sampling_config: SamplingConfig | None = None) -> Completion:
+        rank = self.router.reserve(request_id, routing_session_id=routing_session_id)
+        try:
+            return await self.engines[rank].generate(prompt_token_ids, request_id=request_id,
+                                                     routing_session_id=routing_session_id, sampling_config=sampling_config)
+        finally:
+            self.router.release(request_id)
+
+    async def pull_model_state_dict(self, policy_version: int) -> None:
+        await asyncio.gather(*(e.pull_model_state_dict(policy_version) for e in self.engines))
+
+    async def close(self) -> None:
+        await asyncio.gather(*(e.close() for e in self.engines))
