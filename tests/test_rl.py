@@ -1006,3 +1006,27 @@ def test_data_parallel_engine_spreads_requests_and_keeps_sessions_together():
     run(go())
     with pytest.raises(ValueError):
         DataParallelEngine([GenerationEngine(model=model)])
+
+
+def test_engine_leaves_the_routers_load_counters_alone():
+    """Generation on a model shared with the trainer must not feed the expert-load statistics that drive the
+    trainer's balancing bias."""
+    from torchtitan_b200.experiments.rl import GenerationEngine, SamplingConfig
+    from torchtitan_b200.models import get_model_spec
+
+    spec = get_model_spec("qwen3", "debugmodel_moe_tiny")
+    model = spec.model.build()
+    model.init_states(seed=0)
+    moes = [m_ for m_ in model.modules() if hasattr(m_, "tokens_per_expert_E")]
+    assert moes
+    for m_ in moes:
+        m_.tokens_per_expert_E.fill_(3.0)
+
+    async def go():
+        eng = GenerationEngine(GenerationEngine.Config(threaded=False), model=model)
+        out = await eng.generate([1, 2, 3, 4], request_id="x", sampling_config=SamplingConfig(temperature=0.0, max_tokens=3))
+        await eng.close()
+        return out
+
+    assert len(run(go()).token_ids) == 3
+    assert all(bool((m_.tokens_per_expert_E == 3.0).all()) for m_ in moes)
