@@ -32,6 +32,7 @@ from torchtitan_b200.config import Configurable
 from torchtitan_b200.utils.logging import logger
 
 from . import metrics as m
+from .generator import frozen_router_counters
 from .records import Completion
 
 __all__ = ["SamplingConfig", "GenerationEngine", "DataParallelEngine", "place_model_"]
@@ -243,18 +244,14 @@ class GenerationEngine(Configurable):
         last = torch.tensor(rows, device=dev).cumsum(0) - 1
         was_training = self.model.training
         self.model.eval()
-        # generation must not count towards the routers' load statistics (they steer the trainer's balancing bias)
-        counters = [(mod, mod.tokens_per_expert_E.clone()) for mod in self.model.modules()
-                    if isinstance(getattr(mod, "tokens_per_expert_E", None), torch.Tensor)]
         ctx = AttentionContext(kv_cache=BatchedKVCache([s.cache for s in seqs], rows))
         try:
-            if hasattr(self.model, "output_logits") and getattr(self.model, "tp", None) is None:
-                logits = self.model.output_logits(self.model(tokens, positions, ctx, return_hidden=True)[last])
-            else:
-                logits = self.model(tokens, positions, ctx)[last]
+            with frozen_router_counters(self.model):
+                if hasattr(self.model, "output_logits") and getattr(self.model, "tp", None) is None:
+                    logits = self.model.output_logits(self.model(tokens, positions, ctx, return_hidden=True)[last])
+                else:
+                    logits = self.model(tokens, positions, ctx)[last]
         finally:
-            for mod, saved in counters:
-                mod.tokens_per_expert_E.copy_(saved)
             self.model.train(was_training)
         logits = logits.float()
         now = time.perf_counter()

@@ -8,11 +8,26 @@ process group, and stamps the policy version that the rollout buffer uses to dro
 
 from __future__ import annotations
 
+import contextlib
+
 import torch
 
 from .rollout import SampledResponse
 
-__all__ = ["SamplingGenerator", "CachedGenerator", "WeightSync"]
+__all__ = ["SamplingGenerator", "CachedGenerator", "WeightSync", "frozen_router_counters"]
+
+
+@contextlib.contextmanager
+def frozen_router_counters(model):
+    """Forward passes inside this block do not count towards the MoE routers' expert-load statistics (they drive
+    the trainer's balancing bias, and generated tokens are not training tokens)."""
+    saved = [(m, m.tokens_per_expert_E.clone()) for m in model.modules()
+             if isinstance(getattr(m, "tokens_per_expert_E", None), torch.Tensor)]
+    try:
+        yield
+    finally:
+        for m, t in saved:
+            m.tokens_per_expert_E.copy_(t)
 
 
 class SamplingGenerator:
@@ -29,6 +44,8 @@ class SamplingGenerator:
         dev = next(self.model.parameters()).device
         seq = prompt.to(dev)
         lps = []
+        stack = contextlib.ExitStack()
+        stack.enter_context(frozen_router_counters(self.model))
         for _ in range(max_new_tokens):
             logits = self.model(seq, torch.arange(seq.numel(), device=dev))[-1].float()
             if self.temperature <= 0:
@@ -46,6 +63,7 @@ class SamplingGenerator:
             lps.append(lp)
             if self.eos_id is not None and int(nxt) == self.eos_id:
                 break
+        stack.close()
         n = len(lps)
         return SampledResponse(prompt=prompt.cpu(), response=seq[-n:].cpu(), logprobs=torch.stack(lps).cpu(),
                        policy_version=self.policy_version)
@@ -69,6 +87,8 @@ class CachedGenerator(SamplingGenerator):
         out_tokens, lps = [], []
         was_training = self.model.training
         self.model.eval()
+        stack = contextlib.ExitStack()
+        stack.enter_context(frozen_router_counters(self.model))
         for _ in range(max_new_tokens):
             n = step_in.numel()
             positions = torch.arange(pos0, pos0 + n, device=dev)
@@ -80,6 +100,7 @@ class CachedGenerator(SamplingGenerator):
             step_in = nxt.view(1)
             if self.eos_id is not None and int(nxt) == self.eos_id:
                 break
+        stack.close()
         self.model.train(was_training)
         return SampledResponse(prompt=prompt.cpu(), response=torch.stack(out_tokens).cpu(), logprobs=torch.stack(lps).cpu(),
                        policy_version=self.policy_version)
