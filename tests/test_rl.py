@@ -754,6 +754,10 @@ def test_rl_job_config_validation():
     assert two.generator.threaded and two.controller.async_loop.max_offpolicy_steps >= 3
     dapo = reg.rl_dapo_qwen3_4b_math_8k()
     assert dapo.ratio_clip_high > dapo.ratio_clip_low and dapo.controller.rollouter.advantage.should_std_normalize
+    tp = reg.rl_grpo_debug_alphabet_sort()
+    tp.trainer.parallelism.tensor_parallel_degree = 2
+    with pytest.raises(ValueError, match="rank 0 only"):
+        tp.validate()
     bad = reg.rl_grpo_debug_alphabet_sort()
     bad.num_generators = 2
     with pytest.raises(ValueError, match="share_weights"):

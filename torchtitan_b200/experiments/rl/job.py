@@ -111,6 +111,10 @@ class RLJob(Configurable):
                 raise ValueError("share_weights needs the resident parameter layout (the generator reads full weights)")
             if t.parallelism.pipeline_parallel_degree > 1 or t.parallelism.context_parallel_degree > 1:
                 raise ValueError("the RL trainer supports data and tensor parallelism")
+            if self.share_weights and (t.parallelism.tensor_parallel_degree > 1 or t.parallelism.expert_parallel_degree > 1):
+                # the generator's forward runs on rank 0 alone; tensor- or expert-parallel layers need every rank in it
+                raise ValueError("share_weights generates on rank 0 only, which a tensor- or expert-parallel model cannot "
+                                 "do; use own-copy generators (share_weights = False) with these layouts")
             b = self.controller.async_loop.batcher.batch
             sp = t.parallelism.tensor_parallel_degree if t.parallelism.enable_sequence_parallel else 1
             if b.seq_len * b.local_batch_size % max(sp, 1):
