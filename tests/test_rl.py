@@ -756,7 +756,7 @@ def test_rl_job_config_validation():
     assert dapo.ratio_clip_high > dapo.ratio_clip_low and dapo.controller.rollouter.advantage.should_std_normalize
     tp = reg.rl_grpo_debug_alphabet_sort()
     tp.trainer.parallelism.tensor_parallel_degree = 2
-    with pytest.raises(ValueError, match="rank 0 only"):
+    with pytest.raises(ValueError, match="data parallelism"):
         tp.validate()
     bad = reg.rl_grpo_debug_alphabet_sort()
     bad.num_generators = 2

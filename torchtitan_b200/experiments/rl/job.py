@@ -107,19 +107,17 @@ class RLJob(Configurable):
                 raise ValueError(f"num_generators must be >= 1, got {self.num_generators}")
             if self.share_weights and self.num_generators != 1:
                 raise ValueError("share_weights runs exactly one generator on the training model")
-            if self.share_weights and t.parallelism.fsdp_reshard_after_forward == "always":
-                raise ValueError("share_weights needs the resident parameter layout (the generator reads full weights)")
-            if t.parallelism.pipeline_parallel_degree > 1 or t.parallelism.context_parallel_degree > 1:
-                raise ValueError("the RL trainer supports data and tensor parallelism")
-            if self.share_weights and (t.parallelism.tensor_parallel_degree > 1 or t.parallelism.expert_parallel_degree > 1):
-                # the generator's forward runs on rank 0 alone; tensor- or expert-parallel layers need every rank in it
-                raise ValueError("share_weights generates on rank 0 only, which a tensor- or expert-parallel model cannot "
-                                 "do; use own-copy generators (share_weights = False) with these layouts")
+            if t.parallelism.fsdp_reshard_after_forward == "always":
+                raise ValueError("the RL job needs the resident parameter layout: the generators read (or copy) the "
+                                 "trainer's full weights between optimizer steps")
+            par = t.parallelism
+            if max(par.pipeline_parallel_degree, par.context_parallel_degree, par.tensor_parallel_degree,
+                   par.expert_parallel_degree) > 1:
+                # the generators run the whole model on one device: with shared weights rank 0 generates alone (layers
+                # that need their tensor- / expert-parallel peers cannot), with own copies the pull copies full tensors
+                raise ValueError("the RL job trains with data parallelism (FSDP / HSDP); tensor, expert, context and "
+                                 "pipeline parallelism are not supported here")
             b = self.controller.async_loop.batcher.batch
-            sp = t.parallelism.tensor_parallel_degree if t.parallelism.enable_sequence_parallel else 1
-            if b.seq_len * b.local_batch_size % max(sp, 1):
-                raise ValueError(f"tokens per microbatch ({b.seq_len * b.local_batch_size}) must divide by the "
-                                 f"sequence-parallel degree {sp}")
             # the batcher's grid decides the training shapes
             t.training.max_context_length = b.seq_len
             t.training.num_tokens_per_microbatch_per_dp_rank = b.seq_len * b.local_batch_size
