@@ -134,6 +134,9 @@ class RLJob(Configurable):
 
         self.config = config
         self.forge = forge = ForgeEngine(config.trainer)
+        if any(getattr(e, "sharded_params", False) for e in forge.engines):
+            raise ValueError("the sharding engine chose the sharded parameter layout for this model; the RL job needs "
+                             "full weights between steps: set parallelism.fsdp_reshard_after_forward = never")
         self.rank = dist.get_rank() if dist.is_initialized() else 0
         cls = _LeaderTrainer if dist.is_initialized() and dist.get_world_size() > 1 and self.rank == 0 else PolicyTrainer
         self.trainer = cls(model=forge.model, engine=forge.engines[0], optimizers=forge.optimizers,
