@@ -11,7 +11,8 @@ config and the controller's.  Placement:
   ``generator_devices[i]`` (other GPUs of the node), running in worker threads while the trainer trains; a pull
   copies the trainer's parameters device to device.
 
-With more than one training rank the controller lives on rank 0; it announces every trainer call to the other
+The trainer is data-parallel (FSDP / HSDP) with the resident parameter layout; other layouts are refused at start,
+because a generator runs the whole model on one device.  With more than one training rank the controller lives on rank 0; it announces every trainer call to the other
 ranks (``_LeaderTrainer`` / ``follow``), which run the same call on their shard of the microbatch grid.
 
 Parity: torchtitan/experiments/rl/train.py:46-314 and controller.py:261-520 (setup: Monarch proc meshes for the
