@@ -21,7 +21,7 @@ import math
 import random
 import re
 import string
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 
 from torchtitan_b200.config import Configurable
 from torchtitan_b200.utils.logging import logger
