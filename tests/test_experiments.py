@@ -682,3 +682,16 @@ def test_hf_backend_train_entry(tmp_path):
         assert len(got[name]) in (3, 5) and all(math.isfinite(x) for x in got[name]), (name, got[name])
     assert torch.allclose(torch.tensor(got["one"]), torch.tensor(got["tp2"]), atol=2e-3), (got["one"], got["tp2"])
     assert got["one"][0] != got["one"][-1]
+
+
+def test_compile_passes_from_the_command_line():
+    """``--compile.passes`` on the ordinary trainer's command line folds the graph trainer's pass names into the
+    config at validation; unknown names are refused."""
+    from torchtitan_b200.config import ConfigManager
+
+    cfg = ConfigManager().parse_args(["--module", "llama3", "--config", "llama3_debugmodel", "--compile.passes",
+                                      "full_remat,fsdp_reshard,ep_overlap,regional_inductor"])
+    assert cfg.activation_checkpoint.mode == "full" and cfg.parallelism.fsdp_reshard_after_forward == "always"
+    assert cfg.parallelism.ep_comm == "nvlink"
+    with pytest.raises(ValueError, match="unknown graph_trainer pass"):
+        ConfigManager().parse_args(["--module", "llama3", "--config", "llama3_debugmodel", "--compile.passes", "nonsense"])

@@ -109,6 +109,10 @@ class CompileConfig:
     enable_async_tensor_parallel: bool = False
     components: list[str] = field(default_factory=lambda: ["model", "loss"])
     backend: str = "inductor"
+    passes: list[str] = field(default_factory=list)
+    """Pass names of the reference's graph trainer (``cudagraph``, ``fsdp_reshard``, ``async_tp``, ``ep_overlap``,
+    ``cpu_offload``, ``selective_remat``, ``full_remat``, ``precompile`` ...): each switches on the property of this
+    framework that achieves it (``experiments/graph_trainer``)."""
 
 
 @dataclass(kw_only=True, slots=True)

@@ -32,14 +32,16 @@ from __future__ import annotations
 from torchtitan_b200.trainer import Trainer
 from torchtitan_b200.utils.logging import logger
 
-__all__ = ["GraphTrainer", "apply_passes", "KNOWN_PASSES"]
+__all__ = ["GraphTrainer", "apply_passes", "KNOWN_PASSES", "precompile"]
 
 KNOWN_PASSES = ("cudagraph", "fsdp_overlap", "fsdp_reshard", "async_tp", "ep_overlap", "cpu_offload", "selective_remat",
                 "full_remat", "precompile", "regional_inductor", "full_inductor")
 
 
-def apply_passes(config: "Trainer.Config", passes: list[str]) -> list[str]:
-    """Fold the pass list into ``config`` (in place); returns the passes that changed something."""
+def apply_passes(config: "Trainer.Config", passes: list[str], *, run_precompile: bool = True) -> list[str]:
+    """Fold the pass list into ``config`` (in place); returns the passes that changed something.  With
+    ``run_precompile=False`` the ``precompile`` pass is only recorded (the caller builds once the process group is
+    up, so that rank 0 builds and the others wait)."""
     done = []
     for name in passes:
         if name not in KNOWN_PASSES:
@@ -59,7 +61,8 @@ def apply_passes(config: "Trainer.Config", passes: list[str]) -> list[str]:
         elif name == "full_remat":
             config.activation_checkpoint.mode = "full"
         elif name == "precompile":
-            _precompile()
+            if run_precompile:
+                precompile()
         elif name in ("regional_inductor", "full_inductor"):
             logger.warning(f"graph_trainer pass '{name}' is accepted for compatibility: this framework runs hand-written "
                            "kernels, there is no Inductor path")
@@ -70,7 +73,7 @@ def apply_passes(config: "Trainer.Config", passes: list[str]) -> list[str]:
     return done
 
 
-def _precompile() -> None:
+def precompile() -> None:
     """Build the extension on rank 0 (if stale), then let everybody load the same shared object."""
     import torch.distributed as dist
 

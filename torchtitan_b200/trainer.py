@@ -102,6 +102,10 @@ class Trainer(Configurable):
                 raise ValueError("training.max_context_length must be positive")
             if p.pipeline_parallel_degree > 1 and p.num_pp_microbatches < 1:
                 raise ValueError("parallelism.num_pp_microbatches must be >= 1")
+            if self.compile.passes:
+                from torchtitan_b200.experiments.graph_trainer import apply_passes
+
+                logger.info(f"compile.passes: {apply_passes(self, list(self.compile.passes), run_precompile=False)}")
             if self.compile.enable:
                 logger.warning("compile.enable is accepted for compatibility; this framework runs hand-written "
                                "kernels and CUDA graphs instead of a tracing compiler")
@@ -145,6 +149,10 @@ class Trainer(Configurable):
         rank = dist.get_rank() if dist.is_initialized() else 0
         self.pdims = ParallelDims.from_config(c.parallelism, world, rank).build()
         pd = self.pdims
+        if "precompile" in c.compile.passes:       # rank 0 builds the extension, the others wait and load it
+            from torchtitan_b200.experiments.graph_trainer import precompile
+
+            precompile()
         div = pd.seq_len_divisor
         if c.training.num_tokens_per_microbatch_per_dp_rank % div:
             raise ValueError(f"tokens per microbatch ({c.training.num_tokens_per_microbatch_per_dp_rank}) must be "
