@@ -1034,3 +1034,25 @@ def test_engine_leaves_the_routers_load_counters_alone():
 
     assert len(run(go()).token_ids) == 3
     assert all(bool((m_.tokens_per_expert_E == 3.0).all()) for m_ in moes)
+
+
+def test_engine_stops_at_the_models_context():
+    from torchtitan_b200.experiments.rl import GenerationEngine, SamplingConfig
+
+    _, model = _tiny_llama()
+    ctx = model.config.max_context_length
+    model.config.max_context_length = 12           # pretend the tables end here
+
+    async def go():
+        eng = GenerationEngine(GenerationEngine.Config(threaded=False), model=model)
+        out = await eng.generate(list(range(1, 9)), request_id="a", sampling_config=SamplingConfig(temperature=0.0, max_tokens=50))
+        with pytest.raises(ValueError, match="context"):
+            await eng.generate(list(range(1, 14)), request_id="b")
+        await eng.close()
+        return out
+
+    try:
+        out = run(go())
+    finally:
+        model.config.max_context_length = ctx
+    assert out.finish_reason == "length" and len(out.token_ids) == 12 - 8      # rows 0..11 were fed or produced

@@ -116,6 +116,8 @@ class GenerationEngine(Configurable):
                  weight_source: Callable[["GenerationEngine"], None] | None = None):
         self.config = config or GenerationEngine.Config()
         self.model, self.eos_id, self.weight_source = model, eos_id, weight_source
+        # positions beyond the rotary tables are an error in the kernels: sequences stop there ("length")
+        self.max_context = getattr(getattr(model, "config", None), "max_context_length", None)
         self.policy_version = 0
         self._waiting: list[_Seq] = []
         self._running: list[_Seq] = []
@@ -137,6 +139,9 @@ class GenerationEngine(Configurable):
                               min_policy_version=self.policy_version, max_policy_version=self.policy_version)
         if not prompt_token_ids:
             raise ValueError(f"{request_id}: empty prompt")
+        if self.max_context and len(prompt_token_ids) >= self.max_context:
+            raise ValueError(f"{request_id}: the prompt has {len(prompt_token_ids)} tokens, the model's context is "
+                             f"{self.max_context}")
         s = sampling_config or self.config.sampling
         loop = asyncio.get_running_loop()
         seq = _Seq(request_id=request_id, pending=list(prompt_token_ids), sampling=s, future=loop.create_future(),
@@ -284,6 +289,8 @@ class GenerationEngine(Configurable):
         for stop in sc.stop_sequences:
             if stop and s.out_ids[-len(stop):] == stop:
                 return "stop"
+        if self.max_context and s.pos + 1 >= self.max_context:      # the next row would be past the context
+            return "length"
         return "length" if len(s.out_ids) >= sc.max_tokens else None
 
     def _finish(self, s: _Seq, reason: str) -> None:
