@@ -748,6 +748,7 @@ def test_rl_job_config_validation():
     cfg = ConfigManager().parse_args(_job_args("/tmp/unused"))
     assert cfg.trainer.training.max_context_length == 512 and cfg.trainer.training.num_tokens_per_microbatch_per_dp_rank == 1024
     assert cfg.generator.threaded is False and cfg.controller.trainer_in_thread is False     # shared weights: no threads
+    assert cfg.controller.rollouter.token_env.max_rollout_tokens == 511
     assert cfg.trainer.model.converters == ["lm_head_cast"]
     two = reg.rl_grpo_qwen3_0_6b_async_two_generators()
     two.validate()

@@ -124,6 +124,11 @@ class RLJob(Configurable):
             t.training.num_tokens_per_microbatch_per_dp_rank = b.seq_len * b.local_batch_size
             t.training.num_tokens_per_train_step = -1
             t.dataloader.dataset = "synthetic"
+            env = self.controller.rollouter.token_env
+            if env.max_rollout_tokens is None:
+                # a conversation that no longer fits a packed row ends as "truncated_prompt_too_long" instead of failing
+                # in the generator
+                env.max_rollout_tokens = b.seq_len - 1
             if self.share_weights:
                 self.generator.threaded = False
                 self.controller.trainer_in_thread = False
