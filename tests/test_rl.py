@@ -559,6 +559,7 @@ def _rl_parts(tmp_path, *, steps, prompts_per_step=2, group=4, drop_flat=False, 
             ids = rollout.turns[-1].completion_token_ids if rollout.turns else []
             return sum(t < 1024 for t in ids) / max(len(ids), 1)
 
+    torch.manual_seed(0)                        # sampling draws from the global generator
     spec, _ = _tiny_llama()
     cfg = Trainer.Config()
     cfg.training.mixed_precision_param = "float32"
